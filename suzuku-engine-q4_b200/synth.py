@@ -1,0 +1,85 @@
+"""Seeded synthetic inputs with the shapes and value distributions of the
+benchmark configurations (no model file or dataset is involved).
+
+IQ3_S super-block (110 bytes, 256 weights; reference layout src/q4_quant.c:384-394):
+fp16 d = |N(0,1)| * 2^-6; qs / qh / sign bytes uniform random; the four scale
+bytes uniform random (two uniform 4-bit sub-scales each).  This mirrors the
+reference tests' rule "random payload, sane scale" (src/q4_test.c:250-262).
+"""
+import numpy as np
+
+IQ3S_BLOCK = 110
+QK_K = 256
+
+
+def iq3s_row_bytes(ncols):
+    assert ncols % QK_K == 0
+    return ncols // QK_K * IQ3S_BLOCK
+
+
+def expert_pack_bytes(n_embd, n_ff):
+    """gate [n_ff x n_embd] | up [n_ff x n_embd] | down [n_embd x n_ff]
+    (reference pack order: src/q4_expert.c:962-982)."""
+    return 2 * n_ff * iq3s_row_bytes(n_embd) + n_embd * iq3s_row_bytes(n_ff)
+
+
+def iq3s_blocks(rng, n_blocks):
+    """n_blocks random super-blocks -> uint8 [n_blocks, 110]."""
+    b = rng.integers(0, 256, size=(n_blocks, IQ3S_BLOCK), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal(n_blocks)) * 2.0 ** -6).astype(np.float16)
+    b[:, 0:2] = d.view(np.uint8).reshape(n_blocks, 2)
+    return b
+
+
+def expert_packs(rng, n, n_embd, n_ff):
+    """n packed experts -> uint8 [n, pack_bytes]."""
+    pb = expert_pack_bytes(n_embd, n_ff)
+    assert pb % IQ3S_BLOCK == 0
+    return iq3s_blocks(rng, n * (pb // IQ3S_BLOCK)).reshape(n, pb)
+
+
+def layer(seed, n_expert, n_embd, n_ff):
+    """One MoE layer: routed packs, shared pack, router, norm weight."""
+    rng = np.random.default_rng(seed)
+    return {
+        "experts": expert_packs(rng, n_expert, n_embd, n_ff),
+        "shared": expert_packs(rng, 1, n_embd, n_ff)[0],
+        "router": (rng.standard_normal((n_expert, n_embd)) * 0.02).astype(np.float32),
+        "norm_w": (1.0 + 0.1 * rng.standard_normal(n_embd)).astype(np.float32),
+    }
+
+
+def hidden(seed, n_tok, n_embd):
+    rng = np.random.default_rng(seed)
+    return rng.standard_normal((n_tok, n_embd)).astype(np.float32)
+
+
+def zipf_bias(n_expert, s=1.1):
+    """Additive router-logit bias that skews expert popularity: the log of a
+    Zipf(s) probability mass over expert rank (expert 0 the most popular)."""
+    r = np.arange(1, n_expert + 1, dtype=np.float64)
+    p = r ** -s
+    p /= p.sum()
+    return np.log(p).astype(np.float32)
+
+
+class XorShift64:
+    """The generator the reference's tests use for weight bytes
+    (src/q4_test.c:250-254): x ^= x<<13; x ^= x>>7; x ^= x<<17."""
+
+    def __init__(self, seed):
+        self.s = seed & 0xFFFFFFFFFFFFFFFF
+
+    def next(self):
+        s = self.s
+        s ^= (s << 13) & 0xFFFFFFFFFFFFFFFF
+        s ^= s >> 7
+        s ^= (s << 17) & 0xFFFFFFFFFFFFFFFF
+        self.s = s
+        return s
+
+    def bytes(self, n):
+        out = np.empty(n, np.uint8)
+        for i in range(n):
+            out[i] = self.next() & 0xFF
+        return out
