@@ -1,0 +1,181 @@
+/* q4cuda: B200 (sm_100a) device layer for the routed-expert MoE feed-forward path
+ * with IQ3_S weights and 8-bit activations.
+ *
+ * This header is the drop-in boundary.  The functions named q4_hip_* / q4_mmq_*
+ * keep the names, argument meaning and error behaviour of the reference engine's
+ * device C ABI (src/q4.h:837-1512 of shoutliberte/Suzuku-Engine-q4; each block
+ * below cites the declaration it replaces), so the engine's MoE orchestration
+ * (src/q4_moe.c) links against libq4cuda.so unchanged.  The q4_cuda_* functions
+ * are additions: fused forms of call sequences the engine issues today.
+ *
+ * Conventions (same as the reference, src/q4_rocm.cu:5433-5438):
+ *  - every operation returns bool: true = enqueued; false = NOTHING was enqueued
+ *    (bad shape, unsupported type, library not initialised), so a caller may take
+ *    another path without double-counting work;
+ *  - d_* pointers are device pointers owned by the caller; everything is enqueued
+ *    on one library-owned stream (q4_hip_stream) and nothing synchronises unless
+ *    its comment says so;
+ *  - nothing allocates after q4_hip_init()/q4_hip_moe_scratch_warm(), so every
+ *    compute entry point may be captured in a CUDA graph (q4_hip_graph_begin);
+ *  - there is no CPU fallback: without a usable sm_100 GPU q4_hip_init() returns
+ *    false and every other entry point refuses.
+ *
+ * Only IQ3_S (type id 21) expert tensors and F32 (type id 0) router tensors are
+ * accepted; q4_hip_moe_tok_ok() and q4_mmq_supported() answer for a given shape.
+ */
+#ifndef Q4CUDA_H
+#define Q4CUDA_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ggml type ids used on this path (src/q4.h:20-39). */
+#define Q4_T_F32 0u
+#define Q4_T_IQ3_S 21u
+
+/* ---------------- lifecycle and memory (src/q4.h:1029-1031,1397-1400,1511-1512,
+ * 1233-1235,1232,1359) ---------------- */
+bool q4_hip_init(void);
+void q4_hip_shutdown(void);
+bool q4_hip_ok(void);
+void *q4_hip_stream(void);          /* the compute stream, a cudaStream_t */
+void q4_hip_sync(void);             /* drain the device */
+bool q4_hip_stream_sync(void);      /* drain the compute stream */
+void *q4_hip_malloc(size_t n);
+void q4_hip_free(void *p);
+bool q4_hip_h2d(void *d, const void *h, size_t n);        /* synchronous */
+bool q4_hip_d2h(void *h, const void *d, size_t n);        /* synchronous, after the compute stream */
+bool q4_hip_h2d_async(void *d, const void *h, uint64_t n);
+bool q4_hip_d2h_async(void *h, const void *d, uint64_t n);
+bool q4_hip_fill(float *d, float v, uint64_t n);
+bool q4_hip_copy_async(float *d, const float *s, uint64_t n);
+uint64_t q4_hip_vram_free(void);
+
+/* ---------------- expert arenas (src/q4.h:842-851,1402-1413) ----------------
+ * A fixed-stride device array of packed experts, pack = gate rows | up rows |
+ * down rows (src/q4_expert.c:962-982).  Arena 0 is the main model; the unmarked
+ * names address arena 0.  Up to 4 arenas. */
+bool q4_hip_experts_alloc_a(int arena, uint32_t n_slots, uint64_t slot_bytes);
+void q4_hip_experts_free_a(int arena);
+uint32_t q4_hip_experts_n_a(int arena);
+bool q4_hip_experts_put_a(int arena, uint32_t slot, const uint8_t *host, uint64_t n);
+bool q4_hip_experts_put_async_a(int arena, uint32_t slot, const uint8_t *host, uint64_t n);
+const uint8_t *q4_hip_experts_dev_a(int arena, uint32_t slot);
+const uint8_t *q4_hip_experts_base_a(int arena);
+uint64_t q4_hip_experts_stride_a(int arena);
+bool q4_hip_experts_alloc(uint32_t n_slots, uint64_t slot_bytes);
+void q4_hip_experts_free(void);
+uint32_t q4_hip_experts_n(void);
+bool q4_hip_experts_put(uint32_t slot, const uint8_t *host, uint64_t n);
+bool q4_hip_experts_put_async(uint32_t slot, const uint8_t *host, uint64_t n);
+const uint8_t *q4_hip_experts_dev(uint32_t slot);
+void q4_hip_copy_wait(void);        /* host-waits for queued expert uploads */
+
+/* ---------------- graphs (src/q4.h:1227-1231) ---------------- */
+int q4_hip_graph_begin(void);       /* 1 = capturing, 0 = refused */
+void *q4_hip_graph_end(void);       /* executable graph or NULL */
+uint32_t q4_hip_graph_nodes(void *exec);
+bool q4_hip_graph_launch(void *exec);
+void q4_hip_graph_free(void *exec);
+
+/* ---------------- routed experts, one token (src/q4.h:898-899,930-935,
+ * 1296-1311,956-958) ----------------
+ * y[r] += sum_e wts[e] * down_e . Q8(silu(gate_e . Q8(x)) * (up_e . Q8(x)))
+ * for the n experts at base + slots[e]*stride (+og/ou/od for gate/up/down).
+ * x is quantised per 32 values to int8 ("Q8-A": scale amax/127, round to
+ * nearest even; reference CPU path src/q4_cpuexp.c:605-637); h likewise, per
+ * expert.  d_h receives the n*n_ff fp32 hidden rows.  d_h2/d_down are unused
+ * scratch of the reference's unfused fallback and may be NULL.  n <= 64.
+ * exec: slots/wts are HOST arrays.  exec_dev: device arrays and a device
+ * count.  stage + exec_staged: the host writes the list into mapped memory,
+ * the launch reads it at run time (graph replay with new routing). */
+bool q4_hip_moe_tok_ok(uint32_t gt, uint32_t ut, uint32_t dt, uint32_t in_dim, uint32_t n_ff);
+bool q4_hip_moe_exec(const uint8_t *base, uint64_t stride, const int32_t *slots,
+                     const float *wts, uint32_t n, uint32_t gt, uint64_t og, uint32_t ut,
+                     uint64_t ou, uint32_t dt, uint64_t od, const float *d_x, float *d_h,
+                     float *d_h2, float *d_down, float *d_y, uint32_t n_ff, uint32_t in_dim,
+                     uint32_t n_embd);
+bool q4_hip_moe_exec_dev(const uint8_t *base, uint64_t stride, const int32_t *d_es,
+                         const float *d_ew, const int32_t *d_nhit, uint32_t gt, uint64_t og,
+                         uint32_t ut, uint64_t ou, uint32_t dt, uint64_t od, const float *d_x,
+                         float *d_h, float *d_h2, float *d_down, float *d_y, uint32_t n_ff,
+                         uint32_t in_dim, uint32_t n_embd);
+bool q4_hip_moe_stage(const int32_t *slots, const float *wts, uint32_t n);
+bool q4_hip_moe_exec_staged(const uint8_t *base, uint64_t stride, uint32_t gt, uint64_t og,
+                            uint32_t ut, uint64_t ou, uint32_t dt, uint64_t od,
+                            const float *d_x, float *d_h, float *d_h2, float *d_down,
+                            float *d_y, uint32_t n_ff, uint32_t in_dim, uint32_t n_embd);
+void q4_hip_moe_scratch_warm(void);
+
+/* ---------------- router and norm (src/q4.h:1414-1418,1360-1363,1075-1080) ------- */
+/* softmax over n logits, top-k on strict '>' (equal values keep the lower
+ * index), weights renormalised over the k picks (src/q4_quant.c:715-755).
+ * n <= 1024, k <= 64.  The first form copies the result out and syncs. */
+bool q4_hip_softmax_topk(const float *d_logits, uint32_t n, uint32_t k, int32_t *h_ids,
+                         float *h_wts);
+bool q4_hip_softmax_topk_launch(const float *d_logits, uint32_t n, uint32_t k, int32_t *d_ids,
+                                float *d_wts);
+/* y = x * rsqrt(mean(x^2) + eps) * w over hc groups of n_embd (w may be NULL). */
+bool q4_hip_grouped_rms(const float *x, const float *w, float *y, uint32_t n_embd, uint32_t hc,
+                        float eps);
+bool q4_hip_grouped_rms_n(const float *x, const float *w, float *y, uint32_t n_embd,
+                          uint32_t hc, float eps, uint32_t n_tok);
+/* d_y = scale * W d_x, all device pointers, overwrites y.  F32 or IQ3_S rows. */
+bool q4_hip_gemv_dd(uint32_t ggml_type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                    const float *d_x, float *d_y, float scale);
+bool q4_hip_gemv_dd_n(uint32_t ggml_type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                      const float *d_x, float *d_y, float scale, uint32_t n_batch);
+
+/* ---------------- additions (no single counterpart in the reference) ------------ */
+
+/* Stage tests: the building blocks of the expert kernels, exposed so that the
+ * integer stages can be compared bit for bit with the CPU path.
+ * q4_cuda_quant8: per 32 floats -> int8 q[n], scale d[n/32], sum bs[n/32]
+ *   (src/q4_cpuexp.c:605-637 computes the same three).
+ * q4_cuda_iq3s_dequant: rows*ncols weights -> fp32 (src/q4_quant.c:384-422).
+ * q4_cuda_iq3s_idot: I[r][g] = integer dot of row r's 32-group g with q
+ *   (src/q4_cpuexp.c:694-699,855-892 before the sub-scale multiply). */
+bool q4_cuda_quant8(const float *d_x, uint64_t n, int8_t *d_q, float *d_d, int32_t *d_bs);
+bool q4_cuda_iq3s_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out);
+bool q4_cuda_iq3s_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const int8_t *d_q,
+                       int32_t *d_I);
+
+/* One MoE layer for one token, every stage on the device with no host round
+ * trip: RMSNorm -> router GEMV -> softmax/top-k -> k routed experts + the shared
+ * expert -> y.  Replaces the sequence the engine issues in q4_moe_layer_dev
+ * (src/q4_moe.c:2077-2133: gemv_dd, fill, softmax_topk, moe_exec, shared
+ * gate/up/silu_mul/down, axpy).
+ *   base/stride/og/ou/od: expert arena addressing as in q4_hip_moe_exec;
+ *   routed expert id e lives in slot e, the shared expert in slot shared_slot
+ *   (negative = no shared expert);
+ *   d_x: n_embd fp32 hidden state; d_norm_w may be NULL (no norm weight);
+ *   d_router: [n_expert][n_embd] fp32;
+ *   d_y: n_embd fp32, OVERWRITTEN;
+ *   d_ids/d_wts (topk entries, may be NULL) receive the routing.
+ * n_embd % 256 == 0, n_ff % 256 == 0, n_expert <= 1024, topk <= 63. */
+bool q4_cuda_moe_decode(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou,
+                        uint64_t od, int32_t shared_slot, const float *d_x,
+                        const float *d_norm_w, float eps, const float *d_router,
+                        uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
+                        float *d_y, int32_t *d_ids, float *d_wts);
+
+/* Device-side timing on the compute stream, for benchmarks: records an event
+ * pair around whatever is enqueued between begin and end; ms() waits for the
+ * end event. */
+bool q4_cuda_timer_begin(void);
+bool q4_cuda_timer_end(void);
+float q4_cuda_timer_ms(void);
+/* Number of kernels this library has launched since init (its own count). */
+uint64_t q4_cuda_launch_count(void);
+/* Last error word written by a kernel's self-check (0 = none); clears it. */
+uint32_t q4_cuda_device_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,104 @@
+"""ctypes binding of libq4cuda.so: one Python attribute per symbol declared in
+include/q4cuda.h, with the argument types spelled out.
+
+The library is the product; this module only loads it.  There is no fallback:
+if the shared object is missing, `load()` raises.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libq4cuda.so")
+
+vp = C.c_void_p
+u8p = C.c_void_p
+u32 = C.c_uint32
+u64 = C.c_uint64
+i32 = C.c_int32
+f32 = C.c_float
+b = C.c_bool
+sz = C.c_size_t
+
+# name -> (restype, [argtypes]); kept in the order of include/q4cuda.h
+SIGNATURES = {
+    "q4_hip_init": (b, []),
+    "q4_hip_shutdown": (None, []),
+    "q4_hip_ok": (b, []),
+    "q4_hip_stream": (vp, []),
+    "q4_hip_sync": (None, []),
+    "q4_hip_stream_sync": (b, []),
+    "q4_hip_malloc": (vp, [sz]),
+    "q4_hip_free": (None, [vp]),
+    "q4_hip_h2d": (b, [vp, vp, sz]),
+    "q4_hip_d2h": (b, [vp, vp, sz]),
+    "q4_hip_h2d_async": (b, [vp, vp, u64]),
+    "q4_hip_d2h_async": (b, [vp, vp, u64]),
+    "q4_hip_fill": (b, [vp, f32, u64]),
+    "q4_hip_copy_async": (b, [vp, vp, u64]),
+    "q4_hip_vram_free": (u64, []),
+    "q4_hip_experts_alloc_a": (b, [C.c_int, u32, u64]),
+    "q4_hip_experts_free_a": (None, [C.c_int]),
+    "q4_hip_experts_n_a": (u32, [C.c_int]),
+    "q4_hip_experts_put_a": (b, [C.c_int, u32, vp, u64]),
+    "q4_hip_experts_put_async_a": (b, [C.c_int, u32, vp, u64]),
+    "q4_hip_experts_dev_a": (vp, [C.c_int, u32]),
+    "q4_hip_experts_base_a": (vp, [C.c_int]),
+    "q4_hip_experts_stride_a": (u64, [C.c_int]),
+    "q4_hip_experts_alloc": (b, [u32, u64]),
+    "q4_hip_experts_free": (None, []),
+    "q4_hip_experts_n": (u32, []),
+    "q4_hip_experts_put": (b, [u32, vp, u64]),
+    "q4_hip_experts_put_async": (b, [u32, vp, u64]),
+    "q4_hip_experts_dev": (vp, [u32]),
+    "q4_hip_copy_wait": (None, []),
+    "q4_hip_graph_begin": (C.c_int, []),
+    "q4_hip_graph_end": (vp, []),
+    "q4_hip_graph_nodes": (u32, [vp]),
+    "q4_hip_graph_launch": (b, [vp]),
+    "q4_hip_graph_free": (None, [vp]),
+    "q4_hip_moe_tok_ok": (b, [u32, u32, u32, u32, u32]),
+    "q4_hip_moe_exec": (b, [vp, u64, vp, vp, u32, u32, u64, u32, u64, u32, u64, vp, vp, vp, vp,
+                            vp, u32, u32, u32]),
+    "q4_hip_moe_exec_dev": (b, [vp, u64, vp, vp, vp, u32, u64, u32, u64, u32, u64, vp, vp, vp,
+                                vp, vp, u32, u32, u32]),
+    "q4_hip_moe_stage": (b, [vp, vp, u32]),
+    "q4_hip_moe_exec_staged": (b, [vp, u64, u32, u64, u32, u64, u32, u64, vp, vp, vp, vp, vp,
+                                   u32, u32, u32]),
+    "q4_hip_moe_scratch_warm": (None, []),
+    "q4_hip_softmax_topk": (b, [vp, u32, u32, vp, vp]),
+    "q4_hip_softmax_topk_launch": (b, [vp, u32, u32, vp, vp]),
+    "q4_hip_grouped_rms": (b, [vp, vp, vp, u32, u32, f32]),
+    "q4_hip_grouped_rms_n": (b, [vp, vp, vp, u32, u32, f32, u32]),
+    "q4_hip_gemv_dd": (b, [u32, vp, u64, u64, vp, vp, f32]),
+    "q4_hip_gemv_dd_n": (b, [u32, vp, u64, u64, vp, vp, f32, u32]),
+    "q4_cuda_quant8": (b, [vp, u64, vp, vp, vp]),
+    "q4_cuda_iq3s_dequant": (b, [vp, u64, u64, vp]),
+    "q4_cuda_iq3s_idot": (b, [vp, u64, u64, vp, vp]),
+    "q4_cuda_moe_decode": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32, u32,
+                               vp, vp, vp]),
+    "q4_cuda_timer_begin": (b, []),
+    "q4_cuda_timer_end": (b, []),
+    "q4_cuda_timer_ms": (f32, []),
+    "q4_cuda_launch_count": (u64, []),
+    "q4_cuda_device_error": (u32, []),
+}
+
+_lib = None
+
+
+def load():
+    """dlopen the library and attach signatures.  Raises if it is not built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            "libq4cuda.so is not built (run `python suzuku-engine-q4_b200/build.py`); "
+            "this package has no other compute path")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError = header and library disagree
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib

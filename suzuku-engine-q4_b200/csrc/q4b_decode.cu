@@ -1,0 +1,624 @@
+// Decode-path kernels on the engine's packed-expert layout (110-byte IQ3_S
+// super-blocks, any device pointer): activation quantiser, RMSNorm, router,
+// gate/up + SwiGLU rows, down rows + weighted combine.  These serve the
+// fine-grained entry points (q4_hip_moe_exec and friends) and the stage tests.
+//
+// Reference counterparts: xq8_k (src/q4_rocm.cu:5149), wmoe_iq3_gu_q8
+// (:3912-3989), wmoe_iq3_ya_q8 (:4081-4120), softmax_topk_k (:12703),
+// grouped_rms_k (:11285); arithmetic contract: src/q4_cpuexp.c:605-637,855-892.
+#include "q4b_internal.cuh"
+
+#include <atomic>
+
+#include "../../include/q4cuda.h"
+
+extern std::atomic<uint64_t> g_q4b_launches;
+
+#define Q4B_X_SLICE 64u  // scratch slice that holds the quantised input row
+
+namespace {
+
+// ------------------------------------------------------------------ Q8-A
+// One warp per 32 values.  Slice s reads x + s*xs, writes group s*gps + g.
+__global__ void quant8_k(const float *__restrict__ x, uint64_t xs, uint32_t gps,
+                         uint64_t n_groups, int8_t *__restrict__ q, float *__restrict__ d,
+                         int32_t *__restrict__ bs, uint64_t q_slice, uint64_t d_slice,
+                         const int32_t *__restrict__ n_dev) {
+    const uint64_t g = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (g >= n_groups) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t s = g / gps, gl = g - s * gps;
+    if (n_dev && s >= (uint64_t)*n_dev) return;
+    const float v = x[s * xs + gl * 32u + lane];
+    const float a = q4b_warp_max(fabsf(v));
+    const float sc = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
+    int qi = __float2int_rn(__fmul_rn(v, sc));
+    qi = max(-128, min(127, qi));
+    int sum = qi;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    q[s * q_slice + gl * 32u + lane] = (int8_t)qi;
+    if (lane == 0) {
+        d[s * d_slice + gl] = __fdiv_rn(a, 127.f);
+        if (bs) bs[s * d_slice + gl] = sum;
+    }
+}
+
+// ------------------------------------------------------------------ RMSNorm (+ Q8-A)
+// One block of 256 per (group, token) row.  The sum of squares is kept in
+// fp64 like the scalar reference (src/q4_quant.c:697-706).
+__global__ void rms_q8_k(const float *__restrict__ x, const float *__restrict__ w,
+                         float *__restrict__ y, uint32_t n, uint32_t hc, float eps,
+                         int8_t *__restrict__ q, float *__restrict__ d, int32_t *__restrict__ bs,
+                         uint64_t q_slice, uint64_t d_slice) {
+    const uint32_t c = blockIdx.x, tok = blockIdx.y;
+    const uint64_t row = (uint64_t)tok * hc + c;
+    const float *xc = x + row * n;
+    const float *wc = w ? w + (uint64_t)c * n : nullptr;
+    double ss = 0.0;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) ss += (double)xc[i] * (double)xc[i];
+    __shared__ double sh[8];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31u) == 0) sh[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    double tot = 0.0;
+    for (uint32_t i = 0; i < (blockDim.x >> 5); i++) tot += sh[i];
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(tot / (double)n), eps)));
+    const uint32_t lane = threadIdx.x & 31u;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        float v = __fmul_rn(xc[i], scale);
+        if (wc) v = __fmul_rn(v, wc[i]);
+        if (y) y[row * n + i] = v;
+        if (q) {  // n % 32 == 0 and blockDim % 32 == 0: a warp holds one whole group
+            const float a = q4b_warp_max(fabsf(v));
+            const float sc = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
+            int qi = __float2int_rn(__fmul_rn(v, sc));
+            qi = max(-128, min(127, qi));
+            int sum = qi;
+#pragma unroll
+            for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            q[row * q_slice + i] = (int8_t)qi;
+            if (lane == 0) {
+                d[row * d_slice + (i >> 5)] = __fdiv_rn(a, 127.f);
+                bs[row * d_slice + (i >> 5)] = sum;
+            }
+        }
+    }
+}
+
+// ------------------------------------------------------------------ fp32 GEMV (router)
+// One warp per weight row; grid.y = batch.
+__global__ void gemv_f32_k(const float *__restrict__ W, uint64_t nrows, uint64_t ncols,
+                           const float *__restrict__ x, float *__restrict__ y, float scale) {
+    const uint64_t r = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= nrows) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    const float *wr = W + r * ncols;
+    const float *xb = x + (uint64_t)blockIdx.y * ncols;
+    float acc = 0.f;
+    if ((ncols & 3u) == 0) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(wr);
+        const float4 *x4 = reinterpret_cast<const float4 *>(xb);
+        for (uint64_t i = lane; i < ncols / 4; i += 32) {
+            const float4 a = __ldg(w4 + i), b = x4[i];
+            acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+        }
+    } else {
+        for (uint64_t i = lane; i < ncols; i += 32) acc += wr[i] * xb[i];
+    }
+    acc = q4b_warp_sum(acc);
+    if (lane == 0) y[(uint64_t)blockIdx.y * nrows + r] = scale * acc;
+}
+
+// ------------------------------------------------------------------ IQ3_S helpers
+struct Iq3Group {
+    uint32_t qs_lo, qs_hi, qh, sg, ls;
+};
+// Fields of sub-block ib of the super-block at blk (2-byte aligned address).
+__device__ __forceinline__ Iq3Group iq3_load_group(const uint8_t *blk, uint32_t ib) {
+    Iq3Group g;
+    g.qs_lo = q4b_ld_u32_a2(blk + 2 + 8 * ib);
+    g.qs_hi = q4b_ld_u32_a2(blk + 6 + 8 * ib);
+    g.qh = blk[66 + ib];
+    g.sg = q4b_ld_u32_a2(blk + 74 + 4 * ib);
+    const uint32_t sb = blk[106 + (ib >> 1)];
+    g.ls = 1u + 2u * ((ib & 1u) ? (sb >> 4) : (sb & 15u));
+    return g;
+}
+__device__ __forceinline__ float iq3_block_d(const uint8_t *blk) {
+    return __half2float(__ushort_as_half((unsigned short)q4b_ld_u16(blk)));
+}
+
+// fp32 dequantisation, one thread per 32-weight sub-block.
+__global__ void iq3s_dequant_k(const uint8_t *__restrict__ w, uint64_t n_groups,
+                               float *__restrict__ out) {
+    __shared__ uint32_t tab[512];
+    q4b_fill_code_table(tab);
+    __syncthreads();
+    const uint64_t g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (g >= n_groups) return;
+    const uint8_t *blk = w + (g >> 3) * Q4B_IQ3S_BYTES;
+    const uint32_t ib = (uint32_t)(g & 7u);
+    const Iq3Group f = iq3_load_group(blk, ib);
+    // src/q4_quant.c:397-409: db = d * (1 + 2 s); value = db * magnitude * (+-1)
+    const float db = __fmul_rn(iq3_block_d(blk), (float)f.ls);
+    float *o = out + g * 32u;
+    for (int k = 0; k < 8; k++) {
+        const uint32_t wq = k < 4 ? f.qs_lo : f.qs_hi;
+        const uint32_t idx = ((wq >> (8 * (k & 3))) & 0xffu) | (((f.qh >> k) & 1u) << 8);
+        const uint32_t c = tab[idx];
+        for (int j = 0; j < 4; j++) {
+            const float mag = (float)(2u * ((c >> (8 * j)) & 0xffu) + 1u);
+            const bool neg = (f.sg >> (4 * k + j)) & 1u;
+            o[4 * k + j] = __fmul_rn(__fmul_rn(db, mag), neg ? -1.f : 1.f);
+        }
+    }
+}
+
+// Per-group integer dots of nrows rows against one quantised vector.
+__global__ void iq3s_idot_k(const uint8_t *__restrict__ w, uint64_t nrows, uint32_t ng,
+                            const int8_t *__restrict__ q, int32_t *__restrict__ I) {
+    __shared__ uint32_t tab[512];
+    q4b_fill_code_table(tab);
+    __syncthreads();
+    const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= nrows * ng) return;
+    const uint64_t r = t / ng;
+    const uint32_t g = (uint32_t)(t - r * ng);
+    const uint8_t *blk = w + (r * (ng >> 3) + (g >> 3)) * Q4B_IQ3S_BYTES;
+    const Iq3Group f = iq3_load_group(blk, g & 7u);
+    const int *qg = reinterpret_cast<const int *>(q) + g * 8u;
+    int qv[8];
+    int qsum = 0;
+    for (int k = 0; k < 8; k++) {
+        qv[k] = qg[k];
+        qsum = __dp4a(qv[k], 0x01010101, qsum);
+    }
+    I[t] = q4b_group_idot(f.qs_lo, f.qs_hi, f.qh, f.sg, tab, qv, qsum);
+}
+
+// ------------------------------------------------------------------ router softmax + top-k
+// One warp per token.  p = softmax(logits); k picks by descending p, equal
+// values keep the lower index; weights renormalised over the picks in rank
+// order (src/q4_quant.c:715-755).  Optionally appends the shared expert's slot
+// with weight 1 and writes the entry count.
+__global__ void softmax_topk_k(const float *__restrict__ logits, uint32_t n, uint32_t k,
+                               int32_t *__restrict__ ids, float *__restrict__ wts,
+                               uint32_t out_stride, int32_t shared_slot,
+                               int32_t *__restrict__ n_out) {
+    __shared__ float p[1024];
+    __shared__ float wsel[64];
+    const uint32_t lane = threadIdx.x;
+    const float *l = logits + (uint64_t)blockIdx.x * n;
+    float m = -INFINITY;
+    for (uint32_t i = lane; i < n; i += 32) m = fmaxf(m, l[i]);
+    m = q4b_warp_max(m);
+    float s = 0.f;
+    for (uint32_t i = lane; i < n; i += 32) {
+        const float e = expf(l[i] - m);
+        p[i] = e;
+        s += e;
+    }
+    s = q4b_warp_sum(s);
+    const float inv = s > 0.f ? __fdiv_rn(1.0f, s) : 0.f;
+    for (uint32_t i = lane; i < n; i += 32) p[i] = __fmul_rn(p[i], inv);
+    __syncwarp();
+    // key: value bits above, inverted index below -> max key = largest value,
+    // lowest index among equals.  p >= 0 so the bit pattern orders like the value.
+    auto scan = [&]() {
+        unsigned long long best = 0ull;
+        for (uint32_t i = lane; i < n; i += 32) {
+            const float v = p[i];
+            if (v < 0.f) continue;  // taken
+            const unsigned long long key =
+                ((unsigned long long)__float_as_uint(v) << 32) | (0xffffffffu - i);
+            best = key > best ? key : best;
+        }
+        return best;
+    };
+    unsigned long long mine = scan();
+    if (k > n) k = n;
+    for (uint32_t t = 0; t < k; t++) {
+        unsigned long long best = mine;
+#pragma unroll
+        for (int o = 16; o; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        const uint32_t idx = 0xffffffffu - (uint32_t)(best & 0xffffffffu);
+        if (lane == 0) {
+            ids[(uint64_t)blockIdx.x * out_stride + t] = (int32_t)idx;
+            wsel[t] = __uint_as_float((uint32_t)(best >> 32));
+        }
+        if ((idx & 31u) == lane) {
+            p[idx] = -1.f;
+            mine = scan();
+        }
+    }
+    __syncwarp();
+    if (lane == 0) {
+        float sum = 0.f;
+        for (uint32_t t = 0; t < k; t++) sum = __fadd_rn(sum, wsel[t]);
+        const float wi = sum > 0.f ? __fdiv_rn(1.0f, sum) : 1.f;
+        for (uint32_t t = 0; t < k; t++)
+            wts[(uint64_t)blockIdx.x * out_stride + t] = sum > 0.f ? __fmul_rn(wsel[t], wi) : wsel[t];
+        uint32_t cnt = k;
+        if (shared_slot >= 0) {
+            ids[(uint64_t)blockIdx.x * out_stride + k] = shared_slot;
+            wts[(uint64_t)blockIdx.x * out_stride + k] = 1.0f;
+            cnt++;
+        }
+        if (n_out) n_out[blockIdx.x] = (int32_t)cnt;
+    }
+}
+
+// ------------------------------------------------------------------ gate/up + SwiGLU
+// grid (n_ff/8, experts), 8 warps per block, one warp per hidden unit f:
+// h[e][f] = silu(gate_f . xq) * (up_f . xq).
+__global__ void moe_gu_k(const uint8_t *__restrict__ bg, const uint8_t *__restrict__ bu,
+                         uint64_t stride, const int32_t *__restrict__ slots,
+                         const int32_t *__restrict__ n_dev, const int8_t *__restrict__ xq,
+                         const float *__restrict__ xd, const int32_t *__restrict__ xbs,
+                         uint32_t in_dim, uint32_t n_ff, float *__restrict__ h) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint32_t *tab = reinterpret_cast<uint32_t *>(smem);
+    int *sq = reinterpret_cast<int *>(smem + 2048);
+    const uint32_t ng = in_dim >> 5;
+    float *sd = reinterpret_cast<float *>(smem + 2048 + in_dim);
+    int *sb = reinterpret_cast<int *>(smem + 2048 + in_dim + 4 * ng);
+    const uint32_t e = blockIdx.y;
+    if (n_dev && e >= (uint32_t)*n_dev) return;
+    q4b_fill_code_table(tab);
+    for (uint32_t i = threadIdx.x; i < in_dim / 4; i += blockDim.x)
+        sq[i] = reinterpret_cast<const int *>(xq)[i];
+    for (uint32_t i = threadIdx.x; i < ng; i += blockDim.x) {
+        sd[i] = xd[i];
+        sb[i] = xbs[i];
+    }
+    __syncthreads();
+    const uint32_t f = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (f >= n_ff) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t rb = (uint64_t)(in_dim >> 8) * Q4B_IQ3S_BYTES;
+    const uint64_t off = (uint64_t)slots[e] * stride + (uint64_t)f * rb;
+    const uint8_t *wg = bg + off, *wu = bu + off;
+    float ag = 0.f, au = 0.f;
+    for (uint32_t g = lane; g < ng; g += 32) {
+        const uint32_t blk = g >> 3, ib = g & 7u;
+        const int *qv = sq + g * 8u;
+        const float dx = sd[g];
+        const int qsum = sb[g];
+        {
+            const uint8_t *p = wg + (uint64_t)blk * Q4B_IQ3S_BYTES;
+            const Iq3Group fg = iq3_load_group(p, ib);
+            const int I = q4b_group_idot(fg.qs_lo, fg.qs_hi, fg.qh, fg.sg, tab, qv, qsum);
+            ag = fmaf(__fmul_rn(iq3_block_d(p), dx), (float)(I * (int)fg.ls), ag);
+        }
+        {
+            const uint8_t *p = wu + (uint64_t)blk * Q4B_IQ3S_BYTES;
+            const Iq3Group fg = iq3_load_group(p, ib);
+            const int I = q4b_group_idot(fg.qs_lo, fg.qs_hi, fg.qh, fg.sg, tab, qv, qsum);
+            au = fmaf(__fmul_rn(iq3_block_d(p), dx), (float)(I * (int)fg.ls), au);
+        }
+    }
+    ag = q4b_warp_sum(ag);
+    au = q4b_warp_sum(au);
+    if (lane == 0) h[(uint64_t)e * n_ff + f] = q4b_swiglu(ag, au);
+}
+
+// ------------------------------------------------------------------ down + weighted combine
+// grid (n_embd/8), one warp per output row r:
+// y[r] += sum_e wts[e] * (down_e[r] . hq_e), experts visited in list order by a
+// fixed lane assignment, so the result is reproducible run to run.
+__global__ void moe_ya_k(const uint8_t *__restrict__ bd, uint64_t stride,
+                         const int32_t *__restrict__ slots, const float *__restrict__ wts,
+                         uint32_t n_host, const int32_t *__restrict__ n_dev,
+                         const int8_t *__restrict__ hq, const float *__restrict__ hd,
+                         const int32_t *__restrict__ hbs, uint64_t q_slice, uint64_t d_slice,
+                         uint32_t n_ff, uint32_t n_embd, float *__restrict__ y) {
+    __shared__ uint32_t tab[512];
+    q4b_fill_code_table(tab);
+    __syncthreads();
+    const uint32_t r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= n_embd) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t n = n_dev ? (uint32_t)*n_dev : n_host;
+    const uint32_t ng = n_ff >> 5;
+    const uint64_t rb = (uint64_t)(n_ff >> 8) * Q4B_IQ3S_BYTES;
+    float acc = 0.f;
+    for (uint32_t it = lane; it < n * ng; it += 32) {
+        const uint32_t e = it / ng, g = it - e * ng;
+        const uint8_t *p = bd + (uint64_t)slots[e] * stride + (uint64_t)r * rb +
+                           (uint64_t)(g >> 3) * Q4B_IQ3S_BYTES;
+        const Iq3Group fg = iq3_load_group(p, g & 7u);
+        const int *qg = reinterpret_cast<const int *>(hq + (uint64_t)e * q_slice) + g * 8u;
+        int qv[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) qv[k] = qg[k];
+        const int I = q4b_group_idot(fg.qs_lo, fg.qs_hi, fg.qh, fg.sg, tab, qv,
+                                     hbs[(uint64_t)e * d_slice + g]);
+        const float dd = __fmul_rn(iq3_block_d(p), hd[(uint64_t)e * d_slice + g]);
+        acc = fmaf(__fmul_rn(wts[e], dd), (float)(I * (int)fg.ls), acc);
+    }
+    acc = q4b_warp_sum(acc);
+    if (lane == 0) y[r] += acc;
+}
+
+// IQ3_S rows times fp32 activations (shared-expert style GEMV), warp per row.
+__global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, uint32_t ncols,
+                                const float *__restrict__ x, float *__restrict__ y, float scale) {
+    __shared__ uint32_t tab[512];
+    q4b_fill_code_table(tab);
+    __syncthreads();
+    const uint64_t r = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= nrows) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t ng = ncols >> 5;
+    const uint8_t *row = w + r * (uint64_t)(ncols >> 8) * Q4B_IQ3S_BYTES;
+    const float *xb = x + (uint64_t)blockIdx.y * ncols;
+    float acc = 0.f;
+    for (uint32_t g = lane; g < ng; g += 32) {
+        const uint8_t *p = row + (uint64_t)(g >> 3) * Q4B_IQ3S_BYTES;
+        const Iq3Group f = iq3_load_group(p, g & 7u);
+        const float db = iq3_block_d(p) * (float)f.ls;
+        float sub = 0.f;
+        for (int k = 0; k < 8; k++) {
+            const uint32_t wq = k < 4 ? f.qs_lo : f.qs_hi;
+            const uint32_t idx = ((wq >> (8 * (k & 3))) & 0xffu) | (((f.qh >> k) & 1u) << 8);
+            const uint32_t c = tab[idx];
+            for (int j = 0; j < 4; j++) {
+                const float mag = (float)(2u * ((c >> (8 * j)) & 0xffu) + 1u);
+                const float xv = xb[g * 32u + 4 * k + j];
+                sub += ((f.sg >> (4 * k + j)) & 1u) ? -mag * xv : mag * xv;
+            }
+        }
+        acc += db * sub;
+    }
+    acc = q4b_warp_sum(acc);
+    if (lane == 0) y[(uint64_t)blockIdx.y * nrows + r] = scale * acc;
+}
+
+// ------------------------------------------------------------------ host side
+bool shape_ok(uint32_t gt, uint32_t ut, uint32_t dt, uint32_t in_dim, uint32_t n_ff) {
+    return gt == Q4_T_IQ3_S && ut == Q4_T_IQ3_S && dt == Q4_T_IQ3_S && in_dim && n_ff &&
+           (in_dim % Q4B_QK) == 0 && (n_ff % Q4B_QK) == 0 && in_dim <= Q4B_XQ_MAXLEN &&
+           n_ff <= Q4B_XQ_MAXLEN;
+}
+
+bool launch_quant8(const float *x, uint64_t xs, uint32_t slen, uint32_t ns, int8_t *q, float *d,
+                   int32_t *bs, uint64_t q_slice, uint64_t d_slice, const int32_t *n_dev) {
+    const uint32_t gps = slen >> 5;
+    const uint64_t ngr = (uint64_t)gps * ns;
+    quant8_k<<<(unsigned)((ngr + 7) / 8), 256, 0, g_q4b.stream>>>(x, xs, gps, ngr, q, d, bs,
+                                                                 q_slice, d_slice, n_dev);
+    g_q4b_launches++;
+    return q4b_launch_ok("quant8");
+}
+
+// The common tail of every exec variant: d_x is already quantised into the
+// scratch slice Q4B_X_SLICE.
+bool moe_exec_tail(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
+                   const float *d_wts, uint32_t n_host, const int32_t *d_n, uint64_t og,
+                   uint64_t ou, uint64_t od, float *d_h, float *d_y, uint32_t n_ff,
+                   uint32_t in_dim, uint32_t n_embd) {
+    Q4bState &s = g_q4b;
+    const uint32_t ne = d_n ? 64u : n_host;
+    const int8_t *xq = s.xq + (size_t)Q4B_X_SLICE * Q4B_XQ_MAXLEN;
+    const float *xd = s.xd + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
+    const int32_t *xbs = s.xbs + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
+    const size_t sm = 2048 + in_dim + 8 * (in_dim >> 5);
+    moe_gu_k<<<dim3((n_ff + 7) / 8, ne), 256, sm, s.stream>>>(base + og, base + ou, stride, d_slots,
+                                                             d_n, xq, xd, xbs, in_dim, n_ff, d_h);
+    g_q4b_launches++;
+    if (!q4b_launch_ok("moe_gu")) return false;
+    if (!launch_quant8(d_h, n_ff, n_ff, ne, s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32,
+                       d_n))
+        return false;
+    moe_ya_k<<<(n_embd + 7) / 8, 256, 0, s.stream>>>(base + od, stride, d_slots, d_wts, n_host, d_n,
+                                                    s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN,
+                                                    Q4B_XQ_MAXLEN / 32, n_ff, n_embd, d_y);
+    g_q4b_launches++;
+    return q4b_launch_ok("moe_ya");
+}
+
+bool quant_x(const float *d_x, uint32_t in_dim) {
+    Q4bState &s = g_q4b;
+    return launch_quant8(d_x, 0, in_dim, 1, s.xq + (size_t)Q4B_X_SLICE * Q4B_XQ_MAXLEN,
+                         s.xd + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32),
+                         s.xbs + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32), 0, 0, nullptr);
+}
+
+}  // namespace
+
+extern "C" bool q4_hip_moe_tok_ok(uint32_t gt, uint32_t ut, uint32_t dt, uint32_t in_dim,
+                                  uint32_t n_ff) {
+    return g_q4b.ok && shape_ok(gt, ut, dt, in_dim, n_ff);
+}
+
+extern "C" bool q4_hip_moe_stage(const int32_t *slots, const float *wts, uint32_t n) {
+    if (!g_q4b.ok || !slots || !wts || n == 0 || n > 64) return false;
+    memcpy(g_q4b.es_h, slots, n * sizeof(int32_t));
+    memcpy(g_q4b.ew_h, wts, n * sizeof(float));
+    *g_q4b.en_h = (int32_t)n;
+    return true;
+}
+
+extern "C" bool q4_hip_moe_exec_staged(const uint8_t *base, uint64_t stride, uint32_t gt,
+                                       uint64_t og, uint32_t ut, uint64_t ou, uint32_t dt,
+                                       uint64_t od, const float *d_x, float *d_h, float *d_h2,
+                                       float *d_down, float *d_y, uint32_t n_ff, uint32_t in_dim,
+                                       uint32_t n_embd) {
+    (void)d_h2;
+    (void)d_down;
+    if (!g_q4b.ok || !base || !d_x || !d_h || !d_y || !n_embd) return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff)) return false;
+    if (!quant_x(d_x, in_dim)) return false;
+    return moe_exec_tail(base, stride, g_q4b.es_d, g_q4b.ew_d, 0, g_q4b.en_d, og, ou, od, d_h, d_y,
+                         n_ff, in_dim, n_embd);
+}
+
+extern "C" bool q4_hip_moe_exec(const uint8_t *base, uint64_t stride, const int32_t *slots,
+                                const float *wts, uint32_t n, uint32_t gt, uint64_t og,
+                                uint32_t ut, uint64_t ou, uint32_t dt, uint64_t od,
+                                const float *d_x, float *d_h, float *d_h2, float *d_down,
+                                float *d_y, uint32_t n_ff, uint32_t in_dim, uint32_t n_embd) {
+    (void)d_h2;
+    (void)d_down;
+    if (!g_q4b.ok || !base || !slots || !wts || !n || n > 64 || !d_x || !d_h || !d_y || !n_embd)
+        return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff)) return false;
+    // Like the reference (src/q4_rocm.cu:5441-5445) the list goes through mapped
+    // host memory: the kernels fetch it themselves, no copy node on the stream.
+    // The previous exec must have finished reading it.
+    if (cudaStreamSynchronize(g_q4b.stream) != cudaSuccess) return false;
+    memcpy(g_q4b.es_h, slots, n * sizeof(int32_t));
+    memcpy(g_q4b.ew_h, wts, n * sizeof(float));
+    *g_q4b.en_h = (int32_t)n;
+    if (!quant_x(d_x, in_dim)) return false;
+    return moe_exec_tail(base, stride, g_q4b.es_d, g_q4b.ew_d, n, nullptr, og, ou, od, d_h, d_y,
+                         n_ff, in_dim, n_embd);
+}
+
+extern "C" bool q4_hip_moe_exec_dev(const uint8_t *base, uint64_t stride, const int32_t *d_es,
+                                    const float *d_ew, const int32_t *d_nhit, uint32_t gt,
+                                    uint64_t og, uint32_t ut, uint64_t ou, uint32_t dt, uint64_t od,
+                                    const float *d_x, float *d_h, float *d_h2, float *d_down,
+                                    float *d_y, uint32_t n_ff, uint32_t in_dim, uint32_t n_embd) {
+    (void)d_h2;
+    (void)d_down;
+    if (!g_q4b.ok || !base || !d_es || !d_ew || !d_nhit || !d_x || !d_h || !d_y || !n_embd)
+        return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff)) return false;
+    if (!quant_x(d_x, in_dim)) return false;
+    return moe_exec_tail(base, stride, d_es, d_ew, 0, d_nhit, og, ou, od, d_h, d_y, n_ff, in_dim,
+                         n_embd);
+}
+
+extern "C" bool q4_hip_softmax_topk_launch(const float *d_logits, uint32_t n, uint32_t k,
+                                           int32_t *d_ids, float *d_wts) {
+    if (!g_q4b.ok || !d_logits || !d_ids || !d_wts || n == 0 || n > 1024 || k == 0 || k > 64)
+        return false;
+    softmax_topk_k<<<1, 32, 0, g_q4b.stream>>>(d_logits, n, k, d_ids, d_wts, k, -1, nullptr);
+    g_q4b_launches++;
+    return q4b_launch_ok("softmax_topk");
+}
+
+extern "C" bool q4_hip_softmax_topk(const float *d_logits, uint32_t n, uint32_t k, int32_t *h_ids,
+                                    float *h_wts) {
+    if (!h_ids || !h_wts) return false;
+    Q4bState &s = g_q4b;
+    if (!q4_hip_softmax_topk_launch(d_logits, n, k, s.topk_ids_d, s.topk_wts_d)) return false;
+    const uint32_t kk = k > n ? n : k;
+    Q4B_CHECK(cudaMemcpyAsync(s.topk_ids_h, s.topk_ids_d, kk * 4, cudaMemcpyDeviceToHost, s.stream));
+    Q4B_CHECK(cudaMemcpyAsync(s.topk_wts_h, s.topk_wts_d, kk * 4, cudaMemcpyDeviceToHost, s.stream));
+    Q4B_CHECK(cudaStreamSynchronize(s.stream));
+    memcpy(h_ids, s.topk_ids_h, kk * 4);
+    memcpy(h_wts, s.topk_wts_h, kk * 4);
+    return true;
+}
+
+extern "C" bool q4_hip_grouped_rms_n(const float *x, const float *w, float *y, uint32_t n_embd,
+                                     uint32_t hc, float eps, uint32_t n_tok) {
+    if (!g_q4b.ok || !x || !y || n_embd == 0 || hc == 0 || n_tok == 0) return false;
+    rms_q8_k<<<dim3(hc, n_tok), 256, 0, g_q4b.stream>>>(x, w, y, n_embd, hc, eps, nullptr, nullptr,
+                                                       nullptr, 0, 0);
+    g_q4b_launches++;
+    return q4b_launch_ok("grouped_rms");
+}
+extern "C" bool q4_hip_grouped_rms(const float *x, const float *w, float *y, uint32_t n_embd,
+                                   uint32_t hc, float eps) {
+    return q4_hip_grouped_rms_n(x, w, y, n_embd, hc, eps, 1);
+}
+
+extern "C" bool q4_hip_gemv_dd_n(uint32_t ggml_type, const uint8_t *d_w, uint64_t nrows,
+                                 uint64_t ncols, const float *d_x, float *d_y, float scale,
+                                 uint32_t n_batch) {
+    if (!g_q4b.ok || !d_w || !d_x || !d_y || nrows == 0 || ncols == 0 || n_batch == 0) return false;
+    const dim3 grid((unsigned)((nrows + 7) / 8), n_batch);
+    if (ggml_type == Q4_T_F32) {
+        gemv_f32_k<<<grid, 256, 0, g_q4b.stream>>>(reinterpret_cast<const float *>(d_w), nrows,
+                                                  ncols, d_x, d_y, scale);
+    } else if (ggml_type == Q4_T_IQ3_S) {
+        if (ncols % Q4B_QK) return false;
+        gemv_iq3s_f32_k<<<grid, 256, 0, g_q4b.stream>>>(d_w, nrows, (uint32_t)ncols, d_x, d_y, scale);
+    } else {
+        return false;
+    }
+    g_q4b_launches++;
+    return q4b_launch_ok("gemv");
+}
+extern "C" bool q4_hip_gemv_dd(uint32_t ggml_type, const uint8_t *d_w, uint64_t nrows,
+                               uint64_t ncols, const float *d_x, float *d_y, float scale) {
+    return q4_hip_gemv_dd_n(ggml_type, d_w, nrows, ncols, d_x, d_y, scale, 1);
+}
+
+extern "C" bool q4_cuda_quant8(const float *d_x, uint64_t n, int8_t *d_q, float *d_d,
+                               int32_t *d_bs) {
+    if (!g_q4b.ok || !d_x || !d_q || !d_d || n == 0 || (n & 31u)) return false;
+    const uint64_t ngr = n / 32;
+    quant8_k<<<(unsigned)((ngr + 7) / 8), 256, 0, g_q4b.stream>>>(d_x, 0, (uint32_t)ngr, ngr, d_q,
+                                                                 d_d, d_bs, 0, 0, nullptr);
+    g_q4b_launches++;
+    return q4b_launch_ok("quant8");
+}
+
+extern "C" bool q4_cuda_iq3s_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                                     float *d_out) {
+    if (!g_q4b.ok || !d_w || !d_out || nrows == 0 || ncols == 0 || (ncols % Q4B_QK)) return false;
+    const uint64_t ngr = nrows * ncols / 32;
+    iq3s_dequant_k<<<(unsigned)((ngr + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, ngr, d_out);
+    g_q4b_launches++;
+    return q4b_launch_ok("iq3s_dequant");
+}
+
+extern "C" bool q4_cuda_iq3s_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                                  const int8_t *d_q, int32_t *d_I) {
+    if (!g_q4b.ok || !d_w || !d_q || !d_I || nrows == 0 || ncols == 0 || (ncols % Q4B_QK))
+        return false;
+    const uint64_t items = nrows * (ncols / 32);
+    iq3s_idot_k<<<(unsigned)((items + 255) / 256), 256, 0, g_q4b.stream>>>(
+        d_w, nrows, (uint32_t)(ncols / 32), d_q, d_I);
+    g_q4b_launches++;
+    return q4b_launch_ok("iq3s_idot");
+}
+
+// One MoE layer, one token, as a chain of the kernels above (five launches,
+// no host round trip).
+extern "C" bool q4_cuda_moe_decode(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou,
+                                   uint64_t od, int32_t shared_slot, const float *d_x,
+                                   const float *d_norm_w, float eps, const float *d_router,
+                                   uint32_t n_expert, uint32_t topk, uint32_t n_embd,
+                                   uint32_t n_ff, float *d_y, int32_t *d_ids, float *d_wts) {
+    Q4bState &s = g_q4b;
+    if (!s.ok || !base || !d_x || !d_router || !d_y) return false;
+    if (!shape_ok(Q4_T_IQ3_S, Q4_T_IQ3_S, Q4_T_IQ3_S, n_embd, n_ff)) return false;
+    if (n_expert == 0 || n_expert > 1024 || topk == 0 || topk > 63 || topk > n_expert) return false;
+    int8_t *xq = s.xq + (size_t)Q4B_X_SLICE * Q4B_XQ_MAXLEN;
+    float *xd = s.xd + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
+    int32_t *xbs = s.xbs + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
+    rms_q8_k<<<dim3(1, 1), 256, 0, s.stream>>>(d_x, d_norm_w, s.xn, n_embd, 1, eps, xq, xd, xbs, 0,
+                                              0);
+    g_q4b_launches++;
+    if (!q4b_launch_ok("rms_q8")) return false;
+    gemv_f32_k<<<dim3((n_expert + 7) / 8, 1), 256, 0, s.stream>>>(d_router, n_expert, n_embd, s.xn,
+                                                                 s.logits, 1.0f);
+    g_q4b_launches++;
+    if (!q4b_launch_ok("router_gemv")) return false;
+    softmax_topk_k<<<1, 32, 0, s.stream>>>(s.logits, n_expert, topk, s.r_ids, s.r_wts, 64,
+                                          shared_slot, s.r_cnt);
+    g_q4b_launches++;
+    if (!q4b_launch_ok("softmax_topk")) return false;
+    if (cudaMemsetAsync(d_y, 0, (size_t)n_embd * sizeof(float), s.stream) != cudaSuccess)
+        return false;
+    if (!moe_exec_tail(base, stride, s.r_ids, s.r_wts, 0, s.r_cnt, og, ou, od, s.hbuf, d_y, n_ff,
+                       n_embd, n_embd))
+        return false;
+    if (d_ids &&
+        cudaMemcpyAsync(d_ids, s.r_ids, topk * 4, cudaMemcpyDeviceToDevice, s.stream) != cudaSuccess)
+        return false;
+    if (d_wts &&
+        cudaMemcpyAsync(d_wts, s.r_wts, topk * 4, cudaMemcpyDeviceToDevice, s.stream) != cudaSuccess)
+        return false;
+    return true;
+}

@@ -1,0 +1,333 @@
+// Lifecycle, memory, expert arenas, graphs and timers of the q4cuda library.
+// Counterpart of the reference device layer's plumbing (src/q4_rocm.cu:507-560,
+// 661-801 for streams and arenas); the arithmetic lives in the other files.
+#include "q4b_internal.cuh"
+
+#include <atomic>
+#include <string.h>
+
+#include "../../include/q4cuda.h"
+
+#define Q4B_IQ3S_CODES_DECL static const
+#include "iq3s_codes.h"
+
+Q4bState g_q4b = {};
+std::atomic<uint64_t> g_q4b_launches{0};
+
+namespace {
+
+struct Arena {
+    uint8_t *base;
+    uint32_t n_slots;
+    uint64_t stride;
+    uint64_t bytes;
+};
+Arena g_arena[4] = {};
+
+cudaEvent_t g_ev0, g_ev1;
+bool g_capturing = false;
+
+bool alloc_scratch() {
+    Q4bState &s = g_q4b;
+    if (s.xq) return true;
+    const size_t nq = (size_t)Q4B_XQ_SLICES * Q4B_XQ_MAXLEN;
+    Q4B_CHECK(cudaMalloc(&s.xq, nq));
+    Q4B_CHECK(cudaMalloc(&s.xd, nq / 32 * sizeof(float)));
+    Q4B_CHECK(cudaMalloc(&s.xbs, nq / 32 * sizeof(int32_t)));
+    Q4B_CHECK(cudaMalloc(&s.xn, (size_t)Q4B_MAX_TOK * Q4B_XQ_MAXLEN * sizeof(float)));
+    Q4B_CHECK(cudaMalloc(&s.logits, (size_t)Q4B_MAX_TOK * 1024 * sizeof(float)));
+    Q4B_CHECK(cudaMalloc(&s.r_ids, (size_t)Q4B_MAX_TOK * 64 * sizeof(int32_t)));
+    Q4B_CHECK(cudaMalloc(&s.r_wts, (size_t)Q4B_MAX_TOK * 64 * sizeof(float)));
+    Q4B_CHECK(cudaMalloc(&s.r_cnt, (size_t)Q4B_MAX_TOK * sizeof(int32_t)));
+    Q4B_CHECK(cudaMalloc(&s.hbuf, nq * sizeof(float)));
+    return true;
+}
+
+}  // namespace
+
+extern "C" bool q4_hip_init(void) {
+    Q4bState &s = g_q4b;
+    if (s.ok) return true;
+    int n = 0;
+    if (cudaGetDeviceCount(&n) != cudaSuccess || n == 0) {
+        fprintf(stderr, "q4cuda: no CUDA device; this library has no CPU path\n");
+        return false;
+    }
+    int dev = 0;
+    Q4B_CHECK(cudaGetDevice(&dev));
+    cudaDeviceProp p;
+    Q4B_CHECK(cudaGetDeviceProperties(&p, dev));
+    if (p.major != 10) {
+        fprintf(stderr, "q4cuda: device %d is sm_%d%d; the kernels are built for sm_100a only\n",
+                dev, p.major, p.minor);
+        return false;
+    }
+    s.device = dev;
+    s.n_sm = p.multiProcessorCount;
+    Q4B_CHECK(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
+    Q4B_CHECK(cudaStreamCreateWithFlags(&s.copy_stream, cudaStreamNonBlocking));
+    Q4B_CHECK(cudaMemcpyToSymbol(c_iq3s_codes, q4b_iq3s_codes, sizeof(q4b_iq3s_codes)));
+    Q4B_CHECK(cudaHostAlloc(&s.es_h, 64 * sizeof(int32_t), cudaHostAllocMapped));
+    Q4B_CHECK(cudaHostAlloc(&s.ew_h, 64 * sizeof(float), cudaHostAllocMapped));
+    Q4B_CHECK(cudaHostAlloc(&s.en_h, sizeof(int32_t), cudaHostAllocMapped));
+    Q4B_CHECK(cudaHostGetDevicePointer(&s.es_d, s.es_h, 0));
+    Q4B_CHECK(cudaHostGetDevicePointer(&s.ew_d, s.ew_h, 0));
+    Q4B_CHECK(cudaHostGetDevicePointer(&s.en_d, s.en_h, 0));
+    Q4B_CHECK(cudaHostAlloc(&s.topk_ids_h, 64 * sizeof(int32_t), cudaHostAllocDefault));
+    Q4B_CHECK(cudaHostAlloc(&s.topk_wts_h, 64 * sizeof(float), cudaHostAllocDefault));
+    Q4B_CHECK(cudaMalloc(&s.topk_ids_d, 64 * sizeof(int32_t)));
+    Q4B_CHECK(cudaMalloc(&s.topk_wts_d, 64 * sizeof(float)));
+    Q4B_CHECK(cudaMalloc(&s.err_d, sizeof(uint32_t)));
+    Q4B_CHECK(cudaMemset(s.err_d, 0, sizeof(uint32_t)));
+    Q4B_CHECK(cudaHostAlloc(&s.err_h, sizeof(uint32_t), cudaHostAllocDefault));
+    Q4B_CHECK(cudaEventCreate(&g_ev0));
+    Q4B_CHECK(cudaEventCreate(&g_ev1));
+    if (!alloc_scratch()) return false;
+    s.ok = true;
+    return true;
+}
+
+extern "C" void q4_hip_moe_scratch_warm(void) {
+    if (g_q4b.ok) alloc_scratch();
+}
+
+extern "C" void q4_hip_shutdown(void) {
+    Q4bState &s = g_q4b;
+    if (!s.ok) return;
+    cudaDeviceSynchronize();
+    for (int a = 0; a < 4; a++) {
+        if (g_arena[a].base) cudaFree(g_arena[a].base);
+        g_arena[a] = Arena{};
+    }
+    cudaFree(s.xq);
+    cudaFree(s.xd);
+    cudaFree(s.xbs);
+    cudaFree(s.xn);
+    cudaFree(s.logits);
+    cudaFree(s.r_ids);
+    cudaFree(s.r_wts);
+    cudaFree(s.r_cnt);
+    cudaFree(s.hbuf);
+    cudaFreeHost(s.es_h);
+    cudaFreeHost(s.ew_h);
+    cudaFreeHost(s.en_h);
+    cudaFreeHost(s.topk_ids_h);
+    cudaFreeHost(s.topk_wts_h);
+    cudaFree(s.topk_ids_d);
+    cudaFree(s.topk_wts_d);
+    cudaFree(s.err_d);
+    cudaFreeHost(s.err_h);
+    cudaEventDestroy(g_ev0);
+    cudaEventDestroy(g_ev1);
+    cudaStreamDestroy(s.stream);
+    cudaStreamDestroy(s.copy_stream);
+    s = Q4bState{};
+}
+
+extern "C" bool q4_hip_ok(void) { return g_q4b.ok; }
+extern "C" void *q4_hip_stream(void) { return (void *)g_q4b.stream; }
+extern "C" void q4_hip_sync(void) {
+    if (g_q4b.ok) cudaDeviceSynchronize();
+}
+extern "C" bool q4_hip_stream_sync(void) {
+    return g_q4b.ok && cudaStreamSynchronize(g_q4b.stream) == cudaSuccess;
+}
+
+extern "C" void *q4_hip_malloc(size_t n) {
+    if (!g_q4b.ok || n == 0) return nullptr;
+    void *p = nullptr;
+    if (cudaMalloc(&p, n) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+extern "C" void q4_hip_free(void *p) {
+    if (g_q4b.ok && p) cudaFree(p);
+}
+extern "C" bool q4_hip_h2d(void *d, const void *h, size_t n) {
+    if (!g_q4b.ok || !d || !h) return false;
+    Q4B_CHECK(cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, g_q4b.stream));
+    Q4B_CHECK(cudaStreamSynchronize(g_q4b.stream));
+    return true;
+}
+extern "C" bool q4_hip_d2h(void *h, const void *d, size_t n) {
+    if (!g_q4b.ok || !d || !h) return false;
+    Q4B_CHECK(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, g_q4b.stream));
+    Q4B_CHECK(cudaStreamSynchronize(g_q4b.stream));
+    return true;
+}
+extern "C" bool q4_hip_h2d_async(void *d, const void *h, uint64_t n) {
+    if (!g_q4b.ok || !d || !h) return false;
+    Q4B_CHECK(cudaMemcpyAsync(d, h, n, cudaMemcpyHostToDevice, g_q4b.stream));
+    return true;
+}
+extern "C" bool q4_hip_d2h_async(void *h, const void *d, uint64_t n) {
+    if (!g_q4b.ok || !d || !h) return false;
+    Q4B_CHECK(cudaMemcpyAsync(h, d, n, cudaMemcpyDeviceToHost, g_q4b.stream));
+    return true;
+}
+extern "C" bool q4_hip_copy_async(float *d, const float *s, uint64_t n) {
+    if (!g_q4b.ok || !d || !s) return false;
+    Q4B_CHECK(cudaMemcpyAsync(d, s, n * sizeof(float), cudaMemcpyDeviceToDevice, g_q4b.stream));
+    return true;
+}
+extern "C" uint64_t q4_hip_vram_free(void) {
+    if (!g_q4b.ok) return 0;
+    size_t f = 0, t = 0;
+    if (cudaMemGetInfo(&f, &t) != cudaSuccess) return 0;
+    return f;
+}
+
+__global__ static void fill_k(float *d, float v, uint64_t n) {
+    uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t step = (uint64_t)gridDim.x * blockDim.x;
+    for (; i < n; i += step) d[i] = v;
+}
+extern "C" bool q4_hip_fill(float *d, float v, uint64_t n) {
+    if (!g_q4b.ok || !d || n == 0) return false;
+    uint64_t nb = (n + 255) / 256;
+    if (nb > 4096) nb = 4096;
+    fill_k<<<(unsigned)nb, 256, 0, g_q4b.stream>>>(d, v, n);
+    g_q4b_launches++;
+    return q4b_launch_ok("fill");
+}
+
+// ---- arenas ----
+extern "C" bool q4_hip_experts_alloc_a(int arena, uint32_t n_slots, uint64_t slot_bytes) {
+    if (!g_q4b.ok || arena < 0 || arena >= 4 || n_slots == 0 || slot_bytes == 0) return false;
+    Arena &a = g_arena[arena];
+    if (a.base) return false;
+    // 256 bytes of zeroed slack after the last slot: kernels that fetch whole
+    // 16-byte chunks may read a few bytes past the end of the last pack.
+    const uint64_t bytes = (uint64_t)n_slots * slot_bytes + 256;
+    if (cudaMalloc(&a.base, bytes) != cudaSuccess) {
+        cudaGetLastError();
+        a.base = nullptr;
+        return false;
+    }
+    cudaMemsetAsync(a.base + bytes - 256, 0, 256, g_q4b.stream);
+    a.n_slots = n_slots;
+    a.stride = slot_bytes;
+    a.bytes = bytes;
+    return true;
+}
+extern "C" void q4_hip_experts_free_a(int arena) {
+    if (!g_q4b.ok || arena < 0 || arena >= 4) return;
+    if (g_arena[arena].base) {
+        cudaDeviceSynchronize();
+        cudaFree(g_arena[arena].base);
+    }
+    g_arena[arena] = Arena{};
+}
+extern "C" uint32_t q4_hip_experts_n_a(int arena) {
+    return (arena >= 0 && arena < 4) ? g_arena[arena].n_slots : 0;
+}
+extern "C" bool q4_hip_experts_put_async_a(int arena, uint32_t slot, const uint8_t *host,
+                                           uint64_t n) {
+    if (!g_q4b.ok || arena < 0 || arena >= 4 || !host) return false;
+    Arena &a = g_arena[arena];
+    if (!a.base || slot >= a.n_slots || n > a.stride) return false;
+    Q4B_CHECK(cudaMemcpyAsync(a.base + (uint64_t)slot * a.stride, host, n, cudaMemcpyHostToDevice,
+                              g_q4b.copy_stream));
+    return true;
+}
+extern "C" bool q4_hip_experts_put_a(int arena, uint32_t slot, const uint8_t *host, uint64_t n) {
+    if (!q4_hip_experts_put_async_a(arena, slot, host, n)) return false;
+    Q4B_CHECK(cudaStreamSynchronize(g_q4b.copy_stream));
+    return true;
+}
+extern "C" const uint8_t *q4_hip_experts_dev_a(int arena, uint32_t slot) {
+    if (arena < 0 || arena >= 4 || !g_arena[arena].base || slot >= g_arena[arena].n_slots)
+        return nullptr;
+    return g_arena[arena].base + (uint64_t)slot * g_arena[arena].stride;
+}
+extern "C" const uint8_t *q4_hip_experts_base_a(int arena) {
+    return (arena >= 0 && arena < 4) ? g_arena[arena].base : nullptr;
+}
+extern "C" uint64_t q4_hip_experts_stride_a(int arena) {
+    return (arena >= 0 && arena < 4) ? g_arena[arena].stride : 0;
+}
+extern "C" bool q4_hip_experts_alloc(uint32_t n, uint64_t b) { return q4_hip_experts_alloc_a(0, n, b); }
+extern "C" void q4_hip_experts_free(void) { q4_hip_experts_free_a(0); }
+extern "C" uint32_t q4_hip_experts_n(void) { return q4_hip_experts_n_a(0); }
+extern "C" bool q4_hip_experts_put(uint32_t slot, const uint8_t *h, uint64_t n) {
+    return q4_hip_experts_put_a(0, slot, h, n);
+}
+extern "C" bool q4_hip_experts_put_async(uint32_t slot, const uint8_t *h, uint64_t n) {
+    return q4_hip_experts_put_async_a(0, slot, h, n);
+}
+extern "C" const uint8_t *q4_hip_experts_dev(uint32_t slot) { return q4_hip_experts_dev_a(0, slot); }
+extern "C" void q4_hip_copy_wait(void) {
+    if (g_q4b.ok) cudaStreamSynchronize(g_q4b.copy_stream);
+}
+
+// ---- graphs ----
+extern "C" int q4_hip_graph_begin(void) {
+    if (!g_q4b.ok || g_capturing) return 0;
+    if (cudaStreamBeginCapture(g_q4b.stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    g_capturing = true;
+    return 1;
+}
+extern "C" void *q4_hip_graph_end(void) {
+    if (!g_q4b.ok || !g_capturing) return nullptr;
+    g_capturing = false;
+    cudaGraph_t g = nullptr;
+    if (cudaStreamEndCapture(g_q4b.stream, &g) != cudaSuccess || !g) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    cudaGraphExec_t ex = nullptr;
+    cudaError_t e = cudaGraphInstantiate(&ex, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return (void *)ex;
+}
+extern "C" uint32_t q4_hip_graph_nodes(void *exec) {
+    (void)exec;
+    return 0;  // the reference reports node counts for diagnostics only
+}
+extern "C" bool q4_hip_graph_launch(void *exec) {
+    if (!g_q4b.ok || !exec) return false;
+    Q4B_CHECK(cudaGraphLaunch((cudaGraphExec_t)exec, g_q4b.stream));
+    return true;
+}
+extern "C" void q4_hip_graph_free(void *exec) {
+    if (exec) cudaGraphExecDestroy((cudaGraphExec_t)exec);
+}
+
+// ---- timers / counters ----
+extern "C" bool q4_cuda_timer_begin(void) {
+    if (!g_q4b.ok) return false;
+    Q4B_CHECK(cudaEventRecord(g_ev0, g_q4b.stream));
+    return true;
+}
+extern "C" bool q4_cuda_timer_end(void) {
+    if (!g_q4b.ok) return false;
+    Q4B_CHECK(cudaEventRecord(g_ev1, g_q4b.stream));
+    return true;
+}
+extern "C" float q4_cuda_timer_ms(void) {
+    if (!g_q4b.ok) return -1.f;
+    if (cudaEventSynchronize(g_ev1) != cudaSuccess) return -1.f;
+    float ms = -1.f;
+    if (cudaEventElapsedTime(&ms, g_ev0, g_ev1) != cudaSuccess) return -1.f;
+    return ms;
+}
+extern "C" uint64_t q4_cuda_launch_count(void) { return g_q4b_launches.load(); }
+extern "C" uint32_t q4_cuda_device_error(void) {
+    if (!g_q4b.ok) return 0xffffffffu;
+    if (cudaMemcpyAsync(g_q4b.err_h, g_q4b.err_d, 4, cudaMemcpyDeviceToHost, g_q4b.stream) !=
+            cudaSuccess ||
+        cudaStreamSynchronize(g_q4b.stream) != cudaSuccess)
+        return 0xffffffffu;
+    const uint32_t v = *g_q4b.err_h;
+    if (v) cudaMemsetAsync(g_q4b.err_d, 0, 4, g_q4b.stream);
+    return v;
+}

@@ -1,0 +1,6 @@
+// The whole library as one translation unit: the codebook lives in one
+// __constant__ array that every kernel file reads.
+#include "q4b_internal.cuh"
+
+#include "q4b_runtime.cu"
+#include "q4b_decode.cu"

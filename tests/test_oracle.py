@@ -1,0 +1,175 @@
+"""Pin the CPU oracle: the reference's closed-form known answers, the golden
+vectors generated from the reference's own CPU code, and (where the compiled
+reference is available) bit-for-bit agreement on fresh random inputs."""
+import os
+
+import numpy as np
+import pytest
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden", "iq3s_moe_small.npz")
+
+
+@pytest.fixture(scope="module")
+def gold():
+    return np.load(GOLD)
+
+
+def _bits(a):
+    return np.ascontiguousarray(a, np.float32).view(np.uint32)
+
+
+def test_kat_zero_block_dot_is_256(oracle, gold):
+    # src/q4_test.c:52-58: all-zero IQ3_S block, d = 1.0, x = 1 -> 256
+    blk = np.zeros(110, np.uint8)
+    blk[0:2] = np.array([0x3c00], np.uint16).view(np.uint8)
+    w = oracle.dequant_row(blk, 256)
+    assert abs(float(w.sum()) - 256.0) < 1e-2
+    assert abs(float(gold["kat"]) - 256.0) < 1e-2
+    xq = oracle.quant8(np.ones(256, np.float32))
+    assert abs(oracle.dot8(blk, xq, 256) - 256.0) < 1e-2
+    assert oracle.group_idot(blk, xq, 256).tolist() == [32 * 127] * 8
+
+
+def test_grid_entries_are_odd_below_16(oracle):
+    g = oracle.grid()
+    b = np.stack([(g >> (8 * j)) & 0xFF for j in range(4)])
+    assert ((b % 2) == 1).all() and (b <= 15).all()
+    assert g[0] == 0x01010101 and len(set(g.tolist())) == 512
+
+
+def test_f16_conversion_all_values(oracle):
+    h = np.arange(65536, dtype=np.uint16)
+    ref = h.view(np.float16).astype(np.float32)
+    got = np.array([oracle.f16_to_f32(int(v)) for v in h[::7]], np.float32)
+    exp = ref[::7]
+    nan = np.isnan(exp)
+    assert np.array_equal(np.isnan(got), nan)
+    assert np.array_equal(_bits(got[~nan]), _bits(exp[~nan]))
+
+
+def test_golden_dequant_quant_dots(oracle, gold):
+    H, F = int(gold["H"]), int(gold["F"])
+    packs, x = gold["packs"], gold["x"]
+    rb = H // 256 * 110
+    for r in range(4):
+        got = oracle.dequant_row(packs[0][r * rb:(r + 1) * rb], H)
+        assert np.array_equal(_bits(got), _bits(gold["deq"][r]))
+    xq = oracle.quant8(x)
+    assert xq.tobytes() == gold["xq"].tobytes()
+    assert (xq["q"][1] == 0).all() and xq["d"][1] == 0.0  # the all-zero group
+    dots = oracle.matvec8(packs[0][:F * rb], F, xq, H)
+    assert np.array_equal(_bits(dots), _bits(gold["gate_dots"]))
+
+
+def test_golden_expert_outputs(oracle, gold):
+    H, F = int(gold["H"]), int(gold["F"])
+    packs, x = gold["packs"], gold["x"]
+    y1 = oracle.expert_job([packs[0]], [1.0], x, H, F)
+    assert np.array_equal(_bits(y1), _bits(gold["y1"]))  # one expert: no ordering freedom
+    y2 = oracle.expert_job([packs[0], packs[1]], gold["wts"], x, H, F)
+    # two experts: the reference adds them in a racy order and may fuse the
+    # multiply into the add, so allow the last bits
+    assert np.allclose(y2, gold["y2"], rtol=0, atol=2e-6 * np.abs(gold["y2"]).max())
+
+
+def test_golden_router(oracle, gold):
+    x, nw = gold["x"], gold["norm_w"]
+    xn = oracle.rms_norm(x, nw, 1e-6)
+    assert np.array_equal(_bits(xn), _bits(gold["xn"]))
+    logits = gold["logits"]
+    p = oracle.softmax(logits)
+    assert np.array_equal(_bits(p), _bits(gold["probs"]))
+    ids, w = oracle.topk(p, 6, True)
+    assert ids.tolist() == gold["top_ids"].tolist()
+    assert np.array_equal(_bits(w), _bits(gold["top_w"]))
+    # the planted tie: equal values keep the lower index first
+    li = ids.tolist()
+    if 3 in li and 7 in li:
+        assert li.index(3) < li.index(7)
+    assert 7 not in li or 3 in li
+
+
+def test_integer_dot_matches_dequantised_weights(oracle):
+    rng = np.random.default_rng(5)
+    blk = rng.integers(0, 256, 220, dtype=np.uint8)
+    for b in range(2):
+        blk[110 * b:110 * b + 2] = np.array([0x3c00], np.uint16).view(np.uint8)  # d = 1
+    x = rng.standard_normal(512).astype(np.float32)
+    xq = oracle.quant8(x)
+    I = oracle.group_idot(blk, xq, 512)
+    w = oracle.dequant_row(blk, 512)
+    for g in range(16):
+        wv, ls, _ = oracle.unpack(blk[110 * (g // 8):110 * (g // 8 + 1)])
+        ib = g % 8
+        exp = int(np.dot(wv[32 * ib:32 * ib + 32].astype(np.int64), xq[g]["q"].astype(np.int64)))
+        assert I[g] == exp
+        # dequantised weight = d * ls * signed magnitude
+        assert np.array_equal(w[32 * g:32 * g + 32], wv[32 * ib:32 * ib + 32].astype(np.float32) * ls[ib])
+
+
+def test_quant8_properties(oracle):
+    rng = np.random.default_rng(7)
+    x = (rng.standard_normal(4096) * rng.uniform(1e-3, 1e3, 4096)).astype(np.float32)
+    xq = oracle.quant8(x)
+    xr = (xq["q"].astype(np.float32) * xq["d"][:, None]).ravel()
+    dmax = np.repeat(xq["d"], 32)
+    assert (np.abs(x - xr) <= 0.51 * dmax + 1e-30).all()  # src/q4_cpuexp.c selftest bound
+    assert (xq["bs"] == xq["q"].astype(np.int32).sum(1)).all()
+    assert np.abs(xq["q"]).max() == 127
+    # round-half-even at exact ties
+    t = np.zeros(32, np.float32)
+    t[0] = 127.0
+    t[1] = 0.5
+    t[2] = 1.5
+    t[3] = 2.5
+    t[4] = -0.5
+    q = oracle.quant8(t)["q"][0]
+    assert q[:5].tolist() == [127, 0, 2, 2, 0]
+
+
+def test_topk_edge_cases(oracle):
+    p = np.array([0.1, 0.4, 0.4, 0.05, 0.05], np.float32)
+    ids, w = oracle.topk(p, 3, False)
+    assert ids.tolist() == [1, 2, 0]
+    ids, w = oracle.topk(p, 9, True)  # k > n clamps
+    assert ids[:5].tolist() == [1, 2, 0, 3, 4]
+
+
+def test_mmq_order_dot_close_to_cpu_order(oracle):
+    rng = np.random.default_rng(11)
+    H = 2048
+    row = np.frombuffer(rng.integers(0, 256, H // 256 * 110, dtype=np.uint8).tobytes(), np.uint8).copy()
+    for b in range(H // 256):
+        row[110 * b:110 * b + 2] = np.array([0x2a66], np.uint16).view(np.uint8)
+    x = rng.standard_normal(H).astype(np.float32)
+    q, d = oracle.quant8_mmq(x)
+    a = oracle.dot_mmq(row, q, d, H)
+    b_ = oracle.dot8(row, oracle.quant8(x), H)
+    assert abs(a - b_) <= 2e-3 * (1 + abs(b_))
+    # half-away-from-zero vs half-even: differ only at exact ties
+    t = np.zeros(32, np.float32)
+    t[0], t[1], t[2] = 127.0, 0.5, 2.5
+    assert q.dtype == np.int8 and oracle.quant8_mmq(t)[0][:3].tolist() == [127, 1, 3]
+
+
+def test_against_compiled_reference(oracle, reference):
+    if reference is None:
+        pytest.skip("compiled reference CPU path not available on this machine")
+    assert reference.selftest() == 0
+    rng = np.random.default_rng(3)
+    H, F = 2048, 512
+    rb = H // 256 * 110
+    blocks = rng.integers(0, 256, size=(16, rb), dtype=np.uint8)
+    for r in range(16):
+        for b in range(H // 256):
+            dd = np.float16(abs(rng.standard_normal()) * 2.0 ** -6)
+            blocks[r, 110 * b:110 * b + 2] = np.array([dd]).view(np.uint8)
+    x = rng.standard_normal(H).astype(np.float32)
+    xq = oracle.quant8(x)
+    assert xq.tobytes() == reference.quant8(x).tobytes()
+    for r in range(16):
+        assert np.array_equal(_bits(oracle.dequant_row(blocks[r], H)),
+                              _bits(reference.dequant_row(blocks[r], H)))
+        a = np.float32(oracle.dot8(blocks[r], xq, H))
+        assert _bits(a) == _bits(np.float32(reference.dot8(blocks[r], xq, H)))
+        assert _bits(a) == _bits(np.float32(reference.dot8(blocks[r], xq, H, avx2=True)))
