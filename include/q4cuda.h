@@ -164,6 +164,13 @@ bool q4_cuda_moe_decode(const uint8_t *base, uint64_t stride, uint64_t og, uint6
                         uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
                         float *d_y, int32_t *d_ids, float *d_wts);
 
+/* Seeded synthetic tensors generated on the device (benchmark and smoke
+ * support, no reference counterpart): n_blocks IQ3_S super-blocks with
+ * fp16 d = |N(0,1)| * 2^-6 and uniform random payload bytes; n fp32 values
+ * N(mean, std).  Content depends only on (seed, index). */
+bool q4_cuda_synth_iq3s(uint8_t *d_out, uint64_t n_blocks, uint64_t seed);
+bool q4_cuda_synth_normal(float *d_out, uint64_t n, uint64_t seed, float mean, float std);
+
 /* Device-side timing on the compute stream, for benchmarks: records an event
  * pair around whatever is enqueued between begin and end; ms() waits for the
  * end event. */

@@ -76,6 +76,8 @@ SIGNATURES = {
     "q4_cuda_iq3s_idot": (b, [vp, u64, u64, vp, vp]),
     "q4_cuda_moe_decode": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32, u32,
                                vp, vp, vp]),
+    "q4_cuda_synth_iq3s": (b, [vp, u64, u64]),
+    "q4_cuda_synth_normal": (b, [vp, u64, u64, f32, f32]),
     "q4_cuda_timer_begin": (b, []),
     "q4_cuda_timer_end": (b, []),
     "q4_cuda_timer_ms": (f32, []),

@@ -91,7 +91,11 @@ __device__ __forceinline__ uint32_t q4b_sign_mask4(uint32_t nib) {
     // bit j lands on bit 8j+7 (no two products share a position), then the
     // permute replicates each byte's top bit over the byte.
     const uint32_t t = (nib & 0xfu) * 0x10204080u;
-    return __byte_perm(t, 0, 0xba98);
+    uint32_t m;
+    // prmt with selector bit 3 set: copy the top bit of the chosen byte to all
+    // eight bits (__byte_perm drops that selector bit, so use the instruction).
+    asm("prmt.b32 %0, %1, %1, 0xba98;" : "=r"(m) : "r"(t));
+    return m;
 }
 
 // Integer dot of one 32-weight sub-block with 32 int8 activations.
