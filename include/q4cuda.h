@@ -55,6 +55,9 @@ bool q4_hip_d2h_async(void *h, const void *d, uint64_t n);
 bool q4_hip_fill(float *d, float v, uint64_t n);
 bool q4_hip_copy_async(float *d, const float *s, uint64_t n);
 uint64_t q4_hip_vram_free(void);
+/* Page-locked host memory for asynchronous copies (src/q4.h:1251-1252). */
+void *q4_hip_host_alloc_coh(size_t n);
+void q4_hip_host_free_coh(void *p);
 
 /* ---------------- expert arenas (src/q4.h:842-851,1402-1413) ----------------
  * A fixed-stride device array of packed experts, pack = gate rows | up rows |
@@ -163,6 +166,32 @@ bool q4_cuda_moe_decode(const uint8_t *base, uint64_t stride, uint64_t og, uint6
                         const float *d_norm_w, float eps, const float *d_router,
                         uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
                         float *d_y, int32_t *d_ids, float *d_wts);
+
+/* Resident storage format of an arena.  By default q4_hip_experts_put*_a rewrites
+ * each pack, in place and at the same size, into the library's tiled form of
+ * IQ3_S (every run of eight 110-byte super-blocks regrouped by field so that all
+ * device loads are aligned); base/stride/offset addressing is unchanged and every
+ * entry point recognises pointers into a tiled arena.  Slot sizes must then be a
+ * multiple of 880 bytes (an arena whose slot size is not stays in the engine's
+ * byte order).  No reference counterpart.
+ *   set_tiled_default(0/1): format of arenas allocated afterwards (also: env
+ *     Q4B_TILED=0);
+ *   tiled_a: 1 if the arena is tiled;
+ *   retile_a: convert slots that were filled on the device in engine byte order
+ *     (e.g. by q4_cuda_synth_iq3s);
+ *   get_a: copy a slot back to the host in the engine's byte order (synchronous). */
+void q4_cuda_set_tiled_default(int on);
+int q4_cuda_experts_tiled_a(int arena);
+bool q4_cuda_experts_retile_a(int arena, uint32_t first_slot, uint32_t n_slots);
+bool q4_cuda_experts_get_a(int arena, uint32_t slot, uint8_t *host, uint64_t n);
+
+/* The same layer for a caller that holds HOST buffers (h_x in, h_y out, n_embd
+ * floats each, page-locked for speed): copy in, run, copy out, wait. */
+bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou,
+                             uint64_t od, int32_t shared_slot, const float *h_x,
+                             const float *d_norm_w, float eps, const float *d_router,
+                             uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
+                             float *h_y);
 
 /* Seeded synthetic tensors generated on the device (benchmark and smoke
  * support, no reference counterpart): n_blocks IQ3_S super-blocks with

@@ -69,9 +69,9 @@ def build_ref(ref_dir=DEFAULT_REF, force=False):
     # The reference's own flags for these two objects (its Makefile:6,40-41).
     _run(["gcc", "-O2", "-O3", "-mavx2", "-mfma", "-mf16c", "-pthread", "-fPIC",
           "-w", "-I", ref_src, "-c", "-o", o_shim, shim])
-    _run(["gcc", "-O2", "-pthread", "-fPIC", "-w", "-I", ref_src, "-c", "-o",
+    _run(["gcc", "-O2", "-pthread", "-fopenmp", "-fPIC", "-w", "-I", ref_src, "-c", "-o",
           o_quant, quant])
-    _run(["gcc", "-shared", "-pthread", "-o", REF_SO, o_shim, o_quant, "-lm"])
+    _run(["gcc", "-shared", "-pthread", "-fopenmp", "-o", REF_SO, o_shim, o_quant, "-lm"])
     return REF_SO
 
 

@@ -196,6 +196,7 @@ class Reference:
         L.q4ref_dot_f32.restype = C.c_float
         L.q4ref_dot_f32.argtypes = [_u8p, _f32p, C.c_uint64]
         L.q4ref_time_jobs.restype = C.c_double
+        L.q4ref_time_layers.restype = C.c_double
 
     def quant8(self, x):
         x = _f32(x).ravel()
@@ -300,6 +301,35 @@ class Reference:
                                      C.c_uint32(n_ff), _p(y, _f32p))
         assert t >= 0, t
         return float(t)
+
+
+    def time_layers(self, layers, topk, jobs, x, n_embd, n_ff, eps=1e-6):
+        """layers: list of dicts with 'experts' [E, pack], 'shared' [pack], 'router'
+        [E, n_embd], 'norm_w' [n_embd].  Job j runs layer j % len(layers) on
+        x[j % len(x)].  Returns (seconds, ids [jobs, topk], last y)."""
+        n_expert = layers[0]["experts"].shape[0]
+        keep = []
+        ptrs = []
+        for L in layers:
+            ex = _u8(L["experts"])
+            sh = _u8(L["shared"])
+            keep += [ex, sh]
+            ptrs += [ex.ctypes.data + e * ex.shape[1] for e in range(n_expert)]
+            ptrs.append(sh.ctypes.data)
+        arr = (C.c_void_p * len(ptrs))(*ptrs)
+        routers = [_f32(L["router"]) for L in layers]
+        norms = [_f32(L["norm_w"]) for L in layers]
+        r_arr = (C.c_void_p * len(layers))(*[r.ctypes.data for r in routers])
+        n_arr = (C.c_void_p * len(layers))(*[n.ctypes.data for n in norms])
+        x = _f32(x)
+        y = np.zeros(n_embd, np.float32)
+        ids = np.zeros((jobs, topk), np.int32)
+        t = self.lib.q4ref_time_layers(arr, C.c_uint32(len(layers)), C.c_uint32(n_expert), r_arr,
+                                       n_arr, C.c_float(eps), C.c_uint32(topk), C.c_uint32(jobs),
+                                       _p(x, _f32p), C.c_uint32(x.shape[0]), C.c_uint32(n_embd),
+                                       C.c_uint32(n_ff), _p(y, _f32p), _p(ids, _i32p))
+        assert t >= 0, t
+        return float(t), ids, y
 
 
 _ORACLE = None

@@ -181,3 +181,46 @@ double q4ref_time_jobs(const uint8_t *const *packs, uint32_t n_packs,
     clock_gettime(CLOCK_MONOTONIC, &t1);
     return (double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec);
 }
+
+/* Timed loop for the CPU baseline of a whole MoE layer, one token per job:
+ * RMSNorm -> fp32 router GEMV -> softmax -> top-k (src/q4_quant.c:595-755)
+ * -> one expert job with the k picks plus the shared expert at weight 1
+ * (src/q4_cpuexp.c:2503).  Layer l of job j is j % n_layers; its packs are
+ * packs[l * (n_expert + 1) ..], the shared expert last.  Returns seconds. */
+double q4ref_time_layers(const uint8_t *const *packs, uint32_t n_layers,
+                         uint32_t n_expert, const float *const *routers,
+                         const float *const *norm_w, float eps, uint32_t topk,
+                         uint32_t jobs, const float *x, uint32_t n_x,
+                         uint32_t n_embd, uint32_t n_ff, float *y,
+                         int32_t *ids_out) {
+    float *xn = malloc(sizeof(float) * n_embd);
+    float *p = malloc(sizeof(float) * n_expert);
+    int32_t ids[CPX_MAX_E];
+    float wts[CPX_MAX_E];
+    if (!xn || !p || topk + 1 > CPX_MAX_E) return -1.0;
+    struct timespec t0, t1;
+    clock_gettime(CLOCK_MONOTONIC, &t0);
+    for (uint32_t j = 0; j < jobs; j++) {
+        const uint32_t l = j % n_layers;
+        shim_setup(packs + (size_t)l * (n_expert + 1), n_expert + 1, n_embd, n_ff);
+        q4_rms_norm(x + (size_t)(j % n_x) * n_embd, norm_w[l], xn, n_embd, eps);
+        memset(p, 0, sizeof(float) * n_expert);
+        q4_gemv(Q4_T_F32, (const uint8_t *)routers[l], n_expert, n_embd, xn, p, 1.0f);
+        q4_softmax(p, n_expert);
+        q4_topk(p, n_expert, topk, ids, wts, true);
+        ids[topk] = (int32_t)n_expert;
+        wts[topk] = 1.0f;
+        uint64_t tag = 0;
+        int s;
+        while ((s = q4_cpuex_dispatch2(&g_shim_gguf, &g_shim, 0, xn, ids, wts,
+                                       topk + 1, y, &tag)) == -1)
+            q4_cpuex_retire();
+        if (s < 0) return -1.0;
+        if (!q4_cpuex_join_tag(s, tag)) return -2.0;
+        if (ids_out) memcpy(ids_out + (size_t)j * topk, ids, sizeof(int32_t) * topk);
+    }
+    clock_gettime(CLOCK_MONOTONIC, &t1);
+    free(xn);
+    free(p);
+    return (double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec);
+}

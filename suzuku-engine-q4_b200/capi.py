@@ -36,6 +36,8 @@ SIGNATURES = {
     "q4_hip_fill": (b, [vp, f32, u64]),
     "q4_hip_copy_async": (b, [vp, vp, u64]),
     "q4_hip_vram_free": (u64, []),
+    "q4_hip_host_alloc_coh": (vp, [sz]),
+    "q4_hip_host_free_coh": (None, [vp]),
     "q4_hip_experts_alloc_a": (b, [C.c_int, u32, u64]),
     "q4_hip_experts_free_a": (None, [C.c_int]),
     "q4_hip_experts_n_a": (u32, [C.c_int]),
@@ -76,6 +78,12 @@ SIGNATURES = {
     "q4_cuda_iq3s_idot": (b, [vp, u64, u64, vp, vp]),
     "q4_cuda_moe_decode": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32, u32,
                                vp, vp, vp]),
+    "q4_cuda_set_tiled_default": (None, [C.c_int]),
+    "q4_cuda_experts_tiled_a": (C.c_int, [C.c_int]),
+    "q4_cuda_experts_retile_a": (b, [C.c_int, u32, u32]),
+    "q4_cuda_experts_get_a": (b, [C.c_int, u32, vp, u64]),
+    "q4_cuda_moe_decode_host": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32,
+                                    u32, vp]),
     "q4_cuda_synth_iq3s": (b, [vp, u64, u64]),
     "q4_cuda_synth_normal": (b, [vp, u64, u64, f32, f32]),
     "q4_cuda_timer_begin": (b, []),

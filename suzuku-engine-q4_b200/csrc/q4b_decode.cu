@@ -6,13 +6,17 @@
 // Reference counterparts: xq8_k (src/q4_rocm.cu:5149), wmoe_iq3_gu_q8
 // (:3912-3989), wmoe_iq3_ya_q8 (:4081-4120), softmax_topk_k (:12703),
 // grouped_rms_k (:11285); arithmetic contract: src/q4_cpuexp.c:605-637,855-892.
-#include "q4b_internal.cuh"
+#include "q4b_tile.cuh"
 
 #include <atomic>
 
 #include "../../include/q4cuda.h"
 
 extern std::atomic<uint64_t> g_q4b_launches;
+bool q4b_ptr_tiled(const void *p);
+bool q4b_moe_decode_fused(const uint8_t *, uint64_t, uint64_t, uint64_t, uint64_t, int32_t, const float *,
+                          const float *, float, const float *, uint32_t, uint32_t, uint32_t, uint32_t,
+                          float *, int32_t *, float *);
 
 #define Q4B_X_SLICE 64u  // scratch slice that holds the quantised input row
 
@@ -130,7 +134,54 @@ __device__ __forceinline__ float iq3_block_d(const uint8_t *blk) {
     return __half2float(__ushort_as_half((unsigned short)q4b_ld_u16(blk)));
 }
 
+// The same fields addressed by block number within a matrix, for either storage
+// format.  mat = first byte of the matrix, bi = super-block number (row-major),
+// ib = sub-block.  TILED: the library's arena format (q4b_tile.cuh), where the
+// sign word comes back bit-permuted; otherwise the engine's 110-byte records.
+struct Iq3Fields {
+    uint32_t qs_lo, qs_hi, qh, sg, ls;
+    float d;
+};
+template <bool TILED>
+__device__ __forceinline__ Iq3Fields iq3_fields(const uint8_t *mat, uint64_t bi, uint32_t ib) {
+    Iq3Fields f;
+    if (TILED) {
+        const uint8_t *t = mat + (bi >> 3) * Q4B_TILE_BYTES;
+        const uint32_t b = (uint32_t)(bi & 7u);
+        const uint2 qs = *reinterpret_cast<const uint2 *>(t + Q4B_TILE_OFF_QS + 64u * b + 8u * ib);
+        f.qs_lo = qs.x;
+        f.qs_hi = qs.y;
+        f.qh = t[Q4B_TILE_OFF_QH + 8u * b + ib];
+        f.sg = *reinterpret_cast<const uint32_t *>(t + Q4B_TILE_OFF_SG + 32u * b + 4u * ib);
+        const uint32_t sb = t[Q4B_TILE_OFF_SC + 4u * b + (ib >> 1)];
+        f.ls = 1u + 2u * ((ib & 1u) ? (sb >> 4) : (sb & 15u));
+        f.d = __half2float(*reinterpret_cast<const __half *>(t + 2u * b));
+    } else {
+        const uint8_t *blk = mat + bi * Q4B_IQ3S_BYTES;
+        const Iq3Group g = iq3_load_group(blk, ib);
+        f.qs_lo = g.qs_lo;
+        f.qs_hi = g.qs_hi;
+        f.qh = g.qh;
+        f.sg = g.sg;
+        f.ls = g.ls;
+        f.d = iq3_block_d(blk);
+    }
+    return f;
+}
+// Sign of element e (0..31) of a group from its sign word.
+template <bool TILED>
+__device__ __forceinline__ bool iq3_neg(uint32_t sg, uint32_t e) {
+    return TILED ? ((sg >> (8u * (e & 3u) + 7u - (e >> 2))) & 1u) : ((sg >> e) & 1u);
+}
+template <bool TILED>
+__device__ __forceinline__ int32_t iq3_idot(const Iq3Fields &f, const uint32_t *tab, const int *q,
+                                            int32_t qsum) {
+    return TILED ? q4b_tile_group_idot<1>(f.qs_lo, f.qs_hi, f.qh, f.sg, tab, q, qsum)
+                 : q4b_group_idot(f.qs_lo, f.qs_hi, f.qh, f.sg, tab, q, qsum);
+}
+
 // fp32 dequantisation, one thread per 32-weight sub-block.
+template <bool TILED>
 __global__ void iq3s_dequant_k(const uint8_t *__restrict__ w, uint64_t n_groups,
                                float *__restrict__ out) {
     __shared__ uint32_t tab[512];
@@ -138,11 +189,9 @@ __global__ void iq3s_dequant_k(const uint8_t *__restrict__ w, uint64_t n_groups,
     __syncthreads();
     const uint64_t g = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (g >= n_groups) return;
-    const uint8_t *blk = w + (g >> 3) * Q4B_IQ3S_BYTES;
-    const uint32_t ib = (uint32_t)(g & 7u);
-    const Iq3Group f = iq3_load_group(blk, ib);
+    const Iq3Fields f = iq3_fields<TILED>(w, g >> 3, (uint32_t)(g & 7u));
     // src/q4_quant.c:397-409: db = d * (1 + 2 s); value = db * magnitude * (+-1)
-    const float db = __fmul_rn(iq3_block_d(blk), (float)f.ls);
+    const float db = __fmul_rn(f.d, (float)f.ls);
     float *o = out + g * 32u;
     for (int k = 0; k < 8; k++) {
         const uint32_t wq = k < 4 ? f.qs_lo : f.qs_hi;
@@ -150,13 +199,13 @@ __global__ void iq3s_dequant_k(const uint8_t *__restrict__ w, uint64_t n_groups,
         const uint32_t c = tab[idx];
         for (int j = 0; j < 4; j++) {
             const float mag = (float)(2u * ((c >> (8 * j)) & 0xffu) + 1u);
-            const bool neg = (f.sg >> (4 * k + j)) & 1u;
-            o[4 * k + j] = __fmul_rn(__fmul_rn(db, mag), neg ? -1.f : 1.f);
+            o[4 * k + j] = __fmul_rn(__fmul_rn(db, mag), iq3_neg<TILED>(f.sg, 4 * k + j) ? -1.f : 1.f);
         }
     }
 }
 
 // Per-group integer dots of nrows rows against one quantised vector.
+template <bool TILED>
 __global__ void iq3s_idot_k(const uint8_t *__restrict__ w, uint64_t nrows, uint32_t ng,
                             const int8_t *__restrict__ q, int32_t *__restrict__ I) {
     __shared__ uint32_t tab[512];
@@ -166,8 +215,7 @@ __global__ void iq3s_idot_k(const uint8_t *__restrict__ w, uint64_t nrows, uint3
     if (t >= nrows * ng) return;
     const uint64_t r = t / ng;
     const uint32_t g = (uint32_t)(t - r * ng);
-    const uint8_t *blk = w + (r * (ng >> 3) + (g >> 3)) * Q4B_IQ3S_BYTES;
-    const Iq3Group f = iq3_load_group(blk, g & 7u);
+    const Iq3Fields f = iq3_fields<TILED>(w, r * (ng >> 3) + (g >> 3), g & 7u);
     const int *qg = reinterpret_cast<const int *>(q) + g * 8u;
     int qv[8];
     int qsum = 0;
@@ -175,7 +223,7 @@ __global__ void iq3s_idot_k(const uint8_t *__restrict__ w, uint64_t nrows, uint3
         qv[k] = qg[k];
         qsum = __dp4a(qv[k], 0x01010101, qsum);
     }
-    I[t] = q4b_group_idot(f.qs_lo, f.qs_hi, f.qh, f.sg, tab, qv, qsum);
+    I[t] = iq3_idot<TILED>(f, tab, qv, qsum);
 }
 
 // ------------------------------------------------------------------ router softmax + top-k
@@ -256,6 +304,7 @@ __global__ void softmax_topk_k(const float *__restrict__ logits, uint32_t n, uin
 // ------------------------------------------------------------------ gate/up + SwiGLU
 // grid (n_ff/8, experts), 8 warps per block, one warp per hidden unit f:
 // h[e][f] = silu(gate_f . xq) * (up_f . xq).
+template <bool TILED>
 __global__ void moe_gu_k(const uint8_t *__restrict__ bg, const uint8_t *__restrict__ bu,
                          uint64_t stride, const int32_t *__restrict__ slots,
                          const int32_t *__restrict__ n_dev, const int8_t *__restrict__ xq,
@@ -280,26 +329,23 @@ __global__ void moe_gu_k(const uint8_t *__restrict__ bg, const uint8_t *__restri
     const uint32_t f = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (f >= n_ff) return;
     const uint32_t lane = threadIdx.x & 31u;
-    const uint64_t rb = (uint64_t)(in_dim >> 8) * Q4B_IQ3S_BYTES;
-    const uint64_t off = (uint64_t)slots[e] * stride + (uint64_t)f * rb;
-    const uint8_t *wg = bg + off, *wu = bu + off;
+    const uint32_t nbr = in_dim >> 8;  // super-blocks per row
+    const uint8_t *wg = bg + (uint64_t)slots[e] * stride, *wu = bu + (uint64_t)slots[e] * stride;
     float ag = 0.f, au = 0.f;
     for (uint32_t g = lane; g < ng; g += 32) {
-        const uint32_t blk = g >> 3, ib = g & 7u;
+        const uint64_t bi = (uint64_t)f * nbr + (g >> 3);
         const int *qv = sq + g * 8u;
         const float dx = sd[g];
         const int qsum = sb[g];
         {
-            const uint8_t *p = wg + (uint64_t)blk * Q4B_IQ3S_BYTES;
-            const Iq3Group fg = iq3_load_group(p, ib);
-            const int I = q4b_group_idot(fg.qs_lo, fg.qs_hi, fg.qh, fg.sg, tab, qv, qsum);
-            ag = fmaf(__fmul_rn(iq3_block_d(p), dx), (float)(I * (int)fg.ls), ag);
+            const Iq3Fields fg = iq3_fields<TILED>(wg, bi, g & 7u);
+            const int I = iq3_idot<TILED>(fg, tab, qv, qsum);
+            ag = fmaf(__fmul_rn(fg.d, dx), (float)(I * (int)fg.ls), ag);
         }
         {
-            const uint8_t *p = wu + (uint64_t)blk * Q4B_IQ3S_BYTES;
-            const Iq3Group fg = iq3_load_group(p, ib);
-            const int I = q4b_group_idot(fg.qs_lo, fg.qs_hi, fg.qh, fg.sg, tab, qv, qsum);
-            au = fmaf(__fmul_rn(iq3_block_d(p), dx), (float)(I * (int)fg.ls), au);
+            const Iq3Fields fg = iq3_fields<TILED>(wu, bi, g & 7u);
+            const int I = iq3_idot<TILED>(fg, tab, qv, qsum);
+            au = fmaf(__fmul_rn(fg.d, dx), (float)(I * (int)fg.ls), au);
         }
     }
     ag = q4b_warp_sum(ag);
@@ -311,6 +357,7 @@ __global__ void moe_gu_k(const uint8_t *__restrict__ bg, const uint8_t *__restri
 // grid (n_embd/8), one warp per output row r:
 // y[r] += sum_e wts[e] * (down_e[r] . hq_e), experts visited in list order by a
 // fixed lane assignment, so the result is reproducible run to run.
+template <bool TILED>
 __global__ void moe_ya_k(const uint8_t *__restrict__ bd, uint64_t stride,
                          const int32_t *__restrict__ slots, const float *__restrict__ wts,
                          uint32_t n_host, const int32_t *__restrict__ n_dev,
@@ -325,20 +372,18 @@ __global__ void moe_ya_k(const uint8_t *__restrict__ bd, uint64_t stride,
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t n = n_dev ? (uint32_t)*n_dev : n_host;
     const uint32_t ng = n_ff >> 5;
-    const uint64_t rb = (uint64_t)(n_ff >> 8) * Q4B_IQ3S_BYTES;
+    const uint32_t nbr = n_ff >> 8;
     float acc = 0.f;
     for (uint32_t it = lane; it < n * ng; it += 32) {
         const uint32_t e = it / ng, g = it - e * ng;
-        const uint8_t *p = bd + (uint64_t)slots[e] * stride + (uint64_t)r * rb +
-                           (uint64_t)(g >> 3) * Q4B_IQ3S_BYTES;
-        const Iq3Group fg = iq3_load_group(p, g & 7u);
+        const Iq3Fields fg = iq3_fields<TILED>(bd + (uint64_t)slots[e] * stride,
+                                              (uint64_t)r * nbr + (g >> 3), g & 7u);
         const int *qg = reinterpret_cast<const int *>(hq + (uint64_t)e * q_slice) + g * 8u;
         int qv[8];
 #pragma unroll
         for (int k = 0; k < 8; k++) qv[k] = qg[k];
-        const int I = q4b_group_idot(fg.qs_lo, fg.qs_hi, fg.qh, fg.sg, tab, qv,
-                                     hbs[(uint64_t)e * d_slice + g]);
-        const float dd = __fmul_rn(iq3_block_d(p), hd[(uint64_t)e * d_slice + g]);
+        const int I = iq3_idot<TILED>(fg, tab, qv, hbs[(uint64_t)e * d_slice + g]);
+        const float dd = __fmul_rn(fg.d, hd[(uint64_t)e * d_slice + g]);
         acc = fmaf(__fmul_rn(wts[e], dd), (float)(I * (int)fg.ls), acc);
     }
     acc = q4b_warp_sum(acc);
@@ -346,6 +391,7 @@ __global__ void moe_ya_k(const uint8_t *__restrict__ bd, uint64_t stride,
 }
 
 // IQ3_S rows times fp32 activations (shared-expert style GEMV), warp per row.
+template <bool TILED>
 __global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, uint32_t ncols,
                                 const float *__restrict__ x, float *__restrict__ y, float scale) {
     __shared__ uint32_t tab[512];
@@ -355,13 +401,11 @@ __global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, u
     if (r >= nrows) return;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t ng = ncols >> 5;
-    const uint8_t *row = w + r * (uint64_t)(ncols >> 8) * Q4B_IQ3S_BYTES;
     const float *xb = x + (uint64_t)blockIdx.y * ncols;
     float acc = 0.f;
     for (uint32_t g = lane; g < ng; g += 32) {
-        const uint8_t *p = row + (uint64_t)(g >> 3) * Q4B_IQ3S_BYTES;
-        const Iq3Group f = iq3_load_group(p, g & 7u);
-        const float db = iq3_block_d(p) * (float)f.ls;
+        const Iq3Fields f = iq3_fields<TILED>(w, r * (uint64_t)(ncols >> 8) + (g >> 3), g & 7u);
+        const float db = f.d * (float)f.ls;
         float sub = 0.f;
         for (int k = 0; k < 8; k++) {
             const uint32_t wq = k < 4 ? f.qs_lo : f.qs_hi;
@@ -370,7 +414,7 @@ __global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, u
             for (int j = 0; j < 4; j++) {
                 const float mag = (float)(2u * ((c >> (8 * j)) & 0xffu) + 1u);
                 const float xv = xb[g * 32u + 4 * k + j];
-                sub += ((f.sg >> (4 * k + j)) & 1u) ? -mag * xv : mag * xv;
+                sub += iq3_neg<TILED>(f.sg, 4 * k + j) ? -mag * xv : mag * xv;
             }
         }
         acc += db * sub;
@@ -408,16 +452,26 @@ bool moe_exec_tail(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
     const float *xd = s.xd + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
     const int32_t *xbs = s.xbs + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
     const size_t sm = 2048 + in_dim + 8 * (in_dim >> 5);
-    moe_gu_k<<<dim3((n_ff + 7) / 8, ne), 256, sm, s.stream>>>(base + og, base + ou, stride, d_slots,
-                                                             d_n, xq, xd, xbs, in_dim, n_ff, d_h);
+    const bool tiled = q4b_ptr_tiled(base);
+    if (tiled)
+        moe_gu_k<true><<<dim3((n_ff + 7) / 8, ne), 256, sm, s.stream>>>(
+            base + og, base + ou, stride, d_slots, d_n, xq, xd, xbs, in_dim, n_ff, d_h);
+    else
+        moe_gu_k<false><<<dim3((n_ff + 7) / 8, ne), 256, sm, s.stream>>>(
+            base + og, base + ou, stride, d_slots, d_n, xq, xd, xbs, in_dim, n_ff, d_h);
     g_q4b_launches++;
     if (!q4b_launch_ok("moe_gu")) return false;
     if (!launch_quant8(d_h, n_ff, n_ff, ne, s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32,
                        d_n))
         return false;
-    moe_ya_k<<<(n_embd + 7) / 8, 256, 0, s.stream>>>(base + od, stride, d_slots, d_wts, n_host, d_n,
-                                                    s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN,
-                                                    Q4B_XQ_MAXLEN / 32, n_ff, n_embd, d_y);
+    if (tiled)
+        moe_ya_k<true><<<(n_embd + 7) / 8, 256, 0, s.stream>>>(
+            base + od, stride, d_slots, d_wts, n_host, d_n, s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN,
+            Q4B_XQ_MAXLEN / 32, n_ff, n_embd, d_y);
+    else
+        moe_ya_k<false><<<(n_embd + 7) / 8, 256, 0, s.stream>>>(
+            base + od, stride, d_slots, d_wts, n_host, d_n, s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN,
+            Q4B_XQ_MAXLEN / 32, n_ff, n_embd, d_y);
     g_q4b_launches++;
     return q4b_launch_ok("moe_ya");
 }
@@ -541,7 +595,10 @@ extern "C" bool q4_hip_gemv_dd_n(uint32_t ggml_type, const uint8_t *d_w, uint64_
                                                   ncols, d_x, d_y, scale);
     } else if (ggml_type == Q4_T_IQ3_S) {
         if (ncols % Q4B_QK) return false;
-        gemv_iq3s_f32_k<<<grid, 256, 0, g_q4b.stream>>>(d_w, nrows, (uint32_t)ncols, d_x, d_y, scale);
+        if (q4b_ptr_tiled(d_w))
+            gemv_iq3s_f32_k<true><<<grid, 256, 0, g_q4b.stream>>>(d_w, nrows, (uint32_t)ncols, d_x, d_y, scale);
+        else
+            gemv_iq3s_f32_k<false><<<grid, 256, 0, g_q4b.stream>>>(d_w, nrows, (uint32_t)ncols, d_x, d_y, scale);
     } else {
         return false;
     }
@@ -567,7 +624,10 @@ extern "C" bool q4_cuda_iq3s_dequant(const uint8_t *d_w, uint64_t nrows, uint64_
                                      float *d_out) {
     if (!g_q4b.ok || !d_w || !d_out || nrows == 0 || ncols == 0 || (ncols % Q4B_QK)) return false;
     const uint64_t ngr = nrows * ncols / 32;
-    iq3s_dequant_k<<<(unsigned)((ngr + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, ngr, d_out);
+    if (q4b_ptr_tiled(d_w))
+        iq3s_dequant_k<true><<<(unsigned)((ngr + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, ngr, d_out);
+    else
+        iq3s_dequant_k<false><<<(unsigned)((ngr + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, ngr, d_out);
     g_q4b_launches++;
     return q4b_launch_ok("iq3s_dequant");
 }
@@ -577,8 +637,12 @@ extern "C" bool q4_cuda_iq3s_idot(const uint8_t *d_w, uint64_t nrows, uint64_t n
     if (!g_q4b.ok || !d_w || !d_q || !d_I || nrows == 0 || ncols == 0 || (ncols % Q4B_QK))
         return false;
     const uint64_t items = nrows * (ncols / 32);
-    iq3s_idot_k<<<(unsigned)((items + 255) / 256), 256, 0, g_q4b.stream>>>(
-        d_w, nrows, (uint32_t)(ncols / 32), d_q, d_I);
+    if (q4b_ptr_tiled(d_w))
+        iq3s_idot_k<true><<<(unsigned)((items + 255) / 256), 256, 0, g_q4b.stream>>>(
+            d_w, nrows, (uint32_t)(ncols / 32), d_q, d_I);
+    else
+        iq3s_idot_k<false><<<(unsigned)((items + 255) / 256), 256, 0, g_q4b.stream>>>(
+            d_w, nrows, (uint32_t)(ncols / 32), d_q, d_I);
     g_q4b_launches++;
     return q4b_launch_ok("iq3s_idot");
 }
@@ -594,6 +658,15 @@ extern "C" bool q4_cuda_moe_decode(const uint8_t *base, uint64_t stride, uint64_
     if (!s.ok || !base || !d_x || !d_router || !d_y) return false;
     if (!shape_ok(Q4_T_IQ3_S, Q4_T_IQ3_S, Q4_T_IQ3_S, n_embd, n_ff)) return false;
     if (n_expert == 0 || n_expert > 1024 || topk == 0 || topk > 63 || topk > n_expert) return false;
+    // The single persistent kernel when it applies (Q4B_FUSED=0 forces the chain).
+    static int fused_on = -1;
+    if (fused_on < 0) {
+        const char *e = getenv("Q4B_FUSED");
+        fused_on = !(e && e[0] == '0');
+    }
+    if (fused_on && q4b_moe_decode_fused(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps,
+                                         d_router, n_expert, topk, n_embd, n_ff, d_y, d_ids, d_wts))
+        return true;
     int8_t *xq = s.xq + (size_t)Q4B_X_SLICE * Q4B_XQ_MAXLEN;
     float *xd = s.xd + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
     int32_t *xbs = s.xbs + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
@@ -620,5 +693,26 @@ extern "C" bool q4_cuda_moe_decode(const uint8_t *base, uint64_t stride, uint64_
     if (d_wts &&
         cudaMemcpyAsync(d_wts, s.r_wts, topk * 4, cudaMemcpyDeviceToDevice, s.stream) != cudaSuccess)
         return false;
+    return true;
+}
+
+// The same layer call for a caller that holds host buffers: copies the hidden
+// state in, runs the layer, copies the result out and waits for it.
+extern "C" bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, uint64_t og,
+                                        uint64_t ou, uint64_t od, int32_t shared_slot,
+                                        const float *h_x, const float *d_norm_w, float eps,
+                                        const float *d_router, uint32_t n_expert, uint32_t topk,
+                                        uint32_t n_embd, uint32_t n_ff, float *h_y) {
+    Q4bState &s = g_q4b;
+    if (!s.ok || !h_x || !h_y || n_embd == 0 || n_embd > Q4B_XQ_MAXLEN) return false;
+    // staging rows: the last token row of the norm scratch (in) and the row before it (out)
+    float *d_x = s.xn + (size_t)(Q4B_MAX_TOK - 1) * Q4B_XQ_MAXLEN;
+    float *d_y = s.xn + (size_t)(Q4B_MAX_TOK - 2) * Q4B_XQ_MAXLEN;
+    Q4B_CHECK(cudaMemcpyAsync(d_x, h_x, (size_t)n_embd * 4, cudaMemcpyHostToDevice, s.stream));
+    if (!q4_cuda_moe_decode(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps, d_router,
+                            n_expert, topk, n_embd, n_ff, d_y, nullptr, nullptr))
+        return false;
+    Q4B_CHECK(cudaMemcpyAsync(h_y, d_y, (size_t)n_embd * 4, cudaMemcpyDeviceToHost, s.stream));
+    Q4B_CHECK(cudaStreamSynchronize(s.stream));
     return true;
 }

@@ -1,7 +1,7 @@
 // Lifecycle, memory, expert arenas, graphs and timers of the q4cuda library.
 // Counterpart of the reference device layer's plumbing (src/q4_rocm.cu:507-560,
 // 661-801 for streams and arenas); the arithmetic lives in the other files.
-#include "q4b_internal.cuh"
+#include "q4b_tile.cuh"
 
 #include <atomic>
 #include <string.h>
@@ -21,8 +21,81 @@ struct Arena {
     uint32_t n_slots;
     uint64_t stride;
     uint64_t bytes;
+    bool tiled;  // slots hold the tiled IQ3_S format (q4b_tile.cuh)
 };
 Arena g_arena[4] = {};
+
+// Environment knob, read once: Q4B_TILED=0 keeps arenas in the engine's byte
+// layout (the fused kernels then do not apply and the launch chain runs).
+int g_tiled_default = -1;
+bool tiled_default() {
+    if (g_tiled_default < 0) {
+        const char *e = getenv("Q4B_TILED");
+        g_tiled_default = !(e && e[0] == '0');
+    }
+    return g_tiled_default != 0;
+}
+
+// In-place regrouping of runs of eight 110-byte super-blocks into tiles
+// (forward) or back (inverse).  One warp per tile via shared memory.
+template <bool FORWARD>
+__global__ void tile_permute_k(uint8_t *data, uint64_t n_tiles) {
+    __shared__ __align__(16) uint8_t buf[8][Q4B_TILE_BYTES];
+    const uint32_t w = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint64_t t = (uint64_t)blockIdx.x * 8u + w;
+    if (t >= n_tiles) return;
+    uint8_t *p = data + t * Q4B_TILE_BYTES;
+    uint8_t *b = buf[w];
+    for (uint32_t i = lane; i < Q4B_TILE_BYTES / 16; i += 32)
+        reinterpret_cast<uint4 *>(b)[i] = reinterpret_cast<const uint4 *>(p)[i];
+    __syncwarp();
+    // engine layout of block k: 110k + {0: d, 2: qs[64], 66: qh[8], 74: signs[32], 106: scales[4]}
+    for (uint32_t i = lane; i < Q4B_TILE_BYTES; i += 32) {
+        const uint32_t k = i / 110u, o = i - k * 110u;
+        uint32_t to;
+        if (o < 2)
+            to = Q4B_TILE_OFF_D + 2 * k + o;
+        else if (o < 66)
+            to = Q4B_TILE_OFF_QS + 64 * k + (o - 2);
+        else if (o < 74)
+            to = Q4B_TILE_OFF_QH + 8 * k + (o - 66);
+        else if (o < 106)
+            to = Q4B_TILE_OFF_SG + 32 * k + (o - 74);
+        else
+            to = Q4B_TILE_OFF_SC + 4 * k + (o - 106);
+        if (o >= 74 && o < 106) continue;  // sign words: handled below, as words
+        if (FORWARD)
+            p[to] = b[i];
+        else
+            p[i] = b[to];
+    }
+    for (uint32_t g = lane; g < 64; g += 32) {  // 64 sign words per tile
+        const uint32_t k = g >> 3, ib = g & 7u;
+        const uint32_t eng = 110u * k + 74u + 4u * ib, til = Q4B_TILE_OFF_SG + 32u * k + 4u * ib;
+        if (FORWARD) {
+            const uint32_t w32 = b[eng] | (b[eng + 1] << 8) | (b[eng + 2] << 16) | ((uint32_t)b[eng + 3] << 24);
+            *reinterpret_cast<uint32_t *>(p + til) = q4b_sign_permute(w32);
+        } else {
+            const uint32_t w32 = q4b_sign_unpermute(*reinterpret_cast<const uint32_t *>(b + til));
+            p[eng] = (uint8_t)w32;
+            p[eng + 1] = (uint8_t)(w32 >> 8);
+            p[eng + 2] = (uint8_t)(w32 >> 16);
+            p[eng + 3] = (uint8_t)(w32 >> 24);
+        }
+    }
+}
+
+bool launch_tile_permute(uint8_t *data, uint64_t bytes, bool forward, cudaStream_t st) {
+    const uint64_t n_tiles = bytes / Q4B_TILE_BYTES;
+    if (n_tiles == 0) return true;
+    const unsigned nb = (unsigned)((n_tiles + 7) / 8);
+    if (forward)
+        tile_permute_k<true><<<nb, 256, 0, st>>>(data, n_tiles);
+    else
+        tile_permute_k<false><<<nb, 256, 0, st>>>(data, n_tiles);
+    g_q4b_launches++;
+    return q4b_launch_ok("tile_permute");
+}
 
 cudaEvent_t g_ev0, g_ev1;
 bool g_capturing = false;
@@ -210,6 +283,7 @@ extern "C" bool q4_hip_experts_alloc_a(int arena, uint32_t n_slots, uint64_t slo
     a.n_slots = n_slots;
     a.stride = slot_bytes;
     a.bytes = bytes;
+    a.tiled = tiled_default() && (slot_bytes % Q4B_TILE_BYTES) == 0 && (slot_bytes % 16) == 0;
     return true;
 }
 extern "C" void q4_hip_experts_free_a(int arena) {
@@ -228,8 +302,11 @@ extern "C" bool q4_hip_experts_put_async_a(int arena, uint32_t slot, const uint8
     if (!g_q4b.ok || arena < 0 || arena >= 4 || !host) return false;
     Arena &a = g_arena[arena];
     if (!a.base || slot >= a.n_slots || n > a.stride) return false;
+    if (a.tiled && (n % Q4B_TILE_BYTES)) return false;
     Q4B_CHECK(cudaMemcpyAsync(a.base + (uint64_t)slot * a.stride, host, n, cudaMemcpyHostToDevice,
                               g_q4b.copy_stream));
+    if (a.tiled && !launch_tile_permute(a.base + (uint64_t)slot * a.stride, n, true, g_q4b.copy_stream))
+        return false;
     return true;
 }
 extern "C" bool q4_hip_experts_put_a(int arena, uint32_t slot, const uint8_t *host, uint64_t n) {
@@ -330,4 +407,62 @@ extern "C" uint32_t q4_cuda_device_error(void) {
     const uint32_t v = *g_q4b.err_h;
     if (v) cudaMemsetAsync(g_q4b.err_d, 0, 4, g_q4b.stream);
     return v;
+}
+
+// ---- pinned host memory (reference: q4_hip_host_alloc_coh, src/q4.h:1251-1252) ----
+extern "C" void *q4_hip_host_alloc_coh(size_t n) {
+    if (!g_q4b.ok || n == 0) return nullptr;
+    void *p = nullptr;
+    if (cudaHostAlloc(&p, n, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+extern "C" void q4_hip_host_free_coh(void *p) {
+    if (g_q4b.ok && p) cudaFreeHost(p);
+}
+
+// ---- tiled arenas ----
+bool q4b_ptr_tiled(const void *p) {
+    const uint8_t *q = (const uint8_t *)p;
+    for (int a = 0; a < 4; a++)
+        if (g_arena[a].base && g_arena[a].tiled && q >= g_arena[a].base &&
+            q < g_arena[a].base + g_arena[a].bytes)
+            return true;
+    return false;
+}
+extern "C" void q4_cuda_set_tiled_default(int on) { g_tiled_default = on ? 1 : 0; }
+extern "C" int q4_cuda_experts_tiled_a(int arena) {
+    return (arena >= 0 && arena < 4 && g_arena[arena].base && g_arena[arena].tiled) ? 1 : 0;
+}
+extern "C" bool q4_cuda_experts_retile_a(int arena, uint32_t first_slot, uint32_t n_slots) {
+    if (!g_q4b.ok || arena < 0 || arena >= 4) return false;
+    Arena &a = g_arena[arena];
+    if (!a.base || !a.tiled || (uint64_t)first_slot + n_slots > a.n_slots || n_slots == 0) return false;
+    return launch_tile_permute(a.base + (uint64_t)first_slot * a.stride, (uint64_t)n_slots * a.stride,
+                               true, g_q4b.stream);
+}
+extern "C" bool q4_cuda_experts_get_a(int arena, uint32_t slot, uint8_t *host, uint64_t n) {
+    if (!g_q4b.ok || arena < 0 || arena >= 4 || !host) return false;
+    Arena &a = g_arena[arena];
+    if (!a.base || slot >= a.n_slots || n > a.stride || n == 0) return false;
+    uint8_t *src = a.base + (uint64_t)slot * a.stride;
+    if (!a.tiled) {
+        Q4B_CHECK(cudaMemcpyAsync(host, src, n, cudaMemcpyDeviceToHost, g_q4b.stream));
+        Q4B_CHECK(cudaStreamSynchronize(g_q4b.stream));
+        return true;
+    }
+    if (n % Q4B_TILE_BYTES) return false;
+    uint8_t *tmp = nullptr;
+    if (cudaMalloc(&tmp, n) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    bool ok = cudaMemcpyAsync(tmp, src, n, cudaMemcpyDeviceToDevice, g_q4b.stream) == cudaSuccess &&
+              launch_tile_permute(tmp, n, false, g_q4b.stream) &&
+              cudaMemcpyAsync(host, tmp, n, cudaMemcpyDeviceToHost, g_q4b.stream) == cudaSuccess &&
+              cudaStreamSynchronize(g_q4b.stream) == cudaSuccess;
+    cudaFree(tmp);
+    return ok;
 }

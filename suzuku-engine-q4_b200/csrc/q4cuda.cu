@@ -5,3 +5,4 @@
 #include "q4b_runtime.cu"
 #include "q4b_decode.cu"
 #include "q4b_synth.cu"
+#include "q4b_fused.cu"
