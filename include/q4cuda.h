@@ -193,6 +193,13 @@ bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, uint64_t og, 
                              uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
                              float *h_y);
 
+/* Diagnostics of the single-kernel layer path: when enabled, the kernel records
+ * the GPU's nanosecond timer at its phase boundaries; read copies the last
+ * launch's stamps, out[cta * 16 + slot], and returns the number of CTAs.
+ * enable allocates or frees (call it outside graph capture). */
+bool q4_cuda_fused_profile_enable(int on);
+uint32_t q4_cuda_fused_profile_read(unsigned long long *out, uint32_t max_ctas);
+
 /* Seeded synthetic tensors generated on the device (benchmark and smoke
  * support, no reference counterpart): n_blocks IQ3_S super-blocks with
  * fp16 d = |N(0,1)| * 2^-6 and uniform random payload bytes; n fp32 values

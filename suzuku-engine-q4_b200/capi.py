@@ -84,6 +84,8 @@ SIGNATURES = {
     "q4_cuda_experts_get_a": (b, [C.c_int, u32, vp, u64]),
     "q4_cuda_moe_decode_host": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32,
                                     u32, vp]),
+    "q4_cuda_fused_profile_enable": (b, [C.c_int]),
+    "q4_cuda_fused_profile_read": (u32, [vp, u32]),
     "q4_cuda_synth_iq3s": (b, [vp, u64, u64]),
     "q4_cuda_synth_normal": (b, [vp, u64, u64, f32, f32]),
     "q4_cuda_timer_begin": (b, []),

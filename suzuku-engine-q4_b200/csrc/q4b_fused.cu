@@ -1,23 +1,25 @@
 // One MoE layer for one token as ONE persistent kernel (one CTA per SM):
 //
-//   phase 0  every CTA: RMSNorm of x, Q8-A quantisation, code table -> shared memory
-//   phase 1  router: the CTAs split the fp32 router matrix into 2 KB chunks,
-//            fetched with bulk async copies issued at kernel start
-//            -- grid barrier --
-//   phase 2  every CTA: softmax + top-k (redundantly, from the 512 logits);
-//            gate/up rows of the picked experts and the shared expert, split
-//            evenly over the CTAs as (expert, hidden unit) pairs; the CTA's
-//            down-projection tiles are fetched meanwhile
-//            -- grid barrier --
+//   start    bulk async copies of this CTA's share of the router matrix and of the
+//            shared expert's gate/up tiles are issued before anything else
+//   phase 0  every CTA: code table -> shared memory, RMSNorm of x, Q8-A quantisation
+//   phase 1  router: partial dots of this CTA's 2 KB router chunks
+//            -- grid barrier 1: arrive; while the others arrive, this CTA computes
+//               its share of the shared expert's gate/up rows (they do not depend
+//               on the routing); then wait --
+//   phase 2  every CTA: softmax + top-k (redundantly, from the logits); bulk copies
+//            of this CTA's share of the picked experts' gate/up tiles, then of all
+//            experts' down tiles; gate/up dots, SwiGLU, h -> global
+//            -- grid barrier 2 --
 //   phase 3  every CTA: Q8-A of the hidden rows, down tiles x hq, weighted sum
 //            over the experts in list order, y written
 //
-// Weight bytes cross HBM -> shared memory exactly once, by 1-D bulk async
-// copies (cp.async.bulk, no multicast) that complete on mbarriers; nothing is
-// re-read.  Replaces the reference's per-layer launch chain
-// (src/q4_moe.c:2077-2133; kernels wmoe_iq3_gu_q8 / wmoe_iq3_ya_q8,
-// src/q4_rocm.cu:3912-4120).  Needs the tiled arena format (q4b_tile.cuh),
-// n_embd == 2048 and n_ff == 512.
+// Weight bytes cross HBM -> shared memory exactly once, by 1-D bulk async copies
+// (cp.async.bulk, no multicast) that complete on mbarriers; nothing is re-read.
+// Replaces the reference's per-layer launch chain (src/q4_moe.c:2077-2133;
+// kernels wmoe_iq3_gu_q8 / wmoe_iq3_ya_q8, src/q4_rocm.cu:3912-4120).  Needs the
+// tiled arena format (q4b_tile.cuh), n_embd == 2048, n_ff == 512,
+// n_expert <= 768, topk <= 32.
 #include "q4b_tile.cuh"
 
 #include <atomic>
@@ -29,24 +31,32 @@ bool q4b_ptr_tiled(const void *p);
 
 namespace fused {
 
-constexpr uint32_t NT = 512;          // threads per CTA
+constexpr uint32_t NT = 768;          // threads per CTA
 constexpr uint32_t NW = NT / 32;      // warps
 constexpr uint32_t H = 2048;          // n_embd
 constexpr uint32_t F = 512;           // n_ff
 constexpr uint32_t RCHUNK = 512;      // router chunk: 512 floats = 2 KB
 constexpr uint32_t MAX_E = 40;        // experts per token incl. shared
 constexpr uint32_t UCHUNK = 8;        // gate/up units per bulk-copy chunk
-constexpr uint32_t MAX_CHUNKS = 12;
+constexpr uint32_t MAX_CHUNKS = 8;
+constexpr uint32_t MAX_UNITS = 64;    // routed (expert, hidden unit) pairs per CTA
+constexpr uint32_t MAX_SH = 8;        // shared-expert units per CTA
+constexpr uint32_t MAX_DT = 64;       // down tiles per CTA
 constexpr uint32_t WAIT_LIMIT = 1000000u;  // polls before a wait gives up
 
+// mbarrier slots
+constexpr uint32_t MB_ROUTER = 0, MB_SHARED = 1, MB_DOWN = 2, MB_CHUNK0 = 3;
+constexpr uint32_t N_MBAR = MB_CHUNK0 + MAX_CHUNKS;
+
 // error word bits
-constexpr uint32_t ERR_MBAR = 1u, ERR_GRID = 2u, ERR_SHAPE = 4u;
+constexpr uint32_t ERR_MBAR = 1u, ERR_GRID = 2u;
 
 struct Args {
     const uint8_t *base;
     uint64_t stride, og, ou, od;
     int32_t shared_slot;
     const float *x, *norm_w, *router;
+    const uint32_t *codes;        // 512 byte-expanded codebook words (device memory)
     float eps;
     uint32_t n_expert, topk;
     float *y;
@@ -56,8 +66,9 @@ struct Args {
     float *h;                     // [MAX_E][F]
     unsigned long long *bar;      // grid barrier counter
     uint32_t *err;
+    unsigned long long *prof;     // optional [gridDim.x][16] phase time stamps (ns), or NULL
     // shared-memory carve-up (bytes from the 1024-aligned start)
-    uint32_t off_stage, off_down, stage_bytes, down_bytes;
+    uint32_t off_stage, off_down, off_sh;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -97,51 +108,45 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
         : "memory");
 }
 
-// All CTAs arrive; nobody leaves before the last one has.  The counter only
-// grows: arrival number a belongs to barrier a / gridDim.x, so no reset is
-// needed between barriers or launches.  Bounded: a CTA that waits too long
-// records ERR_GRID and goes on (its results are then meaningless, but nothing
-// hangs).
-__device__ __forceinline__ void grid_barrier(unsigned long long *ctr, uint32_t *err) {
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        const unsigned long long old = atomicAdd(ctr, 1ull);
-        const unsigned long long target = (old / gridDim.x + 1ull) * gridDim.x;
-        uint32_t i = 0;
-        for (; i < WAIT_LIMIT; i++) {
-            unsigned long long v;
-            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
-            if (v >= target) break;
-            __nanosleep(20);
-        }
-        if (i == WAIT_LIMIT) atomicOr(err, ERR_GRID);
-        __threadfence();
+// Phase time stamp for the optional in-kernel profile.
+__device__ __forceinline__ void stamp(const Args &a, uint32_t slot) {
+    if (a.prof && threadIdx.x == 0) {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        a.prof[blockIdx.x * 16u + slot] = t;
     }
-    __syncthreads();
 }
 
-__device__ __forceinline__ float block_reduce_max(float v, float *red) {
-    v = q4b_warp_max(v);
-    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float r = red[0];
-    for (uint32_t i = 1; i < NW; i++) r = fmaxf(r, red[i]);
-    __syncthreads();
-    return r;
+// Grid barrier in two halves.  The counter only grows: every CTA adds one per
+// barrier, so barrier number k of this launch is complete when the counter
+// reaches base + (k + 1) * gridDim.x, where base is the (multiple of gridDim.x)
+// value the counter had when the launch began.  A CTA reads base at its start:
+// it may already see a few arrivals of faster CTAs at the first barrier, so it
+// rounds down.  No reset between barriers or launches.  The wait is bounded: a
+// CTA that waits too long records ERR_GRID and goes on (its results are then
+// meaningless, but nothing hangs).  Both halves are called by thread 0 only,
+// with __syncthreads() before the arrive and after the wait.
+__device__ __forceinline__ unsigned long long grid_barrier_base(const unsigned long long *ctr) {
+    unsigned long long v;
+    asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
+    return v - v % gridDim.x;
 }
-__device__ __forceinline__ float block_reduce_sum(float v, float *red) {
-    v = q4b_warp_sum(v);
-    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
-    __syncthreads();
-    float r = 0.f;
-    for (uint32_t i = 0; i < NW; i++) r += red[i];
-    __syncthreads();
-    return r;
+__device__ __forceinline__ void grid_arrive(unsigned long long *ctr) {
+    asm volatile("red.release.gpu.global.add.u64 [%0], 1;" ::"l"(ctr) : "memory");
+}
+__device__ __forceinline__ void grid_wait(const unsigned long long *ctr, unsigned long long target,
+                                          uint32_t *err) {
+    uint32_t i = 0;
+    for (; i < WAIT_LIMIT; i++) {
+        unsigned long long v;
+        asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(ctr) : "memory");
+        if (v >= target) break;
+    }
+    if (i == WAIT_LIMIT) atomicOr(err, ERR_GRID);
 }
 
 // Q8-A of 32 consecutive floats held four per lane by eight neighbouring lanes.
-// Returns the packed int8x4 word; lane with (lane & 7) == 0 gets d and sum.
+// Returns the packed int8x4 word; every lane gets the group's d and sum.
 __device__ __forceinline__ uint32_t quant8_oct(float4 v, float *d_out, int *bs_out) {
     float a = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
     a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
@@ -164,14 +169,13 @@ __device__ __forceinline__ uint32_t quant8_oct(float4 v, float *d_out, int *bs_o
 
 // Shared-memory layout (offsets from a 1024-byte aligned base):
 //   [0, 65536)        code table, entry i replicated per lane: tab[32 i + lane]
-//   [65536, +...)     small arrays (below), then the two staging regions
+//   [65536, +...)     small arrays (below), then the staging regions
 struct Small {
-    uint64_t mbar[MAX_CHUNKS + 2];  // [0] router, [1..MAX_CHUNKS] gate/up chunks, [last] down
-    alignas(16) float xn[H];        // normalised x (router input)
-    alignas(16) uint32_t xq[H / 4];             // Q8-A of xn, int8x4 words
+    uint64_t mbar[N_MBAR];
+    alignas(16) float xn[H];            // normalised x (router input)
+    alignas(16) uint32_t xq[H / 4];     // Q8-A of xn, int8x4 words
     float xd[H / 32];
     int xbs[H / 32];
-    float p[1024];                  // softmax probabilities
     int32_t ids[MAX_E];
     float wts[MAX_E];
     float red[NW];
@@ -179,85 +183,215 @@ struct Small {
     alignas(16) uint32_t hq[MAX_E][F / 4];  // Q8-A of the hidden rows
     float hd[MAX_E][F / 32];
     int hbs[MAX_E][F / 32];
-    float part[64][4];              // phase-3 partial sums: [tile][row in tile]
+    float part[MAX_DT][4];              // phase-3 partial sums: [tile][row in tile]
+    float gu[MAX_UNITS][2];             // phase-2 gate and up dots of this CTA's units
+    float gu_sh[MAX_SH][2];             // the same for its shared-expert units
+    uint32_t ck[NW][32];                // routing: per-warp ordered candidates (key, index)
+    uint32_t ci[NW][32];
 };
+
+__device__ __forceinline__ float block_reduce_max(float v, float *red) {
+    v = q4b_warp_max(v);
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (uint32_t i = 1; i < NW; i++) r = fmaxf(r, red[i]);
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ float block_reduce_sum(float v, float *red) {
+    v = q4b_warp_sum(v);
+    if ((threadIdx.x & 31u) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = 0.f;
+#pragma unroll
+    for (uint32_t i = 0; i < NW; i++) r += red[i];
+    __syncthreads();
+    return r;
+}
+
+// Softmax over the logits and top-k by the whole CTA; thread i owns expert i
+// (n_expert <= NT).  A pick is the largest probability, the lowest index among
+// equal ones; weights are renormalised in rank order (src/q4_quant.c:715-755).
+// Two stages, nothing indexed dynamically: every warp extracts the ordered
+// top-k of its own 32 experts with warp reductions, then warp 0 merges the NW
+// ordered lists (lane w walks list w).
+__device__ __forceinline__ void route_block(const Args &a, Small &S, uint32_t tid, uint32_t cta) {
+    const uint32_t lane = tid & 31u, warp = tid >> 5;
+    float l = -INFINITY;
+    if (tid < a.n_expert) {
+        const float4 pp = __ldcg(reinterpret_cast<const float4 *>(a.logit_part) + tid);
+        l = (pp.x + pp.y) + (pp.z + pp.w);
+    }
+    const float m = block_reduce_max(l, S.red);
+    const float e = tid < a.n_expert ? expf(l - m) : 0.f;
+    const float s = block_reduce_sum(e, S.red);
+    const float inv = s > 0.f ? __fdiv_rn(1.0f, s) : 0.f;
+    // probabilities are >= 0: their bit patterns order like the values; 0 = none
+    uint32_t key = tid < a.n_expert ? __float_as_uint(__fmul_rn(e, inv)) + 1u : 0u;
+    uint32_t my_key = 0u, my_idx = 0xffffffffu;
+    if (warp * 32u < a.n_expert) {
+        for (uint32_t r = 0; r < a.topk; r++) {
+            const uint32_t kmax = __reduce_max_sync(0xffffffffu, key);
+            const uint32_t imin = __reduce_min_sync(0xffffffffu, key == kmax ? tid : 0xffffffffu);
+            if (lane == r) {
+                my_key = kmax;
+                my_idx = kmax ? imin : 0xffffffffu;
+            }
+            if (tid == imin) key = 0u;
+        }
+    }
+    S.ck[warp][lane] = my_key;
+    S.ci[warp][lane] = my_idx;
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t pos = 0;
+        uint32_t hk = lane < NW ? S.ck[lane][0] : 0u;
+        uint32_t hi = lane < NW ? S.ci[lane][0] : 0xffffffffu;
+        float wsum = 0.f, my_w = 0.f;
+        uint32_t my_id = 0;
+        for (uint32_t t = 0; t < a.topk; t++) {
+            const uint32_t kmax = __reduce_max_sync(0xffffffffu, hk);
+            const uint32_t imin = __reduce_min_sync(0xffffffffu, hk == kmax ? hi : 0xffffffffu);
+            if (hk == kmax && hi == imin) {  // this lane's list head was taken
+                pos++;
+                hk = pos < 32u ? S.ck[lane][pos] : 0u;
+                hi = pos < 32u ? S.ci[lane][pos] : 0xffffffffu;
+            }
+            const float w = __uint_as_float(kmax - 1u);
+            if (lane == t) {
+                my_id = imin;
+                my_w = w;
+            }
+            wsum = __fadd_rn(wsum, w);
+        }
+        if (lane < a.topk) {
+            const float w = wsum > 0.f ? __fmul_rn(my_w, __fdiv_rn(1.0f, wsum)) : my_w;
+            S.ids[lane] = (int32_t)my_id;
+            S.wts[lane] = w;
+            if (cta == 0) {
+                if (a.ids_out) a.ids_out[lane] = (int32_t)my_id;
+                if (a.wts_out) a.wts_out[lane] = w;
+            }
+        }
+        if (lane == 0 && a.shared_slot >= 0) {
+            S.ids[a.topk] = a.shared_slot;
+            S.wts[a.topk] = 1.0f;
+        }
+    }
+}
 
 __global__ void __launch_bounds__(NT, 1) moe_decode_fused_k(const Args a) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t *sm = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     uint32_t *tab = reinterpret_cast<uint32_t *>(sm);
     Small &S = *reinterpret_cast<Small *>(sm + 65536);
-    uint8_t *stage = sm + a.off_stage;  // router chunks, then gate/up tiles
+    uint8_t *stage = sm + a.off_stage;  // router chunks, then routed gate/up tiles
     uint8_t *dstage = sm + a.off_down;  // down tiles
+    uint8_t *sstage = sm + a.off_sh;    // shared-expert gate/up tiles
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t cta = blockIdx.x, ncta = gridDim.x;
-    const uint32_t ne = a.topk + (a.shared_slot >= 0 ? 1u : 0u);
+    const bool has_sh = a.shared_slot >= 0;
+    const uint32_t ne = a.topk + (has_sh ? 1u : 0u);
 
     // ---- work split ----
     const uint32_t n_rchunks = a.n_expert * (H / RCHUNK);
     const uint32_t rc0 = (uint32_t)((uint64_t)cta * n_rchunks / ncta);
     const uint32_t rc1 = (uint32_t)((uint64_t)(cta + 1) * n_rchunks / ncta);
-    const uint32_t n_units = ne * F;  // (expert, hidden unit) pairs
+    const uint32_t n_units = a.topk * F;  // routed (expert, hidden unit) pairs
     const uint32_t u0 = (uint32_t)((uint64_t)cta * n_units / ncta);
     const uint32_t u1 = (uint32_t)((uint64_t)(cta + 1) * n_units / ncta);
+    const uint32_t s0 = has_sh ? (uint32_t)((uint64_t)cta * F / ncta) : 0u;  // shared-expert units
+    const uint32_t s1 = has_sh ? (uint32_t)((uint64_t)(cta + 1) * F / ncta) : 0u;
     const uint32_t n_dtiles = (H / 4) * ne;  // (row quad, expert) pairs, expert fastest
     const uint32_t v0 = (uint32_t)((uint64_t)cta * n_dtiles / ncta);
     const uint32_t v1 = (uint32_t)((uint64_t)(cta + 1) * n_dtiles / ncta);
 
+    // loads with nothing before them in the dependency chain go first
+    float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), wv = make_float4(1.f, 1.f, 1.f, 1.f);
+    uint32_t code = 0;
+    if (tid < H / 4) {
+        xv = reinterpret_cast<const float4 *>(a.x)[tid];
+        if (a.norm_w) wv = reinterpret_cast<const float4 *>(a.norm_w)[tid];
+        code = a.codes[tid];
+    }
+    unsigned long long bar_base = 0;
     if (tid == 0) {
-        for (uint32_t i = 0; i < MAX_CHUNKS + 2; i++) mbar_init(&S.mbar[i], 1);
+        bar_base = grid_barrier_base(a.bar);
+        for (uint32_t i = 0; i < N_MBAR; i++) mbar_init(&S.mbar[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    // router chunks: contiguous in memory
-    if (tid == 0 && rc1 > rc0) {
+    if (tid == 0 && rc1 > rc0) {  // router chunks: contiguous in memory
         const uint32_t bytes = (rc1 - rc0) * RCHUNK * 4u;
-        mbar_expect_tx(&S.mbar[0], bytes);
-        bulk_g2s(stage, a.router + (size_t)rc0 * RCHUNK, bytes, &S.mbar[0]);
+        mbar_expect_tx(&S.mbar[MB_ROUTER], bytes);
+        bulk_g2s(stage, a.router + (size_t)rc0 * RCHUNK, bytes, &S.mbar[MB_ROUTER]);
+    }
+    if (tid == 32 && s1 > s0) {   // shared expert: gate tiles then up tiles of units [s0, s1)
+        const uint32_t bytes = (s1 - s0) * Q4B_TILE_BYTES;
+        const uint8_t *pk = a.base + (uint64_t)a.shared_slot * a.stride;
+        mbar_expect_tx(&S.mbar[MB_SHARED], 2u * bytes);
+        bulk_g2s(sstage, pk + a.og + (size_t)s0 * Q4B_TILE_BYTES, bytes, &S.mbar[MB_SHARED]);
+        bulk_g2s(sstage + (size_t)MAX_SH * Q4B_TILE_BYTES, pk + a.ou + (size_t)s0 * Q4B_TILE_BYTES,
+                 bytes, &S.mbar[MB_SHARED]);
     }
 
+    stamp(a, 0);
     // ---- phase 0: code table, y = 0, RMSNorm, Q8-A ----
-    for (uint32_t i = 0; i < 32; i++) {
-        const uint32_t idx = warp * 32u + i;
-        tab[idx * 32u + lane] = q4b_code_bytes(c_iq3s_codes[idx]);
+    // table entry i replicated once per lane: thread t < 512 holds entry t, a warp
+    // broadcasts its 32 entries one by one
+    if (tid < 512) {
+#pragma unroll 8
+        for (uint32_t i = 0; i < 32; i++) {
+            const uint32_t v = __shfl_sync(0xffffffffu, code, i);
+            tab[(warp * 32u + i) * 32u + lane] = v;
+        }
     }
     for (uint32_t r = cta * NT + tid; r < H; r += ncta * NT) a.y[r] = 0.f;
     {
-        const float4 xv = reinterpret_cast<const float4 *>(a.x)[tid];
         double ss = (double)xv.x * xv.x + (double)xv.y * xv.y + (double)xv.z * xv.z +
                     (double)xv.w * xv.w;
 #pragma unroll
         for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (lane == 0) S.redd[warp] = ss;
         __syncthreads();
-        double tot = 0.0;
-        for (uint32_t i = 0; i < NW; i++) tot += S.redd[i];
-        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(tot / (double)H), a.eps)));
-        float4 v;
-        v.x = __fmul_rn(xv.x, scale);
-        v.y = __fmul_rn(xv.y, scale);
-        v.z = __fmul_rn(xv.z, scale);
-        v.w = __fmul_rn(xv.w, scale);
-        if (a.norm_w) {
-            const float4 wv = reinterpret_cast<const float4 *>(a.norm_w)[tid];
-            v.x = __fmul_rn(v.x, wv.x);
-            v.y = __fmul_rn(v.y, wv.y);
-            v.z = __fmul_rn(v.z, wv.z);
-            v.w = __fmul_rn(v.w, wv.w);
-        }
-        reinterpret_cast<float4 *>(S.xn)[tid] = v;
-        float d;
-        int bs;
-        S.xq[tid] = quant8_oct(v, &d, &bs);
-        if ((lane & 7u) == 0) {
-            S.xd[tid >> 3] = d;
-            S.xbs[tid >> 3] = bs;
+        if (tid < H / 4) {
+            // pairwise, so the sixteen partial sums are not one long dependent chain
+            double t8[8];
+#pragma unroll
+            for (uint32_t i = 0; i < 8; i++) t8[i] = S.redd[2 * i] + S.redd[2 * i + 1];
+            const double tot = ((t8[0] + t8[1]) + (t8[2] + t8[3])) + ((t8[4] + t8[5]) + (t8[6] + t8[7]));
+            // H is a power of two: multiplying by 1/H is the exact division
+            const float scale =
+                __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(tot * (1.0 / (double)H)), a.eps)));
+            float4 v;
+            v.x = __fmul_rn(xv.x, scale);
+            v.y = __fmul_rn(xv.y, scale);
+            v.z = __fmul_rn(xv.z, scale);
+            v.w = __fmul_rn(xv.w, scale);
+            if (a.norm_w) {
+                v.x = __fmul_rn(v.x, wv.x);
+                v.y = __fmul_rn(v.y, wv.y);
+                v.z = __fmul_rn(v.z, wv.z);
+                v.w = __fmul_rn(v.w, wv.w);
+            }
+            reinterpret_cast<float4 *>(S.xn)[tid] = v;
+            float d;
+            int bs;
+            S.xq[tid] = quant8_oct(v, &d, &bs);
+            if ((lane & 7u) == 0) {
+                S.xd[tid >> 3] = d;
+                S.xbs[tid >> 3] = bs;
+            }
         }
     }
     __syncthreads();
+    stamp(a, 1);
 
     // ---- phase 1: router partial dots ----
-    if (rc1 > rc0) mbar_wait(&S.mbar[0], 0, a.err);
+    if (rc1 > rc0) mbar_wait(&S.mbar[MB_ROUTER], 0, a.err);
+    stamp(a, 2);
     for (uint32_t c = rc0 + warp; c < rc1; c += NW) {
         const float4 *w4 = reinterpret_cast<const float4 *>(stage + (size_t)(c - rc0) * RCHUNK * 4u);
         const uint32_t part = c % (H / RCHUNK);
@@ -265,171 +399,159 @@ __global__ void __launch_bounds__(NT, 1) moe_decode_fused_k(const Args a) {
         float acc = 0.f;
 #pragma unroll
         for (uint32_t i = 0; i < RCHUNK / 128; i++) {
-            const float4 wv = w4[lane + 32 * i], xv = x4[lane + 32 * i];
-            acc += wv.x * xv.x + wv.y * xv.y + wv.z * xv.z + wv.w * xv.w;
+            const float4 rw = w4[lane + 32 * i], rx = x4[lane + 32 * i];
+            acc += rw.x * rx.x + rw.y * rx.y + rw.z * rx.z + rw.w * rx.w;
         }
         acc = q4b_warp_sum(acc);
         if (lane == 0) a.logit_part[c] = acc;
     }
-    grid_barrier(a.bar, a.err);
+    stamp(a, 3);
+    __syncthreads();
+    // the last warp signals (its thread waits for the CTA's stores to land), so that
+    // warp 0 and the others go straight on to the shared expert's rows
+    if (tid == NT - 32) grid_arrive(a.bar);
 
-    // ---- phase 2a: softmax + top-k (every CTA, same result) ----
-    {
-        float l[2] = {-INFINITY, -INFINITY};
-        float m = -INFINITY;
-        for (uint32_t j = 0, e = tid; e < a.n_expert; e += NT, j++) {
-            const float4 pp = __ldcg(reinterpret_cast<const float4 *>(a.logit_part) + e);
-            l[j] = (pp.x + pp.y) + (pp.z + pp.w);
-            m = fmaxf(m, l[j]);
-        }
-        m = block_reduce_max(m, S.red);
-        float s = 0.f;
-        for (uint32_t j = 0, e = tid; e < a.n_expert; e += NT, j++) {
-            l[j] = expf(l[j] - m);
-            s += l[j];
-        }
-        s = block_reduce_sum(s, S.red);
-        const float inv = s > 0.f ? __fdiv_rn(1.0f, s) : 0.f;
-        for (uint32_t j = 0, e = tid; e < a.n_expert; e += NT, j++) S.p[e] = __fmul_rn(l[j], inv);
-        __syncthreads();
-        if (warp == 0) {
-            // each lane keeps its strided values in registers; a pick is the
-            // largest value, lowest index among equals
-            float v[32];
-            const uint32_t per = (a.n_expert + 31u) / 32u;
+    // activations of this lane's 64 columns (lane l of a gate/up tile owns columns 64 l ..)
+    int q[16];
 #pragma unroll
-            for (uint32_t j = 0; j < 32; j++)
-                v[j] = (j < per && lane + 32u * j < a.n_expert) ? S.p[lane + 32u * j] : -1.f;
-            float wsum = 0.f;
-            for (uint32_t t = 0; t < a.topk; t++) {
-                float best = -1.f;
-                uint32_t bj = 0;
-#pragma unroll
-                for (uint32_t j = 0; j < 32; j++)
-                    if (j < per && v[j] > best) {
-                        best = v[j];
-                        bj = j;
-                    }
-                // values are >= 0 (or -1 when taken): compare as ordered bits
-                const uint32_t key = best < 0.f ? 0u : __float_as_uint(best) + 1u;
-                const uint32_t kmax = __reduce_max_sync(0xffffffffu, key);
-                const uint32_t cand = key == kmax ? lane + 32u * bj : 0xffffffffu;
-                const uint32_t idx = __reduce_min_sync(0xffffffffu, cand);
-                if ((idx & 31u) == lane) {
-#pragma unroll
-                    for (uint32_t j = 0; j < 32; j++)
-                        if (j == (idx >> 5)) v[j] = -1.f;
-                }
-                if (lane == 0) {
-                    S.ids[t] = (int32_t)idx;
-                    S.wts[t] = __uint_as_float(kmax - 1u);
-                }
-                wsum = __fadd_rn(wsum, __uint_as_float(kmax - 1u));
-            }
-            __syncwarp();
-            if (lane < a.topk && wsum > 0.f)
-                S.wts[lane] = __fmul_rn(S.wts[lane], __fdiv_rn(1.0f, wsum));
-            if (lane == 0 && a.shared_slot >= 0) {
-                S.ids[a.topk] = a.shared_slot;
-                S.wts[a.topk] = 1.0f;
-            }
-            __syncwarp();
-            if (cta == 0 && lane < a.topk) {
-                if (a.ids_out) a.ids_out[lane] = S.ids[lane];
-                if (a.wts_out) a.wts_out[lane] = S.wts[lane];
-            }
-        }
-        __syncthreads();
-    }
+    for (int i = 0; i < 16; i++) q[i] = (int)S.xq[16u * lane + i];
+    const float dx0 = S.xd[2u * lane], dx1 = S.xd[2u * lane + 1];
+    const int bs0 = S.xbs[2u * lane], bs1 = S.xbs[2u * lane + 1];
+    const uint32_t *tl = tab + lane;
 
-    // ---- phase 2b: fetch this CTA's gate/up tiles (chunks of UCHUNK units) and down tiles ----
-    // unit u = e * F + f; chunk k covers units [u0 + k*UCHUNK, ...) cut at expert boundaries
-    // staging: chunk k at stage + k * UCHUNK * 2 * 880: gate tiles then up tiles
-    const uint32_t n_chunks = (u1 - u0 + UCHUNK - 1) / UCHUNK;
-    if (warp == 0) {
-        for (uint32_t k = lane; k < n_chunks; k += 32) {
-            const uint32_t ua = u0 + k * UCHUNK, ub = min(ua + UCHUNK, u1);
-            uint8_t *dst = stage + (size_t)k * UCHUNK * 2u * Q4B_TILE_BYTES;
-            // a chunk may straddle two experts: copy each expert's run separately
-            mbar_expect_tx(&S.mbar[1 + k], (ub - ua) * 2u * Q4B_TILE_BYTES);
-            uint32_t u = ua;
-            while (u < ub) {
-                const uint32_t e = u / F, f = u - e * F;
-                const uint32_t run = min(ub - u, F - f);
-                const uint8_t *pk = a.base + (uint64_t)S.ids[e] * a.stride;
-                bulk_g2s(dst + (size_t)(u - ua) * Q4B_TILE_BYTES, pk + a.og + (size_t)f * Q4B_TILE_BYTES,
-                         run * Q4B_TILE_BYTES, &S.mbar[1 + k]);
-                bulk_g2s(dst + (size_t)(UCHUNK + (u - ua)) * Q4B_TILE_BYTES,
-                         pk + a.ou + (size_t)f * Q4B_TILE_BYTES, run * Q4B_TILE_BYTES, &S.mbar[1 + k]);
-                u += run;
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) mbar_expect_tx(&S.mbar[MAX_CHUNKS + 1], (v1 - v0) * Q4B_TILE_BYTES);
-        __syncwarp();
-        for (uint32_t v = v0 + lane; v < v1; v += 32) {
-            const uint32_t rq = v / ne, e = v - rq * ne;
-            bulk_g2s(dstage + (size_t)(v - v0) * Q4B_TILE_BYTES,
-                     a.base + (uint64_t)S.ids[e] * a.stride + a.od + (size_t)rq * Q4B_TILE_BYTES,
-                     Q4B_TILE_BYTES, &S.mbar[MAX_CHUNKS + 1]);
-        }
-    }
-
-    // ---- phase 2c: gate/up dots, SwiGLU ----
-    {
-        int q[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) q[i] = (int)S.xq[16u * lane + i];
-        const float dx0 = S.xd[2u * lane], dx1 = S.xd[2u * lane + 1];
-        const int bs0 = S.xbs[2u * lane], bs1 = S.xbs[2u * lane + 1];
-        const uint32_t *tl = tab + lane;
-        for (uint32_t u = u0 + warp; u < u1; u += NW) {
-            const uint32_t k = (u - u0) / UCHUNK, i = (u - u0) - k * UCHUNK;
-            mbar_wait(&S.mbar[1 + k], 0, a.err);
-            const uint8_t *tg = stage + ((size_t)k * UCHUNK * 2u + i) * Q4B_TILE_BYTES;
-            const uint8_t *tu = tg + (size_t)UCHUNK * Q4B_TILE_BYTES;
-            float g = q4b_tile_lane_dot(tg, lane, tl, q, dx0, dx1, bs0, bs1);
-            float up = q4b_tile_lane_dot(tu, lane, tl, q, dx0, dx1, bs0, bs1);
-            g = q4b_warp_sum(g);
-            up = q4b_warp_sum(up);
-            if (lane == 0) a.h[u] = q4b_swiglu(g, up);  // u = e * F + f
-        }
-    }
-    grid_barrier(a.bar, a.err);
-
-    // ---- phase 3a: Q8-A of the hidden rows (all experts; 8 lanes per group) ----
-    for (uint32_t w4 = tid; w4 < ne * (F / 4); w4 += NT) {
-        const float4 hv = __ldcg(reinterpret_cast<const float4 *>(a.h) + w4);
-        float d;
-        int bs;
-        const uint32_t word = quant8_oct(hv, &d, &bs);
-        const uint32_t e = w4 / (F / 4), i = w4 - e * (F / 4);
-        S.hq[e][i] = word;
-        if ((lane & 7u) == 0) {
-            S.hd[e][i >> 3] = d;
-            S.hbs[e][i >> 3] = bs;
+    // ---- while the grid gathers: the shared expert's gate/up rows ----
+    if (s1 > s0) {
+        mbar_wait(&S.mbar[MB_SHARED], 0, a.err);
+        for (uint32_t t = warp; t < 2u * (s1 - s0); t += NW) {
+            const uint32_t ul = t >> 1, which = t & 1u;
+            const uint8_t *tile = sstage + ((size_t)which * MAX_SH + ul) * Q4B_TILE_BYTES;
+            float r = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
+            r = q4b_warp_sum(r);
+            if (lane == 0) S.gu_sh[ul][which] = r;
         }
     }
     __syncthreads();
+    if (tid < s1 - s0) a.h[a.topk * F + s0 + tid] = q4b_swiglu(S.gu_sh[tid][0], S.gu_sh[tid][1]);
+    if (tid == 0) grid_wait(a.bar, bar_base + ncta, a.err);
+    __syncthreads();
+    stamp(a, 4);
 
-    // ---- phase 3b: down tiles; tile = 4 rows x 2 blocks; lane: block l/4 -> row (l/8), half (l/4)&1 ----
-    mbar_wait(&S.mbar[MAX_CHUNKS + 1], 0, a.err);
+    // ---- phase 2a: softmax + top-k (every CTA, same result) ----
+    route_block(a, S, tid, cta);
+    __syncthreads();
+    stamp(a, 5);
+
+    // ---- phase 2b: fetch this CTA's routed gate/up tiles (chunks of UCHUNK units) ----
+    // unit u = e * F + f; chunk k covers units [u0 + k*UCHUNK, ...), cut at expert boundaries;
+    // staging: chunk k at stage + k * UCHUNK * 2 * 880: gate tiles then up tiles.
+    // One warp per chunk issues its copies.
+    const uint32_t n_chunks = (u1 - u0 + UCHUNK - 1) / UCHUNK;
+    if (warp < n_chunks && lane == 0) {
+        const uint32_t k = warp;
+        const uint32_t ua = u0 + k * UCHUNK, ub = min(ua + UCHUNK, u1);
+        uint8_t *dst = stage + (size_t)k * UCHUNK * 2u * Q4B_TILE_BYTES;
+        mbar_expect_tx(&S.mbar[MB_CHUNK0 + k], (ub - ua) * 2u * Q4B_TILE_BYTES);
+        uint32_t u = ua;
+        while (u < ub) {  // a chunk may straddle two experts: one copy per expert's run
+            const uint32_t e = u / F, f = u - e * F;
+            const uint32_t run = min(ub - u, F - f);
+            const uint8_t *pk = a.base + (uint64_t)S.ids[e] * a.stride;
+            bulk_g2s(dst + (size_t)(u - ua) * Q4B_TILE_BYTES, pk + a.og + (size_t)f * Q4B_TILE_BYTES,
+                     run * Q4B_TILE_BYTES, &S.mbar[MB_CHUNK0 + k]);
+            bulk_g2s(dst + (size_t)(UCHUNK + (u - ua)) * Q4B_TILE_BYTES,
+                     pk + a.ou + (size_t)f * Q4B_TILE_BYTES, run * Q4B_TILE_BYTES,
+                     &S.mbar[MB_CHUNK0 + k]);
+            u += run;
+        }
+    }
+    stamp(a, 6);
+    // ---- phase 2c: routed gate/up dots (one tile per warp task), SwiGLU ----
+    for (uint32_t t = warp; t < 2u * (u1 - u0); t += NW) {
+        const uint32_t ul = t >> 1, which = t & 1u;
+        const uint32_t k = ul / UCHUNK, i = ul - k * UCHUNK;
+        mbar_wait(&S.mbar[MB_CHUNK0 + k], 0, a.err);
+        if (t == 0) stamp(a, 13);
+        const uint8_t *tile = stage + ((size_t)k * UCHUNK * 2u + which * UCHUNK + i) * Q4B_TILE_BYTES;
+        float r = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
+        r = q4b_warp_sum(r);
+        if (lane == 0) S.gu[ul][which] = r;
+        if (t == 0) stamp(a, 14);
+    }
+    if (n_chunks) mbar_wait(&S.mbar[MB_CHUNK0 + n_chunks - 1], 0, a.err);
+    stamp(a, 15);
+    // The down tiles are needed only after the next grid barrier: the last two warps
+    // ask for them after their own gate/up work, when the last gate/up chunk has landed,
+    // so that they do not compete with the tiles that are needed first.
+    if (warp >= NW - 2) {
+        if (n_chunks) mbar_wait(&S.mbar[MB_CHUNK0 + n_chunks - 1], 0, a.err);
+        const uint32_t t64 = tid - (NW - 2) * 32;
+        if (t64 == 0) mbar_expect_tx(&S.mbar[MB_DOWN], (v1 - v0) * Q4B_TILE_BYTES);
+        for (uint32_t v = v0 + t64; v < v1; v += 64) {
+            const uint32_t rq = v / ne, e = v - rq * ne;
+            bulk_g2s(dstage + (size_t)(v - v0) * Q4B_TILE_BYTES,
+                     a.base + (uint64_t)S.ids[e] * a.stride + a.od + (size_t)rq * Q4B_TILE_BYTES,
+                     Q4B_TILE_BYTES, &S.mbar[MB_DOWN]);
+        }
+    }
+
+    __syncthreads();
+    if (tid < u1 - u0) a.h[u0 + tid] = q4b_swiglu(S.gu[tid][0], S.gu[tid][1]);
+    stamp(a, 7);
+    __syncthreads();
+    if (tid == 0) {
+        grid_arrive(a.bar);
+        grid_wait(a.bar, bar_base + 2ull * ncta, a.err);
+    }
+    __syncthreads();
+    stamp(a, 8);
+
+    // ---- phase 3a: Q8-A of the hidden rows (all experts; 8 lanes per group) ----
+    // all loads first (they are L2 round trips), then the arithmetic
     {
-        const uint32_t *tl = tab + lane;
+        constexpr uint32_t HQ_IT = (MAX_E * (F / 4) + NT - 1) / NT;
+        float4 hreg[HQ_IT];
+#pragma unroll
+        for (uint32_t it = 0; it < HQ_IT; it++) {
+            const uint32_t w4 = tid + it * NT;
+            if (w4 < ne * (F / 4)) hreg[it] = __ldcg(reinterpret_cast<const float4 *>(a.h) + w4);
+        }
+#pragma unroll
+        for (uint32_t it = 0; it < HQ_IT; it++) {
+            const uint32_t w4 = tid + it * NT;
+            if (w4 < ne * (F / 4)) {  // warp-uniform: ne * F / 4 is a multiple of 32
+                float d;
+                int bs;
+                const uint32_t word = quant8_oct(hreg[it], &d, &bs);
+                const uint32_t e = w4 / (F / 4), i = w4 - e * (F / 4);
+                S.hq[e][i] = word;
+                if ((lane & 7u) == 0) {
+                    S.hd[e][i >> 3] = d;
+                    S.hbs[e][i >> 3] = bs;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    stamp(a, 9);
+
+    // ---- phase 3b: down tiles; tile = 4 rows x 2 blocks; lane: block l/4 -> row l/8, half (l/4)&1 ----
+    mbar_wait(&S.mbar[MB_DOWN], 0, a.err);
+    stamp(a, 10);
+    {
         const uint32_t col16 = 16u * (lane & 7u);  // first activation word of this lane's 64 columns
+        const uint32_t g0 = 2u * (lane & 7u);
         for (uint32_t v = v0 + warp; v < v1; v += NW) {
             const uint32_t rq = v / ne, e = v - rq * ne;
-            int q[16];
+            int hqr[16];
 #pragma unroll
             for (int i = 0; i < 16; i += 4) {
                 const uint4 t4 = *reinterpret_cast<const uint4 *>(&S.hq[e][col16 + i]);
-                q[i] = (int)t4.x;
-                q[i + 1] = (int)t4.y;
-                q[i + 2] = (int)t4.z;
-                q[i + 3] = (int)t4.w;
+                hqr[i] = (int)t4.x;
+                hqr[i + 1] = (int)t4.y;
+                hqr[i + 2] = (int)t4.z;
+                hqr[i + 3] = (int)t4.w;
             }
-            const uint32_t g0 = 2u * (lane & 7u);
-            float r = q4b_tile_lane_dot(dstage + (size_t)(v - v0) * Q4B_TILE_BYTES, lane, tl, q,
+            float r = q4b_tile_lane_dot(dstage + (size_t)(v - v0) * Q4B_TILE_BYTES, lane, tl, hqr,
                                         S.hd[e][g0], S.hd[e][g0 + 1], S.hbs[e][g0], S.hbs[e][g0 + 1]);
             r += __shfl_xor_sync(0xffffffffu, r, 1);
             r += __shfl_xor_sync(0xffffffffu, r, 2);
@@ -438,12 +560,13 @@ __global__ void __launch_bounds__(NT, 1) moe_decode_fused_k(const Args a) {
         }
     }
     __syncthreads();
+    stamp(a, 11);
     // combine over the experts in list order; a row quad split between two CTAs is
     // finished with one atomic add from each (y starts at 0, so the sum of the two
     // parts does not depend on which lands first)
-    {
+    if (v1 > v0) {
         const uint32_t rq_first = v0 / ne, rq_last = (v1 - 1) / ne;
-        for (uint32_t t = tid; t < (rq_last - rq_first + 1) * 4u && v1 > v0; t += NT) {
+        for (uint32_t t = tid; t < (rq_last - rq_first + 1) * 4u; t += NT) {
             const uint32_t rq = rq_first + (t >> 2), row = t & 3u;
             const uint32_t va = max(rq * ne, v0), vb = min((rq + 1) * ne, v1);
             float sum = 0.f;
@@ -454,15 +577,17 @@ __global__ void __launch_bounds__(NT, 1) moe_decode_fused_k(const Args a) {
                 atomicAdd(&a.y[rq * 4u + row], sum);
         }
     }
+    stamp(a, 12);
 }
 
 }  // namespace fused
 
-// Scratch of the fused kernel (allocated once, by the first call or by warm).
+// Scratch of the fused kernel (allocated once, by init / scratch_warm).
 static float *g_f_logit_part = nullptr;
 static float *g_f_h = nullptr;
 static unsigned long long *g_f_bar = nullptr;
 static bool g_f_attr_set = false;
+static unsigned long long *g_f_prof = nullptr;  // set by q4_cuda_fused_profile_enable(1)
 
 static bool fused_scratch() {
     if (g_f_bar) return true;
@@ -475,6 +600,8 @@ static bool fused_scratch() {
 
 bool q4b_fused_warm() { return fused_scratch(); }
 
+// After a bounded wait gave up the barrier counter is no longer a multiple of
+// the grid size: start again from zero.
 void q4b_fused_reset_barrier() {
     if (g_f_bar) cudaMemsetAsync(g_f_bar, 0, sizeof(unsigned long long), g_q4b.stream);
 }
@@ -487,18 +614,21 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
                           float *d_y, int32_t *d_ids, float *d_wts) {
     using namespace fused;
     Q4bState &s = g_q4b;
-    if (n_embd != H || n_ff != F || n_expert > 1024 || (n_expert % 4) || topk > 32) return false;
+    if (n_embd != H || n_ff != F || n_expert > NT || topk > 32) return false;
     if (!q4b_ptr_tiled(base) || (og % 16) || (ou % 16) || (od % 16) || (stride % 16)) return false;
     if (((uintptr_t)d_router % 16) || ((uintptr_t)d_x % 16) || (d_norm_w && ((uintptr_t)d_norm_w % 16)))
         return false;
     if (!fused_scratch()) return false;
     const uint32_t ncta = (uint32_t)s.n_sm;
     const uint32_t ne = topk + (shared_slot >= 0 ? 1u : 0u);
-    const uint32_t max_units = (ne * F + ncta - 1) / ncta + 1;
+    const uint32_t max_units = (topk * F + ncta - 1) / ncta + 1;
     const uint32_t n_chunks = (max_units + UCHUNK - 1) / UCHUNK;
+    const uint32_t max_sh = (F + ncta - 1) / ncta + 1;
     const uint32_t max_dt = ((H / 4) * ne + ncta - 1) / ncta + 1;
     const uint32_t max_rc = (n_expert * (H / RCHUNK) + ncta - 1) / ncta + 1;
-    if (n_chunks > MAX_CHUNKS || max_dt > 64 || ne > MAX_E) return false;
+    if (n_chunks > MAX_CHUNKS || n_chunks > NW - 2 || max_dt > MAX_DT || max_units > MAX_UNITS ||
+        max_sh > MAX_SH || ne > MAX_E)
+        return false;
     Args a;
     a.base = base;
     a.stride = stride;
@@ -509,6 +639,7 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
     a.x = d_x;
     a.norm_w = d_norm_w;
     a.router = d_router;
+    a.codes = s.codes_d;
     a.eps = eps;
     a.n_expert = n_expert;
     a.topk = topk;
@@ -519,14 +650,14 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
     a.h = g_f_h;
     a.bar = g_f_bar;
     a.err = s.err_d;
+    a.prof = g_f_prof;
     uint32_t stage_bytes = n_chunks * UCHUNK * 2u * Q4B_TILE_BYTES;
     if (stage_bytes < max_rc * RCHUNK * 4u) stage_bytes = max_rc * RCHUNK * 4u;
     const uint32_t small = (uint32_t)((sizeof(Small) + 127) & ~127u);
     a.off_stage = 65536u + small;
-    a.stage_bytes = (stage_bytes + 127u) & ~127u;
-    a.off_down = a.off_stage + a.stage_bytes;
-    a.down_bytes = max_dt * Q4B_TILE_BYTES;
-    const size_t smem = (size_t)a.off_down + a.down_bytes + 1024;
+    a.off_down = a.off_stage + ((stage_bytes + 127u) & ~127u);
+    a.off_sh = a.off_down + ((max_dt * Q4B_TILE_BYTES + 127u) & ~127u);
+    const size_t smem = (size_t)a.off_sh + 2u * MAX_SH * Q4B_TILE_BYTES + 1024;
     if (smem > 227u * 1024u) return false;
     if (!g_f_attr_set) {
         Q4B_CHECK(cudaFuncSetAttribute(moe_decode_fused_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -549,4 +680,30 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
     }
     g_q4b_launches++;
     return true;
+}
+
+// In-kernel phase profile of the persistent decode kernel (diagnostics).
+// enable(1) allocates the stamp buffer (not inside a capture); read copies the
+// stamps of the last launch: out[cta * 16 + slot] in nanoseconds of the GPU's
+// global timer; returns the number of CTAs.
+extern "C" bool q4_cuda_fused_profile_enable(int on) {
+    if (!g_q4b.ok) return false;
+    if (on && !g_f_prof) {
+        Q4B_CHECK(cudaMalloc(&g_f_prof, (size_t)g_q4b.n_sm * 16 * sizeof(unsigned long long)));
+        Q4B_CHECK(cudaMemset(g_f_prof, 0, (size_t)g_q4b.n_sm * 16 * sizeof(unsigned long long)));
+    } else if (!on && g_f_prof) {
+        cudaStreamSynchronize(g_q4b.stream);
+        cudaFree(g_f_prof);
+        g_f_prof = nullptr;
+    }
+    return true;
+}
+extern "C" uint32_t q4_cuda_fused_profile_read(unsigned long long *out, uint32_t max_ctas) {
+    if (!g_q4b.ok || !g_f_prof || !out) return 0;
+    const uint32_t n = max_ctas < (uint32_t)g_q4b.n_sm ? max_ctas : (uint32_t)g_q4b.n_sm;
+    if (cudaMemcpyAsync(out, g_f_prof, (size_t)n * 16 * sizeof(unsigned long long),
+                        cudaMemcpyDeviceToHost, g_q4b.stream) != cudaSuccess ||
+        cudaStreamSynchronize(g_q4b.stream) != cudaSuccess)
+        return 0;
+    return n;
 }

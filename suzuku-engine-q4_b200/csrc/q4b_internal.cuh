@@ -34,6 +34,7 @@ struct Q4bState {
     float *topk_wts_d;
     uint32_t *err_d;  // device error word (bounded waits, argument checks)
     uint32_t *err_h;
+    uint32_t *codes_d;  // the 512 codebook entries byte-expanded (c_j in byte j), device memory
     // scratch of the fused layer entry points (q4_cuda_moe_decode*)
     float *xn;        // [Q4B_MAX_TOK][Q4B_XQ_MAXLEN] normalised rows
     float *logits;    // [Q4B_MAX_TOK][1024]

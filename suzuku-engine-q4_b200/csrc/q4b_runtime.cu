@@ -12,6 +12,7 @@
 #include "iq3s_codes.h"
 
 Q4bState g_q4b = {};
+bool q4b_fused_warm();  // q4b_fused.cu: scratch of the persistent decode kernel
 std::atomic<uint64_t> g_q4b_launches{0};
 
 namespace {
@@ -113,7 +114,7 @@ bool alloc_scratch() {
     Q4B_CHECK(cudaMalloc(&s.r_wts, (size_t)Q4B_MAX_TOK * 64 * sizeof(float)));
     Q4B_CHECK(cudaMalloc(&s.r_cnt, (size_t)Q4B_MAX_TOK * sizeof(int32_t)));
     Q4B_CHECK(cudaMalloc(&s.hbuf, nq * sizeof(float)));
-    return true;
+    return q4b_fused_warm();
 }
 
 }  // namespace
@@ -153,6 +154,15 @@ extern "C" bool q4_hip_init(void) {
     Q4B_CHECK(cudaMalloc(&s.err_d, sizeof(uint32_t)));
     Q4B_CHECK(cudaMemset(s.err_d, 0, sizeof(uint32_t)));
     Q4B_CHECK(cudaHostAlloc(&s.err_h, sizeof(uint32_t), cudaHostAllocDefault));
+    {
+        uint32_t codes[512];
+        for (int i = 0; i < 512; i++) {
+            const uint32_t c = q4b_iq3s_codes[i];
+            codes[i] = (c & 7u) | ((c & 0x38u) << 5) | ((c & 0x1c0u) << 10) | ((c & 0xe00u) << 15);
+        }
+        Q4B_CHECK(cudaMalloc(&s.codes_d, sizeof(codes)));
+        Q4B_CHECK(cudaMemcpy(s.codes_d, codes, sizeof(codes), cudaMemcpyHostToDevice));
+    }
     Q4B_CHECK(cudaEventCreate(&g_ev0));
     Q4B_CHECK(cudaEventCreate(&g_ev1));
     if (!alloc_scratch()) return false;
@@ -189,6 +199,7 @@ extern "C" void q4_hip_shutdown(void) {
     cudaFree(s.topk_ids_d);
     cudaFree(s.topk_wts_d);
     cudaFree(s.err_d);
+    cudaFree(s.codes_d);
     cudaFreeHost(s.err_h);
     cudaEventDestroy(g_ev0);
     cudaEventDestroy(g_ev1);
