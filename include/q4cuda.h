@@ -134,6 +134,60 @@ bool q4_hip_gemv_dd(uint32_t ggml_type, const uint8_t *d_w, uint64_t nrows, uint
 bool q4_hip_gemv_dd_n(uint32_t ggml_type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
                       const float *d_x, float *d_y, float scale, uint32_t n_batch);
 
+/* ---------------- many tokens: prefill chunks and verify windows ----------------
+ * (src/q4.h:1126-1128, 1131-1175, 1278-1285, 887-897)
+ * The engine's own sequence (src/q4_moe.c:3166-3251, 3697-3748, 3887):
+ *   route_pf   per token: softmax, top-k (ties to the lower index), weights
+ *              renormalised; ids/wts are [n_tok][topk]
+ *   assign_pf  per group of gsz tokens: picks sorted by expert.  Row p of group g
+ *              (p counts from the group's first row g*gsz*topk) belongs to token
+ *              a_tok[g*gsz*topk + p]; rsrc[t*topk+k] = p of pick k of token t (-1 for
+ *              an id outside [0, n_exp)); rw = its weight; ek[g*512+e] = rows of
+ *              expert e; stg[g*512 + i] = i-th used expert; stgn[g] = how many.
+ *              Rows of one expert are in (token, pick) order.  n_exp <= 512.
+ *   quantize   xq rows = Q8-A of x[ids[r]] (ids NULL = identity); xq is an opaque
+ *              buffer of q4_mmq_q8_bytes(rows, cols) bytes
+ *   mul_id     expert e owns xq/dst rows [bounds[e], bounds[e+1]) (device int32,
+ *              n_expert+1 entries), weights at w + e*expert_stride_bytes, w_rows x
+ *              w_cols IQ3_S; dst rows keep the xq order, ld_dst floats apart.  Gate and
+ *              up are one [2*n_ff x n_embd] matrix per expert (contiguous in the pack).
+ *   swiglu     h[r][k] = silu(gu[r][k]) * gu[r][n_ff + k]
+ *   expert_reduce  y[t] += sum_k rw[t][k] * pd[rsrc[t][k]], k ascending
+ * w_cols a multiple of 256 with w_rows * w_cols / 256 a multiple of 8.  Rows of 256,
+ * 512, 1024 or 2048 columns are summed in a fixed order (reproducible); other widths
+ * use atomic adds. */
+int q4_mmq_on(void);
+uint32_t q4_mmq_group(void);
+bool q4_mmq_supported(uint32_t type, uint64_t w_rows);
+uint64_t q4_mmq_q8_bytes(uint64_t rows, uint64_t cols);
+uint64_t q4_mmq_pad(uint64_t row_bytes);
+bool q4_mmq_quantize(const float *x, const int32_t *ids, void *xq, uint32_t w_type, uint64_t cols,
+                     uint64_t rows);
+bool q4_mmq_mul_id(const void *w, uint32_t type, uint64_t w_rows, uint64_t w_cols,
+                   uint64_t expert_stride_bytes, uint32_t n_expert, const void *xq,
+                   const int32_t *bounds, uint32_t max_rows, uint64_t total_rows, float *dst,
+                   uint64_t ld_dst);
+bool q4_mmq_swiglu(const float *gu, float *h, uint64_t rows, uint64_t n_ff);
+bool q4_hip_expert_reduce(float *d_y, const float *d_pd, const int32_t *d_rsrc, const float *d_rw,
+                          uint32_t n_tok, uint32_t topk, uint32_t n_embd);
+bool q4_hip_route_pf(const float *d_rlog, int32_t *d_ids, float *d_wts, uint32_t n_tok,
+                     uint32_t n_exp, uint32_t topk);
+bool q4_hip_assign_pf(const int32_t *d_ids, const float *d_wts, int32_t *d_atok, int32_t *d_rsrc,
+                      float *d_rw, int32_t *d_stg, uint32_t *d_stgn, uint32_t *d_ek, uint32_t gsz,
+                      uint32_t topk, uint32_t n_exp, uint32_t n_tok);
+/* 2..8 token verify window over per-token slot lists (d_es/d_ew at t*64, count in
+ * d_nh[t]): every distinct expert is decoded once and applied to all the tokens that
+ * picked it; d_y[t] (n_embd floats per token) is ADDED to; each token's result is the
+ * one q4_hip_moe_exec_dev gives for that token alone, up to the order of the final
+ * sum.  d_x is n_tok rows of in_dim floats; d_h is unused. */
+bool q4_hip_moe_win_ok(uint32_t gt, uint32_t ut, uint32_t dt, uint32_t in_dim, uint32_t n_ff,
+                       uint32_t n_tok);
+bool q4_hip_moe_exec_win(const uint8_t *base, uint64_t stride, const int32_t *d_es,
+                         const float *d_ew, const int32_t *d_nh, uint32_t n_tok, uint32_t gt,
+                         uint64_t og, uint32_t ut, uint64_t ou, uint32_t dt, uint64_t od,
+                         const float *d_x, float *d_h, float *d_y, uint32_t n_ff, uint32_t in_dim,
+                         uint32_t n_embd);
+
 /* ---------------- additions (no single counterpart in the reference) ------------ */
 
 /* Stage tests: the building blocks of the expert kernels, exposed so that the
@@ -166,6 +220,21 @@ bool q4_cuda_moe_decode(const uint8_t *base, uint64_t stride, uint64_t og, uint6
                         const float *d_norm_w, float eps, const float *d_router,
                         uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
                         float *d_y, int32_t *d_ids, float *d_wts);
+
+/* One MoE layer for n_tok tokens (any number: a verify window, an expert-parallel
+ * shard's batch, a prefill chunk): the sequence above in one call, every stage on
+ * the device.  Arguments as q4_cuda_moe_decode, with d_x / d_y holding n_tok rows,
+ * d_ids / d_wts [n_tok][topk], the shared expert (if any) in slot n_expert and gate
+ * and up contiguous in the pack (ou == og + gate bytes).  d_ws is caller-owned
+ * scratch of at least q4_cuda_moe_layer_n_ws_bytes(...) bytes. */
+uint64_t q4_cuda_moe_layer_n_ws_bytes(uint32_t n_tok, uint32_t topk, uint32_t n_expert,
+                                      uint32_t n_embd, uint32_t n_ff);
+bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou,
+                         uint64_t od, int32_t shared_slot, const float *d_x,
+                         const float *d_norm_w, float eps, const float *d_router,
+                         uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
+                         uint32_t n_tok, float *d_y, int32_t *d_ids, float *d_wts, void *d_ws,
+                         uint64_t ws_bytes);
 
 /* Resident storage format of an arena.  By default q4_hip_experts_put*_a rewrites
  * each pack, in place and at the same size, into the library's tiled form of

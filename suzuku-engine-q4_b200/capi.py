@@ -73,11 +73,28 @@ SIGNATURES = {
     "q4_hip_grouped_rms_n": (b, [vp, vp, vp, u32, u32, f32, u32]),
     "q4_hip_gemv_dd": (b, [u32, vp, u64, u64, vp, vp, f32]),
     "q4_hip_gemv_dd_n": (b, [u32, vp, u64, u64, vp, vp, f32, u32]),
+    "q4_mmq_on": (C.c_int, []),
+    "q4_mmq_group": (u32, []),
+    "q4_mmq_supported": (b, [u32, u64]),
+    "q4_mmq_q8_bytes": (u64, [u64, u64]),
+    "q4_mmq_pad": (u64, [u64]),
+    "q4_mmq_quantize": (b, [vp, vp, vp, u32, u64, u64]),
+    "q4_mmq_mul_id": (b, [vp, u32, u64, u64, u64, u32, vp, vp, u32, u64, vp, u64]),
+    "q4_mmq_swiglu": (b, [vp, vp, u64, u64]),
+    "q4_hip_expert_reduce": (b, [vp, vp, vp, vp, u32, u32, u32]),
+    "q4_hip_route_pf": (b, [vp, vp, vp, u32, u32, u32]),
+    "q4_hip_assign_pf": (b, [vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32, u32]),
+    "q4_hip_moe_win_ok": (b, [u32, u32, u32, u32, u32, u32]),
+    "q4_hip_moe_exec_win": (b, [vp, u64, vp, vp, vp, u32, u32, u64, u32, u64, u32, u64, vp, vp, vp,
+                                u32, u32, u32]),
     "q4_cuda_quant8": (b, [vp, u64, vp, vp, vp]),
     "q4_cuda_iq3s_dequant": (b, [vp, u64, u64, vp]),
     "q4_cuda_iq3s_idot": (b, [vp, u64, u64, vp, vp]),
     "q4_cuda_moe_decode": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32, u32,
                                vp, vp, vp]),
+    "q4_cuda_moe_layer_n_ws_bytes": (u64, [u32, u32, u32, u32, u32]),
+    "q4_cuda_moe_layer_n": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32, u32,
+                                u32, vp, vp, vp, vp, u64]),
     "q4_cuda_set_tiled_default": (None, [C.c_int]),
     "q4_cuda_experts_tiled_a": (C.c_int, [C.c_int]),
     "q4_cuda_experts_retile_a": (b, [C.c_int, u32, u32]),

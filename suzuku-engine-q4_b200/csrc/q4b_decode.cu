@@ -716,3 +716,18 @@ extern "C" bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, ui
     Q4B_CHECK(cudaStreamSynchronize(s.stream));
     return true;
 }
+
+// ---- helpers shared with the many-token path (q4b_grouped.cu) ----
+bool q4b_route_tokens(const float *d_rlog, int32_t *d_ids, float *d_wts, uint32_t n_tok,
+                      uint32_t n_exp, uint32_t topk) {
+    softmax_topk_k<<<n_tok, 32, 0, g_q4b.stream>>>(d_rlog, n_exp, topk, d_ids, d_wts, topk, -1, nullptr);
+    g_q4b_launches++;
+    return q4b_launch_ok("route_tokens");
+}
+bool q4b_rms_rows(const float *x, const float *w, float *y, uint32_t n_embd, float eps,
+                  uint32_t n_tok) {
+    rms_q8_k<<<dim3(1, n_tok), 256, 0, g_q4b.stream>>>(x, w, y, n_embd, 1, eps, nullptr, nullptr,
+                                                      nullptr, 0, 0);
+    g_q4b_launches++;
+    return q4b_launch_ok("rms_rows");
+}

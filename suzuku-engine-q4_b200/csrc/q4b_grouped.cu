@@ -1,0 +1,662 @@
+// The many-token path: rows grouped by expert, every weight tile decoded once
+// and dotted with all the rows of its expert.
+//
+// This is the engine's prefill / verify-window call sequence
+// (src/q4_moe.c:3166-3251, 3697-3748, 3887) behind the same entry points:
+//   q4_hip_route_pf      per-token softmax + top-k            (src/q4_rocm.cu:6383)
+//   q4_hip_assign_pf     rows sorted by expert per token group (src/q4_rocm.cu:6483)
+//   q4_mmq_quantize      activation rows -> 8-bit blocks       (src/q4_mmq.cu:365)
+//   q4_mmq_mul_id        grouped IQ3_S x int8 product          (src/q4_mmq.cu:387)
+//   q4_mmq_swiglu        h = silu(g) * u                       (src/q4_mmq.cu:603)
+//   q4_hip_expert_reduce y[t] += sum_k rw * pd[rsrc]           (src/q4_rocm.cu:15739)
+// plus q4_hip_moe_exec_win (2..8 tokens, src/q4_rocm.cu:7444) and the fused
+// q4_cuda_moe_layer_n built from them.
+//
+// Arithmetic: activations are quantised with Q8-A (src/q4_cpuexp.c:605-637), so a
+// row's result is the same whatever batch it arrives in (the reference's window
+// path has the same property, src/q4_cpuexp.c:1727-1730).  The grouped product
+// here is the CUDA-core form: right for the few rows per expert of decode,
+// verify windows and expert-parallel shards.
+#include "q4b_tile.cuh"
+
+#include <atomic>
+
+#include "../../include/q4cuda.h"
+
+extern std::atomic<uint64_t> g_q4b_launches;
+bool q4b_ptr_tiled(const void *p);
+// defined in q4b_decode.cu
+bool q4b_route_tokens(const float *d_rlog, int32_t *d_ids, float *d_wts, uint32_t n_tok,
+                      uint32_t n_exp, uint32_t topk);
+bool q4b_rms_rows(const float *x, const float *w, float *y, uint32_t n_embd, float eps,
+                  uint32_t n_tok);
+
+namespace grouped {
+
+// Quantised activation rows, planar: int8 q[rows][cols], then float d[rows][cols/32],
+// then int32 bs[rows][cols/32]; each section 256-byte aligned.
+struct Q8View {
+    const int8_t *q;
+    const float *d;
+    const int32_t *bs;
+};
+__host__ __device__ inline uint64_t align256(uint64_t v) { return (v + 255u) & ~(uint64_t)255u; }
+__host__ __device__ inline uint64_t q8_bytes(uint64_t rows, uint64_t cols) {
+    return align256(rows * cols) + 2u * align256(rows * (cols / 32) * 4u) + 256u;
+}
+__host__ __device__ inline Q8View q8_view(const void *buf, uint64_t rows, uint64_t cols) {
+    Q8View v;
+    const uint8_t *p = (const uint8_t *)buf;
+    v.q = (const int8_t *)p;
+    v.d = (const float *)(p + align256(rows * cols));
+    v.bs = (const int32_t *)(p + align256(rows * cols) + align256(rows * (cols / 32) * 4u));
+    return v;
+}
+
+// One warp per 32 values of one gathered row (a negative source row gives zeros).
+__global__ void quantize_rows_k(const float *__restrict__ x, const int32_t *__restrict__ ids,
+                                uint64_t cols, uint64_t rows, int8_t *__restrict__ q,
+                                float *__restrict__ d, int32_t *__restrict__ bs) {
+    const uint32_t gpr = (uint32_t)(cols >> 5);
+    const uint64_t g = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (g >= rows * gpr) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint64_t r = g / gpr, gl = g - r * gpr;
+    const int64_t src = ids ? (int64_t)ids[r] : (int64_t)r;
+    const float v = src >= 0 ? x[(uint64_t)src * cols + gl * 32u + lane] : 0.f;
+    const float a = q4b_warp_max(fabsf(v));
+    const float sc = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
+    int qi = max(-128, min(127, __float2int_rn(__fmul_rn(v, sc))));
+    int sum = qi;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    q[r * cols + gl * 32u + lane] = (int8_t)qi;
+    if (lane == 0) {
+        d[g] = __fdiv_rn(a, 127.f);
+        bs[g] = sum;
+    }
+}
+
+// One 32-weight group -> eight words of sign-applied code bytes c' (weight = 2c'+1).
+template <bool TILED>
+__device__ __forceinline__ void decode_group(const Iq3Fields &f, const uint32_t *tab, uint32_t *cw) {
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const uint32_t wq = k < 4 ? f.qs_lo : f.qs_hi;
+        const uint32_t idx = ((wq >> (8 * (k & 3))) & 0xffu) | (((f.qh >> k) & 1u) << 8);
+        uint32_t m;
+        if (TILED) {
+            const uint32_t t = f.sg << k;
+            m = q4b_prmt(t, t, 0xba98u);
+        } else {
+            m = q4b_sign_mask4(f.sg >> (4 * k));
+        }
+        cw[k] = tab[idx] ^ m;
+    }
+}
+
+// Grouped product.  Entry i (blockIdx.y) owns activation rows [bounds[i], bounds[i+1])
+// and the weight matrix w + slot * expert_stride with slot = act ? act[i] : i; entries
+// at or beyond *n_act (when given) do nothing.  One warp takes eight consecutive
+// super-blocks (one tile): lane l owns block l/4 and sub-block pair l%4.  With B blocks
+// per weight row a tile spans 8/B whole rows when B is 1, 2, 4 or 8 (rows summed by
+// shuffles, reproducible); for any other B a row's blocks lie in several warps and the
+// per-block partial sums are added with atomics into dst, which the caller zeroes.
+template <bool TILED>
+__global__ void __launch_bounds__(256) grouped_rows_k(
+    const uint8_t *__restrict__ w, uint64_t expert_stride, const int32_t *__restrict__ act,
+    const uint32_t *__restrict__ n_act, const int32_t *__restrict__ bounds, Q8View xq,
+    uint32_t cols, uint32_t w_rows, float *__restrict__ dst, uint64_t ld_dst) {
+    __shared__ uint32_t tab[512];
+    const uint32_t entry = blockIdx.y;
+    if (n_act && entry >= *n_act) return;
+    const int32_t r0 = bounds[entry], r1 = bounds[entry + 1];
+    if (r1 <= r0) return;
+    q4b_fill_code_table(tab);
+    __syncthreads();
+    const uint32_t B = cols >> 8;                        // super-blocks per weight row
+    const uint32_t n_tiles = (w_rows * B) >> 3;
+    const uint32_t ti = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (ti >= n_tiles) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint8_t *mat = w + (uint64_t)(act ? act[entry] : (int32_t)entry) * expert_stride;
+    const uint32_t bi = ti * 8u + (lane >> 2);           // this lane's super-block in the matrix
+    const uint32_t wrow = bi / B, brow = bi - wrow * B;  // weight row, block within the row
+    const uint32_t p = lane & 3u;
+    // decode once: the lane's two groups
+    uint32_t cw[16];
+    uint32_t ls0, ls1;
+    float dblk;
+    {
+        const Iq3Fields f0 = iq3_fields<TILED>(mat, bi, 2u * p);
+        const Iq3Fields f1 = iq3_fields<TILED>(mat, bi, 2u * p + 1u);
+        decode_group<TILED>(f0, tab, cw);
+        decode_group<TILED>(f1, tab, cw + 8);
+        ls0 = f0.ls;
+        ls1 = f1.ls;
+        dblk = f0.d;
+    }
+    const uint32_t gcol = brow * 8u + 2u * p;             // first of the lane's two 32-groups
+    const uint32_t ngr = cols >> 5;
+    const bool pow2 = B == 1 || B == 2 || B == 4 || B == 8;
+    const uint32_t lanes_per_row = 4u * B;
+    for (int32_t r = r0; r < r1; r++) {
+        const int4 *qp = reinterpret_cast<const int4 *>(xq.q + (uint64_t)r * cols + gcol * 32u);
+        const int4 q0 = __ldg(qp), q1 = __ldg(qp + 1), q2 = __ldg(qp + 2), q3 = __ldg(qp + 3);
+        const uint64_t go = (uint64_t)r * ngr + gcol;
+        const float dx0 = __ldg(xq.d + go), dx1 = __ldg(xq.d + go + 1);
+        const int b0 = __ldg(xq.bs + go), b1 = __ldg(xq.bs + go + 1);
+        int a0 = 0, a1 = 0;
+        a0 = __dp4a((int)cw[0], q0.x, a0);
+        a0 = __dp4a((int)cw[1], q0.y, a0);
+        a0 = __dp4a((int)cw[2], q0.z, a0);
+        a0 = __dp4a((int)cw[3], q0.w, a0);
+        a0 = __dp4a((int)cw[4], q1.x, a0);
+        a0 = __dp4a((int)cw[5], q1.y, a0);
+        a0 = __dp4a((int)cw[6], q1.z, a0);
+        a0 = __dp4a((int)cw[7], q1.w, a0);
+        a1 = __dp4a((int)cw[8], q2.x, a1);
+        a1 = __dp4a((int)cw[9], q2.y, a1);
+        a1 = __dp4a((int)cw[10], q2.z, a1);
+        a1 = __dp4a((int)cw[11], q2.w, a1);
+        a1 = __dp4a((int)cw[12], q3.x, a1);
+        a1 = __dp4a((int)cw[13], q3.y, a1);
+        a1 = __dp4a((int)cw[14], q3.z, a1);
+        a1 = __dp4a((int)cw[15], q3.w, a1);
+        const int I0 = 2 * a0 + b0, I1 = 2 * a1 + b1;    // sum sign*(2c+1)*q = 2 sum c'q + sum q
+        float v = dblk * ((float)(I0 * (int)ls0) * dx0 + (float)(I1 * (int)ls1) * dx1);
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        float *o = dst + (uint64_t)r * ld_dst + wrow;
+        if (pow2) {  // a weight row is 4*B neighbouring lanes of this warp
+            if (B >= 2) v += __shfl_xor_sync(0xffffffffu, v, 4);
+            if (B >= 4) v += __shfl_xor_sync(0xffffffffu, v, 8);
+            if (B >= 8) v += __shfl_xor_sync(0xffffffffu, v, 16);
+            if ((lane & (lanes_per_row - 1u)) == 0) *o = v;
+        } else if (p == 0) {
+            atomicAdd(o, v);  // other widths: a row is spread over warps, one add per block
+        }
+    }
+}
+
+__global__ void swiglu_rows_k(const float *__restrict__ gu, float *__restrict__ h, uint64_t rows,
+                              uint64_t n_ff) {
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * n_ff) return;
+    const uint64_t r = i / n_ff, k = i - r * n_ff;
+    h[i] = q4b_swiglu(gu[r * 2 * n_ff + k], gu[r * 2 * n_ff + n_ff + k]);
+}
+
+// y[t][c] += sum_k rw[t][k] * pd[rsrc[t][k]][c], picks in order k = 0..topk-1.
+__global__ void expert_reduce_k(float *__restrict__ y, const float *__restrict__ pd,
+                                const int32_t *__restrict__ rsrc, const float *__restrict__ rw,
+                                uint32_t topk, uint32_t n_embd) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= n_embd) return;
+    float acc = 0.f;
+    for (uint32_t k = 0; k < topk; k++) {
+        const int32_t p = rsrc[(uint64_t)t * topk + k];
+        if (p >= 0) acc += rw[(uint64_t)t * topk + k] * pd[(uint64_t)p * n_embd + c];
+    }
+    y[(uint64_t)t * n_embd + c] += acc;
+}
+
+// One block (256 threads) per group of gsz tokens: count picks per expert, prefix,
+// place rows, list the used experts.  Rows of one expert keep (token, pick) order: the
+// picks are walked 256 at a time, one warp after the other, each lane finding its place
+// among the lanes of its warp that picked the same expert.
+__global__ void __launch_bounds__(256) assign_k(
+    const int32_t *__restrict__ ids, const float *__restrict__ wts, int32_t *__restrict__ a_tok,
+    int32_t *__restrict__ rsrc, float *__restrict__ rw, int32_t *__restrict__ stg,
+    uint32_t *__restrict__ stgn, uint32_t *__restrict__ ek, int32_t *__restrict__ cbounds,
+    uint32_t gsz, uint32_t topk, uint32_t n_exp, uint32_t n_tok, uint32_t ek_stride) {
+    extern __shared__ uint32_t sh[];  // cnt[n_exp] then cur[n_exp]
+    uint32_t *cnt = sh, *cur = sh + n_exp;
+    const uint32_t g = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t t0 = g * gsz, t1 = min(t0 + gsz, n_tok);
+    const uint32_t seg = g * gsz * topk, rows = (t1 - t0) * topk;
+    for (uint32_t i = tid; i < n_exp; i += blockDim.x) cnt[i] = 0;
+    __syncthreads();
+    for (uint32_t i = tid; i < rows; i += blockDim.x) {
+        const int32_t e = ids[(uint64_t)t0 * topk + i];
+        if (e >= 0 && (uint32_t)e < n_exp) atomicAdd(&cnt[e], 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t b = 0, nu = 0;
+        for (uint32_t e = 0; e < n_exp; e++) {
+            cur[e] = b;
+            if (cnt[e]) {
+                if (stg) stg[g * ek_stride + nu] = (int32_t)e;
+                if (cbounds) cbounds[g * (ek_stride + 1) + nu] = (int32_t)b;
+                b += cnt[e];
+                nu++;
+            }
+        }
+        if (cbounds) cbounds[g * (ek_stride + 1) + nu] = (int32_t)b;
+        if (stgn) stgn[g] = nu;
+    }
+    __syncthreads();
+    if (ek)
+        for (uint32_t i = tid; i < n_exp; i += blockDim.x) ek[g * ek_stride + i] = cnt[i];
+    for (uint32_t i0 = 0; i0 < rows; i0 += blockDim.x) {
+        const uint32_t i = i0 + tid;
+        int32_t e = -1;
+        uint32_t t = 0, k = 0;
+        if (i < rows) {
+            t = t0 + i / topk;
+            k = i % topk;
+            e = ids[(uint64_t)t * topk + k];
+            if (e < 0 || (uint32_t)e >= n_exp) e = -1;
+        }
+        for (uint32_t wv = 0; wv < 8; wv++) {
+            if (warp == wv) {
+                const uint32_t same = __match_any_sync(0xffffffffu, e);
+                if (e >= 0) {
+                    const uint32_t before = __popc(same & ((1u << lane) - 1u));
+                    const uint32_t pos = cur[e] + before;
+                    a_tok[seg + pos] = (int32_t)t;
+                    rsrc[(uint64_t)t * topk + k] = (int32_t)pos;
+                    rw[(uint64_t)t * topk + k] = wts[(uint64_t)t * topk + k];
+                    __syncwarp(same);
+                    if (before == 0) cur[e] += __popc(same);
+                } else if (i < rows) {
+                    rsrc[(uint64_t)t * topk + k] = -1;
+                    rw[(uint64_t)t * topk + k] = 0.f;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// Append the shared expert (id n_expert, weight 1) as an extra pick of every token:
+// [n_tok][topk] -> [n_tok][topk + 1].
+__global__ void add_shared_pick_k(const int32_t *__restrict__ ids, const float *__restrict__ wts,
+                                  int32_t *__restrict__ ids2, float *__restrict__ wts2,
+                                  uint32_t n_tok, uint32_t topk, int32_t shared_id) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tok * (topk + 1)) return;
+    const uint32_t t = i / (topk + 1), k = i - t * (topk + 1);
+    ids2[i] = k < topk ? ids[t * topk + k] : shared_id;
+    wts2[i] = k < topk ? wts[t * topk + k] : 1.0f;
+}
+
+// Verify window: per-token slot lists (stride 64, count per token; n_tok <= 8) ->
+// entries = distinct slots in order of first appearance, their rows in (token, pick)
+// order, bounds per entry.  One block of 512 threads, one per possible pick.
+__global__ void __launch_bounds__(512) win_assign_k(
+    const int32_t *__restrict__ es, const float *__restrict__ ew, const int32_t *__restrict__ nh,
+    uint32_t n_tok, int32_t *__restrict__ act, uint32_t *__restrict__ n_act,
+    int32_t *__restrict__ bounds, int32_t *__restrict__ a_tok, int32_t *__restrict__ rsrc,
+    float *__restrict__ rw) {
+    __shared__ int32_t slot[512];
+    __shared__ int32_t lead[512];   // index of the first pick with the same slot, or -1 (invalid)
+    __shared__ int32_t ent[512];    // entry number of a leader
+    __shared__ int32_t size[513];
+    const uint32_t i = threadIdx.x, t = i >> 6, k = i & 63u;
+    const bool valid = t < n_tok && (int32_t)k < nh[t];
+    slot[i] = valid ? es[i] : -1;
+    __syncthreads();
+    int32_t first = -1, before = 0;
+    if (valid) {
+        for (uint32_t j = 0; j < i; j++)
+            if (slot[j] == slot[i]) {
+                if (first < 0) first = (int32_t)j;
+                before++;
+            }
+        if (first < 0) first = (int32_t)i;
+    }
+    lead[i] = first;
+    __syncthreads();
+    // entry number of leader i = number of leaders before it
+    int32_t my_ent = 0;
+    if (valid && first == (int32_t)i) {
+        for (uint32_t j = 0; j < i; j++) my_ent += lead[j] == (int32_t)j ? 1 : 0;
+        ent[i] = my_ent;
+        act[my_ent] = slot[i];
+    }
+    size[i] = 0;
+    if (i == 0) size[512] = 0;
+    __syncthreads();
+    if (valid) atomicAdd(&size[ent[first]], 1);
+    __syncthreads();
+    if (i == 0) {
+        int32_t n = 0, b = 0;
+        for (uint32_t j = 0; j < 512; j++) n += lead[j] == (int32_t)j ? 1 : 0;
+        for (int32_t j = 0; j < n; j++) {
+            bounds[j] = b;
+            b += size[j];
+            size[j] = bounds[j];   // becomes the entry's first row
+        }
+        bounds[n] = b;
+        *n_act = (uint32_t)n;
+    }
+    __syncthreads();
+    if (valid) {
+        const int32_t pos = size[ent[first]] + before;
+        a_tok[pos] = (int32_t)t;
+        rsrc[i] = pos;
+        rw[i] = ew[i];
+    } else {
+        rsrc[i] = -1;
+        rw[i] = 0.f;
+    }
+}
+
+bool launch_grouped(const uint8_t *w, uint64_t expert_stride, const int32_t *act,
+                    const uint32_t *n_act, uint32_t n_entries, const int32_t *bounds, Q8View xq,
+                    uint32_t cols, uint32_t w_rows, float *dst, uint64_t ld_dst) {
+    const uint32_t B = cols >> 8;
+    const uint32_t n_tiles = (w_rows * B) >> 3;
+    const dim3 grid((n_tiles + 7) / 8, n_entries);
+    if (q4b_ptr_tiled(w))
+        grouped_rows_k<true><<<grid, 256, 0, g_q4b.stream>>>(w, expert_stride, act, n_act, bounds, xq,
+                                                            cols, w_rows, dst, ld_dst);
+    else
+        grouped_rows_k<false><<<grid, 256, 0, g_q4b.stream>>>(w, expert_stride, act, n_act, bounds, xq,
+                                                             cols, w_rows, dst, ld_dst);
+    g_q4b_launches++;
+    return q4b_launch_ok("grouped_rows");
+}
+
+bool pow2_blocks(uint64_t w_cols) {
+    const uint64_t B = w_cols / 256u;
+    return B == 1 || B == 2 || B == 4 || B == 8;
+}
+
+bool shape_ok(uint32_t type, uint64_t w_rows, uint64_t w_cols) {
+    if (type != Q4_T_IQ3_S || w_rows == 0 || w_cols == 0 || (w_cols % 256u)) return false;
+    const uint64_t B = w_cols / 256u;
+    return ((w_rows * B) % 8u) == 0;
+}
+
+}  // namespace grouped
+
+using namespace grouped;
+
+extern "C" int q4_mmq_on(void) { return g_q4b.ok ? 1 : 0; }
+extern "C" uint32_t q4_mmq_group(void) { return 4096u; }
+extern "C" bool q4_mmq_supported(uint32_t type, uint64_t w_rows) {
+    return g_q4b.ok && type == Q4_T_IQ3_S && w_rows != 0 && (w_rows % 8u) == 0;
+}
+extern "C" uint64_t q4_mmq_q8_bytes(uint64_t rows, uint64_t cols) { return q8_bytes(rows, cols); }
+extern "C" uint64_t q4_mmq_pad(uint64_t row_bytes) {
+    (void)row_bytes;
+    return 0;  // the kernels here never read past a matrix: no zero pad is needed
+}
+
+extern "C" bool q4_mmq_quantize(const float *x, const int32_t *ids, void *xq, uint32_t w_type,
+                                uint64_t cols, uint64_t rows) {
+    if (!g_q4b.ok || !x || !xq || w_type != Q4_T_IQ3_S || rows == 0 || cols == 0 || (cols % 32u))
+        return false;
+    const Q8View v = q8_view(xq, rows, cols);
+    const uint64_t ngr = rows * (cols / 32u);
+    quantize_rows_k<<<(unsigned)((ngr + 7) / 8), 256, 0, g_q4b.stream>>>(
+        x, ids, cols, rows, (int8_t *)v.q, (float *)v.d, (int32_t *)v.bs);
+    g_q4b_launches++;
+    return q4b_launch_ok("quantize_rows");
+}
+
+extern "C" bool q4_mmq_mul_id(const void *w, uint32_t type, uint64_t w_rows, uint64_t w_cols,
+                              uint64_t expert_stride_bytes, uint32_t n_expert, const void *xq,
+                              const int32_t *bounds, uint32_t max_rows, uint64_t total_rows,
+                              float *dst, uint64_t ld_dst) {
+    (void)max_rows;
+    if (!g_q4b.ok || !w || !xq || !bounds || !dst || n_expert == 0 || total_rows == 0) return false;
+    if (!grouped::shape_ok(type, w_rows, w_cols) || ld_dst < w_rows) return false;
+    if (!grouped::pow2_blocks(w_cols) &&
+        cudaMemsetAsync(dst, 0, total_rows * ld_dst * sizeof(float), g_q4b.stream) != cudaSuccess)
+        return false;
+    return launch_grouped((const uint8_t *)w, expert_stride_bytes, nullptr, nullptr, n_expert, bounds,
+                          q8_view(xq, total_rows, w_cols), (uint32_t)w_cols, (uint32_t)w_rows, dst,
+                          ld_dst);
+}
+
+extern "C" bool q4_mmq_swiglu(const float *gu, float *h, uint64_t rows, uint64_t n_ff) {
+    if (!g_q4b.ok || !gu || !h || rows == 0 || n_ff == 0) return false;
+    const uint64_t n = rows * n_ff;
+    swiglu_rows_k<<<(unsigned)((n + 255) / 256), 256, 0, g_q4b.stream>>>(gu, h, rows, n_ff);
+    g_q4b_launches++;
+    return q4b_launch_ok("swiglu_rows");
+}
+
+extern "C" bool q4_hip_expert_reduce(float *d_y, const float *d_pd, const int32_t *d_rsrc,
+                                     const float *d_rw, uint32_t n_tok, uint32_t topk,
+                                     uint32_t n_embd) {
+    if (!g_q4b.ok || !d_y || !d_pd || !d_rsrc || !d_rw || !n_tok || !topk || !n_embd) return false;
+    expert_reduce_k<<<dim3((n_embd + 255) / 256, n_tok), 256, 0, g_q4b.stream>>>(d_y, d_pd, d_rsrc,
+                                                                               d_rw, topk, n_embd);
+    g_q4b_launches++;
+    return q4b_launch_ok("expert_reduce");
+}
+
+extern "C" bool q4_hip_route_pf(const float *d_rlog, int32_t *d_ids, float *d_wts, uint32_t n_tok,
+                                uint32_t n_exp, uint32_t topk) {
+    if (!g_q4b.ok || !d_rlog || !d_ids || !d_wts || !n_tok || n_exp == 0 || n_exp > 1024u || !topk ||
+        topk > 64u)
+        return false;
+    return q4b_route_tokens(d_rlog, d_ids, d_wts, n_tok, n_exp, topk);
+}
+
+static bool launch_assign(const int32_t *d_ids, const float *d_wts, int32_t *d_atok, int32_t *d_rsrc,
+                          float *d_rw, int32_t *d_stg, uint32_t *d_stgn, uint32_t *d_ek,
+                          int32_t *d_cbounds, uint32_t gsz, uint32_t topk, uint32_t n_exp,
+                          uint32_t n_tok, uint32_t ek_stride) {
+    const uint32_t n_g = (n_tok + gsz - 1u) / gsz;
+    assign_k<<<n_g, 256, 2 * n_exp * sizeof(uint32_t), g_q4b.stream>>>(
+        d_ids, d_wts, d_atok, d_rsrc, d_rw, d_stg, d_stgn, d_ek, d_cbounds, gsz, topk, n_exp, n_tok,
+        ek_stride);
+    g_q4b_launches++;
+    return q4b_launch_ok("assign");
+}
+
+extern "C" bool q4_hip_assign_pf(const int32_t *d_ids, const float *d_wts, int32_t *d_atok,
+                                 int32_t *d_rsrc, float *d_rw, int32_t *d_stg, uint32_t *d_stgn,
+                                 uint32_t *d_ek, uint32_t gsz, uint32_t topk, uint32_t n_exp,
+                                 uint32_t n_tok) {
+    if (!g_q4b.ok || !d_ids || !d_wts || !d_atok || !d_rsrc || !d_rw || !d_stg || !d_stgn || !d_ek ||
+        !n_tok || !gsz || !topk || n_exp == 0 || n_exp > 512u || topk > 64u)
+        return false;
+    // tables are 512 entries per group, as in the reference (src/q4_rocm.cu:6545-6548)
+    return launch_assign(d_ids, d_wts, d_atok, d_rsrc, d_rw, d_stg, d_stgn, d_ek, nullptr, gsz, topk,
+                         n_exp, n_tok, 512u);
+}
+
+// ---- the whole layer for n_tok tokens ----
+// Workspace carve-up (all sections 256-byte aligned).
+namespace {
+struct LayerWs {
+    float *xn, *logits, *wts, *wts2, *rw, *gu, *h, *pd;
+    int32_t *ids, *ids2, *atok, *rsrc, *cbounds, *stg;
+    uint32_t *stgn;
+    void *xq, *hq;
+    uint64_t bytes;
+};
+LayerWs carve(uint8_t *p, uint32_t n_tok, uint32_t topk, uint32_t n_expert, uint32_t n_embd,
+              uint32_t n_ff) {
+    LayerWs w;
+    uint64_t off = 0;
+    const uint64_t k1 = topk + 1u, rows = (uint64_t)n_tok * k1;
+    auto take = [&](uint64_t n) {
+        uint8_t *r = p ? p + off : nullptr;
+        off += align256(n);
+        return r;
+    };
+    w.xn = (float *)take((uint64_t)n_tok * n_embd * 4);
+    w.logits = (float *)take((uint64_t)n_tok * n_expert * 4);
+    w.ids = (int32_t *)take((uint64_t)n_tok * topk * 4);
+    w.wts = (float *)take((uint64_t)n_tok * topk * 4);
+    w.ids2 = (int32_t *)take(rows * 4);
+    w.wts2 = (float *)take(rows * 4);
+    w.atok = (int32_t *)take(rows * 4);
+    w.rsrc = (int32_t *)take(rows * 4);
+    w.rw = (float *)take(rows * 4);
+    w.cbounds = (int32_t *)take((uint64_t)(n_expert + 3) * 4);
+    w.stg = (int32_t *)take((uint64_t)(n_expert + 2) * 4);
+    w.stgn = (uint32_t *)take(256);
+    w.xq = take(q8_bytes(rows, n_embd));
+    w.gu = (float *)take(rows * 2 * n_ff * 4);
+    w.h = (float *)take(rows * n_ff * 4);
+    w.hq = take(q8_bytes(rows, n_ff));
+    w.pd = (float *)take(rows * n_embd * 4);
+    w.bytes = off;
+    return w;
+}
+}  // namespace
+
+extern "C" uint64_t q4_cuda_moe_layer_n_ws_bytes(uint32_t n_tok, uint32_t topk, uint32_t n_expert,
+                                                 uint32_t n_embd, uint32_t n_ff) {
+    return carve(nullptr, n_tok, topk, n_expert, n_embd, n_ff).bytes;
+}
+
+extern "C" bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou,
+                                    uint64_t od, int32_t shared_slot, const float *d_x,
+                                    const float *d_norm_w, float eps, const float *d_router,
+                                    uint32_t n_expert, uint32_t topk, uint32_t n_embd,
+                                    uint32_t n_ff, uint32_t n_tok, float *d_y, int32_t *d_ids,
+                                    float *d_wts, void *d_ws, uint64_t ws_bytes) {
+    if (!g_q4b.ok || !base || !d_x || !d_router || !d_y || !d_ws || n_tok == 0) return false;
+    if (n_expert == 0 || n_expert >= 1024u || topk == 0 || topk > 63u || topk > n_expert) return false;
+    if (!grouped::shape_ok(Q4_T_IQ3_S, 2ull * n_ff, n_embd) || !grouped::shape_ok(Q4_T_IQ3_S, n_embd, n_ff))
+        return false;
+    if (ou != og + (uint64_t)n_ff * (n_embd / 256u) * Q4B_IQ3S_BYTES) return false;  // gate|up contiguous
+    if (shared_slot >= 0 && (uint32_t)shared_slot != n_expert) return false;  // shared = slot n_expert
+    const LayerWs w = carve((uint8_t *)d_ws, n_tok, topk, n_expert, n_embd, n_ff);
+    if (ws_bytes < w.bytes) return false;
+    cudaStream_t st = g_q4b.stream;
+    const bool sh = shared_slot >= 0;
+    const uint32_t k1 = topk + (sh ? 1u : 0u), n_e = n_expert + (sh ? 1u : 0u);
+    const uint64_t rows = (uint64_t)n_tok * k1;
+    const uint32_t n_entries = (uint32_t)(rows < n_e ? rows : n_e);  // used experts <= rows
+    if (!q4b_rms_rows(d_x, d_norm_w, w.xn, n_embd, eps, n_tok)) return false;
+    if (!q4_hip_gemv_dd_n(Q4_T_F32, (const uint8_t *)d_router, n_expert, n_embd, w.xn, w.logits, 1.0f,
+                          n_tok))
+        return false;
+    if (!q4b_route_tokens(w.logits, w.ids, w.wts, n_tok, n_expert, topk)) return false;
+    const int32_t *ids = w.ids;
+    const float *wts = w.wts;
+    if (sh) {
+        add_shared_pick_k<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(w.ids, w.wts, w.ids2, w.wts2,
+                                                                        n_tok, topk, (int32_t)n_expert);
+        g_q4b_launches++;
+        if (!q4b_launch_ok("add_shared_pick")) return false;
+        ids = w.ids2;
+        wts = w.wts2;
+    }
+    if (!launch_assign(ids, wts, w.atok, w.rsrc, w.rw, w.stg, w.stgn, nullptr, w.cbounds, n_tok, k1,
+                       n_e, n_tok, n_e))
+        return false;
+    if (!q4_mmq_quantize(w.xn, w.atok, w.xq, Q4_T_IQ3_S, n_embd, rows)) return false;
+    if (!grouped::pow2_blocks(n_embd) &&
+        cudaMemsetAsync(w.gu, 0, rows * 2 * n_ff * 4, st) != cudaSuccess)
+        return false;
+    if (!launch_grouped(base + og, stride, w.stg, w.stgn, n_entries, w.cbounds,
+                        q8_view(w.xq, rows, n_embd), n_embd, 2u * n_ff, w.gu, 2ull * n_ff))
+        return false;
+    if (!q4_mmq_swiglu(w.gu, w.h, rows, n_ff)) return false;
+    if (!q4_mmq_quantize(w.h, nullptr, w.hq, Q4_T_IQ3_S, n_ff, rows)) return false;
+    if (!grouped::pow2_blocks(n_ff) && cudaMemsetAsync(w.pd, 0, rows * n_embd * 4, st) != cudaSuccess)
+        return false;
+    if (!launch_grouped(base + od, stride, w.stg, w.stgn, n_entries, w.cbounds,
+                        q8_view(w.hq, rows, n_ff), n_ff, n_embd, w.pd, n_embd))
+        return false;
+    if (cudaMemsetAsync(d_y, 0, (uint64_t)n_tok * n_embd * 4, st) != cudaSuccess) return false;
+    if (!q4_hip_expert_reduce(d_y, w.pd, w.rsrc, w.rw, n_tok, k1, n_embd)) return false;
+    if (d_ids && cudaMemcpyAsync(d_ids, w.ids, (uint64_t)n_tok * topk * 4, cudaMemcpyDeviceToDevice, st) !=
+                     cudaSuccess)
+        return false;
+    if (d_wts && cudaMemcpyAsync(d_wts, w.wts, (uint64_t)n_tok * topk * 4, cudaMemcpyDeviceToDevice, st) !=
+                     cudaSuccess)
+        return false;
+    return true;
+}
+
+// ---- verify window (2..8 tokens), reference entry point ----
+extern "C" bool q4_hip_moe_win_ok(uint32_t gt, uint32_t ut, uint32_t dt, uint32_t in_dim,
+                                  uint32_t n_ff, uint32_t n_tok) {
+    return g_q4b.ok && gt == Q4_T_IQ3_S && ut == Q4_T_IQ3_S && dt == Q4_T_IQ3_S && n_tok >= 2 &&
+           n_tok <= 8 && in_dim <= 16384u && n_ff <= 4096u &&
+           grouped::shape_ok(Q4_T_IQ3_S, n_ff, in_dim) && grouped::shape_ok(Q4_T_IQ3_S, in_dim, n_ff);
+}
+
+// Library-owned scratch of the window path (allocated by init / scratch_warm):
+// 8 tokens x 64 picks, rows up to 16384 wide, hidden rows up to 4096.
+static uint8_t *g_win_ws = nullptr;
+static uint64_t g_win_ws_bytes = 0;
+bool q4b_window_warm() {
+    if (g_win_ws) return true;
+    const uint64_t rows = 512;
+    g_win_ws_bytes = 8 * align256(rows * 4) + align256(514 * 4) + q8_bytes(rows, 16384) +
+                     align256(rows * 2 * 4096 * 4) + align256(rows * 4096 * 4) + q8_bytes(rows, 4096) +
+                     align256(rows * 16384 * 4) + 4096;
+    if (cudaMalloc(&g_win_ws, g_win_ws_bytes) != cudaSuccess) {
+        cudaGetLastError();
+        g_win_ws = nullptr;
+        return false;
+    }
+    return true;
+}
+
+extern "C" bool q4_hip_moe_exec_win(const uint8_t *base, uint64_t stride, const int32_t *d_es,
+                                    const float *d_ew, const int32_t *d_nh, uint32_t n_tok,
+                                    uint32_t gt, uint64_t og, uint32_t ut, uint64_t ou, uint32_t dt,
+                                    uint64_t od, const float *d_x, float *d_h, float *d_y,
+                                    uint32_t n_ff, uint32_t in_dim, uint32_t n_embd) {
+    (void)d_h;
+    if (!g_q4b.ok || !base || !d_es || !d_ew || !d_nh || !d_x || !d_y) return false;
+    if (!q4_hip_moe_win_ok(gt, ut, dt, in_dim, n_ff, n_tok) || n_embd > 16384u ||
+        !grouped::shape_ok(Q4_T_IQ3_S, n_embd, n_ff))
+        return false;
+    if (!q4b_window_warm()) return false;
+    cudaStream_t st = g_q4b.stream;
+    const uint64_t rows = 512;  // 8 tokens x 64 picks; only the placed rows are touched
+    uint8_t *p = g_win_ws;
+    auto take = [&](uint64_t n) {
+        uint8_t *r = p;
+        p += align256(n);
+        return r;
+    };
+    int32_t *act = (int32_t *)take(rows * 4);
+    uint32_t *n_act = (uint32_t *)take(256);
+    int32_t *atok = (int32_t *)take(rows * 4);
+    int32_t *rsrc = (int32_t *)take(rows * 4);
+    float *rw = (float *)take(rows * 4);
+    int32_t *bounds = (int32_t *)take(514 * 4);
+    void *xq = take(q8_bytes(rows, in_dim));
+    float *gu = (float *)take(rows * 2 * n_ff * 4);
+    float *h = (float *)take(rows * n_ff * 4);
+    void *hq = take(q8_bytes(rows, n_ff));
+    float *pd = (float *)take(rows * n_embd * 4);
+    if ((uint64_t)(p - g_win_ws) > g_win_ws_bytes) return false;
+    if (cudaMemsetAsync(atok, 0xff, rows * 4, st) != cudaSuccess) return false;  // -1: unplaced rows
+    win_assign_k<<<1, 512, 0, st>>>(d_es, d_ew, d_nh, n_tok, act, n_act, bounds, atok, rsrc, rw);
+    g_q4b_launches++;
+    if (!q4b_launch_ok("win_assign")) return false;
+    const uint32_t n_pairs = n_tok * 64u;
+    if (!q4_mmq_quantize(d_x, atok, xq, Q4_T_IQ3_S, in_dim, n_pairs)) return false;
+    const Q8View xv = q8_view(xq, n_pairs, in_dim);
+    if (!grouped::pow2_blocks(in_dim) &&
+        cudaMemsetAsync(gu, 0, (uint64_t)n_pairs * 2 * n_ff * 4, st) != cudaSuccess)
+        return false;
+    if (!grouped::pow2_blocks(n_ff) &&
+        cudaMemsetAsync(pd, 0, (uint64_t)n_pairs * n_embd * 4, st) != cudaSuccess)
+        return false;
+    if (ou == og + (uint64_t)n_ff * (in_dim / 256u) * Q4B_IQ3S_BYTES) {
+        if (!launch_grouped(base + og, stride, act, n_act, n_pairs, bounds, xv, in_dim, 2u * n_ff, gu,
+                            2ull * n_ff))
+            return false;
+    } else if (!launch_grouped(base + og, stride, act, n_act, n_pairs, bounds, xv, in_dim, n_ff, gu,
+                               2ull * n_ff) ||
+               !launch_grouped(base + ou, stride, act, n_act, n_pairs, bounds, xv, in_dim, n_ff,
+                               gu + n_ff, 2ull * n_ff)) {
+        return false;
+    }
+    if (!q4_mmq_swiglu(gu, h, n_pairs, n_ff)) return false;
+    if (!q4_mmq_quantize(h, nullptr, hq, Q4_T_IQ3_S, n_ff, n_pairs)) return false;
+    if (!launch_grouped(base + od, stride, act, n_act, n_pairs, bounds, q8_view(hq, n_pairs, n_ff), n_ff,
+                        n_embd, pd, n_embd))
+        return false;
+    return q4_hip_expert_reduce(d_y, pd, rsrc, rw, n_tok, 64u, n_embd);
+}

@@ -6,3 +6,4 @@
 #include "q4b_decode.cu"
 #include "q4b_synth.cu"
 #include "q4b_fused.cu"
+#include "q4b_grouped.cu"

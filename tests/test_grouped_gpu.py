@@ -1,0 +1,207 @@
+"""The many-token path (prefill chunks, verify windows, batches): routing,
+assignment, grouped IQ3_S x int8 product, combine -- against the CPU oracle and
+with the fixtures of the reference's own tests."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+IQ3_S = 21
+
+
+def _rel(a, b):
+    return float(np.linalg.norm(a.astype(np.float64) - b) / max(np.linalg.norm(b), 1e-30))
+
+
+def test_route_pf_matches_host_softmax_topk(dev, oracle):
+    rng = np.random.default_rng(1)
+    n_tok, n_exp, topk = 17, 512, 10
+    logits = rng.standard_normal((n_tok, n_exp)).astype(np.float32)
+    logits[3, 100] = logits[3, 7]                      # planted tie
+    d_ids, d_w = dev.malloc(n_tok * topk * 4), dev.malloc(n_tok * topk * 4)
+    assert dev.lib.q4_hip_route_pf(dev.upload(logits), d_ids, d_w, n_tok, n_exp, topk)
+    ids = dev.download(d_ids, (n_tok, topk), np.int32)
+    w = dev.download(d_w, (n_tok, topk), np.float32)
+    for t in range(n_tok):
+        i0, w0 = oracle.topk(oracle.softmax(logits[t]), topk, True)
+        assert ids[t].tolist() == i0.tolist()
+        assert (np.abs(w[t] - w0) <= 1e-6 * (1 + np.abs(w0))).all()   # src/q4_test.c:1927-2145
+    assert not dev.lib.q4_hip_route_pf(dev.upload(logits), d_ids, d_w, n_tok, n_exp, 65)
+    assert not dev.lib.q4_hip_route_pf(dev.upload(logits), d_ids, d_w, n_tok, n_exp, 0)
+
+
+def test_assign_pf_invariants(dev):
+    """17 tokens in groups of 8 (src/q4_test.c:1927-2145): every row placed once,
+    back-map consistent, rows of an expert contiguous and hole-free."""
+    rng = np.random.default_rng(2)
+    n_tok, n_exp, topk, gsz = 17, 64, 6, 8
+    ids = np.stack([rng.choice(n_exp, topk, replace=False) for _ in range(n_tok)]).astype(np.int32)
+    ids[5, 2] = -1                                      # poisoned picks are skipped
+    ids[9, 0] = n_exp + 3
+    wts = rng.random((n_tok, topk)).astype(np.float32)
+    n_g = (n_tok + gsz - 1) // gsz
+    d = {k: dev.malloc(4 * max(n_g * gsz * topk, n_g * 512)) for k in
+         ("atok", "rsrc", "rw", "stg", "stgn", "ek")}
+    assert dev.lib.q4_hip_assign_pf(dev.upload(ids), dev.upload(wts), d["atok"], d["rsrc"], d["rw"],
+                                    d["stg"], d["stgn"], d["ek"], gsz, topk, n_exp, n_tok)
+    atok = dev.download(d["atok"], (n_g, gsz * topk), np.int32)
+    rsrc = dev.download(d["rsrc"], (n_tok, topk), np.int32)
+    rw = dev.download(d["rw"], (n_tok, topk), np.float32)
+    stg = dev.download(d["stg"], (n_g, 512), np.int32)
+    stgn = dev.download(d["stgn"], (n_g,), np.uint32)
+    ek = dev.download(d["ek"], (n_g, 512), np.uint32)
+    for g in range(n_g):
+        t0, t1 = g * gsz, min(n_tok, (g + 1) * gsz)
+        valid = [(t, k) for t in range(t0, t1) for k in range(topk) if 0 <= ids[t, k] < n_exp]
+        counts = np.bincount([ids[t, k] for t, k in valid], minlength=n_exp)
+        assert np.array_equal(ek[g, :n_exp], counts)
+        used = np.nonzero(counts)[0]
+        assert stgn[g] == used.size and stg[g, :used.size].tolist() == used.tolist()
+        base = np.concatenate([[0], np.cumsum(counts)])
+        seen = set()
+        for t, k in valid:
+            p = rsrc[t, k]
+            e = ids[t, k]
+            assert base[e] <= p < base[e + 1]           # inside its expert's range
+            assert atok[g, p] == t and p not in seen    # back-map, no duplicate
+            seen.add(p)
+            assert rw[t, k] == wts[t, k]
+        assert seen == set(range(len(valid)))           # hole-free
+        # rows of one expert keep (token, pick) order
+        for e in used:
+            toks = atok[g, base[e]:base[e + 1]]
+            assert (np.diff(toks) >= 0).all()
+    assert rsrc[5, 2] == -1 and rw[5, 2] == 0 and rsrc[9, 0] == -1
+
+
+@pytest.mark.parametrize("wr,wc", [(1280, 2560), (2560, 512), (1024, 2048), (64, 256), (32, 1024)])
+def test_grouped_product_reference_fixture(dev, pkg, oracle, wr, wc):
+    """The reference's grouped-GEMM fixture (src/q4_test.c:206-307): 8 experts with
+    ragged bounds {100,0,1,40,60,30,50,19}, 300 rows gathered by ids[r]=(r*37+e*11)%320,
+    xorshift weight bytes with block scales from {0x2a66,0x2e66,0x30a3}, x in steps of
+    .025.  Checked against the fp64 dequantised dot (the reference's bound, rel-L2 <
+    1e-2) and, much tighter, against the CPU path's int8 dot on the same rows."""
+    n_exp, rows, nsrc = 8, 300, 320
+    per = [100, 0, 1, 40, 60, 30, 50, 19]
+    bounds = np.concatenate([[0], np.cumsum(per)]).astype(np.int32)
+    ids = np.zeros(rows, np.int32)
+    for r in range(rows):
+        e = int(np.searchsorted(bounds, r, side="right") - 1)
+        ids[r] = (r * 37 + e * 11) % nsrc
+    rb = wc // 256 * 110
+    eb = wr * rb
+    rng = np.random.default_rng(88172645463325252 % (2 ** 32) + wr)
+    w = rng.integers(0, 256, size=(n_exp, wr, wc // 256, 110), dtype=np.uint8)
+    ds = np.array([0x2a66, 0x2e66, 0x30a3], np.uint16)
+    e_i, r_i, b_i = np.meshgrid(np.arange(n_exp), np.arange(wr), np.arange(wc // 256), indexing="ij")
+    w[..., 0:2] = ds[(e_i + r_i + b_i) % 3].view(np.uint8).reshape(n_exp, wr, wc // 256, 2)
+    w = w.reshape(n_exp, eb)
+    x = ((rng.integers(0, 41, size=(nsrc, wc)) - 20) * 0.025).astype(np.float32)
+    lib = dev.lib
+    d_w = dev.upload(w)
+    d_xq = dev.malloc(lib.q4_mmq_q8_bytes(rows, wc))
+    d_dst = dev.malloc(rows * wr * 4)
+    assert lib.q4_mmq_supported(IQ3_S, wr)
+    assert lib.q4_mmq_quantize(dev.upload(x), dev.upload(ids), d_xq, IQ3_S, wc, rows)
+    assert lib.q4_mmq_mul_id(d_w, IQ3_S, wr, wc, eb, n_exp, d_xq, dev.upload(bounds), max(per), rows,
+                             d_dst, wr)
+    got = dev.download(d_dst, (rows, wr), np.float32)
+    num = den = 0.0
+    num8 = den8 = 0.0
+    check_rows = list(range(0, rows, 7)) + [100, 101, 299]
+    for r in check_rows:
+        e = int(np.searchsorted(bounds, r, side="right") - 1)
+        xr = x[ids[r]]
+        xq = oracle.quant8(xr)
+        for j in range(0, wr, max(1, wr // 16)):
+            row = w[e][j * rb:(j + 1) * rb]
+            acc = float(np.dot(oracle.dequant_row(row, wc).astype(np.float64), xr))
+            num += (acc - got[r, j]) ** 2
+            den += acc ** 2
+            a8 = oracle.dot8(row, xq, wc)
+            num8 += (a8 - got[r, j]) ** 2
+            den8 += a8 ** 2
+    assert np.sqrt(num / den) < 1e-2
+    assert np.sqrt(num8 / den8) < 1e-5
+    # rows of the empty expert's neighbours are untouched by it; unsupported shapes refuse
+    assert not lib.q4_mmq_mul_id(d_w, 20, wr, wc, eb, n_exp, d_xq, dev.upload(bounds), 100, rows, d_dst, wr)
+    assert not lib.q4_mmq_mul_id(d_w, IQ3_S, wr, wc, eb, n_exp, d_xq, dev.upload(bounds), 100, rows, d_dst, wr - 1)
+
+
+def test_verify_window_matches_single_token_path(dev, pkg, oracle):
+    """4 tokens with 3/5/7/9 picks over 16 slots (src/q4_test.c:2527-2619)."""
+    H, F, n_slots = 2048, 512, 16
+    rng = np.random.default_rng(5)
+    packs = pkg.synth.expert_packs(rng, n_slots, H, F)
+    layer = pkg.MoeLayer(dev, packs, None, np.zeros((n_slots, H), np.float32), None, H, F, 1, arena=1)
+    lib = dev.lib
+    try:
+        n_tok, counts = 4, [3, 5, 7, 9]
+        xs = rng.standard_normal((n_tok, H)).astype(np.float32)
+        es = np.full((n_tok, 64), -7, np.int32)
+        ew = np.zeros((n_tok, 64), np.float32)
+        for t, c in enumerate(counts):
+            es[t, :c] = rng.choice(n_slots, c, replace=False)
+            ew[t, :c] = rng.random(c).astype(np.float32)
+        d_y = dev.malloc(n_tok * H * 4)
+        assert lib.q4_hip_fill(d_y, 0.0, n_tok * H)
+        assert lib.q4_hip_moe_win_ok(IQ3_S, IQ3_S, IQ3_S, H, F, n_tok)
+        assert lib.q4_hip_moe_exec_win(layer.base, layer.stride, dev.upload(es), dev.upload(ew),
+                                       dev.upload(np.array(counts, np.int32)), n_tok, IQ3_S, layer.og,
+                                       IQ3_S, layer.ou, IQ3_S, layer.od, dev.upload(xs), None, d_y,
+                                       F, H, H)
+        y = dev.download(d_y, (n_tok, H), np.float32)
+        for t, c in enumerate(counts):
+            y1, _ = layer.exec_experts(xs[t], es[t, :c], ew[t, :c])
+            assert _rel(y[t], y1) < 1e-5                        # same integers, same row dots
+            y0 = oracle.expert_job([packs[i] for i in es[t, :c]], ew[t, :c], xs[t], H, F)
+            assert _rel(y[t], y0) <= 1e-3
+        assert not lib.q4_hip_moe_win_ok(IQ3_S, IQ3_S, IQ3_S, H, F, 9)
+        assert not lib.q4_hip_moe_win_ok(IQ3_S, 20, IQ3_S, H, F, 4)
+    finally:
+        layer.close()
+
+
+@pytest.mark.parametrize("n_tok,n_expert,topk,tiled", [(4, 64, 10, True), (4, 64, 10, False),
+                                                         (1, 32, 4, True), (33, 48, 6, True)])
+def test_layer_n_matches_oracle_per_token(dev, pkg, oracle, n_tok, n_expert, topk, tiled):
+    H, F = 2048, 512
+    L = pkg.synth.layer(40 + n_tok, n_expert, H, F)
+    xs = pkg.synth.hidden(41, n_tok, H)
+    lib = dev.lib
+    lib.q4_cuda_set_tiled_default(1 if tiled else 0)
+    try:
+        layer = pkg.MoeLayer(dev, L["experts"], L["shared"], L["router"], L["norm_w"], H, F, topk, arena=1)
+    finally:
+        lib.q4_cuda_set_tiled_default(1)
+    try:
+        ws = lib.q4_cuda_moe_layer_n_ws_bytes(n_tok, topk, n_expert, H, F)
+        d_ws = dev.malloc(ws)
+        d_y = dev.malloc(n_tok * H * 4)
+        d_ids, d_w = dev.malloc(n_tok * topk * 4), dev.malloc(n_tok * topk * 4)
+        assert lib.q4_cuda_moe_layer_n(layer.base, layer.stride, layer.og, layer.ou, layer.od,
+                                       layer.shared_slot, dev.upload(xs), layer.d_norm, 1e-6,
+                                       layer.d_router, n_expert, topk, H, F, n_tok, d_y, d_ids, d_w,
+                                       d_ws, ws)
+        y = dev.download(d_y, (n_tok, H), np.float32)
+        ids = dev.download(d_ids, (n_tok, topk), np.int32)
+        for t in range(n_tok):
+            y0, ids0, w0, _ = oracle.moe_layer(xs[t], L["norm_w"], 1e-6, L["router"], topk,
+                                               L["experts"], L["shared"], H, F)
+            assert ids[t].tolist() == ids0.tolist()
+            assert _rel(y[t], y0) <= 1e-3
+        # batch invariance: a token's row does not depend on who else is in the batch
+        if n_tok > 1:
+            d_y1 = dev.malloc(H * 4)
+            assert lib.q4_cuda_moe_layer_n(layer.base, layer.stride, layer.og, layer.ou, layer.od,
+                                           layer.shared_slot, dev.upload(xs[2:3]), layer.d_norm, 1e-6,
+                                           layer.d_router, n_expert, topk, H, F, 1, d_y1, None, None,
+                                           d_ws, ws)
+            y1 = dev.download(d_y1, (H,), np.float32)
+            assert np.array_equal(y1.view(np.uint32), y[2].view(np.uint32))
+        assert not lib.q4_cuda_moe_layer_n(layer.base, layer.stride, layer.og, layer.ou, layer.od,
+                                           layer.shared_slot, dev.upload(xs), layer.d_norm, 1e-6,
+                                           layer.d_router, n_expert, topk, H, F, n_tok, d_y, d_ids,
+                                           d_w, d_ws, ws - 1)
+    finally:
+        layer.close()
