@@ -236,6 +236,27 @@ bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64_t og, uint
                          uint32_t n_tok, float *d_y, int32_t *d_ids, float *d_wts, void *d_ws,
                          uint64_t ws_bytes);
 
+/* Routed experts for one token without any allocation on the call path.  It has no
+ * counterpart in the reference: it exists for hosts that cannot call cudaMalloc by the
+ * time experts run -- the engine's planner gives all free device memory to expert slots
+ * and KV pages at start-up, so a later allocation fails; a stream that is being captured
+ * may not allocate; a latency-bound loop cannot take an allocation's device-wide sync.
+ * Same arithmetic and accumulate semantics as q4_hip_moe_exec_dev (y += sum_e w_e *
+ * FFN_e(x), d_h receives the n hidden rows), with d_slots / d_wts device arrays of n
+ * entries and the work enqueued on the caller's `stream` (a cudaStream_t).  The
+ * quantised activations live in a fixed array inside the library image (about 40 KB per
+ * GPU, held until the process exits) instead of allocated buffers, hence the limits:
+ * n <= 16 experts, in_dim <= 4096, n_ff <= 2048 (larger sizes are refused with a message
+ * on stderr).  q4_hip_init() is not required.  The first call on each device looks up
+ * the array's device address and fills the codebook constant; make that first call
+ * before any stream capture begins.  All calls share the one array, which keeps the
+ * previous call's contents (nothing in it needs clearing: a call overwrites all it
+ * reads); calls that overlap on the GPU race, so serialise them. */
+bool q4_cuda_moe_exec_noalloc(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
+                              const float *d_wts, uint32_t n, uint64_t og, uint64_t ou,
+                              uint64_t od, const float *d_x, float *d_h, float *d_y,
+                              uint32_t n_ff, uint32_t in_dim, uint32_t n_embd, void *stream);
+
 /* Resident storage format of an arena.  By default q4_hip_experts_put*_a rewrites
  * each pack, in place and at the same size, into the library's tiled form of
  * IQ3_S (every run of eight 110-byte super-blocks regrouped by field so that all

@@ -7,3 +7,4 @@
 #include "q4b_synth.cu"
 #include "q4b_fused.cu"
 #include "q4b_grouped.cu"
+#include "q4b_noalloc.cu"
