@@ -224,6 +224,250 @@ def cpu_arm(pkg, layers, x_host, budget_s):
             "ms_per_step": 1e3 * t / jobs, "jobs": jobs}
 
 
+def exchange_id(rank, world, make_id):
+    """Rank 0 makes the 128-byte communicator id; the others fetch it over a local socket."""
+    import socket
+    port = (int(os.environ.get("MASTER_PORT", "29500")) + 1000) % 65536 or 30500
+    addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    if rank == 0:
+        ident = make_id()
+        srv = socket.socket()
+        srv.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        srv.bind((addr, port))
+        srv.listen(world)
+        for _ in range(world - 1):
+            c, _ = srv.accept()
+            c.sendall(ident)
+            c.close()
+        srv.close()
+        return ident
+    deadline = time.time() + 120
+    while True:
+        try:
+            c = socket.create_connection((addr, port), timeout=5)
+            break
+        except OSError:
+            if time.time() > deadline:
+                raise
+            time.sleep(0.2)
+    buf = b""
+    while len(buf) < 128:
+        chunk = c.recv(128 - len(buf))
+        if not chunk:
+            raise RuntimeError("id exchange broke")
+        buf += chunk
+    c.close()
+    return buf
+
+
+EP_TOKENS = 64          # config 4: batch of 64 tokens ...
+EP_LAYERS = 48          # ... through 48 MoE layers
+
+
+class EpJob:
+    """64 tokens x n_layers MoE layers on `world` ranks; this object is one rank's part.
+    world == 1 is the same job on one GPU through q4_cuda_moe_layer_n."""
+
+    def __init__(self, pkg, dev, ep, arena, rank, world, n_layers):
+        import ctypes
+        self.lib = lib = dev.lib
+        self.ep, self.world, self.n_layers, self.arena = ep, world, n_layers, arena
+        self.t_local = EP_TOKENS // world
+        e_local = self.e_local = N_EXPERT // world
+        self.slots_l = e_local + 1
+        bpp = PACK // IQ3S_BLOCK            # super-blocks per expert pack
+        if not lib.q4_hip_experts_alloc_a(arena, n_layers * self.slots_l, PACK):
+            raise MemoryError("expert arena")
+        self.base, self.stride = lib.q4_hip_experts_base_a(arena), lib.q4_hip_experts_stride_a(arena)
+        # expert (layer, e) has the same bytes at every world size: each rank generates
+        # its range of the full seeded tensor, then the layer's shared expert
+        for l in range(n_layers):
+            lb = self.base + l * self.slots_l * self.stride
+            first = (l * (N_EXPERT + 1) + rank * e_local) * bpp
+            assert lib.q4_cuda_synth_iq3s_at(lb, e_local * bpp, 2026, first)
+            assert lib.q4_cuda_synth_iq3s_at(lb + e_local * self.stride, bpp, 2026,
+                                             (l * (N_EXPERT + 1) + N_EXPERT) * bpp)
+        if lib.q4_cuda_experts_tiled_a(arena):
+            assert lib.q4_cuda_experts_retile_a(arena, 0, n_layers * self.slots_l)
+        self.d_router = dev.malloc(n_layers * ROUTER_BYTES)
+        assert lib.q4_cuda_synth_normal(self.d_router, n_layers * N_EXPERT * N_EMBD, 2027, 0.0, 0.02)
+        self.d_norm = dev.malloc(n_layers * N_EMBD * 4)
+        assert lib.q4_cuda_synth_normal(self.d_norm, n_layers * N_EMBD, 2028, 1.0, 0.1)
+        x_all = pkg.synth.hidden(2029, EP_TOKENS, N_EMBD)
+        self.x_host = np.ascontiguousarray(x_all[rank * self.t_local:(rank + 1) * self.t_local])
+        self.nb = nb = self.t_local * N_EMBD * 4
+        self.d_x0, self.d_a, self.d_b = dev.upload(self.x_host), dev.malloc(nb), dev.malloc(nb)
+        self.h_x, self.h_y = lib.q4_hip_host_alloc_coh(nb), lib.q4_hip_host_alloc_coh(nb)
+        ctypes.memmove(self.h_x, self.x_host.ctypes.data, nb)
+        rb = N_EMBD // 256 * IQ3S_BLOCK
+        self.og, self.ou, self.od = 0, N_FF * rb, 2 * N_FF * rb
+        if world == 1:
+            self.ws = lib.q4_cuda_moe_layer_n_ws_bytes(self.t_local, TOPK, N_EXPERT, N_EMBD, N_FF)
+        else:
+            self.ws = ep.q4_cuda_ep_layer_ws_bytes(world, self.t_local, TOPK, N_EXPERT, N_EMBD, N_FF)
+        self.d_ws = dev.malloc(self.ws)
+        self.dev = dev
+        self.graph = None
+
+    def layer(self, l, src, dst):
+        lb = self.base + l * self.slots_l * self.stride
+        nw, rt = self.d_norm + l * N_EMBD * 4, self.d_router + l * ROUTER_BYTES
+        if self.world == 1:
+            ok = self.lib.q4_cuda_moe_layer_n(lb, self.stride, self.og, self.ou, self.od, N_EXPERT, src, nw,
+                                              EPS, rt, N_EXPERT, TOPK, N_EMBD, N_FF, self.t_local, dst,
+                                              None, None, self.d_ws, self.ws)
+        else:
+            ok = self.ep.q4_cuda_ep_layer(lb, self.stride, self.og, self.ou, self.od, 1, src, nw, EPS, rt,
+                                          N_EXPERT, TOPK, N_EMBD, N_FF, self.t_local, dst, self.d_ws, self.ws)
+        if not ok:
+            raise RuntimeError("layer call refused")
+
+    def enqueue(self):
+        src = self.d_x0
+        for l in range(self.n_layers):      # the output of a layer is the next layer's input
+            dst = self.d_a if (l % 2 == 0) else self.d_b
+            self.layer(l, src, dst)
+            src = dst
+        self.d_out = src
+
+    def try_capture(self):
+        """One CUDA graph per step (48 layers); falls back to plain launches if the capture
+        is refused (e.g. by the collective library)."""
+        if os.environ.get("Q4B_BENCH_GRAPH", "1") == "0":
+            return False
+        if self.lib.q4_hip_graph_begin() != 1:
+            return False
+        try:
+            self.enqueue()
+        except RuntimeError:
+            self.lib.q4_hip_graph_end()
+            return False
+        g = self.lib.q4_hip_graph_end()
+        if not g:
+            return False
+        self.graph = g
+        return True
+
+    def step(self):
+        if self.graph:
+            if not self.lib.q4_hip_graph_launch(self.graph):
+                raise RuntimeError("graph launch failed")
+        else:
+            self.enqueue()
+
+    def step_e2e(self):
+        lib = self.lib
+        lib.q4_hip_h2d_async(self.d_x0, self.h_x, self.nb)
+        self.step()
+        lib.q4_hip_d2h_async(self.h_y, self.d_out, self.nb)
+        lib.q4_hip_stream_sync()
+
+    def release(self):
+        self.lib.q4_hip_experts_free_a(self.arena)
+        for p in (self.d_router, self.d_norm, self.d_x0, self.d_a, self.d_b, self.d_ws):
+            self.lib.q4_hip_free(p)
+
+
+def time_job(job, steps, warmup, barrier_max):
+    """(ms resident, ms end to end, launches per step) for `steps` steps, max over ranks."""
+    lib = job.lib
+    l0 = lib.q4_cuda_launch_count()
+    job.enqueue()
+    job.dev.sync()
+    launches = lib.q4_cuda_launch_count() - l0
+    job.try_capture()
+    for _ in range(warmup):
+        job.step()
+    job.dev.sync()
+    barrier_max(0.0)
+    lib.q4_cuda_timer_begin()
+    for _ in range(steps):
+        job.step()
+    lib.q4_cuda_timer_end()
+    ms = barrier_max(lib.q4_cuda_timer_ms())
+    job.dev.sync()
+    for _ in range(2):
+        job.step_e2e()
+    barrier_max(0.0)
+    lib.q4_cuda_timer_begin()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        job.step_e2e()
+    lib.q4_cuda_timer_end()
+    ms_e2e = barrier_max(max(lib.q4_cuda_timer_ms(), 1e3 * (time.perf_counter() - t0)))
+    return ms, ms_e2e, launches
+
+
+def run_ep(a, pkg, rank, world, local, warmup):
+    """Config 4: expert-parallel decode, 64 tokens x 48 layers, experts sharded evenly,
+    router and shared expert replicated, dispatch/combine over NCCL.  Strong scaling: the
+    job (64 x 48 layer-tokens per step) is the same at every N.  Rank 0 afterwards runs the
+    same job alone on its GPU so the line carries its own 1-GPU reference."""
+    import ctypes
+    dev = pkg.Device()
+    lib = dev.lib
+    ep = None
+    if world > 1:
+        ep = pkg.capi.load_ep()
+
+        def make_id():
+            buf = ctypes.create_string_buffer(128)
+            assert ep.q4_cuda_ep_unique_id(buf)
+            return buf.raw
+        ident = exchange_id(rank, world, make_id)
+        assert ep.q4_cuda_ep_init(ident, rank, world), "NCCL communicator"
+
+    def barrier_max(v):
+        if world == 1:
+            return v
+        f = ctypes.c_float(v)
+        assert ep.q4_cuda_ep_allreduce_max(ctypes.byref(f))
+        return f.value
+
+    n_layers = a.layers if a.layers else EP_LAYERS
+    job = EpJob(pkg, dev, ep, 0, rank, world, n_layers)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms, ms_e2e, launches = time_job(job, a.steps, warmup, barrier_max)
+    clocks = sampler.stop() if rank == 0 else None
+    graphed = bool(job.graph)
+    err = lib.q4_cuda_device_error()
+    if err:
+        raise SystemExit("device error word %#x" % err)
+    single = None
+    if world > 1 and rank == 0 and not a.no_cpu:
+        job.release()
+        solo = EpJob(pkg, dev, None, 0, 0, 1, n_layers)
+        s_ms, s_e2e, _ = time_job(solo, a.steps, warmup, lambda v: v)
+        single = {"value": EP_TOKENS * n_layers * a.steps / (s_ms * 1e-3),
+                  "e2e": EP_TOKENS * n_layers * a.steps / (s_e2e * 1e-3), "unit": UNIT,
+                  "ms_per_step": s_ms / a.steps}
+    barrier_max(0.0)
+    if rank == 0:
+        units = EP_TOKENS * n_layers
+        peak, peak_src = read_peaks()
+        # weight bytes a step must read on the busiest rank: all routers + the experts picked
+        print(json.dumps({
+            "metric": METRIC, "value": units * a.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": a.steps, "warmup": warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8 x IQ3_S, fp32 accumulate",
+            "data": "synthetic",
+            "config": {"workload": "config4: expert-parallel decode, 64 tokens x %d MoE layers per step, 512 "
+                                   "experts top-10 + shared, experts sharded %d-way, NCCL dispatch/combine"
+                                   % (n_layers, world),
+                       "l2": "inputs larger than L2: a step reads %d layers of weights" % n_layers,
+                       "tokens_per_rank": job.t_local, "experts_per_rank": job.e_local,
+                       "cuda_graph": graphed, "one_gpu_same_job": single},
+            "clocks": clocks,
+            "e2e": {"value": units * a.steps / (ms_e2e * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": job.nb, "d2h_bytes_per_step": job.nb},
+            "gpu_launches": int(launches * a.steps * 2),
+            "roofline": None, "cpu_baseline": None}))
+    if ep:
+        ep.q4_cuda_ep_shutdown()
+
+
 def dist_setup(n_gpus):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -240,9 +484,13 @@ def main():
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--workload", default="auto", choices=["auto", "ep"],
+                    help="ep: run the 64-token x 48-layer expert-parallel job even on one GPU")
     a = ap.parse_args()
     rank, world, local = dist_setup(a.gpus)
     warmup = max(a.warmup, 3)
+    if world > 1:       # one process per GPU: each sees only its own device
+        os.environ["CUDA_VISIBLE_DEVICES"] = str(local)
 
     entry.build()
     pkg = entry.load_package()
@@ -289,8 +537,11 @@ def main():
         print(json.dumps(line))
         return
 
-    if world > 1:
-        raise SystemExit("multi-GPU expert-parallel arm is not built yet")
+    if world > 1 or a.workload == "ep":
+        if a.steps == 2000 and a.warmup == 200:     # the single-layer defaults are too long here
+            a.steps, warmup = 20, 3
+        run_ep(a, pkg, rank, world, local, warmup)
+        return
 
     wl = Workload(pkg, a.layers)
     lib = wl.lib

@@ -295,6 +295,9 @@ uint32_t q4_cuda_fused_profile_read(unsigned long long *out, uint32_t max_ctas);
  * fp16 d = |N(0,1)| * 2^-6 and uniform random payload bytes; n fp32 values
  * N(mean, std).  Content depends only on (seed, index). */
 bool q4_cuda_synth_iq3s(uint8_t *d_out, uint64_t n_blocks, uint64_t seed);
+/* The same, for blocks [first_block, first_block + n_blocks) of the seeded tensor:
+ * a rank that holds a shard generates exactly the bytes the full tensor has there. */
+bool q4_cuda_synth_iq3s_at(uint8_t *d_out, uint64_t n_blocks, uint64_t seed, uint64_t first_block);
 bool q4_cuda_synth_normal(float *d_out, uint64_t n, uint64_t seed, float mean, float std);
 
 /* Device-side timing on the compute stream, for benchmarks: records an event

@@ -19,7 +19,7 @@ def sources():
     out = []
     for root, _, files in os.walk(CSRC):
         for f in files:
-            if f.endswith((".cu", ".cuh", ".h")):
+            if f.endswith((".cu", ".cuh", ".h")) and f != "q4b_ep.cu":
                 out.append(os.path.join(root, f))
     out.append(os.path.join(os.path.dirname(HERE), "include", "q4cuda.h"))
     return out
@@ -41,5 +41,26 @@ def build(force=False, verbose=False):
     return LIB
 
 
+EP_LIB = os.path.join(HERE, "libq4cuda_ep.so")
+
+
+def build_ep(force=False):
+    """The expert-parallel library (needs NCCL headers and libnccl)."""
+    build(force)
+    src = os.path.join(CSRC, "q4b_ep.cu")
+    deps = [src, LIB, os.path.join(os.path.dirname(HERE), "include", "q4cuda_ep.h")]
+    if not force and os.path.exists(EP_LIB) and all(os.path.getmtime(d) <= os.path.getmtime(EP_LIB) for d in deps):
+        return EP_LIB
+    cmd = ["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+           "--compiler-options", "-fPIC", "-shared", "-o", EP_LIB, src, "-L" + HERE, "-lq4cuda", "-lnccl",
+           "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.stderr.write(" ".join(cmd) + "\n" + r.stdout + r.stderr)
+        raise RuntimeError("nvcc failed (expert-parallel library)")
+    return EP_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build_ep(force="--force" in sys.argv))

@@ -106,6 +106,7 @@ SIGNATURES = {
     "q4_cuda_fused_profile_enable": (b, [C.c_int]),
     "q4_cuda_fused_profile_read": (u32, [vp, u32]),
     "q4_cuda_synth_iq3s": (b, [vp, u64, u64]),
+    "q4_cuda_synth_iq3s_at": (b, [vp, u64, u64, u64]),
     "q4_cuda_synth_normal": (b, [vp, u64, u64, f32, f32]),
     "q4_cuda_timer_begin": (b, []),
     "q4_cuda_timer_end": (b, []),
@@ -132,4 +133,36 @@ def load():
         fn.restype = res
         fn.argtypes = args
     _lib = lib
+    return lib
+
+
+EP_LIB_PATH = os.path.join(_HERE, "libq4cuda_ep.so")
+EP_SIGNATURES = {
+    "q4_cuda_ep_unique_id": (b, [vp]),
+    "q4_cuda_ep_init": (b, [vp, C.c_int, C.c_int]),
+    "q4_cuda_ep_shutdown": (None, []),
+    "q4_cuda_ep_rank": (C.c_int, []),
+    "q4_cuda_ep_world": (C.c_int, []),
+    "q4_cuda_ep_allreduce_max": (b, [vp]),
+    "q4_cuda_ep_layer_ws_bytes": (u64, [u32, u32, u32, u32, u32, u32]),
+    "q4_cuda_ep_layer": (b, [vp, u64, u64, u64, u64, C.c_int, vp, vp, f32, vp, u32, u32, u32, u32, u32,
+                             vp, vp, u64]),
+}
+_ep = None
+
+
+def load_ep():
+    """The expert-parallel library (links NCCL); load() must have succeeded first."""
+    global _ep
+    if _ep is not None:
+        return _ep
+    load()
+    if not os.path.exists(EP_LIB_PATH):
+        raise RuntimeError("libq4cuda_ep.so is not built (run `python suzuku-engine-q4_b200/build.py`)")
+    lib = C.CDLL(EP_LIB_PATH)
+    for name, (res, args) in EP_SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    _ep = lib
     return lib

@@ -1,0 +1,259 @@
+// Expert parallelism over NCCL: libq4cuda_ep.so, one process per GPU.
+//
+// The reference is single-device (src/q4_rocm.cu:545-550), so this has no counterpart
+// there; it shards the same path the way the path shards naturally: experts are
+// independent packs (src/q4_expert.c:962-982) and the per-token combine is a plain
+// weighted sum (src/q4_rocm.cu:15739-15751).
+//
+// Rank r of G holds experts [r*E/G, (r+1)*E/G) in slots 0..E/G-1 of its arena and a
+// copy of the shared expert in slot E/G; the router and norm weights are replicated;
+// each rank owns T_local tokens.  One layer on every rank:
+//   1. RMSNorm, router GEMV, softmax/top-k for its own tokens
+//   2. dispatch: normalised rows + picks of all ranks are gathered everywhere.  With
+//      top-10 of 512 over <= 8 ranks a token visits 1-(1-1/G)^10 = 74..100 % of the
+//      ranks, so the all-to-all degenerates to an all-gather; sending fp32 rows keeps
+//      the quantisation (Q8-A, per row) on the receiving side bit-identical to 1 GPU
+//   3. every rank runs its own experts on the rows that picked them (grouped product,
+//      each tile decoded once), plus the shared expert for the tokens it owns, and
+//      reduces per token: partial[t] = sum of its picks here, in pick order
+//   4. combine: all-to-all of the partial rows to the tokens' owners, summed there in
+//      rank order (reproducible)
+// Everything runs on the library's stream; the only synchronising calls are the NCCL
+// communicator set-up and the explicit barrier helper.
+#include <cuda_runtime.h>
+#include <nccl.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/q4cuda.h"
+#include "../../include/q4cuda_ep.h"
+
+namespace {
+
+ncclComm_t g_comm = nullptr;
+int g_rank = 0, g_world = 1;
+float *g_scalar = nullptr;  // one float for barrier / max
+
+#define EP_NCCL(call)                                                                   \
+    do {                                                                                \
+        ncclResult_t r_ = (call);                                                       \
+        if (r_ != ncclSuccess) {                                                        \
+            fprintf(stderr, "q4cuda_ep: %s failed: %s\n", #call, ncclGetErrorString(r_)); \
+            return false;                                                               \
+        }                                                                               \
+    } while (0)
+
+inline uint64_t al(uint64_t v) { return (v + 255u) & ~(uint64_t)255u; }
+
+// Picks of all T tokens as seen by this rank: expert id -> local slot, others -1; the
+// shared expert (local slot e_local) as one more pick for the tokens this rank owns.
+__global__ void ep_local_picks_k(const int32_t *__restrict__ ids, const float *__restrict__ wts,
+                                 int32_t *__restrict__ lids, float *__restrict__ lw, uint32_t n_tok,
+                                 uint32_t topk, uint32_t e_first, uint32_t e_local, uint32_t t_first,
+                                 uint32_t t_local, int has_shared) {
+    const uint32_t k1 = topk + 1u;
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_tok * k1) return;
+    const uint32_t t = i / k1, k = i - t * k1;
+    int32_t id = -1;
+    float w = 0.f;
+    if (k < topk) {
+        const int32_t e = ids[t * topk + k];
+        if (e >= (int32_t)e_first && e < (int32_t)(e_first + e_local)) {
+            id = e - (int32_t)e_first;
+            w = wts[t * topk + k];
+        }
+    } else if (has_shared && t >= t_first && t < t_first + t_local) {
+        id = (int32_t)e_local;
+        w = 1.0f;
+    }
+    lids[i] = id;
+    lw[i] = w;
+}
+
+// bounds[e] = rows before expert e, from the per-expert row counts (one warp).
+__global__ void ep_bounds_k(const uint32_t *__restrict__ ek, int32_t *__restrict__ bounds,
+                            uint32_t n_exp) {
+    if (threadIdx.x == 0) {
+        int32_t b = 0;
+        for (uint32_t e = 0; e < n_exp; e++) {
+            bounds[e] = b;
+            b += (int32_t)ek[e];
+        }
+        bounds[n_exp] = b;
+    }
+}
+
+// y[t] = sum over ranks s = 0..G-1 of recv[s][t], in that order.
+__global__ void ep_sum_k(const float *__restrict__ recv, float *__restrict__ y, uint32_t n,
+                         uint32_t world) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float acc = 0.f;
+    for (uint32_t s = 0; s < world; s++) acc += recv[(uint64_t)s * n + i];
+    y[i] = acc;
+}
+
+struct EpWs {
+    float *xn_l, *logits, *wts_l, *xn, *wts, *lw, *rw, *gu, *h, *pd, *partial, *recv;
+    int32_t *ids_l, *ids, *lids, *atok, *rsrc, *stg, *bounds;
+    uint32_t *stgn, *ek;
+    void *xq, *hq;
+    uint64_t bytes;
+};
+
+EpWs carve(uint8_t *p, uint32_t world, uint32_t t_local, uint32_t topk, uint32_t n_expert,
+           uint32_t n_embd, uint32_t n_ff) {
+    EpWs w;
+    uint64_t off = 0;
+    const uint64_t T = (uint64_t)world * t_local, k1 = topk + 1u, rows = T * k1;
+    auto take = [&](uint64_t n) {
+        uint8_t *r = p ? p + off : nullptr;
+        off += al(n);
+        return r;
+    };
+    w.xn_l = (float *)take((uint64_t)t_local * n_embd * 4);
+    w.logits = (float *)take((uint64_t)t_local * n_expert * 4);
+    w.ids_l = (int32_t *)take((uint64_t)t_local * topk * 4);
+    w.wts_l = (float *)take((uint64_t)t_local * topk * 4);
+    w.xn = (float *)take(T * n_embd * 4);
+    w.ids = (int32_t *)take(T * topk * 4);
+    w.wts = (float *)take(T * topk * 4);
+    w.lids = (int32_t *)take(rows * 4);
+    w.lw = (float *)take(rows * 4);
+    w.atok = (int32_t *)take(rows * 4);
+    w.rsrc = (int32_t *)take(rows * 4);
+    w.rw = (float *)take(rows * 4);
+    w.stg = (int32_t *)take(512 * 4);
+    w.stgn = (uint32_t *)take(256);
+    w.ek = (uint32_t *)take(512 * 4);
+    w.bounds = (int32_t *)take(514 * 4);
+    w.xq = take(q4_mmq_q8_bytes(rows, n_embd));
+    w.gu = (float *)take(rows * 2 * n_ff * 4);
+    w.h = (float *)take(rows * n_ff * 4);
+    w.hq = take(q4_mmq_q8_bytes(rows, n_ff));
+    w.pd = (float *)take(rows * n_embd * 4);
+    w.partial = (float *)take(T * n_embd * 4);
+    w.recv = (float *)take(T * n_embd * 4);
+    w.bytes = off;
+    return w;
+}
+
+}  // namespace
+
+// ---- communicator ----
+extern "C" bool q4_cuda_ep_unique_id(uint8_t *out128) {
+    if (!out128) return false;
+    ncclUniqueId id;
+    EP_NCCL(ncclGetUniqueId(&id));
+    static_assert(sizeof(ncclUniqueId) == 128, "id size");
+    memcpy(out128, &id, 128);
+    return true;
+}
+
+// The device must already be current and q4_hip_init() done on it.
+extern "C" bool q4_cuda_ep_init(const uint8_t *id128, int rank, int world) {
+    if (!id128 || world < 1 || rank < 0 || rank >= world || g_comm || !q4_hip_ok()) return false;
+    ncclUniqueId id;
+    memcpy(&id, id128, 128);
+    EP_NCCL(ncclCommInitRank(&g_comm, world, id, rank));
+    g_rank = rank;
+    g_world = world;
+    g_scalar = (float *)q4_hip_malloc(256);
+    return g_scalar != nullptr;
+}
+
+extern "C" void q4_cuda_ep_shutdown(void) {
+    if (!g_comm) return;
+    q4_hip_sync();
+    ncclCommDestroy(g_comm);
+    g_comm = nullptr;
+    q4_hip_free(g_scalar);
+    g_scalar = nullptr;
+    g_world = 1;
+    g_rank = 0;
+}
+
+extern "C" int q4_cuda_ep_rank(void) { return g_rank; }
+extern "C" int q4_cuda_ep_world(void) { return g_world; }
+
+// max over ranks of one host float (also a barrier): synchronises.
+extern "C" bool q4_cuda_ep_allreduce_max(float *h_value) {
+    if (!g_comm || !h_value) return false;
+    cudaStream_t st = (cudaStream_t)q4_hip_stream();
+    if (!q4_hip_h2d(g_scalar, h_value, 4)) return false;
+    EP_NCCL(ncclAllReduce(g_scalar, g_scalar, 1, ncclFloat, ncclMax, g_comm, st));
+    return q4_hip_d2h(h_value, g_scalar, 4);
+}
+
+extern "C" uint64_t q4_cuda_ep_layer_ws_bytes(uint32_t world, uint32_t t_local, uint32_t topk,
+                                              uint32_t n_expert, uint32_t n_embd, uint32_t n_ff) {
+    return carve(nullptr, world, t_local, topk, n_expert, n_embd, n_ff).bytes;
+}
+
+// One MoE layer for this rank's t_local tokens (steps 1-4 of the header comment).
+// base/stride/og/ou/od address THIS rank's arena (local slot j = expert rank*E/G + j,
+// shared expert in slot E/G when has_shared); d_router is the full [n_expert][n_embd]
+// matrix; d_x / d_y hold t_local rows.  Every rank must call it with the same shapes.
+extern "C" bool q4_cuda_ep_layer(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou,
+                                 uint64_t od, int has_shared, const float *d_x,
+                                 const float *d_norm_w, float eps, const float *d_router,
+                                 uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
+                                 uint32_t t_local, float *d_y, void *d_ws, uint64_t ws_bytes) {
+    if (!g_comm || !base || !d_x || !d_router || !d_y || !d_ws || t_local == 0) return false;
+    const uint32_t G = (uint32_t)g_world;
+    if (n_expert % G) return false;
+    const uint32_t e_local = n_expert / G, n_e = e_local + 1u;
+    if (n_e > 512u || topk == 0 || topk >= 64u) return false;
+    const EpWs w = carve((uint8_t *)d_ws, G, t_local, topk, n_expert, n_embd, n_ff);
+    if (ws_bytes < w.bytes) return false;
+    cudaStream_t st = (cudaStream_t)q4_hip_stream();
+    const uint32_t T = G * t_local, k1 = topk + 1u;
+    const uint64_t rows = (uint64_t)T * k1;
+    const uint64_t gate_bytes = (uint64_t)n_ff * (n_embd / 256u) * 110u;
+    if (ou != og + gate_bytes) return false;
+    // 1. own tokens: norm, router, top-k
+    if (!q4_hip_grouped_rms_n(d_x, d_norm_w, w.xn_l, n_embd, 1, eps, t_local)) return false;
+    if (!q4_hip_gemv_dd_n(Q4_T_F32, (const uint8_t *)d_router, n_expert, n_embd, w.xn_l, w.logits,
+                          1.0f, t_local))
+        return false;
+    if (!q4_hip_route_pf(w.logits, w.ids_l, w.wts_l, t_local, n_expert, topk)) return false;
+    // 2. dispatch
+    EP_NCCL(ncclGroupStart());
+    EP_NCCL(ncclAllGather(w.xn_l, w.xn, (size_t)t_local * n_embd, ncclFloat, g_comm, st));
+    EP_NCCL(ncclAllGather(w.ids_l, w.ids, (size_t)t_local * topk, ncclInt32, g_comm, st));
+    EP_NCCL(ncclAllGather(w.wts_l, w.wts, (size_t)t_local * topk, ncclFloat, g_comm, st));
+    EP_NCCL(ncclGroupEnd());
+    // 3. local experts on the rows that picked them
+    ep_local_picks_k<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
+        w.ids, w.wts, w.lids, w.lw, T, topk, (uint32_t)g_rank * e_local, e_local,
+        (uint32_t)g_rank * t_local, t_local, has_shared);
+    if (cudaGetLastError() != cudaSuccess) return false;
+    if (cudaMemsetAsync(w.atok, 0xff, rows * 4, st) != cudaSuccess) return false;  // -1 = unused row
+    if (!q4_hip_assign_pf(w.lids, w.lw, w.atok, w.rsrc, w.rw, w.stg, w.stgn, w.ek, T, k1, n_e, T))
+        return false;
+    ep_bounds_k<<<1, 32, 0, st>>>(w.ek, w.bounds, n_e);
+    if (cudaGetLastError() != cudaSuccess) return false;
+    if (!q4_mmq_quantize(w.xn, w.atok, w.xq, Q4_T_IQ3_S, n_embd, rows)) return false;
+    if (!q4_mmq_mul_id(base + og, Q4_T_IQ3_S, 2ull * n_ff, n_embd, stride, n_e, w.xq, w.bounds,
+                       (uint32_t)rows, rows, w.gu, 2ull * n_ff))
+        return false;
+    if (!q4_mmq_swiglu(w.gu, w.h, rows, n_ff)) return false;
+    if (!q4_mmq_quantize(w.h, nullptr, w.hq, Q4_T_IQ3_S, n_ff, rows)) return false;
+    if (!q4_mmq_mul_id(base + od, Q4_T_IQ3_S, n_embd, n_ff, stride, n_e, w.hq, w.bounds,
+                       (uint32_t)rows, rows, w.pd, n_embd))
+        return false;
+    if (cudaMemsetAsync(w.partial, 0, (uint64_t)T * n_embd * 4, st) != cudaSuccess) return false;
+    if (!q4_hip_expert_reduce(w.partial, w.pd, w.rsrc, w.rw, T, k1, n_embd)) return false;
+    // 4. combine
+    const size_t blk = (size_t)t_local * n_embd;
+    EP_NCCL(ncclGroupStart());
+    for (uint32_t p = 0; p < G; p++) {
+        EP_NCCL(ncclSend(w.partial + p * blk, blk, ncclFloat, (int)p, g_comm, st));
+        EP_NCCL(ncclRecv(w.recv + p * blk, blk, ncclFloat, (int)p, g_comm, st));
+    }
+    EP_NCCL(ncclGroupEnd());
+    ep_sum_k<<<(unsigned)((blk + 255) / 256), 256, 0, st>>>(w.recv, d_y, (uint32_t)blk, G);
+    return cudaGetLastError() == cudaSuccess;
+}

@@ -15,7 +15,7 @@
 //            over the experts in list order, y written
 //
 // Weight bytes cross HBM -> shared memory exactly once, by 1-D bulk async copies
-// (cp.async.bulk, no multicast) that complete on mbarriers; nothing is re-read.
+// (plain cp.async.bulk into this CTA only) that complete on mbarriers; nothing is re-read.
 // Replaces the reference's per-layer launch chain (src/q4_moe.c:2077-2133;
 // kernels wmoe_iq3_gu_q8 / wmoe_iq3_ya_q8, src/q4_rocm.cu:3912-4120).  Needs the
 // tiled arena format (q4b_tile.cuh), n_embd == 2048, n_ff == 512,

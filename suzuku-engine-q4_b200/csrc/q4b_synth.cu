@@ -29,10 +29,11 @@ __device__ __forceinline__ float synth_normal(uint64_t seed, uint64_t i) {
     return sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
 }
 
-__global__ void synth_iq3s_k(uint8_t *out, uint64_t n_blocks, uint64_t seed) {
-    const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= n_blocks) return;
-    uint8_t *p = out + b * Q4B_IQ3S_BYTES;
+__global__ void synth_iq3s_k(uint8_t *out, uint64_t n_blocks, uint64_t seed, uint64_t first) {
+    const uint64_t bl = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (bl >= n_blocks) return;
+    uint8_t *p = out + bl * Q4B_IQ3S_BYTES;
+    const uint64_t b = first + bl;  // index in the whole tensor: a shard equals the same range of the full run
     const __half d = __float2half_rn(fabsf(synth_normal(seed, b)) * 0.015625f);
     const unsigned short db = __half_as_ushort(d);
     p[0] = (uint8_t)(db & 0xff);
@@ -55,11 +56,17 @@ __global__ void synth_normal_k(float *out, uint64_t n, uint64_t seed, float mean
 
 }  // namespace
 
-extern "C" bool q4_cuda_synth_iq3s(uint8_t *d_out, uint64_t n_blocks, uint64_t seed) {
+extern "C" bool q4_cuda_synth_iq3s_at(uint8_t *d_out, uint64_t n_blocks, uint64_t seed,
+                                      uint64_t first_block) {
     if (!g_q4b.ok || !d_out || n_blocks == 0) return false;
-    synth_iq3s_k<<<(unsigned)((n_blocks + 255) / 256), 256, 0, g_q4b.stream>>>(d_out, n_blocks, seed);
+    synth_iq3s_k<<<(unsigned)((n_blocks + 255) / 256), 256, 0, g_q4b.stream>>>(d_out, n_blocks, seed,
+                                                                                 first_block);
     g_q4b_launches++;
     return q4b_launch_ok("synth_iq3s");
+}
+
+extern "C" bool q4_cuda_synth_iq3s(uint8_t *d_out, uint64_t n_blocks, uint64_t seed) {
+    return q4_cuda_synth_iq3s_at(d_out, n_blocks, seed, 0);
 }
 
 extern "C" bool q4_cuda_synth_normal(float *d_out, uint64_t n, uint64_t seed, float mean,

@@ -144,3 +144,33 @@ class MoeLayer:
         ids = dev.download(self.d_ids, (self.topk,), np.int32)
         wts = dev.download(self.d_wts, (self.topk,), np.float32)
         return y, ids, wts
+
+
+# ---- expert parallelism: the host-side statement of the partition (libq4cuda_ep.so
+# implements the same rules on the device, csrc/q4b_ep.cu) ----
+def ep_expert_range(rank, world, n_expert):
+    """Experts [first, first + count) live on `rank`."""
+    assert n_expert % world == 0
+    count = n_expert // world
+    return rank * count, count
+
+
+def ep_local_picks(ids, wts, rank, world, n_expert, t_local, has_shared=True):
+    """Picks of all tokens as seen by one rank.
+
+    ids/wts: [T, topk] for all T = world * t_local tokens (token t is owned by rank
+    t // t_local).  Returns (lids, lw) of shape [T, topk + 1]: the local slot of each
+    pick that lives on this rank (else -1, weight 0), and in the last column the shared
+    expert (local slot count, weight 1) for the tokens this rank owns."""
+    first, count = ep_expert_range(rank, world, n_expert)
+    T, topk = ids.shape
+    lids = np.full((T, topk + 1), -1, np.int32)
+    lw = np.zeros((T, topk + 1), np.float32)
+    mine = (ids >= first) & (ids < first + count)
+    lids[:, :topk][mine] = (ids - first)[mine]
+    lw[:, :topk][mine] = wts[mine]
+    if has_shared:
+        own = np.arange(T) // t_local == rank
+        lids[own, topk] = count
+        lw[own, topk] = 1.0
+    return lids, lw

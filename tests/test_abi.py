@@ -21,14 +21,23 @@ def test_every_declared_symbol_is_exported(pkg):
     assert not missing, missing
 
 
+def test_ep_library_exports_its_header(pkg):
+    text = open(os.path.join(ROOT, "include", "q4cuda_ep.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    names = sorted(set(re.findall(r"\b(q4_cuda_ep_\w+)\s*\(", text)))
+    assert sorted(pkg.capi.EP_SIGNATURES) == names
+    lib = pkg.capi.load_ep()
+    assert all(hasattr(lib, n) for n in names)
+    assert lib.q4_cuda_ep_world() == 1
+
+
 def test_binding_table_matches_header(pkg):
     assert sorted(pkg.capi.SIGNATURES) == _declared()
 
 
 def test_no_cpu_fallback(pkg):
-    import torch
-    if torch.cuda.is_available():
-        return  # covered by the gpu tests
+    if os.path.exists("/dev/nvidia0"):
+        return  # a GPU box: covered by the gpu tests
     lib = pkg.capi.load()
     assert lib.q4_hip_init() is False
     assert lib.q4_hip_ok() is False
