@@ -290,6 +290,16 @@ bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, uint64_t og, 
 bool q4_cuda_fused_profile_enable(int on);
 uint32_t q4_cuda_fused_profile_read(unsigned long long *out, uint32_t max_ctas);
 
+/* Which grouped product q4_mmq_mul_id and q4_cuda_moe_layer_n run (no reference
+ * counterpart; the reference picks its tile kernel by row count inside q4_mmq_mul_id,
+ * src/q4_mmq.cu:387-470): -1 = by size (tensor-core kernel when the call averages 8
+ * or more rows per expert and the weight rows are a multiple of 128; otherwise the
+ * streaming CUDA-core kernel on tiled arenas, else the general CUDA-core kernel),
+ * 0 = CUDA-core kernels only, 1 = the tensor-core kernel whenever the shape allows,
+ * 2 = the general CUDA-core kernel only.  Returns false for an unknown mode, or for 1
+ * when the tensor-core path could not be set up. */
+bool q4_cuda_mmq_tc_mode(int mode);
+
 /* Seeded synthetic tensors generated on the device (benchmark and smoke
  * support, no reference counterpart): n_blocks IQ3_S super-blocks with
  * fp16 d = |N(0,1)| * 2^-6 and uniform random payload bytes; n fp32 values

@@ -105,6 +105,7 @@ SIGNATURES = {
                                     u32, vp]),
     "q4_cuda_fused_profile_enable": (b, [C.c_int]),
     "q4_cuda_fused_profile_read": (u32, [vp, u32]),
+    "q4_cuda_mmq_tc_mode": (b, [C.c_int]),
     "q4_cuda_synth_iq3s": (b, [vp, u64, u64]),
     "q4_cuda_synth_iq3s_at": (b, [vp, u64, u64, u64]),
     "q4_cuda_synth_normal": (b, [vp, u64, u64, f32, f32]),

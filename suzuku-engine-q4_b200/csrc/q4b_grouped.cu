@@ -106,75 +106,79 @@ template <bool TILED>
 __global__ void __launch_bounds__(256) grouped_rows_k(
     const uint8_t *__restrict__ w, uint64_t expert_stride, const int32_t *__restrict__ act,
     const uint32_t *__restrict__ n_act, const int32_t *__restrict__ bounds, Q8View xq,
-    uint32_t cols, uint32_t w_rows, float *__restrict__ dst, uint64_t ld_dst) {
+    uint32_t cols, uint32_t w_rows, float *__restrict__ dst, uint64_t ld_dst,
+    const uint32_t *__restrict__ codes) {
     __shared__ uint32_t tab[512];
     const uint32_t entry = blockIdx.y;
     if (n_act && entry >= *n_act) return;
     const int32_t r0 = bounds[entry], r1 = bounds[entry + 1];
     if (r1 <= r0) return;
-    q4b_fill_code_table(tab);
+    tab[threadIdx.x] = __ldg(codes + threadIdx.x);
+    tab[threadIdx.x + 256u] = __ldg(codes + threadIdx.x + 256u);
     __syncthreads();
     const uint32_t B = cols >> 8;                        // super-blocks per weight row
     const uint32_t n_tiles = (w_rows * B) >> 3;
-    const uint32_t ti = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (ti >= n_tiles) return;
-    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t lane = threadIdx.x & 31u, p = lane & 3u;
     const uint8_t *mat = w + (uint64_t)(act ? act[entry] : (int32_t)entry) * expert_stride;
-    const uint32_t bi = ti * 8u + (lane >> 2);           // this lane's super-block in the matrix
-    const uint32_t wrow = bi / B, brow = bi - wrow * B;  // weight row, block within the row
-    const uint32_t p = lane & 3u;
-    // decode once: the lane's two groups
-    uint32_t cw[16];
-    uint32_t ls0, ls1;
-    float dblk;
-    {
-        const Iq3Fields f0 = iq3_fields<TILED>(mat, bi, 2u * p);
-        const Iq3Fields f1 = iq3_fields<TILED>(mat, bi, 2u * p + 1u);
-        decode_group<TILED>(f0, tab, cw);
-        decode_group<TILED>(f1, tab, cw + 8);
-        ls0 = f0.ls;
-        ls1 = f1.ls;
-        dblk = f0.d;
-    }
-    const uint32_t gcol = brow * 8u + 2u * p;             // first of the lane's two 32-groups
     const uint32_t ngr = cols >> 5;
     const bool pow2 = B == 1 || B == 2 || B == 4 || B == 8;
     const uint32_t lanes_per_row = 4u * B;
-    for (int32_t r = r0; r < r1; r++) {
-        const int4 *qp = reinterpret_cast<const int4 *>(xq.q + (uint64_t)r * cols + gcol * 32u);
-        const int4 q0 = __ldg(qp), q1 = __ldg(qp + 1), q2 = __ldg(qp + 2), q3 = __ldg(qp + 3);
-        const uint64_t go = (uint64_t)r * ngr + gcol;
-        const float dx0 = __ldg(xq.d + go), dx1 = __ldg(xq.d + go + 1);
-        const int b0 = __ldg(xq.bs + go), b1 = __ldg(xq.bs + go + 1);
-        int a0 = 0, a1 = 0;
-        a0 = __dp4a((int)cw[0], q0.x, a0);
-        a0 = __dp4a((int)cw[1], q0.y, a0);
-        a0 = __dp4a((int)cw[2], q0.z, a0);
-        a0 = __dp4a((int)cw[3], q0.w, a0);
-        a0 = __dp4a((int)cw[4], q1.x, a0);
-        a0 = __dp4a((int)cw[5], q1.y, a0);
-        a0 = __dp4a((int)cw[6], q1.z, a0);
-        a0 = __dp4a((int)cw[7], q1.w, a0);
-        a1 = __dp4a((int)cw[8], q2.x, a1);
-        a1 = __dp4a((int)cw[9], q2.y, a1);
-        a1 = __dp4a((int)cw[10], q2.z, a1);
-        a1 = __dp4a((int)cw[11], q2.w, a1);
-        a1 = __dp4a((int)cw[12], q3.x, a1);
-        a1 = __dp4a((int)cw[13], q3.y, a1);
-        a1 = __dp4a((int)cw[14], q3.z, a1);
-        a1 = __dp4a((int)cw[15], q3.w, a1);
-        const int I0 = 2 * a0 + b0, I1 = 2 * a1 + b1;    // sum sign*(2c+1)*q = 2 sum c'q + sum q
-        float v = dblk * ((float)(I0 * (int)ls0) * dx0 + (float)(I1 * (int)ls1) * dx1);
-        v += __shfl_xor_sync(0xffffffffu, v, 1);
-        v += __shfl_xor_sync(0xffffffffu, v, 2);
-        float *o = dst + (uint64_t)r * ld_dst + wrow;
-        if (pow2) {  // a weight row is 4*B neighbouring lanes of this warp
-            if (B >= 2) v += __shfl_xor_sync(0xffffffffu, v, 4);
-            if (B >= 4) v += __shfl_xor_sync(0xffffffffu, v, 8);
-            if (B >= 8) v += __shfl_xor_sync(0xffffffffu, v, 16);
-            if ((lane & (lanes_per_row - 1u)) == 0) *o = v;
-        } else if (p == 0) {
-            atomicAdd(o, v);  // other widths: a row is spread over warps, one add per block
+    const uint32_t t_step = gridDim.x * (blockDim.x >> 5);
+    uint32_t ti = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (ti >= n_tiles) return;
+    // the tile after this one is fetched while this one is decoded and used
+    Iq3Fields f0 = iq3_fields<TILED>(mat, ti * 8u + (lane >> 2), 2u * p);
+    Iq3Fields f1 = iq3_fields<TILED>(mat, ti * 8u + (lane >> 2), 2u * p + 1u);
+    for (; ti < n_tiles; ti += t_step) {
+        const uint32_t bi = ti * 8u + (lane >> 2);           // this lane's super-block in the matrix
+        const uint32_t wrow = bi / B, brow = bi - wrow * B;  // weight row, block within the row
+        uint32_t cw[16];
+        decode_group<TILED>(f0, tab, cw);
+        decode_group<TILED>(f1, tab, cw + 8);
+        const int ls0 = (int)f0.ls, ls1 = (int)f1.ls;
+        const float dblk = f0.d;
+        if (ti + t_step < n_tiles) {
+            const uint32_t bn = (ti + t_step) * 8u + (lane >> 2);
+            f0 = iq3_fields<TILED>(mat, bn, 2u * p);
+            f1 = iq3_fields<TILED>(mat, bn, 2u * p + 1u);
+        }
+        const uint32_t gcol = brow * 8u + 2u * p;         // first of the lane's two 32-groups
+        for (int32_t r = r0; r < r1; r++) {
+            const int4 *qp = reinterpret_cast<const int4 *>(xq.q + (uint64_t)r * cols + gcol * 32u);
+            const int4 q0 = __ldg(qp), q1 = __ldg(qp + 1), q2 = __ldg(qp + 2), q3 = __ldg(qp + 3);
+            const uint64_t go = (uint64_t)r * ngr + gcol;
+            const float2 dx = __ldg(reinterpret_cast<const float2 *>(xq.d + go));
+            const int2 bsv = __ldg(reinterpret_cast<const int2 *>(xq.bs + go));
+            int a0 = 0, a1 = 0;
+            a0 = __dp4a((int)cw[0], q0.x, a0);
+            a0 = __dp4a((int)cw[1], q0.y, a0);
+            a0 = __dp4a((int)cw[2], q0.z, a0);
+            a0 = __dp4a((int)cw[3], q0.w, a0);
+            a0 = __dp4a((int)cw[4], q1.x, a0);
+            a0 = __dp4a((int)cw[5], q1.y, a0);
+            a0 = __dp4a((int)cw[6], q1.z, a0);
+            a0 = __dp4a((int)cw[7], q1.w, a0);
+            a1 = __dp4a((int)cw[8], q2.x, a1);
+            a1 = __dp4a((int)cw[9], q2.y, a1);
+            a1 = __dp4a((int)cw[10], q2.z, a1);
+            a1 = __dp4a((int)cw[11], q2.w, a1);
+            a1 = __dp4a((int)cw[12], q3.x, a1);
+            a1 = __dp4a((int)cw[13], q3.y, a1);
+            a1 = __dp4a((int)cw[14], q3.z, a1);
+            a1 = __dp4a((int)cw[15], q3.w, a1);
+            const int I0 = 2 * a0 + bsv.x, I1 = 2 * a1 + bsv.y;  // sum sign*(2c+1)*q = 2 sum c'q + sum q
+            float v = dblk * ((float)(I0 * ls0) * dx.x + (float)(I1 * ls1) * dx.y);
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            float *o = dst + (uint64_t)r * ld_dst + wrow;
+            if (pow2) {  // a weight row is 4*B neighbouring lanes of this warp
+                if (B >= 2) v += __shfl_xor_sync(0xffffffffu, v, 4);
+                if (B >= 4) v += __shfl_xor_sync(0xffffffffu, v, 8);
+                if (B >= 8) v += __shfl_xor_sync(0xffffffffu, v, 16);
+                if ((lane & (lanes_per_row - 1u)) == 0) *o = v;
+            } else if (p == 0) {
+                atomicAdd(o, v);  // other widths: a row is spread over warps, one add per block
+            }
         }
     }
 }
@@ -202,72 +206,108 @@ __global__ void expert_reduce_k(float *__restrict__ y, const float *__restrict__
     y[(uint64_t)t * n_embd + c] += acc;
 }
 
-// One block (256 threads) per group of gsz tokens: count picks per expert, prefix,
-// place rows, list the used experts.  Rows of one expert keep (token, pick) order: the
-// picks are walked 256 at a time, one warp after the other, each lane finding its place
-// among the lanes of its warp that picked the same expert.
+// One block (256 threads) per group of gsz tokens: a stable counting sort of the group's
+// picks by expert.  Each warp owns a contiguous run of picks; per-warp histograms, a
+// prefix over warps and over experts, then every warp places its own run 32 picks at a
+// time, each lane finding its place among the lanes of the warp that picked the same
+// expert.  Rows of one expert therefore keep (token, pick) order.
 __global__ void __launch_bounds__(256) assign_k(
     const int32_t *__restrict__ ids, const float *__restrict__ wts, int32_t *__restrict__ a_tok,
     int32_t *__restrict__ rsrc, float *__restrict__ rw, int32_t *__restrict__ stg,
     uint32_t *__restrict__ stgn, uint32_t *__restrict__ ek, int32_t *__restrict__ cbounds,
     uint32_t gsz, uint32_t topk, uint32_t n_exp, uint32_t n_tok, uint32_t ek_stride) {
-    extern __shared__ uint32_t sh[];  // cnt[n_exp] then cur[n_exp]
-    uint32_t *cnt = sh, *cur = sh + n_exp;
+    extern __shared__ uint32_t sh[];  // hist[8][n_exp], cnt[n_exp], rank[n_exp], wsum[16]
+    uint32_t *hist = sh, *cnt = sh + 8u * n_exp, *rank = cnt + n_exp, *wsum = rank + n_exp;
     const uint32_t g = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t t0 = g * gsz, t1 = min(t0 + gsz, n_tok);
     const uint32_t seg = g * gsz * topk, rows = (t1 - t0) * topk;
-    for (uint32_t i = tid; i < n_exp; i += blockDim.x) cnt[i] = 0;
+    const uint32_t run = ((rows + 7u) / 8u + 31u) & ~31u;  // picks per warp, a multiple of 32
+    const uint32_t i_lo = warp * run, i_hi = min(rows, i_lo + run);
+    const int32_t *gid = ids + (uint64_t)t0 * topk;
+    for (uint32_t i = tid; i < 8u * n_exp; i += blockDim.x) hist[i] = 0;
     __syncthreads();
-    for (uint32_t i = tid; i < rows; i += blockDim.x) {
-        const int32_t e = ids[(uint64_t)t0 * topk + i];
-        if (e >= 0 && (uint32_t)e < n_exp) atomicAdd(&cnt[e], 1u);
+    for (uint32_t i = i_lo + lane; i < i_hi; i += 32u) {
+        const int32_t e = gid[i];
+        if (e >= 0 && (uint32_t)e < n_exp) atomicAdd(&hist[warp * n_exp + e], 1u);
     }
     __syncthreads();
-    if (tid == 0) {
-        uint32_t b = 0, nu = 0;
-        for (uint32_t e = 0; e < n_exp; e++) {
-            cur[e] = b;
-            if (cnt[e]) {
+    // per expert: exclusive prefix over the warps, total in cnt
+    for (uint32_t e = tid; e < n_exp; e += blockDim.x) {
+        uint32_t tot = 0;
+        for (uint32_t wv = 0; wv < 8u; wv++) {
+            const uint32_t c = hist[wv * n_exp + e];
+            hist[wv * n_exp + e] = tot;
+            tot += c;
+        }
+        cnt[e] = tot;
+        if (ek) ek[g * ek_stride + e] = tot;
+    }
+    __syncthreads();
+    // exclusive prefix over experts of (count, used): thread t owns experts [t*per, t*per+per)
+    const uint32_t per = (n_exp + blockDim.x - 1u) / blockDim.x;
+    uint32_t my_c = 0, my_u = 0;
+    for (uint32_t k = 0; k < per; k++) {
+        const uint32_t e = tid * per + k;
+        if (e < n_exp) {
+            my_c += cnt[e];
+            my_u += cnt[e] ? 1u : 0u;
+        }
+    }
+    uint32_t pack = (my_c << 10) | my_u;  // rows < 2^22, used experts <= 1023
+    uint32_t inc = pack;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= (uint32_t)o) inc += v;
+    }
+    if (lane == 31u) wsum[warp] = inc;
+    __syncthreads();
+    uint32_t off = 0;
+    for (uint32_t wv = 0; wv < warp; wv++) off += wsum[wv];
+    uint32_t excl = off + inc - pack;
+    uint32_t b = excl >> 10, nu = excl & 1023u;
+    for (uint32_t k = 0; k < per; k++) {
+        const uint32_t e = tid * per + k;
+        if (e < n_exp) {
+            const uint32_t c = cnt[e];
+            rank[e] = b;  // first row of expert e
+            if (c) {
                 if (stg) stg[g * ek_stride + nu] = (int32_t)e;
                 if (cbounds) cbounds[g * (ek_stride + 1) + nu] = (int32_t)b;
-                b += cnt[e];
                 nu++;
             }
+            b += c;
         }
+    }
+    if (tid == blockDim.x - 1u) {  // totals
         if (cbounds) cbounds[g * (ek_stride + 1) + nu] = (int32_t)b;
         if (stgn) stgn[g] = nu;
     }
     __syncthreads();
-    if (ek)
-        for (uint32_t i = tid; i < n_exp; i += blockDim.x) ek[g * ek_stride + i] = cnt[i];
-    for (uint32_t i0 = 0; i0 < rows; i0 += blockDim.x) {
-        const uint32_t i = i0 + tid;
+    for (uint32_t i0 = i_lo; i0 < i_hi; i0 += 32u) {
+        const uint32_t i = i0 + lane;
         int32_t e = -1;
         uint32_t t = 0, k = 0;
-        if (i < rows) {
+        if (i < i_hi) {
             t = t0 + i / topk;
             k = i % topk;
-            e = ids[(uint64_t)t * topk + k];
+            e = gid[i];
             if (e < 0 || (uint32_t)e >= n_exp) e = -1;
         }
-        for (uint32_t wv = 0; wv < 8; wv++) {
-            if (warp == wv) {
-                const uint32_t same = __match_any_sync(0xffffffffu, e);
-                if (e >= 0) {
-                    const uint32_t before = __popc(same & ((1u << lane) - 1u));
-                    const uint32_t pos = cur[e] + before;
-                    a_tok[seg + pos] = (int32_t)t;
-                    rsrc[(uint64_t)t * topk + k] = (int32_t)pos;
-                    rw[(uint64_t)t * topk + k] = wts[(uint64_t)t * topk + k];
-                    __syncwarp(same);
-                    if (before == 0) cur[e] += __popc(same);
-                } else if (i < rows) {
-                    rsrc[(uint64_t)t * topk + k] = -1;
-                    rw[(uint64_t)t * topk + k] = 0.f;
-                }
-            }
-            __syncthreads();
+        const uint32_t same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0) {
+            const uint32_t before = __popc(same & ((1u << lane) - 1u));
+            const uint32_t pos = rank[e] + hist[warp * n_exp + e] + before;
+            a_tok[seg + pos] = (int32_t)t;
+            rsrc[(uint64_t)t * topk + k] = (int32_t)pos;
+            rw[(uint64_t)t * topk + k] = wts[(uint64_t)t * topk + k];
+        } else if (i < i_hi) {
+            rsrc[(uint64_t)t * topk + k] = -1;
+            rw[(uint64_t)t * topk + k] = 0.f;
         }
+        __syncwarp();
+        if (e >= 0 && (same & ((1u << lane) - 1u)) == 0) hist[warp * n_exp + e] += __popc(same);
+        __syncwarp();
     }
 }
 
@@ -350,15 +390,72 @@ bool launch_grouped(const uint8_t *w, uint64_t expert_stride, const int32_t *act
                     uint32_t cols, uint32_t w_rows, float *dst, uint64_t ld_dst) {
     const uint32_t B = cols >> 8;
     const uint32_t n_tiles = (w_rows * B) >> 3;
-    const dim3 grid((n_tiles + 7) / 8, n_entries);
+    // eight tiles per warp (64 per CTA) where the matrix has that many: the code table and
+    // the CTA start-up are paid once per 56 KB of weights
+    const uint32_t ctas = (n_tiles + 7u) / 8u;
+    const dim3 grid(ctas > 8u ? (ctas + 7u) / 8u : 1u, n_entries);
     if (q4b_ptr_tiled(w))
         grouped_rows_k<true><<<grid, 256, 0, g_q4b.stream>>>(w, expert_stride, act, n_act, bounds, xq,
-                                                            cols, w_rows, dst, ld_dst);
+                                                            cols, w_rows, dst, ld_dst, g_q4b.codes_d);
     else
         grouped_rows_k<false><<<grid, 256, 0, g_q4b.stream>>>(w, expert_stride, act, n_act, bounds, xq,
-                                                             cols, w_rows, dst, ld_dst);
+                                                             cols, w_rows, dst, ld_dst, g_q4b.codes_d);
     g_q4b_launches++;
     return q4b_launch_ok("grouped_rows");
+}
+
+// Which grouped product runs.  The tensor-core kernel pays off once an expert has
+// enough rows to fill a useful part of a 128 x 64 MMA tile; below that the streaming
+// CUDA-core kernel (one decode, a handful of dot products from registers) is the
+// better fit, and the general CUDA-core kernel takes what neither accepts (arenas in
+// the engine's byte order, odd widths).  In the default mode a call is split by
+// entry: entries with TC_MIN_ROWS rows or more go to the tensor cores, the rest to
+// the streaming kernel; each kernel skips the other's entries.
+int g_tc_mode = -1;  // -1 split by rows, 0 CUDA cores only, 1 tensor cores whenever the shape
+                     // allows, 2 the general CUDA-core kernel only
+constexpr uint32_t TC_MIN_ROWS = 12;
+bool launch_grouped_any(const uint8_t *w, uint64_t expert_stride, const int32_t *act,
+                        const uint32_t *n_act, uint32_t n_entries, const int32_t *bounds, Q8View xq,
+                        uint64_t total_rows, uint32_t cols, uint32_t w_rows, float *dst,
+                        uint64_t ld_dst) {
+    const bool tiled = q4b_ptr_tiled(w);
+    const bool tc_ok = g_tc_mode != 0 && g_tc_mode != 2 && mmqtc::g_ready && mmqtc::shape_ok(w_rows, cols);
+    const bool few_ok = g_tc_mode != 2 && g_tc_mode != 1 && tiled && few::shape_ok(w_rows, cols, n_entries);
+    // rows an entry needs before the tensor cores take it
+    uint32_t tc_min = 0xffffffffu;
+    if (tc_ok) tc_min = g_tc_mode == 1 ? 1u : (few_ok ? TC_MIN_ROWS : 0xffffffffu);
+    if (tc_ok && g_tc_mode == -1 && !few_ok && total_rows >= 8ull * n_entries) tc_min = 1u;
+    const bool run_tc = tc_min != 0xffffffffu && total_rows >= tc_min;
+    if (run_tc) {
+        const bool ok = mmqtc::launch(w, expert_stride, act, n_act, n_entries, bounds, xq.q, xq.d,
+                                      total_rows, cols, w_rows, dst, ld_dst, tiled, tc_min);
+        g_q4b_launches++;
+        if (!ok || !q4b_launch_ok("mmq_tc")) return false;
+        if (tc_min <= 1u) return true;
+    }
+    if (few_ok) {
+        few::Args a;
+        a.w = w;
+        a.expert_stride = expert_stride;
+        a.act = act;
+        a.n_act = n_act;
+        a.n_entries = n_entries;
+        a.bounds = bounds;
+        a.xq = xq.q;
+        a.xd = xq.d;
+        a.xbs = xq.bs;
+        a.cols = cols;
+        a.w_rows = w_rows;
+        a.dst = dst;
+        a.ld_dst = ld_dst;
+        a.codes = g_q4b.codes_d;
+        a.err = g_q4b.err_d;
+        a.max_rows = run_tc ? tc_min - 1u : 0x7fffffffu;
+        const bool ok = few::launch(a);
+        g_q4b_launches++;
+        return ok && q4b_launch_ok("grouped_few");
+    }
+    return launch_grouped(w, expert_stride, act, n_act, n_entries, bounds, xq, cols, w_rows, dst, ld_dst);
 }
 
 bool pow2_blocks(uint64_t w_cols) {
@@ -376,6 +473,15 @@ bool shape_ok(uint32_t type, uint64_t w_rows, uint64_t w_cols) {
 
 using namespace grouped;
 
+bool q4b_mmq_tc_warm() {
+    const bool f = few::warm();
+    return mmqtc::warm() && f;
+}
+extern "C" bool q4_cuda_mmq_tc_mode(int mode) {
+    if (mode < -1 || mode > 2 || (mode == 1 && !mmqtc::g_ready)) return false;
+    grouped::g_tc_mode = mode;
+    return true;
+}
 extern "C" int q4_mmq_on(void) { return g_q4b.ok ? 1 : 0; }
 extern "C" uint32_t q4_mmq_group(void) { return 4096u; }
 extern "C" bool q4_mmq_supported(uint32_t type, uint64_t w_rows) {
@@ -409,9 +515,9 @@ extern "C" bool q4_mmq_mul_id(const void *w, uint32_t type, uint64_t w_rows, uin
     if (!grouped::pow2_blocks(w_cols) &&
         cudaMemsetAsync(dst, 0, total_rows * ld_dst * sizeof(float), g_q4b.stream) != cudaSuccess)
         return false;
-    return launch_grouped((const uint8_t *)w, expert_stride_bytes, nullptr, nullptr, n_expert, bounds,
-                          q8_view(xq, total_rows, w_cols), (uint32_t)w_cols, (uint32_t)w_rows, dst,
-                          ld_dst);
+    return launch_grouped_any((const uint8_t *)w, expert_stride_bytes, nullptr, nullptr, n_expert, bounds,
+                              q8_view(xq, total_rows, w_cols), total_rows, (uint32_t)w_cols,
+                              (uint32_t)w_rows, dst, ld_dst);
 }
 
 extern "C" bool q4_mmq_swiglu(const float *gu, float *h, uint64_t rows, uint64_t n_ff) {
@@ -445,7 +551,7 @@ static bool launch_assign(const int32_t *d_ids, const float *d_wts, int32_t *d_a
                           int32_t *d_cbounds, uint32_t gsz, uint32_t topk, uint32_t n_exp,
                           uint32_t n_tok, uint32_t ek_stride) {
     const uint32_t n_g = (n_tok + gsz - 1u) / gsz;
-    assign_k<<<n_g, 256, 2 * n_exp * sizeof(uint32_t), g_q4b.stream>>>(
+    assign_k<<<n_g, 256, (10 * n_exp + 16) * sizeof(uint32_t), g_q4b.stream>>>(
         d_ids, d_wts, d_atok, d_rsrc, d_rw, d_stg, d_stgn, d_ek, d_cbounds, gsz, topk, n_exp, n_tok,
         ek_stride);
     g_q4b_launches++;
@@ -552,15 +658,15 @@ extern "C" bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64
     if (!grouped::pow2_blocks(n_embd) &&
         cudaMemsetAsync(w.gu, 0, rows * 2 * n_ff * 4, st) != cudaSuccess)
         return false;
-    if (!launch_grouped(base + og, stride, w.stg, w.stgn, n_entries, w.cbounds,
-                        q8_view(w.xq, rows, n_embd), n_embd, 2u * n_ff, w.gu, 2ull * n_ff))
+    if (!launch_grouped_any(base + og, stride, w.stg, w.stgn, n_entries, w.cbounds,
+                            q8_view(w.xq, rows, n_embd), rows, n_embd, 2u * n_ff, w.gu, 2ull * n_ff))
         return false;
     if (!q4_mmq_swiglu(w.gu, w.h, rows, n_ff)) return false;
     if (!q4_mmq_quantize(w.h, nullptr, w.hq, Q4_T_IQ3_S, n_ff, rows)) return false;
     if (!grouped::pow2_blocks(n_ff) && cudaMemsetAsync(w.pd, 0, rows * n_embd * 4, st) != cudaSuccess)
         return false;
-    if (!launch_grouped(base + od, stride, w.stg, w.stgn, n_entries, w.cbounds,
-                        q8_view(w.hq, rows, n_ff), n_ff, n_embd, w.pd, n_embd))
+    if (!launch_grouped_any(base + od, stride, w.stg, w.stgn, n_entries, w.cbounds,
+                            q8_view(w.hq, rows, n_ff), rows, n_ff, n_embd, w.pd, n_embd))
         return false;
     if (cudaMemsetAsync(d_y, 0, (uint64_t)n_tok * n_embd * 4, st) != cudaSuccess) return false;
     if (!q4_hip_expert_reduce(d_y, w.pd, w.rsrc, w.rw, n_tok, k1, n_embd)) return false;

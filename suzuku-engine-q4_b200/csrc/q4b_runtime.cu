@@ -14,6 +14,7 @@
 Q4bState g_q4b = {};
 bool q4b_fused_warm();   // q4b_fused.cu: scratch of the persistent decode kernel
 bool q4b_window_warm();  // q4b_grouped.cu: scratch of the verify-window path
+bool q4b_mmq_tc_warm();  // q4b_grouped.cu: tensor-core grouped product (optional)
 std::atomic<uint64_t> g_q4b_launches{0};
 
 namespace {
@@ -115,6 +116,7 @@ bool alloc_scratch() {
     Q4B_CHECK(cudaMalloc(&s.r_wts, (size_t)Q4B_MAX_TOK * 64 * sizeof(float)));
     Q4B_CHECK(cudaMalloc(&s.r_cnt, (size_t)Q4B_MAX_TOK * sizeof(int32_t)));
     Q4B_CHECK(cudaMalloc(&s.hbuf, nq * sizeof(float)));
+    q4b_mmq_tc_warm();  // without it the grouped product stays on the CUDA cores
     return q4b_fused_warm() && q4b_window_warm();
 }
 

@@ -74,13 +74,25 @@ def test_assign_pf_invariants(dev):
     assert rsrc[5, 2] == -1 and rw[5, 2] == 0 and rsrc[9, 0] == -1
 
 
-@pytest.mark.parametrize("wr,wc", [(1280, 2560), (2560, 512), (1024, 2048), (64, 256), (32, 1024)])
-def test_grouped_product_reference_fixture(dev, pkg, oracle, wr, wc):
+@pytest.mark.parametrize("wr,wc,tc", [(1280, 2560, 0), (2560, 512, 0), (1024, 2048, 0), (64, 256, 0),
+                                        (32, 1024, 0), (1280, 2560, 1), (2560, 512, 1), (1024, 2048, 1),
+                                        (128, 256, 1)])
+def test_grouped_product_reference_fixture(dev, pkg, oracle, wr, wc, tc):
     """The reference's grouped-GEMM fixture (src/q4_test.c:206-307): 8 experts with
     ragged bounds {100,0,1,40,60,30,50,19}, 300 rows gathered by ids[r]=(r*37+e*11)%320,
     xorshift weight bytes with block scales from {0x2a66,0x2e66,0x30a3}, x in steps of
     .025.  Checked against the fp64 dequantised dot (the reference's bound, rel-L2 <
-    1e-2) and, much tighter, against the CPU path's int8 dot on the same rows."""
+    1e-2) and, much tighter, against the CPU path's int8 dot on the same rows.  tc = 0
+    runs the CUDA-core kernel, tc = 1 the tensor-core kernel (100 rows = two passes of 64,
+    1 row = the smallest MMA tile)."""
+    assert dev.lib.q4_cuda_mmq_tc_mode(tc)
+    try:
+        _grouped_fixture(dev, pkg, oracle, wr, wc)
+    finally:
+        assert dev.lib.q4_cuda_mmq_tc_mode(-1)
+
+
+def _grouped_fixture(dev, pkg, oracle, wr, wc):
     n_exp, rows, nsrc = 8, 300, 320
     per = [100, 0, 1, 40, 60, 30, 50, 19]
     bounds = np.concatenate([[0], np.cumsum(per)]).astype(np.int32)
@@ -128,6 +140,45 @@ def test_grouped_product_reference_fixture(dev, pkg, oracle, wr, wc):
     assert not lib.q4_mmq_mul_id(d_w, IQ3_S, wr, wc, eb, n_exp, d_xq, dev.upload(bounds), 100, rows, d_dst, wr - 1)
 
 
+def test_tensor_core_integer_parts_exact(dev):
+    """With unit scales the float result IS the integer sum: block scale d = 1, activations
+    integer-valued with a 127 in every group (so q = x and the group scale is 1), K = 256 so
+    every partial sum stays below 2^24.  The tensor-core product must then equal
+    sum_g (1 + 2 s_g) * sum_k w_k x_k computed in integers, exactly."""
+    rng = np.random.default_rng(11)
+    wr, wc, n_exp = 256, 256, 3
+    per = [70, 5, 17]
+    rows = sum(per)
+    bounds = np.concatenate([[0], np.cumsum(per)]).astype(np.int32)
+    w = rng.integers(0, 256, size=(n_exp, wr, 110), dtype=np.uint8)
+    w[..., 0:2] = np.array([0x3c00], np.uint16).view(np.uint8)          # d = 1.0
+    x = rng.integers(-127, 128, size=(rows, wc)).astype(np.float32)
+    x[:, ::32] = 127.0
+    lib = dev.lib
+    d_xq = dev.malloc(lib.q4_mmq_q8_bytes(rows, wc))
+    d_dst = dev.malloc(rows * wr * 4)
+    assert lib.q4_mmq_quantize(dev.upload(x), None, d_xq, IQ3_S, wc, rows)
+    assert lib.q4_cuda_mmq_tc_mode(1)
+    try:
+        assert lib.q4_mmq_mul_id(dev.upload(w.reshape(n_exp, -1)), IQ3_S, wr, wc, wr * 110, n_exp, d_xq,
+                                 dev.upload(bounds), max(per), rows, d_dst, wr)
+    finally:
+        assert lib.q4_cuda_mmq_tc_mode(-1)
+    got = dev.download(d_dst, (rows, wr), np.float32)
+    # integer model of the block (src/q4_quant.c:397-409): the library's own dequantiser
+    # gives d * ls * sign * grid, integer-valued here
+    d_deq = dev.malloc(n_exp * wr * wc * 4)
+    assert lib.q4_cuda_iq3s_dequant(dev.upload(w.reshape(-1)), n_exp * wr, wc, d_deq)
+    wi = dev.download(d_deq, (n_exp, wr, wc), np.float32).astype(np.int64)
+    xi = x.astype(np.int64)
+    for e in range(n_exp):
+        want = xi[bounds[e]:bounds[e + 1]] @ wi[e].T
+        assert np.abs(want).max() < 2 ** 24
+        assert np.array_equal(got[bounds[e]:bounds[e + 1]].astype(np.int64), want)
+        assert np.array_equal(got[bounds[e]:bounds[e + 1]], want.astype(np.float32))
+    assert lib.q4_cuda_device_error() == 0
+
+
 def test_verify_window_matches_single_token_path(dev, pkg, oracle):
     """4 tokens with 3/5/7/9 picks over 16 slots (src/q4_test.c:2527-2619)."""
     H, F, n_slots = 2048, 512, 16
@@ -159,6 +210,7 @@ def test_verify_window_matches_single_token_path(dev, pkg, oracle):
         assert not lib.q4_hip_moe_win_ok(IQ3_S, IQ3_S, IQ3_S, H, F, 9)
         assert not lib.q4_hip_moe_win_ok(IQ3_S, 20, IQ3_S, H, F, 4)
     finally:
+        lib.q4_cuda_mmq_tc_mode(-1)
         layer.close()
 
 
@@ -174,6 +226,8 @@ def test_layer_n_matches_oracle_per_token(dev, pkg, oracle, n_tok, n_expert, top
         layer = pkg.MoeLayer(dev, L["experts"], L["shared"], L["router"], L["norm_w"], H, F, topk, arena=1)
     finally:
         lib.q4_cuda_set_tiled_default(1)
+    # the CUDA-core kernels first: with them a token's result does not depend on the batch
+    assert lib.q4_cuda_mmq_tc_mode(0)
     try:
         ws = lib.q4_cuda_moe_layer_n_ws_bytes(n_tok, topk, n_expert, H, F)
         d_ws = dev.malloc(ws)
@@ -199,9 +253,36 @@ def test_layer_n_matches_oracle_per_token(dev, pkg, oracle, n_tok, n_expert, top
                                            d_ws, ws)
             y1 = dev.download(d_y1, (H,), np.float32)
             assert np.array_equal(y1.view(np.uint32), y[2].view(np.uint32))
+        # the streaming kernel (tiled arenas) and the general kernel do the same sums
+        assert lib.q4_cuda_mmq_tc_mode(2)
+        try:
+            assert lib.q4_cuda_moe_layer_n(layer.base, layer.stride, layer.og, layer.ou, layer.od,
+                                           layer.shared_slot, dev.upload(xs), layer.d_norm, 1e-6,
+                                           layer.d_router, n_expert, topk, H, F, n_tok, d_y, d_ids, d_w,
+                                           d_ws, ws)
+        finally:
+            assert lib.q4_cuda_mmq_tc_mode(-1)
+        y2 = dev.download(d_y, (n_tok, H), np.float32)
+        assert np.array_equal(y2.view(np.uint32), y.view(np.uint32))
+        # the tensor-core kernel, alone (1) or taking the entries with many rows (-1, the
+        # default), agrees to rounding: another order of the same products
+        for mode in (1, -1):
+            assert lib.q4_cuda_mmq_tc_mode(mode)
+            try:
+                assert lib.q4_cuda_moe_layer_n(layer.base, layer.stride, layer.og, layer.ou, layer.od,
+                                               layer.shared_slot, dev.upload(xs), layer.d_norm, 1e-6,
+                                               layer.d_router, n_expert, topk, H, F, n_tok, d_y, d_ids,
+                                               d_w, d_ws, ws)
+            finally:
+                assert lib.q4_cuda_mmq_tc_mode(-1)
+            y3 = dev.download(d_y, (n_tok, H), np.float32)
+            for t in range(n_tok):
+                assert _rel(y3[t], y[t]) < 1e-5
+        assert lib.q4_cuda_device_error() == 0
         assert not lib.q4_cuda_moe_layer_n(layer.base, layer.stride, layer.og, layer.ou, layer.od,
                                            layer.shared_slot, dev.upload(xs), layer.d_norm, 1e-6,
                                            layer.d_router, n_expert, topk, H, F, n_tok, d_y, d_ids,
                                            d_w, d_ws, ws - 1)
     finally:
+        lib.q4_cuda_mmq_tc_mode(-1)
         layer.close()
