@@ -268,11 +268,12 @@ class EpJob:
     """64 tokens x n_layers MoE layers on `world` ranks; this object is one rank's part.
     world == 1 is the same job on one GPU through q4_cuda_moe_layer_n."""
 
-    def __init__(self, pkg, dev, ep, arena, rank, world, n_layers):
+    def __init__(self, pkg, dev, ep, arena, rank, world, n_layers, tokens=EP_TOKENS, zipf=False):
         import ctypes
         self.lib = lib = dev.lib
         self.ep, self.world, self.n_layers, self.arena = ep, world, n_layers, arena
-        self.t_local = EP_TOKENS // world
+        self.tokens = tokens
+        self.t_local = tokens // world
         e_local = self.e_local = N_EXPERT // world
         self.slots_l = e_local + 1
         bpp = PACK // IQ3S_BLOCK            # super-blocks per expert pack
@@ -293,7 +294,22 @@ class EpJob:
         assert lib.q4_cuda_synth_normal(self.d_router, n_layers * N_EXPERT * N_EMBD, 2027, 0.0, 0.02)
         self.d_norm = dev.malloc(n_layers * N_EMBD * 4)
         assert lib.q4_cuda_synth_normal(self.d_norm, n_layers * N_EMBD, 2028, 1.0, 0.1)
-        x_all = pkg.synth.hidden(2029, EP_TOKENS, N_EMBD)
+        x_all = pkg.synth.hidden(2029, tokens, N_EMBD)
+        if zipf:
+            # Expert popularity skewed by a Zipf(1.1) bias on the router logits: every
+            # token carries the same value A in coordinate 0 (norm weight 1 there), and
+            # router column 0 holds bias_e / (normalised A), so logit_e = N(0, ~1) + bias_e.
+            A = 4.0
+            x_all[:, 0] = A
+            xn0 = A / np.sqrt((A * A + N_EMBD - 1.0) / N_EMBD)
+            col = (pkg.synth.zipf_bias(N_EXPERT, 1.1) / xn0).astype(np.float32)
+            one = np.ones(1, np.float32)
+            dev.sync()
+            for l in range(n_layers):
+                r = dev.download(self.d_router + l * ROUTER_BYTES, (N_EXPERT, N_EMBD), np.float32)
+                r[:, 0] = col
+                dev.write(self.d_router + l * ROUTER_BYTES, r)
+                dev.write(self.d_norm + l * N_EMBD * 4, one)
         self.x_host = np.ascontiguousarray(x_all[rank * self.t_local:(rank + 1) * self.t_local])
         self.nb = nb = self.t_local * N_EMBD * 4
         self.d_x0, self.d_a, self.d_b = dev.upload(self.x_host), dev.malloc(nb), dev.malloc(nb)
@@ -363,6 +379,9 @@ class EpJob:
         lib.q4_hip_stream_sync()
 
     def release(self):
+        if self.graph:      # a graph that holds collective nodes must go before the communicator does
+            self.lib.q4_hip_graph_free(self.graph)
+            self.graph = None
         self.lib.q4_hip_experts_free_a(self.arena)
         for p in (self.d_router, self.d_norm, self.d_x0, self.d_a, self.d_b, self.d_ws):
             self.lib.q4_hip_free(p)
@@ -465,7 +484,104 @@ def run_ep(a, pkg, rank, world, local, warmup):
             "gpu_launches": int(launches * a.steps * 2),
             "roofline": None, "cpu_baseline": None}))
     if ep:
-        ep.q4_cuda_ep_shutdown()
+        barrier_max(0.0)
+        if job.graph:
+            lib.q4_hip_graph_free(job.graph)
+            job.graph = None
+        # tearing the communicator down must not be able to hold the process: give it ten seconds
+        t = threading.Thread(target=ep.q4_cuda_ep_shutdown, daemon=True)
+        t.start()
+        t.join(10.0)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
+def run_batch(a, pkg, local, warmup, kind):
+    """One GPU, many tokens per step through q4_cuda_moe_layer_n.
+    verify  (config 2): 4 tokens (1 + 3 drafts) through 48 layers, y of a layer feeding the next.
+    prefill (config 3): 2048 tokens through one layer, expert popularity skewed by Zipf(1.1);
+                        consecutive steps alternate between two layers of weights."""
+    dev = pkg.Device()
+    lib = dev.lib
+    if kind == "verify":
+        tokens, n_layers, zipf = 4, (a.layers or 48), False
+    else:
+        tokens, n_layers, zipf = 2048, 2, True
+    job = EpJob(pkg, dev, None, 0, 0, 1, n_layers, tokens=tokens, zipf=zipf)
+    if kind == "prefill":
+        # one layer per step: step i runs layer i % 2 on the same input rows
+        job.enqueue_all = job.enqueue
+        state = {"i": 0}
+
+        def one_layer():
+            job.layer(state["i"] % n_layers, job.d_x0, job.d_a)
+            state["i"] += 1
+            job.d_out = job.d_a
+        job.enqueue = one_layer
+        job.try_capture = lambda: False
+    # routed rows and distinct experts of the job (for the algorithmic figures), read once
+    d_ids = dev.malloc(tokens * TOPK * 4)
+    rows_total, distinct_total = 0, 0
+    src = job.d_x0
+    for l in range(n_layers):
+        dst = job.d_a if (l % 2 == 0) else job.d_b
+        lb = job.base + l * job.slots_l * job.stride
+        assert lib.q4_cuda_moe_layer_n(lb, job.stride, job.og, job.ou, job.od, N_EXPERT, src,
+                                       job.d_norm + l * N_EMBD * 4, EPS, job.d_router + l * ROUTER_BYTES,
+                                       N_EXPERT, TOPK, N_EMBD, N_FF, tokens, dst, d_ids, None, job.d_ws,
+                                       job.ws)
+        ids = dev.download(d_ids, (tokens, TOPK), np.int32)
+        rows_total += ids.size + tokens
+        distinct_total += len(np.unique(ids)) + 1
+        if kind == "verify":
+            src = dst
+    hist = np.bincount(ids.ravel(), minlength=N_EXPERT)
+    sampler = ClockSampler(local)
+    sampler.start()
+    ms, ms_e2e, launches = time_job(job, a.steps, warmup, lambda v: v)
+    clocks = sampler.stop()
+    err = lib.q4_cuda_device_error()
+    if err:
+        raise SystemExit("device error word %#x" % err)
+    layers_per_step = n_layers if kind == "verify" else 1
+    units = tokens * layers_per_step
+    rows_step = rows_total / n_layers * layers_per_step
+    distinct_step = distinct_total / n_layers * layers_per_step
+    t = ms * 1e-3 / a.steps
+    hbm, src_name = read_peaks()
+    bytes_step = distinct_step * PACK + layers_per_step * ROUTER_BYTES
+    ops_step = rows_step * 3 * N_EMBD * N_FF * 2.0
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
+        os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    int8_peak = 2.0 * float(peaks.get("bf16_tflops", 1590.0))      # dense int8 = twice the bf16 rate
+    if kind == "prefill":
+        roof = {"bound": "tensor", "achieved": ops_step / t / 1e12, "peak": int8_peak, "unit": "TOP/s",
+                "frac": ops_step / t / 1e12 / int8_peak, "traffic": None,
+                "peak_source": "2 x measured bf16 burst" if peaks else "2 x fallback bf16",
+                "hbm_GBps": bytes_step / t / 1e9, "hbm_frac": bytes_step / t / 1e9 / hbm,
+                "kernel": "whole step (%d launches)" % launches}
+    else:
+        roof = {"bound": "hbm", "achieved": bytes_step / t / 1e9, "peak": hbm, "unit": "GB/s",
+                "frac": bytes_step / t / 1e9 / hbm, "traffic": None, "peak_source": src_name,
+                "kernel": "whole step (%d launches)" % launches}
+    name = ("config2: speculative-verify decode, 4 tokens x %d MoE layers per step" % n_layers
+            if kind == "verify" else
+            "config3: prefill chunk, 2048 tokens x 1 MoE layer per step, Zipf(1.1) expert skew "
+            "(rows per expert max %d, median %d)" % (int(hist.max()), int(np.median(hist))))
+    print(json.dumps({
+        "metric": METRIC, "value": units / t, "unit": UNIT, "n_gpus": 1, "steps": a.steps, "warmup": warmup,
+        "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8 x IQ3_S, fp32 accumulate", "data": "synthetic",
+        "config": {"workload": name, "l2": "inputs larger than L2: a step reads %.0f MB of weights"
+                                          % (bytes_step / 1e6),
+                   "routed_rows_per_step": rows_step, "distinct_experts_per_step": distinct_step,
+                   "cuda_graph": bool(job.graph)},
+        "clocks": clocks,
+        "e2e": {"value": units * a.steps / (ms_e2e * 1e-3), "unit": UNIT,
+                "h2d_bytes_per_step": job.nb, "d2h_bytes_per_step": job.nb},
+        "gpu_launches": int(launches * a.steps * 2),
+        "roofline": roof, "cpu_baseline": None}))
 
 
 def dist_setup(n_gpus):
@@ -484,8 +600,9 @@ def main():
     ap.add_argument("--layers", type=int, default=48)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--workload", default="auto", choices=["auto", "ep"],
-                    help="ep: run the 64-token x 48-layer expert-parallel job even on one GPU")
+    ap.add_argument("--workload", default="auto", choices=["auto", "ep", "verify", "prefill"],
+                    help="ep: the 64-token x 48-layer expert-parallel job (config 4) even on one GPU; "
+                         "verify: 4 tokens x 48 layers (config 2); prefill: 2048 tokens x 1 layer (config 3)")
     a = ap.parse_args()
     rank, world, local = dist_setup(a.gpus)
     warmup = max(a.warmup, 3)
@@ -537,6 +654,13 @@ def main():
         print(json.dumps(line))
         return
 
+    if world == 1 and a.workload in ("verify", "prefill"):
+        if a.steps == 2000 and a.warmup == 200:
+            a.steps, warmup = 20, 3
+        if a.layers == 48 and a.workload == "prefill":
+            a.layers = 2
+        run_batch(a, pkg, local, warmup, a.workload)
+        return
     if world > 1 or a.workload == "ep":
         if a.steps == 2000 and a.warmup == 200:     # the single-layer defaults are too long here
             a.steps, warmup = 20, 3

@@ -85,8 +85,10 @@ __device__ __forceinline__ uint32_t chunk_cost(uint32_t rows) {
 }
 
 __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
-    extern __shared__ uint8_t smem_raw[];
-    Smem &s = *reinterpret_cast<Smem *>(((uintptr_t)smem_raw + 127u) & ~(uintptr_t)127u);
+    // used directly (no integer round trip), so that the compiler keeps these as
+    // shared-space accesses; dynamic shared memory starts on the declared alignment
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    Smem &s = *reinterpret_cast<Smem *>(smem_raw);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t n_ent = a.n_act ? min(*a.n_act, a.n_entries) : a.n_entries;
 
@@ -212,17 +214,16 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
     int32_t have_rb = -1;
     int32_t r0 = 0, r1 = 0;
     uint32_t limit = WAIT_LIMIT;   // after a wait gave up the rest run through with short waits
+    uint32_t li = c_lo / cpe, ch = c_lo - li * cpe, st = 0, ph = 0;
     for (uint32_t c = c_lo, k = 0; c < c_hi; c++, k++) {
-        const uint32_t st = k % NSTAGE;
         if (tid == 0) produce(k + NSTAGE - 1u);
         __syncwarp();
-        const uint32_t li = c / cpe, ch = c - li * cpe;
         const uint32_t e = s.live[li];
         if (e != have_e) {
             r0 = a.bounds[e];
             r1 = a.bounds[e + 1];
         }
-        if (!mbar_wait(&s.full[st], (k / NSTAGE) & 1u, limit, a.err)) limit = 1024u;
+        if (!mbar_wait(&s.full[st], ph, limit, a.err)) limit = 1024u;
         // decode this warp's tile into registers, then give the stage back
         const uint8_t *tile = s.stage[st] + warp * Q4B_TILE_BYTES;
         const uint4 qs = *reinterpret_cast<const uint4 *>(tile + Q4B_TILE_OFF_QS + 16u * lane);
@@ -296,6 +297,8 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
                 }
             }
         }
+        if (++ch == cpe) ch = 0, li++;
+        if (++st == NSTAGE) st = 0, ph ^= 1u;
     }
 }
 

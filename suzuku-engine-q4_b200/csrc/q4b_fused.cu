@@ -283,8 +283,10 @@ __device__ __forceinline__ void route_block(const Args &a, Small &S, uint32_t ti
 }
 
 __global__ void __launch_bounds__(NT, 1) moe_decode_fused_k(const Args a) {
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *sm = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // used directly (no integer round trip), so that the compiler keeps these as
+    // shared-space accesses; dynamic shared memory starts on the declared alignment
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t *sm = smem_raw;
     uint32_t *tab = reinterpret_cast<uint32_t *>(sm);
     Small &S = *reinterpret_cast<Small *>(sm + 65536);
     uint8_t *stage = sm + a.off_stage;  // router chunks, then routed gate/up tiles

@@ -164,7 +164,49 @@ struct Args {
     const uint32_t *codes;       // byte-expanded code table, device
     uint32_t *err;               // device error word
     uint32_t min_rows;           // entries with fewer rows are left to the CUDA-core kernel
+    const uint2 *work;           // (entry, first row) per pass of 64 rows, built by worklist_k
+    const uint32_t *n_work;
 };
+
+// One item per (entry with min_rows or more rows, pass of NB rows): a hot expert's
+// rows spread over many CTAs.  One block; entries are scanned 1024 at a time.
+__global__ void __launch_bounds__(1024) worklist_k(const int32_t *__restrict__ bounds,
+                                                   const uint32_t *__restrict__ n_act, uint32_t n_entries,
+                                                   uint32_t min_rows, uint2 *__restrict__ work,
+                                                   uint32_t *__restrict__ n_work, uint32_t cap) {
+    __shared__ uint32_t wsum[32];
+    __shared__ uint32_t base_s;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const uint32_t n_ent = n_act ? min(*n_act, n_entries) : n_entries;
+    if (tid == 0) base_s = 0;
+    __syncthreads();
+    for (uint32_t e0 = 0; e0 < n_ent; e0 += blockDim.x) {
+        const uint32_t e = e0 + tid;
+        int32_t r0 = 0, nr = 0;
+        if (e < n_ent) {
+            r0 = bounds[e];
+            nr = bounds[e + 1] - r0;
+        }
+        const uint32_t np = (nr > 0 && (uint32_t)nr >= min_rows) ? ((uint32_t)nr + NB - 1u) / NB : 0u;
+        uint32_t inc = np;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t t = __shfl_up_sync(0xffffffffu, inc, o);
+            if (lane >= (uint32_t)o) inc += t;
+        }
+        if (lane == 31u) wsum[warp] = inc;
+        __syncthreads();
+        uint32_t off = base_s;
+        for (uint32_t wv = 0; wv < warp; wv++) off += wsum[wv];
+        uint32_t pos = off + inc - np;
+        for (uint32_t p = 0; p < np; p++, pos++)
+            if (pos < cap) work[pos] = make_uint2(e, (uint32_t)r0 + p * NB);
+        __syncthreads();
+        if (tid == blockDim.x - 1u) base_s = off + inc;
+        __syncthreads();
+    }
+    if (tid == 0) *n_work = min(base_s, cap);
+}
 
 constexpr uint32_t WAIT_LIMIT = 1u << 21;   // polls before a wait gives up (about a second)
 constexpr uint32_t ERR_MMQ_TC = 0x400u;
@@ -191,12 +233,15 @@ __device__ __forceinline__ void decode_group_w(const Iq3Fields &f, const uint32_
 template <bool TILED>
 __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_constant__ CUtensorMap map_q,
                                                   const __grid_constant__ CUtensorMap map_d) {
-    extern __shared__ uint8_t smem_raw[];
-    Smem &s = *reinterpret_cast<Smem *>(((uintptr_t)smem_raw + 127u) & ~(uintptr_t)127u);
-    const uint32_t entry = blockIdx.y;
-    if (a.n_act && entry >= *a.n_act) return;
-    const int32_t r0 = a.bounds[entry], r1 = a.bounds[entry + 1];
-    if (r1 <= r0 || (uint32_t)(r1 - r0) < a.min_rows) return;
+    // used directly (no integer round trip), so that the compiler keeps these as
+    // shared-space accesses; dynamic shared memory starts on the declared alignment
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    Smem &s = *reinterpret_cast<Smem *>(smem_raw);
+    if (blockIdx.y >= *a.n_work) return;
+    const uint2 item = a.work[blockIdx.y];
+    const uint32_t entry = item.x;
+    const int32_t r0 = (int32_t)item.y;
+    const int32_t r1 = min(a.bounds[entry + 1], r0 + (int32_t)NB);   // this CTA's pass of the entry's rows
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t B = a.cols >> 8;                 // super-blocks per weight row
     const uint32_t n_it = a.cols / KS;              // steps per pass
@@ -355,6 +400,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapFloatOOBfill);
 static EncodeTiledFn g_encode = nullptr;
 static bool g_ready = false, g_tried = false;
+constexpr uint32_t WORK_CAP = 1u << 16;   // passes per launch: entries + rows / 64 must fit
+static uint2 *g_work = nullptr;           // two lists, used alternately, so that two launches in a
+static uint32_t *g_n_work = nullptr;      // row (gate/up, then down) never share one
+static uint32_t g_work_turn = 0;
 
 // Resolve the driver's tensor-map encoder (no link-time dependency on the driver
 // library) and raise the kernels' shared-memory limit.  Called once, from init.
@@ -376,6 +425,11 @@ bool warm() {
         cudaGetLastError();
         return false;
     }
+    if (cudaMalloc(&g_work, 2 * WORK_CAP * sizeof(uint2)) != cudaSuccess ||
+        cudaMalloc(&g_n_work, 2 * sizeof(uint32_t)) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
     g_ready = true;
     return true;
 }
@@ -389,6 +443,8 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
             uint32_t n_entries, const int32_t *bounds, const int8_t *q, const float *dq, uint64_t rows,
             uint32_t cols, uint32_t w_rows, float *dst, uint64_t ld_dst, bool tiled, uint32_t min_rows) {
     if (!g_ready || !shape_ok(w_rows, cols) || rows == 0 || rows > 0x7fffffffull) return false;
+    const uint64_t max_items = (uint64_t)n_entries + rows / NB;
+    if (max_items > WORK_CAP) return false;
     CUtensorMap map_q, map_d;
     {
         // (16 bytes, row, 16-byte chunk of the row): a box lands as [chunk][row][16 B]
@@ -424,7 +480,12 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
     a.codes = g_q4b.codes_d;
     a.err = g_q4b.err_d;
     a.min_rows = min_rows;
-    const dim3 grid(w_rows / MT, n_entries);
+    const uint32_t turn = g_work_turn++ & 1u;
+    a.work = g_work + turn * WORK_CAP;
+    a.n_work = g_n_work + turn;
+    worklist_k<<<1, 1024, 0, g_q4b.stream>>>(bounds, n_act, n_entries, min_rows, g_work + turn * WORK_CAP,
+                                            g_n_work + turn, WORK_CAP);
+    const dim3 grid(w_rows / MT, (unsigned)max_items);
     if (tiled)
         mmq_tc_k<true><<<grid, NT, SMEM_BYTES, g_q4b.stream>>>(a, map_q, map_d);
     else
