@@ -24,7 +24,12 @@ import sys
 import threading
 import time
 
-import numpy as np
+# CPU arm: the reference's expert pool gets the cores; its small host-side router GEMV (OpenMP in
+# the reference's build) stays on one thread -- an OpenMP team next to the pool's spinning workers
+# was measured 13x slower.  Must be set before the OpenMP runtime is loaded.
+os.environ["OMP_NUM_THREADS"] = os.environ.get("Q4B_REF_OMP", "1")
+
+import numpy as np  # noqa: E402
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -213,7 +218,6 @@ def cpu_arm(pkg, layers, x_host, budget_s):
         return None
     ncpu = os.cpu_count() or 2
     os.environ.setdefault("Q4_CPU_THREADS", str(max(1, min(16, ncpu - 1))))
-    os.environ.setdefault("OMP_NUM_THREADS", str(max(1, min(16, ncpu - 1))))
     t, _, _ = ref.time_layers(layers, TOPK, 4, x_host, N_EMBD, N_FF, EPS)  # warm-up, pool start
     per = max(t / 4, 1e-5)
     jobs = int(max(16, min(20000, budget_s / per)))
@@ -631,7 +635,6 @@ def main():
             return
         ncpu = os.cpu_count() or 2
         os.environ.setdefault("Q4_CPU_THREADS", str(max(1, min(16, ncpu - 1))))
-        os.environ.setdefault("OMP_NUM_THREADS", str(max(1, min(16, ncpu - 1))))
         per_step = 64
         ref.time_layers(layers, TOPK, 8, x, N_EMBD, N_FF, EPS)
         steps = min(a.steps, 200)

@@ -7,10 +7,10 @@
 // the general form; this kernel needs the tiled arena format, 1, 2, 4 or 8
 // super-blocks per weight row and a tile count per matrix that is a multiple of 16.
 //
-// Work: the live entries (those with rows) times the matrix's chunks of 24 tiles
-// (21,120 contiguous bytes; the last chunk of a matrix may be shorter).  CTA b takes the b-th contiguous share of that list,
-// so it stays on one expert for many chunks.  One lane keeps a 6-stage ring of
-// chunks in flight (full/empty mbarriers); each of the 24 warps takes one tile
+// Work: the live entries (those with rows) times the matrix's chunks of 20 tiles
+// (17,600 contiguous bytes; the last chunk of a matrix may be shorter).  CTA b takes the b-th contiguous share of that list,
+// so it stays on one expert for many chunks.  One lane keeps a 7-stage ring of
+// chunks in flight (full/empty mbarriers); each of the 20 warps takes one tile
 // of a chunk: lane l decodes block l/4, groups 2(l%4) and 2(l%4)+1 into registers,
 // releases the stage, and dots the decoded codes with the activation rows, two at a time,
 // whose bytes for exactly those 64 columns it keeps in registers from tile to tile
@@ -19,10 +19,10 @@
 
 namespace few {
 
-constexpr uint32_t NCW = 24;                 // warps = tiles per chunk
+constexpr uint32_t NCW = 20;                 // warps = tiles per chunk
 constexpr uint32_t NT = NCW * 32;
 constexpr uint32_t CHUNK_BYTES = NCW * Q4B_TILE_BYTES;
-constexpr uint32_t NSTAGE = 6;
+constexpr uint32_t NSTAGE = 7;
 constexpr uint32_t RB = 2;                   // activation rows held in registers
 constexpr uint32_t MAX_ENTRIES = 1024;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
@@ -211,17 +211,42 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
     float dx[RB][2];
     int bs[RB][2];
     uint32_t have_e = 0xffffffffu;
-    int32_t have_rb = -1;
     int32_t r0 = 0, r1 = 0;
     uint32_t limit = WAIT_LIMIT;   // after a wait gave up the rest run through with short waits
     uint32_t li = c_lo / cpe, ch = c_lo - li * cpe, st = 0, ph = 0;
+    // sum over the lanes of a weight row, then one lane stores
+    auto finish = [&](float v, int32_t r, uint32_t wrow) {
+        v += __shfl_xor_sync(0xffffffffu, v, 1);
+        v += __shfl_xor_sync(0xffffffffu, v, 2);
+        if (B >= 2) v += __shfl_xor_sync(0xffffffffu, v, 4);
+        if (B >= 4) v += __shfl_xor_sync(0xffffffffu, v, 8);
+        if (B >= 8) v += __shfl_xor_sync(0xffffffffu, v, 16);
+        if ((lane & (lanes_per_row - 1u)) == 0) a.dst[(uint64_t)r * a.ld_dst + wrow] = v;
+    };
     for (uint32_t c = c_lo, k = 0; c < c_hi; c++, k++) {
         if (tid == 0) produce(k + NSTAGE - 1u);
         __syncwarp();
         const uint32_t e = s.live[li];
-        if (e != have_e) {
+        if (e != have_e) {   // next expert: its first RB rows' bytes for this lane's 64 columns
+            have_e = e;
             r0 = a.bounds[e];
             r1 = a.bounds[e + 1];
+#pragma unroll
+            for (uint32_t i = 0; i < RB; i++) {
+                if (r0 + (int32_t)i < r1) {
+                    const uint64_t r = (uint64_t)(r0 + (int32_t)i);
+                    const int4 *qp = reinterpret_cast<const int4 *>(a.xq + r * a.cols + gcol * 32u);
+                    const int4 v0 = __ldg(qp), v1 = __ldg(qp + 1), v2 = __ldg(qp + 2), v3 = __ldg(qp + 3);
+                    q[i][0] = v0.x, q[i][1] = v0.y, q[i][2] = v0.z, q[i][3] = v0.w;
+                    q[i][4] = v1.x, q[i][5] = v1.y, q[i][6] = v1.z, q[i][7] = v1.w;
+                    q[i][8] = v2.x, q[i][9] = v2.y, q[i][10] = v2.z, q[i][11] = v2.w;
+                    q[i][12] = v3.x, q[i][13] = v3.y, q[i][14] = v3.z, q[i][15] = v3.w;
+                    const float2 dv = __ldg(reinterpret_cast<const float2 *>(a.xd + r * ngr + gcol));
+                    const int2 bv = __ldg(reinterpret_cast<const int2 *>(a.xbs + r * ngr + gcol));
+                    dx[i][0] = dv.x, dx[i][1] = dv.y;
+                    bs[i][0] = bv.x, bs[i][1] = bv.y;
+                }
+            }
         }
         if (!mbar_wait(&s.full[st], ph, limit, a.err)) limit = 1024u;
         // decode this warp's tile into registers, then give the stage back
@@ -254,47 +279,43 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
         const int ls0 = (int)(2u * (sc & 15u) + 1u), ls1 = (int)(2u * (sc >> 4) + 1u);
         const uint32_t ti = ch * NCW + warp;                       // tile within the matrix
         const uint32_t wrow = ti * rows_per_tile + blk / B;        // this lane's weight row
-        const int32_t r_end = ti < n_tiles ? r1 : r0;               // a short last chunk leaves warps idle
-        for (int32_t rb = r0; rb < r_end; rb += (int32_t)RB) {
-            if (e != have_e || rb != have_rb) {
-                have_e = e;
-                have_rb = rb;
-#pragma unroll
-                for (uint32_t i = 0; i < RB; i++) {
-                    if (rb + (int32_t)i < r1) {
-                        const uint64_t r = (uint64_t)(rb + (int32_t)i);
-                        const int4 *qp = reinterpret_cast<const int4 *>(a.xq + r * a.cols + gcol * 32u);
-                        const int4 v0 = __ldg(qp), v1 = __ldg(qp + 1), v2 = __ldg(qp + 2), v3 = __ldg(qp + 3);
-                        q[i][0] = v0.x, q[i][1] = v0.y, q[i][2] = v0.z, q[i][3] = v0.w;
-                        q[i][4] = v1.x, q[i][5] = v1.y, q[i][6] = v1.z, q[i][7] = v1.w;
-                        q[i][8] = v2.x, q[i][9] = v2.y, q[i][10] = v2.z, q[i][11] = v2.w;
-                        q[i][12] = v3.x, q[i][13] = v3.y, q[i][14] = v3.z, q[i][15] = v3.w;
-                        const float2 dv = __ldg(reinterpret_cast<const float2 *>(a.xd + r * ngr + gcol));
-                        const int2 bv = __ldg(reinterpret_cast<const int2 *>(a.xbs + r * ngr + gcol));
-                        dx[i][0] = dv.x, dx[i][1] = dv.y;
-                        bs[i][0] = bv.x, bs[i][1] = bv.y;
-                    }
-                }
-            }
+        if (ti < n_tiles) {                                        // a short last chunk leaves warps idle
 #pragma unroll
             for (uint32_t i = 0; i < RB; i++) {
-                if (rb + (int32_t)i < r1) {       // uniform over the warp
+                if (r0 + (int32_t)i < r1) {                        // uniform over the warp
                     int a0 = 0, a1 = 0;
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         a0 = __dp4a((int)cw[j], q[i][j], a0);
                         a1 = __dp4a((int)cw[8 + j], q[i][8 + j], a1);
                     }
+                    // sum sign*(2c+1)*q = 2 sum c'q + sum q; same expression as grouped_rows_k
                     const int I0 = 2 * a0 + bs[i][0], I1 = 2 * a1 + bs[i][1];
-                    float v = d * ((float)(I0 * ls0) * dx[i][0] + (float)(I1 * ls1) * dx[i][1]);
-                    v += __shfl_xor_sync(0xffffffffu, v, 1);
-                    v += __shfl_xor_sync(0xffffffffu, v, 2);
-                    if (B >= 2) v += __shfl_xor_sync(0xffffffffu, v, 4);
-                    if (B >= 4) v += __shfl_xor_sync(0xffffffffu, v, 8);
-                    if (B >= 8) v += __shfl_xor_sync(0xffffffffu, v, 16);
-                    if ((lane & (lanes_per_row - 1u)) == 0)
-                        a.dst[(uint64_t)(rb + (int32_t)i) * a.ld_dst + wrow] = v;
+                    finish(d * ((float)(I0 * ls0) * dx[i][0] + (float)(I1 * ls1) * dx[i][1]),
+                           r0 + (int32_t)i, wrow);
                 }
+            }
+            for (int32_t r = r0 + (int32_t)RB; r < r1; r++) {      // further rows: straight from memory
+                const int4 *qp = reinterpret_cast<const int4 *>(a.xq + (uint64_t)r * a.cols + gcol * 32u);
+                int a0 = 0, a1 = 0;
+                {
+                    const int4 v0 = __ldg(qp), v1 = __ldg(qp + 1);
+                    a0 = __dp4a((int)cw[0], v0.x, a0), a0 = __dp4a((int)cw[1], v0.y, a0);
+                    a0 = __dp4a((int)cw[2], v0.z, a0), a0 = __dp4a((int)cw[3], v0.w, a0);
+                    a0 = __dp4a((int)cw[4], v1.x, a0), a0 = __dp4a((int)cw[5], v1.y, a0);
+                    a0 = __dp4a((int)cw[6], v1.z, a0), a0 = __dp4a((int)cw[7], v1.w, a0);
+                }
+                {
+                    const int4 v2 = __ldg(qp + 2), v3 = __ldg(qp + 3);
+                    a1 = __dp4a((int)cw[8], v2.x, a1), a1 = __dp4a((int)cw[9], v2.y, a1);
+                    a1 = __dp4a((int)cw[10], v2.z, a1), a1 = __dp4a((int)cw[11], v2.w, a1);
+                    a1 = __dp4a((int)cw[12], v3.x, a1), a1 = __dp4a((int)cw[13], v3.y, a1);
+                    a1 = __dp4a((int)cw[14], v3.z, a1), a1 = __dp4a((int)cw[15], v3.w, a1);
+                }
+                const float2 dv = __ldg(reinterpret_cast<const float2 *>(a.xd + (uint64_t)r * ngr + gcol));
+                const int2 bv = __ldg(reinterpret_cast<const int2 *>(a.xbs + (uint64_t)r * ngr + gcol));
+                const int I0 = 2 * a0 + bv.x, I1 = 2 * a1 + bv.y;
+                finish(d * ((float)(I0 * ls0) * dv.x + (float)(I1 * ls1) * dv.y), r, wrow);
             }
         }
         if (++ch == cpe) ch = 0, li++;
