@@ -115,6 +115,92 @@ __global__ void gemv_f32_k(const float *__restrict__ W, uint64_t nrows, uint64_t
     if (lane == 0) y[(uint64_t)blockIdx.y * nrows + r] = scale * acc;
 }
 
+// The same GEMV for a batch of vectors with ncols == 2048: a warp keeps its weight row in
+// registers (16 float4 per lane) and walks 16 vectors (grid.y = batch / 16), so W is read
+// once per 16 vectors instead of once per vector.  Same products in the same order as
+// gemv_f32_k, so a vector's result does not depend on the batch it comes in.
+__global__ void __launch_bounds__(256) gemv_f32_x16_k(const float *__restrict__ W, uint64_t nrows,
+                                                      const float *__restrict__ x, uint32_t n_batch,
+                                                      float *__restrict__ y, float scale) {
+    const uint64_t r = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= nrows) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    const float4 *w4 = reinterpret_cast<const float4 *>(W + r * 2048u);
+    float4 w[16];
+#pragma unroll
+    for (int j = 0; j < 16; j++) w[j] = __ldg(w4 + lane + 32 * j);
+    const uint32_t t0 = blockIdx.y * 16u, t1 = min(n_batch, t0 + 16u);
+    for (uint32_t t = t0; t < t1; t++) {
+        const float4 *x4 = reinterpret_cast<const float4 *>(x + (uint64_t)t * 2048u);
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            const float4 b = x4[lane + 32 * j];
+            acc += w[j].x * b.x + w[j].y * b.y + w[j].z * b.z + w[j].w * b.w;
+        }
+        acc = q4b_warp_sum(acc);
+        if (lane == 0) y[(uint64_t)t * nrows + r] = scale * acc;
+    }
+}
+
+// fp32 product for many tokens at once (the router over a batch): y[t][e] = scale *
+// sum_h x[t][h] W[e][h].  Shared-memory tiles of BM tokens x 64 weight rows x 16 columns,
+// 256 threads, thread (ty, tx) owns BM/16 tokens x 4 weight rows; h runs in ascending
+// order inside every thread.  nrows % 64 == 0 and ncols % 16 == 0.
+template <int BM>
+__global__ void __launch_bounds__(256) gemm_f32_nt_k(const float *__restrict__ W, uint32_t nrows,
+                                                     uint32_t ncols, const float *__restrict__ X,
+                                                     uint32_t n_tok, float *__restrict__ Y, float scale) {
+    constexpr int TM = BM / 16;
+    __shared__ float As[16][BM + 4];
+    __shared__ float Bs[16][64 + 4];
+    const uint32_t tid = threadIdx.x, tx = tid & 15u, ty = tid >> 4;
+    const uint32_t e0 = blockIdx.x * 64u, t0 = blockIdx.y * BM;
+    const uint32_t lr = tid >> 2, lc = (tid & 3u) * 4u;   // loader: row of the tile, first of 4 columns
+    float acc[TM][4];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
+    const bool a_live = lr < (uint32_t)BM && t0 + lr < n_tok;
+    const float *xa = X + (uint64_t)(t0 + (a_live ? lr : 0u)) * ncols + lc;
+    const float *wb = W + (uint64_t)(e0 + lr) * ncols + lc;
+    float4 va = make_float4(0.f, 0.f, 0.f, 0.f), vb;
+    if (a_live) va = *reinterpret_cast<const float4 *>(xa);
+    vb = __ldg(reinterpret_cast<const float4 *>(wb));
+    for (uint32_t h0 = 0; h0 < ncols; h0 += 16u) {
+        if (lr < (uint32_t)BM) As[lc][lr] = va.x, As[lc + 1][lr] = va.y, As[lc + 2][lr] = va.z, As[lc + 3][lr] = va.w;
+        Bs[lc][lr] = vb.x, Bs[lc + 1][lr] = vb.y, Bs[lc + 2][lr] = vb.z, Bs[lc + 3][lr] = vb.w;
+        __syncthreads();
+        if (h0 + 16u < ncols) {   // the next tile's loads fly under this tile's products
+            if (a_live) va = *reinterpret_cast<const float4 *>(xa + h0 + 16u);
+            vb = __ldg(reinterpret_cast<const float4 *>(wb + h0 + 16u));
+        }
+#pragma unroll
+        for (int k = 0; k < 16; k++) {
+            float a[TM];
+#pragma unroll
+            for (int i = 0; i < TM; i++) a[i] = As[k][ty * TM + i];
+            const float4 b = *reinterpret_cast<const float4 *>(&Bs[k][tx * 4u]);
+#pragma unroll
+            for (int i = 0; i < TM; i++) {
+                acc[i][0] = fmaf(a[i], b.x, acc[i][0]);
+                acc[i][1] = fmaf(a[i], b.y, acc[i][1]);
+                acc[i][2] = fmaf(a[i], b.z, acc[i][2]);
+                acc[i][3] = fmaf(a[i], b.w, acc[i][3]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; i++) {
+        const uint32_t t = t0 + ty * TM + i;
+        if (t < n_tok)
+            *reinterpret_cast<float4 *>(Y + (uint64_t)t * nrows + e0 + tx * 4u) =
+                make_float4(scale * acc[i][0], scale * acc[i][1], scale * acc[i][2], scale * acc[i][3]);
+    }
+}
+
 // ------------------------------------------------------------------ IQ3_S helpers
 struct Iq3Group {
     uint32_t qs_lo, qs_hi, qh, sg, ls;
@@ -590,7 +676,15 @@ extern "C" bool q4_hip_gemv_dd_n(uint32_t ggml_type, const uint8_t *d_w, uint64_
                                  uint32_t n_batch) {
     if (!g_q4b.ok || !d_w || !d_x || !d_y || nrows == 0 || ncols == 0 || n_batch == 0) return false;
     const dim3 grid((unsigned)((nrows + 7) / 8), n_batch);
-    if (ggml_type == Q4_T_F32) {
+    if (ggml_type == Q4_T_F32 && n_batch >= 512 && (nrows % 64u) == 0 && (ncols % 16u) == 0 &&
+        nrows <= 0xffffffffull && ncols <= 0xffffffffull) {
+        // a large batch: one tiled product instead of n_batch matrix-vector passes over W
+        gemm_f32_nt_k<64><<<dim3((unsigned)(nrows / 64), (n_batch + 63) / 64), 256, 0, g_q4b.stream>>>(
+            reinterpret_cast<const float *>(d_w), (uint32_t)nrows, (uint32_t)ncols, d_x, n_batch, d_y, scale);
+    } else if (ggml_type == Q4_T_F32 && n_batch >= 2 && ncols == 2048) {
+        gemv_f32_x16_k<<<dim3((unsigned)((nrows + 7) / 8), (n_batch + 15) / 16), 256, 0, g_q4b.stream>>>(
+            reinterpret_cast<const float *>(d_w), nrows, d_x, n_batch, d_y, scale);
+    } else if (ggml_type == Q4_T_F32) {
         gemv_f32_k<<<grid, 256, 0, g_q4b.stream>>>(reinterpret_cast<const float *>(d_w), nrows,
                                                   ncols, d_x, d_y, scale);
     } else if (ggml_type == Q4_T_IQ3_S) {

@@ -53,25 +53,43 @@ __host__ __device__ inline Q8View q8_view(const void *buf, uint64_t rows, uint64
     return v;
 }
 
-// One warp per 32 values of one gathered row (a negative source row gives zeros).
+// Four lanes per 32 values of one gathered row, eight values each (a negative source row
+// gives zeros).  Same arithmetic as quant8_k: d = amax / 127, q = rne(x * (127 / amax)).
 __global__ void quantize_rows_k(const float *__restrict__ x, const int32_t *__restrict__ ids,
                                 uint64_t cols, uint64_t rows, int8_t *__restrict__ q,
                                 float *__restrict__ d, int32_t *__restrict__ bs) {
     const uint32_t gpr = (uint32_t)(cols >> 5);
-    const uint64_t g = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (g >= rows * gpr) return;
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint64_t r = g / gpr, gl = g - r * gpr;
-    const int64_t src = ids ? (int64_t)ids[r] : (int64_t)r;
-    const float v = src >= 0 ? x[(uint64_t)src * cols + gl * 32u + lane] : 0.f;
-    const float a = q4b_warp_max(fabsf(v));
+    const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t g = t >> 2;                       // 32-group
+    const uint32_t part = (uint32_t)t & 3u;          // eight values of it
+    const bool live = g < rows * gpr;                // whole quads are live or not
+    const uint64_t r = live ? g / gpr : 0, gl = live ? g - r * gpr : 0;
+    const int64_t src = !live ? -1 : (ids ? (int64_t)ids[r] : (int64_t)r);
+    float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+    if (src >= 0) {
+        const float4 *p = reinterpret_cast<const float4 *>(x + (uint64_t)src * cols + gl * 32u + part * 8u);
+        v0 = __ldg(p);
+        v1 = __ldg(p + 1);
+    }
+    float a = fmaxf(fmaxf(fmaxf(fabsf(v0.x), fabsf(v0.y)), fmaxf(fabsf(v0.z), fabsf(v0.w))),
+                    fmaxf(fmaxf(fabsf(v1.x), fabsf(v1.y)), fmaxf(fabsf(v1.z), fabsf(v1.w))));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
     const float sc = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
-    int qi = max(-128, min(127, __float2int_rn(__fmul_rn(v, sc))));
-    int sum = qi;
-#pragma unroll
-    for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    q[r * cols + gl * 32u + lane] = (int8_t)qi;
-    if (lane == 0) {
+    auto qz = [&](float v) { return max(-128, min(127, __float2int_rn(__fmul_rn(v, sc)))); };
+    const int q0 = qz(v0.x), q1 = qz(v0.y), q2 = qz(v0.z), q3 = qz(v0.w);
+    const int q4 = qz(v1.x), q5 = qz(v1.y), q6 = qz(v1.z), q7 = qz(v1.w);
+    int sum = q0 + q1 + q2 + q3 + q4 + q5 + q6 + q7;
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (!live) return;
+    uint2 o;
+    o.x = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+          ((uint32_t)(q3 & 0xff) << 24);
+    o.y = (uint32_t)(q4 & 0xff) | ((uint32_t)(q5 & 0xff) << 8) | ((uint32_t)(q6 & 0xff) << 16) |
+          ((uint32_t)(q7 & 0xff) << 24);
+    *reinterpret_cast<uint2 *>(q + r * cols + gl * 32u + part * 8u) = o;
+    if (part == 0) {
         d[g] = __fdiv_rn(a, 127.f);
         bs[g] = sum;
     }
@@ -499,7 +517,7 @@ extern "C" bool q4_mmq_quantize(const float *x, const int32_t *ids, void *xq, ui
         return false;
     const Q8View v = q8_view(xq, rows, cols);
     const uint64_t ngr = rows * (cols / 32u);
-    quantize_rows_k<<<(unsigned)((ngr + 7) / 8), 256, 0, g_q4b.stream>>>(
+    quantize_rows_k<<<(unsigned)((ngr * 4 + 255) / 256), 256, 0, g_q4b.stream>>>(
         x, ids, cols, rows, (int8_t *)v.q, (float *)v.d, (int32_t *)v.bs);
     g_q4b_launches++;
     return q4b_launch_ok("quantize_rows");
