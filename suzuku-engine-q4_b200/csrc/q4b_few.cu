@@ -4,26 +4,29 @@
 // 1-D bulk async copies and keeps the activation bytes a lane needs in registers.
 //
 // Same arithmetic and entry points as grouped_rows_k (q4b_grouped.cu), which stays
-// the general form; this kernel needs the tiled arena format, 1, 2, 4 or 8
-// super-blocks per weight row and a tile count per matrix that is a multiple of 16.
+// the general form; this kernel needs the tiled arena format and 1, 2, 4 or 8
+// super-blocks per weight row.
 //
-// Work: the live entries (those with rows) times the matrix's chunks of 20 tiles
-// (17,600 contiguous bytes; the last chunk of a matrix may be shorter).  CTA b takes the b-th contiguous share of that list,
-// so it stays on one expert for many chunks.  One lane keeps a 7-stage ring of
-// chunks in flight (full/empty mbarriers); each of the 20 warps takes one tile
-// of a chunk: lane l decodes block l/4, groups 2(l%4) and 2(l%4)+1 into registers,
-// releases the stage, and dots the decoded codes with the activation rows, two at a time,
-// whose bytes for exactly those 64 columns it keeps in registers from tile to tile
-// (they change only when the CTA moves to the next expert).
+// Work: the live entries (those with rows) times the matrix's chunks of 16 tiles
+// (14,080 contiguous bytes; the last chunk of a matrix may be shorter).  CTAs split
+// that list by estimated cost into contiguous shares, so a CTA stays on one expert
+// for many chunks.  One lane keeps a 9-stage ring of chunks in flight (full/empty
+// mbarriers); each of the 16 warps takes one tile of a chunk: lane l decodes block
+// l/4, groups 2(l%4) and 2(l%4)+1 into registers, releases the stage, and dots the
+// decoded codes with the expert's activation rows.  The first three rows' bytes for
+// exactly those 64 columns stay in registers from tile to tile (they change only
+// when the CTA moves to the next expert); further rows come from L1/L2 per tile.
+// 16 warps x 128 registers: measured faster than more warps with fewer registers
+// (a few spilled registers cost more here than the lost occupancy).
 #include "q4b_tile.cuh"
 
 namespace few {
 
-constexpr uint32_t NCW = 20;                 // warps = tiles per chunk
+constexpr uint32_t NCW = 16;                 // warps = tiles per chunk
 constexpr uint32_t NT = NCW * 32;
 constexpr uint32_t CHUNK_BYTES = NCW * Q4B_TILE_BYTES;
-constexpr uint32_t NSTAGE = 7;
-constexpr uint32_t RB = 2;                   // activation rows held in registers
+constexpr uint32_t NSTAGE = 9;
+constexpr uint32_t RB = 3;                   // activation rows held in registers
 constexpr uint32_t MAX_ENTRIES = 1024;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
 constexpr uint32_t ERR_FEW = 0x800u;

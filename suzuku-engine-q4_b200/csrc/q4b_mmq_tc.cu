@@ -53,7 +53,7 @@ struct __align__(128) Smem {
     uint8_t b[NSTAGE_B][B_BYTES];
     float da[NSTAGE_B][NB][4];
     float sw[2][4][MT];
-    uint32_t tab2[32 * 512];   // doubled code bytes, one column per lane: entry i for lane l at [32 i + l]
+    uint32_t tab2[512];        // doubled code bytes (2c per byte)
     unsigned long long bar_mma[2];
     unsigned long long bar_b[NSTAGE_B];
     uint32_t tmem_base;
@@ -61,8 +61,8 @@ struct __align__(128) Smem {
 };
 // more than half of an SM's shared memory, so that two of these CTAs (each wants
 // all 512 columns of tensor memory) are never resident together
-constexpr uint32_t SMEM_BYTES = sizeof(Smem) + 128;
-static_assert(SMEM_BYTES > 116 * 1024 && SMEM_BYTES <= 227 * 1024, "shared memory layout");
+constexpr uint32_t SMEM_BYTES = 120 * 1024;
+static_assert(sizeof(Smem) + 128 <= SMEM_BYTES, "shared memory layout");
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -226,7 +226,7 @@ __device__ __forceinline__ void decode_group_w(const Iq3Fields &f, const uint32_
         } else {
             m = q4b_sign_mask4(f.sg >> (4 * k));
         }
-        wv[k] = tab2[idx * 32u] ^ (m | 0x01010101u);
+        wv[k] = tab2[idx] ^ (m | 0x01010101u);
     }
 }
 
@@ -248,7 +248,7 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
     const uint8_t *mat = a.w + (uint64_t)(a.act ? a.act[entry] : (int32_t)entry) * a.expert_stride;
     const uint32_t row0 = blockIdx.x * MT;
 
-    for (uint32_t i = tid; i < 32u * 512u; i += NT) s.tab2[i] = __ldg(a.codes + (i >> 5)) << 1;
+    s.tab2[tid] = __ldg(a.codes + tid) << 1;
     if (tid == 0) {
         mbar_init(&s.bar_mma[0], 1);
         mbar_init(&s.bar_mma[1], 1);
@@ -300,7 +300,7 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
         };
         auto decode_to = [&](const Iq3Fields &f, uint32_t buf) {
             uint32_t wv[8];
-            decode_group_w<TILED>(f, s.tab2 + lane, wv);
+            decode_group_w<TILED>(f, s.tab2, wv);
             uint8_t *p = s.a[buf] + d_off;
             *reinterpret_cast<uint4 *>(p) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
             *reinterpret_cast<uint4 *>(p + A_LBO) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
