@@ -236,13 +236,17 @@ extern "C" bool q4_cuda_ep_layer(const uint8_t *base, uint64_t stride, uint64_t 
     ep_bounds_k<<<1, 32, 0, st>>>(w.ek, w.bounds, n_e);
     if (cudaGetLastError() != cudaSuccess) return false;
     if (!q4_mmq_quantize(w.xn, w.atok, w.xq, Q4_T_IQ3_S, n_embd, rows)) return false;
+    // rows of the largest entry one expects: the shared expert's (own tokens), or a routed
+    // expert's share of all picks with a wide margin; only a hint for the kernel choice
+    const uint32_t share = 4u * (T * topk / n_expert + 1u);
+    const uint32_t max_hint = t_local > share ? t_local : share;
     if (!q4_mmq_mul_id(base + og, Q4_T_IQ3_S, 2ull * n_ff, n_embd, stride, n_e, w.xq, w.bounds,
-                       (uint32_t)rows, rows, w.gu, 2ull * n_ff))
+                       max_hint, rows, w.gu, 2ull * n_ff))
         return false;
     if (!q4_mmq_swiglu(w.gu, w.h, rows, n_ff)) return false;
     if (!q4_mmq_quantize(w.h, nullptr, w.hq, Q4_T_IQ3_S, n_ff, rows)) return false;
     if (!q4_mmq_mul_id(base + od, Q4_T_IQ3_S, n_embd, n_ff, stride, n_e, w.hq, w.bounds,
-                       (uint32_t)rows, rows, w.pd, n_embd))
+                       max_hint, rows, w.pd, n_embd))
         return false;
     if (cudaMemsetAsync(w.partial, 0, (uint64_t)T * n_embd * 4, st) != cudaSuccess) return false;
     if (!q4_hip_expert_reduce(w.partial, w.pd, w.rsrc, w.rw, T, k1, n_embd)) return false;

@@ -435,7 +435,11 @@ constexpr uint32_t TC_MIN_ROWS = 12;
 bool launch_grouped_any(const uint8_t *w, uint64_t expert_stride, const int32_t *act,
                         const uint32_t *n_act, uint32_t n_entries, const int32_t *bounds, Q8View xq,
                         uint64_t total_rows, uint32_t cols, uint32_t w_rows, float *dst,
-                        uint64_t ld_dst) {
+                        uint64_t ld_dst, uint64_t max_rows_hint) {
+    // max_rows_hint: the caller's bound on the rows of its largest entry (0 = unknown).  When
+    // it says no entry reaches the tensor-core threshold that kernel is not launched at all;
+    // should an entry exceed the hint anyway, the streaming kernel still takes it.
+    if (max_rows_hint == 0 || max_rows_hint > total_rows) max_rows_hint = total_rows;
     const bool tiled = q4b_ptr_tiled(w);
     const bool tc_ok = g_tc_mode != 0 && g_tc_mode != 2 && mmqtc::g_ready && mmqtc::shape_ok(w_rows, cols);
     const bool few_ok = g_tc_mode != 2 && g_tc_mode != 1 && tiled && few::shape_ok(w_rows, cols, n_entries);
@@ -443,7 +447,7 @@ bool launch_grouped_any(const uint8_t *w, uint64_t expert_stride, const int32_t 
     uint32_t tc_min = 0xffffffffu;
     if (tc_ok) tc_min = g_tc_mode == 1 ? 1u : (few_ok ? TC_MIN_ROWS : 0xffffffffu);
     if (tc_ok && g_tc_mode == -1 && !few_ok && total_rows >= 8ull * n_entries) tc_min = 1u;
-    const bool run_tc = tc_min != 0xffffffffu && total_rows >= tc_min;
+    const bool run_tc = tc_min != 0xffffffffu && max_rows_hint >= tc_min;
     if (run_tc) {
         const bool ok = mmqtc::launch(w, expert_stride, act, n_act, n_entries, bounds, xq.q, xq.d,
                                       total_rows, cols, w_rows, dst, ld_dst, tiled, tc_min);
@@ -527,7 +531,6 @@ extern "C" bool q4_mmq_mul_id(const void *w, uint32_t type, uint64_t w_rows, uin
                               uint64_t expert_stride_bytes, uint32_t n_expert, const void *xq,
                               const int32_t *bounds, uint32_t max_rows, uint64_t total_rows,
                               float *dst, uint64_t ld_dst) {
-    (void)max_rows;
     if (!g_q4b.ok || !w || !xq || !bounds || !dst || n_expert == 0 || total_rows == 0) return false;
     if (!grouped::shape_ok(type, w_rows, w_cols) || ld_dst < w_rows) return false;
     if (!grouped::pow2_blocks(w_cols) &&
@@ -535,7 +538,7 @@ extern "C" bool q4_mmq_mul_id(const void *w, uint32_t type, uint64_t w_rows, uin
         return false;
     return launch_grouped_any((const uint8_t *)w, expert_stride_bytes, nullptr, nullptr, n_expert, bounds,
                               q8_view(xq, total_rows, w_cols), total_rows, (uint32_t)w_cols,
-                              (uint32_t)w_rows, dst, ld_dst);
+                              (uint32_t)w_rows, dst, ld_dst, max_rows);
 }
 
 extern "C" bool q4_mmq_swiglu(const float *gu, float *h, uint64_t rows, uint64_t n_ff) {
@@ -677,14 +680,15 @@ extern "C" bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64
         cudaMemsetAsync(w.gu, 0, rows * 2 * n_ff * 4, st) != cudaSuccess)
         return false;
     if (!launch_grouped_any(base + og, stride, w.stg, w.stgn, n_entries, w.cbounds,
-                            q8_view(w.xq, rows, n_embd), rows, n_embd, 2u * n_ff, w.gu, 2ull * n_ff))
+                            q8_view(w.xq, rows, n_embd), rows, n_embd, 2u * n_ff, w.gu, 2ull * n_ff,
+                            n_tok))
         return false;
     if (!q4_mmq_swiglu(w.gu, w.h, rows, n_ff)) return false;
     if (!q4_mmq_quantize(w.h, nullptr, w.hq, Q4_T_IQ3_S, n_ff, rows)) return false;
     if (!grouped::pow2_blocks(n_ff) && cudaMemsetAsync(w.pd, 0, rows * n_embd * 4, st) != cudaSuccess)
         return false;
     if (!launch_grouped_any(base + od, stride, w.stg, w.stgn, n_entries, w.cbounds,
-                            q8_view(w.hq, rows, n_ff), rows, n_ff, n_embd, w.pd, n_embd))
+                            q8_view(w.hq, rows, n_ff), rows, n_ff, n_embd, w.pd, n_embd, n_tok))
         return false;
     if (cudaMemsetAsync(d_y, 0, (uint64_t)n_tok * n_embd * 4, st) != cudaSuccess) return false;
     if (!q4_hip_expert_reduce(d_y, w.pd, w.rsrc, w.rw, n_tok, k1, n_embd)) return false;
@@ -768,19 +772,19 @@ extern "C" bool q4_hip_moe_exec_win(const uint8_t *base, uint64_t stride, const 
         cudaMemsetAsync(pd, 0, (uint64_t)n_pairs * n_embd * 4, st) != cudaSuccess)
         return false;
     if (ou == og + (uint64_t)n_ff * (in_dim / 256u) * Q4B_IQ3S_BYTES) {
-        if (!launch_grouped(base + og, stride, act, n_act, n_pairs, bounds, xv, in_dim, 2u * n_ff, gu,
-                            2ull * n_ff))
+        if (!launch_grouped_any(base + og, stride, act, n_act, n_pairs, bounds, xv, n_pairs, in_dim,
+                                2u * n_ff, gu, 2ull * n_ff, n_tok))
             return false;
-    } else if (!launch_grouped(base + og, stride, act, n_act, n_pairs, bounds, xv, in_dim, n_ff, gu,
-                               2ull * n_ff) ||
-               !launch_grouped(base + ou, stride, act, n_act, n_pairs, bounds, xv, in_dim, n_ff,
-                               gu + n_ff, 2ull * n_ff)) {
+    } else if (!launch_grouped_any(base + og, stride, act, n_act, n_pairs, bounds, xv, n_pairs, in_dim, n_ff,
+                                   gu, 2ull * n_ff, n_tok) ||
+               !launch_grouped_any(base + ou, stride, act, n_act, n_pairs, bounds, xv, n_pairs, in_dim, n_ff,
+                                   gu + n_ff, 2ull * n_ff, n_tok)) {
         return false;
     }
     if (!q4_mmq_swiglu(gu, h, n_pairs, n_ff)) return false;
     if (!q4_mmq_quantize(h, nullptr, hq, Q4_T_IQ3_S, n_ff, n_pairs)) return false;
-    if (!launch_grouped(base + od, stride, act, n_act, n_pairs, bounds, q8_view(hq, n_pairs, n_ff), n_ff,
-                        n_embd, pd, n_embd))
+    if (!launch_grouped_any(base + od, stride, act, n_act, n_pairs, bounds, q8_view(hq, n_pairs, n_ff),
+                            n_pairs, n_ff, n_embd, pd, n_embd, n_tok))
         return false;
     return q4_hip_expert_reduce(d_y, pd, rsrc, rw, n_tok, 64u, n_embd);
 }
