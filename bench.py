@@ -142,6 +142,7 @@ class Workload:
         # pinned staging for the end-to-end leg
         self.h_x = lib.q4_hip_host_alloc_coh(N_EMBD * 4)
         self.h_y = lib.q4_hip_host_alloc_coh(N_EMBD * 4)
+        self.y_out = np.zeros(N_EMBD, np.float32)
         self.dev.sync()
 
     def layer_base(self, l):
@@ -189,6 +190,7 @@ class Workload:
                 TOPK, N_EMBD, N_FF, self.h_y)
             if not ok:
                 raise RuntimeError("q4_cuda_moe_decode_host refused")
+            ctypes.memmove(self.y_out.ctypes.data, self.h_y, N_EMBD * 4)   # the step's result, read on the host
 
     def host_layers(self, n):
         """Copies of the first n layers' tensors on the host (for the CPU arm)."""

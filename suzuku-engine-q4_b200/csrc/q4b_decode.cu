@@ -16,7 +16,7 @@ extern std::atomic<uint64_t> g_q4b_launches;
 bool q4b_ptr_tiled(const void *p);
 bool q4b_moe_decode_fused(const uint8_t *, uint64_t, uint64_t, uint64_t, uint64_t, int32_t, const float *,
                           const float *, float, const float *, uint32_t, uint32_t, uint32_t, uint32_t,
-                          float *, int32_t *, float *);
+                          float *, int32_t *, float *, float *, uint32_t *, uint32_t);
 
 #define Q4B_X_SLICE 64u  // scratch slice that holds the quantised input row
 
@@ -759,7 +759,8 @@ extern "C" bool q4_cuda_moe_decode(const uint8_t *base, uint64_t stride, uint64_
         fused_on = !(e && e[0] == '0');
     }
     if (fused_on && q4b_moe_decode_fused(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps,
-                                         d_router, n_expert, topk, n_embd, n_ff, d_y, d_ids, d_wts))
+                                         d_router, n_expert, topk, n_embd, n_ff, d_y, d_ids, d_wts,
+                                         nullptr, nullptr, 0))
         return true;
     int8_t *xq = s.xq + (size_t)Q4B_X_SLICE * Q4B_XQ_MAXLEN;
     float *xd = s.xd + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
@@ -803,6 +804,52 @@ extern "C" bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, ui
     float *d_x = s.xn + (size_t)(Q4B_MAX_TOK - 1) * Q4B_XQ_MAXLEN;
     float *d_y = s.xn + (size_t)(Q4B_MAX_TOK - 2) * Q4B_XQ_MAXLEN;
     Q4B_CHECK(cudaMemcpyAsync(d_x, h_x, (size_t)n_embd * 4, cudaMemcpyHostToDevice, s.stream));
+    // Fast hand-off: when the result buffer is pinned, mapped host memory (q4_hip_host_alloc_coh)
+    // the persistent kernel's last CTA writes y straight into it and raises a mapped flag the
+    // host spins on -- no copy node, no stream wake-up.  Anything else takes copy + sync.
+    static int fused_on = -1;
+    if (fused_on < 0) {
+        const char *e = getenv("Q4B_FUSED");
+        fused_on = !(e && e[0] == '0');
+    }
+    float *y_dev_alias = nullptr;
+    if (fused_on && s.flag_h && base && d_router) {
+        static const void *last_ok = nullptr;      // the attribute query costs about a microsecond
+        static float *last_alias = nullptr;
+        if (h_y == last_ok) {
+            y_dev_alias = last_alias;
+        } else {
+            cudaPointerAttributes at;
+            if (cudaPointerGetAttributes(&at, h_y) == cudaSuccess && at.type == cudaMemoryTypeHost &&
+                at.devicePointer && ((uintptr_t)at.devicePointer % 16u) == 0) {
+                y_dev_alias = (float *)at.devicePointer;
+                last_ok = h_y;
+                last_alias = y_dev_alias;
+            } else {
+                cudaGetLastError();
+            }
+        }
+    }
+    if (y_dev_alias && shape_ok(Q4_T_IQ3_S, Q4_T_IQ3_S, Q4_T_IQ3_S, n_embd, n_ff) && n_expert != 0 &&
+        topk != 0 && topk <= n_expert) {
+        const uint32_t epoch = ++s.flag_epoch ? s.flag_epoch : ++s.flag_epoch;   // never 0
+        if (q4b_moe_decode_fused(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps, d_router,
+                                 n_expert, topk, n_embd, n_ff, d_y, nullptr, nullptr, y_dev_alias,
+                                 s.flag_d, epoch)) {
+            volatile uint32_t *f = s.flag_h;
+            for (uint64_t spins = 0; *f != epoch; spins++) {
+                if (spins > 200000000ull) {        // far beyond any launch: let the stream say why
+                    Q4B_CHECK(cudaStreamSynchronize(s.stream));
+                    return *f == epoch;
+                }
+#if defined(__x86_64__)
+                __builtin_ia32_pause();
+#endif
+            }
+            std::atomic_thread_fence(std::memory_order_acquire);
+            return true;
+        }
+    }
     if (!q4_cuda_moe_decode(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps, d_router,
                             n_expert, topk, n_embd, n_ff, d_y, nullptr, nullptr))
         return false;

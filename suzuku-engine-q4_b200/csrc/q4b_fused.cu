@@ -67,6 +67,9 @@ struct Args {
     unsigned long long *bar;      // grid barrier counter
     uint32_t *err;
     unsigned long long *prof;     // optional [gridDim.x][16] phase time stamps (ns), or NULL
+    float *y_host;                // optional: host-mapped copy of y, written by the last CTA to finish
+    volatile uint32_t *flag_host; // host-mapped word that receives flag_val after y_host is complete
+    uint32_t flag_val;
     // shared-memory carve-up (bytes from the 1024-aligned start)
     uint32_t off_stage, off_down, off_sh;
 };
@@ -171,6 +174,7 @@ __device__ __forceinline__ uint32_t quant8_oct(float4 v, float *d_out, int *bs_o
 //   [0, 65536)        code table, entry i replicated per lane: tab[32 i + lane]
 //   [65536, +...)     small arrays (below), then the staging regions
 struct Small {
+    uint32_t last;   // 1 in the CTA that finished last (host hand-off)
     uint64_t mbar[N_MBAR];
     alignas(16) float xn[H];            // normalised x (router input)
     alignas(16) uint32_t xq[H / 4];     // Q8-A of xn, int8x4 words
@@ -580,6 +584,30 @@ __global__ void __launch_bounds__(NT, 1) moe_decode_fused_k(const Args a) {
         }
     }
     stamp(a, 12);
+    // Host hand-off (the call with host buffers): the CTA that finishes last copies y into
+    // the caller's mapped host buffer and then raises the flag the host is spinning on, so
+    // the result needs neither a copy node nor a stream wake-up.  The count rides on the
+    // barrier counter (a third arrival per CTA keeps it a multiple of the grid size).
+    if (a.y_host) {
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned long long old = atomicAdd(a.bar, 1ull);
+            S.last = old == bar_base + 3ull * ncta - 1ull ? 1u : 0u;
+        }
+        __syncthreads();
+        if (S.last) {
+            __threadfence();
+            for (uint32_t i = tid; i < H / 4u; i += NT)
+                reinterpret_cast<float4 *>(a.y_host)[i] = __ldcg(reinterpret_cast<const float4 *>(a.y) + i);
+            __threadfence_system();
+            __syncthreads();
+            if (tid == 0) {
+                *a.flag_host = a.flag_val;
+                __threadfence_system();
+            }
+        }
+    }
 }
 
 }  // namespace fused
@@ -613,7 +641,8 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
                           uint64_t od, int32_t shared_slot, const float *d_x,
                           const float *d_norm_w, float eps, const float *d_router,
                           uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
-                          float *d_y, int32_t *d_ids, float *d_wts) {
+                          float *d_y, int32_t *d_ids, float *d_wts, float *y_host_dev,
+                          uint32_t *flag_host_dev, uint32_t flag_val) {
     using namespace fused;
     Q4bState &s = g_q4b;
     if (n_embd != H || n_ff != F || n_expert > NT || topk > 32) return false;
@@ -653,6 +682,9 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
     a.bar = g_f_bar;
     a.err = s.err_d;
     a.prof = g_f_prof;
+    a.y_host = y_host_dev;
+    a.flag_host = flag_host_dev;
+    a.flag_val = flag_val;
     uint32_t stage_bytes = n_chunks * UCHUNK * 2u * Q4B_TILE_BYTES;
     if (stage_bytes < max_rc * RCHUNK * 4u) stage_bytes = max_rc * RCHUNK * 4u;
     const uint32_t small = (uint32_t)((sizeof(Small) + 127) & ~127u);

@@ -33,6 +33,8 @@ struct Q4bState {
     int32_t *topk_ids_d;
     float *topk_wts_d;
     uint32_t *err_d;  // device error word (bounded waits, argument checks)
+    uint32_t *flag_h, *flag_d;  // pinned, mapped word for the host hand-off of the decode call
+    uint32_t flag_epoch;
     uint32_t *err_h;
     uint32_t *codes_d;  // the 512 codebook entries byte-expanded (c_j in byte j), device memory
     // scratch of the fused layer entry points (q4_cuda_moe_decode*)

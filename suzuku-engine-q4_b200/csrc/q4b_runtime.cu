@@ -156,6 +156,16 @@ extern "C" bool q4_hip_init(void) {
     Q4B_CHECK(cudaMalloc(&s.topk_wts_d, 64 * sizeof(float)));
     Q4B_CHECK(cudaMalloc(&s.err_d, sizeof(uint32_t)));
     Q4B_CHECK(cudaMemset(s.err_d, 0, sizeof(uint32_t)));
+    s.flag_h = s.flag_d = nullptr;
+    s.flag_epoch = 0;
+    if (cudaHostAlloc((void **)&s.flag_h, 64, cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess &&
+        cudaHostGetDevicePointer((void **)&s.flag_d, s.flag_h, 0) == cudaSuccess) {
+        *s.flag_h = 0;
+    } else {   // no mapped host memory: the host-buffer call keeps its copy + sync form
+        cudaGetLastError();
+        if (s.flag_h) cudaFreeHost(s.flag_h);
+        s.flag_h = s.flag_d = nullptr;
+    }
     Q4B_CHECK(cudaHostAlloc(&s.err_h, sizeof(uint32_t), cudaHostAllocDefault));
     {
         uint32_t codes[512];
@@ -202,6 +212,8 @@ extern "C" void q4_hip_shutdown(void) {
     cudaFree(s.topk_ids_d);
     cudaFree(s.topk_wts_d);
     cudaFree(s.err_d);
+    if (s.flag_h) cudaFreeHost(s.flag_h);
+    s.flag_h = s.flag_d = nullptr;
     cudaFree(s.codes_d);
     cudaFreeHost(s.err_h);
     cudaEventDestroy(g_ev0);
@@ -427,7 +439,8 @@ extern "C" uint32_t q4_cuda_device_error(void) {
 extern "C" void *q4_hip_host_alloc_coh(size_t n) {
     if (!g_q4b.ok || n == 0) return nullptr;
     void *p = nullptr;
-    if (cudaHostAlloc(&p, n, cudaHostAllocDefault) != cudaSuccess) {
+    // mapped as well as pinned: kernels may write results straight into it
+    if (cudaHostAlloc(&p, n, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
         cudaGetLastError();
         return nullptr;
     }

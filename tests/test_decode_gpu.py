@@ -269,3 +269,39 @@ def test_moe_layer_small(dev, pkg, oracle):
 def test_config1_moe_layer_full_shape(dev, pkg, oracle):
     """hidden 2048, intermediate 512, 512 experts top-10 + shared, one token."""
     _check_layer(dev, pkg, oracle, 22, 512, 2048, 512, 10, n_tok=2)
+
+
+def test_decode_host_buffers_match_device_call(dev, pkg):
+    """q4_cuda_moe_decode_host: pinned + mapped result buffer (the kernel writes y into host
+    memory and raises a flag the host spins on) and an ordinary pageable buffer (copy + sync)
+    both return exactly what the device-pointer call computes; repeated calls do not
+    interfere (the flag carries an epoch)."""
+    import ctypes
+    H, F, E, K = 2048, 512, 64, 8
+    L = pkg.synth.layer(91, E, H, F)
+    xs = pkg.synth.hidden(92, 3, H)
+    layer = pkg.MoeLayer(dev, L["experts"], L["shared"], L["router"], L["norm_w"], H, F, K, arena=2)
+    lib = dev.lib
+    try:
+        h_x = lib.q4_hip_host_alloc_coh(H * 4)
+        h_y = lib.q4_hip_host_alloc_coh(H * 4)
+        assert h_x and h_y
+        y_page = np.zeros(H, np.float32)
+        for x in xs:
+            want, _, _ = layer.decode(x)
+            ctypes.memmove(h_x, x.ctypes.data, H * 4)
+            ctypes.memset(h_y, 0, H * 4)
+            assert lib.q4_cuda_moe_decode_host(layer.base, layer.stride, layer.og, layer.ou, layer.od,
+                                               layer.shared_slot, h_x, layer.d_norm, 1e-6, layer.d_router,
+                                               E, K, H, F, h_y)
+            got = np.ctypeslib.as_array(ctypes.cast(h_y, ctypes.POINTER(ctypes.c_float)), (H,)).copy()
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+            assert lib.q4_cuda_moe_decode_host(layer.base, layer.stride, layer.og, layer.ou, layer.od,
+                                               layer.shared_slot, x.ctypes.data, layer.d_norm, 1e-6,
+                                               layer.d_router, E, K, H, F, y_page.ctypes.data)
+            assert np.array_equal(y_page.view(np.uint32), want.view(np.uint32))
+        lib.q4_hip_host_free_coh(h_x)
+        lib.q4_hip_host_free_coh(h_y)
+        assert lib.q4_cuda_device_error() == 0
+    finally:
+        layer.close()
