@@ -43,6 +43,9 @@ PACK = 2 * N_FF * (N_EMBD // 256) * IQ3S_BLOCK + N_EMBD * (N_FF // 256) * IQ3S_B
 ROUTER_BYTES = N_EXPERT * N_EMBD * 4
 # algorithmic bytes of one layer-token: router + (top-k + shared) expert packs
 STEP_BYTES = ROUTER_BYTES + (TOPK + 1) * PACK
+# DRAM bytes of one launch of the persistent decode kernel, from an ncu capture of this
+# workload (read 19,163,136 + write 0..256); the algorithmic figure is STEP_BYTES
+FUSED_DRAM_BYTES_PER_LAUNCH = 19163136
 METRIC = "moe_layer_decode_tokens_per_s"
 UNIT = "layer-tok/s"
 
@@ -722,7 +725,10 @@ def main():
                 "h2d_bytes_per_step": N_EMBD * 4, "d2h_bytes_per_step": N_EMBD * 4},
         "gpu_launches": int(round(launches_per_step * a.steps * 2)),
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": None, "peak_source": peak_src,
+                     "frac": achieved / peak, "traffic": FUSED_DRAM_BYTES_PER_LAUNCH,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch "
+                                       "(profiles/decode1_fused_kernel.md)",
+                     "peak_source": peak_src,
                      "kernel": "whole step (%g launches/step)" % launches_per_step},
         "cpu_baseline": cpu,
     }
