@@ -87,6 +87,9 @@ __device__ __forceinline__ uint32_t chunk_cost(uint32_t rows) {
     return 6u + 2u * rows + (rows > RB ? rows : 0u);
 }
 
+// BB = super-blocks per weight row (1, 2, 4 or 8), a template parameter so that the row
+// geometry and the depth of the shuffle sum are compile-time constants.
+template <uint32_t BB>
 __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
     // used directly (no integer round trip), so that the compiler keeps these as
     // shared-space accesses; dynamic shared memory starts on the declared alignment
@@ -130,7 +133,7 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
     __syncthreads();
     const uint32_t n_live = s.n_live;
     if (n_live == 0) return;
-    const uint32_t B = a.cols >> 8;
+    constexpr uint32_t B = BB;
     const uint32_t n_tiles = (a.w_rows * B) >> 3;
     const uint32_t cpe = (n_tiles + NCW - 1u) / NCW;           // chunks per entry (the last may be short)
     // split by cost, not by chunk count: entries differ in rows
@@ -205,11 +208,11 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
     // ---- consumers ----
     const uint32_t *tab = s.tab + lane;
     const uint32_t p = lane & 3u, blk = lane >> 2;
-    const uint32_t lanes_per_row = 4u * B;               // B in {1, 2, 4, 8}
+    constexpr uint32_t lanes_per_row = 4u * B;
     const uint32_t brow = blk & (B - 1u);                // block within the weight row
     const uint32_t gcol = brow * 8u + 2u * p;            // first of the lane's two 32-groups
     const uint32_t ngr = a.cols >> 5;
-    const uint32_t rows_per_tile = 8u / B;
+    constexpr uint32_t rows_per_tile = 8u / B;
     int q[RB][16];
     float dx[RB][2];
     int bs[RB][2];
@@ -328,8 +331,14 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
 
 static bool g_ready = false;
 bool warm() {
-    if (cudaFuncSetAttribute(grouped_few_k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-        cudaSuccess) {
+    if (cudaFuncSetAttribute(grouped_few_k<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(grouped_few_k<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(grouped_few_k<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(grouped_few_k<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+            cudaSuccess) {
         cudaGetLastError();
         return false;
     }
@@ -346,7 +355,13 @@ bool shape_ok(uint64_t w_rows, uint64_t w_cols, uint32_t n_entries) {
 }
 
 bool launch(const Args &a) {
-    grouped_few_k<<<g_q4b.n_sm, NT, SMEM_BYTES, g_q4b.stream>>>(a);
+    switch (a.cols >> 8) {
+    case 1: grouped_few_k<1><<<g_q4b.n_sm, NT, SMEM_BYTES, g_q4b.stream>>>(a); break;
+    case 2: grouped_few_k<2><<<g_q4b.n_sm, NT, SMEM_BYTES, g_q4b.stream>>>(a); break;
+    case 4: grouped_few_k<4><<<g_q4b.n_sm, NT, SMEM_BYTES, g_q4b.stream>>>(a); break;
+    case 8: grouped_few_k<8><<<g_q4b.n_sm, NT, SMEM_BYTES, g_q4b.stream>>>(a); break;
+    default: return false;
+    }
     return true;
 }
 
