@@ -290,6 +290,25 @@ bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, uint64_t og, 
 bool q4_cuda_fused_profile_enable(int on);
 uint32_t q4_cuda_fused_profile_read(unsigned long long *out, uint32_t max_ctas);
 
+/* Fused forms of two steps of the prefill sequence (no reference counterpart):
+ * swiglu_quantize = q4_mmq_swiglu followed by q4_mmq_quantize of the result, without the fp32
+ * h rows in between (hq of q4_mmq_q8_bytes(rows, n_ff) bytes); expert_reduce_set =
+ * q4_hip_expert_reduce onto a zeroed y, without the zeroing. */
+bool q4_cuda_mmq_swiglu_quantize(const float *gu, void *hq, uint64_t rows, uint64_t n_ff);
+bool q4_cuda_expert_reduce_set(float *d_y, const float *d_pd, const int32_t *d_rsrc, const float *d_rw,
+                               uint32_t n_tok, uint32_t topk, uint32_t n_embd);
+
+/* Row assignment for one rank of an expert-parallel layer (no reference counterpart): the picks
+ * of all n_tok tokens (global expert ids) -> rows of the experts [own_first, own_first + own_count)
+ * this rank holds, renumbered from 0; with has_shared one more pick (local expert own_count,
+ * weight 1) for tokens [tok_first, tok_first + tok_count).  d_atok/d_rsrc/d_rw as
+ * q4_hip_assign_pf with topk + has_shared columns and one group of n_tok tokens (unused rows of
+ * d_atok get -1); d_bounds receives own_count + has_shared + 1 row bounds for q4_mmq_mul_id. */
+bool q4_cuda_assign_local(const int32_t *d_ids, const float *d_wts, int32_t *d_atok, int32_t *d_rsrc,
+                          float *d_rw, int32_t *d_bounds, uint32_t n_tok, uint32_t topk,
+                          uint32_t own_first, uint32_t own_count, int has_shared, uint32_t tok_first,
+                          uint32_t tok_count);
+
 /* Which grouped product q4_mmq_mul_id and q4_cuda_moe_layer_n run (no reference
  * counterpart; the reference picks its tile kernel by row count inside q4_mmq_mul_id,
  * src/q4_mmq.cu:387-470): -1 = by size (tensor-core kernel when the call averages 8

@@ -105,6 +105,9 @@ SIGNATURES = {
                                     u32, vp]),
     "q4_cuda_fused_profile_enable": (b, [C.c_int]),
     "q4_cuda_fused_profile_read": (u32, [vp, u32]),
+    "q4_cuda_mmq_swiglu_quantize": (b, [vp, vp, u64, u64]),
+    "q4_cuda_expert_reduce_set": (b, [vp, vp, vp, vp, u32, u32, u32]),
+    "q4_cuda_assign_local": (b, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, C.c_int, u32, u32]),
     "q4_cuda_mmq_tc_mode": (b, [C.c_int]),
     "q4_cuda_synth_iq3s": (b, [vp, u64, u64]),
     "q4_cuda_synth_iq3s_at": (b, [vp, u64, u64, u64]),

@@ -46,45 +46,6 @@ float *g_scalar = nullptr;  // one float for barrier / max
 
 inline uint64_t al(uint64_t v) { return (v + 255u) & ~(uint64_t)255u; }
 
-// Picks of all T tokens as seen by this rank: expert id -> local slot, others -1; the
-// shared expert (local slot e_local) as one more pick for the tokens this rank owns.
-__global__ void ep_local_picks_k(const int32_t *__restrict__ ids, const float *__restrict__ wts,
-                                 int32_t *__restrict__ lids, float *__restrict__ lw, uint32_t n_tok,
-                                 uint32_t topk, uint32_t e_first, uint32_t e_local, uint32_t t_first,
-                                 uint32_t t_local, int has_shared) {
-    const uint32_t k1 = topk + 1u;
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_tok * k1) return;
-    const uint32_t t = i / k1, k = i - t * k1;
-    int32_t id = -1;
-    float w = 0.f;
-    if (k < topk) {
-        const int32_t e = ids[t * topk + k];
-        if (e >= (int32_t)e_first && e < (int32_t)(e_first + e_local)) {
-            id = e - (int32_t)e_first;
-            w = wts[t * topk + k];
-        }
-    } else if (has_shared && t >= t_first && t < t_first + t_local) {
-        id = (int32_t)e_local;
-        w = 1.0f;
-    }
-    lids[i] = id;
-    lw[i] = w;
-}
-
-// bounds[e] = rows before expert e, from the per-expert row counts (one warp).
-__global__ void ep_bounds_k(const uint32_t *__restrict__ ek, int32_t *__restrict__ bounds,
-                            uint32_t n_exp) {
-    if (threadIdx.x == 0) {
-        int32_t b = 0;
-        for (uint32_t e = 0; e < n_exp; e++) {
-            bounds[e] = b;
-            b += (int32_t)ek[e];
-        }
-        bounds[n_exp] = b;
-    }
-}
-
 // y[t] = sum over ranks s = 0..G-1 of recv[s][t], in that order.
 __global__ void ep_sum_k(const float *__restrict__ recv, float *__restrict__ y, uint32_t n,
                          uint32_t world) {
@@ -226,15 +187,10 @@ extern "C" bool q4_cuda_ep_layer(const uint8_t *base, uint64_t stride, uint64_t 
     EP_NCCL(ncclAllGather(w.wts_l, w.wts, (size_t)t_local * topk, ncclFloat, g_comm, st));
     EP_NCCL(ncclGroupEnd());
     // 3. local experts on the rows that picked them
-    ep_local_picks_k<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(
-        w.ids, w.wts, w.lids, w.lw, T, topk, (uint32_t)g_rank * e_local, e_local,
-        (uint32_t)g_rank * t_local, t_local, has_shared);
-    if (cudaGetLastError() != cudaSuccess) return false;
-    if (cudaMemsetAsync(w.atok, 0xff, rows * 4, st) != cudaSuccess) return false;  // -1 = unused row
-    if (!q4_hip_assign_pf(w.lids, w.lw, w.atok, w.rsrc, w.rw, w.stg, w.stgn, w.ek, T, k1, n_e, T))
+    if (!q4_cuda_assign_local(w.ids, w.wts, w.atok, w.rsrc, w.rw, w.bounds, T, topk,
+                              (uint32_t)g_rank * e_local, e_local, has_shared, (uint32_t)g_rank * t_local,
+                              t_local))
         return false;
-    ep_bounds_k<<<1, 32, 0, st>>>(w.ek, w.bounds, n_e);
-    if (cudaGetLastError() != cudaSuccess) return false;
     if (!q4_mmq_quantize(w.xn, w.atok, w.xq, Q4_T_IQ3_S, n_embd, rows)) return false;
     // rows of the largest entry one expects: the shared expert's (own tokens), or a routed
     // expert's share of all picks with a wide margin; only a hint for the kernel choice
@@ -243,13 +199,11 @@ extern "C" bool q4_cuda_ep_layer(const uint8_t *base, uint64_t stride, uint64_t 
     if (!q4_mmq_mul_id(base + og, Q4_T_IQ3_S, 2ull * n_ff, n_embd, stride, n_e, w.xq, w.bounds,
                        max_hint, rows, w.gu, 2ull * n_ff))
         return false;
-    if (!q4_mmq_swiglu(w.gu, w.h, rows, n_ff)) return false;
-    if (!q4_mmq_quantize(w.h, nullptr, w.hq, Q4_T_IQ3_S, n_ff, rows)) return false;
+    if (!q4_cuda_mmq_swiglu_quantize(w.gu, w.hq, rows, n_ff)) return false;
     if (!q4_mmq_mul_id(base + od, Q4_T_IQ3_S, n_embd, n_ff, stride, n_e, w.hq, w.bounds,
                        max_hint, rows, w.pd, n_embd))
         return false;
-    if (cudaMemsetAsync(w.partial, 0, (uint64_t)T * n_embd * 4, st) != cudaSuccess) return false;
-    if (!q4_hip_expert_reduce(w.partial, w.pd, w.rsrc, w.rw, T, k1, n_embd)) return false;
+    if (!q4_cuda_expert_reduce_set(w.partial, w.pd, w.rsrc, w.rw, T, k1, n_embd)) return false;
     // 4. combine
     const size_t blk = (size_t)t_local * n_embd;
     EP_NCCL(ncclGroupStart());

@@ -209,7 +209,59 @@ __global__ void swiglu_rows_k(const float *__restrict__ gu, float *__restrict__ 
     h[i] = q4b_swiglu(gu[r * 2 * n_ff + k], gu[r * 2 * n_ff + n_ff + k]);
 }
 
-// y[t][c] += sum_k rw[t][k] * pd[rsrc[t][k]][c], picks in order k = 0..topk-1.
+// h = silu(g) * u and its Q8-A quantisation in one pass (the values swiglu_rows_k followed by
+// quantize_rows_k would give): four lanes per 32 hidden values, eight each.
+__global__ void swiglu_quant_rows_k(const float *__restrict__ gu, uint64_t rows, uint64_t n_ff,
+                                    int8_t *__restrict__ q, float *__restrict__ d,
+                                    int32_t *__restrict__ bs) {
+    const uint32_t gpr = (uint32_t)(n_ff >> 5);
+    const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const uint64_t g = t >> 2;
+    const uint32_t part = (uint32_t)t & 3u;
+    const bool live = g < rows * gpr;
+    const uint64_t r = live ? g / gpr : 0, gl = live ? g - r * gpr : 0;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = 0.f;
+    if (live) {
+        const float4 *pg = reinterpret_cast<const float4 *>(gu + r * 2 * n_ff + gl * 32u + part * 8u);
+        const float4 *pu = reinterpret_cast<const float4 *>(gu + r * 2 * n_ff + n_ff + gl * 32u + part * 8u);
+        const float4 g0 = __ldg(pg), g1 = __ldg(pg + 1), u0 = __ldg(pu), u1 = __ldg(pu + 1);
+        v[0] = q4b_swiglu(g0.x, u0.x), v[1] = q4b_swiglu(g0.y, u0.y);
+        v[2] = q4b_swiglu(g0.z, u0.z), v[3] = q4b_swiglu(g0.w, u0.w);
+        v[4] = q4b_swiglu(g1.x, u1.x), v[5] = q4b_swiglu(g1.y, u1.y);
+        v[6] = q4b_swiglu(g1.z, u1.z), v[7] = q4b_swiglu(g1.w, u1.w);
+    }
+    float a = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) a = fmaxf(a, fabsf(v[i]));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+    const float sc = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
+    int qi[8], sum = 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        qi[i] = max(-128, min(127, __float2int_rn(__fmul_rn(v[i], sc))));
+        sum += qi[i];
+    }
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (!live) return;
+    uint2 o;
+    o.x = (uint32_t)(qi[0] & 0xff) | ((uint32_t)(qi[1] & 0xff) << 8) | ((uint32_t)(qi[2] & 0xff) << 16) |
+          ((uint32_t)(qi[3] & 0xff) << 24);
+    o.y = (uint32_t)(qi[4] & 0xff) | ((uint32_t)(qi[5] & 0xff) << 8) | ((uint32_t)(qi[6] & 0xff) << 16) |
+          ((uint32_t)(qi[7] & 0xff) << 24);
+    *reinterpret_cast<uint2 *>(q + r * n_ff + gl * 32u + part * 8u) = o;
+    if (part == 0) {
+        d[g] = __fdiv_rn(a, 127.f);
+        bs[g] = sum;
+    }
+}
+
+// y[t][c] (+)= sum_k rw[t][k] * pd[rsrc[t][k]][c], picks in order k = 0..topk-1; ADD = false
+// overwrites y (same value as adding to a zeroed y).
+template <bool ADD>
 __global__ void expert_reduce_k(float *__restrict__ y, const float *__restrict__ pd,
                                 const int32_t *__restrict__ rsrc, const float *__restrict__ rw,
                                 uint32_t topk, uint32_t n_embd) {
@@ -221,7 +273,10 @@ __global__ void expert_reduce_k(float *__restrict__ y, const float *__restrict__
         const int32_t p = rsrc[(uint64_t)t * topk + k];
         if (p >= 0) acc += rw[(uint64_t)t * topk + k] * pd[(uint64_t)p * n_embd + c];
     }
-    y[(uint64_t)t * n_embd + c] += acc;
+    if (ADD)
+        y[(uint64_t)t * n_embd + c] += acc;
+    else
+        y[(uint64_t)t * n_embd + c] = 0.f + acc;
 }
 
 // One block (256 threads) per group of gsz tokens: a stable counting sort of the group's
@@ -233,7 +288,15 @@ __global__ void __launch_bounds__(256) assign_k(
     const int32_t *__restrict__ ids, const float *__restrict__ wts, int32_t *__restrict__ a_tok,
     int32_t *__restrict__ rsrc, float *__restrict__ rw, int32_t *__restrict__ stg,
     uint32_t *__restrict__ stgn, uint32_t *__restrict__ ek, int32_t *__restrict__ cbounds,
-    uint32_t gsz, uint32_t topk, uint32_t n_exp, uint32_t n_tok, uint32_t ek_stride) {
+    uint32_t gsz, uint32_t topk, uint32_t n_exp, uint32_t n_tok, uint32_t ek_stride,
+    uint32_t topk_in, int32_t extra_id, int32_t own_first, uint32_t own_count, uint32_t tok_first,
+    uint32_t tok_count, int32_t *__restrict__ bounds_full) {
+    // ids/wts hold topk_in columns per token; when topk == topk_in + 1 the last pick of every
+    // token is extra_id with weight 1 (the shared expert), not read from memory.
+    // own_count != 0 (expert parallelism): only picks of experts [own_first, own_first +
+    // own_count) are placed, renumbered from 0, and the extra pick only for tokens
+    // [tok_first, tok_first + tok_count).  bounds_full (optional) receives the first row of
+    // every expert and the total: n_exp + 1 values.  Rows of a_tok beyond the total get -1.
     extern __shared__ uint32_t sh[];  // hist[8][n_exp], cnt[n_exp], rank[n_exp], wsum[16]
     uint32_t *hist = sh, *cnt = sh + 8u * n_exp, *rank = cnt + n_exp, *wsum = rank + n_exp;
     const uint32_t g = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -241,11 +304,21 @@ __global__ void __launch_bounds__(256) assign_k(
     const uint32_t seg = g * gsz * topk, rows = (t1 - t0) * topk;
     const uint32_t run = ((rows + 7u) / 8u + 31u) & ~31u;  // picks per warp, a multiple of 32
     const uint32_t i_lo = warp * run, i_hi = min(rows, i_lo + run);
-    const int32_t *gid = ids + (uint64_t)t0 * topk;
+    auto pick_id = [&](uint32_t i) -> int32_t {   // i = pick index within the group
+        const uint32_t t = i / topk, k = i - t * topk;
+        if (k >= topk_in)
+            return (own_count && (t0 + t < tok_first || t0 + t >= tok_first + tok_count)) ? -1 : extra_id;
+        int32_t e = ids[(uint64_t)(t0 + t) * topk_in + k];
+        if (own_count) {
+            e -= own_first;
+            if (e < 0 || (uint32_t)e >= own_count) e = -1;
+        }
+        return e;
+    };
     for (uint32_t i = tid; i < 8u * n_exp; i += blockDim.x) hist[i] = 0;
     __syncthreads();
     for (uint32_t i = i_lo + lane; i < i_hi; i += 32u) {
-        const int32_t e = gid[i];
+        const int32_t e = pick_id(i);
         if (e >= 0 && (uint32_t)e < n_exp) atomicAdd(&hist[warp * n_exp + e], 1u);
     }
     __syncthreads();
@@ -300,8 +373,13 @@ __global__ void __launch_bounds__(256) assign_k(
     if (tid == blockDim.x - 1u) {  // totals
         if (cbounds) cbounds[g * (ek_stride + 1) + nu] = (int32_t)b;
         if (stgn) stgn[g] = nu;
+        wsum[8] = b;
     }
     __syncthreads();
+    if (bounds_full)
+        for (uint32_t e = tid; e <= n_exp; e += blockDim.x)
+            bounds_full[g * (n_exp + 1) + e] = (int32_t)(e < n_exp ? rank[e] : wsum[8]);
+    for (uint32_t i = wsum[8] + tid; i < rows; i += blockDim.x) a_tok[seg + i] = -1;   // unused rows
     for (uint32_t i0 = i_lo; i0 < i_hi; i0 += 32u) {
         const uint32_t i = i0 + lane;
         int32_t e = -1;
@@ -309,7 +387,7 @@ __global__ void __launch_bounds__(256) assign_k(
         if (i < i_hi) {
             t = t0 + i / topk;
             k = i % topk;
-            e = gid[i];
+            e = pick_id(i);
             if (e < 0 || (uint32_t)e >= n_exp) e = -1;
         }
         const uint32_t same = __match_any_sync(0xffffffffu, e);
@@ -318,7 +396,7 @@ __global__ void __launch_bounds__(256) assign_k(
             const uint32_t pos = rank[e] + hist[warp * n_exp + e] + before;
             a_tok[seg + pos] = (int32_t)t;
             rsrc[(uint64_t)t * topk + k] = (int32_t)pos;
-            rw[(uint64_t)t * topk + k] = wts[(uint64_t)t * topk + k];
+            rw[(uint64_t)t * topk + k] = k < topk_in ? wts[(uint64_t)t * topk_in + k] : 1.0f;
         } else if (i < i_hi) {
             rsrc[(uint64_t)t * topk + k] = -1;
             rw[(uint64_t)t * topk + k] = 0.f;
@@ -327,18 +405,6 @@ __global__ void __launch_bounds__(256) assign_k(
         if (e >= 0 && (same & ((1u << lane) - 1u)) == 0) hist[warp * n_exp + e] += __popc(same);
         __syncwarp();
     }
-}
-
-// Append the shared expert (id n_expert, weight 1) as an extra pick of every token:
-// [n_tok][topk] -> [n_tok][topk + 1].
-__global__ void add_shared_pick_k(const int32_t *__restrict__ ids, const float *__restrict__ wts,
-                                  int32_t *__restrict__ ids2, float *__restrict__ wts2,
-                                  uint32_t n_tok, uint32_t topk, int32_t shared_id) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_tok * (topk + 1)) return;
-    const uint32_t t = i / (topk + 1), k = i - t * (topk + 1);
-    ids2[i] = k < topk ? ids[t * topk + k] : shared_id;
-    wts2[i] = k < topk ? wts[t * topk + k] : 1.0f;
 }
 
 // Verify window: per-token slot lists (stride 64, count per token; n_tok <= 8) ->
@@ -553,10 +619,28 @@ extern "C" bool q4_hip_expert_reduce(float *d_y, const float *d_pd, const int32_
                                      const float *d_rw, uint32_t n_tok, uint32_t topk,
                                      uint32_t n_embd) {
     if (!g_q4b.ok || !d_y || !d_pd || !d_rsrc || !d_rw || !n_tok || !topk || !n_embd) return false;
-    expert_reduce_k<<<dim3((n_embd + 255) / 256, n_tok), 256, 0, g_q4b.stream>>>(d_y, d_pd, d_rsrc,
-                                                                               d_rw, topk, n_embd);
+    expert_reduce_k<true><<<dim3((n_embd + 255) / 256, n_tok), 256, 0, g_q4b.stream>>>(
+        d_y, d_pd, d_rsrc, d_rw, topk, n_embd);
     g_q4b_launches++;
     return q4b_launch_ok("expert_reduce");
+}
+extern "C" bool q4_cuda_expert_reduce_set(float *d_y, const float *d_pd, const int32_t *d_rsrc,
+                                          const float *d_rw, uint32_t n_tok, uint32_t topk,
+                                          uint32_t n_embd) {
+    if (!g_q4b.ok || !d_y || !d_pd || !d_rsrc || !d_rw || !n_tok || !topk || !n_embd) return false;
+    expert_reduce_k<false><<<dim3((n_embd + 255) / 256, n_tok), 256, 0, g_q4b.stream>>>(
+        d_y, d_pd, d_rsrc, d_rw, topk, n_embd);
+    g_q4b_launches++;
+    return q4b_launch_ok("expert_reduce_set");
+}
+extern "C" bool q4_cuda_mmq_swiglu_quantize(const float *gu, void *hq, uint64_t rows, uint64_t n_ff) {
+    if (!g_q4b.ok || !gu || !hq || rows == 0 || n_ff == 0 || (n_ff % 32u)) return false;
+    const Q8View v = q8_view(hq, rows, n_ff);
+    const uint64_t ngr = rows * (n_ff / 32u);
+    swiglu_quant_rows_k<<<(unsigned)((ngr * 4 + 255) / 256), 256, 0, g_q4b.stream>>>(
+        gu, rows, n_ff, (int8_t *)v.q, (float *)v.d, (int32_t *)v.bs);
+    g_q4b_launches++;
+    return q4b_launch_ok("swiglu_quantize");
 }
 
 extern "C" bool q4_hip_route_pf(const float *d_rlog, int32_t *d_ids, float *d_wts, uint32_t n_tok,
@@ -570,11 +654,14 @@ extern "C" bool q4_hip_route_pf(const float *d_rlog, int32_t *d_ids, float *d_wt
 static bool launch_assign(const int32_t *d_ids, const float *d_wts, int32_t *d_atok, int32_t *d_rsrc,
                           float *d_rw, int32_t *d_stg, uint32_t *d_stgn, uint32_t *d_ek,
                           int32_t *d_cbounds, uint32_t gsz, uint32_t topk, uint32_t n_exp,
-                          uint32_t n_tok, uint32_t ek_stride) {
+                          uint32_t n_tok, uint32_t ek_stride, uint32_t topk_in = 0,
+                          int32_t extra_id = -1, int32_t own_first = 0, uint32_t own_count = 0,
+                          uint32_t tok_first = 0, uint32_t tok_count = 0, int32_t *d_bounds_full = nullptr) {
     const uint32_t n_g = (n_tok + gsz - 1u) / gsz;
     assign_k<<<n_g, 256, (10 * n_exp + 16) * sizeof(uint32_t), g_q4b.stream>>>(
         d_ids, d_wts, d_atok, d_rsrc, d_rw, d_stg, d_stgn, d_ek, d_cbounds, gsz, topk, n_exp, n_tok,
-        ek_stride);
+        ek_stride, topk_in ? topk_in : topk, extra_id, own_first, own_count, tok_first, tok_count,
+        d_bounds_full);
     g_q4b_launches++;
     return q4b_launch_ok("assign");
 }
@@ -589,6 +676,24 @@ extern "C" bool q4_hip_assign_pf(const int32_t *d_ids, const float *d_wts, int32
     // tables are 512 entries per group, as in the reference (src/q4_rocm.cu:6545-6548)
     return launch_assign(d_ids, d_wts, d_atok, d_rsrc, d_rw, d_stg, d_stgn, d_ek, nullptr, gsz, topk,
                          n_exp, n_tok, 512u);
+}
+
+// Assignment for one rank of an expert-parallel layer: all n_tok tokens' picks (d_ids/d_wts,
+// [n_tok][topk], global expert ids) -> rows of the experts this rank owns, renumbered from 0,
+// plus (has_shared) one pick of local expert own_count, weight 1, for tokens [tok_first,
+// tok_first + tok_count).  Outputs as q4_hip_assign_pf with topk + has_shared columns, one
+// group; d_bounds receives own_count + has_shared + 1 row bounds.
+extern "C" bool q4_cuda_assign_local(const int32_t *d_ids, const float *d_wts, int32_t *d_atok,
+                                     int32_t *d_rsrc, float *d_rw, int32_t *d_bounds, uint32_t n_tok,
+                                     uint32_t topk, uint32_t own_first, uint32_t own_count,
+                                     int has_shared, uint32_t tok_first, uint32_t tok_count) {
+    if (!g_q4b.ok || !d_ids || !d_wts || !d_atok || !d_rsrc || !d_rw || !d_bounds || !n_tok || !topk ||
+        own_count == 0 || own_count + (has_shared ? 1u : 0u) > 1023u || topk > 63u)
+        return false;
+    const uint32_t k1 = topk + (has_shared ? 1u : 0u), n_e = own_count + (has_shared ? 1u : 0u);
+    return launch_assign(d_ids, d_wts, d_atok, d_rsrc, d_rw, nullptr, nullptr, nullptr, nullptr, n_tok, k1,
+                         n_e, n_tok, n_e, topk, has_shared ? (int32_t)own_count : -1, (int32_t)own_first,
+                         own_count, tok_first, tok_count, d_bounds);
 }
 
 // ---- the whole layer for n_tok tokens ----
@@ -662,18 +767,9 @@ extern "C" bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64
                           n_tok))
         return false;
     if (!q4b_route_tokens(w.logits, w.ids, w.wts, n_tok, n_expert, topk)) return false;
-    const int32_t *ids = w.ids;
-    const float *wts = w.wts;
-    if (sh) {
-        add_shared_pick_k<<<(unsigned)((rows + 255) / 256), 256, 0, st>>>(w.ids, w.wts, w.ids2, w.wts2,
-                                                                        n_tok, topk, (int32_t)n_expert);
-        g_q4b_launches++;
-        if (!q4b_launch_ok("add_shared_pick")) return false;
-        ids = w.ids2;
-        wts = w.wts2;
-    }
-    if (!launch_assign(ids, wts, w.atok, w.rsrc, w.rw, w.stg, w.stgn, nullptr, w.cbounds, n_tok, k1,
-                       n_e, n_tok, n_e))
+    // the shared expert is one more pick (id n_expert, weight 1) of every token, added on the fly
+    if (!launch_assign(w.ids, w.wts, w.atok, w.rsrc, w.rw, w.stg, w.stgn, nullptr, w.cbounds, n_tok, k1,
+                       n_e, n_tok, n_e, topk, sh ? (int32_t)n_expert : -1))
         return false;
     if (!q4_mmq_quantize(w.xn, w.atok, w.xq, Q4_T_IQ3_S, n_embd, rows)) return false;
     if (!grouped::pow2_blocks(n_embd) &&
@@ -683,15 +779,13 @@ extern "C" bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64
                             q8_view(w.xq, rows, n_embd), rows, n_embd, 2u * n_ff, w.gu, 2ull * n_ff,
                             n_tok))
         return false;
-    if (!q4_mmq_swiglu(w.gu, w.h, rows, n_ff)) return false;
-    if (!q4_mmq_quantize(w.h, nullptr, w.hq, Q4_T_IQ3_S, n_ff, rows)) return false;
+    if (!q4_cuda_mmq_swiglu_quantize(w.gu, w.hq, rows, n_ff)) return false;
     if (!grouped::pow2_blocks(n_ff) && cudaMemsetAsync(w.pd, 0, rows * n_embd * 4, st) != cudaSuccess)
         return false;
     if (!launch_grouped_any(base + od, stride, w.stg, w.stgn, n_entries, w.cbounds,
                             q8_view(w.hq, rows, n_ff), rows, n_ff, n_embd, w.pd, n_embd, n_tok))
         return false;
-    if (cudaMemsetAsync(d_y, 0, (uint64_t)n_tok * n_embd * 4, st) != cudaSuccess) return false;
-    if (!q4_hip_expert_reduce(d_y, w.pd, w.rsrc, w.rw, n_tok, k1, n_embd)) return false;
+    if (!q4_cuda_expert_reduce_set(d_y, w.pd, w.rsrc, w.rw, n_tok, k1, n_embd)) return false;
     if (d_ids && cudaMemcpyAsync(d_ids, w.ids, (uint64_t)n_tok * topk * 4, cudaMemcpyDeviceToDevice, st) !=
                      cudaSuccess)
         return false;
