@@ -164,8 +164,9 @@ struct Args {
     const uint32_t *codes;       // byte-expanded code table, device
     uint32_t *err;               // device error word
     uint32_t min_rows;           // entries with fewer rows are left to the CUDA-core kernel
-    const uint2 *work;           // (entry, first row) per pass of 64 rows, built by worklist_k
+    const uint2 *work;           // (entry, first row) per pass, built by worklist_k
     const uint32_t *n_work;
+    uint32_t pass_rows;          // activation rows per pass: 64, or 16 to spread a small call over more CTAs
 };
 
 // One item per (entry with min_rows or more rows, pass of NB rows): a hot expert's
@@ -173,7 +174,8 @@ struct Args {
 __global__ void __launch_bounds__(1024) worklist_k(const int32_t *__restrict__ bounds,
                                                    const uint32_t *__restrict__ n_act, uint32_t n_entries,
                                                    uint32_t min_rows, uint2 *__restrict__ work,
-                                                   uint32_t *__restrict__ n_work, uint32_t cap) {
+                                                   uint32_t *__restrict__ n_work, uint32_t cap,
+                                                   uint32_t pass_rows) {
     __shared__ uint32_t wsum[32];
     __shared__ uint32_t base_s;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
@@ -187,7 +189,8 @@ __global__ void __launch_bounds__(1024) worklist_k(const int32_t *__restrict__ b
             r0 = bounds[e];
             nr = bounds[e + 1] - r0;
         }
-        const uint32_t np = (nr > 0 && (uint32_t)nr >= min_rows) ? ((uint32_t)nr + NB - 1u) / NB : 0u;
+        const uint32_t np =
+            (nr > 0 && (uint32_t)nr >= min_rows) ? ((uint32_t)nr + pass_rows - 1u) / pass_rows : 0u;
         uint32_t inc = np;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -200,7 +203,7 @@ __global__ void __launch_bounds__(1024) worklist_k(const int32_t *__restrict__ b
         for (uint32_t wv = 0; wv < warp; wv++) off += wsum[wv];
         uint32_t pos = off + inc - np;
         for (uint32_t p = 0; p < np; p++, pos++)
-            if (pos < cap) work[pos] = make_uint2(e, (uint32_t)r0 + p * NB);
+            if (pos < cap) work[pos] = make_uint2(e, (uint32_t)r0 + p * pass_rows);
         __syncthreads();
         if (tid == blockDim.x - 1u) base_s = off + inc;
         __syncthreads();
@@ -241,7 +244,7 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
     const uint2 item = a.work[blockIdx.y];
     const uint32_t entry = item.x;
     const int32_t r0 = (int32_t)item.y;
-    const int32_t r1 = min(a.bounds[entry + 1], r0 + (int32_t)NB);   // this CTA's pass of the entry's rows
+    const int32_t r1 = min(a.bounds[entry + 1], r0 + (int32_t)a.pass_rows);   // this CTA's pass of the rows
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t B = a.cols >> 8;                 // super-blocks per weight row
     const uint32_t n_it = a.cols / KS;              // steps per pass
@@ -444,7 +447,10 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
             uint32_t n_entries, const int32_t *bounds, const int8_t *q, const float *dq, uint64_t rows,
             uint32_t cols, uint32_t w_rows, float *dst, uint64_t ld_dst, bool tiled, uint32_t min_rows) {
     if (!g_ready || !shape_ok(w_rows, cols) || rows == 0 || rows > 0x7fffffffull) return false;
-    const uint64_t max_items = (uint64_t)n_entries + rows / NB;
+    // a small call (decode batches: a handful of entries reach the threshold) is cut into
+    // passes of 16 rows so that its few entries still spread over many SMs
+    const uint32_t pass_rows = rows <= 2048u ? 16u : NB;
+    const uint64_t max_items = (uint64_t)n_entries + rows / pass_rows;
     if (max_items > WORK_CAP) return false;
     CUtensorMap map_q, map_d;
     {
@@ -484,8 +490,9 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
     const uint32_t turn = g_work_turn++ & 1u;
     a.work = g_work + turn * WORK_CAP;
     a.n_work = g_n_work + turn;
+    a.pass_rows = pass_rows;
     worklist_k<<<1, 1024, 0, g_q4b.stream>>>(bounds, n_act, n_entries, min_rows, g_work + turn * WORK_CAP,
-                                            g_n_work + turn, WORK_CAP);
+                                            g_n_work + turn, WORK_CAP, pass_rows);
     const dim3 grid(w_rows / MT, (unsigned)max_items);
     if (tiled)
         mmq_tc_k<true><<<grid, NT, SMEM_BYTES, g_q4b.stream>>>(a, map_q, map_d);
