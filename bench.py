@@ -176,10 +176,24 @@ class Workload:
                 raise RuntimeError("graph capture failed")
             self.graphs.append(g)
 
-    def run_resident(self, n_graphs, first=0):
+    def capture_tail(self, n):
+        """One more graph of n < g_steps steps: the remainder when the step count is not a
+        multiple of the graph length."""
+        self.tail = None
+        if n:
+            assert self.lib.q4_hip_graph_begin() == 1
+            for i in range(n):
+                self.step(i, self.d_xpool + (i % self.n_x) * N_EMBD * 4)
+            self.tail = self.lib.q4_hip_graph_end()
+            if not self.tail:
+                raise RuntimeError("graph capture failed")
+
+    def run_resident(self, n_graphs, first=0, tail=False):
         for r in range(first, first + n_graphs):
             if not self.lib.q4_hip_graph_launch(self.graphs[r % len(self.graphs)]):
                 raise RuntimeError("graph launch failed")
+        if tail and self.tail and not self.lib.q4_hip_graph_launch(self.tail):
+            raise RuntimeError("graph launch failed")
 
     def run_e2e(self, steps, first=0):
         import ctypes
@@ -678,12 +692,13 @@ def main():
     wl = Workload(pkg, a.layers)
     lib = wl.lib
     launches0 = lib.q4_cuda_launch_count()
-    # graph length: the largest divisor of the step count that is <= the layer count,
-    # so that exactly `steps` steps are timed
-    g_steps = max(d for d in range(1, a.layers + 1) if a.steps % d == 0)
+    # graphs of one pass over the layers each, plus one shorter graph for the remainder, so
+    # that exactly `steps` steps are timed whatever the step count
+    g_steps = min(a.layers, a.steps)
     wl.capture(g_steps)
     launches_per_step = (lib.q4_cuda_launch_count() - launches0) / (len(wl.graphs) * g_steps)
     n_graphs = a.steps // g_steps
+    wl.capture_tail(a.steps % g_steps)
     wl.run_resident((warmup + g_steps - 1) // g_steps)
     wl.dev.sync()
 
@@ -692,7 +707,7 @@ def main():
     # --- device-resident throughput ---
     wl.dev.sync()
     lib.q4_cuda_timer_begin()
-    wl.run_resident(n_graphs)
+    wl.run_resident(n_graphs, tail=True)
     lib.q4_cuda_timer_end()
     ms = lib.q4_cuda_timer_ms()
     wl.dev.sync()

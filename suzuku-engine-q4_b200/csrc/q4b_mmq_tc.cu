@@ -132,6 +132,34 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, int32_t *v) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int32_t *v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
+        : "r"(taddr)
+        : "memory");
+}
+// Packed fp32 pairs (sm_100 f32x2 arithmetic): two products / two fused multiply-adds per
+// instruction, each rounded like the scalar form.
+__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
+                                                   unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -287,9 +315,12 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
         const uint32_t n_mma = (nrows + 15u) & ~15u;
         const uint32_t idesc = instr_desc(n_mma);
         const bool e_live = 16u * e_cs < nrows;
-        float acc[16];
+        // per output column two running sums, over the even and the odd groups, held as one
+        // packed pair so that a step's scaling is one packed multiply and one packed FMA per
+        // two groups; they are added once at the end
+        unsigned long long acc2[16];
 #pragma unroll
-        for (int j = 0; j < 16; j++) acc[j] = 0.f;
+        for (int j = 0; j < 16; j++) acc2[j] = 0ull;
 
         // producer side of step `it` (global step index g): activations by TMA
         auto issue_b = [&](uint32_t it, uint32_t g) {
@@ -357,21 +388,24 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
             }
             tc_fence_after();
             if (e_live) {
-                float swk[4];
+                const unsigned long long sw01 = pack2(s.sw[buf][0][e_row], s.sw[buf][1][e_row]);
+                const unsigned long long sw23 = pack2(s.sw[buf][2][e_row], s.sw[buf][3][e_row]);
 #pragma unroll
-                for (uint32_t k = 0; k < 4; k++) swk[k] = s.sw[buf][k][e_row];
+                for (uint32_t h = 0; h < 2; h++) {       // two groups at a time ...
 #pragma unroll
-                for (uint32_t h = 0; h < 2; h++) {   // two groups at a time: 32 accumulator words live
-                    int32_t c[2][16];
-                    tmem_ld16(e_taddr + buf * 256u + (2u * h) * NB, c[0]);
-                    tmem_ld16(e_taddr + buf * 256u + (2u * h + 1u) * NB, c[1]);
-                    tmem_ld_wait();
+                    for (uint32_t cq = 0; cq < 2; cq++) {  // ... and eight columns: 16 accumulator words live
+                        int32_t c0[8], c1[8];
+                        tmem_ld8(e_taddr + buf * 256u + (2u * h) * NB + 8u * cq, c0);
+                        tmem_ld8(e_taddr + buf * 256u + (2u * h + 1u) * NB + 8u * cq, c1);
+                        tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; j++) {
-                        const float2 dq =
-                            *reinterpret_cast<const float2 *>(&s.da[sb][16u * e_cs + j][2u * h]);
-                        acc[j] = fmaf(__fmul_rn((float)c[0][j], swk[2u * h]), dq.x, acc[j]);
-                        acc[j] = fmaf(__fmul_rn((float)c[1][j], swk[2u * h + 1u]), dq.y, acc[j]);
+                        for (int j = 0; j < 8; j++) {
+                            const unsigned long long dq = *reinterpret_cast<const unsigned long long *>(
+                                &s.da[sb][16u * e_cs + 8u * cq + j][2u * h]);
+                            const unsigned long long t =
+                                mul2(pack2((float)c0[j], (float)c1[j]), h ? sw23 : sw01);
+                            acc2[8 * cq + j] = fma2(t, dq, acc2[8 * cq + j]);
+                        }
                     }
                 }
             }
@@ -383,8 +417,11 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
         if (e_live) {
             float *o = a.dst + (uint64_t)(rc + 16 * (int32_t)e_cs) * a.ld_dst + row0 + e_row;
 #pragma unroll
-            for (int j = 0; j < 16; j++)
-                if (16u * e_cs + j < nrows) o[(uint64_t)j * a.ld_dst] = acc[j];
+            for (int j = 0; j < 16; j++) {
+                float even, odd;
+                unpack2(acc2[j], even, odd);
+                if (16u * e_cs + j < nrows) o[(uint64_t)j * a.ld_dst] = even + odd;
+            }
         }
     }
     tc_fence_before();
