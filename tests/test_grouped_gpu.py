@@ -286,3 +286,49 @@ def test_layer_n_matches_oracle_per_token(dev, pkg, oracle, n_tok, n_expert, top
     finally:
         lib.q4_cuda_mmq_tc_mode(-1)
         layer.close()
+
+
+@pytest.mark.parametrize("per", [[0, 0, 0, 0], [0, 12, 0, 11], [64, 0, 65, 1], [3, 0, 0, 129]])
+def test_grouped_product_edge_row_counts(dev, pkg, oracle, per):
+    """Row counts at the edges of the kernels' ranges, on a tiled arena: no rows at all (nothing may
+    be written), 11 / 12 rows (either side of the tensor-core threshold, one call split between the
+    two kernels), 64 / 65 (one pass / two passes), 129 (three passes, the last with one row).
+    Every kernel choice must agree with the CPU path's int8 dot."""
+    H, F, n_exp = 2048, 512, 4
+    rng = np.random.default_rng(7 + sum(per))
+    packs = pkg.synth.expert_packs(rng, n_exp, H, F)
+    layer = pkg.MoeLayer(dev, packs, None, np.zeros((n_exp, H), np.float32), None, H, F, 1, arena=1)
+    lib = dev.lib
+    try:
+        rows = sum(per)
+        bounds = np.concatenate([[0], np.cumsum(per)]).astype(np.int32)
+        nr = max(rows, 1)
+        x = rng.standard_normal((nr, H)).astype(np.float32)
+        d_xq = dev.malloc(lib.q4_mmq_q8_bytes(nr, H))
+        d_dst = dev.malloc(nr * 2 * F * 4)
+        sentinel = np.full((nr, 2 * F), 7.5, np.float32)
+        assert lib.q4_mmq_quantize(dev.upload(x), None, d_xq, IQ3_S, H, nr)
+        rb = pkg.synth.iq3s_row_bytes(H)
+        for mode in (-1, 0, 1, 2):
+            dev.write(d_dst, sentinel)
+            assert lib.q4_cuda_mmq_tc_mode(mode)
+            try:
+                ok = lib.q4_mmq_mul_id(layer.base + layer.og, IQ3_S, 2 * F, H, layer.stride, n_exp, d_xq,
+                                       dev.upload(bounds), max(per), nr if rows else 1, d_dst, 2 * F)
+            finally:
+                assert lib.q4_cuda_mmq_tc_mode(-1)
+            assert ok
+            got = dev.download(d_dst, (nr, 2 * F), np.float32)
+            if rows == 0:
+                assert np.array_equal(got, sentinel)        # no rows: nothing written
+                continue
+            for r in sorted({0, rows - 1, rows // 2, min(rows - 1, 64), min(rows - 1, 11)}):
+                e = int(np.searchsorted(bounds, r, side="right") - 1)
+                xq = oracle.quant8(x[r])
+                for j in (0, 1, 511, 512, 1023):
+                    row = packs[e][j * rb:(j + 1) * rb]
+                    want = oracle.dot8(row, xq, H)
+                    assert abs(got[r, j] - want) <= 1e-5 * (abs(want) + 1e-3), (mode, r, j, got[r, j], want)
+        assert lib.q4_cuda_device_error() == 0
+    finally:
+        layer.close()
