@@ -228,6 +228,16 @@ def host_synth_layers(pkg, n, seed=2026):
     return [pkg.synth.layer(seed + 17 * l, N_EXPERT, N_EMBD, N_FF) for l in range(n)]
 
 
+def cpu_model():
+    try:
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("model name"):
+                return line.split(":", 1)[1].strip()
+    except OSError:
+        pass
+    return "unknown"
+
+
 def cpu_arm(pkg, layers, x_host, budget_s):
     """Time the reference's CPU path (oracle/_ref) for whole layer-tokens."""
     from oracle import pyoracle
@@ -241,7 +251,7 @@ def cpu_arm(pkg, layers, x_host, budget_s):
     per = max(t / 4, 1e-5)
     jobs = int(max(16, min(20000, budget_s / per)))
     t, _, _ = ref.time_layers(layers, TOPK, jobs, x_host, N_EMBD, N_FF, EPS)
-    return {"value": jobs / t, "unit": UNIT, "cores": ref.threads(), "kind": kind,
+    return {"value": jobs / t, "unit": UNIT, "cores": ref.threads(), "kind": kind, "cpu_model": cpu_model(),
             "sample": "%d layer-tokens over %d layers (%.1f s), router+top-k on the host, "
                       "experts on the reference's worker pool" % (jobs, len(layers), t),
             "ms_per_step": 1e3 * t / jobs, "jobs": jobs}
@@ -440,6 +450,20 @@ def time_job(job, steps, warmup, barrier_max):
     return ms, ms_e2e, launches
 
 
+def ep_roofline(world, n_layers, t_step):
+    """HBM roofline of the expert-parallel job over all ranks: every rank reads the router of
+    each layer and the packs of the distinct experts routed to it plus its copy of the shared
+    expert.  The number of distinct routed experts per layer is the expectation for uniform
+    routing, E * (1 - (1 - k/E)^T) = 367 of 512 at 64 tokens, not a count of this run."""
+    hbm, src = read_peaks()
+    distinct = N_EXPERT * (1.0 - (1.0 - TOPK / N_EXPERT) ** EP_TOKENS)
+    per_layer = world * (ROUTER_BYTES + PACK) + distinct * PACK
+    achieved = per_layer * n_layers / t_step / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": hbm * world, "unit": "GB/s",
+            "frac": achieved / (hbm * world), "traffic": None, "peak_source": src + " x n_gpus",
+            "kernel": "whole step, all ranks; expected distinct experts %.0f per layer" % distinct}
+
+
 def run_ep(a, pkg, rank, world, local, warmup):
     """Config 4: expert-parallel decode, 64 tokens x 48 layers, experts sharded evenly,
     router and shared expert replicated, dispatch/combine over NCCL.  Strong scaling: the
@@ -505,7 +529,7 @@ def run_ep(a, pkg, rank, world, local, warmup):
             "e2e": {"value": units * a.steps / (ms_e2e * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": job.nb, "d2h_bytes_per_step": job.nb},
             "gpu_launches": int(launches * a.steps * 2),
-            "roofline": None, "cpu_baseline": None}))
+            "roofline": ep_roofline(world, n_layers, ms * 1e-3 / a.steps), "cpu_baseline": None}))
     if ep:
         barrier_max(0.0)
         if job.graph:
@@ -670,7 +694,7 @@ def main():
                 "vs_baseline": None, "dtype": "int8 x IQ3_S, fp32 accumulate", "data": "synthetic",
                 "config": dict(config, sample="%d layer-tokens per step over 2 layers" % per_step),
                 "cpu_baseline": {"value": val, "unit": UNIT, "cores": ref.threads(),
-                                 "kind": "reference",
+                                 "kind": "reference", "cpu_model": cpu_model(),
                                  "sample": "%d steps x %d layer-tokens" % (steps, per_step)},
                 "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         print(json.dumps(line))
