@@ -20,8 +20,10 @@
  *  - there is no CPU fallback: without a usable sm_100 GPU q4_hip_init() returns
  *    false and every other entry point refuses.
  *
- * Only IQ3_S (type id 21) expert tensors and F32 (type id 0) router tensors are
- * accepted; q4_hip_moe_tok_ok() and q4_mmq_supported() answer for a given shape.
+ * Expert tensors are IQ3_S (type id 21); the one-token exec calls also take IQ4_NL (type id
+ * 20) as the down projection's type, for packs kept in an arena in the engine's byte order.
+ * Router tensors are F32 (type id 0).  q4_hip_moe_tok_ok() and q4_mmq_supported() answer
+ * for a given shape and type mix.
  */
 #ifndef Q4CUDA_H
 #define Q4CUDA_H
@@ -37,6 +39,7 @@ extern "C" {
 /* ggml type ids used on this path (src/q4.h:20-39). */
 #define Q4_T_F32 0u
 #define Q4_T_IQ3_S 21u
+#define Q4_T_IQ4_NL 20u   /* accepted as the down projection's type (dt) of the one-token exec calls */
 
 /* ---------------- lifecycle and memory (src/q4.h:1029-1031,1397-1400,1511-1512,
  * 1233-1235,1232,1359) ---------------- */
@@ -198,6 +201,11 @@ bool q4_hip_moe_exec_win(const uint8_t *base, uint64_t stride, const int32_t *d_
  * q4_cuda_iq3s_idot: I[r][g] = integer dot of row r's 32-group g with q
  *   (src/q4_cpuexp.c:694-699,855-892 before the sub-scale multiply). */
 bool q4_cuda_quant8(const float *d_x, uint64_t n, int8_t *d_q, float *d_d, int32_t *d_bs);
+/* The same two stages for IQ4_NL rows (18-byte blocks of 32; src/q4_quant.c:270-290,
+ * src/q4_cpuexp.c:977-996): fp32 dequantisation, and I[r][g] = table value x q per block. */
+bool q4_cuda_iq4nl_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out);
+bool q4_cuda_iq4nl_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const int8_t *d_q,
+                        int32_t *d_I);
 bool q4_cuda_iq3s_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out);
 bool q4_cuda_iq3s_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const int8_t *d_q,
                        int32_t *d_I);

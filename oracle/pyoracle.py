@@ -51,6 +51,8 @@ class Oracle:
         L.q4o_iq3s_dot_mmq.argtypes = [_u8p, _i8p, _f32p, C.c_uint64]
         L.q4o_silu.restype = C.c_float
         L.q4o_silu.argtypes = [C.c_float]
+        L.q4o_iq4nl_dot8.restype = C.c_float
+        L.q4o_iq4nl_dot8.argtypes = [_u8p, C.c_void_p, C.c_uint64]
 
     def grid(self):
         return np.array([self.lib.q4o_iq3s_grid(i) for i in range(512)], dtype=np.uint32)
@@ -89,6 +91,34 @@ class Oracle:
         row = _u8(row)
         return float(self.lib.q4o_iq3s_dot8(_p(row, _u8p), C.c_void_p(xq.ctypes.data),
                                             C.c_uint64(n)))
+
+    # ---- IQ4_NL (a routed expert's down projection may use it) ----
+    def iq4nl_dequant_row(self, row, n):
+        row = _u8(row)
+        out = np.zeros(n, np.float32)
+        self.lib.q4o_iq4nl_dequant_row(_p(row, _u8p), C.c_uint64(n), _p(out, _f32p))
+        return out
+
+    def iq4nl_group_idot(self, row, xq, n):
+        row = _u8(row)
+        out = np.zeros(n // 32, np.int32)
+        self.lib.q4o_iq4nl_group_idot(_p(row, _u8p), C.c_void_p(xq.ctypes.data), C.c_uint64(n),
+                                      _p(out, _i32p))
+        return out
+
+    def iq4nl_dot8(self, row, xq, n):
+        row = _u8(row)
+        return float(self.lib.q4o_iq4nl_dot8(_p(row, _u8p), C.c_void_p(xq.ctypes.data), C.c_uint64(n)))
+
+    def expert_job_t(self, packs, wts, x, n_embd, n_ff, down_type):
+        packs = [_u8(p) for p in packs]
+        arr = (C.c_void_p * len(packs))(*[p.ctypes.data for p in packs])
+        wts = _f32(wts)
+        x = _f32(x)
+        y = np.zeros(n_embd, np.float32)
+        self.lib.q4o_expert_job_t(arr, _p(wts, _f32p), C.c_uint32(len(packs)), _p(x, _f32p),
+                                  C.c_uint32(n_embd), C.c_uint32(n_ff), C.c_uint32(down_type), _p(y, _f32p))
+        return y
 
     def matvec8(self, mat, rows, xq, n):
         """rows x n IQ3_S matrix times one quantised activation vector."""
@@ -195,6 +225,10 @@ class Reference:
             f.argtypes = [_u8p, C.c_void_p, C.c_uint64]
         L.q4ref_dot_f32.restype = C.c_float
         L.q4ref_dot_f32.argtypes = [_u8p, _f32p, C.c_uint64]
+        L.q4ref_dot8_t.restype = C.c_float
+        L.q4ref_dot8_t.argtypes = [C.c_uint32, _u8p, C.c_void_p, C.c_uint64]
+        L.q4ref_dot8_avx2_iq4nl.restype = C.c_float
+        L.q4ref_dot8_avx2_iq4nl.argtypes = [_u8p, C.c_void_p, C.c_uint64]
         L.q4ref_time_jobs.restype = C.c_double
         L.q4ref_time_layers.restype = C.c_double
 
@@ -208,6 +242,23 @@ class Reference:
         row = _u8(row)
         f = self.lib.q4ref_dot8_avx2 if avx2 else self.lib.q4ref_dot8
         return float(f(_p(row, _u8p), C.c_void_p(xq.ctypes.data), C.c_uint64(n)))
+
+    def set_down_type(self, type_id):
+        """Type of the down projection of the packs handed to expert_job (21 IQ3_S, 20 IQ4_NL)."""
+        self.lib.q4ref_set_down_type(C.c_uint32(type_id))
+
+    def dequant_row_t(self, type_id, row, n):
+        row = _u8(row)
+        out = np.zeros(n, np.float32)
+        assert self.lib.q4ref_dequant_row_t(C.c_uint32(type_id), _p(row, _u8p), C.c_uint64(n), _p(out, _f32p))
+        return out
+
+    def dot8_t(self, type_id, row, xq, n, avx2_iq4nl=False):
+        row = _u8(row)
+        if avx2_iq4nl:
+            return float(self.lib.q4ref_dot8_avx2_iq4nl(_p(row, _u8p), C.c_void_p(xq.ctypes.data), C.c_uint64(n)))
+        return float(self.lib.q4ref_dot8_t(C.c_uint32(type_id), _p(row, _u8p), C.c_void_p(xq.ctypes.data),
+                                           C.c_uint64(n)))
 
     def dot_f32(self, row, x, n):
         row = _u8(row)

@@ -14,6 +14,7 @@
 #include <string.h>
 
 #include "iq3s_codes.h"
+#include "iq4nl_codes.h"
 
 uint32_t q4o_iq3s_grid(uint32_t idx) {
     const uint32_t c = q4b_iq3s_codes[idx & 511u];
@@ -176,6 +177,90 @@ void q4o_expert_ffn(const uint8_t *pack, const q4o_q8 *xq, uint32_t n_embd,
     if (hq_out) memcpy(hq_out, hq, sizeof(q4o_q8) * (n_ff / 32));
     free(h);
     free(hq);
+}
+
+/* ---- IQ4_NL ---- */
+static const int8_t q4o_iq4nl_values[16] = Q4B_IQ4NL_VALUES;
+
+void q4o_iq4nl_dequant_row(const uint8_t *src, uint64_t n, float *dst) {
+    for (uint64_t b = 0; b < n / 32; b++) {
+        const uint8_t *blk = src + b * Q4O_IQ4NL_BYTES;
+        const float d = q4o_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+        for (int j = 0; j < 16; j++) {
+            dst[32 * b + j] = d * (float)q4o_iq4nl_values[blk[2 + j] & 0xf];
+            dst[32 * b + j + 16] = d * (float)q4o_iq4nl_values[blk[2 + j] >> 4];
+        }
+    }
+}
+
+static void iq4nl_unpack(const uint8_t *blk, int8_t w[32]) {
+    for (int j = 0; j < 16; j++) {
+        w[j] = q4o_iq4nl_values[blk[2 + j] & 0xf];
+        w[j + 16] = q4o_iq4nl_values[blk[2 + j] >> 4];
+    }
+}
+
+void q4o_iq4nl_group_idot(const uint8_t *row, const q4o_q8 *x, uint64_t n, int32_t *I) {
+    int8_t w[32];
+    for (uint64_t b = 0; b < n / 32; b++) {
+        iq4nl_unpack(row + b * Q4O_IQ4NL_BYTES, w);
+        int32_t s = 0;
+        for (int i = 0; i < 32; i++) s += (int32_t)w[i] * x[b].q[i];
+        I[b] = s;
+    }
+}
+
+float q4o_iq4nl_dot8(const uint8_t *row, const q4o_q8 *x, uint64_t n) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int8_t w[32];
+    for (uint64_t b = 0; b < n / 32; b++) {
+        const uint8_t *blk = row + b * Q4O_IQ4NL_BYTES;
+        iq4nl_unpack(blk, w);
+        const float dd = q4o_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8))) * x[b].d; /* :989 */
+        for (int lane = 0; lane < 8; lane++) {
+            int32_t s = 0;
+            for (int t = 0; t < 4; t++) s += (int32_t)w[4 * lane + t] * x[b].q[4 * lane + t];
+            acc[lane] = fmaf(dd, (float)s, acc[lane]); /* src/q4_cpuexp.c:988-993 */
+        }
+    }
+    return ((acc[0] + acc[4]) + (acc[2] + acc[6])) + ((acc[1] + acc[5]) + (acc[3] + acc[7]));
+}
+
+uint64_t q4o_row_bytes(uint32_t type, uint64_t ncols) {
+    return type == Q4O_T_IQ4_NL ? (ncols / 32) * Q4O_IQ4NL_BYTES : (ncols / Q4O_QK_K) * Q4O_IQ3S_BYTES;
+}
+
+void q4o_expert_ffn_t(const uint8_t *pack, const q4o_q8 *xq, uint32_t n_embd, uint32_t n_ff,
+                      uint32_t down_type, float wt, float *y, float *h_out, q4o_q8 *hq_out) {
+    if (down_type == Q4O_T_IQ3_S) {
+        q4o_expert_ffn(pack, xq, n_embd, n_ff, wt, y, h_out, hq_out);
+        return;
+    }
+    const uint64_t rb_gu = q4o_row_bytes(Q4O_T_IQ3_S, n_embd), rb_d = q4o_row_bytes(down_type, n_ff);
+    const uint8_t *gate = pack, *up = pack + (uint64_t)n_ff * rb_gu, *down = up + (uint64_t)n_ff * rb_gu;
+    float *h = (float *)malloc(sizeof(float) * n_ff);
+    q4o_q8 *hq = (q4o_q8 *)malloc(sizeof(q4o_q8) * (n_ff / 32));
+    for (uint32_t r = 0; r < n_ff; r++)
+        h[r] = q4o_silu(q4o_iq3s_dot8(gate + r * rb_gu, xq, n_embd)) * q4o_iq3s_dot8(up + r * rb_gu, xq, n_embd);
+    q4o_quant8(h, n_ff, hq);
+    for (uint32_t r = 0; r < n_embd; r++) {
+        const float t = wt * q4o_iq4nl_dot8(down + r * rb_d, hq, n_ff);
+        y[r] = y[r] + t;
+    }
+    if (h_out) memcpy(h_out, h, sizeof(float) * n_ff);
+    if (hq_out) memcpy(hq_out, hq, sizeof(q4o_q8) * (n_ff / 32));
+    free(h);
+    free(hq);
+}
+
+void q4o_expert_job_t(const uint8_t *const *packs, const float *wts, uint32_t k, const float *x,
+                      uint32_t n_embd, uint32_t n_ff, uint32_t down_type, float *y) {
+    q4o_q8 *xq = (q4o_q8 *)malloc(sizeof(q4o_q8) * (n_embd / 32));
+    q4o_quant8(x, n_embd, xq);
+    memset(y, 0, sizeof(float) * n_embd);
+    for (uint32_t e = 0; e < k; e++)
+        q4o_expert_ffn_t(packs[e], xq, n_embd, n_ff, down_type, wts[e], y, NULL, NULL);
+    free(xq);
 }
 
 void q4o_expert_job(const uint8_t *const *packs, const float *wts, uint32_t k,

@@ -105,6 +105,27 @@ void q4o_moe_layer(const float *x, const float *norm_w, float eps,
                    const uint8_t *shared_pack, uint32_t n_embd, uint32_t n_ff,
                    float *y, int32_t *ids_out, float *wts_out, float *xn_out);
 
+/* ---- IQ4_NL (ggml type 20): 18-byte blocks of 32 weights, fp16 d + 16 bytes of 4-bit codes;
+ * weight j = d * table[qs[j] & 15], weight j + 16 = d * table[qs[j] >> 4]
+ * (src/q4_quant.c:270-290).  A routed expert's down projection may use it
+ * (src/q4_rocm.cu:4926-4944 lists the accepted types). ---- */
+#define Q4O_T_IQ3_S 21u
+#define Q4O_T_IQ4_NL 20u
+#define Q4O_IQ4NL_BYTES 18
+void q4o_iq4nl_dequant_row(const uint8_t *src, uint64_t n, float *dst);
+/* I[g] = sum over the 32 weights of block g of table value * q (int32, exact). */
+void q4o_iq4nl_group_idot(const uint8_t *row, const q4o_q8 *x, uint64_t n, int32_t *I);
+/* Row dot against Q8-A activations in the CPU path's order (src/q4_cpuexp.c:977-996): eight
+ * running sums over 4-element slices, one fused multiply-add per block, fixed final tree. */
+float q4o_iq4nl_dot8(const uint8_t *row, const q4o_q8 *x, uint64_t n);
+/* Bytes of one row of ncols weights in the given type (IQ3_S or IQ4_NL). */
+uint64_t q4o_row_bytes(uint32_t type, uint64_t ncols);
+/* q4o_expert_ffn / q4o_expert_job with the down projection's type given (gate and up IQ3_S). */
+void q4o_expert_ffn_t(const uint8_t *pack, const q4o_q8 *xq, uint32_t n_embd, uint32_t n_ff,
+                      uint32_t down_type, float wt, float *y, float *h_out, q4o_q8 *hq_out);
+void q4o_expert_job_t(const uint8_t *const *packs, const float *wts, uint32_t k, const float *x,
+                      uint32_t n_embd, uint32_t n_ff, uint32_t down_type, float *y);
+
 /* ---- "Q8-C": the q8_1 block quantiser the reference's grouped prefill GEMM
  * uses (third_party/llama.cpp/ggml/src/ggml-cuda/quantize.cu:491-553):
  * d_inv = 127/amax, q = roundf(x * d_inv) (half away from zero), d = 1/d_inv.

@@ -49,15 +49,18 @@ const uint8_t *q4_expert_host_ptr(const q4_expert_cache *c, int32_t layer,
     return c->packs[eid];
 }
 
-static void shim_tensor(q4_tensor *t, uint64_t cols, uint64_t rows, uint32_t n_exp) {
+static uint32_t g_shim_down_type = Q4_T_IQ3_S;   /* type of the down projection of the packs */
+void q4ref_set_down_type(uint32_t type) { g_shim_down_type = type; }
+
+static void shim_tensor(q4_tensor *t, uint32_t type, uint64_t cols, uint64_t rows, uint32_t n_exp) {
     memset(t, 0, sizeof *t);
     t->n_dims = 3;
     t->ne[0] = cols;
     t->ne[1] = rows;
     t->ne[2] = n_exp;
-    t->ggml_type = Q4_T_IQ3_S;
+    t->ggml_type = type;
     t->n_experts = (int32_t)n_exp;
-    t->nbytes = q4_row_bytes(Q4_T_IQ3_S, cols) * rows * n_exp;
+    t->nbytes = q4_row_bytes(type, cols) * rows * n_exp;
     t->kind = Q4_KIND_ROUTED;
 }
 
@@ -65,9 +68,9 @@ static void shim_setup(const uint8_t *const *packs, uint32_t n_packs,
                        uint32_t n_embd, uint32_t n_ff) {
     g_shim.packs = packs;
     g_shim.n_packs = n_packs;
-    shim_tensor(&g_shim.tg, n_embd, n_ff, n_packs);
-    shim_tensor(&g_shim.tu, n_embd, n_ff, n_packs);
-    shim_tensor(&g_shim.td, n_ff, n_embd, n_packs);
+    shim_tensor(&g_shim.tg, Q4_T_IQ3_S, n_embd, n_ff, n_packs);
+    shim_tensor(&g_shim.tu, Q4_T_IQ3_S, n_embd, n_ff, n_packs);
+    shim_tensor(&g_shim.td, g_shim_down_type, n_ff, n_embd, n_packs);
     g_shim.sg = g_shim.tg.nbytes / n_packs;
     g_shim.su = g_shim.tu.nbytes / n_packs;
     g_shim.sd = g_shim.td.nbytes / n_packs;
@@ -105,6 +108,20 @@ float q4ref_dot_f32(const uint8_t *row, const float *x, uint64_t n) {
 
 int q4ref_dequant_row(const uint8_t *src, uint64_t n, float *dst) {
     return q4_dequant_row(Q4_T_IQ3_S, src, n, dst) ? 1 : 0;
+}
+/* The same three for any type the CPU path takes. */
+int q4ref_dequant_row_t(uint32_t type, const uint8_t *src, uint64_t n, float *dst) {
+    return q4_dequant_row(type, src, n, dst) ? 1 : 0;
+}
+float q4ref_dot8_t(uint32_t type, const uint8_t *row, const void *xq, uint64_t n) {
+    float v = 0.f;
+    cpx_fgrid_init();
+    cpx_esigns_init();
+    cpx_dot8(type, row, (const cpx_q8 *)xq, n, &v);
+    return v;
+}
+float q4ref_dot8_avx2_iq4nl(const uint8_t *row, const void *xq, uint64_t n) {
+    return dq8_iq4_nl(row, (const cpx_q8 *)xq, n);
 }
 
 /* y (+)= W x through the scalar reference GEMV (src/q4_quant.c:595-626). */

@@ -476,6 +476,89 @@ __global__ void moe_ya_k(const uint8_t *__restrict__ bd, uint64_t stride,
     if (lane == 0) y[r] += acc;
 }
 
+// ------------------------------------------------------------------ IQ4_NL (down projection)
+// 18-byte blocks of 32 weights: fp16 d, then 16 bytes whose low / high nibble index the
+// format's 16-value table for weights j / j + 16 (src/q4_quant.c:270-290).  The kernels keep
+// a 256-entry table in shared memory: code byte -> (low value, high value) as two int8.
+__device__ __forceinline__ void iq4nl_fill_pair_table(uint16_t *pair) {
+    const int8_t kv[16] = Q4B_IQ4NL_VALUES;
+    for (uint32_t b = threadIdx.x; b < 256u; b += blockDim.x)
+        pair[b] = (uint16_t)((uint8_t)kv[b & 15u] | ((uint16_t)(uint8_t)kv[b >> 4] << 8));
+}
+// Integer dot of one block with its 32 activation bytes (q: eight int8x4 words): exact int32.
+__device__ __forceinline__ int32_t iq4nl_block_idot(const uint8_t *blk, const uint16_t *pair,
+                                                    const int *q) {
+    int32_t acc = 0;
+#pragma unroll
+    for (int w = 0; w < 4; w++) {       // four code bytes -> weights 4w..4w+3 and 16+4w..16+4w+3
+        const uint32_t c01 = q4b_ld_u16(blk + 2 + 4 * w), c23 = q4b_ld_u16(blk + 4 + 4 * w);
+        const uint32_t p0 = pair[c01 & 0xffu], p1 = pair[c01 >> 8], p2 = pair[c23 & 0xffu], p3 = pair[c23 >> 8];
+        const uint32_t lo = (p0 & 0xffu) | ((p1 & 0xffu) << 8) | ((p2 & 0xffu) << 16) | ((p3 & 0xffu) << 24);
+        const uint32_t hi = (p0 >> 8) | ((p1 >> 8) << 8) | ((p2 >> 8) << 16) | ((p3 >> 8) << 24);
+        acc = __dp4a((int)lo, q[w], acc);
+        acc = __dp4a((int)hi, q[4 + w], acc);
+    }
+    return acc;
+}
+
+__global__ void iq4nl_dequant_k(const uint8_t *__restrict__ w, uint64_t n_blocks, float *__restrict__ out) {
+    const int8_t kv[16] = Q4B_IQ4NL_VALUES;
+    const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    const uint8_t *blk = w + b * 18u;
+    const float d = __half2float(__ushort_as_half((unsigned short)q4b_ld_u16(blk)));
+    for (int j = 0; j < 16; j++) {
+        out[b * 32u + j] = __fmul_rn(d, (float)kv[blk[2 + j] & 15u]);
+        out[b * 32u + j + 16] = __fmul_rn(d, (float)kv[blk[2 + j] >> 4]);
+    }
+}
+
+// I[r][g] for nrows rows of ng blocks against one quantised vector.
+__global__ void iq4nl_idot_k(const uint8_t *__restrict__ w, uint64_t nrows, uint32_t ng,
+                             const int8_t *__restrict__ q, int32_t *__restrict__ I) {
+    __shared__ uint16_t pair[256];
+    iq4nl_fill_pair_table(pair);
+    __syncthreads();
+    const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= nrows * ng) return;
+    const uint32_t g = (uint32_t)(t % ng);
+    int qv[8];
+    for (int k = 0; k < 8; k++) qv[k] = reinterpret_cast<const int *>(q)[g * 8u + k];
+    I[t] = iq4nl_block_idot(w + t * 18u, pair, qv);
+}
+
+// Down projection with IQ4_NL rows: the counterpart of moe_ya_k (same reduction shape).
+__global__ void moe_ya_iq4nl_k(const uint8_t *__restrict__ bd, uint64_t stride,
+                               const int32_t *__restrict__ slots, const float *__restrict__ wts,
+                               uint32_t n_host, const int32_t *__restrict__ n_dev,
+                               const int8_t *__restrict__ hq, const float *__restrict__ hd,
+                               uint64_t q_slice, uint64_t d_slice, uint32_t n_ff, uint32_t n_embd,
+                               float *__restrict__ y) {
+    __shared__ uint16_t pair[256];
+    iq4nl_fill_pair_table(pair);
+    __syncthreads();
+    const uint32_t r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= n_embd) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t n = n_dev ? (uint32_t)*n_dev : n_host;
+    const uint32_t ng = n_ff >> 5;
+    float acc = 0.f;
+    for (uint32_t it = lane; it < n * ng; it += 32) {
+        const uint32_t e = it / ng, g = it - e * ng;
+        const uint8_t *blk = bd + (uint64_t)slots[e] * stride + ((uint64_t)r * ng + g) * 18u;
+        const int *qg = reinterpret_cast<const int *>(hq + (uint64_t)e * q_slice) + g * 8u;
+        int qv[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) qv[k] = qg[k];
+        const int I = iq4nl_block_idot(blk, pair, qv);
+        const float d = __half2float(__ushort_as_half((unsigned short)q4b_ld_u16(blk)));
+        const float dd = __fmul_rn(d, hd[(uint64_t)e * d_slice + g]);
+        acc = fmaf(__fmul_rn(wts[e], dd), (float)I, acc);
+    }
+    acc = q4b_warp_sum(acc);
+    if (lane == 0) y[r] += acc;
+}
+
 // IQ3_S rows times fp32 activations (shared-expert style GEMV), warp per row.
 template <bool TILED>
 __global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, uint32_t ncols,
@@ -510,11 +593,16 @@ __global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, u
 }
 
 // ------------------------------------------------------------------ host side
+// gate and up IQ3_S; down IQ3_S or IQ4_NL (the first of the other formats the engine's call
+// sites accept, src/q4_rocm.cu:4926-4944)
 bool shape_ok(uint32_t gt, uint32_t ut, uint32_t dt, uint32_t in_dim, uint32_t n_ff) {
-    return gt == Q4_T_IQ3_S && ut == Q4_T_IQ3_S && dt == Q4_T_IQ3_S && in_dim && n_ff &&
-           (in_dim % Q4B_QK) == 0 && (n_ff % Q4B_QK) == 0 && in_dim <= Q4B_XQ_MAXLEN &&
+    return gt == Q4_T_IQ3_S && ut == Q4_T_IQ3_S && (dt == Q4_T_IQ3_S || dt == Q4_T_IQ4_NL) && in_dim &&
+           n_ff && (in_dim % Q4B_QK) == 0 && (n_ff % Q4B_QK) == 0 && in_dim <= Q4B_XQ_MAXLEN &&
            n_ff <= Q4B_XQ_MAXLEN;
 }
+
+// A pack with an IQ4_NL part cannot live in a tiled arena (the tiling regroups IQ3_S bytes).
+bool place_ok(uint32_t dt, const void *base) { return dt != Q4_T_IQ4_NL || !q4b_ptr_tiled(base); }
 
 bool launch_quant8(const float *x, uint64_t xs, uint32_t slen, uint32_t ns, int8_t *q, float *d,
                    int32_t *bs, uint64_t q_slice, uint64_t d_slice, const int32_t *n_dev) {
@@ -531,7 +619,7 @@ bool launch_quant8(const float *x, uint64_t xs, uint32_t slen, uint32_t ns, int8
 bool moe_exec_tail(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
                    const float *d_wts, uint32_t n_host, const int32_t *d_n, uint64_t og,
                    uint64_t ou, uint64_t od, float *d_h, float *d_y, uint32_t n_ff,
-                   uint32_t in_dim, uint32_t n_embd) {
+                   uint32_t in_dim, uint32_t n_embd, uint32_t dt = Q4_T_IQ3_S) {
     Q4bState &s = g_q4b;
     const uint32_t ne = d_n ? 64u : n_host;
     const int8_t *xq = s.xq + (size_t)Q4B_X_SLICE * Q4B_XQ_MAXLEN;
@@ -550,7 +638,11 @@ bool moe_exec_tail(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
     if (!launch_quant8(d_h, n_ff, n_ff, ne, s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32,
                        d_n))
         return false;
-    if (tiled)
+    if (dt == Q4_T_IQ4_NL) {
+        moe_ya_iq4nl_k<<<(n_embd + 7) / 8, 256, 0, s.stream>>>(base + od, stride, d_slots, d_wts, n_host, d_n,
+                                                              s.xq, s.xd, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32,
+                                                              n_ff, n_embd, d_y);
+    } else if (tiled)
         moe_ya_k<true><<<(n_embd + 7) / 8, 256, 0, s.stream>>>(
             base + od, stride, d_slots, d_wts, n_host, d_n, s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN,
             Q4B_XQ_MAXLEN / 32, n_ff, n_embd, d_y);
@@ -592,10 +684,10 @@ extern "C" bool q4_hip_moe_exec_staged(const uint8_t *base, uint64_t stride, uin
     (void)d_h2;
     (void)d_down;
     if (!g_q4b.ok || !base || !d_x || !d_h || !d_y || !n_embd) return false;
-    if (!shape_ok(gt, ut, dt, in_dim, n_ff)) return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(dt, base)) return false;
     if (!quant_x(d_x, in_dim)) return false;
     return moe_exec_tail(base, stride, g_q4b.es_d, g_q4b.ew_d, 0, g_q4b.en_d, og, ou, od, d_h, d_y,
-                         n_ff, in_dim, n_embd);
+                         n_ff, in_dim, n_embd, dt);
 }
 
 extern "C" bool q4_hip_moe_exec(const uint8_t *base, uint64_t stride, const int32_t *slots,
@@ -607,7 +699,7 @@ extern "C" bool q4_hip_moe_exec(const uint8_t *base, uint64_t stride, const int3
     (void)d_down;
     if (!g_q4b.ok || !base || !slots || !wts || !n || n > 64 || !d_x || !d_h || !d_y || !n_embd)
         return false;
-    if (!shape_ok(gt, ut, dt, in_dim, n_ff)) return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(dt, base)) return false;
     // Like the reference (src/q4_rocm.cu:5441-5445) the list goes through mapped
     // host memory: the kernels fetch it themselves, no copy node on the stream.
     // The previous exec must have finished reading it.
@@ -617,7 +709,7 @@ extern "C" bool q4_hip_moe_exec(const uint8_t *base, uint64_t stride, const int3
     *g_q4b.en_h = (int32_t)n;
     if (!quant_x(d_x, in_dim)) return false;
     return moe_exec_tail(base, stride, g_q4b.es_d, g_q4b.ew_d, n, nullptr, og, ou, od, d_h, d_y,
-                         n_ff, in_dim, n_embd);
+                         n_ff, in_dim, n_embd, dt);
 }
 
 extern "C" bool q4_hip_moe_exec_dev(const uint8_t *base, uint64_t stride, const int32_t *d_es,
@@ -629,10 +721,10 @@ extern "C" bool q4_hip_moe_exec_dev(const uint8_t *base, uint64_t stride, const 
     (void)d_down;
     if (!g_q4b.ok || !base || !d_es || !d_ew || !d_nhit || !d_x || !d_h || !d_y || !n_embd)
         return false;
-    if (!shape_ok(gt, ut, dt, in_dim, n_ff)) return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(dt, base)) return false;
     if (!quant_x(d_x, in_dim)) return false;
     return moe_exec_tail(base, stride, d_es, d_ew, 0, d_nhit, og, ou, od, d_h, d_y, n_ff, in_dim,
-                         n_embd);
+                         n_embd, dt);
 }
 
 extern "C" bool q4_hip_softmax_topk_launch(const float *d_logits, uint32_t n, uint32_t k,
@@ -724,6 +816,23 @@ extern "C" bool q4_cuda_iq3s_dequant(const uint8_t *d_w, uint64_t nrows, uint64_
         iq3s_dequant_k<false><<<(unsigned)((ngr + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, ngr, d_out);
     g_q4b_launches++;
     return q4b_launch_ok("iq3s_dequant");
+}
+
+extern "C" bool q4_cuda_iq4nl_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out) {
+    if (!g_q4b.ok || !d_w || !d_out || nrows == 0 || ncols == 0 || (ncols % 32u)) return false;
+    const uint64_t nb = nrows * (ncols / 32u);
+    iq4nl_dequant_k<<<(unsigned)((nb + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, nb, d_out);
+    g_q4b_launches++;
+    return q4b_launch_ok("iq4nl_dequant");
+}
+extern "C" bool q4_cuda_iq4nl_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const int8_t *d_q,
+                                   int32_t *d_I) {
+    if (!g_q4b.ok || !d_w || !d_q || !d_I || nrows == 0 || ncols == 0 || (ncols % 32u)) return false;
+    const uint64_t n = nrows * (ncols / 32u);
+    iq4nl_idot_k<<<(unsigned)((n + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, nrows, (uint32_t)(ncols / 32u),
+                                                                     d_q, d_I);
+    g_q4b_launches++;
+    return q4b_launch_ok("iq4nl_idot");
 }
 
 extern "C" bool q4_cuda_iq3s_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols,

@@ -6,6 +6,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include "iq4nl_codes.h"
+
 #define Q4_T_F32 0u
 #define Q4_T_IQ3_S 21u
 

@@ -31,6 +31,34 @@ def iq3s_blocks(rng, n_blocks):
     return b
 
 
+IQ4NL_BLOCK = 18
+
+
+def iq4nl_blocks(rng, n_blocks):
+    """n_blocks random IQ4_NL blocks (fp16 d = |N(0,1)| * 2^-6, 16 bytes of 4-bit codes)."""
+    b = rng.integers(0, 256, size=(n_blocks, IQ4NL_BLOCK), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal(n_blocks)) * 2.0 ** -6).astype(np.float16)
+    b[:, 0:2] = d.view(np.uint8).reshape(n_blocks, 2)
+    return b
+
+
+def expert_pack_bytes_mixed(n_embd, n_ff):
+    """gate, up IQ3_S; down IQ4_NL (one of the mixes the engine's call sites accept,
+    src/q4_rocm.cu:4926-4944)."""
+    return 2 * n_ff * iq3s_row_bytes(n_embd) + n_embd * (n_ff // 32) * IQ4NL_BLOCK
+
+
+def expert_packs_mixed(rng, n, n_embd, n_ff):
+    """n packed experts with an IQ4_NL down projection -> uint8 [n, pack_bytes]."""
+    gu = 2 * n_ff * iq3s_row_bytes(n_embd)
+    dn = n_embd * (n_ff // 32) * IQ4NL_BLOCK
+    out = np.empty((n, gu + dn), np.uint8)
+    for e in range(n):
+        out[e, :gu] = iq3s_blocks(rng, gu // IQ3S_BLOCK).reshape(-1)
+        out[e, gu:] = iq4nl_blocks(rng, dn // IQ4NL_BLOCK).reshape(-1)
+    return out
+
+
 def expert_packs(rng, n, n_embd, n_ff):
     """n packed experts -> uint8 [n, pack_bytes]."""
     pb = expert_pack_bytes(n_embd, n_ff)

@@ -1,0 +1,94 @@
+"""IQ4_NL as the down projection's format (the first of the other routed-expert formats the engine's
+call sites accept, src/q4_rocm.cu:4926-4944): stage tests bit for bit, then the one-token exec calls
+on packs of IQ3_S gate/up + IQ4_NL down against the CPU oracle."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+IQ3_S, IQ4_NL = 21, 20
+
+
+def test_iq4nl_dequant_and_integer_dots_bit_exact(dev, pkg, oracle):
+    rng = np.random.default_rng(5)
+    nrows, n = 9, 512
+    w = pkg.synth.iq4nl_blocks(rng, nrows * n // 32).reshape(nrows, -1)
+    lib = dev.lib
+    d_w = dev.upload(w)
+    d_out = dev.malloc(nrows * n * 4)
+    assert lib.q4_cuda_iq4nl_dequant(d_w, nrows, n, d_out)
+    got = dev.download(d_out, (nrows, n), np.float32)
+    x = rng.standard_normal(n).astype(np.float32)
+    xq = oracle.quant8(x)
+    d_q = dev.upload(np.ascontiguousarray(xq["q"]))
+    d_I = dev.malloc(nrows * (n // 32) * 4)
+    assert lib.q4_cuda_iq4nl_idot(d_w, nrows, n, d_q, d_I)
+    I = dev.download(d_I, (nrows, n // 32), np.int32)
+    for r in range(nrows):
+        want = oracle.iq4nl_dequant_row(w[r], n)
+        assert np.array_equal(got[r].view(np.uint32), want.view(np.uint32))
+        assert np.array_equal(I[r], oracle.iq4nl_group_idot(w[r], xq, n))
+    assert not lib.q4_cuda_iq4nl_dequant(d_w, nrows, 500, d_out)     # not a multiple of 32
+
+
+@pytest.mark.parametrize("H,F", [(512, 256), (2048, 512)])
+def test_exec_with_iq4nl_down_matches_oracle(dev, pkg, oracle, H, F):
+    rng = np.random.default_rng(H)
+    n_slots, k = 6, 4
+    packs = pkg.synth.expert_packs_mixed(rng, n_slots, H, F)
+    pb = packs.shape[1]
+    assert pb == pkg.synth.expert_pack_bytes_mixed(H, F)
+    lib = dev.lib
+    lib.q4_cuda_set_tiled_default(0)          # mixed packs stay in the engine's byte order
+    try:
+        assert lib.q4_hip_experts_alloc_a(3, n_slots, pb)
+    finally:
+        lib.q4_cuda_set_tiled_default(1)
+    try:
+        for e in range(n_slots):
+            row = np.ascontiguousarray(packs[e])
+            assert lib.q4_hip_experts_put_a(3, e, row.ctypes.data, pb)
+        base, stride = lib.q4_hip_experts_base_a(3), lib.q4_hip_experts_stride_a(3)
+        rb = pkg.synth.iq3s_row_bytes(H)
+        og, ou, od = 0, F * rb, 2 * F * rb
+        assert lib.q4_hip_moe_tok_ok(IQ3_S, IQ3_S, IQ4_NL, H, F)
+        assert not lib.q4_hip_moe_tok_ok(IQ4_NL, IQ3_S, IQ3_S, H, F)      # gate/up stay IQ3_S
+        x = rng.standard_normal(H).astype(np.float32)
+        slots = rng.choice(n_slots, k, replace=False).astype(np.int32)
+        wts = rng.random(k).astype(np.float32)
+        d_x, d_y, d_h = dev.upload(x), dev.malloc(H * 4), dev.malloc(64 * F * 4)
+        assert lib.q4_hip_fill(d_y, 0.0, H)
+        assert lib.q4_hip_moe_exec(base, stride, slots.ctypes.data, wts.ctypes.data, k, IQ3_S, og, IQ3_S, ou,
+                                   IQ4_NL, od, d_x, d_h, None, None, d_y, F, H, H)
+        y = dev.download(d_y, (H,), np.float32)
+        want = oracle.expert_job_t([packs[s] for s in slots], wts, x, H, F, IQ4_NL)
+        assert np.linalg.norm(y - want) / np.linalg.norm(want) <= 1e-3
+        # device-side list form, same result bit for bit
+        assert lib.q4_hip_fill(d_y, 0.0, H)
+        assert lib.q4_hip_moe_exec_dev(base, stride, dev.upload(slots), dev.upload(wts),
+                                       dev.upload(np.array([k], np.int32)), IQ3_S, og, IQ3_S, ou, IQ4_NL, od,
+                                       d_x, d_h, None, None, d_y, F, H, H)
+        y2 = dev.download(d_y, (H,), np.float32)
+        assert np.array_equal(y2.view(np.uint32), y.view(np.uint32))
+        assert lib.q4_cuda_device_error() == 0
+    finally:
+        lib.q4_hip_experts_free_a(3)
+
+
+def test_iq4nl_down_refused_on_a_tiled_arena(dev, pkg):
+    """The tiled arena format regroups IQ3_S bytes; a pack with an IQ4_NL part in it is refused
+    before anything is enqueued."""
+    H, F = 2048, 512
+    lib = dev.lib
+    pb = pkg.synth.expert_pack_bytes(H, F)          # a size the tiling accepts
+    assert lib.q4_hip_experts_alloc_a(3, 2, pb)
+    try:
+        assert lib.q4_cuda_experts_tiled_a(3) == 1
+        base, stride = lib.q4_hip_experts_base_a(3), lib.q4_hip_experts_stride_a(3)
+        slots, wts = np.array([0], np.int32), np.array([1.0], np.float32)
+        d_x, d_y, d_h = dev.malloc(H * 4), dev.malloc(H * 4), dev.malloc(64 * F * 4)
+        n0 = lib.q4_cuda_launch_count()
+        assert not lib.q4_hip_moe_exec(base, stride, slots.ctypes.data, wts.ctypes.data, 1, IQ3_S, 0, IQ3_S, 1,
+                                       IQ4_NL, 2, d_x, d_h, None, None, d_y, F, H, H)
+        assert lib.q4_cuda_launch_count() == n0
+    finally:
+        lib.q4_hip_experts_free_a(3)

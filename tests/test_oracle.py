@@ -173,3 +173,47 @@ def test_against_compiled_reference(oracle, reference):
         a = np.float32(oracle.dot8(blocks[r], xq, H))
         assert _bits(a) == _bits(np.float32(reference.dot8(blocks[r], xq, H)))
         assert _bits(a) == _bits(np.float32(reference.dot8(blocks[r], xq, H, avx2=True)))
+
+
+# ---- IQ4_NL (type 20): a routed expert's down projection may use it ----
+def test_iq4nl_oracle_pinned_to_reference(pkg, oracle, reference):
+    """Dequantisation, the per-block integer dots and the Q8-A row dot of the restatement against the
+    reference's own code (src/q4_quant.c:270-290, src/q4_cpuexp.c:977-996) on seeded blocks: bit-exact."""
+    if reference is None:
+        pytest.skip("reference CPU path not built here")
+    rng = np.random.default_rng(2024)
+    n = 512
+    rows = pkg.synth.iq4nl_blocks(rng, 6 * n // 32).reshape(6, -1)
+    x = rng.standard_normal(n).astype(np.float32)
+    xq = oracle.quant8(x)
+    for row in rows:
+        a, b = oracle.iq4nl_dequant_row(row, n), reference.dequant_row_t(20, row, n)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+        got = oracle.iq4nl_dot8(row, xq, n)
+        for want in (reference.dot8_t(20, row, xq, n, avx2_iq4nl=True), reference.dot8_t(20, row, xq, n)):
+            assert np.float32(got).view(np.uint32) == np.float32(want).view(np.uint32)
+        # integer parts: table value x q summed per block, against a direct numpy evaluation
+        I = oracle.iq4nl_group_idot(row, xq, n)
+        w = np.rint(oracle.iq4nl_dequant_row(np.concatenate(
+            [np.concatenate([np.array([0x00, 0x3c], np.uint8), blk[2:]]) for blk in row.reshape(-1, 18)]), n))
+        want_I = (w.reshape(-1, 32).astype(np.int64) * xq["q"].astype(np.int64)).sum(1)
+        assert np.array_equal(I, want_I)
+
+
+def test_expert_job_with_iq4nl_down_matches_reference(pkg, oracle, reference):
+    """gate/up IQ3_S, down IQ4_NL through the reference's worker pool (q4_cpuex_dispatch2) vs the
+    restatement; y is summed by the pool in worker order, hence the last-bit tolerance."""
+    if reference is None:
+        pytest.skip("reference CPU path not built here")
+    H, F, k = 512, 256, 3
+    rng = np.random.default_rng(77)
+    packs = pkg.synth.expert_packs_mixed(rng, k, H, F)
+    x = rng.standard_normal(H).astype(np.float32)
+    wts = rng.random(k).astype(np.float32)
+    reference.set_down_type(20)
+    try:
+        want = reference.expert_job(list(packs), np.arange(k, dtype=np.int32), wts, x, H, F)
+    finally:
+        reference.set_down_type(21)
+    got = oracle.expert_job_t(list(packs), wts, x, H, F, 20)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < 2e-6
