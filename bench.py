@@ -196,17 +196,25 @@ class Workload:
             raise RuntimeError("graph launch failed")
 
     def run_e2e(self, steps, first=0):
+        """Per step: the token's row is written into pinned host memory, the layer runs through the
+        host-buffer call (arguments bound once per layer), the 8 KB result is read on the host."""
         import ctypes
         lib = self.lib
+        if not hasattr(self, "plans"):
+            self.plans = []
+            for l in range(self.n_layers):
+                p = lib.q4_cuda_decode_plan(self.layer_base(l), self.stride, self.og, self.ou, self.od,
+                                            N_EXPERT, self.d_norm + l * N_EMBD * 4, EPS,
+                                            self.d_router + l * ROUTER_BYTES, N_EXPERT, TOPK, N_EMBD, N_FF)
+                if not p:
+                    raise RuntimeError("q4_cuda_decode_plan refused")
+                self.plans.append(p)
+        run, h_x, h_y = lib.q4_cuda_decode_plan_host, self.h_x, self.h_y
         for i in range(first, first + steps):
-            l = i % self.n_layers
-            ctypes.memmove(self.h_x, self.x_host[i % self.n_x].ctypes.data, N_EMBD * 4)
-            ok = lib.q4_cuda_moe_decode_host(
-                self.layer_base(l), self.stride, self.og, self.ou, self.od, N_EXPERT, self.h_x,
-                self.d_norm + l * N_EMBD * 4, EPS, self.d_router + l * ROUTER_BYTES, N_EXPERT,
-                TOPK, N_EMBD, N_FF, self.h_y)
+            ctypes.memmove(h_x, self.x_host[i % self.n_x].ctypes.data, N_EMBD * 4)
+            ok = run(self.plans[i % self.n_layers], h_x, h_y)
             if not ok:
-                raise RuntimeError("q4_cuda_moe_decode_host refused")
+                raise RuntimeError("q4_cuda_decode_plan_host refused")
             ctypes.memmove(self.y_out.ctypes.data, self.h_y, N_EMBD * 4)   # the step's result, read on the host
 
     def host_layers(self, n):

@@ -290,6 +290,16 @@ bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, uint64_t og, 
                              const float *d_norm_w, float eps, const float *d_router,
                              uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
                              float *h_y);
+/* A layer's arguments bound once: the per-token calls then take only the token's buffers
+ * (an engine decodes thousands of tokens through the same layer).  plan() returns NULL for a
+ * shape the path does not take; plan_dev = q4_cuda_moe_decode, plan_host =
+ * q4_cuda_moe_decode_host with the bound arguments. */
+void *q4_cuda_decode_plan(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou, uint64_t od,
+                          int32_t shared_slot, const float *d_norm_w, float eps, const float *d_router,
+                          uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff);
+bool q4_cuda_decode_plan_dev(void *plan, const float *d_x, float *d_y, int32_t *d_ids, float *d_wts);
+bool q4_cuda_decode_plan_host(void *plan, const float *h_x, float *h_y);
+void q4_cuda_decode_plan_free(void *plan);
 
 /* Diagnostics of the single-kernel layer path: when enabled, the kernel records
  * the GPU's nanosecond timer at its phase boundaries; read copies the last

@@ -105,6 +105,10 @@ SIGNATURES = {
     "q4_cuda_experts_get_a": (b, [C.c_int, u32, vp, u64]),
     "q4_cuda_moe_decode_host": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32,
                                     u32, vp]),
+    "q4_cuda_decode_plan": (vp, [vp, u64, u64, u64, u64, i32, vp, f32, vp, u32, u32, u32, u32]),
+    "q4_cuda_decode_plan_dev": (b, [vp, vp, vp, vp, vp]),
+    "q4_cuda_decode_plan_host": (b, [vp, vp, vp]),
+    "q4_cuda_decode_plan_free": (None, [vp]),
     "q4_cuda_fused_profile_enable": (b, [C.c_int]),
     "q4_cuda_fused_profile_read": (u32, [vp, u32]),
     "q4_cuda_mmq_swiglu_quantize": (b, [vp, vp, u64, u64]),

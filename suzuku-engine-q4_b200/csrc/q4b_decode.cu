@@ -16,7 +16,7 @@ extern std::atomic<uint64_t> g_q4b_launches;
 bool q4b_ptr_tiled(const void *p);
 bool q4b_moe_decode_fused(const uint8_t *, uint64_t, uint64_t, uint64_t, uint64_t, int32_t, const float *,
                           const float *, float, const float *, uint32_t, uint32_t, uint32_t, uint32_t,
-                          float *, int32_t *, float *, float *, uint32_t *, uint32_t);
+                          float *, int32_t *, float *, float *, uint32_t *, uint32_t, const float *);
 
 #define Q4B_X_SLICE 64u  // scratch slice that holds the quantised input row
 
@@ -869,7 +869,7 @@ extern "C" bool q4_cuda_moe_decode(const uint8_t *base, uint64_t stride, uint64_
     }
     if (fused_on && q4b_moe_decode_fused(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps,
                                          d_router, n_expert, topk, n_embd, n_ff, d_y, d_ids, d_wts,
-                                         nullptr, nullptr, 0))
+                                         nullptr, nullptr, 0, nullptr))
         return true;
     int8_t *xq = s.xq + (size_t)Q4B_X_SLICE * Q4B_XQ_MAXLEN;
     float *xd = s.xd + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
@@ -912,7 +912,6 @@ extern "C" bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, ui
     // staging rows: the last token row of the norm scratch (in) and the row before it (out)
     float *d_x = s.xn + (size_t)(Q4B_MAX_TOK - 1) * Q4B_XQ_MAXLEN;
     float *d_y = s.xn + (size_t)(Q4B_MAX_TOK - 2) * Q4B_XQ_MAXLEN;
-    Q4B_CHECK(cudaMemcpyAsync(d_x, h_x, (size_t)n_embd * 4, cudaMemcpyHostToDevice, s.stream));
     // Fast hand-off: when the result buffer is pinned, mapped host memory (q4_hip_host_alloc_coh)
     // the persistent kernel's last CTA writes y straight into it and raises a mapped flag the
     // host spins on -- no copy node, no stream wake-up.  Anything else takes copy + sync.
@@ -942,9 +941,10 @@ extern "C" bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, ui
     if (y_dev_alias && shape_ok(Q4_T_IQ3_S, Q4_T_IQ3_S, Q4_T_IQ3_S, n_embd, n_ff) && n_expert != 0 &&
         topk != 0 && topk <= n_expert) {
         const uint32_t epoch = ++s.flag_epoch ? s.flag_epoch : ++s.flag_epoch;   // never 0
+        // the hidden row goes in with the launch (kernel parameter block): no copy node either
         if (q4b_moe_decode_fused(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps, d_router,
                                  n_expert, topk, n_embd, n_ff, d_y, nullptr, nullptr, y_dev_alias,
-                                 s.flag_d, epoch)) {
+                                 s.flag_d, epoch, h_x)) {
             volatile uint32_t *f = s.flag_h;
             for (uint64_t spins = 0; *f != epoch; spins++) {
                 if (spins > 200000000ull) {        // far beyond any launch: let the stream say why
@@ -959,12 +959,48 @@ extern "C" bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, ui
             return true;
         }
     }
+    Q4B_CHECK(cudaMemcpyAsync(d_x, h_x, (size_t)n_embd * 4, cudaMemcpyHostToDevice, s.stream));
     if (!q4_cuda_moe_decode(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps, d_router,
                             n_expert, topk, n_embd, n_ff, d_y, nullptr, nullptr))
         return false;
     Q4B_CHECK(cudaMemcpyAsync(h_y, d_y, (size_t)n_embd * 4, cudaMemcpyDeviceToHost, s.stream));
     Q4B_CHECK(cudaStreamSynchronize(s.stream));
     return true;
+}
+
+// ---- a layer's arguments bound once (the per-token call then takes the two buffers only) ----
+struct Q4bDecodePlan {
+    const uint8_t *base;
+    uint64_t stride, og, ou, od;
+    int32_t shared_slot;
+    const float *d_norm_w, *d_router;
+    float eps;
+    uint32_t n_expert, topk, n_embd, n_ff;
+};
+extern "C" void *q4_cuda_decode_plan(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou,
+                                     uint64_t od, int32_t shared_slot, const float *d_norm_w, float eps,
+                                     const float *d_router, uint32_t n_expert, uint32_t topk,
+                                     uint32_t n_embd, uint32_t n_ff) {
+    if (!g_q4b.ok || !base || !d_router) return nullptr;
+    if (!shape_ok(Q4_T_IQ3_S, Q4_T_IQ3_S, Q4_T_IQ3_S, n_embd, n_ff)) return nullptr;
+    if (n_expert == 0 || n_expert > 1024 || topk == 0 || topk > 63 || topk > n_expert) return nullptr;
+    Q4bDecodePlan *p = new Q4bDecodePlan{base, stride, og, ou, od, shared_slot, d_norm_w, d_router,
+                                         eps, n_expert, topk, n_embd, n_ff};
+    return p;
+}
+extern "C" void q4_cuda_decode_plan_free(void *plan) { delete (Q4bDecodePlan *)plan; }
+extern "C" bool q4_cuda_decode_plan_dev(void *plan, const float *d_x, float *d_y, int32_t *d_ids,
+                                        float *d_wts) {
+    const Q4bDecodePlan *p = (const Q4bDecodePlan *)plan;
+    return p && q4_cuda_moe_decode(p->base, p->stride, p->og, p->ou, p->od, p->shared_slot, d_x, p->d_norm_w,
+                                   p->eps, p->d_router, p->n_expert, p->topk, p->n_embd, p->n_ff, d_y, d_ids,
+                                   d_wts);
+}
+extern "C" bool q4_cuda_decode_plan_host(void *plan, const float *h_x, float *h_y) {
+    const Q4bDecodePlan *p = (const Q4bDecodePlan *)plan;
+    return p && q4_cuda_moe_decode_host(p->base, p->stride, p->og, p->ou, p->od, p->shared_slot, h_x,
+                                        p->d_norm_w, p->eps, p->d_router, p->n_expert, p->topk, p->n_embd,
+                                        p->n_ff, h_y);
 }
 
 // ---- helpers shared with the many-token path (q4b_grouped.cu) ----

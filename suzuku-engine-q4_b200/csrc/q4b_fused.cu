@@ -286,7 +286,9 @@ __device__ __forceinline__ void route_block(const Args &a, Small &S, uint32_t ti
     }
 }
 
-__global__ void __launch_bounds__(NT, 1) moe_decode_fused_k(const Args a) {
+// The kernel body; xrow is the token's hidden row as H/4 float4: device memory for the
+// device-pointer call, the kernel's own parameter block for the host-buffer call.
+__device__ __forceinline__ void fused_body(const Args &a, const float4 *xrow) {
     // used directly (no integer round trip), so that the compiler keeps these as
     // shared-space accesses; dynamic shared memory starts on the declared alignment
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -318,7 +320,7 @@ __global__ void __launch_bounds__(NT, 1) moe_decode_fused_k(const Args a) {
     float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), wv = make_float4(1.f, 1.f, 1.f, 1.f);
     uint32_t code = 0;
     if (tid < H / 4) {
-        xv = reinterpret_cast<const float4 *>(a.x)[tid];
+        xv = xrow[tid];
         if (a.norm_w) wv = reinterpret_cast<const float4 *>(a.norm_w)[tid];
         code = a.codes[tid];
     }
@@ -610,6 +612,19 @@ __global__ void __launch_bounds__(NT, 1) moe_decode_fused_k(const Args a) {
     }
 }
 
+__global__ void __launch_bounds__(NT, 1) moe_decode_fused_k(const Args a) {
+    fused_body(a, reinterpret_cast<const float4 *>(a.x));
+}
+
+// The host-buffer form: the 8 KB hidden row travels inside the launch's parameter block, so
+// the call needs no separate host-to-device copy ahead of the kernel.
+struct XRow {
+    float4 v[H / 4];
+};
+__global__ void __launch_bounds__(NT, 1) moe_decode_fused_xp_k(const Args a, const __grid_constant__ XRow xr) {
+    fused_body(a, xr.v);
+}
+
 }  // namespace fused
 
 // Scratch of the fused kernel (allocated once, by init / scratch_warm).
@@ -642,12 +657,13 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
                           const float *d_norm_w, float eps, const float *d_router,
                           uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
                           float *d_y, int32_t *d_ids, float *d_wts, float *y_host_dev,
-                          uint32_t *flag_host_dev, uint32_t flag_val) {
+                          uint32_t *flag_host_dev, uint32_t flag_val, const float *h_x_param) {
     using namespace fused;
     Q4bState &s = g_q4b;
     if (n_embd != H || n_ff != F || n_expert > NT || topk > 32) return false;
     if (!q4b_ptr_tiled(base) || (og % 16) || (ou % 16) || (od % 16) || (stride % 16)) return false;
-    if (((uintptr_t)d_router % 16) || ((uintptr_t)d_x % 16) || (d_norm_w && ((uintptr_t)d_norm_w % 16)))
+    if (((uintptr_t)d_router % 16) || (!h_x_param && ((uintptr_t)d_x % 16)) ||
+        (d_norm_w && ((uintptr_t)d_norm_w % 16)))
         return false;
     if (!fused_scratch()) return false;
     const uint32_t ncta = (uint32_t)s.n_sm;
@@ -696,6 +712,8 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
     if (!g_f_attr_set) {
         Q4B_CHECK(cudaFuncSetAttribute(moe_decode_fused_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        227 * 1024));
+        Q4B_CHECK(cudaFuncSetAttribute(moe_decode_fused_xp_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       227 * 1024));
         g_f_attr_set = true;
     }
     cudaLaunchConfig_t cfg = {};
@@ -708,7 +726,15 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
     at[0].val.cooperative = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, moe_decode_fused_k, a) != cudaSuccess) {
+    cudaError_t le;
+    if (h_x_param) {
+        static XRow xr;   // filled and consumed inside this call: the launch copies its parameters
+        memcpy(xr.v, h_x_param, sizeof(xr.v));
+        le = cudaLaunchKernelEx(&cfg, moe_decode_fused_xp_k, a, xr);
+    } else {
+        le = cudaLaunchKernelEx(&cfg, moe_decode_fused_k, a);
+    }
+    if (le != cudaSuccess) {
         fprintf(stderr, "q4cuda: fused decode launch failed: %s\n", cudaGetErrorString(cudaGetLastError()));
         return false;
     }

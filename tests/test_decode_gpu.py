@@ -300,6 +300,22 @@ def test_decode_host_buffers_match_device_call(dev, pkg):
                                                layer.shared_slot, x.ctypes.data, layer.d_norm, 1e-6,
                                                layer.d_router, E, K, H, F, y_page.ctypes.data)
             assert np.array_equal(y_page.view(np.uint32), want.view(np.uint32))
+        # the same layer with its arguments bound once
+        plan = lib.q4_cuda_decode_plan(layer.base, layer.stride, layer.og, layer.ou, layer.od,
+                                       layer.shared_slot, layer.d_norm, 1e-6, layer.d_router, E, K, H, F)
+        assert plan
+        want, _, _ = layer.decode(xs[1])
+        ctypes.memmove(h_x, xs[1].ctypes.data, H * 4)
+        ctypes.memset(h_y, 0, H * 4)
+        assert lib.q4_cuda_decode_plan_host(plan, h_x, h_y)
+        got = np.ctypeslib.as_array(ctypes.cast(h_y, ctypes.POINTER(ctypes.c_float)), (H,)).copy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        d_y2 = dev.malloc(H * 4)
+        assert lib.q4_cuda_decode_plan_dev(plan, dev.upload(xs[1]), d_y2, None, None)
+        assert np.array_equal(dev.download(d_y2, (H,), np.float32).view(np.uint32), want.view(np.uint32))
+        lib.q4_cuda_decode_plan_free(plan)
+        assert not lib.q4_cuda_decode_plan(layer.base, layer.stride, layer.og, layer.ou, layer.od,
+                                           layer.shared_slot, layer.d_norm, 1e-6, layer.d_router, E, 0, H, F)
         lib.q4_hip_host_free_coh(h_x)
         lib.q4_hip_host_free_coh(h_y)
         assert lib.q4_cuda_device_error() == 0
