@@ -2,6 +2,7 @@
 #include "q4_moe_b200.h"
 
 #include <stddef.h>
+#include <string.h>
 
 #include "../../include/q4cuda.h"
 
@@ -29,6 +30,43 @@ bool q4b_moe_layer_load(q4b_moe_layer *L, int arena, const uint8_t *packs, const
     L->arena = arena;
     L->first_slot = 0;
     L->shared_slot = shared ? (int32_t)n_expert : -1;
+    L->n_embd = n_embd;
+    L->n_ff = n_ff;
+    L->n_expert = n_expert;
+    q4b_moe_layer_offsets(L);
+    return true;
+}
+
+bool q4b_moe_layer_load_stacked(q4b_moe_layer *L, int arena, const uint8_t *gate_exps,
+                                const uint8_t *up_exps, const uint8_t *down_exps,
+                                const uint8_t *sh_gate, const uint8_t *sh_up, const uint8_t *sh_down,
+                                uint32_t n_expert, uint32_t n_embd, uint32_t n_ff) {
+    if (!L || !gate_exps || !up_exps || !down_exps || n_expert == 0 || (n_embd % 256u) || (n_ff % 256u))
+        return false;
+    const bool sh = sh_gate && sh_up && sh_down;
+    if (!sh && (sh_gate || sh_up || sh_down)) return false;
+    const uint64_t sg = (uint64_t)n_ff * q4b_iq3s_row_bytes(n_embd), su = sg;
+    const uint64_t sd = (uint64_t)n_embd * q4b_iq3s_row_bytes(n_ff), pb = sg + su + sd;
+    if (!q4_hip_experts_alloc_a(arena, n_expert + (sh ? 1u : 0u), pb)) return false;
+    /* two staging packs: one is filled while the other's upload is in flight */
+    uint8_t *stage = (uint8_t *)q4_hip_host_alloc_coh(2 * pb);
+    if (!stage) return false;
+    bool ok = true;
+    for (uint32_t e = 0; ok && e < n_expert + (sh ? 1u : 0u); e++) {
+        uint8_t *p = stage + (uint64_t)(e & 1u) * pb;
+        if (e >= 2 && (e & 1u) == 0) q4_hip_copy_wait();   /* both staging packs may be in flight */
+        const bool shared = e == n_expert;
+        memcpy(p, shared ? sh_gate : gate_exps + (uint64_t)e * sg, sg);
+        memcpy(p + sg, shared ? sh_up : up_exps + (uint64_t)e * su, su);
+        memcpy(p + sg + su, shared ? sh_down : down_exps + (uint64_t)e * sd, sd);
+        ok = q4_hip_experts_put_async_a(arena, e, p, pb);
+    }
+    q4_hip_copy_wait();
+    q4_hip_host_free_coh(stage);
+    if (!ok) return false;
+    L->arena = arena;
+    L->first_slot = 0;
+    L->shared_slot = sh ? (int32_t)n_expert : -1;
     L->n_embd = n_embd;
     L->n_ff = n_ff;
     L->n_expert = n_expert;

@@ -39,6 +39,16 @@ void q4b_moe_layer_offsets(q4b_moe_layer *L);
 bool q4b_moe_layer_load(q4b_moe_layer *L, int arena, const uint8_t *packs, const uint8_t *shared,
                         uint32_t n_expert, uint32_t n_embd, uint32_t n_ff);
 
+/* The same from the tensors as a model file stores them: ffn_gate_exps / ffn_up_exps /
+ * ffn_down_exps hold all experts' matrices of one kind back to back (expert e at e * slice);
+ * the pack of expert e is its gate, up and down slices in that order
+ * (src/q4_expert.c:962-993).  sh_* are the shared expert's three matrices (all NULL = none).
+ * Packs are assembled in page-locked staging memory and queued on the copy stream. */
+bool q4b_moe_layer_load_stacked(q4b_moe_layer *L, int arena, const uint8_t *gate_exps,
+                                const uint8_t *up_exps, const uint8_t *down_exps,
+                                const uint8_t *sh_gate, const uint8_t *sh_up, const uint8_t *sh_down,
+                                uint32_t n_expert, uint32_t n_embd, uint32_t n_ff);
+
 /* Scratch floats q4_moe_layer_dev needs at d_ws (src/q4_moe.c:2062-2065 sizes it the same way). */
 uint64_t q4_moe_layer_dev_ws_floats(const q4b_moe_layer *L);
 

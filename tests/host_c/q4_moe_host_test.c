@@ -128,6 +128,34 @@ int main(void) {
     CHECK(q4_moe_layer_dev_n(&L, d_x, d_y, T, d_wsn, wsn), "q4_moe_layer_dev_n");
     CHECK(q4_hip_d2h(got_b, d_y, sizeof(float) * T * H), "download");
     for (int t = 0; t < T; t++) CHECK(rel_l2(got_b + t * H, want + t * H, H) <= 1e-3, "batched call vs oracle");
+    /* (d) the loader from stacked tensors (one tensor per matrix kind, experts back to back)
+     * builds the same packs: read them back in the engine's byte order and compare */
+    {
+        const uint64_t sg = (uint64_t)F * q4b_iq3s_row_bytes(H), sd = (uint64_t)H * q4b_iq3s_row_bytes(F);
+        uint8_t *gate = malloc((size_t)E * sg), *up = malloc((size_t)E * sg), *down = malloc((size_t)E * sd);
+        uint8_t *back = malloc((size_t)pb);
+        CHECK(gate && up && down && back, "host allocation");
+        for (int e = 0; e < E; e++) {
+            memcpy(gate + (uint64_t)e * sg, packs + (uint64_t)e * pb, sg);
+            memcpy(up + (uint64_t)e * sg, packs + (uint64_t)e * pb + sg, sg);
+            memcpy(down + (uint64_t)e * sd, packs + (uint64_t)e * pb + 2 * sg, sd);
+        }
+        const uint8_t *shp = packs + (uint64_t)E * pb;
+        q4b_moe_layer L2;
+        memset(&L2, 0, sizeof L2);
+        CHECK(q4b_moe_layer_load_stacked(&L2, 1, gate, up, down, shp, shp + sg, shp + 2 * sg, E, H, F),
+              "stacked load");
+        CHECK(L2.shared_slot == E && L2.ou == sg && L2.od == 2 * sg, "stacked layer geometry");
+        for (int e = 0; e <= E; e += 7) {
+            CHECK(q4_cuda_experts_get_a(1, (uint32_t)e, back, pb), "pack read-back");
+            CHECK(memcmp(back, packs + (uint64_t)e * pb, pb) == 0, "stacked loader built a different pack");
+        }
+        CHECK(q4_cuda_experts_get_a(1, E, back, pb) && memcmp(back, shp, pb) == 0, "shared pack differs");
+        CHECK(!q4b_moe_layer_load_stacked(&L2, 2, gate, up, down, shp, NULL, NULL, E, H, F),
+              "half-given shared expert must be refused");
+        q4_hip_experts_free_a(1);
+        free(gate), free(up), free(down), free(back);
+    }
     /* refusals: nothing is enqueued for a shape the path does not take */
     q4b_moe_layer bad = L;
     bad.topk = 0;
