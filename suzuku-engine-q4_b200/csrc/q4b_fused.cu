@@ -604,10 +604,8 @@ __device__ __forceinline__ void fused_body(const Args &a, const float4 *xrow) {
                 reinterpret_cast<float4 *>(a.y_host)[i] = __ldcg(reinterpret_cast<const float4 *>(a.y) + i);
             __threadfence_system();
             __syncthreads();
-            if (tid == 0) {
-                *a.flag_host = a.flag_val;
-                __threadfence_system();
-            }
+            if (tid == 0) *a.flag_host = a.flag_val;   // every writer fenced at system scope above
+            stamp(a, 15);   // in the last CTA only: when the flag was written
         }
     }
 }
