@@ -20,8 +20,8 @@
  *  - there is no CPU fallback: without a usable sm_100 GPU q4_hip_init() returns
  *    false and every other entry point refuses.
  *
- * Expert tensors are IQ3_S (type id 21); the one-token exec calls also take IQ4_NL (type id
- * 20) as the down projection's type, for packs kept in an arena in the engine's byte order.
+ * Expert tensors are IQ3_S (type id 21); the one-token exec calls also take IQ4_NL (20) and
+ * IQ4_XS (23) for gate+up and/or down, for packs kept in an arena in the engine's byte order.
  * Router tensors are F32 (type id 0).  q4_hip_moe_tok_ok() and q4_mmq_supported() answer
  * for a given shape and type mix.
  */
@@ -39,7 +39,8 @@ extern "C" {
 /* ggml type ids used on this path (src/q4.h:20-39). */
 #define Q4_T_F32 0u
 #define Q4_T_IQ3_S 21u
-#define Q4_T_IQ4_NL 20u   /* accepted as the down projection's type (dt) of the one-token exec calls */
+#define Q4_T_IQ4_NL 20u   /* these two: accepted by the one-token exec calls as the type of gate+up */
+#define Q4_T_IQ4_XS 23u   /* (gt == ut) and/or of down (dt) */
 
 /* ---------------- lifecycle and memory (src/q4.h:1029-1031,1397-1400,1511-1512,
  * 1233-1235,1232,1359) ---------------- */
@@ -206,6 +207,11 @@ bool q4_cuda_quant8(const float *d_x, uint64_t n, int8_t *d_q, float *d_d, int32
 bool q4_cuda_iq4nl_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out);
 bool q4_cuda_iq4nl_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const int8_t *d_q,
                         int32_t *d_I);
+/* ... and by type id, 20 (IQ4_NL) or 23 (IQ4_XS, 136-byte super-blocks; src/q4_quant.c:455-480,
+ * src/q4_cpuexp.c:945-975). */
+bool q4_cuda_iq4_dequant(uint32_t type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out);
+bool q4_cuda_iq4_idot(uint32_t type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                      const int8_t *d_q, int32_t *d_I);
 bool q4_cuda_iq3s_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out);
 bool q4_cuda_iq3s_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const int8_t *d_q,
                        int32_t *d_I);

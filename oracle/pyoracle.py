@@ -53,6 +53,8 @@ class Oracle:
         L.q4o_silu.argtypes = [C.c_float]
         L.q4o_iq4nl_dot8.restype = C.c_float
         L.q4o_iq4nl_dot8.argtypes = [_u8p, C.c_void_p, C.c_uint64]
+        L.q4o_dot8_t.restype = C.c_float
+        L.q4o_dot8_t.argtypes = [C.c_uint32, _u8p, C.c_void_p, C.c_uint64]
 
     def grid(self):
         return np.array([self.lib.q4o_iq3s_grid(i) for i in range(512)], dtype=np.uint32)
@@ -110,15 +112,35 @@ class Oracle:
         row = _u8(row)
         return float(self.lib.q4o_iq4nl_dot8(_p(row, _u8p), C.c_void_p(xq.ctypes.data), C.c_uint64(n)))
 
-    def expert_job_t(self, packs, wts, x, n_embd, n_ff, down_type):
+    def expert_job_t(self, packs, wts, x, n_embd, n_ff, down_type, gu_type=21):
         packs = [_u8(p) for p in packs]
         arr = (C.c_void_p * len(packs))(*[p.ctypes.data for p in packs])
         wts = _f32(wts)
         x = _f32(x)
         y = np.zeros(n_embd, np.float32)
         self.lib.q4o_expert_job_t(arr, _p(wts, _f32p), C.c_uint32(len(packs)), _p(x, _f32p),
-                                  C.c_uint32(n_embd), C.c_uint32(n_ff), C.c_uint32(down_type), _p(y, _f32p))
+                                  C.c_uint32(n_embd), C.c_uint32(n_ff), C.c_uint32(gu_type),
+                                  C.c_uint32(down_type), _p(y, _f32p))
         return y
+
+    # ---- IQ4_XS ----
+    def iq4xs_dequant_row(self, row, n):
+        row = _u8(row)
+        out = np.zeros(n, np.float32)
+        self.lib.q4o_iq4xs_dequant_row(_p(row, _u8p), C.c_uint64(n), _p(out, _f32p))
+        return out
+
+    def iq4xs_group_idot(self, row, xq, n):
+        row = _u8(row)
+        out = np.zeros(n // 32, np.int32)
+        self.lib.q4o_iq4xs_group_idot(_p(row, _u8p), C.c_void_p(xq.ctypes.data), C.c_uint64(n),
+                                      _p(out, _i32p))
+        return out
+
+    def dot8_t(self, type_id, row, xq, n):
+        row = _u8(row)
+        return float(self.lib.q4o_dot8_t(C.c_uint32(type_id), _p(row, _u8p), C.c_void_p(xq.ctypes.data),
+                                         C.c_uint64(n)))
 
     def matvec8(self, mat, rows, xq, n):
         """rows x n IQ3_S matrix times one quantised activation vector."""
@@ -229,6 +251,8 @@ class Reference:
         L.q4ref_dot8_t.argtypes = [C.c_uint32, _u8p, C.c_void_p, C.c_uint64]
         L.q4ref_dot8_avx2_iq4nl.restype = C.c_float
         L.q4ref_dot8_avx2_iq4nl.argtypes = [_u8p, C.c_void_p, C.c_uint64]
+        L.q4ref_dot8_avx2_iq4xs.restype = C.c_float
+        L.q4ref_dot8_avx2_iq4xs.argtypes = [_u8p, C.c_void_p, C.c_uint64]
         L.q4ref_time_jobs.restype = C.c_double
         L.q4ref_time_layers.restype = C.c_double
 
@@ -247,16 +271,22 @@ class Reference:
         """Type of the down projection of the packs handed to expert_job (21 IQ3_S, 20 IQ4_NL)."""
         self.lib.q4ref_set_down_type(C.c_uint32(type_id))
 
+    def set_gu_type(self, type_id):
+        """Type of the gate and up projections of the packs handed to expert_job."""
+        self.lib.q4ref_set_gu_type(C.c_uint32(type_id))
+
     def dequant_row_t(self, type_id, row, n):
         row = _u8(row)
         out = np.zeros(n, np.float32)
         assert self.lib.q4ref_dequant_row_t(C.c_uint32(type_id), _p(row, _u8p), C.c_uint64(n), _p(out, _f32p))
         return out
 
-    def dot8_t(self, type_id, row, xq, n, avx2_iq4nl=False):
+    def dot8_t(self, type_id, row, xq, n, avx2_iq4nl=False, avx2_iq4xs=False):
         row = _u8(row)
         if avx2_iq4nl:
             return float(self.lib.q4ref_dot8_avx2_iq4nl(_p(row, _u8p), C.c_void_p(xq.ctypes.data), C.c_uint64(n)))
+        if avx2_iq4xs:
+            return float(self.lib.q4ref_dot8_avx2_iq4xs(_p(row, _u8p), C.c_void_p(xq.ctypes.data), C.c_uint64(n)))
         return float(self.lib.q4ref_dot8_t(C.c_uint32(type_id), _p(row, _u8p), C.c_void_p(xq.ctypes.data),
                                            C.c_uint64(n)))
 

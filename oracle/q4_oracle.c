@@ -226,25 +226,89 @@ float q4o_iq4nl_dot8(const uint8_t *row, const q4o_q8 *x, uint64_t n) {
     return ((acc[0] + acc[4]) + (acc[2] + acc[6])) + ((acc[1] + acc[5]) + (acc[3] + acc[7]));
 }
 
+/* ---- IQ4_XS ---- */
+static int iq4xs_ls(const uint8_t *blk, int ib) {
+    const uint16_t sh = (uint16_t)(blk[2] | (blk[3] << 8));
+    return ((blk[4 + ib / 2] >> (4 * (ib % 2))) & 0xf) | ((int)((sh >> (2 * ib)) & 3) << 4);
+}
+static void iq4xs_unpack_group(const uint8_t *blk, int ib, int8_t w[32]) {
+    const uint8_t *qs = blk + 8 + 16 * ib;
+    for (int j = 0; j < 16; j++) {
+        w[j] = q4o_iq4nl_values[qs[j] & 0xf];
+        w[j + 16] = q4o_iq4nl_values[qs[j] >> 4];
+    }
+}
+
+void q4o_iq4xs_dequant_row(const uint8_t *src, uint64_t n, float *dst) {
+    int8_t w[32];
+    for (uint64_t b = 0; b < n / Q4O_QK_K; b++) {
+        const uint8_t *blk = src + b * Q4O_IQ4XS_BYTES;
+        const float d = q4o_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+        for (int ib = 0; ib < 8; ib++) {
+            const float dl = d * (float)(iq4xs_ls(blk, ib) - 32);
+            iq4xs_unpack_group(blk, ib, w);
+            for (int j = 0; j < 32; j++) dst[256 * b + 32 * ib + j] = dl * (float)w[j];
+        }
+    }
+}
+
+void q4o_iq4xs_group_idot(const uint8_t *row, const q4o_q8 *x, uint64_t n, int32_t *I) {
+    int8_t w[32];
+    for (uint64_t b = 0; b < n / Q4O_QK_K; b++)
+        for (int ib = 0; ib < 8; ib++) {
+            iq4xs_unpack_group(row + b * Q4O_IQ4XS_BYTES, ib, w);
+            int32_t s = 0;
+            for (int i = 0; i < 32; i++) s += (int32_t)w[i] * x[8 * b + ib].q[i];
+            I[8 * b + ib] = s;
+        }
+}
+
+float q4o_iq4xs_dot8(const uint8_t *row, const q4o_q8 *x, uint64_t n) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    int8_t w[32];
+    for (uint64_t b = 0; b < n / Q4O_QK_K; b++) {
+        const uint8_t *blk = row + b * Q4O_IQ4XS_BYTES;
+        const float d = q4o_f16_to_f32((uint16_t)(blk[0] | (blk[1] << 8)));
+        for (int ib = 0; ib < 8; ib++) {
+            const q4o_q8 *xg = x + 8 * b + ib;
+            const int ls = iq4xs_ls(blk, ib) - 32;
+            iq4xs_unpack_group(blk, ib, w);
+            const float dd = d * xg->d; /* src/q4_cpuexp.c:968 */
+            for (int lane = 0; lane < 8; lane++) {
+                int32_t s = 0;
+                for (int t = 0; t < 4; t++) s += (int32_t)w[4 * lane + t] * xg->q[4 * lane + t];
+                acc[lane] = fmaf(dd, (float)(s * ls), acc[lane]); /* :966-972 */
+            }
+        }
+    }
+    return ((acc[0] + acc[4]) + (acc[2] + acc[6])) + ((acc[1] + acc[5]) + (acc[3] + acc[7]));
+}
+
 uint64_t q4o_row_bytes(uint32_t type, uint64_t ncols) {
-    return type == Q4O_T_IQ4_NL ? (ncols / 32) * Q4O_IQ4NL_BYTES : (ncols / Q4O_QK_K) * Q4O_IQ3S_BYTES;
+    if (type == Q4O_T_IQ4_NL) return (ncols / 32) * Q4O_IQ4NL_BYTES;
+    if (type == Q4O_T_IQ4_XS) return (ncols / Q4O_QK_K) * Q4O_IQ4XS_BYTES;
+    return (ncols / Q4O_QK_K) * Q4O_IQ3S_BYTES;
+}
+
+float q4o_dot8_t(uint32_t type, const uint8_t *row, const q4o_q8 *x, uint64_t n) {
+    if (type == Q4O_T_IQ4_NL) return q4o_iq4nl_dot8(row, x, n);
+    if (type == Q4O_T_IQ4_XS) return q4o_iq4xs_dot8(row, x, n);
+    return q4o_iq3s_dot8(row, x, n);
 }
 
 void q4o_expert_ffn_t(const uint8_t *pack, const q4o_q8 *xq, uint32_t n_embd, uint32_t n_ff,
-                      uint32_t down_type, float wt, float *y, float *h_out, q4o_q8 *hq_out) {
-    if (down_type == Q4O_T_IQ3_S) {
-        q4o_expert_ffn(pack, xq, n_embd, n_ff, wt, y, h_out, hq_out);
-        return;
-    }
-    const uint64_t rb_gu = q4o_row_bytes(Q4O_T_IQ3_S, n_embd), rb_d = q4o_row_bytes(down_type, n_ff);
+                      uint32_t gu_type, uint32_t down_type, float wt, float *y, float *h_out,
+                      q4o_q8 *hq_out) {
+    const uint64_t rb_gu = q4o_row_bytes(gu_type, n_embd), rb_d = q4o_row_bytes(down_type, n_ff);
     const uint8_t *gate = pack, *up = pack + (uint64_t)n_ff * rb_gu, *down = up + (uint64_t)n_ff * rb_gu;
     float *h = (float *)malloc(sizeof(float) * n_ff);
     q4o_q8 *hq = (q4o_q8 *)malloc(sizeof(q4o_q8) * (n_ff / 32));
     for (uint32_t r = 0; r < n_ff; r++)
-        h[r] = q4o_silu(q4o_iq3s_dot8(gate + r * rb_gu, xq, n_embd)) * q4o_iq3s_dot8(up + r * rb_gu, xq, n_embd);
+        h[r] = q4o_silu(q4o_dot8_t(gu_type, gate + r * rb_gu, xq, n_embd)) *
+               q4o_dot8_t(gu_type, up + r * rb_gu, xq, n_embd);
     q4o_quant8(h, n_ff, hq);
     for (uint32_t r = 0; r < n_embd; r++) {
-        const float t = wt * q4o_iq4nl_dot8(down + r * rb_d, hq, n_ff);
+        const float t = wt * q4o_dot8_t(down_type, down + r * rb_d, hq, n_ff);
         y[r] = y[r] + t;
     }
     if (h_out) memcpy(h_out, h, sizeof(float) * n_ff);
@@ -254,12 +318,12 @@ void q4o_expert_ffn_t(const uint8_t *pack, const q4o_q8 *xq, uint32_t n_embd, ui
 }
 
 void q4o_expert_job_t(const uint8_t *const *packs, const float *wts, uint32_t k, const float *x,
-                      uint32_t n_embd, uint32_t n_ff, uint32_t down_type, float *y) {
+                      uint32_t n_embd, uint32_t n_ff, uint32_t gu_type, uint32_t down_type, float *y) {
     q4o_q8 *xq = (q4o_q8 *)malloc(sizeof(q4o_q8) * (n_embd / 32));
     q4o_quant8(x, n_embd, xq);
     memset(y, 0, sizeof(float) * n_embd);
     for (uint32_t e = 0; e < k; e++)
-        q4o_expert_ffn_t(packs[e], xq, n_embd, n_ff, down_type, wts[e], y, NULL, NULL);
+        q4o_expert_ffn_t(packs[e], xq, n_embd, n_ff, gu_type, down_type, wts[e], y, NULL, NULL);
     free(xq);
 }
 

@@ -118,13 +118,24 @@ void q4o_iq4nl_group_idot(const uint8_t *row, const q4o_q8 *x, uint64_t n, int32
 /* Row dot against Q8-A activations in the CPU path's order (src/q4_cpuexp.c:977-996): eight
  * running sums over 4-element slices, one fused multiply-add per block, fixed final tree. */
 float q4o_iq4nl_dot8(const uint8_t *row, const q4o_q8 *x, uint64_t n);
-/* Bytes of one row of ncols weights in the given type (IQ3_S or IQ4_NL). */
+/* ---- IQ4_XS (ggml type 23): 136-byte super-blocks of 256 weights: fp16 d, u16 scales_h,
+ * scales_l[4], qs[128]; group ib has the 6-bit scale ls = low nibble | two high bits, weight =
+ * d * (ls - 32) * table[code] with the IQ4_NL table and nibble order
+ * (src/q4_quant.c:455-480; row dot src/q4_cpuexp.c:945-975). ---- */
+#define Q4O_T_IQ4_XS 23u
+#define Q4O_IQ4XS_BYTES 136
+void q4o_iq4xs_dequant_row(const uint8_t *src, uint64_t n, float *dst);
+void q4o_iq4xs_group_idot(const uint8_t *row, const q4o_q8 *x, uint64_t n, int32_t *I);
+float q4o_iq4xs_dot8(const uint8_t *row, const q4o_q8 *x, uint64_t n);
+/* By type id (IQ3_S, IQ4_NL, IQ4_XS). */
 uint64_t q4o_row_bytes(uint32_t type, uint64_t ncols);
-/* q4o_expert_ffn / q4o_expert_job with the down projection's type given (gate and up IQ3_S). */
+float q4o_dot8_t(uint32_t type, const uint8_t *row, const q4o_q8 *x, uint64_t n);
+/* q4o_expert_ffn / q4o_expert_job with the types of gate+up and of down given. */
 void q4o_expert_ffn_t(const uint8_t *pack, const q4o_q8 *xq, uint32_t n_embd, uint32_t n_ff,
-                      uint32_t down_type, float wt, float *y, float *h_out, q4o_q8 *hq_out);
+                      uint32_t gu_type, uint32_t down_type, float wt, float *y, float *h_out,
+                      q4o_q8 *hq_out);
 void q4o_expert_job_t(const uint8_t *const *packs, const float *wts, uint32_t k, const float *x,
-                      uint32_t n_embd, uint32_t n_ff, uint32_t down_type, float *y);
+                      uint32_t n_embd, uint32_t n_ff, uint32_t gu_type, uint32_t down_type, float *y);
 
 /* ---- "Q8-C": the q8_1 block quantiser the reference's grouped prefill GEMM
  * uses (third_party/llama.cpp/ggml/src/ggml-cuda/quantize.cu:491-553):

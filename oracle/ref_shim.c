@@ -50,7 +50,9 @@ const uint8_t *q4_expert_host_ptr(const q4_expert_cache *c, int32_t layer,
 }
 
 static uint32_t g_shim_down_type = Q4_T_IQ3_S;   /* type of the down projection of the packs */
+static uint32_t g_shim_gu_type = Q4_T_IQ3_S;     /* type of gate and up */
 void q4ref_set_down_type(uint32_t type) { g_shim_down_type = type; }
+void q4ref_set_gu_type(uint32_t type) { g_shim_gu_type = type; }
 
 static void shim_tensor(q4_tensor *t, uint32_t type, uint64_t cols, uint64_t rows, uint32_t n_exp) {
     memset(t, 0, sizeof *t);
@@ -68,8 +70,8 @@ static void shim_setup(const uint8_t *const *packs, uint32_t n_packs,
                        uint32_t n_embd, uint32_t n_ff) {
     g_shim.packs = packs;
     g_shim.n_packs = n_packs;
-    shim_tensor(&g_shim.tg, Q4_T_IQ3_S, n_embd, n_ff, n_packs);
-    shim_tensor(&g_shim.tu, Q4_T_IQ3_S, n_embd, n_ff, n_packs);
+    shim_tensor(&g_shim.tg, g_shim_gu_type, n_embd, n_ff, n_packs);
+    shim_tensor(&g_shim.tu, g_shim_gu_type, n_embd, n_ff, n_packs);
     shim_tensor(&g_shim.td, g_shim_down_type, n_ff, n_embd, n_packs);
     g_shim.sg = g_shim.tg.nbytes / n_packs;
     g_shim.su = g_shim.tu.nbytes / n_packs;
@@ -122,6 +124,9 @@ float q4ref_dot8_t(uint32_t type, const uint8_t *row, const void *xq, uint64_t n
 }
 float q4ref_dot8_avx2_iq4nl(const uint8_t *row, const void *xq, uint64_t n) {
     return dq8_iq4_nl(row, (const cpx_q8 *)xq, n);
+}
+float q4ref_dot8_avx2_iq4xs(const uint8_t *row, const void *xq, uint64_t n) {
+    return dq8_iq4_xs(row, (const cpx_q8 *)xq, n);
 }
 
 /* y (+)= W x through the scalar reference GEMV (src/q4_quant.c:595-626). */

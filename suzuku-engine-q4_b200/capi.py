@@ -90,6 +90,8 @@ SIGNATURES = {
     "q4_cuda_quant8": (b, [vp, u64, vp, vp, vp]),
     "q4_cuda_iq4nl_dequant": (b, [vp, u64, u64, vp]),
     "q4_cuda_iq4nl_idot": (b, [vp, u64, u64, vp, vp]),
+    "q4_cuda_iq4_dequant": (b, [u32, vp, u64, u64, vp]),
+    "q4_cuda_iq4_idot": (b, [u32, vp, u64, u64, vp, vp]),
     "q4_cuda_iq3s_dequant": (b, [vp, u64, u64, vp]),
     "q4_cuda_iq3s_idot": (b, [vp, u64, u64, vp, vp]),
     "q4_cuda_moe_decode": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32, u32,

@@ -476,22 +476,23 @@ __global__ void moe_ya_k(const uint8_t *__restrict__ bd, uint64_t stride,
     if (lane == 0) y[r] += acc;
 }
 
-// ------------------------------------------------------------------ IQ4_NL (down projection)
-// 18-byte blocks of 32 weights: fp16 d, then 16 bytes whose low / high nibble index the
-// format's 16-value table for weights j / j + 16 (src/q4_quant.c:270-290).  The kernels keep
-// a 256-entry table in shared memory: code byte -> (low value, high value) as two int8.
-__device__ __forceinline__ void iq4nl_fill_pair_table(uint16_t *pair) {
+// ------------------------------------------------------------------ IQ4_NL and IQ4_XS
+// Both index the same 16-value table with 4-bit codes, 16 code bytes per 32 weights (low nibbles
+// = weights 0..15, high nibbles = 16..31).  IQ4_NL: 18-byte blocks, fp16 d + codes
+// (src/q4_quant.c:270-290).  IQ4_XS: 136-byte super-blocks of 256, fp16 d, u16 scales_h,
+// scales_l[4], qs[128]; group scale = d * (ls - 32), ls six bits (src/q4_quant.c:455-480).
+// The kernels keep a 256-entry table in shared memory: code byte -> (low value, high value).
+__device__ __forceinline__ void iq4_fill_pair_table(uint16_t *pair) {
     const int8_t kv[16] = Q4B_IQ4NL_VALUES;
     for (uint32_t b = threadIdx.x; b < 256u; b += blockDim.x)
         pair[b] = (uint16_t)((uint8_t)kv[b & 15u] | ((uint16_t)(uint8_t)kv[b >> 4] << 8));
 }
-// Integer dot of one block with its 32 activation bytes (q: eight int8x4 words): exact int32.
-__device__ __forceinline__ int32_t iq4nl_block_idot(const uint8_t *blk, const uint16_t *pair,
-                                                    const int *q) {
+// Integer dot of 16 code bytes (2-byte aligned) with their 32 activation bytes: exact int32.
+__device__ __forceinline__ int32_t iq4_codes_idot(const uint8_t *codes, const uint16_t *pair, const int *q) {
     int32_t acc = 0;
 #pragma unroll
     for (int w = 0; w < 4; w++) {       // four code bytes -> weights 4w..4w+3 and 16+4w..16+4w+3
-        const uint32_t c01 = q4b_ld_u16(blk + 2 + 4 * w), c23 = q4b_ld_u16(blk + 4 + 4 * w);
+        const uint32_t c01 = q4b_ld_u16(codes + 4 * w), c23 = q4b_ld_u16(codes + 4 * w + 2);
         const uint32_t p0 = pair[c01 & 0xffu], p1 = pair[c01 >> 8], p2 = pair[c23 & 0xffu], p3 = pair[c23 >> 8];
         const uint32_t lo = (p0 & 0xffu) | ((p1 & 0xffu) << 8) | ((p2 & 0xffu) << 16) | ((p3 & 0xffu) << 24);
         const uint32_t hi = (p0 >> 8) | ((p1 >> 8) << 8) | ((p2 >> 8) << 16) | ((p3 >> 8) << 24);
@@ -500,60 +501,127 @@ __device__ __forceinline__ int32_t iq4nl_block_idot(const uint8_t *blk, const ui
     }
     return acc;
 }
+// Group g (32 weights) of a row of type T (20 or 23): where its codes are, its integer scale
+// factor and the fp16 block scale.
+template <uint32_t T>
+__device__ __forceinline__ const uint8_t *iq4_group(const uint8_t *row, uint32_t g, int *lsf, float *d) {
+    if (T == Q4_T_IQ4_NL) {
+        const uint8_t *blk = row + (uint64_t)g * 18u;
+        *lsf = 1;
+        *d = __half2float(__ushort_as_half((unsigned short)q4b_ld_u16(blk)));
+        return blk + 2;
+    }
+    const uint8_t *blk = row + (uint64_t)(g >> 3) * 136u;
+    const uint32_t ib = g & 7u;
+    const uint32_t sh = q4b_ld_u16(blk + 2);
+    *lsf = (int)(((blk[4 + (ib >> 1)] >> (4u * (ib & 1u))) & 0xfu) | (((sh >> (2u * ib)) & 3u) << 4)) - 32;
+    *d = __half2float(__ushort_as_half((unsigned short)q4b_ld_u16(blk)));
+    return blk + 8 + 16u * ib;
+}
+__host__ __device__ inline uint64_t iq4_row_bytes(uint32_t type, uint64_t ncols) {
+    return type == Q4_T_IQ4_NL ? (ncols / 32u) * 18u : (ncols / 256u) * 136u;
+}
 
-__global__ void iq4nl_dequant_k(const uint8_t *__restrict__ w, uint64_t n_blocks, float *__restrict__ out) {
+template <uint32_t T>
+__global__ void iq4_dequant_k(const uint8_t *__restrict__ w, uint64_t n_groups, uint32_t gpr,
+                              float *__restrict__ out) {
     const int8_t kv[16] = Q4B_IQ4NL_VALUES;
-    const uint64_t b = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (b >= n_blocks) return;
-    const uint8_t *blk = w + b * 18u;
-    const float d = __half2float(__ushort_as_half((unsigned short)q4b_ld_u16(blk)));
+    const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= n_groups) return;
+    const uint64_t r = t / gpr;
+    int lsf;
+    float d;
+    const uint8_t *codes = iq4_group<T>(w + r * iq4_row_bytes(T, 32ull * gpr), (uint32_t)(t - r * gpr), &lsf, &d);
+    const float dl = T == Q4_T_IQ4_NL ? d : __fmul_rn(d, (float)lsf);
     for (int j = 0; j < 16; j++) {
-        out[b * 32u + j] = __fmul_rn(d, (float)kv[blk[2 + j] & 15u]);
-        out[b * 32u + j + 16] = __fmul_rn(d, (float)kv[blk[2 + j] >> 4]);
+        out[t * 32u + j] = __fmul_rn(dl, (float)kv[codes[j] & 15u]);
+        out[t * 32u + j + 16] = __fmul_rn(dl, (float)kv[codes[j] >> 4]);
     }
 }
 
-// I[r][g] for nrows rows of ng blocks against one quantised vector.
-__global__ void iq4nl_idot_k(const uint8_t *__restrict__ w, uint64_t nrows, uint32_t ng,
-                             const int8_t *__restrict__ q, int32_t *__restrict__ I) {
+// I[r][g] for nrows rows of gpr groups against one quantised vector.
+template <uint32_t T>
+__global__ void iq4_idot_k(const uint8_t *__restrict__ w, uint64_t nrows, uint32_t gpr,
+                           const int8_t *__restrict__ q, int32_t *__restrict__ I) {
     __shared__ uint16_t pair[256];
-    iq4nl_fill_pair_table(pair);
+    iq4_fill_pair_table(pair);
     __syncthreads();
     const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t >= nrows * ng) return;
-    const uint32_t g = (uint32_t)(t % ng);
+    if (t >= nrows * gpr) return;
+    const uint64_t r = t / gpr;
+    const uint32_t g = (uint32_t)(t - r * gpr);
     int qv[8];
     for (int k = 0; k < 8; k++) qv[k] = reinterpret_cast<const int *>(q)[g * 8u + k];
-    I[t] = iq4nl_block_idot(w + t * 18u, pair, qv);
+    int lsf;
+    float d;
+    const uint8_t *codes = iq4_group<T>(w + r * iq4_row_bytes(T, 32ull * gpr), g, &lsf, &d);
+    I[t] = iq4_codes_idot(codes, pair, qv);
 }
 
-// Down projection with IQ4_NL rows: the counterpart of moe_ya_k (same reduction shape).
-__global__ void moe_ya_iq4nl_k(const uint8_t *__restrict__ bd, uint64_t stride,
-                               const int32_t *__restrict__ slots, const float *__restrict__ wts,
-                               uint32_t n_host, const int32_t *__restrict__ n_dev,
-                               const int8_t *__restrict__ hq, const float *__restrict__ hd,
-                               uint64_t q_slice, uint64_t d_slice, uint32_t n_ff, uint32_t n_embd,
-                               float *__restrict__ y) {
+// Gate/up + SwiGLU with rows of type T: one warp per (expert, hidden unit); the counterpart of
+// moe_gu_k.  h[e][f] = silu(gate_f . xq) * (up_f . xq).
+template <uint32_t T>
+__global__ void moe_gu4_k(const uint8_t *__restrict__ bg, const uint8_t *__restrict__ bu, uint64_t stride,
+                          const int32_t *__restrict__ slots, const int32_t *__restrict__ n_dev,
+                          const int8_t *__restrict__ xq, const float *__restrict__ xd, uint32_t in_dim,
+                          uint32_t n_ff, float *__restrict__ h) {
     __shared__ uint16_t pair[256];
-    iq4nl_fill_pair_table(pair);
+    iq4_fill_pair_table(pair);
+    __syncthreads();
+    const uint32_t e = blockIdx.y;
+    if (n_dev && e >= (uint32_t)*n_dev) return;
+    const uint32_t f = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (f >= n_ff) return;
+    const uint32_t lane = threadIdx.x & 31u, ng = in_dim >> 5;
+    const uint64_t rb = iq4_row_bytes(T, in_dim);
+    const uint8_t *rg = bg + (uint64_t)slots[e] * stride + (uint64_t)f * rb;
+    const uint8_t *ru = bu + (uint64_t)slots[e] * stride + (uint64_t)f * rb;
+    float ag = 0.f, au = 0.f;
+    for (uint32_t g = lane; g < ng; g += 32) {
+        int qv[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) qv[k] = reinterpret_cast<const int *>(xq)[g * 8u + k];
+        const float dx = xd[g];
+        int lsf;
+        float d;
+        const uint8_t *cg = iq4_group<T>(rg, g, &lsf, &d);
+        ag = fmaf(__fmul_rn(d, dx), (float)(iq4_codes_idot(cg, pair, qv) * lsf), ag);
+        const uint8_t *cu = iq4_group<T>(ru, g, &lsf, &d);
+        au = fmaf(__fmul_rn(d, dx), (float)(iq4_codes_idot(cu, pair, qv) * lsf), au);
+    }
+    ag = q4b_warp_sum(ag);
+    au = q4b_warp_sum(au);
+    if (lane == 0) h[(uint64_t)e * n_ff + f] = q4b_swiglu(ag, au);
+}
+
+// Down projection with rows of type T: the counterpart of moe_ya_k (same reduction shape).
+template <uint32_t T>
+__global__ void moe_ya4_k(const uint8_t *__restrict__ bd, uint64_t stride, const int32_t *__restrict__ slots,
+                          const float *__restrict__ wts, uint32_t n_host, const int32_t *__restrict__ n_dev,
+                          const int8_t *__restrict__ hq, const float *__restrict__ hd, uint64_t q_slice,
+                          uint64_t d_slice, uint32_t n_ff, uint32_t n_embd, float *__restrict__ y) {
+    __shared__ uint16_t pair[256];
+    iq4_fill_pair_table(pair);
     __syncthreads();
     const uint32_t r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (r >= n_embd) return;
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t n = n_dev ? (uint32_t)*n_dev : n_host;
     const uint32_t ng = n_ff >> 5;
+    const uint64_t rb = iq4_row_bytes(T, n_ff);
     float acc = 0.f;
     for (uint32_t it = lane; it < n * ng; it += 32) {
         const uint32_t e = it / ng, g = it - e * ng;
-        const uint8_t *blk = bd + (uint64_t)slots[e] * stride + ((uint64_t)r * ng + g) * 18u;
         const int *qg = reinterpret_cast<const int *>(hq + (uint64_t)e * q_slice) + g * 8u;
         int qv[8];
 #pragma unroll
         for (int k = 0; k < 8; k++) qv[k] = qg[k];
-        const int I = iq4nl_block_idot(blk, pair, qv);
-        const float d = __half2float(__ushort_as_half((unsigned short)q4b_ld_u16(blk)));
+        int lsf;
+        float d;
+        const uint8_t *codes = iq4_group<T>(bd + (uint64_t)slots[e] * stride + (uint64_t)r * rb, g, &lsf, &d);
+        const int I = iq4_codes_idot(codes, pair, qv);
         const float dd = __fmul_rn(d, hd[(uint64_t)e * d_slice + g]);
-        acc = fmaf(__fmul_rn(wts[e], dd), (float)I, acc);
+        acc = fmaf(__fmul_rn(wts[e], dd), (float)(I * lsf), acc);
     }
     acc = q4b_warp_sum(acc);
     if (lane == 0) y[r] += acc;
@@ -593,16 +661,18 @@ __global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, u
 }
 
 // ------------------------------------------------------------------ host side
-// gate and up IQ3_S; down IQ3_S or IQ4_NL (the first of the other formats the engine's call
-// sites accept, src/q4_rocm.cu:4926-4944)
+// gate and up of one type, down of any: IQ3_S, IQ4_NL or IQ4_XS (the first of the other formats
+// the engine's call sites accept, src/q4_rocm.cu:4926-4944)
+bool type_ok(uint32_t t) { return t == Q4_T_IQ3_S || t == Q4_T_IQ4_NL || t == Q4_T_IQ4_XS; }
 bool shape_ok(uint32_t gt, uint32_t ut, uint32_t dt, uint32_t in_dim, uint32_t n_ff) {
-    return gt == Q4_T_IQ3_S && ut == Q4_T_IQ3_S && (dt == Q4_T_IQ3_S || dt == Q4_T_IQ4_NL) && in_dim &&
-           n_ff && (in_dim % Q4B_QK) == 0 && (n_ff % Q4B_QK) == 0 && in_dim <= Q4B_XQ_MAXLEN &&
-           n_ff <= Q4B_XQ_MAXLEN;
+    return gt == ut && type_ok(gt) && type_ok(dt) && in_dim && n_ff && (in_dim % Q4B_QK) == 0 &&
+           (n_ff % Q4B_QK) == 0 && in_dim <= Q4B_XQ_MAXLEN && n_ff <= Q4B_XQ_MAXLEN;
 }
 
-// A pack with an IQ4_NL part cannot live in a tiled arena (the tiling regroups IQ3_S bytes).
-bool place_ok(uint32_t dt, const void *base) { return dt != Q4_T_IQ4_NL || !q4b_ptr_tiled(base); }
+// A pack with a part that is not IQ3_S cannot live in a tiled arena (the tiling regroups IQ3_S bytes).
+bool place_ok(uint32_t gt, uint32_t dt, const void *base) {
+    return (gt == Q4_T_IQ3_S && dt == Q4_T_IQ3_S) || !q4b_ptr_tiled(base);
+}
 
 bool launch_quant8(const float *x, uint64_t xs, uint32_t slen, uint32_t ns, int8_t *q, float *d,
                    int32_t *bs, uint64_t q_slice, uint64_t d_slice, const int32_t *n_dev) {
@@ -619,7 +689,8 @@ bool launch_quant8(const float *x, uint64_t xs, uint32_t slen, uint32_t ns, int8
 bool moe_exec_tail(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
                    const float *d_wts, uint32_t n_host, const int32_t *d_n, uint64_t og,
                    uint64_t ou, uint64_t od, float *d_h, float *d_y, uint32_t n_ff,
-                   uint32_t in_dim, uint32_t n_embd, uint32_t dt = Q4_T_IQ3_S) {
+                   uint32_t in_dim, uint32_t n_embd, uint32_t dt = Q4_T_IQ3_S,
+                   uint32_t gt = Q4_T_IQ3_S) {
     Q4bState &s = g_q4b;
     const uint32_t ne = d_n ? 64u : n_host;
     const int8_t *xq = s.xq + (size_t)Q4B_X_SLICE * Q4B_XQ_MAXLEN;
@@ -627,7 +698,13 @@ bool moe_exec_tail(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
     const int32_t *xbs = s.xbs + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
     const size_t sm = 2048 + in_dim + 8 * (in_dim >> 5);
     const bool tiled = q4b_ptr_tiled(base);
-    if (tiled)
+    if (gt == Q4_T_IQ4_NL)
+        moe_gu4_k<Q4_T_IQ4_NL><<<dim3((n_ff + 7) / 8, ne), 256, 0, s.stream>>>(
+            base + og, base + ou, stride, d_slots, d_n, xq, xd, in_dim, n_ff, d_h);
+    else if (gt == Q4_T_IQ4_XS)
+        moe_gu4_k<Q4_T_IQ4_XS><<<dim3((n_ff + 7) / 8, ne), 256, 0, s.stream>>>(
+            base + og, base + ou, stride, d_slots, d_n, xq, xd, in_dim, n_ff, d_h);
+    else if (tiled)
         moe_gu_k<true><<<dim3((n_ff + 7) / 8, ne), 256, sm, s.stream>>>(
             base + og, base + ou, stride, d_slots, d_n, xq, xd, xbs, in_dim, n_ff, d_h);
     else
@@ -638,11 +715,15 @@ bool moe_exec_tail(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
     if (!launch_quant8(d_h, n_ff, n_ff, ne, s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32,
                        d_n))
         return false;
-    if (dt == Q4_T_IQ4_NL) {
-        moe_ya_iq4nl_k<<<(n_embd + 7) / 8, 256, 0, s.stream>>>(base + od, stride, d_slots, d_wts, n_host, d_n,
-                                                              s.xq, s.xd, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32,
-                                                              n_ff, n_embd, d_y);
-    } else if (tiled)
+    if (dt == Q4_T_IQ4_NL)
+        moe_ya4_k<Q4_T_IQ4_NL><<<(n_embd + 7) / 8, 256, 0, s.stream>>>(
+            base + od, stride, d_slots, d_wts, n_host, d_n, s.xq, s.xd, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32, n_ff,
+            n_embd, d_y);
+    else if (dt == Q4_T_IQ4_XS)
+        moe_ya4_k<Q4_T_IQ4_XS><<<(n_embd + 7) / 8, 256, 0, s.stream>>>(
+            base + od, stride, d_slots, d_wts, n_host, d_n, s.xq, s.xd, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32, n_ff,
+            n_embd, d_y);
+    else if (tiled)
         moe_ya_k<true><<<(n_embd + 7) / 8, 256, 0, s.stream>>>(
             base + od, stride, d_slots, d_wts, n_host, d_n, s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN,
             Q4B_XQ_MAXLEN / 32, n_ff, n_embd, d_y);
@@ -684,10 +765,10 @@ extern "C" bool q4_hip_moe_exec_staged(const uint8_t *base, uint64_t stride, uin
     (void)d_h2;
     (void)d_down;
     if (!g_q4b.ok || !base || !d_x || !d_h || !d_y || !n_embd) return false;
-    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(dt, base)) return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(gt, dt, base)) return false;
     if (!quant_x(d_x, in_dim)) return false;
     return moe_exec_tail(base, stride, g_q4b.es_d, g_q4b.ew_d, 0, g_q4b.en_d, og, ou, od, d_h, d_y,
-                         n_ff, in_dim, n_embd, dt);
+                         n_ff, in_dim, n_embd, dt, gt);
 }
 
 extern "C" bool q4_hip_moe_exec(const uint8_t *base, uint64_t stride, const int32_t *slots,
@@ -699,7 +780,7 @@ extern "C" bool q4_hip_moe_exec(const uint8_t *base, uint64_t stride, const int3
     (void)d_down;
     if (!g_q4b.ok || !base || !slots || !wts || !n || n > 64 || !d_x || !d_h || !d_y || !n_embd)
         return false;
-    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(dt, base)) return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(gt, dt, base)) return false;
     // Like the reference (src/q4_rocm.cu:5441-5445) the list goes through mapped
     // host memory: the kernels fetch it themselves, no copy node on the stream.
     // The previous exec must have finished reading it.
@@ -709,7 +790,7 @@ extern "C" bool q4_hip_moe_exec(const uint8_t *base, uint64_t stride, const int3
     *g_q4b.en_h = (int32_t)n;
     if (!quant_x(d_x, in_dim)) return false;
     return moe_exec_tail(base, stride, g_q4b.es_d, g_q4b.ew_d, n, nullptr, og, ou, od, d_h, d_y,
-                         n_ff, in_dim, n_embd, dt);
+                         n_ff, in_dim, n_embd, dt, gt);
 }
 
 extern "C" bool q4_hip_moe_exec_dev(const uint8_t *base, uint64_t stride, const int32_t *d_es,
@@ -721,10 +802,10 @@ extern "C" bool q4_hip_moe_exec_dev(const uint8_t *base, uint64_t stride, const 
     (void)d_down;
     if (!g_q4b.ok || !base || !d_es || !d_ew || !d_nhit || !d_x || !d_h || !d_y || !n_embd)
         return false;
-    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(dt, base)) return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(gt, dt, base)) return false;
     if (!quant_x(d_x, in_dim)) return false;
     return moe_exec_tail(base, stride, d_es, d_ew, 0, d_nhit, og, ou, od, d_h, d_y, n_ff, in_dim,
-                         n_embd, dt);
+                         n_embd, dt, gt);
 }
 
 extern "C" bool q4_hip_softmax_topk_launch(const float *d_logits, uint32_t n, uint32_t k,
@@ -818,21 +899,41 @@ extern "C" bool q4_cuda_iq3s_dequant(const uint8_t *d_w, uint64_t nrows, uint64_
     return q4b_launch_ok("iq3s_dequant");
 }
 
-extern "C" bool q4_cuda_iq4nl_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out) {
-    if (!g_q4b.ok || !d_w || !d_out || nrows == 0 || ncols == 0 || (ncols % 32u)) return false;
-    const uint64_t nb = nrows * (ncols / 32u);
-    iq4nl_dequant_k<<<(unsigned)((nb + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, nb, d_out);
+// Stage tests for the 4-bit formats: type 20 (IQ4_NL) or 23 (IQ4_XS).
+extern "C" bool q4_cuda_iq4_dequant(uint32_t type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                                    float *d_out) {
+    if (!g_q4b.ok || !d_w || !d_out || nrows == 0 || ncols == 0) return false;
+    if (!(type == Q4_T_IQ4_NL && (ncols % 32u) == 0) && !(type == Q4_T_IQ4_XS && (ncols % 256u) == 0))
+        return false;
+    const uint32_t gpr = (uint32_t)(ncols / 32u);
+    const uint64_t n = nrows * gpr;
+    if (type == Q4_T_IQ4_NL)
+        iq4_dequant_k<Q4_T_IQ4_NL><<<(unsigned)((n + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, n, gpr, d_out);
+    else
+        iq4_dequant_k<Q4_T_IQ4_XS><<<(unsigned)((n + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, n, gpr, d_out);
     g_q4b_launches++;
-    return q4b_launch_ok("iq4nl_dequant");
+    return q4b_launch_ok("iq4_dequant");
+}
+extern "C" bool q4_cuda_iq4_idot(uint32_t type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                                 const int8_t *d_q, int32_t *d_I) {
+    if (!g_q4b.ok || !d_w || !d_q || !d_I || nrows == 0 || ncols == 0) return false;
+    if (!(type == Q4_T_IQ4_NL && (ncols % 32u) == 0) && !(type == Q4_T_IQ4_XS && (ncols % 256u) == 0))
+        return false;
+    const uint32_t gpr = (uint32_t)(ncols / 32u);
+    const uint64_t n = nrows * gpr;
+    if (type == Q4_T_IQ4_NL)
+        iq4_idot_k<Q4_T_IQ4_NL><<<(unsigned)((n + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, nrows, gpr, d_q, d_I);
+    else
+        iq4_idot_k<Q4_T_IQ4_XS><<<(unsigned)((n + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, nrows, gpr, d_q, d_I);
+    g_q4b_launches++;
+    return q4b_launch_ok("iq4_idot");
+}
+extern "C" bool q4_cuda_iq4nl_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out) {
+    return q4_cuda_iq4_dequant(Q4_T_IQ4_NL, d_w, nrows, ncols, d_out);
 }
 extern "C" bool q4_cuda_iq4nl_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const int8_t *d_q,
                                    int32_t *d_I) {
-    if (!g_q4b.ok || !d_w || !d_q || !d_I || nrows == 0 || ncols == 0 || (ncols % 32u)) return false;
-    const uint64_t n = nrows * (ncols / 32u);
-    iq4nl_idot_k<<<(unsigned)((n + 255) / 256), 256, 0, g_q4b.stream>>>(d_w, nrows, (uint32_t)(ncols / 32u),
-                                                                     d_q, d_I);
-    g_q4b_launches++;
-    return q4b_launch_ok("iq4nl_idot");
+    return q4_cuda_iq4_idot(Q4_T_IQ4_NL, d_w, nrows, ncols, d_q, d_I);
 }
 
 extern "C" bool q4_cuda_iq3s_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols,

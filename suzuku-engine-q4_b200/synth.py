@@ -59,6 +59,37 @@ def expert_packs_mixed(rng, n, n_embd, n_ff):
     return out
 
 
+IQ4XS_BLOCK = 136
+
+
+def iq4xs_blocks(rng, n_blocks):
+    """n_blocks random IQ4_XS super-blocks (fp16 d = |N(0,1)| * 2^-6, everything else uniform)."""
+    b = rng.integers(0, 256, size=(n_blocks, IQ4XS_BLOCK), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal(n_blocks)) * 2.0 ** -6).astype(np.float16)
+    b[:, 0:2] = d.view(np.uint8).reshape(n_blocks, 2)
+    return b
+
+
+def row_bytes(type_id, ncols):
+    return {21: ncols // 256 * IQ3S_BLOCK, 20: ncols // 32 * IQ4NL_BLOCK, 23: ncols // 256 * IQ4XS_BLOCK}[type_id]
+
+
+def blocks_of(rng, type_id, nbytes):
+    make, bs = {21: (iq3s_blocks, IQ3S_BLOCK), 20: (iq4nl_blocks, IQ4NL_BLOCK), 23: (iq4xs_blocks, IQ4XS_BLOCK)}[type_id]
+    return make(rng, nbytes // bs).reshape(-1)
+
+
+def expert_packs_typed(rng, n, n_embd, n_ff, gu_type, down_type):
+    """n packed experts, gate and up of one format, down of another -> uint8 [n, pack_bytes]."""
+    gu = 2 * n_ff * row_bytes(gu_type, n_embd)
+    dn = n_embd * row_bytes(down_type, n_ff)
+    out = np.empty((n, gu + dn), np.uint8)
+    for e in range(n):
+        out[e, :gu] = blocks_of(rng, gu_type, gu)
+        out[e, gu:] = blocks_of(rng, down_type, dn)
+    return out
+
+
 def expert_packs(rng, n, n_embd, n_ff):
     """n packed experts -> uint8 [n, pack_bytes]."""
     pb = expert_pack_bytes(n_embd, n_ff)

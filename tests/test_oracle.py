@@ -217,3 +217,40 @@ def test_expert_job_with_iq4nl_down_matches_reference(pkg, oracle, reference):
         reference.set_down_type(21)
     got = oracle.expert_job_t(list(packs), wts, x, H, F, 20)
     assert np.linalg.norm(got - want) / np.linalg.norm(want) < 2e-6
+
+
+def test_iq4xs_oracle_pinned_to_reference(pkg, oracle, reference):
+    """IQ4_XS (type 23): dequantisation and the Q8-A row dot bit-exact against the reference's
+    q4_dequant_row / dq8_iq4_xs / cpx_dot8 (src/q4_quant.c:455-480, src/q4_cpuexp.c:945-975)."""
+    if reference is None:
+        pytest.skip("reference CPU path not built here")
+    rng = np.random.default_rng(2025)
+    n = 1024
+    rows = pkg.synth.iq4xs_blocks(rng, 5 * n // 256).reshape(5, -1)
+    xq = oracle.quant8(rng.standard_normal(n).astype(np.float32))
+    for row in rows:
+        a, b = oracle.iq4xs_dequant_row(row, n), reference.dequant_row_t(23, row, n)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+        got = oracle.dot8_t(23, row, xq, n)
+        for want in (reference.dot8_t(23, row, xq, n, avx2_iq4xs=True), reference.dot8_t(23, row, xq, n)):
+            assert np.float32(got).view(np.uint32) == np.float32(want).view(np.uint32)
+
+
+@pytest.mark.parametrize("gu,dn", [(23, 21), (23, 20), (21, 23), (20, 23)])
+def test_expert_job_other_format_mixes_match_reference(pkg, oracle, reference, gu, dn):
+    if reference is None:
+        pytest.skip("reference CPU path not built here")
+    H, F, k = 512, 256, 3
+    rng = np.random.default_rng(gu * 100 + dn)
+    packs = pkg.synth.expert_packs_typed(rng, k, H, F, gu, dn)
+    x = rng.standard_normal(H).astype(np.float32)
+    wts = rng.random(k).astype(np.float32)
+    reference.set_gu_type(gu)
+    reference.set_down_type(dn)
+    try:
+        want = reference.expert_job(list(packs), np.arange(k, dtype=np.int32), wts, x, H, F)
+    finally:
+        reference.set_gu_type(21)
+        reference.set_down_type(21)
+    got = oracle.expert_job_t(list(packs), wts, x, H, F, dn, gu)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < 2e-6

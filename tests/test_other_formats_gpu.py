@@ -1,11 +1,11 @@
-"""IQ4_NL as the down projection's format (the first of the other routed-expert formats the engine's
-call sites accept, src/q4_rocm.cu:4926-4944): stage tests bit for bit, then the one-token exec calls
-on packs of IQ3_S gate/up + IQ4_NL down against the CPU oracle."""
+"""The first two of the other routed-expert formats the engine's call sites accept
+(src/q4_rocm.cu:4926-4944): IQ4_NL and IQ4_XS, for gate+up and/or down.  Stage tests bit for bit,
+then the one-token exec calls on packs of mixed formats against the CPU oracle."""
 import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
-IQ3_S, IQ4_NL = 21, 20
+IQ3_S, IQ4_NL, IQ4_XS = 21, 20, 23
 
 
 def test_iq4nl_dequant_and_integer_dots_bit_exact(dev, pkg, oracle):
@@ -30,13 +30,35 @@ def test_iq4nl_dequant_and_integer_dots_bit_exact(dev, pkg, oracle):
     assert not lib.q4_cuda_iq4nl_dequant(d_w, nrows, 500, d_out)     # not a multiple of 32
 
 
-@pytest.mark.parametrize("H,F", [(512, 256), (2048, 512)])
-def test_exec_with_iq4nl_down_matches_oracle(dev, pkg, oracle, H, F):
-    rng = np.random.default_rng(H)
+def test_iq4xs_dequant_and_integer_dots_bit_exact(dev, pkg, oracle):
+    rng = np.random.default_rng(6)
+    nrows, n = 7, 1024
+    w = pkg.synth.iq4xs_blocks(rng, nrows * n // 256).reshape(nrows, -1)
+    lib = dev.lib
+    d_w = dev.upload(w)
+    d_out = dev.malloc(nrows * n * 4)
+    assert lib.q4_cuda_iq4_dequant(IQ4_XS, d_w, nrows, n, d_out)
+    got = dev.download(d_out, (nrows, n), np.float32)
+    xq = oracle.quant8(rng.standard_normal(n).astype(np.float32))
+    d_I = dev.malloc(nrows * (n // 32) * 4)
+    assert lib.q4_cuda_iq4_idot(IQ4_XS, d_w, nrows, n, dev.upload(np.ascontiguousarray(xq["q"])), d_I)
+    I = dev.download(d_I, (nrows, n // 32), np.int32)
+    for r in range(nrows):
+        assert np.array_equal(got[r].view(np.uint32), oracle.iq4xs_dequant_row(w[r], n).view(np.uint32))
+        assert np.array_equal(I[r], oracle.iq4xs_group_idot(w[r], xq, n))
+    assert not lib.q4_cuda_iq4_dequant(IQ4_XS, d_w, nrows, 1000, d_out)   # not a multiple of 256
+    assert not lib.q4_cuda_iq4_dequant(IQ3_S, d_w, nrows, n, d_out)       # not a 4-bit format
+
+
+@pytest.mark.parametrize("H,F,gu,dn", [(512, 256, IQ3_S, IQ4_NL), (2048, 512, IQ3_S, IQ4_NL),
+                                       (512, 256, IQ3_S, IQ4_XS), (512, 256, IQ4_XS, IQ3_S),
+                                       (2048, 512, IQ4_XS, IQ4_XS), (512, 256, IQ4_NL, IQ4_NL),
+                                       (512, 256, IQ4_XS, IQ4_NL)])
+def test_exec_with_other_formats_matches_oracle(dev, pkg, oracle, H, F, gu, dn):
+    rng = np.random.default_rng(H + 7 * gu + dn)
     n_slots, k = 6, 4
-    packs = pkg.synth.expert_packs_mixed(rng, n_slots, H, F)
+    packs = pkg.synth.expert_packs_typed(rng, n_slots, H, F, gu, dn)
     pb = packs.shape[1]
-    assert pb == pkg.synth.expert_pack_bytes_mixed(H, F)
     lib = dev.lib
     lib.q4_cuda_set_tiled_default(0)          # mixed packs stay in the engine's byte order
     try:
@@ -48,24 +70,25 @@ def test_exec_with_iq4nl_down_matches_oracle(dev, pkg, oracle, H, F):
             row = np.ascontiguousarray(packs[e])
             assert lib.q4_hip_experts_put_a(3, e, row.ctypes.data, pb)
         base, stride = lib.q4_hip_experts_base_a(3), lib.q4_hip_experts_stride_a(3)
-        rb = pkg.synth.iq3s_row_bytes(H)
+        rb = pkg.synth.row_bytes(gu, H)
         og, ou, od = 0, F * rb, 2 * F * rb
-        assert lib.q4_hip_moe_tok_ok(IQ3_S, IQ3_S, IQ4_NL, H, F)
-        assert not lib.q4_hip_moe_tok_ok(IQ4_NL, IQ3_S, IQ3_S, H, F)      # gate/up stay IQ3_S
+        assert lib.q4_hip_moe_tok_ok(gu, gu, dn, H, F)
+        assert not lib.q4_hip_moe_tok_ok(IQ4_NL, IQ3_S, IQ3_S, H, F)      # gate and up share a type
+        assert not lib.q4_hip_moe_tok_ok(IQ3_S, IQ3_S, 12, H, F)          # a type this path does not take
         x = rng.standard_normal(H).astype(np.float32)
         slots = rng.choice(n_slots, k, replace=False).astype(np.int32)
         wts = rng.random(k).astype(np.float32)
         d_x, d_y, d_h = dev.upload(x), dev.malloc(H * 4), dev.malloc(64 * F * 4)
         assert lib.q4_hip_fill(d_y, 0.0, H)
-        assert lib.q4_hip_moe_exec(base, stride, slots.ctypes.data, wts.ctypes.data, k, IQ3_S, og, IQ3_S, ou,
-                                   IQ4_NL, od, d_x, d_h, None, None, d_y, F, H, H)
+        assert lib.q4_hip_moe_exec(base, stride, slots.ctypes.data, wts.ctypes.data, k, gu, og, gu, ou,
+                                   dn, od, d_x, d_h, None, None, d_y, F, H, H)
         y = dev.download(d_y, (H,), np.float32)
-        want = oracle.expert_job_t([packs[s] for s in slots], wts, x, H, F, IQ4_NL)
+        want = oracle.expert_job_t([packs[s] for s in slots], wts, x, H, F, dn, gu)
         assert np.linalg.norm(y - want) / np.linalg.norm(want) <= 1e-3
         # device-side list form, same result bit for bit
         assert lib.q4_hip_fill(d_y, 0.0, H)
         assert lib.q4_hip_moe_exec_dev(base, stride, dev.upload(slots), dev.upload(wts),
-                                       dev.upload(np.array([k], np.int32)), IQ3_S, og, IQ3_S, ou, IQ4_NL, od,
+                                       dev.upload(np.array([k], np.int32)), gu, og, gu, ou, dn, od,
                                        d_x, d_h, None, None, d_y, F, H, H)
         y2 = dev.download(d_y, (H,), np.float32)
         assert np.array_equal(y2.view(np.uint32), y.view(np.uint32))
