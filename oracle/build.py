@@ -18,7 +18,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 CODES_DIR = os.path.join(ROOT, "suzuku-engine-q4_b200", "csrc")
-DEFAULT_REF = os.environ.get("Q4_REFERENCE_DIR", "/root/reference")
+# the reference checkout: named by the environment, else the directory "reference" beside this repository
+DEFAULT_REF = os.environ.get("Q4_REFERENCE_DIR", os.path.join(os.path.dirname(ROOT), "reference"))
 
 ORACLE_SO = os.path.join(HERE, "_build", "libq4oracle.so")
 REF_SO = os.path.join(HERE, "_ref", "libq4ref.so")
