@@ -288,11 +288,12 @@ def test_layer_n_matches_oracle_per_token(dev, pkg, oracle, n_tok, n_expert, top
         layer.close()
 
 
-@pytest.mark.parametrize("per", [[0, 0, 0, 0], [0, 12, 0, 11], [64, 0, 65, 1], [3, 0, 0, 129]])
+@pytest.mark.parametrize("per", [[0, 0, 0, 0], [2100, 11, 12, 5], [64, 0, 65, 1], [3, 0, 0, 129]])
 def test_grouped_product_edge_row_counts(dev, pkg, oracle, per):
     """Row counts at the edges of the kernels' ranges, on a tiled arena: no rows at all (nothing may
-    be written), 11 / 12 rows (either side of the tensor-core threshold, one call split between the
-    two kernels), 64 / 65 (one pass / two passes), 129 (three passes, the last with one row).
+    be written), 11 / 12 rows either side of the tensor-core threshold next to an expert with
+    2100 rows (one call, two kernels), 64 / 65 (one pass / two passes), 129 (three passes, the last
+    with one row).
     Every kernel choice must agree with the CPU path's int8 dot."""
     H, F, n_exp = 2048, 512, 4
     rng = np.random.default_rng(7 + sum(per))
@@ -322,13 +323,16 @@ def test_grouped_product_edge_row_counts(dev, pkg, oracle, per):
             if rows == 0:
                 assert np.array_equal(got, sentinel)        # no rows: nothing written
                 continue
-            for r in sorted({0, rows - 1, rows // 2, min(rows - 1, 64), min(rows - 1, 11)}):
+            for r in sorted({0, rows - 1, rows // 2, min(rows - 1, 64), min(rows - 1, 11), max(0, rows - 6),
+                             max(0, rows - 30), max(0, rows - 40)}):
                 e = int(np.searchsorted(bounds, r, side="right") - 1)
                 xq = oracle.quant8(x[r])
                 for j in (0, 1, 511, 512, 1023):
                     row = packs[e][j * rb:(j + 1) * rb]
                     want = oracle.dot8(row, xq, H)
-                    assert abs(got[r, j] - want) <= 1e-5 * (abs(want) + 1e-3), (mode, r, j, got[r, j], want)
+                    # fp32 sums of 64 group terms in different orders: a few units in the last place of
+                    # the largest term, not of the (possibly cancelling) result
+                    assert abs(got[r, j] - want) <= 1e-5 * abs(want) + 2e-5, (mode, r, j, got[r, j], want)
         assert lib.q4_cuda_device_error() == 0
     finally:
         layer.close()
