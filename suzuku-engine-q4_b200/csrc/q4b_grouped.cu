@@ -518,9 +518,22 @@ bool launch_grouped_any(const uint8_t *w, uint64_t expert_stride, const int32_t 
     if (tc_ok) tc_min = g_tc_mode == 1 ? 1u : (few_ok ? TC_MIN_ROWS : 0xffffffffu);
     if (tc_ok && g_tc_mode == -1 && !few_ok && total_rows >= 8ull * n_entries) tc_min = 1u;
     const bool run_tc = tc_min != 0xffffffffu && max_rows_hint >= tc_min;
+    // When a call is split, the two kernels touch disjoint entries and rows: the tensor-core
+    // kernel goes to a side stream forked off the compute stream and joined after the streaming
+    // kernel, so a handful of many-row experts (a decode batch's shared expert) does not cost a
+    // launch of its own length; the streaming kernel's CTAs on the SMs the other kernel holds
+    // simply start a little later.
+    const bool side = run_tc && tc_min > 1u && few_ok;
     if (run_tc) {
+        cudaStream_t st = g_q4b.stream;
+        if (side) {
+            if (cudaEventRecord(g_q4b.ev_fork, g_q4b.stream) != cudaSuccess ||
+                cudaStreamWaitEvent(g_q4b.aux_stream, g_q4b.ev_fork, 0) != cudaSuccess)
+                return false;
+            st = g_q4b.aux_stream;
+        }
         const bool ok = mmqtc::launch(w, expert_stride, act, n_act, n_entries, bounds, xq.q, xq.d,
-                                      total_rows, cols, w_rows, dst, ld_dst, tiled, tc_min);
+                                      total_rows, cols, w_rows, dst, ld_dst, tiled, tc_min, st);
         g_q4b_launches++;
         if (!ok || !q4b_launch_ok("mmq_tc")) return false;
         if (tc_min <= 1u) return true;
@@ -545,7 +558,11 @@ bool launch_grouped_any(const uint8_t *w, uint64_t expert_stride, const int32_t 
         a.max_rows = run_tc ? tc_min - 1u : 0x7fffffffu;
         const bool ok = few::launch(a);
         g_q4b_launches++;
-        return ok && q4b_launch_ok("grouped_few");
+        if (!ok || !q4b_launch_ok("grouped_few")) return false;
+        if (side && (cudaEventRecord(g_q4b.ev_join, g_q4b.aux_stream) != cudaSuccess ||
+                     cudaStreamWaitEvent(g_q4b.stream, g_q4b.ev_join, 0) != cudaSuccess))
+            return false;
+        return true;
     }
     return launch_grouped(w, expert_stride, act, n_act, n_entries, bounds, xq, cols, w_rows, dst, ld_dst);
 }

@@ -21,6 +21,8 @@ struct Q4bState {
     int n_sm;
     cudaStream_t stream;       // the one compute stream every op is enqueued on
     cudaStream_t copy_stream;  // expert uploads
+    cudaStream_t aux_stream;   // work forked off the compute stream and joined back (two kernels side by side)
+    cudaEvent_t ev_fork, ev_join;
     // activation-quantisation scratch (library-owned, allocated by init/warm)
     int8_t *xq;    // [Q4B_XQ_SLICES][Q4B_XQ_MAXLEN]
     float *xd;     // [Q4B_XQ_SLICES][Q4B_XQ_MAXLEN/32]

@@ -482,7 +482,8 @@ bool shape_ok(uint64_t w_rows, uint64_t w_cols) {
 // q: int8 [rows][cols] row-major; d: float [rows][cols/32].
 bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const uint32_t *n_act,
             uint32_t n_entries, const int32_t *bounds, const int8_t *q, const float *dq, uint64_t rows,
-            uint32_t cols, uint32_t w_rows, float *dst, uint64_t ld_dst, bool tiled, uint32_t min_rows) {
+            uint32_t cols, uint32_t w_rows, float *dst, uint64_t ld_dst, bool tiled, uint32_t min_rows,
+            cudaStream_t stream) {
     if (!g_ready || !shape_ok(w_rows, cols) || rows == 0 || rows > 0x7fffffffull) return false;
     // a small call (decode batches: a handful of entries reach the threshold) is cut into
     // passes of 16 rows so that its few entries still spread over many SMs
@@ -528,13 +529,13 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
     a.work = g_work + turn * WORK_CAP;
     a.n_work = g_n_work + turn;
     a.pass_rows = pass_rows;
-    worklist_k<<<1, 1024, 0, g_q4b.stream>>>(bounds, n_act, n_entries, min_rows, g_work + turn * WORK_CAP,
+    worklist_k<<<1, 1024, 0, stream>>>(bounds, n_act, n_entries, min_rows, g_work + turn * WORK_CAP,
                                             g_n_work + turn, WORK_CAP, pass_rows);
     const dim3 grid(w_rows / MT, (unsigned)max_items);
     if (tiled)
-        mmq_tc_k<true><<<grid, NT, SMEM_BYTES, g_q4b.stream>>>(a, map_q, map_d);
+        mmq_tc_k<true><<<grid, NT, SMEM_BYTES, stream>>>(a, map_q, map_d);
     else
-        mmq_tc_k<false><<<grid, NT, SMEM_BYTES, g_q4b.stream>>>(a, map_q, map_d);
+        mmq_tc_k<false><<<grid, NT, SMEM_BYTES, stream>>>(a, map_q, map_d);
     return true;
 }
 

@@ -143,6 +143,9 @@ extern "C" bool q4_hip_init(void) {
     s.n_sm = p.multiProcessorCount;
     Q4B_CHECK(cudaStreamCreateWithFlags(&s.stream, cudaStreamNonBlocking));
     Q4B_CHECK(cudaStreamCreateWithFlags(&s.copy_stream, cudaStreamNonBlocking));
+    Q4B_CHECK(cudaStreamCreateWithFlags(&s.aux_stream, cudaStreamNonBlocking));
+    Q4B_CHECK(cudaEventCreateWithFlags(&s.ev_fork, cudaEventDisableTiming));
+    Q4B_CHECK(cudaEventCreateWithFlags(&s.ev_join, cudaEventDisableTiming));
     Q4B_CHECK(cudaMemcpyToSymbol(c_iq3s_codes, q4b_iq3s_codes, sizeof(q4b_iq3s_codes)));
     Q4B_CHECK(cudaHostAlloc(&s.es_h, 64 * sizeof(int32_t), cudaHostAllocMapped));
     Q4B_CHECK(cudaHostAlloc(&s.ew_h, 64 * sizeof(float), cudaHostAllocMapped));
@@ -220,6 +223,9 @@ extern "C" void q4_hip_shutdown(void) {
     cudaEventDestroy(g_ev1);
     cudaStreamDestroy(s.stream);
     cudaStreamDestroy(s.copy_stream);
+    cudaStreamDestroy(s.aux_stream);
+    cudaEventDestroy(s.ev_fork);
+    cudaEventDestroy(s.ev_join);
     s = Q4bState{};
 }
 
