@@ -57,9 +57,8 @@ __global__ void ep_sum_k(const float *__restrict__ recv, float *__restrict__ y, 
 }
 
 struct EpWs {
-    float *xn_l, *logits, *wts_l, *xn, *wts, *lw, *rw, *gu, *h, *pd, *partial, *recv;
-    int32_t *ids_l, *ids, *lids, *atok, *rsrc, *stg, *bounds;
-    uint32_t *stgn, *ek;
+    float *xn_l, *logits, *wts_l, *xn, *wts, *rw, *gu, *pd, *partial, *recv;
+    int32_t *ids_l, *ids, *atok, *rsrc, *bounds;
     void *xq, *hq;
     uint64_t bytes;
 };
@@ -81,18 +80,12 @@ EpWs carve(uint8_t *p, uint32_t world, uint32_t t_local, uint32_t topk, uint32_t
     w.xn = (float *)take(T * n_embd * 4);
     w.ids = (int32_t *)take(T * topk * 4);
     w.wts = (float *)take(T * topk * 4);
-    w.lids = (int32_t *)take(rows * 4);
-    w.lw = (float *)take(rows * 4);
     w.atok = (int32_t *)take(rows * 4);
     w.rsrc = (int32_t *)take(rows * 4);
     w.rw = (float *)take(rows * 4);
-    w.stg = (int32_t *)take(512 * 4);
-    w.stgn = (uint32_t *)take(256);
-    w.ek = (uint32_t *)take(512 * 4);
-    w.bounds = (int32_t *)take(514 * 4);
+    w.bounds = (int32_t *)take(1025 * 4);
     w.xq = take(q4_mmq_q8_bytes(rows, n_embd));
     w.gu = (float *)take(rows * 2 * n_ff * 4);
-    w.h = (float *)take(rows * n_ff * 4);
     w.hq = take(q4_mmq_q8_bytes(rows, n_ff));
     w.pd = (float *)take(rows * n_embd * 4);
     w.partial = (float *)take(T * n_embd * 4);
