@@ -36,7 +36,7 @@ constexpr uint32_t NW = NT / 32;      // warps
 constexpr uint32_t H = 2048;          // n_embd
 constexpr uint32_t F = 512;           // n_ff
 constexpr uint32_t RCHUNK = 512;      // router chunk: 512 floats = 2 KB
-constexpr uint32_t MAX_E = 40;        // experts per token incl. shared
+constexpr uint32_t MAX_E = 24;        // experts per token incl. shared (more: the launch chain runs)
 constexpr uint32_t UCHUNK = 8;        // gate/up units per bulk-copy chunk
 constexpr uint32_t MAX_CHUNKS = 8;
 constexpr uint32_t MAX_UNITS = 64;    // routed (expert, hidden unit) pairs per CTA
@@ -312,9 +312,10 @@ __device__ __forceinline__ void fused_body(const Args &a, const float4 *xrow) {
     const uint32_t u1 = (uint32_t)((uint64_t)(cta + 1) * n_units / ncta);
     const uint32_t s0 = has_sh ? (uint32_t)((uint64_t)cta * F / ncta) : 0u;  // shared-expert units
     const uint32_t s1 = has_sh ? (uint32_t)((uint64_t)(cta + 1) * F / ncta) : 0u;
-    const uint32_t n_dtiles = (H / 4) * ne;  // (row quad, expert) pairs, expert fastest
-    const uint32_t v0 = (uint32_t)((uint64_t)cta * n_dtiles / ncta);
-    const uint32_t v1 = (uint32_t)((uint64_t)(cta + 1) * n_dtiles / ncta);
+    // down tiles = (row quad, expert) pairs, expert fastest; a CTA takes whole row quads, so every
+    // output row is summed over the experts by one CTA, in list order, and written once
+    const uint32_t v0 = (uint32_t)((uint64_t)cta * (H / 4) / ncta) * ne;
+    const uint32_t v1 = (uint32_t)((uint64_t)(cta + 1) * (H / 4) / ncta) * ne;
 
     // loads with nothing before them in the dependency chain go first
     float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), wv = make_float4(1.f, 1.f, 1.f, 1.f);
@@ -356,7 +357,6 @@ __device__ __forceinline__ void fused_body(const Args &a, const float4 *xrow) {
             tab[(warp * 32u + i) * 32u + lane] = v;
         }
     }
-    for (uint32_t r = cta * NT + tid; r < H; r += ncta * NT) a.y[r] = 0.f;
     {
         double ss = (double)xv.x * xv.x + (double)xv.y * xv.y + (double)xv.z * xv.z +
                     (double)xv.w * xv.w;
@@ -569,27 +569,21 @@ __device__ __forceinline__ void fused_body(const Args &a, const float4 *xrow) {
     }
     __syncthreads();
     stamp(a, 11);
-    // combine over the experts in list order; a row quad split between two CTAs is
-    // finished with one atomic add from each (y starts at 0, so the sum of the two
-    // parts does not depend on which lands first)
-    if (v1 > v0) {
-        const uint32_t rq_first = v0 / ne, rq_last = (v1 - 1) / ne;
-        for (uint32_t t = tid; t < (rq_last - rq_first + 1) * 4u; t += NT) {
-            const uint32_t rq = rq_first + (t >> 2), row = t & 3u;
-            const uint32_t va = max(rq * ne, v0), vb = min((rq + 1) * ne, v1);
-            float sum = 0.f;
-            for (uint32_t v = va; v < vb; v++) sum += S.part[v - v0][row];
-            if (vb - va == ne)
-                a.y[rq * 4u + row] = sum;
-            else
-                atomicAdd(&a.y[rq * 4u + row], sum);
-        }
+    // combine over the experts in list order
+    for (uint32_t t = tid; t < ((v1 - v0) / ne) * 4u; t += NT) {
+        const uint32_t ql = t >> 2, row = t & 3u;
+        float sum = 0.f;
+        for (uint32_t e = 0; e < ne; e++) sum += S.part[ql * ne + e][row];
+        const uint32_t r = (v0 / ne + ql) * 4u + row;
+        a.y[r] = sum;
     }
     stamp(a, 12);
-    // Host hand-off (the call with host buffers): the CTA that finishes last copies y into
-    // the caller's mapped host buffer and then raises the flag the host is spinning on, so
-    // the result needs neither a copy node nor a stream wake-up.  The count rides on the
-    // barrier counter (a third arrival per CTA keeps it a multiple of the grid size).
+    // Host hand-off (the call with host buffers): the CTA that finishes last copies y into the
+    // caller's pinned, mapped host buffer and then raises the flag the host is spinning on, so
+    // the result needs neither a copy node nor a stream wake-up.  One CTA writes and fences at
+    // system scope: having every CTA write its own rows and fence was measured slower (148
+    // system-scope fences over the PCIe writes instead of one).  The count rides on the barrier
+    // counter (a third arrival per CTA keeps it a multiple of the grid size).
     if (a.y_host) {
         __threadfence();
         __syncthreads();
@@ -669,7 +663,7 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
     const uint32_t max_units = (topk * F + ncta - 1) / ncta + 1;
     const uint32_t n_chunks = (max_units + UCHUNK - 1) / UCHUNK;
     const uint32_t max_sh = (F + ncta - 1) / ncta + 1;
-    const uint32_t max_dt = ((H / 4) * ne + ncta - 1) / ncta + 1;
+    const uint32_t max_dt = ((H / 4 + ncta - 1) / ncta) * ne;
     const uint32_t max_rc = (n_expert * (H / RCHUNK) + ncta - 1) / ncta + 1;
     if (n_chunks > MAX_CHUNKS || n_chunks > NW - 2 || max_dt > MAX_DT || max_units > MAX_UNITS ||
         max_sh > MAX_SH || ne > MAX_E)
