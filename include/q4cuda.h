@@ -192,6 +192,74 @@ bool q4_hip_moe_exec_win(const uint8_t *base, uint64_t stride, const int32_t *d_
                          const float *d_x, float *d_h, float *d_y, uint32_t n_ff, uint32_t in_dim,
                          uint32_t n_embd);
 
+/* ---------------- the engine's small steps around the expert products ----------------
+ * What src/q4_moe.c issues between the products above: elementwise updates, one-row
+ * reductions, the shared expert's gate, the decode layer's pack/final pair
+ * (src/q4.h:971-976, 1130-1133, 1219-1226, 1321-1326, 1384, 1396, 1512).  All enqueue on
+ * the compute stream; n counts floats. */
+void q4_hip_clear(void);                                     /* drop a pending CUDA error */
+bool q4_hip_silu(float *d, uint64_t n);                      /* d = d / (1 + exp(-d)) */
+bool q4_hip_sigmoid(float *d, uint64_t n);
+bool q4_hip_scale(float *d, float s, uint64_t n);
+bool q4_hip_scale_silu(float *x, float s, uint64_t n);       /* v = s x; x = silu(v) */
+bool q4_hip_mul(float *y, const float *a, const float *b, uint64_t n);
+bool q4_hip_add(float *y, const float *a, const float *b, uint64_t n);
+bool q4_hip_mul_sig(float *y, const float *a, const float *g, uint64_t n);   /* y = a sigmoid(g) */
+bool q4_hip_silu_mul(float *g, const float *u, uint64_t n);  /* g = silu(g) u */
+bool q4_hip_axpy(float *y, const float *x, float a, uint64_t n);
+bool q4_hip_axpy_dalpha(float *y, const float *x, const float *d_alpha, uint64_t n);
+bool q4_hip_axpy_rows(float *d_y, const float *d_x, const float *d_sg, uint32_t n, uint32_t n_tok);
+bool q4_hip_dot(const float *a, const float *b, float *out, uint32_t n);
+bool q4_hip_dot_sigmoid(const float *a, const float *b, float *out, uint32_t n);
+/* d_y[t] += sigmoid(d_w . d_x[t]) * d_sh[t] for t < n_tok, one launch. */
+bool q4_hip_sgate_axpy(float *d_y, const float *d_sh, const float *d_w, const float *d_x, uint32_t n,
+                       uint32_t n_tok);
+/* Head of a decode layer: d_y = 0; *d_dot = sigmoid(d_x . d_sgate) when d_sgate is given;
+ * sm = silu(sm) * sm2 over n_sm floats; *flag_d += 1 when given.  qx (quantise x for the exec
+ * that follows) needs nothing here: the exec entry points quantise x themselves. */
+bool q4_hip_moe_pack(float *d_y, const float *d_x, const float *d_sgate, float *d_dot, void *flag_d,
+                     uint32_t n_embd, bool qx, float *sm, const float *sm2, uint32_t n_sm);
+/* Tail: v = y + hy + sh * (dot ? *dot : 1); res[c] += v * 2 sigmoid(inj[c] / hc), c < hc. */
+bool q4_hip_moe_final(float *res, const float *y, const float *hy, const float *sh, const float *dot,
+                      const float *inj, uint32_t n_embd, uint32_t hc);
+/* Up to 8 matrices against one vector in one launch (src/q4.h:960-970); act != 0 gives
+ * that segment out = silu(act * out).  Types here: F32 and IQ3_S. */
+typedef struct {
+    const uint8_t *w;
+    float *out;
+    uint32_t rows;
+    uint32_t ty;
+    float act;
+} q4_seg_t;
+bool q4_hip_gemv_m(const q4_seg_t *segs, uint32_t nseg, const float *d_x, uint32_t in_dim);
+/* Routed experts of n_tok tokens over packed DEVICE lists: token t owns entries
+ * [h_off[t], h_off[t+1]) (host offsets, at most 64 per token) of d_slots / d_wts, row t of
+ * d_x and d_y, rows h_off[t].. of d_h (src/q4.h:895-902).  d_y is ADDED to. */
+bool q4_hip_moe_exec_tok(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
+                         const float *d_wts, const uint32_t *h_off, uint32_t n_tok, uint32_t gt,
+                         uint64_t og, uint32_t ut, uint64_t ou, uint32_t dt, uint64_t od,
+                         const float *d_x, float *d_h, float *d_h2, float *d_y, uint32_t n_ff,
+                         uint32_t in_dim, uint32_t n_embd);
+/* 2..8-row GEMV on 8-bit activations (src/q4.h:913-927): d_y[t][r] = scale * W[r] . q8(d_x[t]),
+ * IQ3_S rows; between hold(x) and release() calls on the same x reuse its quantisation. */
+bool q4_mmvq_n(uint32_t ty, const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const float *d_x,
+               float *d_y, float scale, uint32_t n);
+void q4_mmvq_warm(void);
+void q4_mmvq_hold(const float *d_x);
+void q4_mmvq_release(void);
+int q4_mmvq_on(void);
+void q4_mmvq_verify(int on);
+void q4_mmvq_set(int v);
+/* Expert-indexed weight buffers and the gather into them (src/q4.h:1144-1174).  With every
+ * expert resident in slot = id the engine can pass the arena itself to q4_mmq_mul_id and skip
+ * both.  A copy gathered from a tiled arena keeps the tiled byte order (whole 880-byte tiles). */
+bool q4_mmq_wbuf(uint64_t gu_bytes, uint64_t d_bytes, uint32_t n_exp, uint8_t **gu, uint8_t **d);
+bool q4_mmq_gather(const uint8_t *abase, uint64_t astride, uint64_t goff, uint64_t gu_bytes,
+                   uint64_t doff, uint64_t d_bytes, uint64_t gu_dst, uint64_t d_dst,
+                   const int32_t *d_eid, const int32_t *d_slot, uint32_t n, uint8_t *d_gu,
+                   uint8_t *d_d);
+int q4_xg_on(void);   /* 0: the reference's fp16 prefill product is not offered */
+
 /* ---------------- additions (no single counterpart in the reference) ------------ */
 
 /* Stage tests: the building blocks of the expert kernels, exposed so that the

@@ -87,6 +87,36 @@ SIGNATURES = {
     "q4_hip_moe_win_ok": (b, [u32, u32, u32, u32, u32, u32]),
     "q4_hip_moe_exec_win": (b, [vp, u64, vp, vp, vp, u32, u32, u64, u32, u64, u32, u64, vp, vp, vp,
                                 u32, u32, u32]),
+    "q4_hip_clear": (None, []),
+    "q4_hip_silu": (b, [vp, u64]),
+    "q4_hip_sigmoid": (b, [vp, u64]),
+    "q4_hip_scale": (b, [vp, f32, u64]),
+    "q4_hip_scale_silu": (b, [vp, f32, u64]),
+    "q4_hip_mul": (b, [vp, vp, vp, u64]),
+    "q4_hip_add": (b, [vp, vp, vp, u64]),
+    "q4_hip_mul_sig": (b, [vp, vp, vp, u64]),
+    "q4_hip_silu_mul": (b, [vp, vp, u64]),
+    "q4_hip_axpy": (b, [vp, vp, f32, u64]),
+    "q4_hip_axpy_dalpha": (b, [vp, vp, vp, u64]),
+    "q4_hip_axpy_rows": (b, [vp, vp, vp, u32, u32]),
+    "q4_hip_dot": (b, [vp, vp, vp, u32]),
+    "q4_hip_dot_sigmoid": (b, [vp, vp, vp, u32]),
+    "q4_hip_sgate_axpy": (b, [vp, vp, vp, vp, u32, u32]),
+    "q4_hip_moe_pack": (b, [vp, vp, vp, vp, vp, u32, b, vp, vp, u32]),
+    "q4_hip_moe_final": (b, [vp, vp, vp, vp, vp, vp, u32, u32]),
+    "q4_hip_gemv_m": (b, [vp, u32, vp, u32]),
+    "q4_hip_moe_exec_tok": (b, [vp, u64, vp, vp, vp, u32, u32, u64, u32, u64, u32, u64, vp, vp, vp, vp,
+                                u32, u32, u32]),
+    "q4_mmvq_n": (b, [u32, vp, u64, u64, vp, vp, f32, u32]),
+    "q4_mmvq_warm": (None, []),
+    "q4_mmvq_hold": (None, [vp]),
+    "q4_mmvq_release": (None, []),
+    "q4_mmvq_on": (C.c_int, []),
+    "q4_mmvq_verify": (None, [C.c_int]),
+    "q4_mmvq_set": (None, [C.c_int]),
+    "q4_mmq_wbuf": (b, [u64, u64, u32, vp, vp]),
+    "q4_mmq_gather": (b, [vp, u64, u64, u64, u64, u64, u64, u64, vp, vp, u32, vp, vp]),
+    "q4_xg_on": (C.c_int, []),
     "q4_cuda_quant8": (b, [vp, u64, vp, vp, vp]),
     "q4_cuda_iq4nl_dequant": (b, [vp, u64, u64, vp]),
     "q4_cuda_iq4nl_idot": (b, [vp, u64, u64, vp, vp]),

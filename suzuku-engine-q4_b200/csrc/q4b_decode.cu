@@ -627,18 +627,13 @@ __global__ void moe_ya4_k(const uint8_t *__restrict__ bd, uint64_t stride, const
     if (lane == 0) y[r] += acc;
 }
 
-// IQ3_S rows times fp32 activations (shared-expert style GEMV), warp per row.
+// IQ3_S row r times an fp32 vector, one warp (every lane gets its partial sum; the caller
+// reduces).  Lane l takes groups l, l + 32, ...; tab = the 512 byte-expanded codes.
 template <bool TILED>
-__global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, uint32_t ncols,
-                                const float *__restrict__ x, float *__restrict__ y, float scale) {
-    __shared__ uint32_t tab[512];
-    q4b_fill_code_table(tab);
-    __syncthreads();
-    const uint64_t r = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (r >= nrows) return;
-    const uint32_t lane = threadIdx.x & 31u;
+__device__ __forceinline__ float iq3s_row_dot_f32(const uint8_t *__restrict__ w, uint64_t r, uint32_t ncols,
+                                                  const float *__restrict__ xb, const uint32_t *tab,
+                                                  uint32_t lane) {
     const uint32_t ng = ncols >> 5;
-    const float *xb = x + (uint64_t)blockIdx.y * ncols;
     float acc = 0.f;
     for (uint32_t g = lane; g < ng; g += 32) {
         const Iq3Fields f = iq3_fields<TILED>(w, r * (uint64_t)(ncols >> 8) + (g >> 3), g & 7u);
@@ -656,6 +651,20 @@ __global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, u
         }
         acc += db * sub;
     }
+    return acc;
+}
+
+// IQ3_S rows times fp32 activations (shared-expert style GEMV), warp per row.
+template <bool TILED>
+__global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, uint32_t ncols,
+                                const float *__restrict__ x, float *__restrict__ y, float scale) {
+    __shared__ uint32_t tab[512];
+    q4b_fill_code_table(tab);
+    __syncthreads();
+    const uint64_t r = (uint64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (r >= nrows) return;
+    const uint32_t lane = threadIdx.x & 31u;
+    float acc = iq3s_row_dot_f32<TILED>(w, r, ncols, x + (uint64_t)blockIdx.y * ncols, tab, lane);
     acc = q4b_warp_sum(acc);
     if (lane == 0) y[(uint64_t)blockIdx.y * nrows + r] = scale * acc;
 }

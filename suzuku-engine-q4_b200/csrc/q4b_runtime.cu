@@ -14,6 +14,9 @@
 Q4bState g_q4b = {};
 bool q4b_fused_warm();   // q4b_fused.cu: scratch of the persistent decode kernel
 bool q4b_window_warm();  // q4b_grouped.cu: scratch of the verify-window path
+bool q4b_elem_warm();    // q4b_elem.cu: lists of the per-token exec, rows of the 2..8-row GEMV
+void q4b_elem_shutdown();
+bool q4b_wbuf_tiled(const void *p);
 bool q4b_mmq_tc_warm();  // q4b_grouped.cu: tensor-core grouped product (optional)
 std::atomic<uint64_t> g_q4b_launches{0};
 
@@ -117,7 +120,7 @@ bool alloc_scratch() {
     Q4B_CHECK(cudaMalloc(&s.r_cnt, (size_t)Q4B_MAX_TOK * sizeof(int32_t)));
     Q4B_CHECK(cudaMalloc(&s.hbuf, nq * sizeof(float)));
     q4b_mmq_tc_warm();  // without it the grouped product stays on the CUDA cores
-    return q4b_fused_warm() && q4b_window_warm();
+    return q4b_fused_warm() && q4b_window_warm() && q4b_elem_warm();
 }
 
 }  // namespace
@@ -198,6 +201,7 @@ extern "C" void q4_hip_shutdown(void) {
         if (g_arena[a].base) cudaFree(g_arena[a].base);
         g_arena[a] = Arena{};
     }
+    q4b_elem_shutdown();
     cudaFree(s.xq);
     cudaFree(s.xd);
     cudaFree(s.xbs);
@@ -463,7 +467,7 @@ bool q4b_ptr_tiled(const void *p) {
         if (g_arena[a].base && g_arena[a].tiled && q >= g_arena[a].base &&
             q < g_arena[a].base + g_arena[a].bytes)
             return true;
-    return false;
+    return q4b_wbuf_tiled(p);   // a gathered copy of a tiled arena keeps its byte order
 }
 extern "C" void q4_cuda_set_tiled_default(int on) { g_tiled_default = on ? 1 : 0; }
 extern "C" int q4_cuda_experts_tiled_a(int arena) {

@@ -9,4 +9,5 @@
 #include "q4b_mmq_tc.cu"
 #include "q4b_few.cu"
 #include "q4b_grouped.cu"
+#include "q4b_elem.cu"
 #include "q4b_noalloc.cu"

@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 def _declared():
     text = open(os.path.join(ROOT, "include", "q4cuda.h")).read()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(q4_(?:hip|cuda|mmq)_\w+)\s*\(", text)))
+    return sorted(set(re.findall(r"\b(q4_(?:hip|cuda|mmq|mmvq|xg)_\w+)\s*\(", text)))
 
 
 def test_every_declared_symbol_is_exported(pkg):
