@@ -254,11 +254,100 @@ void q4_mmvq_set(int v);
  * expert resident in slot = id the engine can pass the arena itself to q4_mmq_mul_id and skip
  * both.  A copy gathered from a tiled arena keeps the tiled byte order (whole 880-byte tiles). */
 bool q4_mmq_wbuf(uint64_t gu_bytes, uint64_t d_bytes, uint32_t n_exp, uint8_t **gu, uint8_t **d);
+/* Point the two buffers at the caller's memory, or drop them (NULL); from the first call on
+ * q4_mmq_wbuf never allocates and fails while they are dropped or too small.  The sizes come
+ * from q4_mmq_wbuf_size / _need, which read the engine's model struct and therefore live in
+ * suzuku-engine-q4_b200/host/q4_engine_glue.c, compiled with the engine. */
+bool q4_mmq_wbuf_lend(void *gu, uint64_t gu_bytes, void *d, uint64_t d_bytes);
 bool q4_mmq_gather(const uint8_t *abase, uint64_t astride, uint64_t goff, uint64_t gu_bytes,
                    uint64_t doff, uint64_t d_bytes, uint64_t gu_dst, uint64_t d_dst,
                    const int32_t *d_eid, const int32_t *d_slot, uint32_t n, uint8_t *d_gu,
                    uint8_t *d_d);
 int q4_xg_on(void);   /* 0: the reference's fp16 prefill product is not offered */
+
+/* ---------------- the rest of what src/q4_moe.c references ----------------
+ * So that the engine's MoE layer code links unchanged.  Real: host-memory helpers
+ * (src/q4.h:1058-1060), a memset ordered with the expert uploads (:1319), GEMV with host
+ * operands or a row gather (:1061-1077; F32 and IQ3_S), the SwiGLU alias (:1108). */
+bool q4_hip_host_register(void *p, size_t n);
+void *q4_hip_host_devptr(void *p);
+void q4_hip_host_unregister(void *p);
+bool q4_hip_copy_memset(void *dst, int v, size_t n);
+bool q4_hip_gemv(uint32_t ggml_type, const uint8_t *w, uint64_t nrows, uint64_t ncols, const float *x,
+                 float *y, float scale);                       /* host W, x, y; synchronous */
+bool q4_hip_gemv_dev(uint32_t ggml_type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                     const float *x, float *y, float scale);   /* device W; host x, y */
+bool q4_hip_gemv_dd_n_which(uint32_t ggml_type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                            const float *d_x, float *d_y, float scale, uint32_t n_batch,
+                            const int32_t *which);             /* token i reads x[which[i]] */
+bool q4_hip_moe_act(float *d_g, const float *d_u, uint64_t n);  /* = q4_hip_silu_mul */
+void q4_hip_mark_pt(int slot);                                  /* no-op */
+/* Declined: always false (nothing enqueued), the reference's answer for an uncovered type.
+ * The float-activation prefill products (src/q4.h:1090-1122) come after q4_mmq_mul_id in the
+ * engine's order of preference; Q4_K / Q8_0 dense forms and the fp16 prefill product are
+ * outside this path. */
+bool q4_hip_moe_pf(uint32_t type, const uint8_t *wbase, uint64_t stride, uint64_t woff,
+                   const int32_t *d_slots, const uint32_t *d_eb, const uint32_t *d_ec,
+                   const int32_t *d_atok, const float *d_x, float *d_out, uint32_t nrows,
+                   uint32_t ncols, uint32_t ne);
+bool q4_hip_moe_pf2(uint32_t type, const uint8_t *wbase, uint64_t stride, uint64_t woff0,
+                    uint64_t woff1, const int32_t *d_slots, const uint32_t *d_eb,
+                    const uint32_t *d_ec, const int32_t *d_atok, const float *d_x, float *d_out0,
+                    float *d_out1, uint32_t nrows, uint32_t ncols, uint32_t ne);
+bool q4_hip_moe_wmma(uint32_t type, const uint8_t *wbase, uint64_t stride, uint64_t woff,
+                     const int32_t *d_slots, const uint32_t *d_eb, const uint32_t *d_ec,
+                     const int32_t *d_atok, const float *d_x, float *d_out, uint32_t nrows,
+                     uint32_t ncols, uint32_t ne);
+bool q4_hip_moe_wmma2(uint32_t type, const uint8_t *wbase, uint64_t stride, uint64_t woff0,
+                      uint64_t woff1, const int32_t *d_slots, const uint32_t *d_eb,
+                      const uint32_t *d_ec, const int32_t *d_atok, const float *d_x, float *d_out,
+                      uint32_t nrows, uint32_t ncols, uint32_t ne);
+bool q4_hip_gateup_q4k(const uint8_t *d_gate, const uint8_t *d_up, const float *d_x, float *d_h,
+                       uint32_t n_ff, uint32_t n_embd);
+bool q4_hip_gateup_q4k_n_which(const uint8_t *d_gate, const uint8_t *d_up, const float *d_x,
+                               float *d_h, uint32_t n_ff, uint32_t n_embd, uint32_t n_tok,
+                               const int32_t *which);
+bool q4_hip_q8_reuse(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const float *d_x,
+                     const int32_t *which, float *d_y, float scale, uint32_t n_batch);
+bool q4_xg_gu_type(uint32_t type);
+bool q4_xg_dn_type(uint32_t type);
+bool q4_xg_shape_ok(uint32_t n_embd, uint32_t n_ff);
+uint32_t q4_xg_tile_cap(uint32_t rows, uint32_t n_exp);
+uint32_t q4_xg_tiles(const uint32_t *ek, const uint32_t *ebase, const int32_t *slot, uint32_t n_exp,
+                     int32_t *out, uint32_t cap);
+bool q4_xg_cvt(const float *x, void *x16, uint64_t n);
+bool q4_xg_gu(uint32_t type, const uint8_t *abase, uint64_t astride, uint64_t og, uint64_t ou,
+              uint32_t n_embd, uint32_t n_ff, const int32_t *d_tiles, uint32_t n_tiles,
+              const void *x16, const int32_t *d_atok, void *h16);
+bool q4_xg_dn(uint32_t type, const uint8_t *abase, uint64_t astride, uint64_t od, uint32_t n_ff,
+              uint32_t n_embd, const int32_t *d_tiles, uint32_t n_tiles, const void *h16, float *out);
+/* Expert offload machinery (router-miss mailbox, CPU-pool waits, prefetch prediction,
+ * verify-timeline stamps; src/q4.h:1236-1259, 1266-1295, 293-300): not present where every
+ * expert is resident.  The calls answer false / 0 and enqueue nothing; the engine then routes
+ * with q4_hip_softmax_topk[_launch] and runs q4_hip_moe_exec[_dev]. */
+bool q4_hip_route_dev(const float *d_rlog, const int32_t *devtab, int32_t *d_es, float *d_ew,
+                      int32_t *d_nhit, const int32_t *restab, int32_t *d_res_s, float *d_res_w,
+                      int32_t *d_res_n, uint32_t res_cap, void *mail, unsigned long long *d_seq,
+                      unsigned long long *d_rseq, unsigned long long *d_prof, uint32_t n_exp,
+                      uint32_t topk);
+bool q4_hip_route_dev_n(const float *d_rlog, const int32_t *devtab, int32_t *d_es, float *d_ew,
+                        int32_t *d_nh, void *mail, unsigned long long *d_seq,
+                        unsigned long long *d_rseq, unsigned long long *d_prof, uint32_t n_exp,
+                        uint32_t topk, uint32_t n_tok);
+bool q4_hip_cpx_wait(void *done_d, void *expect_d, void *progress_d);
+bool q4_hip_cpx_spin_init(void);
+bool q4_hip_cpx_spin(const unsigned long long *want_d, const unsigned long long *done_d);
+unsigned long long q4_hip_cpx_wait_timeouts(void);
+void q4_hip_cpx_wait_reset(void);
+unsigned long long q4_hip_cpx_wait_lastseen(void);
+size_t q4_hip_pred_size(void);
+bool q4_hip_pred_sel(const float *d_plog, const int32_t *devtab, const unsigned long long *d_tseq,
+                     unsigned long long *d_cnt, void *stg, uint32_t n_exp, uint32_t n_tok,
+                     uint32_t kmax, float pmin);
+bool q4_hip_vtl_init(void);
+bool q4_hip_vtl_stamp(uint32_t slot);
+bool q4_hip_vtl_read(double *out, uint32_t n, double off_ns);
+double q4_hip_vtl_calib(void);
 
 /* ---------------- additions (no single counterpart in the reference) ------------ */
 

@@ -6,6 +6,7 @@
                                  (src/q4_cpuexp.c + src/q4_quant.c compiled
                                  unmodified, plus ref_shim.c); built only when a
                                  reference checkout is present
+  oracle/_ref/q4_moe.o, q4_engine_glue.o   objects of the link check (engine_link_symbols)
 
 Both are test infrastructure: only tests, the smoke check and the benchmark's
 CPU-baseline leg load them.  Run `python oracle/build.py [--ref <checkout>]`.
@@ -74,6 +75,29 @@ def build_ref(ref_dir=DEFAULT_REF, force=False):
           o_quant, quant])
     _run(["gcc", "-shared", "-pthread", "-fopenmp", "-o", REF_SO, o_shim, o_quant, "-lm"])
     return REF_SO
+
+
+def engine_link_symbols(ref_dir=DEFAULT_REF):
+    """The link check of the drop-in boundary: compile the reference engine's MoE layer code
+    (src/q4_moe.c) and the engine-side glue to objects (into oracle/_ref/, nothing is linked
+    or run) and return (device symbols q4_moe.o leaves undefined, symbols the glue defines).
+    None when no reference checkout is present."""
+    ref_src = os.path.join(ref_dir, "src")
+    moe = os.path.join(ref_src, "q4_moe.c")
+    if not os.path.exists(moe):
+        return None
+    out_dir = os.path.dirname(REF_SO)
+    os.makedirs(out_dir, exist_ok=True)
+    o_moe = os.path.join(out_dir, "q4_moe.o")
+    o_glue = os.path.join(out_dir, "q4_engine_glue.o")
+    glue = os.path.join(ROOT, "suzuku-engine-q4_b200", "host", "q4_engine_glue.c")
+    _run(["gcc", "-O1", "-w", "-I", ref_src, "-c", "-o", o_moe, moe])
+    _run(["gcc", "-O2", "-Wall", "-Werror", "-I", ref_src, "-c", "-o", o_glue, glue])
+    und = subprocess.run(["nm", "-u", o_moe], capture_output=True, text=True, check=True).stdout.split()
+    dev = sorted(n for n in und if n.startswith(("q4_hip_", "q4_mmq_", "q4_xg_", "q4_mmvq_", "q4_hgemm_")))
+    defs = subprocess.run(["nm", "--defined-only", o_glue], capture_output=True, text=True, check=True).stdout
+    glue_syms = sorted(line.split()[-1] for line in defs.splitlines() if " T " in line)
+    return dev, glue_syms
 
 
 def main():

@@ -115,8 +115,47 @@ SIGNATURES = {
     "q4_mmvq_verify": (None, [C.c_int]),
     "q4_mmvq_set": (None, [C.c_int]),
     "q4_mmq_wbuf": (b, [u64, u64, u32, vp, vp]),
+    "q4_mmq_wbuf_lend": (b, [vp, u64, vp, u64]),
     "q4_mmq_gather": (b, [vp, u64, u64, u64, u64, u64, u64, u64, vp, vp, u32, vp, vp]),
     "q4_xg_on": (C.c_int, []),
+    "q4_hip_host_register": (b, [vp, sz]),
+    "q4_hip_host_devptr": (vp, [vp]),
+    "q4_hip_host_unregister": (None, [vp]),
+    "q4_hip_copy_memset": (b, [vp, C.c_int, sz]),
+    "q4_hip_gemv": (b, [u32, vp, u64, u64, vp, vp, f32]),
+    "q4_hip_gemv_dev": (b, [u32, vp, u64, u64, vp, vp, f32]),
+    "q4_hip_gemv_dd_n_which": (b, [u32, vp, u64, u64, vp, vp, f32, u32, vp]),
+    "q4_hip_moe_act": (b, [vp, vp, u64]),
+    "q4_hip_mark_pt": (None, [C.c_int]),
+    "q4_hip_moe_pf": (b, [u32, vp, u64, u64, vp, vp, vp, vp, vp, vp, u32, u32, u32]),
+    "q4_hip_moe_pf2": (b, [u32, vp, u64, u64, u64, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32]),
+    "q4_hip_moe_wmma": (b, [u32, vp, u64, u64, vp, vp, vp, vp, vp, vp, u32, u32, u32]),
+    "q4_hip_moe_wmma2": (b, [u32, vp, u64, u64, u64, vp, vp, vp, vp, vp, vp, u32, u32, u32]),
+    "q4_hip_gateup_q4k": (b, [vp, vp, vp, vp, u32, u32]),
+    "q4_hip_gateup_q4k_n_which": (b, [vp, vp, vp, vp, u32, u32, u32, vp]),
+    "q4_hip_q8_reuse": (b, [vp, u64, u64, vp, vp, vp, f32, u32]),
+    "q4_xg_gu_type": (b, [u32]),
+    "q4_xg_dn_type": (b, [u32]),
+    "q4_xg_shape_ok": (b, [u32, u32]),
+    "q4_xg_tile_cap": (u32, [u32, u32]),
+    "q4_xg_tiles": (u32, [vp, vp, vp, u32, vp, u32]),
+    "q4_xg_cvt": (b, [vp, vp, u64]),
+    "q4_xg_gu": (b, [u32, vp, u64, u64, u64, u32, u32, vp, u32, vp, vp, vp]),
+    "q4_xg_dn": (b, [u32, vp, u64, u64, u32, u32, vp, u32, vp, vp]),
+    "q4_hip_route_dev": (b, [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, vp, vp, vp, vp, u32, u32]),
+    "q4_hip_route_dev_n": (b, [vp, vp, vp, vp, vp, vp, vp, vp, vp, u32, u32, u32]),
+    "q4_hip_cpx_wait": (b, [vp, vp, vp]),
+    "q4_hip_cpx_spin_init": (b, []),
+    "q4_hip_cpx_spin": (b, [vp, vp]),
+    "q4_hip_cpx_wait_timeouts": (C.c_ulonglong, []),
+    "q4_hip_cpx_wait_reset": (None, []),
+    "q4_hip_cpx_wait_lastseen": (C.c_ulonglong, []),
+    "q4_hip_pred_size": (sz, []),
+    "q4_hip_pred_sel": (b, [vp, vp, vp, vp, vp, u32, u32, u32, f32]),
+    "q4_hip_vtl_init": (b, []),
+    "q4_hip_vtl_stamp": (b, [u32]),
+    "q4_hip_vtl_read": (b, [vp, u32, C.c_double]),
+    "q4_hip_vtl_calib": (C.c_double, []),
     "q4_cuda_quant8": (b, [vp, u64, vp, vp, vp]),
     "q4_cuda_iq4nl_dequant": (b, [vp, u64, u64, vp]),
     "q4_cuda_iq4nl_idot": (b, [vp, u64, u64, vp, vp]),

@@ -200,6 +200,7 @@ int g_mv_on = 1;
 uint8_t *g_wbuf_gu = nullptr, *g_wbuf_d = nullptr;
 uint64_t g_wbuf_gu_bytes = 0, g_wbuf_d_bytes = 0;
 bool g_wbuf_tiled = false;
+bool g_wbuf_lent = false;   // the buffers are the caller's memory (q4_mmq_wbuf_lend)
 
 bool warm() {
     if (!g_tok_es) {
@@ -241,8 +242,11 @@ void q4b_elem_shutdown() {
     cudaFree(g_tok_nh);
     cudaFree(g_mv_xq);
     cudaFree(g_mv_bounds);
-    cudaFree(g_wbuf_gu);
-    cudaFree(g_wbuf_d);
+    if (!g_wbuf_lent) {
+        cudaFree(g_wbuf_gu);
+        cudaFree(g_wbuf_d);
+    }
+    g_wbuf_lent = false;
     g_tok_es = nullptr;
     g_tok_ew = nullptr;
     g_tok_nh = nullptr;
@@ -437,9 +441,34 @@ extern "C" bool q4_mmvq_n(uint32_t ty, const uint8_t *d_w, uint64_t nrows, uint6
 // in slot = id it can pass the arena itself to q4_mmq_mul_id and skip both calls.
 extern "C" int q4_xg_on(void) { return 0; }  // the fp16 prefill product of the reference: not offered
 
+// Lend mode (src/q4.h:1165-1169): from the first q4_mmq_wbuf_lend on, the two buffers are the
+// caller's memory (or absent) and q4_mmq_wbuf never allocates again.
+extern "C" bool q4_mmq_wbuf_lend(void *gu, uint64_t gu_bytes, void *d, uint64_t d_bytes) {
+    if (!g_q4b.ok) return false;
+    if (!elem::g_wbuf_lent) {
+        cudaStreamSynchronize(g_q4b.stream);
+        cudaFree(elem::g_wbuf_gu);
+        cudaFree(elem::g_wbuf_d);
+        elem::g_wbuf_lent = true;
+    }
+    elem::g_wbuf_gu = (uint8_t *)gu;
+    elem::g_wbuf_d = (uint8_t *)d;
+    elem::g_wbuf_gu_bytes = gu ? gu_bytes : 0;
+    elem::g_wbuf_d_bytes = d ? d_bytes : 0;
+    elem::g_wbuf_tiled = false;
+    return true;
+}
+
 extern "C" bool q4_mmq_wbuf(uint64_t gu_bytes, uint64_t d_bytes, uint32_t n_exp, uint8_t **gu, uint8_t **d) {
     if (!g_q4b.ok || !gu || !d || !n_exp) return false;
     const uint64_t need_gu = gu_bytes * n_exp, need_d = d_bytes * n_exp;
+    if (elem::g_wbuf_lent) {   // borrowed buffers only
+        if (!elem::g_wbuf_gu || !elem::g_wbuf_d || need_gu > elem::g_wbuf_gu_bytes || need_d > elem::g_wbuf_d_bytes)
+            return false;
+        *gu = elem::g_wbuf_gu;
+        *d = elem::g_wbuf_d;
+        return true;
+    }
     if (need_gu > elem::g_wbuf_gu_bytes) {
         cudaStreamSynchronize(g_q4b.stream);
         cudaFree(elem::g_wbuf_gu);

@@ -10,4 +10,5 @@
 #include "q4b_few.cu"
 #include "q4b_grouped.cu"
 #include "q4b_elem.cu"
+#include "q4b_compat.cu"
 #include "q4b_noalloc.cu"

@@ -53,3 +53,22 @@ def test_product_does_not_import_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h", ".c")):
                 text = open(os.path.join(root, f)).read()
                 assert "pyoracle" not in text and "q4_oracle" not in text, f
+
+
+def test_reference_moe_layer_code_links_against_the_library(pkg):
+    """Every device symbol the reference's src/q4_moe.c references is exported by libq4cuda.so
+    or defined by the engine-side glue (host/q4_engine_glue.c).  Needs the reference checkout:
+    the file is compiled to an object, nothing of it is linked or run."""
+    import pytest
+    from oracle import build as obuild
+    got = obuild.engine_link_symbols()
+    if got is None:
+        pytest.skip("no reference checkout on this machine")
+    wanted, glue = got
+    assert len(wanted) > 90, len(wanted)
+    lib = ctypes.CDLL(pkg.capi.LIB_PATH)
+    missing = [n for n in wanted if not hasattr(lib, n) and n not in glue]
+    assert not missing, missing
+    # and the header declares what the library resolves for it
+    declared = set(_declared())
+    assert not [n for n in wanted if n not in glue and n not in declared]

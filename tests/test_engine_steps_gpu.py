@@ -260,3 +260,69 @@ def test_gather_into_expert_indexed_buffers(dev, pkg, tiled):
         assert lib.q4_cuda_device_error() == 0
     finally:
         layer.close()
+
+
+def test_gemv_forms_with_host_operands_and_row_gather(dev, pkg, oracle):
+    """q4_hip_gemv (host W), q4_hip_gemv_dev (device W, host x and y), q4_hip_gemv_dd_n_which
+    (token i reads row which[i]) (src/q4.h:1061-1077)."""
+    rng = np.random.default_rng(12)
+    lib = dev.lib
+    nrows, ncols, n_tok = 40, 1024, 6
+    x = rng.standard_normal((n_tok, ncols)).astype(np.float32)
+    wf = (rng.standard_normal((nrows, ncols)) * 0.05).astype(np.float32)
+    wq = pkg.synth.iq3s_blocks(rng, nrows * ncols // 256).reshape(nrows, -1)
+    deq = np.stack([oracle.dequant_row(wq[r], ncols) for r in range(nrows)]).astype(np.float64)
+    y = np.zeros(nrows, np.float32)
+    for ty, w, ref in ((F32, wf, wf.astype(np.float64)), (IQ3_S, wq, deq)):
+        w = np.ascontiguousarray(w)
+        assert lib.q4_hip_gemv(ty, w.ctypes.data, nrows, ncols, x[0].ctypes.data, y.ctypes.data, 2.0)
+        assert _rel(y, 2.0 * (ref @ x[0])) < 1e-5
+        d_w = dev.upload(w)
+        assert lib.q4_hip_gemv_dev(ty, d_w, nrows, ncols, x[1].ctypes.data, y.ctypes.data, 1.0)
+        assert _rel(y, ref @ x[1]) < 1e-5
+        which = np.array([5, 0, 0, 3], np.int32)
+        d_y = dev.malloc(4 * nrows * 4)
+        assert lib.q4_hip_gemv_dd_n_which(ty, d_w, nrows, ncols, dev.upload(x), d_y, 0.5, 4, dev.upload(which))
+        got = dev.download(d_y, (4, nrows), np.float32)
+        assert _rel(got, 0.5 * (x[which].astype(np.float64) @ ref.T)) < 1e-5
+        assert lib.q4_hip_gemv_dd_n_which(ty, d_w, nrows, ncols, dev.upload(x), d_y, 0.5, 4, None)
+        assert _rel(dev.download(d_y, (4, nrows), np.float32), 0.5 * (x[:4].astype(np.float64) @ ref.T)) < 1e-5
+    assert not lib.q4_hip_gemv(12, wf.ctypes.data, nrows, ncols, x[0].ctypes.data, y.ctypes.data, 1.0)
+
+
+def test_host_memory_helpers_and_declined_calls(dev):
+    lib = dev.lib
+    buf = np.zeros(4096, np.uint8)
+    if lib.q4_hip_host_register(buf.ctypes.data, buf.nbytes):
+        alias = lib.q4_hip_host_devptr(buf.ctypes.data)
+        assert alias
+        assert lib.q4_hip_copy_memset(alias, 0x5a, 1024)     # on the copy stream, into the host page
+        lib.q4_hip_copy_wait()
+        lib.q4_hip_sync()
+        assert (buf[:1024] == 0x5a).all() and not buf[1024:].any()
+        lib.q4_hip_host_unregister(buf.ctypes.data)
+    d = dev.malloc(256)
+    assert lib.q4_hip_copy_memset(d, 7, 256)
+    lib.q4_hip_copy_wait()
+    assert (dev.download(d, (256,), np.uint8) == 7).all()
+    g, u = np.linspace(-3, 3, 64, dtype=np.float32), np.full(64, 2.0, np.float32)
+    d_g = dev.upload(g)
+    assert lib.q4_hip_moe_act(d_g, dev.upload(u), 64)
+    np.testing.assert_allclose(dev.download(d_g, (64,), np.float32), g * _sig(g) * 2.0, rtol=2e-6, atol=2e-6)
+    # alternates and offload machinery answer "nothing enqueued"
+    n0 = lib.q4_cuda_launch_count()
+    assert not lib.q4_hip_moe_pf(IQ3_S, None, 0, 0, None, None, None, None, None, None, 8, 256, 1)
+    assert not lib.q4_hip_moe_wmma2(IQ3_S, None, 0, 0, 0, None, None, None, None, None, None, 8, 256, 1)
+    assert not lib.q4_hip_route_dev_n(None, None, None, None, None, None, None, None, None, 512, 10, 4)
+    assert not lib.q4_hip_cpx_spin_init() and not lib.q4_hip_vtl_init()
+    assert lib.q4_hip_cpx_wait_timeouts() == 0 and lib.q4_hip_pred_size() == 152
+    assert not lib.q4_xg_gu_type(IQ3_S) and lib.q4_xg_tile_cap(64, 512) == 0
+    assert lib.q4_cuda_launch_count() == n0
+    # lend mode of the expert-indexed buffers: borrowed memory, never an allocation
+    a, b = dev.malloc(1 << 20), dev.malloc(1 << 20)
+    p_gu, p_d = C.c_void_p(), C.c_void_p()
+    assert lib.q4_mmq_wbuf_lend(a, 1 << 20, b, 1 << 20)
+    assert lib.q4_mmq_wbuf(1 << 18, 1 << 18, 4, C.byref(p_gu), C.byref(p_d)) and p_gu.value == a and p_d.value == b
+    assert not lib.q4_mmq_wbuf(1 << 18, 1 << 18, 5, C.byref(p_gu), C.byref(p_d))       # too small: refused
+    assert lib.q4_mmq_wbuf_lend(None, 0, None, 0)
+    assert not lib.q4_mmq_wbuf(16, 16, 1, C.byref(p_gu), C.byref(p_d))                 # dropped: refused
