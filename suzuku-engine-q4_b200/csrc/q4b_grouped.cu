@@ -34,22 +34,34 @@ bool q4b_rms_rows(const float *x, const float *w, float *y, uint32_t n_embd, flo
 namespace grouped {
 
 // Quantised activation rows, planar: int8 q[rows][cols], then float d[rows][cols/32],
-// then int32 bs[rows][cols/32]; each section 256-byte aligned.
+// then int32 bs[rows][cols/32]; then scratch of the tensor-core product, which that product
+// fills itself: two fp16 planes [rows][cols] and one float per row.  Each section 256-byte aligned.
 struct Q8View {
     const int8_t *q;
     const float *d;
     const int32_t *bs;
+    __half *h1, *h2;
+    float *rs;
 };
 __host__ __device__ inline uint64_t align256(uint64_t v) { return (v + 255u) & ~(uint64_t)255u; }
 __host__ __device__ inline uint64_t q8_bytes(uint64_t rows, uint64_t cols) {
-    return align256(rows * cols) + 2u * align256(rows * (cols / 32) * 4u) + 256u;
+    return align256(rows * cols) + 2u * align256(rows * (cols / 32) * 4u) + 2u * align256(rows * cols * 2u) +
+           align256(rows * 4u) + 256u;
 }
 __host__ __device__ inline Q8View q8_view(const void *buf, uint64_t rows, uint64_t cols) {
     Q8View v;
-    const uint8_t *p = (const uint8_t *)buf;
+    uint8_t *p = (uint8_t *)buf;
     v.q = (const int8_t *)p;
-    v.d = (const float *)(p + align256(rows * cols));
-    v.bs = (const int32_t *)(p + align256(rows * cols) + align256(rows * (cols / 32) * 4u));
+    p += align256(rows * cols);
+    v.d = (const float *)p;
+    p += align256(rows * (cols / 32) * 4u);
+    v.bs = (const int32_t *)p;
+    p += align256(rows * (cols / 32) * 4u);
+    v.h1 = (__half *)p;
+    p += align256(rows * cols * 2u);
+    v.h2 = (__half *)p;
+    p += align256(rows * cols * 2u);
+    v.rs = (float *)p;
     return v;
 }
 
@@ -532,7 +544,7 @@ bool launch_grouped_any(const uint8_t *w, uint64_t expert_stride, const int32_t 
                 return false;
             st = g_q4b.aux_stream;
         }
-        const bool ok = mmqtc::launch(w, expert_stride, act, n_act, n_entries, bounds, xq.q, xq.d,
+        const bool ok = mmqtc::launch(w, expert_stride, act, n_act, n_entries, bounds, xq.q, xq.d, xq.h1, xq.h2, xq.rs,
                                       total_rows, cols, w_rows, dst, ld_dst, tiled, tc_min, st);
         g_q4b_launches++;
         if (!ok || !q4b_launch_ok("mmq_tc")) return false;

@@ -1,32 +1,58 @@
-// Grouped IQ3_S x int8 product on the tensor cores (tcgen05, kind::i8, int32
-// accumulators in tensor memory) for the many-rows-per-expert case of
-// q4_mmq_mul_id (src/q4_mmq.cu:387, the reference's tile kernel mmq_iq3s_k).
+// Grouped IQ3_S x 8-bit product on the tensor cores (tcgen05, fp32 accumulators in tensor
+// memory) for the many-rows-per-expert case of q4_mmq_mul_id (src/q4_mmq.cu:387, the
+// reference's tile kernel mmq_iq3s_k).
 //
-// Arithmetic.  The product is defined per 32-element group (src/q4_mmq.cu:130-
-// 217): I[m][n][g] = sum_k w[m][k] q[n][k] with w = sign * grid byte (odd, |w| <=
-// 15) and q the 8-bit activation, then out[m][n] = sum_g (float)I * (ls * d) *
-// dq[n][g].  A group is exactly one K = 32 step of the 8-bit MMA, so every I is
-// produced by one instruction into its own accumulator columns and is exact; the
-// scale of a group differs per weight row AND per activation row, so the
-// scaling cannot be folded into the MMA and runs on the CUDA cores.
+// Arithmetic.  The product is defined per 32-element group (src/q4_mmq.cu:130-217):
+//   out[m][n] = sum_g (float)I[m][n][g] * (ls[m][g] * d[m]) * dq[n][g],  I = sum_k w q
+// with w = sign * grid byte (odd, |w| <= 15), ls = 1 + 2 s (odd, <= 31), d the super-block's
+// fp16 scale and q, dq the 8-bit activation and its group scale.  The group scale differs per
+// weight row AND per activation row, so with 8-bit integer MMAs (one K = 32 instruction per
+// group) every group's int32 sums have to come back to the CUDA cores for int -> float and two
+// multiplies: 3.3 instructions per output element and group, 30 times the MMA's own time -
+// that form of this kernel ran with the tensor pipe 3 % busy.  Here the scales ride in the
+// operands instead:
+//   A[m][k] = w * ls                as fp16: an integer of magnitude <= 465, exact
+//   B[n][k] = q * dq[n][g] / rs[n]  as the sum of two fp16 numbers (rs = a power of two that
+//                                   brings the row's largest value below 1): 22 bits
+// and the fp16 MMA accumulates A * B in fp32 over the eight groups of a super-block, whose
+// sum needs one multiply by d[m] (and the whole row one by rs[n]) on the CUDA cores: 1/8
+// fused multiply-add per element and group instead of 3.3 instructions.  The products are
+// the reference's integers times the reference's scales; a term differs from the exact one by
+// at most 2^-22 of its size (the two-term expansion of q * dq) and the group sums are added in
+// fp32 by the tensor core instead of after an exact integer sum.  With unit scales the result
+// is the exact integer product (tested bit for bit); against the CUDA-core kernels, which do
+// form the integer sums, the outputs agree to ~1e-6 rel-L2.
 //
-// One CTA owns 128 weight rows of one expert (the M side of the MMA; a weight
-// row is a lane of tensor memory, so its scale is a per-thread scalar) and walks
-// the expert's activation rows 64 at a time (the N side).  Per step of 128 k
-// (four groups):
-//   all 512 threads   decode 128 rows x 4 groups of IQ3_S into int8 core
-//                     matrices in shared memory (K-major, no swizzle; the K
-//                     chunks are 144 bytes apart so the 16-byte stores of a
-//                     quarter warp fall in different banks)
-//   TMA               activation rows [64][128 B] through a rank-3 map
-//                     (16 B, row, chunk) that lands them as core matrices, and
-//                     their group scales [64][4] through a rank-2 map
-//   one thread        four MMAs 128 x N x 32, one per group, then a commit
-//   all 16 warps      tcgen05.ld of the previous step's accumulators, int ->
-//                     float, two multiply-adds per element into registers
-// Steps are double-buffered in shared and tensor memory: the MMAs of step i+1
-// run under the scaling of step i.  Every wait is bounded; a wait that gives up
-// sets the error word and the CTA runs to its end (results then undefined).
+// One CTA owns 128 weight rows of one expert (the M side; a weight row is a lane of tensor
+// memory, so d[m] is a per-thread scalar) and one pass of up to 64 activation rows (N side).
+// Per step of 128 k (four groups; two steps = one super-block = one accumulator):
+//   16 warps          decode 128 rows x 4 groups of IQ3_S into fp16 rows of 128 bytes in
+//                     shared memory under the 128-byte swizzle (the layout TMA writes for the
+//                     other operand; a quarter warp's 16-byte stores hit eight different
+//                     16-byte columns); the fields of a step are loaded four steps ahead
+//                     into registers that are never moved (the loop is unrolled by four)
+//   copy warp         the two fp16 planes of the activation rows as [rows][128 B] TMA boxes
+//                     under the 128-byte swizzle, second plane stored right behind the first,
+//                     so that one MMA takes both as its N side
+//   MMA warp          waits for both operands, issues 8 MMAs 128 x 2N x 16 with precomputed
+//                     descriptors and commits; it does nothing else, because one thread's
+//                     instruction stream is slow (~60 cycles per MMA, ~250 per barrier test
+//                     while the other warps keep the shared-memory pipe busy)
+//   16 warps          after every second step: tcgen05.ld of the finished super-block's
+//                     accumulator (both planes' halves), one add and one FMA per element
+// The warps meet only through mbarriers (weights full / MMAs done / accumulator read /
+// activations landed / stage free): weights and activations are double-buffered in shared
+// memory, super-blocks in tensor memory.  Every wait is bounded; a wait that gives up sets
+// the error word and the CTA runs to its end (results then undefined).
+//
+// What was measured on the way (a 20k-row call, 160 experts, 1024 x 2048 weights): all warps
+// decoding and one of them also issuing, with __syncthreads between the stages, 0.74 ms; the
+// issue moved to its own warp 0.59; both planes in one MMA 0.58; copies in a second extra warp
+// 0.50; field registers that are not moved (a move waits for its load) 0.44.  Asking for
+// 200 KB of shared memory instead of 168 KB cost 15 %: the scattered field loads live on the
+// L1 cache that is left.  A 16-byte-wide TMA box that lands as core matrices directly costs one
+// request per 16 bytes (~2000 cycles per step); an unswizzled weight layout was as fast as the
+// swizzled one.
 #include <cuda.h>
 
 #include "q4b_internal.cuh"
@@ -34,35 +60,37 @@
 
 namespace mmqtc {
 
-constexpr uint32_t NT = 512;           // threads
+constexpr uint32_t NDW = 16;           // decode + epilogue warps
+constexpr uint32_t NT = 32 * (NDW + 2); // plus one warp that issues the MMAs and one that issues the copies
 constexpr uint32_t MT = 128;           // weight rows per CTA
 constexpr uint32_t NB = 64;            // activation rows per pass
-constexpr uint32_t KS = 128;           // k per step (four groups)
-constexpr uint32_t A_LBO = 144;        // bytes between the K chunks of a core-matrix row group
-constexpr uint32_t A_SBO = 8 * A_LBO;  // bytes between 8-row groups
-constexpr uint32_t A_BYTES = (MT / 8) * A_SBO;
-constexpr uint32_t B_LBO = NB * 16;    // [chunk][row][16 B]
-constexpr uint32_t B_SBO = 128;
-constexpr uint32_t B_BYTES = 8 * B_LBO;
-constexpr uint32_t DA_BYTES = NB * 16;  // [row][4 floats]
-constexpr uint32_t NSTAGE_B = 3;
-constexpr uint32_t TMEM_COLS = 512;
+constexpr uint32_t KS = 128;           // k per step (four groups = 16 K chunks of 8 halves)
+constexpr uint32_t A_ATOM = MT * 128;  // 64 k of the CTA's weight rows: [row][128 B], 128-byte swizzle
+constexpr uint32_t A_BYTES = 2 * A_ATOM;         // a step: 32 KB
+constexpr uint32_t B_ATOM = 2 * NB * 128;  // 64 k of the pass's rows, first plane then second plane:
+                                           // [plane][row][128 B] under the 128-byte swizzle
+constexpr uint32_t B_SBO = 1024;       // eight rows of 128 bytes
+constexpr uint32_t NSTAGE_B = 2;
+constexpr uint32_t NA = 2;             // weight-operand buffers (decode runs up to NA steps ahead of the MMAs)
+constexpr uint32_t NACC = 2;           // accumulators: super-blocks in flight between MMA and epilogue
+constexpr uint32_t ACC_COLS = 2 * NB;  // an accumulator: the two planes' products side by side
+constexpr uint32_t TMEM_COLS = NACC * ACC_COLS;
 
-struct __align__(128) Smem {
-    uint8_t a[2][A_BYTES];
-    uint8_t b[NSTAGE_B][B_BYTES];
-    float da[NSTAGE_B][NB][4];
-    float sw[2][4][MT];
-    uint32_t tab2[512];        // doubled code bytes (2c per byte)
-    unsigned long long bar_mma[2];
-    unsigned long long bar_b[NSTAGE_B];
+struct __align__(1024) Smem {
+    uint8_t a[NA][A_BYTES];
+    uint8_t b[NSTAGE_B][2][B_ATOM];   // every [row][128 B] block starts on a 1024-byte boundary
+    float dr[4][MT];           // d of the weight rows of the last four super-blocks
+    uint32_t tabk[512];        // code bytes 2c with bit 7 flipped
+    unsigned long long bar_mma[NA];    // a step's MMAs are complete (operand buffer free)
+    unsigned long long a_full[NA];     // all decode warps have written a step's weights
+    unsigned long long acc_empty[NACC];  // all epilogue warps have read a super-block's accumulator
+    unsigned long long bar_b[NSTAGE_B];     // a step's activation planes have landed
+    unsigned long long b_empty[NSTAGE_B];   // the MMAs that read a stage are complete
     uint32_t tmem_base;
     uint32_t failed;
 };
-// more than half of an SM's shared memory, so that two of these CTAs (each wants
-// all 512 columns of tensor memory) are never resident together
-constexpr uint32_t SMEM_BYTES = 120 * 1024;
-static_assert(sizeof(Smem) + 128 <= SMEM_BYTES, "shared memory layout");
+constexpr uint32_t SMEM_BYTES = 136 * 1024;
+static_assert(sizeof(Smem) <= SMEM_BYTES, "shared memory layout");
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -74,6 +102,9 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long *bar, uint32_t
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                  "r"(bytes)
                  : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 // Bounded wait on a phase parity.  Returns false after giving up.
 __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t parity, uint32_t limit) {
@@ -98,17 +129,30 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint3
     return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) |
            ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
 }
-// D int32, A and B signed 8-bit, both K-major, M = 128.
-__device__ __forceinline__ uint32_t instr_desc(uint32_t n) {
-    return (2u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((MT >> 4) << 24);
+// K-major rows of 128 bytes under the 128-byte swizzle (what a TMA load with that swizzle
+// writes): 8-row groups 1024 bytes apart; the K offset inside the 128 bytes is part of the
+// start address.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | (1ull << 16) | ((uint64_t)(B_SBO >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
 }
-__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc) {
+__device__ __forceinline__ uint64_t desc64(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+// D fp32, A and B fp16, both K-major, M = 128.
+__device__ __forceinline__ uint32_t instr_desc(uint32_t n) {
+    return (1u << 4) | ((n >> 3) << 17) | ((MT >> 4) << 24);
+}
+// D (+)= A * B; acc = 0 overwrites the accumulator.
+__device__ __forceinline__ void mma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, 0, 0;\n\t"  // accumulate = false: D = A * B
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         :
-        : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc)
+        : "r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc)
         : "memory");
 }
 __device__ __forceinline__ void mma_commit(unsigned long long *bar) {
@@ -122,20 +166,13 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, int32_t *v) {
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *v) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]),
           "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]),
           "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, int32_t *v) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7])
         : "r"(taddr)
         : "memory");
 }
@@ -195,6 +232,8 @@ struct Args {
     const uint2 *work;           // (entry, first row) per pass, built by worklist_k
     const uint32_t *n_work;
     uint32_t pass_rows;          // activation rows per pass: 64, or 16 to spread a small call over more CTAs
+    uint32_t box_rows;           // rows per activation copy = the MMA's N per plane
+    const float *rs;             // per activation row: the power of two its fp16 planes were divided by
 };
 
 // One item per (entry with min_rows or more rows, pass of NB rows): a hot expert's
@@ -242,13 +281,20 @@ __global__ void __launch_bounds__(1024) worklist_k(const int32_t *__restrict__ b
 constexpr uint32_t WAIT_LIMIT = 1u << 21;   // polls before a wait gives up (about a second)
 constexpr uint32_t ERR_MMQ_TC = 0x400u;
 
-// One 32-weight group as true int8 weights: byte = sign * (2c + 1).  With t = 2c
-// (even) and m the 0x00/0xFF sign mask, t ^ (m | 1) is 2c+1 or ~(2c) = -(2c+1).
+// One 32-weight group as fp16 integers w * ls (w = sign * (2c + 1)), 32 halves in 16 words.
+// With t = 2c (even) and m the 0x00/0xFF sign mask, y = ((t ^ 0x80) ^ m) | 1 is the byte
+// w + 128 (t + 1 or ~t, bit 7 flipped).  A byte y under a high byte 0x64 is the fp16 number
+// 1024 + y, and the fused (1024 + y) * ls - 1152 * ls = w * ls is exact: every operand and the
+// result are integers within fp16's exact range.
 template <bool TILED>
-__device__ __forceinline__ void decode_group_w(const Iq3Fields &f, const uint32_t *tab2, uint32_t *wv) {
+__device__ __forceinline__ void decode_group_h(const Iq3Fields &f, const uint32_t *tabk, uint32_t *hv) {
+    const __half ls = __uint2half_rn(f.ls);
+    const __half2 L2 = __half2half2(ls);
+    const __half2 C2 = __half2half2(__hmul(ls, __float2half_rn(-1152.f)));
 #pragma unroll
     for (int k = 0; k < 8; k++) {
         const uint32_t wq = k < 4 ? f.qs_lo : f.qs_hi;
+        // (a byte permute that assembles the index in one instruction measured 13 % slower here)
         const uint32_t idx = ((wq >> (8 * (k & 3))) & 0xffu) | (((f.qh >> k) & 1u) << 8);
         uint32_t m;
         if (TILED) {
@@ -257,33 +303,88 @@ __device__ __forceinline__ void decode_group_w(const Iq3Fields &f, const uint32_
         } else {
             m = q4b_sign_mask4(f.sg >> (4 * k));
         }
-        wv[k] = tab2[idx] ^ (m | 0x01010101u);
+        const uint32_t y = (tabk[idx] ^ m) | 0x01010101u;
+        const uint32_t h01 = q4b_prmt(y, 0x64646464u, 0x5140u);
+        const uint32_t h23 = q4b_prmt(y, 0x64646464u, 0x7362u);
+        const __half2 r01 = __hfma2(*reinterpret_cast<const __half2 *>(&h01), L2, C2);
+        const __half2 r23 = __hfma2(*reinterpret_cast<const __half2 *>(&h23), L2, C2);
+        hv[2 * k] = *reinterpret_cast<const uint32_t *>(&r01);
+        hv[2 * k + 1] = *reinterpret_cast<const uint32_t *>(&r23);
     }
 }
 
+// A group's fields as loaded, with nothing computed from them yet: the loads are issued
+// steps ahead of the decode, and arithmetic on a loaded value would wait for it on the spot.
+struct RawFields {
+    uint32_t qs_lo, qs_hi, qh, sg, sc, d;
+};
 template <bool TILED>
-__global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_constant__ CUtensorMap map_q,
-                                                  const __grid_constant__ CUtensorMap map_d) {
+__device__ __forceinline__ RawFields raw_fields(const uint8_t *mat, uint64_t bi, uint32_t ib) {
+    RawFields r;
+    if (TILED) {
+        const uint8_t *t = mat + (bi >> 3) * Q4B_TILE_BYTES;
+        const uint32_t b = (uint32_t)(bi & 7u);
+        const uint2 qs = *reinterpret_cast<const uint2 *>(t + Q4B_TILE_OFF_QS + 64u * b + 8u * ib);
+        r.qs_lo = qs.x;
+        r.qs_hi = qs.y;
+        r.qh = t[Q4B_TILE_OFF_QH + 8u * b + ib];
+        r.sg = *reinterpret_cast<const uint32_t *>(t + Q4B_TILE_OFF_SG + 32u * b + 4u * ib);
+        r.sc = t[Q4B_TILE_OFF_SC + 4u * b + (ib >> 1)];
+        r.d = *reinterpret_cast<const uint16_t *>(t + 2u * b);
+    } else {   // the engine's byte order: unaligned fields are assembled (and waited for) here
+        const Iq3Fields f = iq3_fields<false>(mat, bi, ib);
+        r.qs_lo = f.qs_lo;
+        r.qs_hi = f.qs_hi;
+        r.qh = f.qh;
+        r.sg = f.sg;
+        r.sc = ((f.ls - 1u) >> 1) * 0x11u;
+        r.d = __half_as_ushort(__float2half_rn(f.d));
+    }
+    return r;
+}
+__device__ __forceinline__ Iq3Fields cook_fields(uint32_t ib, const RawFields &r) {
+    Iq3Fields f;
+    f.qs_lo = r.qs_lo;
+    f.qs_hi = r.qs_hi;
+    f.qh = r.qh;
+    f.sg = r.sg;
+    f.ls = 1u + 2u * ((ib & 1u) ? (r.sc >> 4) : (r.sc & 15u));
+    f.d = __half2float(__ushort_as_half((unsigned short)r.d));
+    return f;
+}
+
+template <bool TILED>
+__global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_constant__ CUtensorMap map_h1,
+                                                  const __grid_constant__ CUtensorMap map_h2) {
     // used directly (no integer round trip), so that the compiler keeps these as
     // shared-space accesses; dynamic shared memory starts on the declared alignment
-    extern __shared__ __align__(128) uint8_t smem_raw[];
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
     Smem &s = *reinterpret_cast<Smem *>(smem_raw);
     if (blockIdx.y >= *a.n_work) return;
     const uint2 item = a.work[blockIdx.y];
     const uint32_t entry = item.x;
-    const int32_t r0 = (int32_t)item.y;
-    const int32_t r1 = min(a.bounds[entry + 1], r0 + (int32_t)a.pass_rows);   // this CTA's pass of the rows
+    const int32_t rc = (int32_t)item.y;                                       // this CTA's pass of the rows
+    const int32_t r1 = min(a.bounds[entry + 1], rc + (int32_t)min(a.pass_rows, NB));
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t B = a.cols >> 8;                 // super-blocks per weight row
-    const uint32_t n_it = a.cols / KS;              // steps per pass
+    const uint32_t n_it = a.cols / KS;              // steps (even: two per super-block)
     const uint8_t *mat = a.w + (uint64_t)(a.act ? a.act[entry] : (int32_t)entry) * a.expert_stride;
     const uint32_t row0 = blockIdx.x * MT;
+    const uint32_t nrows = (uint32_t)(r1 - rc);
+    const uint32_t box = a.box_rows;                // rows a copy brings: 64, or 16 for the small passes
+    const uint32_t idesc = instr_desc(2u * box);
 
-    s.tab2[tid] = __ldg(a.codes + tid) << 1;
+    if (tid < 512u) s.tabk[tid] = (__ldg(a.codes + tid) << 1) ^ 0x80808080u;
     if (tid == 0) {
-        mbar_init(&s.bar_mma[0], 1);
-        mbar_init(&s.bar_mma[1], 1);
-        for (uint32_t i = 0; i < NSTAGE_B; i++) mbar_init(&s.bar_b[i], 1);
+        for (uint32_t i = 0; i < NA; i++) {
+            mbar_init(&s.bar_mma[i], 1);
+            mbar_init(&s.a_full[i], NDW);
+        }
+        for (uint32_t i = 0; i < NACC; i++) mbar_init(&s.acc_empty[i], NDW);
+        for (uint32_t i = 0; i < NSTAGE_B; i++) {
+            mbar_init(&s.bar_b[i], 1);
+            mbar_init(&s.b_empty[i], 1);
+        }
         s.failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -299,129 +400,136 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
     tc_fence_after();
     const uint32_t tmem = s.tmem_base;
 
-    // decode role: weight row d_row of the CTA's 128, group d_g of the step's four
-    const uint32_t d_row = tid >> 2, d_g = tid & 3u;
-    const uint64_t d_blk0 = (uint64_t)(row0 + d_row) * B;
-    const uint32_t d_off = (d_row >> 3) * A_SBO + (2u * d_g) * A_LBO + (d_row & 7u) * 16u;
-    // scaling role: tensor-memory lanes of this warp's quadrant, 16 of the 64 columns
-    const uint32_t e_q = warp & 3u, e_cs = warp >> 2;
-    const uint32_t e_row = 32u * e_q + lane;
-    const uint32_t e_taddr = tmem + ((32u * e_q) << 16) + 16u * e_cs;
-
-    uint32_t gi = 0;        // steps issued so far by this CTA, across passes (buffer phases)
+    // A bounded wait that records its failure; afterwards the CTA keeps going with short waits.
     uint32_t wait_limit = WAIT_LIMIT;
-    for (int32_t rc = r0; rc < r1; rc += (int32_t)NB) {
-        const uint32_t nrows = min((uint32_t)(r1 - rc), NB);
-        const uint32_t n_mma = (nrows + 15u) & ~15u;
-        const uint32_t idesc = instr_desc(n_mma);
-        const bool e_live = 16u * e_cs < nrows;
-        // per output column two running sums, over the even and the odd groups, held as one
-        // packed pair so that a step's scaling is one packed multiply and one packed FMA per
-        // two groups; they are added once at the end
-        unsigned long long acc2[16];
-#pragma unroll
-        for (int j = 0; j < 16; j++) acc2[j] = 0ull;
-
-        // producer side of step `it` (global step index g): activations by TMA
-        auto issue_b = [&](uint32_t it, uint32_t g) {
-            const uint32_t sb = g % NSTAGE_B;
-            mbar_expect_tx(&s.bar_b[sb], B_BYTES + DA_BYTES);
-            tma_load_3d(s.b[sb], &map_q, &s.bar_b[sb], 0, rc, (int)(it * 8u));
-            tma_load_2d(&s.da[sb][0][0], &map_d, &s.bar_b[sb], (int)(it * 4u), rc);
-        };
-        auto load_fields = [&](uint32_t it) {
-            return iq3_fields<TILED>(mat, d_blk0 + (it >> 1), (it & 1u) * 4u + d_g);
-        };
-        auto decode_to = [&](const Iq3Fields &f, uint32_t buf) {
-            uint32_t wv[8];
-            decode_group_w<TILED>(f, s.tab2, wv);
-            uint8_t *p = s.a[buf] + d_off;
-            *reinterpret_cast<uint4 *>(p) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
-            *reinterpret_cast<uint4 *>(p + A_LBO) = make_uint4(wv[4], wv[5], wv[6], wv[7]);
-            s.sw[buf][d_g][d_row] = __fmul_rn((float)f.ls, f.d);
-        };
-        auto issue_mma = [&](uint32_t g) {   // one thread
-            const uint32_t buf = g & 1u, sb = g % NSTAGE_B;
-            if (!mbar_wait(&s.bar_b[sb], (g / NSTAGE_B) & 1u, wait_limit)) {
-                atomicOr(a.err, ERR_MMQ_TC | 1u);
-                s.failed = 1;
-            }
-            tc_fence_after();
-            const uint32_t a_addr = smem_u32(s.a[buf]), b_addr = smem_u32(s.b[sb]);
-#pragma unroll
-            for (uint32_t k = 0; k < 4; k++)
-                mma_i8(tmem + buf * 256u + k * NB, smem_desc(a_addr + 2u * k * A_LBO, A_LBO, A_SBO),
-                       smem_desc(b_addr + 2u * k * B_LBO, B_LBO, B_SBO), idesc);
-            mma_commit(&s.bar_mma[buf]);
-        };
-
-        // prologue: step 0 of this pass
-        if (tid == 0) {
-            issue_b(0, gi);
-            if (n_it > 1) issue_b(1, gi + 1);
+    auto wait = [&](unsigned long long *bar, uint32_t parity, uint32_t code) {
+        if (!mbar_wait(bar, parity, wait_limit)) {
+            atomicOr(a.err, ERR_MMQ_TC | code);
+            wait_limit = 1024u;
         }
-        // the fields of a step are fetched two steps before they are decoded
-        Iq3Fields fcur = load_fields(0);
-        Iq3Fields fnext = n_it > 1 ? load_fields(1) : fcur;
-        Iq3Fields fnext2 = n_it > 2 ? load_fields(2) : fcur;
-        decode_to(fcur, gi & 1u);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncthreads();
-        if (tid == 0) issue_mma(gi);
+    };
 
-        for (uint32_t it = 0; it < n_it; it++) {
-            const uint32_t g = gi + it, buf = g & 1u, sb = g % NSTAGE_B;
-            if (it + 1 < n_it) {
-                fcur = fnext;
-                fnext = fnext2;
-                if (it + 3 < n_it) fnext2 = load_fields(it + 3);
-                if (it + 2 < n_it && tid == 0) issue_b(it + 2, g + 2);
-                decode_to(fcur, buf ^ 1u);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    if (warp == NDW) {
+        // ---- the MMA warp (one lane): waits for both operands of a step, issues its MMAs, commits ----
+        if (lane == 0) {
+            const uint64_t a_d0 = smem_desc_sw128(smem_u32(s.a[0])), b_d0 = smem_desc_sw128(smem_u32(s.b[0][0]));
+            const uint32_t a_lo0 = (uint32_t)a_d0, a_hi = (uint32_t)(a_d0 >> 32);
+            const uint32_t b_lo0 = (uint32_t)b_d0, b_hi = (uint32_t)(b_d0 >> 32);
+            for (uint32_t it = 0; it < n_it; it++) {
+                const uint32_t buf = it % NA, sb = it % NSTAGE_B, sbk = it >> 1, accb = sbk % NACC;
+                // the accumulator of this super-block was read out NACC super-blocks ago
+                if ((it & 1u) == 0 && sbk >= NACC) wait(&s.acc_empty[accb], (sbk / NACC - 1u) & 1u, 4u);
+                wait(&s.a_full[buf], (it / NA) & 1u, 8u);
+                wait(&s.bar_b[sb], (it / NSTAGE_B) & 1u, 1u);
+                tc_fence_after();
+                // descriptors differ from step to step only in the start-address field (low word)
+                const uint32_t a_lo = a_lo0 + buf * (A_BYTES >> 4), b_lo = b_lo0 + sb * ((2u * B_ATOM) >> 4);
+                const uint32_t d_addr = tmem + accb * ACC_COLS;
+#pragma unroll
+                for (uint32_t k = 0; k < 8; k++)   // one MMA per 16 k: both planes are its N side
+                    mma_f16(d_addr, desc64(a_lo + (k >> 2) * (A_ATOM >> 4) + (k & 3u) * 2u, a_hi),
+                            desc64(b_lo + (k >> 2) * (B_ATOM >> 4) + (k & 3u) * 2u, b_hi), idesc,
+                            k ? 1u : (it & 1u));
+                mma_commit(&s.bar_mma[buf]);
+                mma_commit(&s.b_empty[sb]);
             }
-            __syncthreads();
-            if (it + 1 < n_it && tid == 0) issue_mma(g + 1);
-            // scaling of step it
-            if (!mbar_wait(&s.bar_mma[buf], (g >> 1) & 1u, wait_limit)) {
-                atomicOr(a.err, ERR_MMQ_TC | 2u);
-                s.failed = 1;
-            }
-            tc_fence_after();
-            if (e_live) {
-                const unsigned long long sw01 = pack2(s.sw[buf][0][e_row], s.sw[buf][1][e_row]);
-                const unsigned long long sw23 = pack2(s.sw[buf][2][e_row], s.sw[buf][3][e_row]);
+        }
+    } else if (warp == NDW + 1u) {
+        // ---- the copy warp (one lane): both activation planes of a step by TMA, NSTAGE_B - 1 ahead ----
+        if (lane == 0) {
+            for (uint32_t it = 0; it < n_it; it++) {
+                // the stage was last read by step it - NSTAGE_B
+                const uint32_t sb = it % NSTAGE_B;
+                if (it >= NSTAGE_B) wait(&s.b_empty[sb], (it / NSTAGE_B - 1u) & 1u, 16u);
+                mbar_expect_tx(&s.bar_b[sb], 4u * box * 128u);
 #pragma unroll
-                for (uint32_t h = 0; h < 2; h++) {       // two groups at a time ...
-#pragma unroll
-                    for (uint32_t cq = 0; cq < 2; cq++) {  // ... and eight columns: 16 accumulator words live
-                        int32_t c0[8], c1[8];
-                        tmem_ld8(e_taddr + buf * 256u + (2u * h) * NB + 8u * cq, c0);
-                        tmem_ld8(e_taddr + buf * 256u + (2u * h + 1u) * NB + 8u * cq, c1);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 8; j++) {
-                            const unsigned long long dq = *reinterpret_cast<const unsigned long long *>(
-                                &s.da[sb][16u * e_cs + 8u * cq + j][2u * h]);
-                            const unsigned long long t =
-                                mul2(pack2((float)c0[j], (float)c1[j]), h ? sw23 : sw01);
-                            acc2[8 * cq + j] = fma2(t, dq, acc2[8 * cq + j]);
-                        }
-                    }
+                for (uint32_t at = 0; at < 2; at++) {
+                    tma_load_2d(s.b[sb][at], &map_h1, &s.bar_b[sb], (int)(it * KS + at * 64u), rc);
+                    tma_load_2d(s.b[sb][at] + box * 128u, &map_h2, &s.bar_b[sb], (int)(it * KS + at * 64u), rc);
                 }
             }
-            tc_fence_before();
-            __syncthreads();
-            if (s.failed) wait_limit = 1024u;   // keep going to the end, without long waits
         }
-        gi += n_it;
+    } else {
+        // ---- the 16 decode + epilogue warps ----
+        // decode: a warp takes eight weight rows (one 8-row group of core matrices) x the step's
+        // four groups; lanes 8g..8g+7 hold group g, so a quarter warp's 16-byte stores of one K
+        // chunk are 128 contiguous bytes, and the warp's loads still cover 8 rows x 4 adjacent groups
+        const uint32_t d_row = (warp << 3) | (lane & 7u), d_g = lane >> 3;
+        const uint64_t d_blk0 = (uint64_t)(row0 + d_row) * B;
+        // swizzled position of 16-byte chunk j (0..3) of this thread's group: atom d_g / 2, row d_row,
+        // chunk (4 (d_g & 1) + j) ^ (row & 7)
+        const uint32_t d_base = (d_g >> 1) * A_ATOM + d_row * 128u;
+        const uint32_t d_c0 = 4u * (d_g & 1u), d_x = lane & 7u;
+        // epilogue: tensor-memory lanes of this warp's quadrant, 16 of the 64 columns
+        const uint32_t e_q = warp & 3u, e_cs = warp >> 2;
+        const uint32_t e_row = 32u * e_q + lane;
+        const uint32_t e_taddr = tmem + ((32u * e_q) << 16) + 16u * e_cs;
+        const bool e_live = 16u * e_cs < nrows;
+        float acc[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) acc[j] = 0.f;
+
+        auto load_fields = [&](uint32_t it) {
+            return raw_fields<TILED>(mat, d_blk0 + (it >> 1), (it & 1u) * 4u + d_g);
+        };
+        // step `done` has completed: its operand buffer is free; with an odd step the super-block's
+        // accumulator is complete and is folded into the running sums
+        auto retire = [&](uint32_t done) {
+            wait(&s.bar_mma[done % NA], (done / NA) & 1u, 2u);
+            if (done & 1u) {
+                const uint32_t sbk = done >> 1;
+                tc_fence_after();
+                if (e_live) {
+                    const float dr = s.dr[sbk & 3u][e_row];
+                    uint32_t v[16], v2[16];
+                    tmem_ld16(e_taddr + (sbk % NACC) * ACC_COLS, v);
+                    tmem_ld16(e_taddr + (sbk % NACC) * ACC_COLS + box, v2);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; j++)
+                        acc[j] = fmaf(dr, __uint_as_float(v[j]) + __uint_as_float(v2[j]), acc[j]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.acc_empty[sbk % NACC]);
+            }
+        };
+        // The fields of a step are fetched PF steps before they are decoded, into a slot that is
+        // never moved (the loop is unrolled by PF): a register move would wait for its load.
+        constexpr uint32_t PF = 4;
+        RawFields fq[PF];
+#pragma unroll
+        for (uint32_t u = 0; u < PF; u++) fq[u] = load_fields(u < n_it ? u : 0u);
+        for (uint32_t it0 = 0; it0 < n_it; it0 += PF) {
+#pragma unroll
+            for (uint32_t u = 0; u < PF; u++) {
+                const uint32_t it = it0 + u;
+                if (it >= n_it) break;
+                if (it >= NA) retire(it - NA);
+                {
+                    uint32_t hv[16];
+                    const Iq3Fields f = cook_fields((it & 1u) * 4u + d_g, fq[u]);
+                    decode_group_h<TILED>(f, s.tabk, hv);
+                    uint8_t *p = s.a[it % NA] + d_base;
+#pragma unroll
+                    for (uint32_t c = 0; c < 4; c++)
+                        *reinterpret_cast<uint4 *>(p + (((d_c0 + c) ^ d_x) << 4)) =
+                            make_uint4(hv[4 * c], hv[4 * c + 1], hv[4 * c + 2], hv[4 * c + 3]);
+                    if (d_g == 0 && (it & 1u) == 0) s.dr[(it >> 1) & 3u][d_row] = f.d;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&s.a_full[it % NA]);
+                if (it + PF < n_it) fq[u] = load_fields(it + PF);
+            }
+        }
+        for (uint32_t t = n_it > NA ? n_it - NA : 0u; t < n_it; t++) retire(t);
         if (e_live) {
             float *o = a.dst + (uint64_t)(rc + 16 * (int32_t)e_cs) * a.ld_dst + row0 + e_row;
+            const float *rs = a.rs + rc + 16 * (int32_t)e_cs;
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                float even, odd;
-                unpack2(acc2[j], even, odd);
-                if (16u * e_cs + j < nrows) o[(uint64_t)j * a.ld_dst] = even + odd;
-            }
+            for (int j = 0; j < 16; j++)
+                if (16u * e_cs + j < nrows) o[(uint64_t)j * a.ld_dst] = acc[j] * __ldg(rs + j);
         }
     }
     tc_fence_before();
@@ -430,6 +538,50 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS)
                      : "memory");
+    }
+}
+
+// The fp16 planes of the quantised activation rows: x = q * dq (the value the 8-bit row stands
+// for), divided by the power of two rs that brings the row's largest magnitude below 1, as
+// h1 = fp16(x / rs) and h2 = fp16(x / rs - h1).  One CTA per row.
+__global__ void __launch_bounds__(256) planes_k(const int8_t *__restrict__ q, const float *__restrict__ dq,
+                                                uint32_t cols, __half *__restrict__ h1, __half *__restrict__ h2,
+                                                float *__restrict__ rs) {
+    __shared__ float red[8];
+    const uint64_t row = blockIdx.x;
+    const uint32_t gpr = cols >> 5, tid = threadIdx.x;
+    const float *d = dq + row * gpr;
+    float m = 0.f;
+    for (uint32_t g = tid; g < gpr; g += 256u) m = fmaxf(m, d[g]);
+    m = q4b_warp_max(m);
+    if ((tid & 31u) == 0) red[tid >> 5] = m;
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; i++) m = fmaxf(m, red[i]);
+    int e = 0;
+    if (m > 0.f) (void)frexpf(m * 127.f, &e);   // 127 dq = the group's largest magnitude
+    const float inv = ldexpf(1.f, -e);
+    if (tid == 0) rs[row] = ldexpf(1.f, e);
+    const int8_t *qr = q + row * cols;
+    __half *o1 = h1 + row * cols, *o2 = h2 + row * cols;
+    for (uint32_t c = tid * 8u; c < cols; c += 2048u) {   // eight values per thread and turn
+        const uint2 w = *reinterpret_cast<const uint2 *>(qr + c);
+        const float sc = d[c >> 5] * inv;
+        uint32_t p1[4], p2[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const uint32_t word = i < 2 ? w.x : w.y;
+            const int qa = (int)(int8_t)(word >> (16 * (i & 1))), qb = (int)(int8_t)(word >> (16 * (i & 1) + 8));
+            const float xa = (float)qa * sc, xb = (float)qb * sc;
+            const __half2 a1 = __floats2half2_rn(xa, xb);
+            const float2 back = __half22float2(a1);
+            const __half2 a2 = __floats2half2_rn(xa - back.x, xb - back.y);
+            p1[i] = *reinterpret_cast<const uint32_t *>(&a1);
+            p2[i] = *reinterpret_cast<const uint32_t *>(&a2);
+        }
+        *reinterpret_cast<uint4 *>(o1 + c) = make_uint4(p1[0], p1[1], p1[2], p1[3]);
+        *reinterpret_cast<uint4 *>(o2 + c) = make_uint4(p2[0], p2[1], p2[2], p2[3]);
     }
 }
 
@@ -479,39 +631,31 @@ bool shape_ok(uint64_t w_rows, uint64_t w_cols) {
     return w_rows != 0 && (w_rows % MT) == 0 && w_cols != 0 && (w_cols % 256u) == 0 && w_cols <= 65536u;
 }
 
-// q: int8 [rows][cols] row-major; d: float [rows][cols/32].
+// q: int8 [rows][cols] row-major; dq: float [rows][cols/32]; h1, h2: fp16 [rows][cols] and
+// rs: float [rows], scratch this call fills (planes_k) before the product reads it.
 bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const uint32_t *n_act,
-            uint32_t n_entries, const int32_t *bounds, const int8_t *q, const float *dq, uint64_t rows,
-            uint32_t cols, uint32_t w_rows, float *dst, uint64_t ld_dst, bool tiled, uint32_t min_rows,
-            cudaStream_t stream) {
+            uint32_t n_entries, const int32_t *bounds, const int8_t *q, const float *dq, __half *h1,
+            __half *h2, float *rs, uint64_t rows, uint32_t cols, uint32_t w_rows, float *dst,
+            uint64_t ld_dst, bool tiled, uint32_t min_rows, cudaStream_t stream) {
     if (!g_ready || !shape_ok(w_rows, cols) || rows == 0 || rows > 0x7fffffffull) return false;
     // a small call (decode batches: a handful of entries reach the threshold) is cut into
     // passes of 16 rows so that its few entries still spread over many SMs
     const uint32_t pass_rows = rows <= 2048u ? 16u : NB;
     const uint64_t max_items = (uint64_t)n_entries + rows / pass_rows;
     if (max_items > WORK_CAP) return false;
-    CUtensorMap map_q, map_d;
-    {
-        // (16 bytes, row, 16-byte chunk of the row): a box lands as [chunk][row][16 B]
-        const cuuint64_t dims[3] = {16, rows, cols / 16u};
-        const cuuint64_t strides[2] = {cols, 16};
-        const cuuint32_t box[3] = {16, NB, 8};
-        const cuuint32_t es[3] = {1, 1, 1};
-        if (g_encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, (void *)q, dims, strides, box, es,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+    CUtensorMap maps[2];
+    for (int pl = 0; pl < 2; pl++) {
+        // rows of fp16; a box is 64 k (128 bytes) of NB rows, stored with the 128-byte swizzle
+        const cuuint64_t dims[2] = {cols, rows};
+        const cuuint64_t strides[1] = {(cuuint64_t)cols * 2u};
+        const cuuint32_t box[2] = {64, pass_rows < NB ? pass_rows : NB};
+        const cuuint32_t es[2] = {1, 1};
+        if (g_encode(&maps[pl], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (void *)(pl ? h2 : h1), dims, strides, box, es,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return false;
     }
-    {
-        const cuuint64_t dims[2] = {cols / 32u, rows};
-        const cuuint64_t strides[1] = {(cuuint64_t)(cols / 32u) * 4u};
-        const cuuint32_t box[2] = {4, NB};
-        const cuuint32_t es[2] = {1, 1};
-        if (g_encode(&map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)dq, dims, strides, box, es,
-                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
-                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return false;
-    }
+    planes_k<<<(unsigned)rows, 256, 0, stream>>>(q, dq, cols, h1, h2, rs);
     Args a;
     a.w = w;
     a.expert_stride = expert_stride;
@@ -529,13 +673,15 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
     a.work = g_work + turn * WORK_CAP;
     a.n_work = g_n_work + turn;
     a.pass_rows = pass_rows;
+    a.rs = rs;
+    a.box_rows = pass_rows < NB ? pass_rows : NB;
     worklist_k<<<1, 1024, 0, stream>>>(bounds, n_act, n_entries, min_rows, g_work + turn * WORK_CAP,
                                             g_n_work + turn, WORK_CAP, pass_rows);
     const dim3 grid(w_rows / MT, (unsigned)max_items);
     if (tiled)
-        mmq_tc_k<true><<<grid, NT, SMEM_BYTES, stream>>>(a, map_q, map_d);
+        mmq_tc_k<true><<<grid, NT, SMEM_BYTES, stream>>>(a, maps[0], maps[1]);
     else
-        mmq_tc_k<false><<<grid, NT, SMEM_BYTES, stream>>>(a, map_q, map_d);
+        mmq_tc_k<false><<<grid, NT, SMEM_BYTES, stream>>>(a, maps[0], maps[1]);
     return true;
 }
 
