@@ -291,12 +291,12 @@ __global__ void expert_reduce_k(float *__restrict__ y, const float *__restrict__
         y[(uint64_t)t * n_embd + c] = 0.f + acc;
 }
 
-// One block (256 threads) per group of gsz tokens: a stable counting sort of the group's
-// picks by expert.  Each warp owns a contiguous run of picks; per-warp histograms, a
+// One block (256 threads, or 1024 for a large group) per group of gsz tokens: a stable counting
+// sort of the group's picks by expert.  Each warp owns a contiguous run of picks; per-warp histograms, a
 // prefix over warps and over experts, then every warp places its own run 32 picks at a
 // time, each lane finding its place among the lanes of the warp that picked the same
 // expert.  Rows of one expert therefore keep (token, pick) order.
-__global__ void __launch_bounds__(256) assign_k(
+__global__ void __launch_bounds__(1024) assign_k(
     const int32_t *__restrict__ ids, const float *__restrict__ wts, int32_t *__restrict__ a_tok,
     int32_t *__restrict__ rsrc, float *__restrict__ rw, int32_t *__restrict__ stg,
     uint32_t *__restrict__ stgn, uint32_t *__restrict__ ek, int32_t *__restrict__ cbounds,
@@ -309,12 +309,13 @@ __global__ void __launch_bounds__(256) assign_k(
     // own_count) are placed, renumbered from 0, and the extra pick only for tokens
     // [tok_first, tok_first + tok_count).  bounds_full (optional) receives the first row of
     // every expert and the total: n_exp + 1 values.  Rows of a_tok beyond the total get -1.
-    extern __shared__ uint32_t sh[];  // hist[8][n_exp], cnt[n_exp], rank[n_exp], wsum[16]
-    uint32_t *hist = sh, *cnt = sh + 8u * n_exp, *rank = cnt + n_exp, *wsum = rank + n_exp;
+    extern __shared__ uint32_t sh[];  // hist[nw][n_exp], cnt[n_exp], rank[n_exp], wsum[40]
+    const uint32_t nw = blockDim.x >> 5;
+    uint32_t *hist = sh, *cnt = sh + nw * n_exp, *rank = cnt + n_exp, *wsum = rank + n_exp;
     const uint32_t g = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t t0 = g * gsz, t1 = min(t0 + gsz, n_tok);
     const uint32_t seg = g * gsz * topk, rows = (t1 - t0) * topk;
-    const uint32_t run = ((rows + 7u) / 8u + 31u) & ~31u;  // picks per warp, a multiple of 32
+    const uint32_t run = ((rows + nw - 1u) / nw + 31u) & ~31u;  // picks per warp, a multiple of 32
     const uint32_t i_lo = warp * run, i_hi = min(rows, i_lo + run);
     auto pick_id = [&](uint32_t i) -> int32_t {   // i = pick index within the group
         const uint32_t t = i / topk, k = i - t * topk;
@@ -327,17 +328,21 @@ __global__ void __launch_bounds__(256) assign_k(
         }
         return e;
     };
-    for (uint32_t i = tid; i < 8u * n_exp; i += blockDim.x) hist[i] = 0;
+    for (uint32_t i = tid; i < nw * n_exp; i += blockDim.x) hist[i] = 0;
     __syncthreads();
-    for (uint32_t i = i_lo + lane; i < i_hi; i += 32u) {
-        const int32_t e = pick_id(i);
-        if (e >= 0 && (uint32_t)e < n_exp) atomicAdd(&hist[warp * n_exp + e], 1u);
+    for (uint32_t i0 = i_lo; i0 < i_hi; i0 += 32u) {   // one add per distinct expert of the 32 picks
+        const uint32_t i = i0 + lane;
+        int32_t e = i < i_hi ? pick_id(i) : -1;
+        if (e < 0 || (uint32_t)e >= n_exp) e = -1;
+        const uint32_t same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0 && (same & ((1u << lane) - 1u)) == 0) hist[warp * n_exp + e] += __popc(same);
+        __syncwarp();
     }
     __syncthreads();
     // per expert: exclusive prefix over the warps, total in cnt
     for (uint32_t e = tid; e < n_exp; e += blockDim.x) {
         uint32_t tot = 0;
-        for (uint32_t wv = 0; wv < 8u; wv++) {
+        for (uint32_t wv = 0; wv < nw; wv++) {
             const uint32_t c = hist[wv * n_exp + e];
             hist[wv * n_exp + e] = tot;
             tot += c;
@@ -385,13 +390,13 @@ __global__ void __launch_bounds__(256) assign_k(
     if (tid == blockDim.x - 1u) {  // totals
         if (cbounds) cbounds[g * (ek_stride + 1) + nu] = (int32_t)b;
         if (stgn) stgn[g] = nu;
-        wsum[8] = b;
+        wsum[32] = b;
     }
     __syncthreads();
     if (bounds_full)
         for (uint32_t e = tid; e <= n_exp; e += blockDim.x)
-            bounds_full[g * (n_exp + 1) + e] = (int32_t)(e < n_exp ? rank[e] : wsum[8]);
-    for (uint32_t i = wsum[8] + tid; i < rows; i += blockDim.x) a_tok[seg + i] = -1;   // unused rows
+            bounds_full[g * (n_exp + 1) + e] = (int32_t)(e < n_exp ? rank[e] : wsum[32]);
+    for (uint32_t i = wsum[32] + tid; i < rows; i += blockDim.x) a_tok[seg + i] = -1;   // unused rows
     for (uint32_t i0 = i_lo; i0 < i_hi; i0 += 32u) {
         const uint32_t i = i0 + lane;
         int32_t e = -1;
@@ -594,7 +599,14 @@ bool shape_ok(uint32_t type, uint64_t w_rows, uint64_t w_cols) {
 
 using namespace grouped;
 
+// shared memory of assign_k with 32 warps and 1024 experts; the limit is raised once, at warm-up
+constexpr size_t ASSIGN_SMEM_MAX = (34u * 1024u + 48u) * sizeof(uint32_t);
 bool q4b_mmq_tc_warm() {
+    if (cudaFuncSetAttribute(assign_k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ASSIGN_SMEM_MAX) !=
+        cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
     const bool f = few::warm();
     return mmqtc::warm() && f;
 }
@@ -691,7 +703,12 @@ static bool launch_assign(const int32_t *d_ids, const float *d_wts, int32_t *d_a
                           int32_t extra_id = -1, int32_t own_first = 0, uint32_t own_count = 0,
                           uint32_t tok_first = 0, uint32_t tok_count = 0, int32_t *d_bounds_full = nullptr) {
     const uint32_t n_g = (n_tok + gsz - 1u) / gsz;
-    assign_k<<<n_g, 256, (10 * n_exp + 16) * sizeof(uint32_t), g_q4b.stream>>>(
+    // a large group gets 32 warps (a histogram per warp: up to 34 x n_exp words of shared memory)
+    const uint64_t rows = (uint64_t)(gsz < n_tok ? gsz : n_tok) * topk;
+    const uint32_t nt = rows > 4096u ? 1024u : 256u;
+    const size_t sm = ((nt / 32u + 2u) * n_exp + 48u) * sizeof(uint32_t);
+    if (sm > ASSIGN_SMEM_MAX) return false;
+    assign_k<<<n_g, nt, sm, g_q4b.stream>>>(
         d_ids, d_wts, d_atok, d_rsrc, d_rw, d_stg, d_stgn, d_ek, d_cbounds, gsz, topk, n_exp, n_tok,
         ek_stride, topk_in ? topk_in : topk, extra_id, own_first, own_count, tok_first, tok_count,
         d_bounds_full);
