@@ -30,7 +30,7 @@
 //                     shared memory under the 128-byte swizzle (the layout TMA writes for the
 //                     other operand; a quarter warp's 16-byte stores hit eight different
 //                     16-byte columns); the fields of a step are loaded four steps ahead
-//                     into registers that are never moved (the loop is unrolled by four)
+//                     into registers that are never moved (the loop is unrolled by the prefetch depth)
 //   copy warp         the two fp16 planes of the activation rows as [rows][128 B] TMA boxes
 //                     under the 128-byte swizzle, second plane stored right behind the first,
 //                     so that one MMA takes both as its N side
@@ -233,6 +233,7 @@ struct Args {
     const uint32_t *n_work;
     uint32_t pass_rows;          // activation rows per pass: 64, or 16 to spread a small call over more CTAs
     uint32_t box_rows;           // rows per activation copy = the MMA's N per plane
+    uint32_t mt_per_cta;         // 128-row weight tiles one CTA walks (grid.x = tiles / this)
     const float *rs;             // per activation row: the power of two its fp16 planes were divided by
 };
 
@@ -369,7 +370,9 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
     const uint32_t B = a.cols >> 8;                 // super-blocks per weight row
     const uint32_t n_it = a.cols / KS;              // steps (even: two per super-block)
     const uint8_t *mat = a.w + (uint64_t)(a.act ? a.act[entry] : (int32_t)entry) * a.expert_stride;
-    const uint32_t row0 = blockIdx.x * MT;
+    const uint32_t n_mt = a.mt_per_cta;             // 128-row tiles of weight rows this CTA walks
+    const uint32_t row0 = blockIdx.x * MT * n_mt;
+    const uint32_t n_s = n_it * n_mt;               // steps over all its tiles: one pipeline
     const uint32_t nrows = (uint32_t)(r1 - rc);
     const uint32_t box = a.box_rows;                // rows a copy brings: 64, or 16 for the small passes
     const uint32_t idesc = instr_desc(2u * box);
@@ -415,7 +418,7 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
             const uint64_t a_d0 = smem_desc_sw128(smem_u32(s.a[0])), b_d0 = smem_desc_sw128(smem_u32(s.b[0][0]));
             const uint32_t a_lo0 = (uint32_t)a_d0, a_hi = (uint32_t)(a_d0 >> 32);
             const uint32_t b_lo0 = (uint32_t)b_d0, b_hi = (uint32_t)(b_d0 >> 32);
-            for (uint32_t it = 0; it < n_it; it++) {
+            for (uint32_t it = 0; it < n_s; it++) {   // it: step over all tiles
                 const uint32_t buf = it % NA, sb = it % NSTAGE_B, sbk = it >> 1, accb = sbk % NACC;
                 // the accumulator of this super-block was read out NACC super-blocks ago
                 if ((it & 1u) == 0 && sbk >= NACC) wait(&s.acc_empty[accb], (sbk / NACC - 1u) & 1u, 4u);
@@ -437,10 +440,11 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
     } else if (warp == NDW + 1u) {
         // ---- the copy warp (one lane): both activation planes of a step by TMA, NSTAGE_B - 1 ahead ----
         if (lane == 0) {
-            for (uint32_t it = 0; it < n_it; it++) {
-                // the stage was last read by step it - NSTAGE_B
-                const uint32_t sb = it % NSTAGE_B;
-                if (it >= NSTAGE_B) wait(&s.b_empty[sb], (it / NSTAGE_B - 1u) & 1u, 16u);
+            uint32_t it = 0;   // step within the tile: every tile reads the same rows again
+            for (uint32_t st = 0; st < n_s; st++, it = it + 1u == n_it ? 0u : it + 1u) {
+                // the stage was last read by step st - NSTAGE_B
+                const uint32_t sb = st % NSTAGE_B;
+                if (st >= NSTAGE_B) wait(&s.b_empty[sb], (st / NSTAGE_B - 1u) & 1u, 16u);
                 mbar_expect_tx(&s.bar_b[sb], 4u * box * 128u);
 #pragma unroll
                 for (uint32_t at = 0; at < 2; at++) {
@@ -455,7 +459,7 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
         // four groups; lanes 8g..8g+7 hold group g, so a quarter warp's 16-byte stores of one K
         // chunk are 128 contiguous bytes, and the warp's loads still cover 8 rows x 4 adjacent groups
         const uint32_t d_row = (warp << 3) | (lane & 7u), d_g = lane >> 3;
-        const uint64_t d_blk0 = (uint64_t)(row0 + d_row) * B;
+        const uint32_t d_blk0 = (row0 + d_row) * B;   // in tile m: + m * MT * B (a matrix has < 2^32 blocks)
         // swizzled position of 16-byte chunk j (0..3) of this thread's group: atom d_g / 2, row d_row,
         // chunk (4 (d_g & 1) + j) ^ (row & 7)
         const uint32_t d_base = (d_g >> 1) * A_ATOM + d_row * 128u;
@@ -469,9 +473,18 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
 #pragma unroll
         for (int j = 0; j < 16; j++) acc[j] = 0.f;
 
-        auto load_fields = [&](uint32_t it) {
-            return raw_fields<TILED>(mat, d_blk0 + (it >> 1), (it & 1u) * 4u + d_g);
+        // steps are fetched in order: (tile, step in tile) advance by counters, not divisions
+        uint32_t pf_it = 0;
+        uint32_t pf_blk = d_blk0;   // first block of this thread's row in the tile being fetched
+        auto load_next_fields = [&]() {
+            const RawFields r = raw_fields<TILED>(mat, (uint64_t)(pf_blk + (pf_it >> 1)), (pf_it & 1u) * 4u + d_g);
+            if (++pf_it == n_it) {
+                pf_it = 0;
+                pf_blk += MT * B;
+            }
+            return r;
         };
+        uint32_t rt_it = 0, rt_m = 0;   // (step in tile, tile) of the next step to retire
         // step `done` has completed: its operand buffer is free; with an odd step the super-block's
         // accumulator is complete and is folded into the running sums
         auto retire = [&](uint32_t done) {
@@ -492,19 +505,37 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s.acc_empty[sbk % NACC]);
+                if (rt_it + 1u == n_it) {   // the tile's last super-block: write its rows out
+                    if (e_live) {
+                        const uint32_t m = rt_m;
+                        float *o = a.dst + (uint64_t)(rc + 16 * (int32_t)e_cs) * a.ld_dst + row0 + m * MT + e_row;
+                        const float *rs = a.rs + rc + 16 * (int32_t)e_cs;
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (16u * e_cs + j < nrows) o[(uint64_t)j * a.ld_dst] = acc[j] * __ldg(rs + j);
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; j++) acc[j] = 0.f;
+                }
+            }
+            if (++rt_it == n_it) {
+                rt_it = 0;
+                rt_m++;
             }
         };
         // The fields of a step are fetched PF steps before they are decoded, into a slot that is
         // never moved (the loop is unrolled by PF): a register move would wait for its load.
-        constexpr uint32_t PF = 4;
+        constexpr uint32_t PF = 3;
         RawFields fq[PF];
 #pragma unroll
-        for (uint32_t u = 0; u < PF; u++) fq[u] = load_fields(u < n_it ? u : 0u);
-        for (uint32_t it0 = 0; it0 < n_it; it0 += PF) {
+        for (uint32_t u = 0; u < PF; u++)
+            if (u < n_s) fq[u] = load_next_fields();
+            else fq[u] = fq[0];
+        for (uint32_t it0 = 0; it0 < n_s; it0 += PF) {
 #pragma unroll
             for (uint32_t u = 0; u < PF; u++) {
-                const uint32_t it = it0 + u;
-                if (it >= n_it) break;
+                const uint32_t it = it0 + u;   // step over all tiles; steps per tile are even
+                if (it >= n_s) break;
                 if (it >= NA) retire(it - NA);
                 {
                     uint32_t hv[16];
@@ -520,17 +551,10 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s.a_full[it % NA]);
-                if (it + PF < n_it) fq[u] = load_fields(it + PF);
+                if (it + PF < n_s) fq[u] = load_next_fields();
             }
         }
-        for (uint32_t t = n_it > NA ? n_it - NA : 0u; t < n_it; t++) retire(t);
-        if (e_live) {
-            float *o = a.dst + (uint64_t)(rc + 16 * (int32_t)e_cs) * a.ld_dst + row0 + e_row;
-            const float *rs = a.rs + rc + 16 * (int32_t)e_cs;
-#pragma unroll
-            for (int j = 0; j < 16; j++)
-                if (16u * e_cs + j < nrows) o[(uint64_t)j * a.ld_dst] = acc[j] * __ldg(rs + j);
-        }
+        for (uint32_t t = n_s > NA ? n_s - NA : 0u; t < n_s; t++) retire(t);
     }
     tc_fence_before();
     __syncthreads();
@@ -677,7 +701,14 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
     a.box_rows = pass_rows < NB ? pass_rows : NB;
     worklist_k<<<1, 1024, 0, stream>>>(bounds, n_act, n_entries, min_rows, g_work + turn * WORK_CAP,
                                             g_n_work + turn, WORK_CAP, pass_rows);
-    const dim3 grid(w_rows / MT, (unsigned)max_items);
+    // a CTA walks enough 128-row tiles of its pass for about 16 steps: start-up (work item,
+    // table, pipeline fill) is then paid once per 16 steps also where a tile has few (K = 512: 4)
+    const uint32_t n_tiles = w_rows / MT, n_it = cols / KS;
+    uint32_t mt = 1;
+    for (uint32_t c = 1; c <= n_tiles && c * n_it <= 16u; c++)
+        if (n_tiles % c == 0) mt = c;
+    a.mt_per_cta = mt;
+    const dim3 grid(n_tiles / mt, (unsigned)max_items);
     if (tiled)
         mmq_tc_k<true><<<grid, NT, SMEM_BYTES, stream>>>(a, maps[0], maps[1]);
     else
