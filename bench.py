@@ -312,6 +312,8 @@ class EpJob:
     def __init__(self, pkg, dev, ep, arena, rank, world, n_layers, tokens=EP_TOKENS, zipf=False):
         import ctypes
         self.lib = lib = dev.lib
+        if os.environ.get("Q4B_TC_MODE"):   # experiments: which grouped-product kernel runs (default: split by rows)
+            assert lib.q4_cuda_mmq_tc_mode(int(os.environ["Q4B_TC_MODE"]))
         self.ep, self.world, self.n_layers, self.arena = ep, world, n_layers, arena
         self.tokens = tokens
         self.t_local = tokens // world
