@@ -145,15 +145,16 @@ __global__ void __launch_bounds__(256) gemv_f32_x16_k(const float *__restrict__ 
 
 // fp32 product for many tokens at once (the router over a batch): y[t][e] = scale *
 // sum_h x[t][h] W[e][h].  Shared-memory tiles of BM tokens x 64 weight rows x 16 columns,
-// 256 threads, thread (ty, tx) owns BM/16 tokens x 4 weight rows; h runs in ascending
-// order inside every thread.  nrows % 64 == 0 and ncols % 16 == 0.
+// 256 threads, thread (ty, tx) owns BM/16 tokens x 4 weight rows (its tokens' values come as
+// float4 from the transposed tile); h runs in ascending order inside every thread.  nrows % 64 == 0 and ncols % 16 == 0.
 template <int BM>
 __global__ void __launch_bounds__(256) gemm_f32_nt_k(const float *__restrict__ W, uint32_t nrows,
                                                      uint32_t ncols, const float *__restrict__ X,
                                                      uint32_t n_tok, float *__restrict__ Y, float scale) {
-    constexpr int TM = BM / 16;
-    __shared__ float As[16][BM + 4];
-    __shared__ float Bs[16][64 + 4];
+    constexpr int TM = BM / 16;      // tokens per thread: 4 or 8
+    constexpr int NA = BM / 64;      // loader passes over the token tile
+    __shared__ __align__(16) float As[16][BM + 4];
+    __shared__ __align__(16) float Bs[16][64 + 4];
     const uint32_t tid = threadIdx.x, tx = tid & 15u, ty = tid >> 4;
     const uint32_t e0 = blockIdx.x * 64u, t0 = blockIdx.y * BM;
     const uint32_t lr = tid >> 2, lc = (tid & 3u) * 4u;   // loader: row of the tile, first of 4 columns
@@ -162,25 +163,39 @@ __global__ void __launch_bounds__(256) gemm_f32_nt_k(const float *__restrict__ W
     for (int i = 0; i < TM; i++)
 #pragma unroll
         for (int j = 0; j < 4; j++) acc[i][j] = 0.f;
-    const bool a_live = lr < (uint32_t)BM && t0 + lr < n_tok;
-    const float *xa = X + (uint64_t)(t0 + (a_live ? lr : 0u)) * ncols + lc;
+    const float *xa[NA];
+    bool a_live[NA];
+    float4 va[NA], vb;
+#pragma unroll
+    for (int p = 0; p < NA; p++) {
+        a_live[p] = t0 + lr + 64u * p < n_tok;
+        xa[p] = X + (uint64_t)(t0 + (a_live[p] ? lr + 64u * p : 0u)) * ncols + lc;
+        va[p] = a_live[p] ? *reinterpret_cast<const float4 *>(xa[p]) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     const float *wb = W + (uint64_t)(e0 + lr) * ncols + lc;
-    float4 va = make_float4(0.f, 0.f, 0.f, 0.f), vb;
-    if (a_live) va = *reinterpret_cast<const float4 *>(xa);
     vb = __ldg(reinterpret_cast<const float4 *>(wb));
     for (uint32_t h0 = 0; h0 < ncols; h0 += 16u) {
-        if (lr < (uint32_t)BM) As[lc][lr] = va.x, As[lc + 1][lr] = va.y, As[lc + 2][lr] = va.z, As[lc + 3][lr] = va.w;
+#pragma unroll
+        for (int p = 0; p < NA; p++) {
+            const uint32_t r = lr + 64u * p;
+            As[lc][r] = va[p].x, As[lc + 1][r] = va[p].y, As[lc + 2][r] = va[p].z, As[lc + 3][r] = va[p].w;
+        }
         Bs[lc][lr] = vb.x, Bs[lc + 1][lr] = vb.y, Bs[lc + 2][lr] = vb.z, Bs[lc + 3][lr] = vb.w;
         __syncthreads();
         if (h0 + 16u < ncols) {   // the next tile's loads fly under this tile's products
-            if (a_live) va = *reinterpret_cast<const float4 *>(xa + h0 + 16u);
+#pragma unroll
+            for (int p = 0; p < NA; p++)
+                if (a_live[p]) va[p] = *reinterpret_cast<const float4 *>(xa[p] + h0 + 16u);
             vb = __ldg(reinterpret_cast<const float4 *>(wb + h0 + 16u));
         }
 #pragma unroll
         for (int k = 0; k < 16; k++) {
             float a[TM];
 #pragma unroll
-            for (int i = 0; i < TM; i++) a[i] = As[k][ty * TM + i];
+            for (int i = 0; i < TM; i += 4) {
+                const float4 t = *reinterpret_cast<const float4 *>(&As[k][ty * TM + i]);
+                a[i] = t.x, a[i + 1] = t.y, a[i + 2] = t.z, a[i + 3] = t.w;
+            }
             const float4 b = *reinterpret_cast<const float4 *>(&Bs[k][tx * 4u]);
 #pragma unroll
             for (int i = 0; i < TM; i++) {
@@ -861,7 +876,7 @@ extern "C" bool q4_hip_gemv_dd_n(uint32_t ggml_type, const uint8_t *d_w, uint64_
     if (ggml_type == Q4_T_F32 && n_batch >= 512 && (nrows % 64u) == 0 && (ncols % 16u) == 0 &&
         nrows <= 0xffffffffull && ncols <= 0xffffffffull) {
         // a large batch: one tiled product instead of n_batch matrix-vector passes over W
-        gemm_f32_nt_k<64><<<dim3((unsigned)(nrows / 64), (n_batch + 63) / 64), 256, 0, g_q4b.stream>>>(
+        gemm_f32_nt_k<128><<<dim3((unsigned)(nrows / 64), (n_batch + 127) / 128), 256, 0, g_q4b.stream>>>(
             reinterpret_cast<const float *>(d_w), (uint32_t)nrows, (uint32_t)ncols, d_x, n_batch, d_y, scale);
     } else if (ggml_type == Q4_T_F32 && n_batch >= 2 && ncols == 2048) {
         gemv_f32_x16_k<<<dim3((unsigned)((nrows + 7) / 8), (n_batch + 15) / 16), 256, 0, g_q4b.stream>>>(
