@@ -354,6 +354,17 @@ __device__ __forceinline__ Iq3Fields cook_fields(uint32_t ib, const RawFields &r
     return f;
 }
 
+// A thread's 16 finished sums of one weight row: out[j] = v[j] * rs[j] for the first n columns.
+// Not inlined: it runs once per tile, and inlined into the unrolled step loop its predicated
+// stores were issued every step (a third more instructions).
+__device__ __noinline__ void store_tile(float *o, uint64_t ld, const float *rs, uint32_t n, float4 a0, float4 a1,
+                                        float4 a2, float4 a3) {
+    const float v[16] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w, a2.x, a2.y, a2.z, a2.w, a3.x, a3.y, a3.z, a3.w};
+#pragma unroll
+    for (int j = 0; j < 16; j++)
+        if ((uint32_t)j < n) o[(uint64_t)j * ld] = v[j] * __ldg(rs + j);
+}
+
 template <bool TILED>
 __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_constant__ CUtensorMap map_h1,
                                                   const __grid_constant__ CUtensorMap map_h2) {
@@ -506,14 +517,12 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s.acc_empty[sbk % NACC]);
                 if (rt_it + 1u == n_it) {   // the tile's last super-block: write its rows out
-                    if (e_live) {
-                        const uint32_t m = rt_m;
-                        float *o = a.dst + (uint64_t)(rc + 16 * (int32_t)e_cs) * a.ld_dst + row0 + m * MT + e_row;
-                        const float *rs = a.rs + rc + 16 * (int32_t)e_cs;
-#pragma unroll
-                        for (int j = 0; j < 16; j++)
-                            if (16u * e_cs + j < nrows) o[(uint64_t)j * a.ld_dst] = acc[j] * __ldg(rs + j);
-                    }
+                    if (e_live)
+                        store_tile(a.dst + (uint64_t)(rc + 16 * (int32_t)e_cs) * a.ld_dst + row0 + rt_m * MT + e_row,
+                                   a.ld_dst, a.rs + rc + 16 * (int32_t)e_cs, min(16u, nrows - 16u * e_cs),
+                                   make_float4(acc[0], acc[1], acc[2], acc[3]), make_float4(acc[4], acc[5], acc[6], acc[7]),
+                                   make_float4(acc[8], acc[9], acc[10], acc[11]),
+                                   make_float4(acc[12], acc[13], acc[14], acc[15]));
 #pragma unroll
                     for (int j = 0; j < 16; j++) acc[j] = 0.f;
                 }
