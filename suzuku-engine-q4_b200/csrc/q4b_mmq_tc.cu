@@ -534,7 +534,9 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
         };
         // The fields of a step are fetched PF steps before they are decoded, into a slot that is
         // never moved (the loop is unrolled by PF): a register move would wait for its load.
-        constexpr uint32_t PF = 3;
+        // (measured: 2 steps ahead 1.15 ms per prefill step, 3 ahead 1.17 - an odd unroll makes the step's
+        // parity a run-time value in every stage -, 4 ahead spills)
+        constexpr uint32_t PF = 2;
         RawFields fq[PF];
 #pragma unroll
         for (uint32_t u = 0; u < PF; u++)
