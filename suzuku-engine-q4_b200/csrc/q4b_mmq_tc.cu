@@ -29,8 +29,9 @@
 //   16 warps          decode 128 rows x 4 groups of IQ3_S into fp16 rows of 128 bytes in
 //                     shared memory under the 128-byte swizzle (the layout TMA writes for the
 //                     other operand; a quarter warp's 16-byte stores hit eight different
-//                     16-byte columns); the fields of a step are loaded four steps ahead
-//                     into registers that are never moved (the loop is unrolled by the prefetch depth)
+//                     16-byte columns); the fields of a step are loaded two steps ahead
+//                     into registers that are never moved (the loop is unrolled by two);
+//                     a CTA walks several 128-row tiles of its pass in one pipeline
 //   copy warp         the two fp16 planes of the activation rows as [rows][128 B] TMA boxes
 //                     under the 128-byte swizzle, second plane stored right behind the first,
 //                     so that one MMA takes both as its N side
