@@ -326,3 +326,24 @@ def test_host_memory_helpers_and_declined_calls(dev):
     assert not lib.q4_mmq_wbuf(1 << 18, 1 << 18, 5, C.byref(p_gu), C.byref(p_d))       # too small: refused
     assert lib.q4_mmq_wbuf_lend(None, 0, None, 0)
     assert not lib.q4_mmq_wbuf(16, 16, 1, C.byref(p_gu), C.byref(p_d))                 # dropped: refused
+
+
+@pytest.mark.parametrize("n_batch", [1, 5, 64, 600])
+def test_batched_fp32_gemv_all_kernel_paths(dev, n_batch):
+    """q4_hip_gemv_dd_n on the router's shape (src/q4.h:1069-1071): one vector per launch row, 16 vectors
+    per weight row held in registers, and from 512 vectors on a tiled product (the last token tile ragged)."""
+    rng = np.random.default_rng(n_batch)
+    lib = dev.lib
+    nrows, ncols = 512, 2048
+    w = (rng.standard_normal((nrows, ncols)) * 0.02).astype(np.float32)
+    x = rng.standard_normal((n_batch, ncols)).astype(np.float32)
+    d_y = dev.malloc(n_batch * nrows * 4)
+    assert lib.q4_hip_gemv_dd_n(F32, dev.upload(w), nrows, ncols, dev.upload(x), d_y, 0.5, n_batch)
+    y = dev.download(d_y, (n_batch, nrows), np.float32)
+    want = 0.5 * (x.astype(np.float64) @ w.astype(np.float64).T)
+    assert _rel(y, want) < 2e-6
+    assert np.abs(y - want).max() <= 1e-5 * np.abs(want).max()
+    # a vector's logits do not depend on the batch it came in, beyond the summation order
+    d_y1 = dev.malloc(nrows * 4)
+    assert lib.q4_hip_gemv_dd_n(F32, dev.upload(w), nrows, ncols, dev.upload(x[n_batch - 1]), d_y1, 0.5, 1)
+    assert _rel(dev.download(d_y1, (nrows,), np.float32), y[n_batch - 1]) < 2e-6
