@@ -492,7 +492,7 @@ bool q4_cuda_assign_local(const int32_t *d_ids, const float *d_wts, int32_t *d_a
 
 /* Which grouped product q4_mmq_mul_id and q4_cuda_moe_layer_n run (no reference
  * counterpart; the reference picks its tile kernel by row count inside q4_mmq_mul_id,
- * src/q4_mmq.cu:387-470): -1 = by size (experts with 8 rows or more go to the tensor-core
+ * src/q4_mmq.cu:387-470): -1 = by size (experts with 12 rows or more go to the tensor-core
  * kernel when the weight rows are a multiple of 128; the others to the streaming CUDA-core
  * kernel on tiled arenas, else to the general CUDA-core kernel),
  * 0 = CUDA-core kernels only, 1 = the tensor-core kernel whenever the shape allows,

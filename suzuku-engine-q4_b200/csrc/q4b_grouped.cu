@@ -514,13 +514,15 @@ bool launch_grouped(const uint8_t *w, uint64_t expert_stride, const int32_t *act
 // the streaming kernel; each kernel skips the other's entries.
 int g_tc_mode = -1;  // -1 split by rows, 0 CUDA cores only, 1 tensor cores whenever the shape
                      // allows, 2 the general CUDA-core kernel only
-// An entry goes to the tensor cores from 8 rows: beyond the three rows it keeps in registers the
+// An entry goes to the tensor cores from 12 rows: beyond the three rows it keeps in registers the
 // streaming kernel re-fetches the activation rows for every tile, which costs more than the
 // tensor-core kernel's fixed work per tile.  Measured (48 layers of 64 tokens / 48 layers of 4
 // tokens / one layer of 2048 tokens): split at 12: 18.7 / 3.53 / 1.19 ms, at 8: 18.7 / 3.53 /
 // 1.17, at 4: 18.9 / 5.50 / 1.16 (a 4-token window's shared expert, weights cold, is the
-// streaming kernel's case), everything streamed: 33 ms for the first.
-constexpr uint32_t TC_MIN_ROWS = 8;
+// streaming kernel's case), everything streamed: 33 ms for the first.  At 8 the shared expert of
+// an 8-way expert-parallel rank (8 own tokens, weights cold) moves to the tensor cores with its
+// four helper launches per layer: 9.3 ms per step against 7.8 ms with the split at 12.
+constexpr uint32_t TC_MIN_ROWS = 12;
 bool launch_grouped_any(const uint8_t *w, uint64_t expert_stride, const int32_t *act,
                         const uint32_t *n_act, uint32_t n_entries, const int32_t *bounds, Q8View xq,
                         uint64_t total_rows, uint32_t cols, uint32_t w_rows, float *dst,

@@ -288,10 +288,10 @@ def test_layer_n_matches_oracle_per_token(dev, pkg, oracle, n_tok, n_expert, top
         layer.close()
 
 
-@pytest.mark.parametrize("per", [[0, 0, 0, 0], [2100, 7, 8, 5], [64, 0, 65, 1], [3, 0, 0, 129]])
+@pytest.mark.parametrize("per", [[0, 0, 0, 0], [2100, 11, 12, 5], [64, 0, 65, 1], [3, 0, 0, 129]])
 def test_grouped_product_edge_row_counts(dev, pkg, oracle, per):
     """Row counts at the edges of the kernels' ranges, on a tiled arena: no rows at all (nothing may
-    be written), 7 / 8 rows either side of the tensor-core threshold next to an expert with
+    be written), 11 / 12 rows either side of the tensor-core threshold next to an expert with
     2100 rows (one call, two kernels), 64 / 65 (one pass / two passes), 129 (three passes, the last
     with one row).
     Every kernel choice must agree with the CPU path's int8 dot."""
