@@ -112,12 +112,15 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t pari
     const uint32_t a = smem_u32(bar);
     for (uint32_t i = 0; i < limit; i++) {
         uint32_t ok;
+        // the time hint (ns) lets the hardware park the thread instead of having it poll: the
+        // MMA and copy warps wait most of the time and would otherwise take issue slots from
+        // the decode warps on their schedulers
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(a), "r"(parity)
+            : "r"(a), "r"(parity), "r"(2000u)
             : "memory");
         if (ok) return true;
     }
@@ -280,7 +283,7 @@ __global__ void __launch_bounds__(1024) worklist_k(const int32_t *__restrict__ b
     if (tid == 0) *n_work = min(base_s, cap);
 }
 
-constexpr uint32_t WAIT_LIMIT = 1u << 21;   // polls before a wait gives up (about a second)
+constexpr uint32_t WAIT_LIMIT = 1u << 19;   // tries (of up to 2 us each) before a wait gives up: about a second
 constexpr uint32_t ERR_MMQ_TC = 0x400u;
 
 // One 32-weight group as fp16 integers w * ls (w = sign * (2c + 1)), 32 halves in 16 words.
