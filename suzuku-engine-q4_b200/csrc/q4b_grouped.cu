@@ -290,6 +290,46 @@ __global__ void expert_reduce_k(float *__restrict__ y, const float *__restrict__
     else
         y[(uint64_t)t * n_embd + c] = 0.f + acc;
 }
+// The same sums four columns per thread (n_embd % 4 == 0, 16-byte aligned rows): the picks'
+// rows are read as float4, each column still adds its picks in the order k = 0..topk-1.
+template <bool ADD>
+__global__ void __launch_bounds__(256) expert_reduce4_k(float *__restrict__ y, const float *__restrict__ pd,
+                                                        const int32_t *__restrict__ rsrc,
+                                                        const float *__restrict__ rw, uint32_t topk,
+                                                        uint32_t n_embd) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t c4 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c4 >= n_embd / 4u) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t k = 0; k < topk; k++) {
+        const int32_t p = rsrc[(uint64_t)t * topk + k];
+        if (p >= 0) {
+            const float w = rw[(uint64_t)t * topk + k];
+            const float4 v = __ldcs(reinterpret_cast<const float4 *>(pd + (uint64_t)p * n_embd) + c4);
+            acc.x += w * v.x;
+            acc.y += w * v.y;
+            acc.z += w * v.z;
+            acc.w += w * v.w;
+        }
+    }
+    float4 *o = reinterpret_cast<float4 *>(y + (uint64_t)t * n_embd) + c4;
+    if (ADD) {
+        const float4 old = *o;
+        *o = make_float4(old.x + acc.x, old.y + acc.y, old.z + acc.z, old.w + acc.w);
+    } else {
+        *o = make_float4(0.f + acc.x, 0.f + acc.y, 0.f + acc.z, 0.f + acc.w);
+    }
+}
+template <bool ADD>
+static void launch_expert_reduce(float *y, const float *pd, const int32_t *rsrc, const float *rw, uint32_t n_tok,
+                                 uint32_t topk, uint32_t n_embd) {
+    if ((n_embd & 3u) == 0 && (((uintptr_t)y | (uintptr_t)pd) & 15u) == 0)
+        expert_reduce4_k<ADD><<<dim3((n_embd / 4u + 255u) / 256u, n_tok), 256, 0, g_q4b.stream>>>(y, pd, rsrc, rw,
+                                                                                                topk, n_embd);
+    else
+        expert_reduce_k<ADD><<<dim3((n_embd + 255) / 256, n_tok), 256, 0, g_q4b.stream>>>(y, pd, rsrc, rw, topk,
+                                                                                         n_embd);
+}
 
 // One block (256 threads, or 1024 for a large group) per group of gsz tokens: a stable counting
 // sort of the group's picks by expert.  Each warp owns a contiguous run of picks; per-warp histograms, a
@@ -668,8 +708,7 @@ extern "C" bool q4_hip_expert_reduce(float *d_y, const float *d_pd, const int32_
                                      const float *d_rw, uint32_t n_tok, uint32_t topk,
                                      uint32_t n_embd) {
     if (!g_q4b.ok || !d_y || !d_pd || !d_rsrc || !d_rw || !n_tok || !topk || !n_embd) return false;
-    expert_reduce_k<true><<<dim3((n_embd + 255) / 256, n_tok), 256, 0, g_q4b.stream>>>(
-        d_y, d_pd, d_rsrc, d_rw, topk, n_embd);
+    launch_expert_reduce<true>(d_y, d_pd, d_rsrc, d_rw, n_tok, topk, n_embd);
     g_q4b_launches++;
     return q4b_launch_ok("expert_reduce");
 }
@@ -677,8 +716,7 @@ extern "C" bool q4_cuda_expert_reduce_set(float *d_y, const float *d_pd, const i
                                           const float *d_rw, uint32_t n_tok, uint32_t topk,
                                           uint32_t n_embd) {
     if (!g_q4b.ok || !d_y || !d_pd || !d_rsrc || !d_rw || !n_tok || !topk || !n_embd) return false;
-    expert_reduce_k<false><<<dim3((n_embd + 255) / 256, n_tok), 256, 0, g_q4b.stream>>>(
-        d_y, d_pd, d_rsrc, d_rw, topk, n_embd);
+    launch_expert_reduce<false>(d_y, d_pd, d_rsrc, d_rw, n_tok, topk, n_embd);
     g_q4b_launches++;
     return q4b_launch_ok("expert_reduce_set");
 }

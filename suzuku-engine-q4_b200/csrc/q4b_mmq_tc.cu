@@ -582,29 +582,35 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
 
 // The fp16 planes of the quantised activation rows: x = q * dq (the value the 8-bit row stands
 // for), divided by the power of two rs that brings the row's largest magnitude below 1, as
-// h1 = fp16(x / rs) and h2 = fp16(x / rs - h1).  One CTA per row.
+// h1 = fp16(x / rs) and h2 = fp16(x / rs - h1).  A row is taken by tpr = min(256, cols / 8)
+// threads, eight values each per turn; a CTA of 256 threads holds 256 / tpr rows.
 __global__ void __launch_bounds__(256) planes_k(const int8_t *__restrict__ q, const float *__restrict__ dq,
-                                                uint32_t cols, __half *__restrict__ h1, __half *__restrict__ h2,
+                                                uint64_t rows, uint32_t cols, uint32_t tpr,
+                                                __half *__restrict__ h1, __half *__restrict__ h2,
                                                 float *__restrict__ rs) {
     __shared__ float red[8];
-    const uint64_t row = blockIdx.x;
-    const uint32_t gpr = cols >> 5, tid = threadIdx.x;
-    const float *d = dq + row * gpr;
+    const uint32_t tid = threadIdx.x, rpb = 256u / tpr, sub = tid / tpr, t = tid - sub * tpr;
+    const uint64_t row = (uint64_t)blockIdx.x * rpb + sub;
+    const bool live = sub < rpb && row < rows;   // 256 % tpr threads at the end of the CTA have no row
+    const uint32_t gpr = cols >> 5;
+    const float *d = dq + (live ? row : 0) * gpr;
     float m = 0.f;
-    for (uint32_t g = tid; g < gpr; g += 256u) m = fmaxf(m, d[g]);
+    if (live)
+        for (uint32_t c = t * 8u; c < cols; c += tpr * 8u) m = fmaxf(m, d[c >> 5]);   // every group is seen
     m = q4b_warp_max(m);
     if ((tid & 31u) == 0) red[tid >> 5] = m;
     __syncthreads();
-    m = red[0];
-#pragma unroll
-    for (int i = 1; i < 8; i++) m = fmaxf(m, red[i]);
+    if (!live) return;
+    const uint32_t w0 = sub * (tpr >> 5), w1 = w0 + (tpr >> 5);   // the row's warps (tpr is a multiple of 32)
+    m = red[w0];
+    for (uint32_t i = w0 + 1u; i < w1; i++) m = fmaxf(m, red[i]);
     int e = 0;
     if (m > 0.f) (void)frexpf(m * 127.f, &e);   // 127 dq = the group's largest magnitude
     const float inv = ldexpf(1.f, -e);
-    if (tid == 0) rs[row] = ldexpf(1.f, e);
+    if (t == 0) rs[row] = ldexpf(1.f, e);
     const int8_t *qr = q + row * cols;
     __half *o1 = h1 + row * cols, *o2 = h2 + row * cols;
-    for (uint32_t c = tid * 8u; c < cols; c += 2048u) {   // eight values per thread and turn
+    for (uint32_t c = t * 8u; c < cols; c += tpr * 8u) {   // eight values per thread and turn
         const uint2 w = *reinterpret_cast<const uint2 *>(qr + c);
         const float sc = d[c >> 5] * inv;
         uint32_t p1[4], p2[4];
@@ -694,7 +700,11 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
                      CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return false;
     }
-    planes_k<<<(unsigned)rows, 256, 0, stream>>>(q, dq, cols, h1, h2, rs);
+    {
+        const uint32_t tpr = cols / 8u < 256u ? cols / 8u : 256u;   // cols % 256 == 0: a multiple of 32
+        const uint32_t rpb = 256u / tpr;
+        planes_k<<<(unsigned)((rows + rpb - 1) / rpb), 256, 0, stream>>>(q, dq, rows, cols, tpr, h1, h2, rs);
+    }
     Args a;
     a.w = w;
     a.expert_stride = expert_stride;
