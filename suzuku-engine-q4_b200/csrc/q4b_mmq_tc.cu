@@ -127,12 +127,6 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t pari
     return false;
 }
 
-// K-major, no swizzle: start address, leading (K chunk) and stride (8-row group)
-// byte offsets in 16-byte units, descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
-    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) |
-           ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
-}
 // K-major rows of 128 bytes under the 128-byte swizzle (what a TMA load with that swizzle
 // writes): 8-row groups 1024 bytes apart; the K offset inside the 128 bytes is part of the
 // start address.
@@ -180,37 +174,8 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *v) {
         : "r"(taddr)
         : "memory");
 }
-// Packed fp32 pairs (sm_100 f32x2 arithmetic): two products / two fused multiply-adds per
-// instruction, each rounded like the scalar form.
-__device__ __forceinline__ unsigned long long pack2(float lo, float hi) {
-    unsigned long long r;
-    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-    return r;
-}
-__device__ __forceinline__ void unpack2(unsigned long long v, float &lo, float &hi) {
-    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
-    unsigned long long r;
-    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-    return r;
-}
-__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b,
-                                                   unsigned long long c) {
-    unsigned long long r;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-    return r;
-}
 __device__ __forceinline__ void tmem_ld_wait() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tma_load_3d(void *dst, const CUtensorMap *map, unsigned long long *bar,
-                                            int c0, int c1, int c2) {
-    asm volatile(
-        "cp.async.bulk.tensor.3d.shared::cta.global.tile.mbarrier::complete_tx::bytes "
-        "[%0], [%1, {%2, %3, %4}], [%5];" ::"r"(smem_u32(dst)),
-        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(smem_u32(bar))
-        : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, unsigned long long *bar,
                                             int c0, int c1) {
