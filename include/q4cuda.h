@@ -464,12 +464,42 @@ bool q4_cuda_decode_plan_dev(void *plan, const float *d_x, float *d_y, int32_t *
 bool q4_cuda_decode_plan_host(void *plan, const float *h_x, float *h_y);
 void q4_cuda_decode_plan_free(void *plan);
 
+/* A stack of MoE layers for one token in ONE launch: y of layer l is x of layer l + 1 (no
+ * counterpart in the reference, whose graph issues the per-layer chain once per layer,
+ * src/q4_moe.c:2077-2133).  All layers share the shape, the arena stride and the pack offsets;
+ * each has its own expert base (slot 0 of that layer), norm weights (may be NULL) and router.
+ * plan() copies the descriptors to the device (it allocates: call it outside graph capture)
+ * and returns NULL for a shape the persistent kernel does not take (n_embd 2048, n_ff 512,
+ * n_expert <= 768, topk <= 32, tiled arena, at most 64 layers); the caller then loops over
+ * q4_cuda_moe_decode.  _dev: d_x in, d_y out (both n_embd floats, d_y OVERWRITTEN), d_ids /
+ * d_wts [n_layers][topk] or NULL.  _host: the same with page-locked host buffers, waits for
+ * the result; false if the kernel reported an error (q4_cuda_device_error says which).
+ * Launches on the library's stream must not overlap (they share the exchange scratch). */
+typedef struct {
+    const uint8_t *base;
+    const float *d_norm_w;
+    const float *d_router;
+} q4_cuda_stack_layer_t;
+void *q4_cuda_decode_stack_plan(const q4_cuda_stack_layer_t *layers, uint32_t n_layers, uint64_t stride,
+                                uint64_t og, uint64_t ou, uint64_t od, int32_t shared_slot, float eps,
+                                uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff);
+uint32_t q4_cuda_decode_stack_layers(void *plan);
+bool q4_cuda_decode_stack_dev(void *plan, const float *d_x, float *d_y, int32_t *d_ids, float *d_wts);
+bool q4_cuda_decode_stack_host(void *plan, const float *h_x, float *h_y);
+void q4_cuda_decode_stack_free(void *plan);
+
 /* Diagnostics of the single-kernel layer path: when enabled, the kernel records
- * the GPU's nanosecond timer at its phase boundaries; read copies the last
- * launch's stamps, out[cta * 16 + slot], and returns the number of CTAs.
- * enable allocates or frees (call it outside graph capture). */
+ * the GPU's nanosecond timer at the phase boundaries of one layer of the launch
+ * (profile_layer, default 0); read copies the last launch's stamps, out[cta * 16 + slot],
+ * and returns the number of CTAs.  enable allocates or frees (call it outside graph
+ * capture).  wait_limit sets how many polls a CTA spends waiting for another CTA's
+ * values before it gives up and sets bit 2 (value 4) of the device error word
+ * (0 = the default, about a tenth of a second); it exists so that a test can make the
+ * wait run out. */
 bool q4_cuda_fused_profile_enable(int on);
+void q4_cuda_fused_profile_layer(uint32_t layer);
 uint32_t q4_cuda_fused_profile_read(unsigned long long *out, uint32_t max_ctas);
+void q4_cuda_decode_wait_limit(uint32_t polls);
 
 /* Fused forms of two steps of the prefill sequence (no reference counterpart):
  * swiglu_quantize = q4_mmq_swiglu followed by q4_mmq_quantize of the result, without the fp32

@@ -180,7 +180,14 @@ SIGNATURES = {
     "q4_cuda_decode_plan_dev": (b, [vp, vp, vp, vp, vp]),
     "q4_cuda_decode_plan_host": (b, [vp, vp, vp]),
     "q4_cuda_decode_plan_free": (None, [vp]),
+    "q4_cuda_decode_stack_plan": (vp, [vp, u32, u64, u64, u64, u64, i32, f32, u32, u32, u32, u32]),
+    "q4_cuda_decode_stack_layers": (u32, [vp]),
+    "q4_cuda_decode_stack_dev": (b, [vp, vp, vp, vp, vp]),
+    "q4_cuda_decode_stack_host": (b, [vp, vp, vp]),
+    "q4_cuda_decode_stack_free": (None, [vp]),
     "q4_cuda_fused_profile_enable": (b, [C.c_int]),
+    "q4_cuda_fused_profile_layer": (None, [u32]),
+    "q4_cuda_decode_wait_limit": (None, [u32]),
     "q4_cuda_fused_profile_read": (u32, [vp, u32]),
     "q4_cuda_mmq_swiglu_quantize": (b, [vp, vp, u64, u64]),
     "q4_cuda_expert_reduce_set": (b, [vp, vp, vp, vp, u32, u32, u32]),

@@ -62,7 +62,9 @@ extern "C" void *q4_hip_host_devptr(void *p) {
     }
     return d;
 }
+void q4b_stack_forget_host(const void *h);
 extern "C" void q4_hip_host_unregister(void *p) {
+    if (g_q4b.ok && p) q4b_stack_forget_host(p);
     if (g_q4b.ok && p && cudaHostUnregister(p) != cudaSuccess) cudaGetLastError();
 }
 // Ordered with the expert uploads: the copy stream.

@@ -17,6 +17,10 @@ bool q4b_ptr_tiled(const void *p);
 bool q4b_moe_decode_fused(const uint8_t *, uint64_t, uint64_t, uint64_t, uint64_t, int32_t, const float *,
                           const float *, float, const float *, uint32_t, uint32_t, uint32_t, uint32_t,
                           float *, int32_t *, float *, float *, uint32_t *, uint32_t, const float *);
+float *q4b_host_alias(const void *h);
+bool q4b_wait_flag(uint32_t epoch);
+uint32_t q4b_next_flag_epoch();
+static bool decode_fused_on();
 
 #define Q4B_X_SLICE 64u  // scratch slice that holds the quantised input row
 
@@ -987,11 +991,7 @@ extern "C" bool q4_cuda_moe_decode(const uint8_t *base, uint64_t stride, uint64_
     if (!shape_ok(Q4_T_IQ3_S, Q4_T_IQ3_S, Q4_T_IQ3_S, n_embd, n_ff)) return false;
     if (n_expert == 0 || n_expert > 1024 || topk == 0 || topk > 63 || topk > n_expert) return false;
     // The single persistent kernel when it applies (Q4B_FUSED=0 forces the chain).
-    static int fused_on = -1;
-    if (fused_on < 0) {
-        const char *e = getenv("Q4B_FUSED");
-        fused_on = !(e && e[0] == '0');
-    }
+    const bool fused_on = decode_fused_on();
     if (fused_on && q4b_moe_decode_fused(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps,
                                          d_router, n_expert, topk, n_embd, n_ff, d_y, d_ids, d_wts,
                                          nullptr, nullptr, 0, nullptr))
@@ -1040,49 +1040,20 @@ extern "C" bool q4_cuda_moe_decode_host(const uint8_t *base, uint64_t stride, ui
     // Fast hand-off: when the result buffer is pinned, mapped host memory (q4_hip_host_alloc_coh)
     // the persistent kernel's last CTA writes y straight into it and raises a mapped flag the
     // host spins on -- no copy node, no stream wake-up.  Anything else takes copy + sync.
-    static int fused_on = -1;
-    if (fused_on < 0) {
-        const char *e = getenv("Q4B_FUSED");
-        fused_on = !(e && e[0] == '0');
-    }
+    const bool fused_on = decode_fused_on();
+    // The alias of the result buffer is looked up on every call (about a microsecond): a cached
+    // alias would outlive a buffer that was freed and whose address was handed out again.
+    // q4_cuda_decode_plan_host keeps the alias with the plan instead.
     float *y_dev_alias = nullptr;
-    if (fused_on && s.flag_h && base && d_router) {
-        static const void *last_ok = nullptr;      // the attribute query costs about a microsecond
-        static float *last_alias = nullptr;
-        if (h_y == last_ok) {
-            y_dev_alias = last_alias;
-        } else {
-            cudaPointerAttributes at;
-            if (cudaPointerGetAttributes(&at, h_y) == cudaSuccess && at.type == cudaMemoryTypeHost &&
-                at.devicePointer && ((uintptr_t)at.devicePointer % 16u) == 0) {
-                y_dev_alias = (float *)at.devicePointer;
-                last_ok = h_y;
-                last_alias = y_dev_alias;
-            } else {
-                cudaGetLastError();
-            }
-        }
-    }
+    if (fused_on && s.flag_h && base && d_router) y_dev_alias = q4b_host_alias(h_y);
     if (y_dev_alias && shape_ok(Q4_T_IQ3_S, Q4_T_IQ3_S, Q4_T_IQ3_S, n_embd, n_ff) && n_expert != 0 &&
         topk != 0 && topk <= n_expert) {
-        const uint32_t epoch = ++s.flag_epoch ? s.flag_epoch : ++s.flag_epoch;   // never 0
+        const uint32_t epoch = q4b_next_flag_epoch();
         // the hidden row goes in with the launch (kernel parameter block): no copy node either
         if (q4b_moe_decode_fused(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps, d_router,
                                  n_expert, topk, n_embd, n_ff, d_y, nullptr, nullptr, y_dev_alias,
-                                 s.flag_d, epoch, h_x)) {
-            volatile uint32_t *f = s.flag_h;
-            for (uint64_t spins = 0; *f != epoch; spins++) {
-                if (spins > 200000000ull) {        // far beyond any launch: let the stream say why
-                    Q4B_CHECK(cudaStreamSynchronize(s.stream));
-                    return *f == epoch;
-                }
-#if defined(__x86_64__)
-                __builtin_ia32_pause();
-#endif
-            }
-            std::atomic_thread_fence(std::memory_order_acquire);
-            return true;
-        }
+                                 s.flag_d, epoch, h_x))
+            return q4b_wait_flag(epoch);
     }
     Q4B_CHECK(cudaMemcpyAsync(d_x, h_x, (size_t)n_embd * 4, cudaMemcpyHostToDevice, s.stream));
     if (!q4_cuda_moe_decode(base, stride, og, ou, od, shared_slot, d_x, d_norm_w, eps, d_router,
@@ -1101,7 +1072,16 @@ struct Q4bDecodePlan {
     const float *d_norm_w, *d_router;
     float eps;
     uint32_t n_expert, topk, n_embd, n_ff;
+    void *stack;    // the one-layer form of q4_cuda_decode_stack_plan when the persistent kernel takes the shape
 };
+static bool decode_fused_on() {
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("Q4B_FUSED");
+        on = !(e && e[0] == '0');
+    }
+    return on != 0;
+}
 extern "C" void *q4_cuda_decode_plan(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou,
                                      uint64_t od, int32_t shared_slot, const float *d_norm_w, float eps,
                                      const float *d_router, uint32_t n_expert, uint32_t topk,
@@ -1110,22 +1090,36 @@ extern "C" void *q4_cuda_decode_plan(const uint8_t *base, uint64_t stride, uint6
     if (!shape_ok(Q4_T_IQ3_S, Q4_T_IQ3_S, Q4_T_IQ3_S, n_embd, n_ff)) return nullptr;
     if (n_expert == 0 || n_expert > 1024 || topk == 0 || topk > 63 || topk > n_expert) return nullptr;
     Q4bDecodePlan *p = new Q4bDecodePlan{base, stride, og, ou, od, shared_slot, d_norm_w, d_router,
-                                         eps, n_expert, topk, n_embd, n_ff};
+                                         eps, n_expert, topk, n_embd, n_ff, nullptr};
+    if (decode_fused_on()) {
+        const q4_cuda_stack_layer_t one = {base, d_norm_w, d_router};
+        p->stack = q4_cuda_decode_stack_plan(&one, 1, stride, og, ou, od, shared_slot, eps, n_expert, topk,
+                                             n_embd, n_ff);
+    }
     return p;
 }
-extern "C" void q4_cuda_decode_plan_free(void *plan) { delete (Q4bDecodePlan *)plan; }
+extern "C" void q4_cuda_decode_plan_free(void *plan) {
+    Q4bDecodePlan *p = (Q4bDecodePlan *)plan;
+    if (!p) return;
+    if (p->stack) q4_cuda_decode_stack_free(p->stack);
+    delete p;
+}
 extern "C" bool q4_cuda_decode_plan_dev(void *plan, const float *d_x, float *d_y, int32_t *d_ids,
                                         float *d_wts) {
     const Q4bDecodePlan *p = (const Q4bDecodePlan *)plan;
-    return p && q4_cuda_moe_decode(p->base, p->stride, p->og, p->ou, p->od, p->shared_slot, d_x, p->d_norm_w,
-                                   p->eps, p->d_router, p->n_expert, p->topk, p->n_embd, p->n_ff, d_y, d_ids,
-                                   d_wts);
+    if (!p) return false;
+    if (p->stack) return q4_cuda_decode_stack_dev(p->stack, d_x, d_y, d_ids, d_wts);
+    return q4_cuda_moe_decode(p->base, p->stride, p->og, p->ou, p->od, p->shared_slot, d_x, p->d_norm_w,
+                              p->eps, p->d_router, p->n_expert, p->topk, p->n_embd, p->n_ff, d_y, d_ids,
+                              d_wts);
 }
 extern "C" bool q4_cuda_decode_plan_host(void *plan, const float *h_x, float *h_y) {
     const Q4bDecodePlan *p = (const Q4bDecodePlan *)plan;
-    return p && q4_cuda_moe_decode_host(p->base, p->stride, p->og, p->ou, p->od, p->shared_slot, h_x,
-                                        p->d_norm_w, p->eps, p->d_router, p->n_expert, p->topk, p->n_embd,
-                                        p->n_ff, h_y);
+    if (!p) return false;
+    if (p->stack) return q4_cuda_decode_stack_host(p->stack, h_x, h_y);
+    return q4_cuda_moe_decode_host(p->base, p->stride, p->og, p->ou, p->od, p->shared_slot, h_x,
+                                   p->d_norm_w, p->eps, p->d_router, p->n_expert, p->topk, p->n_embd,
+                                   p->n_ff, h_y);
 }
 
 // ---- helpers shared with the many-token path (q4b_grouped.cu) ----

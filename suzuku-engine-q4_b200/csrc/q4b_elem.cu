@@ -77,52 +77,77 @@ __global__ void __launch_bounds__(256) dot_k(const float *a, const float *b, flo
     if (threadIdx.x == 0) *out = SIG ? 1.f / (1.f + expf(-d)) : d;
 }
 
-// dy[t][i] += sigmoid(w . x[t]) * dsh[t][i]: every CTA recomputes its token's gate (the row is
-// L2-resident) and adds its slice, one launch for the GEMV, the sigmoid and the add.
-__global__ void __launch_bounds__(256) sgate_axpy_k(float *dy, const float *dsh, const float *w,
-                                                    const float *x, uint32_t n) {
+// ---- per-token rows: y[t] += g_t * x[t], the gate g_t one scalar per token ----
+// One CTA per token sweeps the whole row (float4 when the row allows), after the gate functor
+// has produced the token's scalar for all its threads: a table entry, or the sigmoid of a dot
+// product the CTA forms first (the shared expert's gate, src/q4_moe.c:1404-1435).
+struct GateTable {
+    const float *g;
+    __device__ float operator()(uint32_t t, uint32_t, float *) const { return g[t]; }
+};
+struct GateSigmoidDot {
+    const float *w, *x;
+    __device__ float operator()(uint32_t t, uint32_t n, float *red) const {
+        const float d = block_dot(w, x + (size_t)t * n, n, red);
+        return 1.f / (1.f + expf(-d));
+    }
+};
+template <class Gate>
+__global__ void __launch_bounds__(256) gated_rows_k(float *y, const float *x, uint32_t n, Gate gate) {
     __shared__ float red[8];
-    const uint32_t t = blockIdx.y;
-    const float d = block_dot(w, x + (size_t)t * n, n, red);
-    const float sg = 1.f / (1.f + expf(-d));
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) dy[(size_t)t * n + i] += sg * dsh[(size_t)t * n + i];
-}
-__global__ void __launch_bounds__(256) axpy_rows_k(float *dy, const float *dx, const float *sg, uint32_t n) {
-    const uint32_t t = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) dy[(size_t)t * n + i] += sg[t] * dx[(size_t)t * n + i];
+    const uint32_t t = blockIdx.x;
+    const OpAxpy op{gate(t, n, red)};
+    float *yr = y + (size_t)t * n;
+    const float *xr = x + (size_t)t * n;
+    if ((n & 3u) == 0 && ((((uintptr_t)yr) | ((uintptr_t)xr)) & 15u) == 0) {
+        for (uint32_t i = threadIdx.x; i < (n >> 2); i += blockDim.x) {
+            float4 vy = reinterpret_cast<float4 *>(yr)[i];
+            const float4 vx = reinterpret_cast<const float4 *>(xr)[i];
+            vy.x = op(vy.x, vx.x, 0.f);
+            vy.y = op(vy.y, vx.y, 0.f);
+            vy.z = op(vy.z, vx.z, 0.f);
+            vy.w = op(vy.w, vx.w, 0.f);
+            reinterpret_cast<float4 *>(yr)[i] = vy;
+        }
+    } else {
+        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) yr[i] = op(yr[i], xr[i], 0.f);
+    }
 }
 
-// ---- decode layer head and tail (src/q4_rocm.cu:15920-16024) ----
-// pack: y = 0; optional gate scalar sigmoid(x . sgate) -> *dot; optional SwiGLU of the shared
-// expert's projections in place (sm = silu(sm) * sm2); optional counter bump.  One CTA.
+// ---- decode layer head and tail (the engine's pack / final pair, src/q4.h:971-976) ----
+// Head, one CTA: y = 0; the shared expert's projections through the SwiGLU functor in place;
+// the optional gate scalar sigmoid(x . sgate); the optional counter bump last.
 __global__ void __launch_bounds__(256) moe_pack_k(float *y, const float *x, const float *sgate, float *dot,
                                                   uint32_t *flag, uint32_t n_embd, float *sm,
                                                   const float *sm2, uint32_t n_sm) {
     __shared__ float red[8];
-    for (uint32_t j = threadIdx.x; j < n_embd; j += 256u) y[j] = 0.f;
-    for (uint32_t j = threadIdx.x; j < n_sm; j += 256u) {
-        const float v = sm[j];
-        sm[j] = v / (1.f + expf(-v)) * sm2[j];
-    }
+    const OpSiluMul act{};
+    for (uint32_t j = threadIdx.x; j < n_sm; j += blockDim.x) sm[j] = act(sm[j], sm2[j], 0.f);
+    for (uint32_t j = threadIdx.x; j < n_embd; j += blockDim.x) y[j] = 0.f;
     if (sgate) {
-        const float d = block_dot(x, sgate, n_embd, red);
-        if (threadIdx.x == 0) *dot = 1.f / (1.f + expf(-d));
+        const float g = GateSigmoidDot{sgate, x}(0, n_embd, red);
+        if (threadIdx.x == 0) *dot = g;
     }
     __syncthreads();
-    if (threadIdx.x == 0 && flag) ++*flag;
+    if (flag && threadIdx.x == 0) *flag += 1u;
 }
-// final: v = y + hy + sh * (dot ? *dot : 1); res[c] += v * 2 sigmoid(inj[c] / hc) for c < hc.
+// Tail: the hc stream factors 2 sigmoid(inj[c] / hc) are formed once per CTA in shared memory;
+// the CTA then walks its share of the row, forms the layer's sum once per element and adds its
+// multiples to the hc residual streams.
+constexpr uint32_t FINAL_MAX_HC = 64;
 __global__ void __launch_bounds__(256) moe_final_k(float *res, const float *y, const float *hy, const float *sh,
                                                    const float *dot, const float *inj, uint32_t n_embd,
                                                    uint32_t hc) {
-    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_embd) return;
-    const float v = y[i] + hy[i] + sh[i] * (dot ? *dot : 1.f);
-    const float inv = 1.f / (float)hc;
-    for (uint32_t c = 0; c < hc; c++) {
-        const float w = 2.f / (1.f + expf(-inj[c] * inv));
-        res[(size_t)c * n_embd + i] += v * w;
+    __shared__ float factor[FINAL_MAX_HC];
+    const OpSigmoid sig{};
+    for (uint32_t c = threadIdx.x; c < hc; c += blockDim.x) factor[c] = 2.f * sig(inj[c] / (float)hc, 0.f, 0.f);
+    __syncthreads();
+    const float gate = dot ? *dot : 1.f;
+    const uint32_t step = gridDim.x * blockDim.x;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_embd; i += step) {
+        const float sum = (y[i] + hy[i]) + sh[i] * gate;
+        float *stream = res + i;
+        for (uint32_t c = 0; c < hc; c++, stream += n_embd) *stream += sum * factor[c];
     }
 }
 
@@ -294,7 +319,7 @@ extern "C" bool q4_hip_axpy_dalpha(float *y, const float *x, const float *d_alph
 }
 extern "C" bool q4_hip_axpy_rows(float *d_y, const float *d_x, const float *d_sg, uint32_t n, uint32_t n_tok) {
     if (!g_q4b.ok || !d_y || !d_x || !d_sg || !n || !n_tok) return false;
-    elem::axpy_rows_k<<<dim3((n + 255u) / 256u, n_tok), 256, 0, g_q4b.stream>>>(d_y, d_x, d_sg, n);
+    elem::gated_rows_k<<<n_tok, 256, 0, g_q4b.stream>>>(d_y, d_x, n, elem::GateTable{d_sg});
     g_q4b_launches++;
     return q4b_launch_ok("axpy_rows");
 }
@@ -313,7 +338,7 @@ extern "C" bool q4_hip_dot_sigmoid(const float *a, const float *b, float *out, u
 extern "C" bool q4_hip_sgate_axpy(float *d_y, const float *d_sh, const float *d_w, const float *d_x, uint32_t n,
                                   uint32_t n_tok) {
     if (!g_q4b.ok || !d_y || !d_sh || !d_w || !d_x || !n || !n_tok) return false;
-    elem::sgate_axpy_k<<<dim3((n + 255u) / 256u, n_tok), 256, 0, g_q4b.stream>>>(d_y, d_sh, d_w, d_x, n);
+    elem::gated_rows_k<<<n_tok, 256, 0, g_q4b.stream>>>(d_y, d_sh, n, elem::GateSigmoidDot{d_w, d_x});
     g_q4b_launches++;
     return q4b_launch_ok("sgate_axpy");
 }
@@ -333,8 +358,12 @@ extern "C" bool q4_hip_moe_pack(float *d_y, const float *d_x, const float *d_sga
 }
 extern "C" bool q4_hip_moe_final(float *res, const float *y, const float *hy, const float *sh, const float *dot,
                                  const float *inj, uint32_t n_embd, uint32_t hc) {
-    if (!g_q4b.ok || !res || !y || !hy || !sh || !inj || !n_embd || !hc) return false;
-    elem::moe_final_k<<<(n_embd + 255u) / 256u, 256, 0, g_q4b.stream>>>(res, y, hy, sh, dot, inj, n_embd, hc);
+    if (!g_q4b.ok || !n_embd || !hc || hc > elem::FINAL_MAX_HC) return false;
+    for (const float *p : {(const float *)res, y, hy, sh, inj})
+        if (!p) return false;
+    uint32_t blocks = (n_embd + 255u) / 256u;
+    if (blocks > (uint32_t)g_q4b.n_sm * 4u) blocks = (uint32_t)g_q4b.n_sm * 4u;
+    elem::moe_final_k<<<blocks, 256, 0, g_q4b.stream>>>(res, y, hy, sh, dot, inj, n_embd, hc);
     g_q4b_launches++;
     return q4b_launch_ok("moe_final");
 }
@@ -530,9 +559,10 @@ extern "C" bool q4_mmq_gather(const uint8_t *abase, uint64_t astride, uint64_t g
                               uint8_t *d_d) {
     if (!abase || !d_eid || !d_slot || !d_gu || !d_d || !n) return !n;
     if (!g_q4b.ok || gu_dst < gu_bytes || d_dst < d_bytes) return false;
-    const uintptr_t al = (uintptr_t)abase | astride | goff | gu_bytes | doff | d_bytes | gu_dst | d_dst |
-                         (uintptr_t)d_gu | (uintptr_t)d_d;
-    if (al & 15u) return false;   // packs, offsets and strides of IQ3_S experts are multiples of 16
+    // the copy moves 16-byte words: every address, offset, size and stride must be a whole number of them
+    for (const uint64_t v : {(uint64_t)(uintptr_t)abase, (uint64_t)(uintptr_t)d_gu, (uint64_t)(uintptr_t)d_d, astride,
+                             goff, doff, gu_bytes, d_bytes, gu_dst, d_dst})
+        if (v % 16u) return false;
     const bool tiled = q4b_ptr_tiled(abase);
     // a tiled arena's bytes stay tiled in the copy: whole 880-byte tiles must move together
     if (tiled && ((goff % Q4B_TILE_BYTES) || (doff % Q4B_TILE_BYTES) || (gu_bytes % Q4B_TILE_BYTES) ||

@@ -12,7 +12,9 @@
 #include "iq3s_codes.h"
 
 Q4bState g_q4b = {};
-bool q4b_fused_warm();   // q4b_fused.cu: scratch of the persistent decode kernel
+bool q4b_fused_warm();   // q4b_stack.cu: scratch of the persistent decode kernel
+void q4b_fused_shutdown();
+void q4b_stack_forget_host(const void *h);
 bool q4b_window_warm();  // q4b_grouped.cu: scratch of the verify-window path
 bool q4b_elem_warm();    // q4b_elem.cu: lists of the per-token exec, rows of the 2..8-row GEMV
 void q4b_elem_shutdown();
@@ -202,6 +204,8 @@ extern "C" void q4_hip_shutdown(void) {
         g_arena[a] = Arena{};
     }
     q4b_elem_shutdown();
+    q4b_fused_shutdown();
+    q4b_stack_forget_host(nullptr);
     cudaFree(s.xq);
     cudaFree(s.xd);
     cudaFree(s.xbs);
@@ -457,7 +461,10 @@ extern "C" void *q4_hip_host_alloc_coh(size_t n) {
     return p;
 }
 extern "C" void q4_hip_host_free_coh(void *p) {
-    if (g_q4b.ok && p) cudaFreeHost(p);
+    if (g_q4b.ok && p) {
+        q4b_stack_forget_host(p);   // a decode plan may hold this buffer's device alias
+        cudaFreeHost(p);
+    }
 }
 
 // ---- tiled arenas ----

@@ -5,7 +5,7 @@
 #include "q4b_runtime.cu"
 #include "q4b_decode.cu"
 #include "q4b_synth.cu"
-#include "q4b_fused.cu"
+#include "q4b_stack.cu"
 #include "q4b_mmq_tc.cu"
 #include "q4b_few.cu"
 #include "q4b_grouped.cu"
