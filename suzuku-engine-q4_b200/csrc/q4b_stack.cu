@@ -5,14 +5,15 @@
 //   phase 0  the token's row (layer 0: the caller's x; later: the previous layer's y, taken
 //            from the exchange words), RMSNorm, Q8-A quantisation -- every CTA the same
 //   phase 1  router: dots of this CTA's rows of the router matrix (fetched one layer
-//            ahead), published as exchange words; the shared expert's gate/up rows (also
-//            fetched ahead), SwiGLU, published
+//            ahead; one warp per quarter row), published as exchange words, four partial
+//            sums per expert; the shared expert's gate/up rows (also fetched ahead),
+//            SwiGLU, published
 //   phase 2  all logits from the exchange words; the top-k by LOGIT order (softmax is
 //            monotone), and at once the bulk copies of this CTA's share of the picked
-//            experts' gate/up tiles; while those fly: softmax, the check that the
-//            probability order gives the same picks (src/q4_quant.c:715-755 picks on
-//            probabilities, ties to the lower index), the renormalised weights; gate/up
-//            dots, SwiGLU, hidden values published; copies of the down tiles
+//            experts' gate/up tiles, then of its down tiles; while those fly: softmax, the
+//            check that the probability order gives the same picks (src/q4_quant.c:715-755
+//            picks on probabilities, ties to the lower index), the renormalised weights;
+//            gate/up dots, SwiGLU, hidden values published
 //   phase 3  all hidden values from the exchange words, Q8-A per expert, down tiles x hq,
 //            weighted sum over the experts in list order, y published (last layer: written)
 //
@@ -31,7 +32,8 @@
 // cp.async.bulk into this CTA only) that complete on mbarriers.
 // Replaces the reference's per-layer launch chain (src/q4_moe.c:2077-2133; kernels
 // wmoe_iq3_gu_q8 / wmoe_iq3_ya_q8, src/q4_rocm.cu:3912-4120).  Needs the tiled arena
-// format (q4b_tile.cuh), n_embd == 2048, n_ff == 512, n_expert <= 768, topk <= 32.
+// format (q4b_tile.cuh), n_embd == 2048, n_ff == 512, n_expert <= 512, topk <= 15.
+// 512 threads per CTA: at 768 the 80-register limit spilled inside the tile loops.
 #include "q4b_tile.cuh"
 
 #include <atomic>
@@ -43,17 +45,17 @@ bool q4b_ptr_tiled(const void *p);
 
 namespace stk {
 
-constexpr uint32_t NT = 768;          // threads per CTA
+constexpr uint32_t NT = 512;          // threads per CTA
 constexpr uint32_t NW = NT / 32;      // warps
 constexpr uint32_t H = 2048;          // n_embd
 constexpr uint32_t F = 512;           // n_ff
-constexpr uint32_t MAX_E = 24;        // experts per token incl. shared (more: the launch chain runs)
+constexpr uint32_t MAX_E = 16;        // experts per token incl. shared (more: the launch chain runs)
 constexpr uint32_t UCHUNK = 8;        // gate/up units per bulk-copy chunk
 constexpr uint32_t MAX_CHUNKS = 6;
-constexpr uint32_t MAX_UNITS = 48;    // routed (expert, hidden unit) pairs per CTA (four tile tasks per warp)
+constexpr uint32_t MAX_UNITS = 48;    // routed (expert, hidden unit) pairs per CTA
 constexpr uint32_t MAX_SH = 8;        // shared-expert units per CTA
-constexpr uint32_t MAX_DT = 72;       // down tiles per CTA (three per warp)
-constexpr uint32_t MAX_RROWS = 8;     // router rows per CTA
+constexpr uint32_t MAX_DT = 72;       // down tiles per CTA
+constexpr uint32_t MAX_RROWS = 4;     // router rows per CTA
 constexpr uint32_t MAX_LAYERS = 64;   // layers per launch (epochs are spaced by this)
 constexpr uint32_t MBAR_LIMIT = 1000000u;   // polls before an mbarrier wait gives up
 constexpr uint32_t POLL_LIMIT = 400000u;    // default polls before an exchange-word wait gives up
@@ -85,13 +87,12 @@ struct Args {
     int32_t *ids_out;         // [n_layers][topk] or NULL
     float *wts_out;
     unsigned long long *xw;   // exchange words: [H] a layer's output row
-    unsigned long long *lw;   //                 [NT] logits (permuted, see logit_pos)
+    unsigned long long *lw;   //                 [NT][4] partial logits (permuted, see logit_pos)
     unsigned long long *hw;   //                 [MAX_E * F] hidden values
     unsigned long long *ctr;  // [0] CTA starts (launch number = value / grid), [1] CTA finishes of host hand-offs
     uint32_t *err;
     unsigned long long *prof; // optional [gridDim.x][16] phase time stamps (ns) of layer prof_layer, or NULL
     uint32_t prof_layer;
-    uint32_t prof_arrivals;   // diagnostic: slots 13..15 = first gate/up chunk, last chunk, down tiles landed
     float *y_host;            // optional: host-mapped copy of y, written by the last CTA to finish
     volatile uint32_t *flag_host; // host-mapped word that receives flag_val (bit 31: error word was set)
     uint32_t flag_val;
@@ -124,8 +125,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 // Bounded wait: gives up after MBAR_LIMIT polls and records it.
 __device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, uint32_t *err) {
-    for (uint32_t i = 0; i < MBAR_LIMIT; i++)
+    for (uint32_t i = 0; i < MBAR_LIMIT; i++) {
         if (mbar_try_wait(bar, parity)) return;
+        __nanosleep(40);
+    }
     atomicOr(err, ERR_MBAR);
 }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes,
@@ -142,20 +145,10 @@ __device__ __forceinline__ void xw_store(unsigned long long *p, float v, uint32_
     const unsigned long long w = ((unsigned long long)ep << 32) | (unsigned long long)__float_as_uint(v);
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
-// One word; bounded.
-__device__ __forceinline__ float xw_poll1(const unsigned long long *p, uint32_t ep, uint32_t limit,
-                                          uint32_t *err) {
-    unsigned long long w = 0;
-    uint32_t i = 0;
-    for (; i < limit; i++) {
-        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
-        if ((uint32_t)(w >> 32) == ep) break;
-        if (i > 2) __nanosleep(32);
-    }
-    if (i == limit) atomicOr(err, ERR_POLL);
-    return __uint_as_float((uint32_t)w);
-}
-// Four consecutive words (32-byte aligned); bounded.
+// Four consecutive words (32-byte aligned); bounded.  The loop polls without pausing: a pause
+// between polls (nanosleep) cost a microsecond per layer, and so did keeping more than one
+// group of a thread in flight or letting one lane per warp watch for the rest -- what counts
+// is how soon after the store the first successful load is issued.
 __device__ __forceinline__ float4 xw_poll4(const unsigned long long *p, uint32_t ep, uint32_t limit,
                                            uint32_t *err) {
     unsigned long long a = 0, b = 0, c = 0, d = 0;
@@ -166,7 +159,6 @@ __device__ __forceinline__ float4 xw_poll4(const unsigned long long *p, uint32_t
         if ((uint32_t)(a >> 32) == ep && (uint32_t)(b >> 32) == ep && (uint32_t)(c >> 32) == ep &&
             (uint32_t)(d >> 32) == ep)
             break;
-        if (i > 2) __nanosleep(32);
     }
     if (i == limit) atomicOr(err, ERR_POLL);
     return make_float4(__uint_as_float((uint32_t)a), __uint_as_float((uint32_t)b),
@@ -180,12 +172,6 @@ __device__ __forceinline__ void stamp(const Args &a, bool on, uint32_t slot) {
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
         a.prof[blockIdx.x * 16u + slot] = t;
     }
-}
-
-__device__ __forceinline__ void stamp_any(const Args &a, uint32_t slot) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    a.prof[blockIdx.x * 16u + slot] = t;
 }
 
 // Q8-A of 32 consecutive floats held four per lane by eight neighbouring lanes.
@@ -541,32 +527,26 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         uint32_t ep = S.ep0 + l;      // this layer's epoch (skips 0 on wrap-around)
         if (ep < S.ep0) ep += 1u;
 
-        // ---- phase 1: router rows x xn (one warp per row) ----
+        // ---- phase 1: router rows x xn, one warp per quarter row ----
         if (r1 > r0) mbar_wait(&S.mbar[MB_ROUTER], par, a.err);
         stamp(a, prof, 2);
-        long long dbg_c0 = clock64();
-        for (uint32_t rep = 0; rep < ((prof && a.prof_arrivals == 1) ? 2u : 1u); rep++) {
-        if (rep == 1) {
-            if (tid == 0) a.prof[blockIdx.x * 16u + 13u] = (unsigned long long)(clock64() - dbg_c0);
-            dbg_c0 = clock64();
-        }
-        for (uint32_t r = r0 + warp; r < r1; r += NW) {
-            const float4 *w4 = reinterpret_cast<const float4 *>(stage + (size_t)(r - r0) * H * 4u);
-            const float4 *x4 = reinterpret_cast<const float4 *>(S.xn);
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 1
+        for (uint32_t c = warp; c < 4u * (r1 - r0); c += NW) {
+            const uint32_t rl = c >> 2, part = c & 3u;
+            const float4 *w4 = reinterpret_cast<const float4 *>(stage + ((size_t)rl * H + part * (H / 4)) * 4u);
+            const float4 *x4 = reinterpret_cast<const float4 *>(S.xn + part * (H / 4));
+            float acc = 0.f;
 #pragma unroll
-            for (uint32_t i = 0; i < H / 128; i++) {
+            for (uint32_t i = 0; i < H / 4 / 128; i++) {
                 const float4 rw = w4[lane + 32 * i], rx = x4[lane + 32 * i];
-                acc[i & 3u] += rw.x * rx.x + rw.y * rx.y + rw.z * rx.z + rw.w * rx.w;
+                acc += rw.x * rx.x + rw.y * rx.y + rw.z * rx.z + rw.w * rx.w;
             }
-            const float t = q4b_warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
-            // logits: written here, read by every CTA in phase 2 of this layer; a CTA reaches this
-            // line for the next layer only after all CTAs published this layer's y, i.e. after
-            // they all finished reading these words
-            if (lane == 0) xw_store(a.lw + logit_pos(r, nwe), t, ep);
+            acc = q4b_warp_sum(acc);
+            // logits (four partial sums per expert): written here, read by every CTA in phase 2 of
+            // this layer; a CTA reaches this line for the next layer only after all CTAs published
+            // this layer's y, i.e. after they all finished reading these words
+            if (lane == 0) xw_store(a.lw + 4u * logit_pos(r0 + rl, nwe) + part, acc, ep);
         }
-        }
-        if (prof && a.prof_arrivals == 1 && tid == 0) a.prof[blockIdx.x * 16u + 14u] = (unsigned long long)(clock64() - dbg_c0);
         stamp(a, prof, 3);
 
         // activations of this lane's 64 columns (lane l of a gate/up tile owns columns 64 l ..)
@@ -607,7 +587,8 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         float lg = 0.f;
         uint32_t key = 0u;
         if (ex_ok) {
-            lg = xw_poll1(a.lw + tid, ep, limit, a.err);
+            const float4 pp = xw_poll4(a.lw + 4u * tid, ep, limit, a.err);
+            lg = (pp.x + pp.y) + (pp.z + pp.w);
             key = float_key(lg);
         }
         stamp(a, prof, 5);
@@ -670,50 +651,19 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
             }
         }
         stamp(a, prof, 7);
-        if (prof && a.prof_arrivals == 2 && warp == NW - 1) {
-            // diagnostic: when did the copies land?  (this warp watches instead of starting its dots)
-            if (n_chunks) mbar_wait(&S.mbar[MB_CHUNK0], par_chunk, a.err);
-            if (lane == 0) stamp_any(a, 13);
-            if (n_chunks) mbar_wait(&S.mbar[MB_CHUNK0 + n_chunks - 1], par_chunk, a.err);
-            if (lane == 0) stamp_any(a, 14);
-            mbar_wait(&S.mbar[MB_DOWN], par_chunk, a.err);
-            if (lane == 0) stamp_any(a, 15);
-        }
         // ---- phase 2c: routed gate/up dots (one tile per warp task), SwiGLU ----
-        {
-            // a warp's tasks keep their lane partials in registers; the warp reductions of all of
-            // them run interleaved at the end (one chain of shuffles instead of one per task)
-            constexpr uint32_t GT = (2u * MAX_UNITS + NW - 1u) / NW;
-            float racc[GT];
-            const uint32_t n_task = 2u * (u1 - u0);
-#pragma unroll
-            for (uint32_t i = 0; i < GT; i++) {
-                const uint32_t t = warp + i * NW;
-                racc[i] = 0.f;
-                if (t < n_task) {
-                    const uint32_t ul = t >> 1, which = t & 1u;
-                    const uint32_t k = ul / UCHUNK, j = ul - k * UCHUNK;
-                    mbar_wait(&S.mbar[MB_CHUNK0 + k], par_chunk, a.err);
-                    if (t == 0 && a.prof_arrivals != 2) stamp(a, prof, 13);
-                    const uint8_t *tile = stage + ((size_t)k * UCHUNK * 2u + which * UCHUNK + j) * Q4B_TILE_BYTES;
-                    racc[i] = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
-                }
-            }
-#pragma unroll
-            for (int o = 16; o; o >>= 1) {
-#pragma unroll
-                for (uint32_t i = 0; i < GT; i++)
-                    if (warp + i * NW < n_task) racc[i] += __shfl_xor_sync(0xffffffffu, racc[i], o);
-            }
-            if (lane == 0) {
-#pragma unroll
-                for (uint32_t i = 0; i < GT; i++) {
-                    const uint32_t t = warp + i * NW;
-                    if (t < n_task) S.gu[t >> 1][t & 1u] = racc[i];
-                }
-            }
+#pragma unroll 1
+        for (uint32_t t = warp; t < 2u * (u1 - u0); t += NW) {
+            const uint32_t ul = t >> 1, which = t & 1u;
+            const uint32_t k = ul / UCHUNK, j = ul - k * UCHUNK;
+            mbar_wait(&S.mbar[MB_CHUNK0 + k], par_chunk, a.err);
+            if (t == 0) stamp(a, prof, 13);
+            const uint8_t *tile = stage + ((size_t)k * UCHUNK * 2u + which * UCHUNK + j) * Q4B_TILE_BYTES;
+            float r = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
+            r = q4b_warp_sum(r);
+            if (lane == 0) S.gu[ul][which] = r;
         }
-        if (a.prof_arrivals == 0) stamp(a, prof, 14);
+        stamp(a, prof, 14);
         __syncthreads();   // also: every warp is done with the gate/up tiles
         if (tid < u1 - u0) xw_store(a.hw + u0 + tid, q4b_swiglu(S.gu[tid][0], S.gu[tid][1]), ep);
         if (tid == 0 && more && r1 > r0) {   // next layer's router rows
@@ -755,41 +705,24 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         {
             const uint32_t col16 = 16u * (lane & 7u);  // first activation word of this lane's 64 columns
             const uint32_t g0 = 2u * (lane & 7u);
-            constexpr uint32_t DT = (MAX_DT + NW - 1u) / NW;
-            float rd[DT];
+#pragma unroll 1
+            for (uint32_t v = v0 + warp; v < v1; v += NW) {
+                const uint32_t rq = v / ne, e = v - rq * ne;
+                int hqr[16];
 #pragma unroll
-            for (uint32_t i = 0; i < DT; i++) {
-                const uint32_t v = v0 + warp + i * NW;
-                rd[i] = 0.f;
-                long long dbg_c1 = clock64();
-                if (v < v1) {
-                    const uint32_t rq = v / ne, e = v - rq * ne;
-                    int hqr[16];
-#pragma unroll
-                    for (int c = 0; c < 16; c += 4) {
-                        const uint4 t4 = *reinterpret_cast<const uint4 *>(&S.hq[e][col16 + c]);
-                        hqr[c] = (int)t4.x;
-                        hqr[c + 1] = (int)t4.y;
-                        hqr[c + 2] = (int)t4.z;
-                        hqr[c + 3] = (int)t4.w;
-                    }
-                    rd[i] = q4b_tile_lane_dot(dstage + (size_t)(v - v0) * Q4B_TILE_BYTES, lane, tl, hqr,
-                                              S.hd[e][g0], S.hd[e][g0 + 1], S.hbs[e][g0], S.hbs[e][g0 + 1]);
-                    if (prof && a.prof_arrivals == 1 && tid == 0 && i == 0 && rd[i] != 12345.f) a.prof[blockIdx.x * 16u + 15u] = (unsigned long long)(clock64() - dbg_c1);
+                for (int c = 0; c < 16; c += 4) {
+                    const uint4 t4 = *reinterpret_cast<const uint4 *>(&S.hq[e][col16 + c]);
+                    hqr[c] = (int)t4.x;
+                    hqr[c + 1] = (int)t4.y;
+                    hqr[c + 2] = (int)t4.z;
+                    hqr[c + 3] = (int)t4.w;
                 }
-            }
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-#pragma unroll
-                for (uint32_t i = 0; i < DT; i++)
-                    if (v0 + warp + i * NW < v1) rd[i] += __shfl_xor_sync(0xffffffffu, rd[i], o);
-            }
-            if ((lane & 7u) == 0) {
-#pragma unroll
-                for (uint32_t i = 0; i < DT; i++) {
-                    const uint32_t v = v0 + warp + i * NW;
-                    if (v < v1) S.part[v - v0][lane >> 3] = S.wts[v % ne] * rd[i];
-                }
+                float r = q4b_tile_lane_dot(dstage + (size_t)(v - v0) * Q4B_TILE_BYTES, lane, tl, hqr,
+                                            S.hd[e][g0], S.hd[e][g0 + 1], S.hbs[e][g0], S.hbs[e][g0 + 1]);
+                r += __shfl_xor_sync(0xffffffffu, r, 1);
+                r += __shfl_xor_sync(0xffffffffu, r, 2);
+                r += __shfl_xor_sync(0xffffffffu, r, 4);
+                if ((lane & 7u) == 0) S.part[v - v0][lane >> 3] = S.wts[e] * r;
             }
         }
         __syncthreads();
@@ -866,12 +799,11 @@ static unsigned long long *g_s_ctr = nullptr;
 static bool g_s_attr_set = false;
 static unsigned long long *g_s_prof = nullptr;  // set by q4_cuda_fused_profile_enable(1)
 static uint32_t g_s_prof_layer = 0;
-static uint32_t g_s_prof_arrivals = 0;
 static uint32_t g_s_poll_limit = stk::POLL_LIMIT;
 
 static bool stack_scratch() {
     if (g_s_ctr) return true;
-    const size_t words = (size_t)stk::H + stk::NT + (size_t)stk::MAX_E * stk::F;
+    const size_t words = (size_t)stk::H + 4u * stk::NT + (size_t)stk::MAX_E * stk::F;
     Q4B_CHECK(cudaMalloc(&g_s_words, words * sizeof(unsigned long long)));
     Q4B_CHECK(cudaMemset(g_s_words, 0, words * sizeof(unsigned long long)));
     Q4B_CHECK(cudaMalloc(&g_s_ctr, 2 * sizeof(unsigned long long)));
@@ -903,7 +835,7 @@ static bool stack_shape_ok(const uint8_t *base, uint64_t stride, uint64_t og, ui
     const uint32_t n_chunks = (max_units + UCHUNK - 1) / UCHUNK;
     const uint32_t max_sh = (F + ncta - 1) / ncta + 1;
     const uint32_t max_dt = ((H / 4 + ncta - 1) / ncta) * ne;
-    const uint32_t max_rr = (n_expert + ncta - 1) / ncta + 1;
+    const uint32_t max_rr = (n_expert + ncta - 1) / ncta;
     if (n_chunks > MAX_CHUNKS || n_chunks > NW - 2 || max_dt > MAX_DT || max_units > MAX_UNITS ||
         max_sh > MAX_SH || ne > MAX_E || max_rr > MAX_RROWS)
         return false;
@@ -955,12 +887,11 @@ static bool stack_launch(const stk::Layer &l0, const stk::Layer *d_layers, uint3
     a.wts_out = d_wts;
     a.xw = g_s_words;
     a.lw = g_s_words + H;
-    a.hw = g_s_words + H + NT;
+    a.hw = g_s_words + H + 4u * NT;
     a.ctr = g_s_ctr;
     a.err = s.err_d;
     a.prof = g_s_prof;
     a.prof_layer = g_s_prof_layer < n_layers ? g_s_prof_layer : n_layers - 1;
-    a.prof_arrivals = g_s_prof_arrivals;
     a.y_host = y_host_dev;
     a.flag_host = flag_host_dev;
     a.flag_val = flag_val;
@@ -1180,10 +1111,7 @@ extern "C" bool q4_cuda_fused_profile_enable(int on) {
     }
     return true;
 }
-extern "C" void q4_cuda_fused_profile_layer(uint32_t layer) {
-    g_s_prof_arrivals = layer >> 30;     // top bits: 2 = record when the weight copies landed instead
-    g_s_prof_layer = layer & 0x3fffffffu;
-}
+extern "C" void q4_cuda_fused_profile_layer(uint32_t layer) { g_s_prof_layer = layer; }
 extern "C" uint32_t q4_cuda_fused_profile_read(unsigned long long *out, uint32_t max_ctas) {
     if (!g_q4b.ok || !g_s_prof || !out) return 0;
     const uint32_t n = max_ctas < (uint32_t)g_q4b.n_sm ? max_ctas : (uint32_t)g_q4b.n_sm;
