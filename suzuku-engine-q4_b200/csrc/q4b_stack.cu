@@ -219,8 +219,6 @@ struct Small {
     float hd[MAX_E][F / 32];
     int hbs[MAX_E][F / 32];
     float part[MAX_DT][4];              // phase-3 partial sums: [tile][row in tile]
-    float gu[MAX_UNITS][2];             // phase-2 gate and up dots of this CTA's units
-    float gu_sh[MAX_SH][2];             // the same for its shared-expert units
     uint32_t ck[NW][32];                // selection: candidates (key, index); general path: per-warp lists
     uint32_t ci[NW][32];
 };
@@ -559,20 +557,25 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         // ---- the shared expert's gate/up rows (its tiles were fetched a layer ahead) ----
         if (s1 > s0) {
             mbar_wait(&S.mbar[MB_SHARED], par, a.err);
-            // on the last warps: the first ones hold the router rows, the two run side by side
-            for (uint32_t t = NW - 1u - warp; t < 2u * (s1 - s0); t += NW) {
-                const uint32_t ul = t >> 1, which = t & 1u;
-                const uint8_t *tile = sstage + ((size_t)which * MAX_SH + ul) * Q4B_TILE_BYTES;
-                float r = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
-                r = q4b_warp_sum(r);
-                if (lane == 0) S.gu_sh[ul][which] = r;
+            // One warp per hidden unit: its gate tile and its up tile back to back (two independent
+            // instruction streams), both sums, SwiGLU, and the value goes out at once.  On the
+            // last warps: the first ones hold the router rows, the two run side by side.
+            // Hidden values: written here and after the routed dots, read by every CTA in phase 3
+            // of this layer; a CTA reaches these lines for the next layer only after all CTAs
+            // published this layer's y, i.e. after they all finished reading these words.
+            for (uint32_t ul = NW - 1u - warp; ul < s1 - s0; ul += NW) {
+                const uint8_t *tile = sstage + (size_t)ul * Q4B_TILE_BYTES;
+                float g = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
+                float u = q4b_tile_lane_dot(tile + (size_t)MAX_SH * Q4B_TILE_BYTES, lane, tl, q, dx0, dx1, bs0, bs1);
+#pragma unroll
+                for (int o = 16; o; o >>= 1) {
+                    g += __shfl_xor_sync(0xffffffffu, g, o);
+                    u += __shfl_xor_sync(0xffffffffu, u, o);
+                }
+                if (lane == 0) xw_store(a.hw + a.topk * F + s0 + ul, q4b_swiglu(g, u), ep);
             }
         }
-        __syncthreads();   // also: every warp is done with the router rows and the shared tiles
-        // hidden values: written here and after the routed dots, read by every CTA in phase 3 of
-        // this layer; same argument as for the logits
-        if (tid < s1 - s0)
-            xw_store(a.hw + a.topk * F + s0 + tid, q4b_swiglu(S.gu_sh[tid][0], S.gu_sh[tid][1]), ep);
+        __syncthreads();   // every warp is done with the router rows and the shared tiles
         if (tid == 32 && more && s1 > s0) {   // next layer's shared-expert tiles
             const uint32_t bytes = (s1 - s0) * Q4B_TILE_BYTES;
             const uint8_t *pk = nxt.base + (uint64_t)a.shared_slot * a.stride;
@@ -651,21 +654,24 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
             }
         }
         stamp(a, prof, 7);
-        // ---- phase 2c: routed gate/up dots (one tile per warp task), SwiGLU ----
+        // ---- phase 2c: routed hidden units (gate and up tile of a unit by one warp), SwiGLU ----
 #pragma unroll 1
-        for (uint32_t t = warp; t < 2u * (u1 - u0); t += NW) {
-            const uint32_t ul = t >> 1, which = t & 1u;
+        for (uint32_t ul = warp; ul < u1 - u0; ul += NW) {
             const uint32_t k = ul / UCHUNK, j = ul - k * UCHUNK;
             mbar_wait(&S.mbar[MB_CHUNK0 + k], par_chunk, a.err);
-            if (t == 0) stamp(a, prof, 13);
-            const uint8_t *tile = stage + ((size_t)k * UCHUNK * 2u + which * UCHUNK + j) * Q4B_TILE_BYTES;
-            float r = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
-            r = q4b_warp_sum(r);
-            if (lane == 0) S.gu[ul][which] = r;
+            if (ul == 0) stamp(a, prof, 13);
+            const uint8_t *tile = stage + ((size_t)k * UCHUNK * 2u + j) * Q4B_TILE_BYTES;
+            float g = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
+            float u = q4b_tile_lane_dot(tile + (size_t)UCHUNK * Q4B_TILE_BYTES, lane, tl, q, dx0, dx1, bs0, bs1);
+#pragma unroll
+            for (int o = 16; o; o >>= 1) {
+                g += __shfl_xor_sync(0xffffffffu, g, o);
+                u += __shfl_xor_sync(0xffffffffu, u, o);
+            }
+            if (lane == 0) xw_store(a.hw + u0 + ul, q4b_swiglu(g, u), ep);
         }
         stamp(a, prof, 14);
-        __syncthreads();   // also: every warp is done with the gate/up tiles
-        if (tid < u1 - u0) xw_store(a.hw + u0 + tid, q4b_swiglu(S.gu[tid][0], S.gu[tid][1]), ep);
+        __syncthreads();   // every warp is done with the gate/up tiles
         if (tid == 0 && more && r1 > r0) {   // next layer's router rows
             const uint32_t bytes = (r1 - r0) * H * 4u;
             mbar_expect_tx(&S.mbar[MB_ROUTER], bytes);
@@ -705,24 +711,39 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         {
             const uint32_t col16 = 16u * (lane & 7u);  // first activation word of this lane's 64 columns
             const uint32_t g0 = 2u * (lane & 7u);
+            // DK tiles per warp task: DK independent instruction streams for the scheduler to
+            // interleave (a lone tile dot is a chain of dependent shared-memory lookups)
+            constexpr uint32_t DK = 3;
 #pragma unroll 1
-            for (uint32_t v = v0 + warp; v < v1; v += NW) {
-                const uint32_t rq = v / ne, e = v - rq * ne;
-                int hqr[16];
+            for (uint32_t v = v0 + DK * warp; v < v1; v += DK * NW) {
+                float r[DK];
+                uint32_t e[DK];
 #pragma unroll
-                for (int c = 0; c < 16; c += 4) {
-                    const uint4 t4 = *reinterpret_cast<const uint4 *>(&S.hq[e][col16 + c]);
-                    hqr[c] = (int)t4.x;
-                    hqr[c + 1] = (int)t4.y;
-                    hqr[c + 2] = (int)t4.z;
-                    hqr[c + 3] = (int)t4.w;
+                for (uint32_t i = 0; i < DK; i++) {
+                    const uint32_t vi = min(v + i, v1 - 1u);   // past the end: the last tile again, not stored
+                    e[i] = vi % ne;
+                    int hqr[16];
+#pragma unroll
+                    for (int c = 0; c < 16; c += 4) {
+                        const uint4 t4 = *reinterpret_cast<const uint4 *>(&S.hq[e[i]][col16 + c]);
+                        hqr[c] = (int)t4.x;
+                        hqr[c + 1] = (int)t4.y;
+                        hqr[c + 2] = (int)t4.z;
+                        hqr[c + 3] = (int)t4.w;
+                    }
+                    r[i] = q4b_tile_lane_dot(dstage + (size_t)(vi - v0) * Q4B_TILE_BYTES, lane, tl, hqr,
+                                             S.hd[e[i]][g0], S.hd[e[i]][g0 + 1], S.hbs[e[i]][g0], S.hbs[e[i]][g0 + 1]);
                 }
-                float r = q4b_tile_lane_dot(dstage + (size_t)(v - v0) * Q4B_TILE_BYTES, lane, tl, hqr,
-                                            S.hd[e][g0], S.hd[e][g0 + 1], S.hbs[e][g0], S.hbs[e][g0 + 1]);
-                r += __shfl_xor_sync(0xffffffffu, r, 1);
-                r += __shfl_xor_sync(0xffffffffu, r, 2);
-                r += __shfl_xor_sync(0xffffffffu, r, 4);
-                if ((lane & 7u) == 0) S.part[v - v0][lane >> 3] = S.wts[e] * r;
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) {
+#pragma unroll
+                    for (uint32_t i = 0; i < DK; i++) r[i] += __shfl_xor_sync(0xffffffffu, r[i], o);
+                }
+                if ((lane & 7u) == 0) {
+#pragma unroll
+                    for (uint32_t i = 0; i < DK; i++)
+                        if (v + i < v1) S.part[v + i - v0][lane >> 3] = S.wts[e[i]] * r[i];
+                }
             }
         }
         __syncthreads();
