@@ -546,6 +546,10 @@ bool q4_cuda_synth_normal(float *d_out, uint64_t n, uint64_t seed, float mean, f
 bool q4_cuda_timer_begin(void);
 bool q4_cuda_timer_end(void);
 float q4_cuda_timer_ms(void);
+/* The same with many marks: mark(i) records mark i (i < 2048) on the compute stream;
+ * between_ms(i, j) waits for mark j and returns the device time from mark i to mark j. */
+bool q4_cuda_timer_mark(uint32_t i);
+float q4_cuda_timer_between_ms(uint32_t i, uint32_t j);
 /* Number of kernels this library has launched since init (its own count). */
 uint64_t q4_cuda_launch_count(void);
 /* Last error word written by a kernel's self-check (0 = none); clears it. */

@@ -255,6 +255,7 @@ class Reference:
         L.q4ref_dot8_avx2_iq4xs.argtypes = [_u8p, C.c_void_p, C.c_uint64]
         L.q4ref_time_jobs.restype = C.c_double
         L.q4ref_time_layers.restype = C.c_double
+        L.q4ref_time_layers_win.restype = C.c_double
 
     def quant8(self, x):
         x = _f32(x).ravel()
@@ -411,6 +412,32 @@ class Reference:
                                        C.c_uint32(n_ff), _p(y, _f32p), _p(ids, _i32p))
         assert t >= 0, t
         return float(t), ids, y
+
+    def time_layers_win(self, layers, topk, steps, x, n_embd, n_ff, chain, eps=1e-6):
+        """`steps` layer jobs of len(x) tokens each through the reference's host routing and its
+        window jobs (q4_cpuex_dispatch_win).  Job j runs layer j % len(layers); chain: a job's
+        output rows feed the next.  Returns (seconds, seconds spent in norm + router + top-k, y)."""
+        n_expert = layers[0]["experts"].shape[0]
+        keep, ptrs = [], []
+        for L in layers:
+            ex, sh = _u8(L["experts"]), _u8(L["shared"])
+            keep += [ex, sh]
+            ptrs += [ex.ctypes.data + e * ex.shape[1] for e in range(n_expert)]
+            ptrs.append(sh.ctypes.data)
+        arr = (C.c_void_p * len(ptrs))(*ptrs)
+        routers = [_f32(L["router"]) for L in layers]
+        norms = [_f32(L["norm_w"]) for L in layers]
+        r_arr = (C.c_void_p * len(layers))(*[r.ctypes.data for r in routers])
+        n_arr = (C.c_void_p * len(layers))(*[n.ctypes.data for n in norms])
+        x = _f32(x)
+        y = np.zeros_like(x)
+        rs = C.c_double(0.0)
+        t = self.lib.q4ref_time_layers_win(arr, C.c_uint32(len(layers)), C.c_uint32(n_expert), r_arr, n_arr,
+                                           C.c_float(eps), C.c_uint32(topk), C.c_uint32(steps), _p(x, _f32p),
+                                           C.c_uint32(x.shape[0]), C.c_uint32(n_embd), C.c_uint32(n_ff),
+                                           C.c_int(1 if chain else 0), _p(y, _f32p), C.byref(rs))
+        assert t >= 0, t
+        return float(t), float(rs.value), y
 
 
 _ORACLE = None

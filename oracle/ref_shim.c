@@ -246,3 +246,83 @@ double q4ref_time_layers(const uint8_t *const *packs, uint32_t n_layers,
     free(p);
     return (double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec);
 }
+
+static double shim_now(void) {
+    struct timespec t;
+    clock_gettime(CLOCK_MONOTONIC, &t);
+    return (double)t.tv_sec + 1e-9 * (double)t.tv_nsec;
+}
+
+/* Timed loop for the CPU baseline of the many-token workloads: `steps` layer jobs of
+ * n_tok tokens each.  Per layer job every token is normed and routed on the host
+ * (q4_rms_norm, q4_gemv F32, q4_softmax, q4_topk: src/q4_quant.c:595-755); the expert
+ * work then goes to the worker pool in windows of as many tokens as one window job takes
+ * (at most 8 tokens and 64 picks, src/q4_cpuexp.c:2618-2640), the shared expert as one
+ * more pick of every token at weight 1; a last single token goes through the one-token
+ * job.  Layer l of job j is j % n_layers (packs as in q4ref_time_layers).  chain != 0:
+ * the output rows of a job are the input rows of the next (a stack of layers); else
+ * every job reads x.  x, y, scratch: n_tok rows of n_embd floats.  Returns seconds
+ * (< 0 on error); *router_s receives the part spent in norm + router + softmax + top-k. */
+double q4ref_time_layers_win(const uint8_t *const *packs, uint32_t n_layers, uint32_t n_expert,
+                             const float *const *routers, const float *const *norm_w, float eps,
+                             uint32_t topk, uint32_t steps, const float *x, uint32_t n_tok,
+                             uint32_t n_embd, uint32_t n_ff, int chain, float *y, double *router_s) {
+    const uint32_t k1 = topk + 1;
+    uint32_t win = 64u / k1;
+    if (win > 8) win = 8;
+    if (k1 > CPX_MAX_E || win < 1 || n_tok == 0) return -1.0;
+    float *xn = malloc(sizeof(float) * (size_t)n_tok * n_embd);
+    float *cur = malloc(sizeof(float) * (size_t)n_tok * n_embd);
+    float *p = malloc(sizeof(float) * n_expert);
+    int32_t *ids = malloc(sizeof(int32_t) * (size_t)n_tok * k1);
+    float *wts = malloc(sizeof(float) * (size_t)n_tok * k1);
+    uint32_t tn[8];
+    if (!xn || !cur || !p || !ids || !wts) return -1.0;
+    memcpy(cur, x, sizeof(float) * (size_t)n_tok * n_embd);
+    for (uint32_t t = 0; t < 8; t++) tn[t] = k1;
+    double t_router = 0.0;
+    const double t0 = shim_now();
+    for (uint32_t j = 0; j < steps; j++) {
+        const uint32_t l = j % n_layers;
+        shim_setup(packs + (size_t)l * (n_expert + 1), n_expert + 1, n_embd, n_ff);
+        const double r0 = shim_now();
+        for (uint32_t t = 0; t < n_tok; t++) {
+            q4_rms_norm(cur + (size_t)t * n_embd, norm_w[l], xn + (size_t)t * n_embd, n_embd, eps);
+            memset(p, 0, sizeof(float) * n_expert);
+            q4_gemv(Q4_T_F32, (const uint8_t *)routers[l], n_expert, n_embd, xn + (size_t)t * n_embd, p, 1.0f);
+            q4_softmax(p, n_expert);
+            q4_topk(p, n_expert, topk, ids + (size_t)t * k1, wts + (size_t)t * k1, true);
+            ids[(size_t)t * k1 + topk] = (int32_t)n_expert;
+            wts[(size_t)t * k1 + topk] = 1.0f;
+        }
+        t_router += shim_now() - r0;
+        for (uint32_t t = 0; t < n_tok;) {
+            uint32_t n = n_tok - t < win ? n_tok - t : win;
+            uint64_t tag = 0;
+            int s;
+            if (n >= 2) {
+                while ((s = q4_cpuex_dispatch_win(&g_shim_gguf, &g_shim, 0, xn + (size_t)t * n_embd, n,
+                                                  ids + (size_t)t * k1, wts + (size_t)t * k1, tn,
+                                                  y + (size_t)t * n_embd, &tag)) == -1)
+                    q4_cpuex_retire();
+            } else {
+                while ((s = q4_cpuex_dispatch2(&g_shim_gguf, &g_shim, 0, xn + (size_t)t * n_embd,
+                                               ids + (size_t)t * k1, wts + (size_t)t * k1, k1,
+                                               y + (size_t)t * n_embd, &tag)) == -1)
+                    q4_cpuex_retire();
+            }
+            if (s < 0) return -1.0;
+            if (!q4_cpuex_join_tag(s, tag)) return -2.0;
+            t += n;
+        }
+        if (chain) memcpy(cur, y, sizeof(float) * (size_t)n_tok * n_embd);
+    }
+    const double t1 = shim_now();
+    if (router_s) *router_s = t_router;
+    free(xn);
+    free(cur);
+    free(p);
+    free(ids);
+    free(wts);
+    return t1 - t0;
+}

@@ -199,6 +199,8 @@ SIGNATURES = {
     "q4_cuda_timer_begin": (b, []),
     "q4_cuda_timer_end": (b, []),
     "q4_cuda_timer_ms": (f32, []),
+    "q4_cuda_timer_mark": (b, [u32]),
+    "q4_cuda_timer_between_ms": (f32, [u32, u32]),
     "q4_cuda_launch_count": (u64, []),
     "q4_cuda_device_error": (u32, []),
 }

@@ -54,6 +54,7 @@ extern Q4bState g_q4b;
 #define Q4B_XQ_SLICES 80u     // >= 64 experts per exec + shared + tokens of a window
 #define Q4B_XQ_MAXLEN 16384u  // widest activation row the decode path quantises
 #define Q4B_MAX_TOK 8u        // tokens per fused decode / verify call
+#define Q4B_MAX_MARKS 2048u   // q4_cuda_timer_mark slots
 
 #define Q4B_CHECK(call)                                                              \
     do {                                                                             \

@@ -15,6 +15,7 @@ Q4bState g_q4b = {};
 bool q4b_fused_warm();   // q4b_stack.cu: scratch of the persistent decode kernel
 void q4b_fused_shutdown();
 void q4b_stack_forget_host(const void *h);
+static void timer_marks_shutdown();
 bool q4b_window_warm();  // q4b_grouped.cu: scratch of the verify-window path
 bool q4b_elem_warm();    // q4b_elem.cu: lists of the per-token exec, rows of the 2..8-row GEMV
 void q4b_elem_shutdown();
@@ -229,6 +230,7 @@ extern "C" void q4_hip_shutdown(void) {
     cudaFreeHost(s.err_h);
     cudaEventDestroy(g_ev0);
     cudaEventDestroy(g_ev1);
+    timer_marks_shutdown();
     cudaStreamDestroy(s.stream);
     cudaStreamDestroy(s.copy_stream);
     cudaStreamDestroy(s.aux_stream);
@@ -436,6 +438,30 @@ extern "C" float q4_cuda_timer_ms(void) {
     float ms = -1.f;
     if (cudaEventElapsedTime(&ms, g_ev0, g_ev1) != cudaSuccess) return -1.f;
     return ms;
+}
+// A row of marks on the compute stream (events created on first use, kept until shutdown): a
+// benchmark that repeats a timed region marks its boundaries and reads the intervals afterwards.
+static cudaEvent_t g_marks[Q4B_MAX_MARKS];
+static uint32_t g_marks_made = 0;
+extern "C" bool q4_cuda_timer_mark(uint32_t i) {
+    if (!g_q4b.ok || i >= Q4B_MAX_MARKS) return false;
+    while (g_marks_made <= i) {
+        Q4B_CHECK(cudaEventCreate(&g_marks[g_marks_made]));
+        g_marks_made++;
+    }
+    Q4B_CHECK(cudaEventRecord(g_marks[i], g_q4b.stream));
+    return true;
+}
+extern "C" float q4_cuda_timer_between_ms(uint32_t i, uint32_t j) {
+    if (!g_q4b.ok || i >= g_marks_made || j >= g_marks_made) return -1.f;
+    if (cudaEventSynchronize(g_marks[j]) != cudaSuccess) return -1.f;
+    float ms = -1.f;
+    if (cudaEventElapsedTime(&ms, g_marks[i], g_marks[j]) != cudaSuccess) return -1.f;
+    return ms;
+}
+static void timer_marks_shutdown() {
+    for (uint32_t i = 0; i < g_marks_made; i++) cudaEventDestroy(g_marks[i]);
+    g_marks_made = 0;
 }
 extern "C" uint64_t q4_cuda_launch_count(void) { return g_q4b_launches.load(); }
 extern "C" uint32_t q4_cuda_device_error(void) {
