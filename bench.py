@@ -11,12 +11,22 @@ layers of seeded synthetic weights, 33 GB resident in HBM) so no step finds its
 weights in L2.  Metric: layer-tokens per second.
 
 Printed: one JSON line (see the keys below).  `value` is timed with inputs
-resident on the device; `e2e` goes through the same C-ABI call with the token's
-hidden state copied from pinned host memory and the result read back every
-step.  `cpu_baseline` times the reference engine's own CPU path for the same
-layer on this host's cores.  `--impl reference` prints that CPU arm alone.
+resident on the device (the K steps run as launches of the persistent kernel over
+consecutive layers, y of a layer feeding the next); `e2e` goes through the
+one-layer C-ABI call with the token's hidden state copied from pinned host memory
+and the result read back every step.  Whatever K is, the timed set of steps is
+repeated until at least 50 ms have been timed; the per-step time is the median
+over the repeats.  `cpu_baseline` times the reference engine's own CPU path for
+the same layer on this host's cores.  `details.other_workloads` carries the other
+benchmark configurations (0, 2, 3 and 4 on one GPU), each with its own roofline
+and CPU figure.  `--impl reference` prints the CPU arm alone.
+
+N >= 2 (one process per GPU, torchrun environment): config 4, expert-parallel
+decode of 64 tokens through 48 layers, strong scaling.
 """
 import argparse
+import atexit
+import ctypes
 import json
 import os
 import subprocess
@@ -25,9 +35,10 @@ import threading
 import time
 
 # CPU arm: the reference's expert pool gets the cores; its small host-side router GEMV (OpenMP in
-# the reference's build) stays on one thread -- an OpenMP team next to the pool's spinning workers
-# was measured 13x slower.  Must be set before the OpenMP runtime is loaded.
-os.environ["OMP_NUM_THREADS"] = os.environ.get("Q4B_REF_OMP", "1")
+# the reference's build) stays on one thread unless told otherwise -- an OpenMP team next to the
+# pool's spinning workers was measured 13x slower (the line reports a figure with a passive team
+# beside it).  Must be set before the OpenMP runtime is loaded.
+os.environ.setdefault("OMP_NUM_THREADS", "1")
 
 import numpy as np  # noqa: E402
 
@@ -43,21 +54,47 @@ PACK = 2 * N_FF * (N_EMBD // 256) * IQ3S_BLOCK + N_EMBD * (N_FF // 256) * IQ3S_B
 ROUTER_BYTES = N_EXPERT * N_EMBD * 4
 # algorithmic bytes of one layer-token: router + (top-k + shared) expert packs
 STEP_BYTES = ROUTER_BYTES + (TOPK + 1) * PACK
-# DRAM bytes of one launch of the persistent decode kernel, from an ncu capture of this
-# workload (read 19,163,136 + write 0..256); the algorithmic figure is STEP_BYTES
-FUSED_DRAM_BYTES_PER_LAUNCH = 19159040
 METRIC = "moe_layer_decode_tokens_per_s"
 UNIT = "layer-tok/s"
+DTYPE = "int8 x IQ3_S, fp32 accumulate"
+MIN_TIMED_MS = 50.0
+SEED = 2026
+N_LAYERS = 48
+
+CONFIG1 = {"workload": "config1: one MoE layer, decode batch 1, hidden 2048, ff 512, "
+                       "512 experts top-10 + shared, IQ3_S x q8",
+           "layers_rotated": N_LAYERS,
+           "l2": "inputs larger than L2: every step reads a different layer (a repeat of the "
+                 "timed steps reads at least 380 MB of weights)",
+           "algorithmic_bytes_per_step": STEP_BYTES}
+
+
+def config4(world, n_layers):
+    return {"workload": "config4: expert-parallel decode, 64 tokens x %d MoE layers per step, 512 "
+                        "experts top-10 + shared, experts sharded %d-way, NCCL dispatch/combine"
+                        % (n_layers, world),
+            "l2": "inputs larger than L2: a step reads %d layers of weights" % n_layers,
+            "tokens_per_rank": 64 // world, "experts_per_rank": N_EXPERT // world}
 
 
 def read_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         try:
-            return float(json.load(open(p))["hbm_gbs"]), "measured"
+            d = json.load(open(p))
+            return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
         except Exception:
             pass
-    return 6650.0, "fallback"
+    return 6650.0, 1590.0, "fallback"
+
+
+def read_traffic(name):
+    """DRAM bytes per unit from the small JSON beside a profile summary (None if absent)."""
+    p = os.path.join(ROOT, "profiles", name)
+    try:
+        return json.load(open(p))
+    except Exception:
+        return None
 
 
 class ClockSampler:
@@ -111,131 +148,6 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-class Workload:
-    """48 layers of synthetic weights generated on the device."""
-
-    def __init__(self, pkg, n_layers, seed=2026):
-        self.pkg = pkg
-        self.dev = pkg.Device()
-        lib = self.lib = self.dev.lib
-        self.n_layers = n_layers
-        self.slots_per_layer = N_EXPERT + 1
-        n_slots = n_layers * self.slots_per_layer
-        if not lib.q4_hip_experts_alloc_a(0, n_slots, PACK):
-            raise MemoryError("expert arena of %d slots" % n_slots)
-        self.base = lib.q4_hip_experts_base_a(0)
-        self.stride = lib.q4_hip_experts_stride_a(0)
-        assert lib.q4_cuda_synth_iq3s(self.base, n_slots * (PACK // IQ3S_BLOCK), seed)
-        self.tiled = bool(lib.q4_cuda_experts_tiled_a(0))
-        if self.tiled:      # generated in the engine's byte order: convert to the resident format
-            assert lib.q4_cuda_experts_retile_a(0, 0, n_slots)
-        self.d_router = self.dev.malloc(n_layers * ROUTER_BYTES)
-        assert lib.q4_cuda_synth_normal(self.d_router, n_layers * N_EXPERT * N_EMBD, seed + 1, 0.0, 0.02)
-        self.d_norm = self.dev.malloc(n_layers * N_EMBD * 4)
-        assert lib.q4_cuda_synth_normal(self.d_norm, n_layers * N_EMBD, seed + 2, 1.0, 0.1)
-        self.n_x = 64
-        self.x_host = pkg.synth.hidden(seed + 3, self.n_x, N_EMBD)
-        self.d_xpool = self.dev.upload(self.x_host)
-        self.d_x = self.dev.malloc(N_EMBD * 4)
-        self.d_y = self.dev.malloc(N_EMBD * 4)
-        self.d_ids = self.dev.malloc(64 * 4)
-        self.d_wts = self.dev.malloc(64 * 4)
-        rb = N_EMBD // 256 * IQ3S_BLOCK
-        self.og, self.ou, self.od = 0, N_FF * rb, 2 * N_FF * rb
-        # pinned staging for the end-to-end leg
-        self.h_x = lib.q4_hip_host_alloc_coh(N_EMBD * 4)
-        self.h_y = lib.q4_hip_host_alloc_coh(N_EMBD * 4)
-        self.y_out = np.zeros(N_EMBD, np.float32)
-        self.dev.sync()
-
-    def layer_base(self, l):
-        return self.base + l * self.slots_per_layer * self.stride
-
-    def step(self, i, d_x):
-        l = i % self.n_layers
-        ok = self.lib.q4_cuda_moe_decode(
-            self.layer_base(l), self.stride, self.og, self.ou, self.od, N_EXPERT, d_x,
-            self.d_norm + l * N_EMBD * 4, EPS, self.d_router + l * ROUTER_BYTES, N_EXPERT, TOPK,
-            N_EMBD, N_FF, self.d_y, self.d_ids, self.d_wts)
-        if not ok:
-            raise RuntimeError("q4_cuda_moe_decode refused")
-
-    def capture(self, g_steps):
-        """CUDA graphs of g_steps consecutive steps each (one layer per step), enough
-        of them to visit every layer, so that the device-resident leg is not paced
-        by the host's launch loop."""
-        self.g_steps = g_steps
-        self.graphs = []
-        n_var = (self.n_layers + g_steps - 1) // g_steps
-        for v in range(n_var):
-            assert self.lib.q4_hip_graph_begin() == 1
-            for i in range(v * g_steps, (v + 1) * g_steps):
-                self.step(i, self.d_xpool + (i % self.n_x) * N_EMBD * 4)
-            g = self.lib.q4_hip_graph_end()
-            if not g:
-                raise RuntimeError("graph capture failed")
-            self.graphs.append(g)
-
-    def capture_tail(self, n):
-        """One more graph of n < g_steps steps: the remainder when the step count is not a
-        multiple of the graph length."""
-        self.tail = None
-        if n:
-            assert self.lib.q4_hip_graph_begin() == 1
-            for i in range(n):
-                self.step(i, self.d_xpool + (i % self.n_x) * N_EMBD * 4)
-            self.tail = self.lib.q4_hip_graph_end()
-            if not self.tail:
-                raise RuntimeError("graph capture failed")
-
-    def run_resident(self, n_graphs, first=0, tail=False):
-        for r in range(first, first + n_graphs):
-            if not self.lib.q4_hip_graph_launch(self.graphs[r % len(self.graphs)]):
-                raise RuntimeError("graph launch failed")
-        if tail and self.tail and not self.lib.q4_hip_graph_launch(self.tail):
-            raise RuntimeError("graph launch failed")
-
-    def run_e2e(self, steps, first=0):
-        """Per step: the token's row is written into pinned host memory, the layer runs through the
-        host-buffer call (arguments bound once per layer), the 8 KB result is read on the host."""
-        import ctypes
-        lib = self.lib
-        if not hasattr(self, "plans"):
-            self.plans = []
-            for l in range(self.n_layers):
-                p = lib.q4_cuda_decode_plan(self.layer_base(l), self.stride, self.og, self.ou, self.od,
-                                            N_EXPERT, self.d_norm + l * N_EMBD * 4, EPS,
-                                            self.d_router + l * ROUTER_BYTES, N_EXPERT, TOPK, N_EMBD, N_FF)
-                if not p:
-                    raise RuntimeError("q4_cuda_decode_plan refused")
-                self.plans.append(p)
-        run, h_x, h_y = lib.q4_cuda_decode_plan_host, self.h_x, self.h_y
-        for i in range(first, first + steps):
-            ctypes.memmove(h_x, self.x_host[i % self.n_x].ctypes.data, N_EMBD * 4)
-            ok = run(self.plans[i % self.n_layers], h_x, h_y)
-            if not ok:
-                raise RuntimeError("q4_cuda_decode_plan_host refused")
-            ctypes.memmove(self.y_out.ctypes.data, self.h_y, N_EMBD * 4)   # the step's result, read on the host
-
-    def host_layers(self, n):
-        """Copies of the first n layers' tensors on the host (for the CPU arm)."""
-        out = []
-        for l in range(n):
-            packs = np.empty((self.slots_per_layer, PACK), np.uint8)
-            for e in range(self.slots_per_layer):   # engine byte order, whatever the arena holds
-                assert self.lib.q4_cuda_experts_get_a(0, l * self.slots_per_layer + e,
-                                                      packs[e].ctypes.data, PACK)
-            out.append({
-                "experts": packs[:N_EXPERT], "shared": packs[N_EXPERT],
-                "router": self.dev.download(self.d_router + l * ROUTER_BYTES, (N_EXPERT, N_EMBD), np.float32),
-                "norm_w": self.dev.download(self.d_norm + l * N_EMBD * 4, (N_EMBD,), np.float32)})
-        return out
-
-
-def host_synth_layers(pkg, n, seed=2026):
-    return [pkg.synth.layer(seed + 17 * l, N_EXPERT, N_EMBD, N_FF) for l in range(n)]
-
-
 def cpu_model():
     try:
         for line in open("/proc/cpuinfo"):
@@ -244,25 +156,6 @@ def cpu_model():
     except OSError:
         pass
     return "unknown"
-
-
-def cpu_arm(pkg, layers, x_host, budget_s):
-    """Time the reference's CPU path (oracle/_ref) for whole layer-tokens."""
-    from oracle import pyoracle
-    ref = pyoracle.reference()
-    kind = "reference"
-    if ref is None:
-        return None
-    ncpu = os.cpu_count() or 2
-    os.environ.setdefault("Q4_CPU_THREADS", str(max(1, min(16, ncpu - 1))))
-    t, _, _ = ref.time_layers(layers, TOPK, 4, x_host, N_EMBD, N_FF, EPS)  # warm-up, pool start
-    per = max(t / 4, 1e-5)
-    jobs = int(max(16, min(20000, budget_s / per)))
-    t, _, _ = ref.time_layers(layers, TOPK, jobs, x_host, N_EMBD, N_FF, EPS)
-    return {"value": jobs / t, "unit": UNIT, "cores": ref.threads(), "kind": kind, "cpu_model": cpu_model(),
-            "sample": "%d layer-tokens over %d layers (%.1f s), router+top-k on the host, "
-                      "experts on the reference's worker pool" % (jobs, len(layers), t),
-            "ms_per_step": 1e3 * t / jobs, "jobs": jobs}
 
 
 def exchange_id(rank, world, make_id):
@@ -301,100 +194,289 @@ def exchange_id(rank, world, make_id):
     return buf
 
 
-EP_TOKENS = 64          # config 4: batch of 64 tokens ...
-EP_LAYERS = 48          # ... through 48 MoE layers
+def median_step(lib, enqueue_set, units_per_set, warm_sets, min_ms=MIN_TIMED_MS, max_repeats=1000):
+    """Device time per unit: `enqueue_set(r)` enqueues one set of steps (repeat number r); the
+    set is repeated until min_ms have been timed, each repeat between its own pair of marks on
+    the compute stream.  Returns (median ms per unit, repeats, total timed ms, launches)."""
+    for r in range(warm_sets):
+        enqueue_set(r)
+    lib.q4_hip_stream_sync()
+    # a first timed repeat sizes the run
+    lib.q4_cuda_timer_mark(0)
+    enqueue_set(warm_sets)
+    lib.q4_cuda_timer_mark(1)
+    first = max(lib.q4_cuda_timer_between_ms(0, 1), 1e-4)
+    repeats = int(min(max_repeats, max(3, np.ceil(1.3 * min_ms / first))))   # the first set runs slow
+    l0 = lib.q4_cuda_launch_count()
+    for r in range(repeats):
+        lib.q4_cuda_timer_mark(2 * r)
+        enqueue_set(warm_sets + 1 + r)
+        lib.q4_cuda_timer_mark(2 * r + 1)
+    per = [lib.q4_cuda_timer_between_ms(2 * r, 2 * r + 1) for r in range(repeats)]
+    launches = lib.q4_cuda_launch_count() - l0
+    return float(np.median(per)) / units_per_set, repeats, float(np.sum(per)), int(launches)
 
 
-class EpJob:
-    """64 tokens x n_layers MoE layers on `world` ranks; this object is one rank's part.
-    world == 1 is the same job on one GPU through q4_cuda_moe_layer_n."""
+def median_wall(run_set, units_per_set, warm_sets, min_ms=MIN_TIMED_MS, max_repeats=1000):
+    """Wall-clock time per unit of a host-synchronous set of steps, median over repeats."""
+    for r in range(warm_sets):
+        run_set(r)
+    t0 = time.perf_counter()
+    run_set(warm_sets)
+    first = max(1e3 * (time.perf_counter() - t0), 1e-3)
+    repeats = int(min(max_repeats, max(3, np.ceil(min_ms / first))))
+    per = []
+    for r in range(repeats):
+        t0 = time.perf_counter()
+        run_set(warm_sets + 1 + r)
+        per.append(1e3 * (time.perf_counter() - t0))
+    return float(np.median(per)) / units_per_set, repeats
 
-    def __init__(self, pkg, dev, ep, arena, rank, world, n_layers, tokens=EP_TOKENS, zipf=False):
-        import ctypes
-        self.lib = lib = dev.lib
-        if os.environ.get("Q4B_TC_MODE"):   # experiments: which grouped-product kernel runs (default: split by rows)
-            assert lib.q4_cuda_mmq_tc_mode(int(os.environ["Q4B_TC_MODE"]))
-        self.ep, self.world, self.n_layers, self.arena = ep, world, n_layers, arena
-        self.tokens = tokens
-        self.t_local = tokens // world
-        e_local = self.e_local = N_EXPERT // world
-        self.slots_l = e_local + 1
+
+class StackDesc(ctypes.Structure):
+    _fields_ = [("base", ctypes.c_void_p), ("norm", ctypes.c_void_p), ("router", ctypes.c_void_p)]
+
+
+class Model:
+    """n_layers MoE layers of seeded synthetic weights generated on the device: an arena of
+    n_layers x (experts_here + 1) packs (the shared expert last in each layer), fp32 routers
+    and norm weights.  Expert (layer, e) has the same bytes whatever shard holds it: a rank
+    of an expert-parallel run generates its range [e_first, e_first + e_count) of the full
+    seeded tensor."""
+
+    def __init__(self, dev, n_layers, arena=0, e_first=0, e_count=N_EXPERT, seed=SEED):
+        self.dev, self.lib = dev, dev.lib
+        lib = self.lib
+        self.n_layers, self.arena, self.e_count = n_layers, arena, e_count
+        self.slots_l = e_count + 1
         bpp = PACK // IQ3S_BLOCK            # super-blocks per expert pack
         if not lib.q4_hip_experts_alloc_a(arena, n_layers * self.slots_l, PACK):
-            raise MemoryError("expert arena")
+            raise MemoryError("expert arena of %d slots" % (n_layers * self.slots_l))
         self.base, self.stride = lib.q4_hip_experts_base_a(arena), lib.q4_hip_experts_stride_a(arena)
-        # expert (layer, e) has the same bytes at every world size: each rank generates
-        # its range of the full seeded tensor, then the layer's shared expert
         for l in range(n_layers):
-            lb = self.base + l * self.slots_l * self.stride
-            first = (l * (N_EXPERT + 1) + rank * e_local) * bpp
-            assert lib.q4_cuda_synth_iq3s_at(lb, e_local * bpp, 2026, first)
-            assert lib.q4_cuda_synth_iq3s_at(lb + e_local * self.stride, bpp, 2026,
+            lb = self.layer_base(l)
+            assert lib.q4_cuda_synth_iq3s_at(lb, e_count * bpp, seed, (l * (N_EXPERT + 1) + e_first) * bpp)
+            assert lib.q4_cuda_synth_iq3s_at(lb + e_count * self.stride, bpp, seed,
                                              (l * (N_EXPERT + 1) + N_EXPERT) * bpp)
-        if lib.q4_cuda_experts_tiled_a(arena):
+        self.tiled = bool(lib.q4_cuda_experts_tiled_a(arena))
+        if self.tiled:      # generated in the engine's byte order: convert to the resident format
             assert lib.q4_cuda_experts_retile_a(arena, 0, n_layers * self.slots_l)
         self.d_router = dev.malloc(n_layers * ROUTER_BYTES)
-        assert lib.q4_cuda_synth_normal(self.d_router, n_layers * N_EXPERT * N_EMBD, 2027, 0.0, 0.02)
+        assert lib.q4_cuda_synth_normal(self.d_router, n_layers * N_EXPERT * N_EMBD, seed + 1, 0.0, 0.02)
         self.d_norm = dev.malloc(n_layers * N_EMBD * 4)
-        assert lib.q4_cuda_synth_normal(self.d_norm, n_layers * N_EMBD, 2028, 1.0, 0.1)
-        x_all = pkg.synth.hidden(2029, tokens, N_EMBD)
-        if zipf:
-            # Expert popularity skewed by a Zipf(1.1) bias on the router logits: every
-            # token carries the same value A in coordinate 0 (norm weight 1 there), and
-            # router column 0 holds bias_e / (normalised A), so logit_e = N(0, ~1) + bias_e.
-            A = 4.0
-            x_all[:, 0] = A
-            xn0 = A / np.sqrt((A * A + N_EMBD - 1.0) / N_EMBD)
-            col = (pkg.synth.zipf_bias(N_EXPERT, 1.1) / xn0).astype(np.float32)
-            one = np.ones(1, np.float32)
-            dev.sync()
-            for l in range(n_layers):
-                r = dev.download(self.d_router + l * ROUTER_BYTES, (N_EXPERT, N_EMBD), np.float32)
-                r[:, 0] = col
-                dev.write(self.d_router + l * ROUTER_BYTES, r)
-                dev.write(self.d_norm + l * N_EMBD * 4, one)
+        assert lib.q4_cuda_synth_normal(self.d_norm, n_layers * N_EMBD, seed + 2, 1.0, 0.1)
+        rb = N_EMBD // 256 * IQ3S_BLOCK
+        self.og, self.ou, self.od = 0, N_FF * rb, 2 * N_FF * rb
+        dev.sync()
+
+    def layer_base(self, l):
+        return self.base + l * self.slots_l * self.stride
+
+    def router(self, l):
+        return self.d_router + l * ROUTER_BYTES
+
+    def norm(self, l):
+        return self.d_norm + l * N_EMBD * 4
+
+    def zipf_skew(self, pkg, x_all):
+        """Expert popularity skewed by a Zipf(1.1) bias on the router logits: every token carries
+        the same value A in coordinate 0 (norm weight 1 there), and router column 0 holds
+        bias_e / (normalised A), so logit_e = N(0, ~1) + bias_e."""
+        A = 4.0
+        x_all[:, 0] = A
+        xn0 = A / np.sqrt((A * A + N_EMBD - 1.0) / N_EMBD)
+        col = (pkg.synth.zipf_bias(N_EXPERT, 1.1) / xn0).astype(np.float32)
+        one = np.ones(1, np.float32)
+        self.dev.sync()
+        for l in range(self.n_layers):
+            r = self.dev.download(self.router(l), (N_EXPERT, N_EMBD), np.float32)
+            r[:, 0] = col
+            self.dev.write(self.router(l), r)
+            self.dev.write(self.norm(l), one)
+
+    def host_layers(self, layers):
+        """Copies of some layers' tensors on the host, engine byte order (for the CPU arm)."""
+        assert self.e_count == N_EXPERT
+        out = []
+        for l in layers:
+            packs = np.empty((self.slots_l, PACK), np.uint8)
+            for e in range(self.slots_l):
+                assert self.lib.q4_cuda_experts_get_a(self.arena, l * self.slots_l + e, packs[e].ctypes.data, PACK)
+            out.append({
+                "experts": packs[:N_EXPERT], "shared": packs[N_EXPERT],
+                "router": self.dev.download(self.router(l), (N_EXPERT, N_EMBD), np.float32),
+                "norm_w": self.dev.download(self.norm(l), (N_EMBD,), np.float32)})
+        return out
+
+    def release(self):
+        self.lib.q4_hip_experts_free_a(self.arena)
+        self.dev.free(self.d_router)
+        self.dev.free(self.d_norm)
+
+
+class Decode1:
+    """Config 1 on a Model: one token, one layer per step."""
+
+    def __init__(self, pkg, model):
+        self.pkg, self.m, self.dev, self.lib = pkg, model, model.dev, model.lib
+        lib, dev = self.lib, self.dev
+        self.n_x = 64
+        self.x_host = pkg.synth.hidden(SEED + 3, self.n_x, N_EMBD)
+        self.d_xpool = dev.upload(self.x_host)
+        self.d_y = dev.malloc(N_EMBD * 4)
+        self.h_x = lib.q4_hip_host_alloc_coh(N_EMBD * 4)
+        self.h_y = lib.q4_hip_host_alloc_coh(N_EMBD * 4)
+        self.y_out = np.zeros(N_EMBD, np.float32)
+        self.stack_plans = {}
+        self.plans = None
+
+    def stack_plan(self, first, count):
+        """The persistent kernel over layers first, first + 1, ... (mod the model's layers)."""
+        key = (first, count)
+        if key not in self.stack_plans:
+            m = self.m
+            arr = (StackDesc * count)()
+            for i in range(count):
+                l = (first + i) % m.n_layers
+                arr[i].base, arr[i].norm, arr[i].router = m.layer_base(l), m.norm(l), m.router(l)
+            p = self.lib.q4_cuda_decode_stack_plan(arr, count, m.stride, m.og, m.ou, m.od, N_EXPERT, EPS,
+                                                   N_EXPERT, TOPK, N_EMBD, N_FF)
+            if not p:
+                raise RuntimeError("q4_cuda_decode_stack_plan refused")
+            self.stack_plans[key] = p
+        return self.stack_plans[key]
+
+    def enqueue_steps(self, k, r):
+        """k consecutive layer-steps of one token (repeat number r picks the token and the first
+        layer), as launches of at most 48 layers each; y of a layer is x of the next."""
+        m = self.m
+        first = (r * k) % m.n_layers
+        x = self.d_xpool + (r % self.n_x) * N_EMBD * 4
+        done = 0
+        while done < k:
+            n = min(m.n_layers, k - done)
+            if not self.lib.q4_cuda_decode_stack_dev(self.stack_plan((first + done) % m.n_layers, n), x, self.d_y,
+                                                     None, None):
+                raise RuntimeError("q4_cuda_decode_stack_dev refused")
+            x = self.d_y    # the next launch continues from this one's output (same buffer: read at
+            done += n       # the start of the launch, written at its end)
+
+    def e2e_steps(self, k, r):
+        """k steps through the one-layer host-buffer call: the token's row is written into pinned
+        host memory, the layer runs, the 8 KB result is read on the host -- every step."""
+        lib, m = self.lib, self.m
+        if self.plans is None:
+            self.plans = []
+            for l in range(m.n_layers):
+                p = lib.q4_cuda_decode_plan(m.layer_base(l), m.stride, m.og, m.ou, m.od, N_EXPERT, m.norm(l), EPS,
+                                            m.router(l), N_EXPERT, TOPK, N_EMBD, N_FF)
+                if not p:
+                    raise RuntimeError("q4_cuda_decode_plan refused")
+                self.plans.append(p)
+        run, h_x, h_y = lib.q4_cuda_decode_plan_host, self.h_x, self.h_y
+        for i in range(r * k, r * k + k):
+            ctypes.memmove(h_x, self.x_host[i % self.n_x].ctypes.data, N_EMBD * 4)
+            if not run(self.plans[i % m.n_layers], h_x, h_y):
+                raise RuntimeError("q4_cuda_decode_plan_host refused")
+            ctypes.memmove(self.y_out.ctypes.data, h_y, N_EMBD * 4)
+
+    def e2e_stack(self, r):
+        """One token through all layers in one host-buffer call (row in, row out)."""
+        ctypes.memmove(self.h_x, self.x_host[r % self.n_x].ctypes.data, N_EMBD * 4)
+        if not self.lib.q4_cuda_decode_stack_host(self.stack_plan(0, self.m.n_layers), self.h_x, self.h_y):
+            raise RuntimeError("q4_cuda_decode_stack_host refused")
+        ctypes.memmove(self.y_out.ctypes.data, self.h_y, N_EMBD * 4)
+
+    def release(self):
+        for p in self.stack_plans.values():
+            self.lib.q4_cuda_decode_stack_free(p)
+        for p in self.plans or []:
+            self.lib.q4_cuda_decode_plan_free(p)
+        self.stack_plans, self.plans = {}, None
+        self.lib.q4_hip_host_free_coh(self.h_x)
+        self.lib.q4_hip_host_free_coh(self.h_y)
+
+
+EP_TOKENS = 64          # config 4: batch of 64 tokens ...
+
+
+class BatchJob:
+    """`tokens` tokens through the layers of a Model, y of a layer feeding the next (chain) or
+    every layer on the same input rows; this object is one rank's part (world == 1: the whole
+    job on one GPU through q4_cuda_moe_layer_n)."""
+
+    def __init__(self, pkg, model, ep, rank, world, tokens, layers, chain=True, x_all=None):
+        self.pkg, self.m, self.dev, self.lib = pkg, model, model.dev, model.lib
+        lib, dev = self.lib, self.dev
+        self.ep, self.world, self.layers, self.chain = ep, world, list(layers), chain
+        self.tokens = tokens
+        self.t_local = tokens // world
+        if x_all is None:
+            x_all = pkg.synth.hidden(SEED + 3, tokens, N_EMBD)
         self.x_host = np.ascontiguousarray(x_all[rank * self.t_local:(rank + 1) * self.t_local])
         self.nb = nb = self.t_local * N_EMBD * 4
         self.d_x0, self.d_a, self.d_b = dev.upload(self.x_host), dev.malloc(nb), dev.malloc(nb)
         self.h_x, self.h_y = lib.q4_hip_host_alloc_coh(nb), lib.q4_hip_host_alloc_coh(nb)
         ctypes.memmove(self.h_x, self.x_host.ctypes.data, nb)
-        rb = N_EMBD // 256 * IQ3S_BLOCK
-        self.og, self.ou, self.od = 0, N_FF * rb, 2 * N_FF * rb
         if world == 1:
             self.ws = lib.q4_cuda_moe_layer_n_ws_bytes(self.t_local, TOPK, N_EXPERT, N_EMBD, N_FF)
         else:
             self.ws = ep.q4_cuda_ep_layer_ws_bytes(world, self.t_local, TOPK, N_EXPERT, N_EMBD, N_FF)
         self.d_ws = dev.malloc(self.ws)
-        self.dev = dev
         self.graph = None
+        self.d_out = self.d_a
+        self.one_per_step = False   # a step is ONE layer, the layers taken in turn (no chaining)
+        self.turn = 0
 
-    def layer(self, l, src, dst):
-        lb = self.base + l * self.slots_l * self.stride
-        nw, rt = self.d_norm + l * N_EMBD * 4, self.d_router + l * ROUTER_BYTES
+    def layer(self, l, src, dst, d_ids=None):
+        m = self.m
         if self.world == 1:
-            ok = self.lib.q4_cuda_moe_layer_n(lb, self.stride, self.og, self.ou, self.od, N_EXPERT, src, nw,
-                                              EPS, rt, N_EXPERT, TOPK, N_EMBD, N_FF, self.t_local, dst,
-                                              None, None, self.d_ws, self.ws)
+            ok = self.lib.q4_cuda_moe_layer_n(m.layer_base(l), m.stride, m.og, m.ou, m.od, N_EXPERT, src, m.norm(l),
+                                              EPS, m.router(l), N_EXPERT, TOPK, N_EMBD, N_FF, self.t_local, dst,
+                                              d_ids, None, self.d_ws, self.ws)
         else:
-            ok = self.ep.q4_cuda_ep_layer(lb, self.stride, self.og, self.ou, self.od, 1, src, nw, EPS, rt,
-                                          N_EXPERT, TOPK, N_EMBD, N_FF, self.t_local, dst, self.d_ws, self.ws)
+            ok = self.ep.q4_cuda_ep_layer(m.layer_base(l), m.stride, m.og, m.ou, m.od, 1, src, m.norm(l), EPS,
+                                          m.router(l), N_EXPERT, TOPK, N_EMBD, N_FF, self.t_local, dst, self.d_ws,
+                                          self.ws)
         if not ok:
             raise RuntimeError("layer call refused")
 
-    def enqueue(self):
+    def enqueue(self, layers=None):
+        if self.one_per_step:
+            self.layer(self.layers[self.turn % len(self.layers)], self.d_x0, self.d_a)
+            self.turn += 1
+            self.d_out = self.d_a
+            return
         src = self.d_x0
-        for l in range(self.n_layers):      # the output of a layer is the next layer's input
-            dst = self.d_a if (l % 2 == 0) else self.d_b
+        for i, l in enumerate(layers if layers is not None else self.layers):
+            dst = self.d_a if (i % 2 == 0) else self.d_b
             self.layer(l, src, dst)
-            src = dst
-        self.d_out = src
+            if self.chain:
+                src = dst
+        self.d_out = dst
+
+    def routing_stats(self):
+        """(routed rows incl. shared, distinct experts incl. shared, last layer's histogram),
+        summed over the job's layers, read once from the device."""
+        assert self.world == 1
+        d_ids = self.dev.malloc(self.tokens * TOPK * 4)
+        rows, distinct, src, hist = 0, 0, self.d_x0, None
+        for i, l in enumerate(self.layers):
+            dst = self.d_a if (i % 2 == 0) else self.d_b
+            self.layer(l, src, dst, d_ids)
+            ids = self.dev.download(d_ids, (self.tokens, TOPK), np.int32)
+            rows += ids.size + self.tokens
+            distinct += len(np.unique(ids)) + 1
+            hist = np.bincount(ids.ravel(), minlength=N_EXPERT)
+            if self.chain:
+                src = dst
+        self.dev.free(d_ids)
+        return rows, distinct, hist
 
     def try_capture(self):
-        """One CUDA graph per step (48 layers); falls back to plain launches if the capture
-        is refused (e.g. by the collective library)."""
-        if os.environ.get("Q4B_BENCH_GRAPH", "1") == "0":
-            return False
-        if self.lib.q4_hip_graph_begin() != 1:
+        """One CUDA graph per step; plain launches if the capture is refused (e.g. by the
+        collective library)."""
+        if self.one_per_step or self.lib.q4_hip_graph_begin() != 1:
             return False
         try:
             self.enqueue()
@@ -421,51 +503,285 @@ class EpJob:
         lib.q4_hip_d2h_async(self.h_y, self.d_out, self.nb)
         lib.q4_hip_stream_sync()
 
+    def output(self):
+        return self.dev.download(self.d_out, (self.t_local, N_EMBD), np.float32)
+
     def release(self):
         if self.graph:      # a graph that holds collective nodes must go before the communicator does
             self.lib.q4_hip_graph_free(self.graph)
             self.graph = None
-        self.lib.q4_hip_experts_free_a(self.arena)
-        for p in (self.d_router, self.d_norm, self.d_x0, self.d_a, self.d_b, self.d_ws):
-            self.lib.q4_hip_free(p)
+        for p in (self.d_x0, self.d_a, self.d_b, self.d_ws):
+            self.dev.free(p)
+        self.lib.q4_hip_host_free_coh(self.h_x)
+        self.lib.q4_hip_host_free_coh(self.h_y)
 
 
-def time_job(job, steps, warmup, barrier_max):
-    """(ms resident, ms end to end, launches per step) for `steps` steps, max over ranks."""
+def time_job(job, steps, warmup, barrier_max, min_ms=MIN_TIMED_MS):
+    """(median ms per step resident, median ms per step end to end, launches per step, repeats)
+    for sets of `steps` steps, max over ranks."""
     lib = job.lib
     l0 = lib.q4_cuda_launch_count()
     job.enqueue()
     job.dev.sync()
     launches = lib.q4_cuda_launch_count() - l0
     job.try_capture()
-    for _ in range(warmup):
+    for _ in range(max(warmup, 3)):
         job.step()
     job.dev.sync()
+    # size the run on a first timed set (the same count on every rank)
     barrier_max(0.0)
-    lib.q4_cuda_timer_begin()
+    lib.q4_cuda_timer_mark(0)
     for _ in range(steps):
         job.step()
-    lib.q4_cuda_timer_end()
-    ms = barrier_max(lib.q4_cuda_timer_ms())
+    lib.q4_cuda_timer_mark(1)
+    first = barrier_max(max(lib.q4_cuda_timer_between_ms(0, 1), 1e-3))
+    repeats = int(min(500, max(3, np.ceil(1.3 * min_ms / first))))
+    per = []
+    for r in range(repeats):
+        barrier_max(0.0)
+        lib.q4_cuda_timer_mark(0)
+        for _ in range(steps):
+            job.step()
+        lib.q4_cuda_timer_mark(1)
+        per.append(barrier_max(lib.q4_cuda_timer_between_ms(0, 1)))
+    ms = float(np.median(per)) / steps
     job.dev.sync()
     for _ in range(2):
         job.step_e2e()
-    barrier_max(0.0)
-    lib.q4_cuda_timer_begin()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        job.step_e2e()
-    lib.q4_cuda_timer_end()
-    ms_e2e = barrier_max(max(lib.q4_cuda_timer_ms(), 1e3 * (time.perf_counter() - t0)))
-    return ms, ms_e2e, launches
+    per = []
+    for r in range(max(3, min(repeats, int(np.ceil(min_ms / (ms * steps))) + 1))):
+        barrier_max(0.0)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            job.step_e2e()
+        per.append(barrier_max(1e3 * (time.perf_counter() - t0)))
+    ms_e2e = float(np.median(per)) / steps
+    return ms, ms_e2e, launches, repeats
 
+
+# ------------------------------------------------------------------ CPU arms (the reference's own code)
+
+def ref_lib():
+    from oracle import pyoracle
+    ref = pyoracle.reference()
+    if ref is not None:
+        ncpu = os.cpu_count() or 2
+        os.environ.setdefault("Q4_CPU_THREADS", str(max(1, min(16, ncpu - 1))))
+    return ref
+
+
+def cpu_layers_tokens(ref, layers, x, n_tok, budget_s, chain=True):
+    """Times layer jobs of n_tok tokens each on the reference's CPU path for about budget_s
+    seconds: host-side norm + fp32 router + softmax/top-k per token, expert work on its worker
+    pool (one-token jobs for n_tok == 1, window jobs otherwise).  Returns the baseline dict."""
+    x = np.ascontiguousarray(x[:n_tok])
+    t, _, _ = ref.time_layers_win(layers, TOPK, 2, x, N_EMBD, N_FF, chain, EPS)     # warm-up, pool start
+    per = max(t / 2, 1e-5)
+    steps = int(max(4, min(20000, budget_s / per)))
+    t, t_router, _ = ref.time_layers_win(layers, TOPK, steps, x, N_EMBD, N_FF, chain, EPS)
+    lt = steps * n_tok
+    return {"value": lt / t, "unit": UNIT, "cores": ref.threads(), "kind": "reference", "cpu_model": cpu_model(),
+            "sample": "%d layer jobs of %d token(s) over %d layers of weights (%.1f s): norm, router, top-k on "
+                      "the host, experts on the reference's worker pool (%s)"
+                      % (steps, n_tok, len(layers), t, "q4_cpuex_dispatch2" if n_tok == 1 else
+                         "q4_cpuex_dispatch_win, windows of up to %d tokens" % min(8, 64 // (TOPK + 1))),
+            "ms_per_step": 1e3 * t / lt, "router_ms": 1e3 * t_router / lt,
+            "experts_ms": 1e3 * (t - t_router) / lt, "omp_threads": int(os.environ.get("OMP_NUM_THREADS", "1"))}
+
+
+def cpu_probe_main(a):
+    """Child process of the default run: config 1 on the CPU path with the OpenMP settings the
+    parent put into the environment, host-generated weights; prints one JSON object."""
+    pkg = entry.load_package()
+    ref = ref_lib()
+    if ref is None:
+        print(json.dumps({"unavailable": "compiled reference CPU path (oracle/_ref) not present"}))
+        return
+    layers = [pkg.synth.layer(SEED + 17 * l, N_EXPERT, N_EMBD, N_FF) for l in range(2)]
+    x = pkg.synth.hidden(7, 64, N_EMBD)
+    d = cpu_layers_tokens(ref, layers, x, 1, a.cpu_seconds)
+    print(json.dumps({k: d[k] for k in ("value", "ms_per_step", "router_ms", "experts_ms", "cores", "omp_threads")}))
+
+
+def cpu_probe_passive_omp(seconds):
+    """The same CPU arm with a small passive OpenMP team for the router product (the default
+    arm keeps it on one thread), so that choice is visible in numbers."""
+    env = dict(os.environ, OMP_NUM_THREADS="4", OMP_WAIT_POLICY="passive")
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--cpu-probe", "--cpu-seconds", str(seconds)],
+                           env=env, capture_output=True, text=True, timeout=240)
+        line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1]
+        d = json.loads(line)
+        d["omp_wait_policy"] = "passive"
+        return d
+    except Exception as e:   # the figure is an extra: its absence must not fail the run
+        return {"unavailable": "%s" % e}
+
+
+def cpu_config0(ref, layer, x, budget_s):
+    """Config 0 on the CPU path: one expert, one token per job, distinct experts back to back."""
+    packs = [layer["experts"][e] for e in range(N_EXPERT)]
+    jobs = 256
+    ids = (np.arange(jobs, dtype=np.int32) % N_EXPERT).reshape(jobs, 1)
+    wts = np.ones((jobs, 1), np.float32)
+    t = ref.time_jobs(packs, ids, wts, 1, x, N_EMBD, N_FF)
+    reps = int(max(1, min(200, budget_s / max(t, 1e-4))))
+    ids = np.tile(ids, (reps, 1))
+    wts = np.tile(wts, (reps, 1))
+    t = ref.time_jobs(packs, ids, wts, 1, x, N_EMBD, N_FF)
+    n = jobs * reps
+    return {"value": n / t, "unit": "expert-tok/s", "cores": ref.threads(), "kind": "reference",
+            "cpu_model": cpu_model(), "sample": "%d one-expert jobs over 512 distinct experts (%.1f s), "
+            "q4_cpuex_dispatch2 with k = 1" % (n, t), "ms_per_step": 1e3 * t / n}
+
+
+# ------------------------------------------------------------------ the other configurations on one GPU
+
+def roof_hbm(bytes_per_step, t_step, kernel):
+    hbm, _, src = read_peaks()
+    ach = bytes_per_step / t_step / 1e9
+    return {"bound": "hbm", "achieved": ach, "peak": hbm, "unit": "GB/s", "frac": ach / hbm, "traffic": None,
+            "peak_source": src, "kernel": kernel}
+
+
+def measure_config0(pkg, model, ref_layer=None, cpu_s=0.0):
+    """Config 0: ONE expert's feed-forward for one token per unit, 512 distinct experts back to
+    back (q4_hip_moe_exec_dev with a one-entry list; a CUDA graph of 512 calls per set)."""
+    dev, lib = model.dev, model.lib
+    n = N_EXPERT
+    x = pkg.synth.hidden(SEED + 5, 1, N_EMBD)[0]
+    d_x, d_y, d_h = dev.upload(x), dev.malloc(N_EMBD * 4), dev.malloc(N_FF * 4)
+    d_es = dev.upload(np.arange(n, dtype=np.int32))
+    d_ew = dev.upload(np.ones(n, np.float32))
+    d_one = dev.upload(np.array([1], np.int32))
+    lib.q4_hip_fill(d_y, 0.0, N_EMBD)
+
+    def call(e, layer):
+        if not lib.q4_hip_moe_exec_dev(model.layer_base(layer), model.stride, d_es + 4 * e, d_ew + 4 * e, d_one, 21,
+                                       model.og, 21, model.ou, 21, model.od, d_x, d_h, None, None, d_y, N_FF,
+                                       N_EMBD, N_EMBD):
+            raise RuntimeError("q4_hip_moe_exec_dev refused")
+    graphs = []
+    for layer in range(min(2, model.n_layers)):      # two layers in turn: 1.4 GB between reuses
+        assert lib.q4_hip_graph_begin() == 1
+        for e in range(n):
+            call(e, layer)
+        g = lib.q4_hip_graph_end()
+        if not g:
+            raise RuntimeError("graph capture failed")
+        graphs.append(g)
+    ms, repeats, _, launches = median_step(
+        lib, lambda r: lib.q4_hip_graph_launch(graphs[r % len(graphs)]) or None, n, 2)
+    # end to end: the token's row goes up, one expert runs, the 8 KB result comes back, per unit
+    h_x, h_y = lib.q4_hip_host_alloc_coh(N_EMBD * 4), lib.q4_hip_host_alloc_coh(N_EMBD * 4)
+    ctypes.memmove(h_x, x.ctypes.data, N_EMBD * 4)
+    es = np.arange(n, dtype=np.int32)
+    one = np.ones(1, np.float32)
+
+    def e2e_set(r):
+        for e in range(64):
+            lib.q4_hip_h2d_async(d_x, h_x, N_EMBD * 4)
+            lib.q4_hip_fill(d_y, 0.0, N_EMBD)
+            if not lib.q4_hip_moe_exec(model.layer_base(r % 2), model.stride, es[e:].ctypes.data, one.ctypes.data, 1,
+                                       21, model.og, 21, model.ou, 21, model.od, d_x, d_h, None, None, d_y, N_FF,
+                                       N_EMBD, N_EMBD):
+                raise RuntimeError("q4_hip_moe_exec refused")
+            lib.q4_hip_d2h_async(h_y, d_y, N_EMBD * 4)
+            lib.q4_hip_stream_sync()
+    ms_e2e, _ = median_wall(e2e_set, 64, 1)
+    for g in graphs:
+        lib.q4_hip_graph_free(g)
+    for p in (d_x, d_y, d_h, d_es, d_ew, d_one):
+        dev.free(p)
+    lib.q4_hip_host_free_coh(h_x)
+    lib.q4_hip_host_free_coh(h_y)
+    entry_ = {"workload": "config0: one IQ3_S expert feed-forward (gate, up, SwiGLU, down), one token per unit, "
+                          "512 distinct experts back to back",
+              "value": 1e3 / ms, "unit": "expert-tok/s", "ms_per_step": ms, "repeats": repeats,
+              "gpu_launches_per_unit": launches / (repeats * n),
+              "e2e": {"value": 1e3 / ms_e2e, "unit": "expert-tok/s", "h2d_bytes_per_step": N_EMBD * 4,
+                      "d2h_bytes_per_step": N_EMBD * 4},
+              "roofline": roof_hbm(PACK, ms * 1e-3, "whole unit (launch chain)"), "cpu_baseline": None}
+    if ref_layer is not None and cpu_s > 0:
+        ref = ref_lib()
+        if ref is not None:
+            entry_["cpu_baseline"] = cpu_config0(ref, ref_layer, pkg.synth.hidden(7, 64, N_EMBD), cpu_s)
+    return entry_
+
+
+def measure_batch(pkg, model, kind, steps, warmup, cpu_layers=None, cpu_s=0.0):
+    """verify  (config 2): 4 tokens (1 + 3 drafts) through 48 layers per step, y of a layer feeding the next.
+    prefill (config 3): 2048 tokens through one layer per step, expert popularity skewed by Zipf(1.1);
+                        consecutive steps alternate between two layers of weights.
+    ep1     (config 4 on one GPU): 64 tokens through 48 layers per step."""
+    if kind == "verify":
+        tokens, layers, name = 4, range(model.n_layers), \
+            "config2: speculative-verify decode, 4 tokens x %d MoE layers per step" % model.n_layers
+    elif kind == "ep1":
+        tokens, layers, name = EP_TOKENS, range(model.n_layers), config4(1, model.n_layers)["workload"]
+    else:
+        tokens, layers, name = 2048, range(model.n_layers), None
+    x_all = pkg.synth.hidden(SEED + 3, tokens, N_EMBD)
+    if kind == "prefill":
+        model.zipf_skew(pkg, x_all)
+    job = BatchJob(pkg, model, None, 0, 1, tokens, layers, chain=(kind != "prefill"), x_all=x_all)
+    rows, distinct, hist = job.routing_stats()
+    n_l = len(job.layers)
+    if kind == "prefill":
+        job.one_per_step = True
+        name = ("config3: prefill chunk, 2048 tokens x 1 MoE layer per step, Zipf(1.1) expert skew "
+                "(rows per expert max %d, median %d)" % (int(hist.max()), int(np.median(hist))))
+    layers_per_step = 1 if kind == "prefill" else n_l
+    ms, ms_e2e, launches, repeats = time_job(job, steps, warmup, lambda v: v)
+    err = job.lib.q4_cuda_device_error()
+    if err:
+        raise SystemExit("device error word %#x" % err)
+    units = tokens * layers_per_step
+    rows_step = rows / n_l * layers_per_step
+    distinct_step = distinct / n_l * layers_per_step
+    t = ms * 1e-3
+    hbm, tc_peak, src = read_peaks()
+    bytes_step = distinct_step * PACK + layers_per_step * ROUTER_BYTES
+    if kind == "prefill":
+        # the grouped product runs as 16-bit floating-point MMAs (the scales ride in the operands):
+        # the denominator is the measured dense bf16 rate; the numerator counts each weight x
+        # activation product once, although the kernel spends two MMAs on it (a two-term expansion)
+        ops_step = rows_step * 3 * N_EMBD * N_FF * 2.0
+        roof = {"bound": "tensor", "achieved": ops_step / t / 1e12, "peak": tc_peak, "unit": "TFLOP/s",
+                "frac": ops_step / t / 1e12 / tc_peak, "traffic": None, "peak_source": src + " bf16 burst",
+                "hbm_GBps": bytes_step / t / 1e9, "hbm_frac": bytes_step / t / 1e9 / hbm,
+                "kernel": "whole step (%d launches)" % launches}
+    else:
+        roof = roof_hbm(bytes_step, t, "whole step (%d launches)" % launches)
+    out = {"workload": name, "value": units / t, "unit": UNIT, "ms_per_step": ms, "steps": steps,
+           "repeats": repeats, "tokens_per_step": tokens, "layers_per_step": layers_per_step,
+           "routed_rows_per_step": rows_step, "distinct_experts_per_step": distinct_step,
+           "cuda_graph": bool(job.graph), "gpu_launches_per_step": launches,
+           "e2e": {"value": units / (ms_e2e * 1e-3), "unit": UNIT, "h2d_bytes_per_step": job.nb,
+                   "d2h_bytes_per_step": job.nb},
+           "roofline": roof, "cpu_baseline": None}
+    if kind == "prefill" and cpu_s > 0:     # the skewed routers
+        cpu_layers = model.host_layers(range(min(2, model.n_layers)))
+    if cpu_layers is not None and cpu_s > 0:
+        ref = ref_lib()
+        if ref is not None:
+            n_tok = min(tokens, 64 if kind != "prefill" else 160)
+            cb = cpu_layers_tokens(ref, cpu_layers, x_all, n_tok, cpu_s, chain=(kind != "prefill"))
+            if n_tok != tokens:
+                cb["sample"] += "; %d of the step's %d tokens" % (n_tok, tokens)
+            out["cpu_baseline"] = cb
+    job.release()
+    return out
+
+
+# ------------------------------------------------------------------ config 4 on N GPUs
 
 def ep_roofline(world, n_layers, t_step):
     """HBM roofline of the expert-parallel job over all ranks: every rank reads the router of
     each layer and the packs of the distinct experts routed to it plus its copy of the shared
     expert.  The number of distinct routed experts per layer is the expectation for uniform
     routing, E * (1 - (1 - k/E)^T) = 367 of 512 at 64 tokens, not a count of this run."""
-    hbm, src = read_peaks()
+    hbm, _, src = read_peaks()
     distinct = N_EXPERT * (1.0 - (1.0 - TOPK / N_EXPERT) ** EP_TOKENS)
     per_layer = world * (ROUTER_BYTES + PACK) + distinct * PACK
     achieved = per_layer * n_layers / t_step / 1e9
@@ -478,8 +794,8 @@ def run_ep(a, pkg, rank, world, local, warmup):
     """Config 4: expert-parallel decode, 64 tokens x 48 layers, experts sharded evenly,
     router and shared expert replicated, dispatch/combine over NCCL.  Strong scaling: the
     job (64 x 48 layer-tokens per step) is the same at every N.  Rank 0 afterwards runs the
-    same job alone on its GPU so the line carries its own 1-GPU reference."""
-    import ctypes
+    same job alone on its GPU: the line carries its own 1-GPU reference, the speed-up against
+    it, and the difference between the two results for the tokens rank 0 owns."""
     dev = pkg.Device()
     lib = dev.lib
     ep = None
@@ -500,46 +816,73 @@ def run_ep(a, pkg, rank, world, local, warmup):
         assert ep.q4_cuda_ep_allreduce_max(ctypes.byref(f))
         return f.value
 
-    n_layers = a.layers if a.layers else EP_LAYERS
-    job = EpJob(pkg, dev, ep, 0, rank, world, n_layers)
+    n_layers = a.layers if a.layers else N_LAYERS
+    e_local = N_EXPERT // world
+    model = Model(dev, n_layers, 0, rank * e_local, e_local)
+    job = BatchJob(pkg, model, ep, rank, world, EP_TOKENS, range(n_layers))
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    ms, ms_e2e, launches = time_job(job, a.steps, warmup, barrier_max)
+    ms, ms_e2e, launches, repeats = time_job(job, a.steps, warmup, barrier_max)
     clocks = sampler.stop() if rank == 0 else None
     graphed = bool(job.graph)
     err = lib.q4_cuda_device_error()
     if err:
         raise SystemExit("device error word %#x" % err)
-    single = None
+    floor_us = None
+    if ep is not None and hasattr(ep, "q4_cuda_ep_exchange_floor_us"):
+        f = ctypes.c_float(0.0)
+        if ep.q4_cuda_ep_exchange_floor_us(job.t_local, N_EMBD, TOPK, job.d_ws, job.ws, ctypes.byref(f)):
+            floor_us = barrier_max(f.value)
+    # results for the comparison with one GPU: the first layer alone (every rank takes part in its
+    # exchanges), and the whole stack
+    job.enqueue(layers=[0])
+    dev.sync()
+    y_ep_l0 = job.output() if rank == 0 else None
+    job.step()
+    dev.sync()
+    y_ep = job.output() if rank == 0 else None
+    details = {"cuda_graph": graphed, "repeats": repeats, "exchange_floor_us": floor_us}
     if world > 1 and rank == 0 and not a.no_cpu:
         job.release()
-        solo = EpJob(pkg, dev, None, 0, 0, 1, n_layers)
-        s_ms, s_e2e, _ = time_job(solo, a.steps, warmup, lambda v: v)
-        single = {"value": EP_TOKENS * n_layers * a.steps / (s_ms * 1e-3),
-                  "e2e": EP_TOKENS * n_layers * a.steps / (s_e2e * 1e-3), "unit": UNIT,
-                  "ms_per_step": s_ms / a.steps}
+        model.release()
+        m1 = Model(dev, n_layers, 0)
+        solo = BatchJob(pkg, m1, None, 0, 1, EP_TOKENS, range(n_layers))
+        s_ms, s_e2e, _, _ = time_job(solo, a.steps, warmup, lambda v: v)
+
+        def rel(got, want):
+            return float(np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30))
+        solo.enqueue(layers=[0])
+        dev.sync()
+        rel_l0 = rel(y_ep_l0, solo.output()[:job.t_local])
+        solo.step()
+        dev.sync()
+        rel_all = rel(y_ep, solo.output()[:job.t_local])
+        units1 = EP_TOKENS * n_layers
+        details["one_gpu_same_job"] = {"value": units1 / (s_ms * 1e-3), "e2e": units1 / (s_e2e * 1e-3),
+                                       "unit": UNIT, "ms_per_step": s_ms}
+        details["speedup_vs_one_gpu"] = s_ms / ms
+        # One layer from the same input rows: the two runs differ in the order of one fp32 sum per
+        # output value.  This bound fails the run.  After a stack of layers the difference is
+        # reported only: every layer's 8-bit quantiser turns a last-bit difference of its input
+        # into a rounding flip now and then.
+        details["parity_vs_one_gpu_rel_l2"] = rel_l0
+        details["parity_vs_one_gpu_rel_l2_after_%d_layers" % n_layers] = rel_all
+        if not rel_l0 <= 1e-5:
+            raise SystemExit("expert-parallel result differs from the one-GPU result: rel-L2 %g" % rel_l0)
     barrier_max(0.0)
     if rank == 0:
         units = EP_TOKENS * n_layers
-        peak, peak_src = read_peaks()
-        # weight bytes a step must read on the busiest rank: all routers + the experts picked
         print(json.dumps({
-            "metric": METRIC, "value": units * a.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
-            "steps": a.steps, "warmup": warmup, "ms_per_step": ms / a.steps, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "int8 x IQ3_S, fp32 accumulate",
-            "data": "synthetic",
-            "config": {"workload": "config4: expert-parallel decode, 64 tokens x %d MoE layers per step, 512 "
-                                   "experts top-10 + shared, experts sharded %d-way, NCCL dispatch/combine"
-                                   % (n_layers, world),
-                       "l2": "inputs larger than L2: a step reads %d layers of weights" % n_layers,
-                       "tokens_per_rank": job.t_local, "experts_per_rank": job.e_local,
-                       "cuda_graph": graphed, "one_gpu_same_job": single},
-            "clocks": clocks,
-            "e2e": {"value": units * a.steps / (ms_e2e * 1e-3), "unit": UNIT,
+            "metric": METRIC, "value": units / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": a.steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": DTYPE, "data": "synthetic",
+            "config": config4(world, n_layers), "details": details, "clocks": clocks,
+            "e2e": {"value": units / (ms_e2e * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": job.nb, "d2h_bytes_per_step": job.nb},
-            "gpu_launches": int(launches * a.steps * 2),
-            "roofline": ep_roofline(world, n_layers, ms * 1e-3 / a.steps), "cpu_baseline": None}))
+            "gpu_launches": int(launches * a.steps * repeats),
+            "roofline": ep_roofline(world, n_layers, ms * 1e-3), "cpu_baseline": None}))
+        sys.stdout.flush()
     if ep:
         barrier_max(0.0)
         if job.graph:
@@ -551,240 +894,173 @@ def run_ep(a, pkg, rank, world, local, warmup):
         t.join(10.0)
         sys.stdout.flush()
         sys.stderr.flush()
-        os._exit(0)
+        try:
+            atexit._run_exitfuncs()     # whatever the interpreter or its host registered for exit
+        finally:
+            os._exit(0)
 
 
-def run_batch(a, pkg, local, warmup, kind):
-    """One GPU, many tokens per step through q4_cuda_moe_layer_n.
-    verify  (config 2): 4 tokens (1 + 3 drafts) through 48 layers, y of a layer feeding the next.
-    prefill (config 3): 2048 tokens through one layer, expert popularity skewed by Zipf(1.1);
-                        consecutive steps alternate between two layers of weights."""
+# ------------------------------------------------------------------ the reference arm and main
+
+def run_reference(a, pkg, rank, world, warmup):
+    """The reference's own CPU implementation of the path on this host's cores (oracle/_ref: its
+    q4_cpuexp.c / q4_quant.c compiled unmodified), on the configuration the GPU arm runs at this
+    N: config 1 at N = 1, config 4 (64 tokens through the layers, window jobs) at N >= 2.  Each
+    step is a bounded sample of the workload.  Rank 0 alone runs it."""
+    if rank != 0:
+        return
+    ref = ref_lib()
+    if ref is None:
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "compiled reference CPU path (oracle/_ref) not present"}))
+        return
+    layers = [pkg.synth.layer(SEED + 17 * l, N_EXPERT, N_EMBD, N_FF) for l in range(2)]
+    steps = min(a.steps, 200)
+    if world == 1:
+        config, n_tok, jobs, scaling = CONFIG1, 1, 64, "weak"
+        what = "%d layer-tokens per step (one-token jobs) over 2 layers of weights" % jobs
+    else:
+        config, n_tok, jobs, scaling = config4(world, a.layers or N_LAYERS), EP_TOKENS, 4, "strong"
+        what = "%d layers of the step's %d per step, all 64 tokens, over 2 layers of weights" % (
+            jobs, a.layers or N_LAYERS)
+    x = pkg.synth.hidden(7, 64, N_EMBD)[:n_tok]
+    ref.time_layers_win(layers, TOPK, 2, x, N_EMBD, N_FF, True, EPS)
+    for _ in range(min(warmup, 3)):
+        ref.time_layers_win(layers, TOPK, jobs, x, N_EMBD, N_FF, True, EPS)
+    t, t_router = 0.0, 0.0
+    for _ in range(steps):
+        dt, dr, _ = ref.time_layers_win(layers, TOPK, jobs, x, N_EMBD, N_FF, True, EPS)
+        t += dt
+        t_router += dr
+    lt = steps * jobs * n_tok
+    val = lt / t
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": a.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": 1e3 * t / steps, "higher_is_better": True, "scaling": scaling,
+        "vs_baseline": None, "dtype": DTYPE, "data": "synthetic", "config": config,
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": ref.threads(), "kind": "reference",
+                         "cpu_model": cpu_model(), "sample": "%d steps x %s" % (steps, what),
+                         "router_ms": 1e3 * t_router / lt, "experts_ms": 1e3 * (t - t_router) / lt,
+                         "omp_threads": int(os.environ.get("OMP_NUM_THREADS", "1"))},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+def dist_setup():
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")),
+            int(os.environ.get("LOCAL_RANK", "0")))
+
+
+def run_config1(a, pkg, local, warmup):
     dev = pkg.Device()
     lib = dev.lib
-    if kind == "verify":
-        tokens, n_layers, zipf = 4, (a.layers or 48), False
-    else:
-        tokens, n_layers, zipf = 2048, 2, True
-    job = EpJob(pkg, dev, None, 0, 0, 1, n_layers, tokens=tokens, zipf=zipf)
-    if kind == "prefill":
-        # one layer per step: step i runs layer i % 2 on the same input rows
-        job.enqueue_all = job.enqueue
-        state = {"i": 0}
-
-        def one_layer():
-            job.layer(state["i"] % n_layers, job.d_x0, job.d_a)
-            state["i"] += 1
-            job.d_out = job.d_a
-        job.enqueue = one_layer
-        job.try_capture = lambda: False
-    # routed rows and distinct experts of the job (for the algorithmic figures), read once
-    d_ids = dev.malloc(tokens * TOPK * 4)
-    rows_total, distinct_total = 0, 0
-    src = job.d_x0
-    for l in range(n_layers):
-        dst = job.d_a if (l % 2 == 0) else job.d_b
-        lb = job.base + l * job.slots_l * job.stride
-        assert lib.q4_cuda_moe_layer_n(lb, job.stride, job.og, job.ou, job.od, N_EXPERT, src,
-                                       job.d_norm + l * N_EMBD * 4, EPS, job.d_router + l * ROUTER_BYTES,
-                                       N_EXPERT, TOPK, N_EMBD, N_FF, tokens, dst, d_ids, None, job.d_ws,
-                                       job.ws)
-        ids = dev.download(d_ids, (tokens, TOPK), np.int32)
-        rows_total += ids.size + tokens
-        distinct_total += len(np.unique(ids)) + 1
-        if kind == "verify":
-            src = dst
-    hist = np.bincount(ids.ravel(), minlength=N_EXPERT)
+    model = Model(dev, a.layers)
+    d1 = Decode1(pkg, model)
+    k = a.steps
     sampler = ClockSampler(local)
     sampler.start()
-    ms, ms_e2e, launches = time_job(job, a.steps, warmup, lambda v: v)
+    # --- device-resident: K consecutive layer-steps per set, sets repeated to >= 50 ms ---
+    ms, repeats, timed_ms, launches = median_step(lib, lambda r: d1.enqueue_steps(k, r), k,
+                                                  max(1, (warmup + k - 1) // k))
+    # --- end to end through the one-layer host-buffer call, every step ---
+    ke = min(k, 256)
+    ms_e2e, rep_e2e = median_wall(lambda r: d1.e2e_steps(ke, r), ke, max(1, (min(warmup, 50) + ke - 1) // ke))
+    ms_e2e_stack, _ = median_wall(d1.e2e_stack, model.n_layers, 2)
     clocks = sampler.stop()
     err = lib.q4_cuda_device_error()
     if err:
         raise SystemExit("device error word %#x" % err)
-    layers_per_step = n_layers if kind == "verify" else 1
-    units = tokens * layers_per_step
-    rows_step = rows_total / n_layers * layers_per_step
-    distinct_step = distinct_total / n_layers * layers_per_step
-    t = ms * 1e-3 / a.steps
-    hbm, src_name = read_peaks()
-    bytes_step = distinct_step * PACK + layers_per_step * ROUTER_BYTES
-    ops_step = rows_step * 3 * N_EMBD * N_FF * 2.0
-    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(
-        os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
-    # the grouped product runs as 16-bit floating-point MMAs (the scales ride in the operands):
-    # the denominator is the measured dense bf16 rate; the numerator counts each weight x
-    # activation product once, although the kernel spends two MMAs on it (a two-term expansion)
-    tc_peak = float(peaks.get("bf16_tflops", 1590.0))
-    if kind == "prefill":
-        roof = {"bound": "tensor", "achieved": ops_step / t / 1e12, "peak": tc_peak, "unit": "TFLOP/s",
-                "frac": ops_step / t / 1e12 / tc_peak, "traffic": None,
-                "peak_source": "measured bf16 burst" if peaks else "fallback bf16",
-                "hbm_GBps": bytes_step / t / 1e9, "hbm_frac": bytes_step / t / 1e9 / hbm,
-                "kernel": "whole step (%d launches)" % launches}
-    else:
-        roof = {"bound": "hbm", "achieved": bytes_step / t / 1e9, "peak": hbm, "unit": "GB/s",
-                "frac": bytes_step / t / 1e9 / hbm, "traffic": None, "peak_source": src_name,
-                "kernel": "whole step (%d launches)" % launches}
-    name = ("config2: speculative-verify decode, 4 tokens x %d MoE layers per step" % n_layers
-            if kind == "verify" else
-            "config3: prefill chunk, 2048 tokens x 1 MoE layer per step, Zipf(1.1) expert skew "
-            "(rows per expert max %d, median %d)" % (int(hist.max()), int(np.median(hist))))
-    print(json.dumps({
-        "metric": METRIC, "value": units / t, "unit": UNIT, "n_gpus": 1, "steps": a.steps, "warmup": warmup,
-        "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8 x IQ3_S, fp32 accumulate", "data": "synthetic",
-        "config": {"workload": name, "l2": "inputs larger than L2: a step reads %.0f MB of weights"
-                                          % (bytes_step / 1e6),
-                   "routed_rows_per_step": rows_step, "distinct_experts_per_step": distinct_step,
-                   "cuda_graph": bool(job.graph)},
-        "clocks": clocks,
-        "e2e": {"value": units * a.steps / (ms_e2e * 1e-3), "unit": UNIT,
-                "h2d_bytes_per_step": job.nb, "d2h_bytes_per_step": job.nb},
-        "gpu_launches": int(launches * a.steps * 2),
-        "roofline": roof, "cpu_baseline": None}))
-
-
-def dist_setup(n_gpus):
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    return rank, world, local
+    hbm, _, peak_src = read_peaks()
+    achieved = STEP_BYTES / (ms * 1e-3) / 1e9
+    tr = read_traffic("decode_stack_kernel.json")
+    cpu_layers, cpu, details = None, None, {}
+    if not a.no_cpu:
+        cpu_layers = model.host_layers(range(min(2, model.n_layers)))
+        ref = ref_lib()
+        if ref is not None:
+            cpu = cpu_layers_tokens(ref, cpu_layers, d1.x_host, 1, a.cpu_seconds)
+            cpu["jobs_router_on_a_passive_openmp_team"] = cpu_probe_passive_omp(min(a.cpu_seconds, 5.0))
+    details["repeats"] = repeats
+    details["timed_ms"] = timed_ms
+    details["steps_per_launch"] = min(k, model.n_layers)
+    details["e2e_repeats"] = rep_e2e
+    details["e2e_stack"] = {"value": 1e3 / ms_e2e_stack, "unit": UNIT,
+                            "what": "one host-buffer call per token through all %d layers (8 KB in, 8 KB out per "
+                                    "call)" % model.n_layers}
+    d1.release()
+    if not a.no_others:
+        cs = 0.0 if a.no_cpu else min(a.cpu_seconds, 4.0)
+        others = [measure_config0(pkg, model, cpu_layers[0] if cpu_layers else None, cs),
+                  measure_batch(pkg, model, "verify", 5, 3, cpu_layers, cs),
+                  measure_batch(pkg, model, "ep1", 3, 3, cpu_layers, cs)]
+        model.release()
+        m2 = Model(dev, 2)
+        others.insert(2, measure_batch(pkg, m2, "prefill", 10, 3, None, cs))
+        m2.release()
+        details["other_workloads"] = others
+    line = {
+        "metric": METRIC, "value": 1e3 / ms, "unit": UNIT, "n_gpus": 1, "steps": k, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": DTYPE, "data": "synthetic", "config": dict(CONFIG1, layers_rotated=a.layers),
+        "details": details, "clocks": clocks,
+        "e2e": {"value": 1e3 / ms_e2e, "unit": UNIT, "h2d_bytes_per_step": N_EMBD * 4,
+                "d2h_bytes_per_step": N_EMBD * 4},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,
+                     "traffic": tr.get("dram_bytes_per_layer_token") if tr else None,
+                     "traffic_source": tr.get("source") if tr else None, "peak_source": peak_src,
+                     "kernel": "moe_decode_stack_k, one launch per %d steps" % min(k, model.n_layers)},
+        "cpu_baseline": cpu,
+    }
+    print(json.dumps(line))
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=480)
+    ap.add_argument("--warmup", type=int, default=48)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=48)
+    ap.add_argument("--layers", type=int, default=N_LAYERS)
     ap.add_argument("--cpu-seconds", type=float, default=10.0)
-    ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--workload", default="auto", choices=["auto", "ep", "verify", "prefill"],
-                    help="ep: the 64-token x 48-layer expert-parallel job (config 4) even on one GPU; "
-                         "verify: 4 tokens x 48 layers (config 2); prefill: 2048 tokens x 1 layer (config 3)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU legs (and the one-GPU rerun at N >= 2)")
+    ap.add_argument("--no-others", action="store_true", help="config 1 only: skip details.other_workloads")
+    ap.add_argument("--workload", default="auto", choices=["auto", "config0", "verify", "prefill", "ep"],
+                    help="one of the other configurations alone on one GPU (its entry is printed)")
+    ap.add_argument("--cpu-probe", action="store_true", help=argparse.SUPPRESS)
     a = ap.parse_args()
-    rank, world, local = dist_setup(a.gpus)
+    rank, world, local = dist_setup()
     warmup = max(a.warmup, 3)
     if world > 1:       # one process per GPU: each sees only its own device
         os.environ["CUDA_VISIBLE_DEVICES"] = str(local)
-
+    if a.cpu_probe:
+        entry.build()
+        cpu_probe_main(a)
+        return
     entry.build()
     pkg = entry.load_package()
-    config = {"workload": "config1: one MoE layer, decode batch 1, hidden 2048, ff 512, "
-                          "512 experts top-10 + shared, IQ3_S x q8",
-              "layers_rotated": a.layers, "l2": "inputs larger than L2: every step reads a "
-              "different layer (router+shared weights of all layers exceed L2)",
-              "algorithmic_bytes_per_step": STEP_BYTES}
-
     if a.impl == "reference":
-        if rank != 0:
-            return
-        layers = host_synth_layers(pkg, 2)
-        x = pkg.synth.hidden(7, 64, N_EMBD)
-        # K steps, each a bounded sample of the workload
-        from oracle import pyoracle
-        ref = pyoracle.reference()
-        if ref is None:
-            print(json.dumps({"impl": "reference", "unavailable":
-                              "compiled reference CPU path (oracle/_ref) not present"}))
-            return
-        ncpu = os.cpu_count() or 2
-        os.environ.setdefault("Q4_CPU_THREADS", str(max(1, min(16, ncpu - 1))))
-        per_step = 64
-        ref.time_layers(layers, TOPK, 8, x, N_EMBD, N_FF, EPS)
-        steps = min(a.steps, 200)
-        for _ in range(min(warmup, 3)):
-            ref.time_layers(layers, TOPK, per_step, x, N_EMBD, N_FF, EPS)
-        t = 0.0
-        for _ in range(steps):
-            dt, _, _ = ref.time_layers(layers, TOPK, per_step, x, N_EMBD, N_FF, EPS)
-            t += dt
-        val = steps * per_step / t
-        line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT,
-                "n_gpus": a.gpus, "steps": steps, "warmup": warmup,
-                "ms_per_step": 1e3 * t / steps, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": "int8 x IQ3_S, fp32 accumulate", "data": "synthetic",
-                "config": dict(config, sample="%d layer-tokens per step over 2 layers" % per_step),
-                "cpu_baseline": {"value": val, "unit": UNIT, "cores": ref.threads(),
-                                 "kind": "reference", "cpu_model": cpu_model(),
-                                 "sample": "%d steps x %d layer-tokens" % (steps, per_step)},
-                "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-        print(json.dumps(line))
+        run_reference(a, pkg, rank, world, warmup)
         return
-
-    if world == 1 and a.workload in ("verify", "prefill"):
-        if a.steps == 2000 and a.warmup == 200:
-            a.steps, warmup = 20, 3
-        if a.layers == 48 and a.workload == "prefill":
-            a.layers = 2
-        run_batch(a, pkg, local, warmup, a.workload)
-        return
-    if world > 1 or a.workload == "ep":
-        if a.steps == 2000 and a.warmup == 200:     # the single-layer defaults are too long here
-            a.steps, warmup = 20, 3
+    if world > 1:
         run_ep(a, pkg, rank, world, local, warmup)
         return
-
-    wl = Workload(pkg, a.layers)
-    lib = wl.lib
-    launches0 = lib.q4_cuda_launch_count()
-    # graphs of one pass over the layers each, plus one shorter graph for the remainder, so
-    # that exactly `steps` steps are timed whatever the step count
-    g_steps = min(a.layers, a.steps)
-    wl.capture(g_steps)
-    launches_per_step = (lib.q4_cuda_launch_count() - launches0) / (len(wl.graphs) * g_steps)
-    n_graphs = a.steps // g_steps
-    wl.capture_tail(a.steps % g_steps)
-    wl.run_resident((warmup + g_steps - 1) // g_steps)
-    wl.dev.sync()
-
-    sampler = ClockSampler(local)
-    sampler.start()
-    # --- device-resident throughput ---
-    wl.dev.sync()
-    lib.q4_cuda_timer_begin()
-    wl.run_resident(n_graphs, tail=True)
-    lib.q4_cuda_timer_end()
-    ms = lib.q4_cuda_timer_ms()
-    wl.dev.sync()
-    # --- end to end through the C ABI with host buffers ---
-    wl.run_e2e(min(warmup, 50))
-    lib.q4_cuda_timer_begin()
-    t0 = time.perf_counter()
-    wl.run_e2e(a.steps, first=warmup)
-    lib.q4_cuda_timer_end()
-    ms_e2e_dev = lib.q4_cuda_timer_ms()
-    ms_e2e = max(ms_e2e_dev, 1e3 * (time.perf_counter() - t0))
-    clocks = sampler.stop()
-    err = lib.q4_cuda_device_error()
-    if err:
-        raise SystemExit("device error word %#x" % err)
-
-    peak, peak_src = read_peaks()
-    per_launch_s = ms * 1e-3 / a.steps
-    achieved = STEP_BYTES / per_launch_s / 1e9
-    cpu = None
-    if not a.no_cpu:
-        cpu = cpu_arm(pkg, wl.host_layers(2), wl.x_host, a.cpu_seconds)
-    line = {
-        "metric": METRIC, "value": a.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": 1,
-        "steps": a.steps, "warmup": warmup, "ms_per_step": ms / a.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8 x IQ3_S, fp32 accumulate", "data": "synthetic", "config": config,
-        "clocks": clocks,
-        "e2e": {"value": a.steps / (ms_e2e * 1e-3), "unit": UNIT,
-                "h2d_bytes_per_step": N_EMBD * 4, "d2h_bytes_per_step": N_EMBD * 4},
-        "gpu_launches": int(round(launches_per_step * a.steps * 2)),
-        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                     "frac": achieved / peak, "traffic": FUSED_DRAM_BYTES_PER_LAUNCH,
-                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one launch "
-                                       "(profiles/decode1_fused_kernel.md)",
-                     "peak_source": peak_src,
-                     "kernel": "whole step (%g launches/step)" % launches_per_step},
-        "cpu_baseline": cpu,
-    }
-    print(json.dumps(line))
+    if a.workload != "auto":
+        dev = pkg.Device()
+        cs = 0.0 if a.no_cpu else min(a.cpu_seconds, 4.0)
+        if a.workload == "prefill":
+            model = Model(dev, 2)
+            out = measure_batch(pkg, model, "prefill", min(a.steps, 20), warmup, None, cs)
+        else:
+            model = Model(dev, a.layers)
+            cl = model.host_layers(range(min(2, a.layers))) if cs else None
+            if a.workload == "config0":
+                out = measure_config0(pkg, model, cl[0] if cl else None, cs)
+            else:
+                out = measure_batch(pkg, model, "verify" if a.workload == "verify" else "ep1", min(a.steps, 20),
+                                    warmup, cl, cs)
+        print(json.dumps(out))
+        return
+    run_config1(a, pkg, local, warmup)
 
 
 if __name__ == "__main__":
