@@ -418,9 +418,11 @@ bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64_t og, uint
  * quantised activations live in a fixed array inside the library image (about 40 KB per
  * GPU, held until the process exits) instead of allocated buffers, hence the limits:
  * n <= 16 experts, in_dim <= 4096, n_ff <= 2048 (larger sizes are refused with a message
- * on stderr).  q4_hip_init() is not required.  The first call on each device looks up
- * the array's device address and fills the codebook constant; make that first call
- * before any stream capture begins.  All calls share the one array, which keeps the
+ * on stderr; every argument check comes before the first launch, so false from a check means
+ * nothing was enqueued -- false can also report a launch error of the runtime itself after
+ * part of the sequence went out).  q4_hip_init() is not required.  The first call on each
+ * device looks up the array's device address, fills the codebook constant and waits for
+ * that copy; make that first call before any stream capture begins.  All calls share the one array, which keeps the
  * previous call's contents (nothing in it needs clearing: a call overwrites all it
  * reads); calls that overlap on the GPU race, so serialise them. */
 bool q4_cuda_moe_exec_noalloc(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
@@ -432,11 +434,12 @@ bool q4_cuda_moe_exec_noalloc(const uint8_t *base, uint64_t stride, const int32_
  * each pack, in place and at the same size, into the library's tiled form of
  * IQ3_S (every run of eight 110-byte super-blocks regrouped by field so that all
  * device loads are aligned); base/stride/offset addressing is unchanged and every
- * entry point recognises pointers into a tiled arena.  Slot sizes must then be a
- * multiple of 880 bytes (an arena whose slot size is not stays in the engine's
- * byte order).  No reference counterpart.
- *   set_tiled_default(0/1): format of arenas allocated afterwards (also: env
- *     Q4B_TILED=0);
+ * entry point recognises pointers into a tiled arena.  Only arenas whose slot size is
+ * that of an all-IQ3_S pack (a multiple of 84480 bytes = 330 * 256) are tiled; any other
+ * slot size stays in the engine's byte order.  No reference counterpart.
+ *   set_tiled_default(0/1/2): format of arenas allocated afterwards (also: env
+ *     Q4B_TILED=0); 2 = the caller vouches that the slots hold IQ3_S bytes only, and
+ *     any slot size that is a multiple of the 880-byte tile is tiled (single matrices);
  *   tiled_a: 1 if the arena is tiled;
  *   retile_a: convert slots that were filled on the device in engine byte order
  *     (e.g. by q4_cuda_synth_iq3s);

@@ -701,6 +701,12 @@ bool shape_ok(uint32_t gt, uint32_t ut, uint32_t dt, uint32_t in_dim, uint32_t n
 bool place_ok(uint32_t gt, uint32_t dt, const void *base) {
     return (gt == Q4_T_IQ3_S && dt == Q4_T_IQ3_S) || !q4b_ptr_tiled(base);
 }
+// In a tiled arena a matrix must start on a tile: the kernels address whole 880-byte tiles.
+bool tile_offsets_ok(const void *base, uint64_t stride, uint64_t og, uint64_t ou, uint64_t od) {
+    if (!q4b_ptr_tiled(base)) return true;
+    return (stride % Q4B_TILE_BYTES) == 0 && (og % Q4B_TILE_BYTES) == 0 && (ou % Q4B_TILE_BYTES) == 0 &&
+           (od % Q4B_TILE_BYTES) == 0;
+}
 
 bool launch_quant8(const float *x, uint64_t xs, uint32_t slen, uint32_t ns, int8_t *q, float *d,
                    int32_t *bs, uint64_t q_slice, uint64_t d_slice, const int32_t *n_dev) {
@@ -793,7 +799,8 @@ extern "C" bool q4_hip_moe_exec_staged(const uint8_t *base, uint64_t stride, uin
     (void)d_h2;
     (void)d_down;
     if (!g_q4b.ok || !base || !d_x || !d_h || !d_y || !n_embd) return false;
-    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(gt, dt, base)) return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(gt, dt, base) || !tile_offsets_ok(base, stride, og, ou, od))
+        return false;
     if (!quant_x(d_x, in_dim)) return false;
     return moe_exec_tail(base, stride, g_q4b.es_d, g_q4b.ew_d, 0, g_q4b.en_d, og, ou, od, d_h, d_y,
                          n_ff, in_dim, n_embd, dt, gt);
@@ -808,7 +815,8 @@ extern "C" bool q4_hip_moe_exec(const uint8_t *base, uint64_t stride, const int3
     (void)d_down;
     if (!g_q4b.ok || !base || !slots || !wts || !n || n > 64 || !d_x || !d_h || !d_y || !n_embd)
         return false;
-    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(gt, dt, base)) return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(gt, dt, base) || !tile_offsets_ok(base, stride, og, ou, od))
+        return false;
     // Like the reference (src/q4_rocm.cu:5441-5445) the list goes through mapped
     // host memory: the kernels fetch it themselves, no copy node on the stream.
     // The previous exec must have finished reading it.
@@ -830,7 +838,8 @@ extern "C" bool q4_hip_moe_exec_dev(const uint8_t *base, uint64_t stride, const 
     (void)d_down;
     if (!g_q4b.ok || !base || !d_es || !d_ew || !d_nhit || !d_x || !d_h || !d_y || !n_embd)
         return false;
-    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(gt, dt, base)) return false;
+    if (!shape_ok(gt, ut, dt, in_dim, n_ff) || !place_ok(gt, dt, base) || !tile_offsets_ok(base, stride, og, ou, od))
+        return false;
     if (!quant_x(d_x, in_dim)) return false;
     return moe_exec_tail(base, stride, d_es, d_ew, 0, d_nhit, og, ou, od, d_h, d_y, n_ff, in_dim,
                          n_embd, dt, gt);

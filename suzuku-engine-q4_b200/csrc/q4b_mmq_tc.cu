@@ -17,9 +17,13 @@
 // and the fp16 MMA accumulates A * B in fp32 over the eight groups of a super-block, whose
 // sum needs one multiply by d[m] (and the whole row one by rs[n]) on the CUDA cores: 1/8
 // fused multiply-add per element and group instead of 3.3 instructions.  The products are
-// the reference's integers times the reference's scales; a term differs from the exact one by
-// at most 2^-22 of its size (the two-term expansion of q * dq) and the group sums are added in
-// fp32 by the tensor core instead of after an exact integer sum.  With unit scales the result
+// the reference's integers times the reference's scales; a term q * dq differs from the exact
+// one by at most max(2^-22 of its size, 2^-25 of rs) -- the second plane of a value far below
+// the row's maximum falls into fp16's subnormal range, whose spacing is 2^-24 of rs -- and the
+// group sums are added in fp32 by the tensor core instead of after an exact integer sum.  The
+// error is therefore small against the row's largest group, not against every group: a row
+// with one channel 1000 times the rest keeps ~15 bits for the rest (tested: the outputs still
+// agree with the CUDA-core kernels to < 1e-4 rel-L2); q4_cuda_mmq_tc_mode(0) avoids it.  With unit scales the result
 // is the exact integer product (tested bit for bit); against the CUDA-core kernels, which do
 // form the integer sums, the outputs agree to ~1e-6 rel-L2.
 //
@@ -652,7 +656,7 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
     // passes of 16 rows so that its few entries still spread over many SMs
     const uint32_t pass_rows = rows <= 2048u ? 16u : NB;
     const uint64_t max_items = (uint64_t)n_entries + rows / pass_rows;
-    if (max_items > WORK_CAP) return false;
+    if (max_items > WORK_CAP || max_items > 65535u) return false;   // the pass index is gridDim.y
     CUtensorMap maps[2];
     for (int pl = 0; pl < 2; pl++) {
         // rows of fp16; a box is 64 k (128 bytes) of NB rows, stored with the 128-byte swizzle

@@ -71,6 +71,14 @@ NoAllocScratch *na_setup() {
         fprintf(stderr, "q4cuda: no-alloc exec: codebook upload failed: %s\n", cudaGetErrorString(e));
         return nullptr;
     }
+    // The upload comes from pageable memory: the call may return before the copy has landed, and
+    // it is ordered on the legacy default stream only, not against the caller's stream.  Wait
+    // for it once (a synchronisation, not an allocation).
+    e = cudaStreamSynchronize(0);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "q4cuda: no-alloc exec: codebook upload did not complete: %s\n", cudaGetErrorString(e));
+        return nullptr;
+    }
     g_na_ptr[dev] = (NoAllocScratch *)p;
     return g_na_ptr[dev];
 }
@@ -94,10 +102,15 @@ extern "C" bool q4_cuda_moe_exec_noalloc(const uint8_t *base, uint64_t stride,
         fprintf(stderr, "q4cuda: no-alloc exec: in_dim and n_ff must be multiples of 256\n");
         return false;
     }
+    const bool tiled = q4b_ptr_tiled(base);
+    if (tiled && ((stride % Q4B_TILE_BYTES) || (og % Q4B_TILE_BYTES) || (ou % Q4B_TILE_BYTES) ||
+                  (od % Q4B_TILE_BYTES))) {
+        fprintf(stderr, "q4cuda: no-alloc exec: in a tiled arena the three matrices must start on 880-byte tiles\n");
+        return false;
+    }
     NoAllocScratch *s = na_setup();
     if (!s) return false;
     cudaStream_t st = (cudaStream_t)stream;
-    const bool tiled = q4b_ptr_tiled(base);
     // x -> Q8-A
     {
         const uint32_t gps = in_dim >> 5;

@@ -325,7 +325,13 @@ extern "C" bool q4_hip_experts_alloc_a(int arena, uint32_t n_slots, uint64_t slo
     a.n_slots = n_slots;
     a.stride = slot_bytes;
     a.bytes = bytes;
-    a.tiled = tiled_default() && (slot_bytes % Q4B_TILE_BYTES) == 0 && (slot_bytes % 16) == 0;
+    // Tiled only where the slot can hold nothing but an all-IQ3_S pack: gate, up and down of
+    // widths that are multiples of 256 make 330 * n_ff * n_embd / 256 = a multiple of 84480
+    // bytes.  A multiple of 880 alone is not enough: a pack with an IQ4_NL down projection can
+    // have such a size, and tiling its bytes on upload would scramble it (such a pack stays in
+    // the engine's byte order; the exec calls refuse a non-IQ3_S part on a tiled arena before
+    // anything is enqueued).
+    a.tiled = tiled_default() && (slot_bytes % (g_tiled_default == 2 ? Q4B_TILE_BYTES : 84480u)) == 0;
     return true;
 }
 extern "C" void q4_hip_experts_free_a(int arena) {
@@ -502,7 +508,7 @@ bool q4b_ptr_tiled(const void *p) {
             return true;
     return q4b_wbuf_tiled(p);   // a gathered copy of a tiled arena keeps its byte order
 }
-extern "C" void q4_cuda_set_tiled_default(int on) { g_tiled_default = on ? 1 : 0; }
+extern "C" void q4_cuda_set_tiled_default(int on) { g_tiled_default = on == 2 ? 2 : (on ? 1 : 0); }
 extern "C" int q4_cuda_experts_tiled_a(int arena) {
     return (arena >= 0 && arena < 4 && g_arena[arena].base && g_arena[arena].tiled) ? 1 : 0;
 }

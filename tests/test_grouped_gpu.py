@@ -342,3 +342,45 @@ def test_grouped_product_edge_row_counts(dev, pkg, oracle, per):
         assert lib.q4_cuda_device_error() == 0
     finally:
         layer.close()
+
+
+def test_tensor_core_product_with_an_outlier_channel(dev, pkg, oracle):
+    """The tensor-core product carries an activation row as two fp16 planes scaled by one power
+    of two per row, so its error is small against the row's largest group, not against every
+    group.  Rows with one group 1000 times the rest (hidden states have such channels) must
+    still agree with the CUDA-core kernels, which form the exact integer sums, and with the CPU
+    int8 dot."""
+    H, F, n_exp, rows = 2048, 512, 2, 40
+    rng = np.random.default_rng(31)
+    packs = pkg.synth.expert_packs(rng, n_exp, H, F)
+    layer = pkg.MoeLayer(dev, packs, None, np.zeros((n_exp, H), np.float32), None, H, F, 1, arena=1)
+    lib = dev.lib
+    try:
+        x = rng.standard_normal((rows, H)).astype(np.float32)
+        x[:, 96:128] *= 1000.0                                   # one 32-group per row
+        bounds = np.array([0, rows // 2, rows], np.int32)
+        d_xq = dev.malloc(lib.q4_mmq_q8_bytes(rows, H))
+        d_dst = dev.malloc(rows * 2 * F * 4)
+        assert lib.q4_mmq_quantize(dev.upload(x), None, d_xq, IQ3_S, H, rows)
+        out = {}
+        for mode in (0, 1):
+            assert lib.q4_cuda_mmq_tc_mode(mode)
+            try:
+                assert lib.q4_mmq_mul_id(layer.base + layer.og, IQ3_S, 2 * F, H, layer.stride, n_exp, d_xq,
+                                         dev.upload(bounds), rows // 2, rows, d_dst, 2 * F)
+            finally:
+                assert lib.q4_cuda_mmq_tc_mode(-1)
+            out[mode] = dev.download(d_dst, (rows, 2 * F), np.float32)
+        worst = max(_rel(out[1][r], out[0][r]) for r in range(rows))
+        print("outlier rows: tensor-core vs CUDA-core product, worst rel-L2 %.3g" % worst)
+        assert worst < 1e-4
+        rb = pkg.synth.iq3s_row_bytes(H)
+        for r in (0, rows - 1):
+            xq = oracle.quant8(x[r])
+            e = 0 if r < rows // 2 else 1
+            want = np.array([oracle.dot8(packs[e][j * rb:(j + 1) * rb], xq, H) for j in range(0, 2 * F, 37)])
+            assert _rel(out[1][r, ::37], want) <= 1e-3
+        assert lib.q4_cuda_device_error() == 0
+    finally:
+        lib.q4_cuda_mmq_tc_mode(-1)
+        layer.close()

@@ -115,3 +115,40 @@ def test_iq4nl_down_refused_on_a_tiled_arena(dev, pkg):
         assert lib.q4_cuda_launch_count() == n0
     finally:
         lib.q4_hip_experts_free_a(3)
+
+
+def test_mixed_pack_of_a_tile_multiple_size_is_not_tiled(dev, pkg, oracle):
+    """An arena is tiled only when its slot size is that of an all-IQ3_S pack.  Here the pack has
+    an IQ4_NL down projection and its size is a multiple of the 880-byte tile all the same
+    (hidden 2816, intermediate 1280): it must stay in the engine's byte order on upload and run."""
+    H, F, n_slots, k = 2816, 1280, 3, 2
+    rng = np.random.default_rng(9)
+    packs = pkg.synth.expert_packs_typed(rng, n_slots, H, F, IQ3_S, IQ4_NL)
+    pb = packs.shape[1]
+    assert pb % 880 == 0 and pb % 84480 != 0
+    lib = dev.lib
+    assert lib.q4_hip_experts_alloc_a(3, n_slots, pb)           # the default format rule decides
+    try:
+        assert lib.q4_cuda_experts_tiled_a(3) == 0
+        for e in range(n_slots):
+            row = np.ascontiguousarray(packs[e])
+            assert lib.q4_hip_experts_put_a(3, e, row.ctypes.data, pb)
+        back = np.empty(pb, np.uint8)
+        assert lib.q4_cuda_experts_get_a(3, 1, back.ctypes.data, pb)
+        assert np.array_equal(back, packs[1])
+        base, stride = lib.q4_hip_experts_base_a(3), lib.q4_hip_experts_stride_a(3)
+        rb = pkg.synth.row_bytes(IQ3_S, H)
+        og, ou, od = 0, F * rb, 2 * F * rb
+        x = rng.standard_normal(H).astype(np.float32)
+        slots = np.array([2, 0], np.int32)
+        wts = rng.random(k).astype(np.float32)
+        d_x, d_y, d_h = dev.upload(x), dev.malloc(H * 4), dev.malloc(64 * F * 4)
+        assert lib.q4_hip_fill(d_y, 0.0, H)
+        assert lib.q4_hip_moe_exec(base, stride, slots.ctypes.data, wts.ctypes.data, k, IQ3_S, og, IQ3_S, ou,
+                                   IQ4_NL, od, d_x, d_h, None, None, d_y, F, H, H)
+        y = dev.download(d_y, (H,), np.float32)
+        want = oracle.expert_job_t([packs[s] for s in slots], wts, x, H, F, IQ4_NL, IQ3_S)
+        assert np.linalg.norm(y - want) / np.linalg.norm(want) <= 1e-3
+        assert lib.q4_cuda_device_error() == 0
+    finally:
+        lib.q4_hip_experts_free_a(3)

@@ -20,7 +20,7 @@ def arena(dev, pkg):
 
     def make(packs, tiled=True, arena_id=2):
         lib = dev.lib
-        lib.q4_cuda_set_tiled_default(1 if tiled else 0)
+        lib.q4_cuda_set_tiled_default(2 if tiled else 0)   # 2: these slots hold IQ3_S bytes only, whatever their size
         assert lib.q4_hip_experts_alloc_a(arena_id, packs.shape[0], packs.shape[1])
         lib.q4_cuda_set_tiled_default(1)
         made.append(arena_id)
