@@ -71,7 +71,7 @@ CONFIG1 = {"workload": "config1: one MoE layer, decode batch 1, hidden 2048, ff 
 
 def config4(world, n_layers):
     return {"workload": "config4: expert-parallel decode, 64 tokens x %d MoE layers per step, 512 "
-                        "experts top-10 + shared, experts sharded %d-way, NCCL dispatch/combine"
+                        "experts top-10 + shared, experts sharded %d-way over NCCL"
                         % (n_layers, world),
             "l2": "inputs larger than L2: a step reads %d layers of weights" % n_layers,
             "tokens_per_rank": 64 // world, "experts_per_rank": N_EXPERT // world}
@@ -405,7 +405,7 @@ class BatchJob:
     every layer on the same input rows; this object is one rank's part (world == 1: the whole
     job on one GPU through q4_cuda_moe_layer_n)."""
 
-    def __init__(self, pkg, model, ep, rank, world, tokens, layers, chain=True, x_all=None):
+    def __init__(self, pkg, model, ep, rank, world, tokens, layers, chain=True, x_all=None, form="ar"):
         self.pkg, self.m, self.dev, self.lib = pkg, model, model.dev, model.lib
         lib, dev = self.lib, self.dev
         self.ep, self.world, self.layers, self.chain = ep, world, list(layers), chain
@@ -413,8 +413,14 @@ class BatchJob:
         self.t_local = tokens // world
         if x_all is None:
             x_all = pkg.synth.hidden(SEED + 3, tokens, N_EMBD)
-        self.x_host = np.ascontiguousarray(x_all[rank * self.t_local:(rank + 1) * self.t_local])
-        self.nb = nb = self.t_local * N_EMBD * 4
+        # expert-parallel forms: "ar" keeps all token rows on every rank and sums the ranks' partial
+        # rows with one all-reduce per layer; "a2a" keeps a rank's own tokens only and exchanges
+        # twice per layer (gather of rows and picks, all-to-all of partial rows)
+        self.form = form
+        self.rows = tokens if (world > 1 and form == "ar") else self.t_local
+        first = 0 if self.rows == tokens else rank * self.t_local
+        self.x_host = np.ascontiguousarray(x_all[first:first + self.rows])
+        self.nb = nb = self.rows * N_EMBD * 4
         self.d_x0, self.d_a, self.d_b = dev.upload(self.x_host), dev.malloc(nb), dev.malloc(nb)
         self.h_x, self.h_y = lib.q4_hip_host_alloc_coh(nb), lib.q4_hip_host_alloc_coh(nb)
         ctypes.memmove(self.h_x, self.x_host.ctypes.data, nb)
@@ -435,9 +441,9 @@ class BatchJob:
                                               EPS, m.router(l), N_EXPERT, TOPK, N_EMBD, N_FF, self.t_local, dst,
                                               d_ids, None, self.d_ws, self.ws)
         else:
-            ok = self.ep.q4_cuda_ep_layer(m.layer_base(l), m.stride, m.og, m.ou, m.od, 1, src, m.norm(l), EPS,
-                                          m.router(l), N_EXPERT, TOPK, N_EMBD, N_FF, self.t_local, dst, self.d_ws,
-                                          self.ws)
+            call = self.ep.q4_cuda_ep_layer_ar if self.form == "ar" else self.ep.q4_cuda_ep_layer
+            ok = call(m.layer_base(l), m.stride, m.og, m.ou, m.od, 1, src, m.norm(l), EPS, m.router(l), N_EXPERT,
+                      TOPK, N_EMBD, N_FF, self.t_local, dst, self.d_ws, self.ws)
         if not ok:
             raise RuntimeError("layer call refused")
 
@@ -504,7 +510,7 @@ class BatchJob:
         lib.q4_hip_stream_sync()
 
     def output(self):
-        return self.dev.download(self.d_out, (self.t_local, N_EMBD), np.float32)
+        return self.dev.download(self.d_out, (self.rows, N_EMBD), np.float32)
 
     def release(self):
         if self.graph:      # a graph that holds collective nodes must go before the communicator does
@@ -829,11 +835,12 @@ def run_ep(a, pkg, rank, world, local, warmup):
     err = lib.q4_cuda_device_error()
     if err:
         raise SystemExit("device error word %#x" % err)
-    floor_us = None
-    if ep is not None and hasattr(ep, "q4_cuda_ep_exchange_floor_us"):
-        f = ctypes.c_float(0.0)
-        if ep.q4_cuda_ep_exchange_floor_us(job.t_local, N_EMBD, TOPK, job.d_ws, job.ws, ctypes.byref(f)):
-            floor_us = barrier_max(f.value)
+    floor = None
+    if ep is not None:
+        f2 = (ctypes.c_float * 2)()
+        if ep.q4_cuda_ep_exchange_floor_us(job.t_local, N_EMBD, TOPK, N_EXPERT, N_FF, job.d_ws, job.ws, 50, f2):
+            floor = {"gather_plus_all_to_all": barrier_max(f2[0]), "all_reduce": barrier_max(f2[1]),
+                     "what": "one layer's collectives alone, with the layer's payload sizes, microseconds"}
     # results for the comparison with one GPU: the first layer alone (every rank takes part in its
     # exchanges), and the whole stack
     job.enqueue(layers=[0])
@@ -842,7 +849,15 @@ def run_ep(a, pkg, rank, world, local, warmup):
     job.step()
     dev.sync()
     y_ep = job.output() if rank == 0 else None
-    details = {"cuda_graph": graphed, "repeats": repeats, "exchange_floor_us": floor_us}
+    details = {"cuda_graph": graphed, "repeats": repeats, "exchange_floor_us": floor,
+               "form": "every rank holds all 64 token rows; one all-reduce of the partial rows per layer"}
+    if ep is not None:
+        # the two-exchange form of the same job (tokens split over the ranks), for comparison
+        job2 = BatchJob(pkg, model, ep, rank, world, EP_TOKENS, range(n_layers), form="a2a")
+        ms2, _, launches2, _ = time_job(job2, a.steps, warmup, barrier_max, min_ms=20.0)
+        details["two_exchange_form"] = {"ms_per_step": ms2, "value": EP_TOKENS * n_layers / (ms2 * 1e-3),
+                                        "unit": UNIT, "launches_per_step": launches2}
+        job2.release()
     if world > 1 and rank == 0 and not a.no_cpu:
         job.release()
         model.release()
@@ -854,10 +869,10 @@ def run_ep(a, pkg, rank, world, local, warmup):
             return float(np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30))
         solo.enqueue(layers=[0])
         dev.sync()
-        rel_l0 = rel(y_ep_l0, solo.output()[:job.t_local])
+        rel_l0 = rel(y_ep_l0, solo.output()[:job.rows])
         solo.step()
         dev.sync()
-        rel_all = rel(y_ep, solo.output()[:job.t_local])
+        rel_all = rel(y_ep, solo.output()[:job.rows])
         units1 = EP_TOKENS * n_layers
         details["one_gpu_same_job"] = {"value": units1 / (s_ms * 1e-3), "e2e": units1 / (s_e2e * 1e-3),
                                        "unit": UNIT, "ms_per_step": s_ms}

@@ -43,6 +43,20 @@ bool q4_cuda_ep_layer(const uint8_t *base, uint64_t stride, uint64_t og, uint64_
                       const float *d_router, uint32_t n_expert, uint32_t topk, uint32_t n_embd,
                       uint32_t n_ff, uint32_t t_local, float *d_y, void *d_ws, uint64_t ws_bytes);
 
+/* The one-collective form of the same layer: d_x and d_y hold ALL world * t_local token rows,
+ * identical on every rank; each rank norms and routes every token itself, runs its own experts
+ * (and the shared expert for tokens [rank * t_local, (rank + 1) * t_local)), and one all-reduce
+ * leaves the summed rows in d_y on every rank.  Same arguments otherwise; n_expert <= n_embd. */
+bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou, uint64_t od,
+                         int has_shared, const float *d_x, const float *d_norm_w, float eps,
+                         const float *d_router, uint32_t n_expert, uint32_t topk, uint32_t n_embd,
+                         uint32_t n_ff, uint32_t t_local, float *d_y, void *d_ws, uint64_t ws_bytes);
+/* Cost of one layer's collectives alone, microseconds (mean of iters rounds with the layer's
+ * payload sizes): out2[0] the two exchanges of q4_cuda_ep_layer, out2[1] the all-reduce of
+ * q4_cuda_ep_layer_ar.  Synchronises; d_ws as for the layer calls. */
+bool q4_cuda_ep_exchange_floor_us(uint32_t t_local, uint32_t n_embd, uint32_t topk, uint32_t n_expert,
+                                  uint32_t n_ff, void *d_ws, uint64_t ws_bytes, uint32_t iters, float *out2);
+
 #ifdef __cplusplus
 }
 #endif

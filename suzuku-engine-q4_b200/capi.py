@@ -237,6 +237,9 @@ EP_SIGNATURES = {
     "q4_cuda_ep_layer_ws_bytes": (u64, [u32, u32, u32, u32, u32, u32]),
     "q4_cuda_ep_layer": (b, [vp, u64, u64, u64, u64, C.c_int, vp, vp, f32, vp, u32, u32, u32, u32, u32,
                              vp, vp, u64]),
+    "q4_cuda_ep_layer_ar": (b, [vp, u64, u64, u64, u64, C.c_int, vp, vp, f32, vp, u32, u32, u32, u32, u32,
+                                vp, vp, u64]),
+    "q4_cuda_ep_exchange_floor_us": (b, [u32, u32, u32, u32, u32, vp, u64, u32, vp]),
 }
 _ep = None
 

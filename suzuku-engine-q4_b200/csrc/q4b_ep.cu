@@ -208,3 +208,101 @@ extern "C" bool q4_cuda_ep_layer(const uint8_t *base, uint64_t stride, uint64_t 
     ep_sum_k<<<(unsigned)((blk + 255) / 256), 256, 0, st>>>(w.recv, d_y, (uint32_t)blk, G);
     return cudaGetLastError() == cudaSuccess;
 }
+
+// The same layer in its one-collective form.  Every rank holds ALL T = world * t_local token
+// rows (d_x and d_y have T rows, identical on every rank): each rank norms and routes all
+// tokens itself (the router is replicated; at decode batch sizes that costs less than an
+// exchange), runs its own experts on the rows that picked them plus the shared expert for the
+// tokens [rank * t_local, (rank + 1) * t_local), and ONE all-reduce sums the per-rank partial
+// rows into d_y on every rank -- which is the next layer's input, already in place.  One
+// collective and nine launches per layer instead of two exchanges and twelve launches; at 64
+// tokens the all-reduce moves 512 KB.  Results equal the single-GPU ones up to the order of the
+// fp32 sum over ranks.
+extern "C" bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64_t og, uint64_t ou,
+                                    uint64_t od, int has_shared, const float *d_x,
+                                    const float *d_norm_w, float eps, const float *d_router,
+                                    uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
+                                    uint32_t t_local, float *d_y, void *d_ws, uint64_t ws_bytes) {
+    if (!g_comm || !base || !d_x || !d_router || !d_y || !d_ws || t_local == 0) return false;
+    const uint32_t G = (uint32_t)g_world;
+    if (n_expert % G) return false;
+    const uint32_t e_local = n_expert / G, n_e = e_local + 1u;
+    if (n_e > 512u || topk == 0 || topk >= 64u) return false;
+    const EpWs w = carve((uint8_t *)d_ws, G, t_local, topk, n_expert, n_embd, n_ff);
+    if (ws_bytes < w.bytes) return false;
+    cudaStream_t st = (cudaStream_t)q4_hip_stream();
+    const uint32_t T = G * t_local, k1 = topk + 1u;
+    const uint64_t rows = (uint64_t)T * k1;
+    if (ou != og + (uint64_t)n_ff * (n_embd / 256u) * 110u) return false;
+    // all tokens: norm, router, top-k (w.recv doubles as the T x n_expert logits: T * n_embd floats
+    // hold them as long as n_expert <= n_embd)
+    if (n_expert > n_embd) return false;
+    if (!q4_hip_grouped_rms_n(d_x, d_norm_w, w.xn, n_embd, 1, eps, T)) return false;
+    if (!q4_hip_gemv_dd_n(Q4_T_F32, (const uint8_t *)d_router, n_expert, n_embd, w.xn, w.recv, 1.0f, T))
+        return false;
+    if (!q4_hip_route_pf(w.recv, w.ids, w.wts, T, n_expert, topk)) return false;
+    // local experts on the rows that picked them, the shared expert for this rank's tokens
+    if (!q4_cuda_assign_local(w.ids, w.wts, w.atok, w.rsrc, w.rw, w.bounds, T, topk,
+                              (uint32_t)g_rank * e_local, e_local, has_shared, (uint32_t)g_rank * t_local,
+                              t_local))
+        return false;
+    if (!q4_mmq_quantize(w.xn, w.atok, w.xq, Q4_T_IQ3_S, n_embd, rows)) return false;
+    const uint32_t share = 4u * (T * topk / n_expert + 1u);
+    const uint32_t max_hint = t_local > share ? t_local : share;
+    if (!q4_mmq_mul_id(base + og, Q4_T_IQ3_S, 2ull * n_ff, n_embd, stride, n_e, w.xq, w.bounds,
+                       max_hint, rows, w.gu, 2ull * n_ff))
+        return false;
+    if (!q4_cuda_mmq_swiglu_quantize(w.gu, w.hq, rows, n_ff)) return false;
+    if (!q4_mmq_mul_id(base + od, Q4_T_IQ3_S, n_embd, n_ff, stride, n_e, w.hq, w.bounds,
+                       max_hint, rows, w.pd, n_embd))
+        return false;
+    if (!q4_cuda_expert_reduce_set(w.partial, w.pd, w.rsrc, w.rw, T, k1, n_embd)) return false;
+    EP_NCCL(ncclAllReduce(w.partial, d_y, (size_t)T * n_embd, ncclFloat, ncclSum, g_comm, st));
+    return true;
+}
+
+// What the collectives of one layer cost by themselves, with the layer's payload sizes and
+// nothing else on the stream: out[0] = the two exchanges of q4_cuda_ep_layer (gather of rows
+// and picks, all-to-all of partial rows), out[1] = the one all-reduce of q4_cuda_ep_layer_ar;
+// microseconds per layer, mean of `iters` back-to-back rounds.  Synchronises.
+extern "C" bool q4_cuda_ep_exchange_floor_us(uint32_t t_local, uint32_t n_embd, uint32_t topk, uint32_t n_expert,
+                                             uint32_t n_ff, void *d_ws, uint64_t ws_bytes, uint32_t iters,
+                                             float *out2) {
+    if (!g_comm || !d_ws || !out2 || iters == 0 || t_local == 0) return false;
+    const uint32_t G = (uint32_t)g_world;
+    const EpWs w = carve((uint8_t *)d_ws, G, t_local, topk, n_expert, n_embd, n_ff);
+    if (ws_bytes < w.bytes) return false;
+    cudaStream_t st = (cudaStream_t)q4_hip_stream();
+    const uint32_t T = G * t_local;
+    const size_t blk = (size_t)t_local * n_embd;
+    cudaEvent_t e0, e1;
+    if (cudaEventCreate(&e0) != cudaSuccess || cudaEventCreate(&e1) != cudaSuccess) return false;
+    for (int form = 0; form < 2; form++) {
+        for (uint32_t it = 0; it < iters + 3u; it++) {
+            if (it == 3u) cudaEventRecord(e0, st);
+            if (form == 0) {
+                EP_NCCL(ncclGroupStart());
+                EP_NCCL(ncclAllGather(w.xn_l, w.xn, (size_t)t_local * n_embd, ncclFloat, g_comm, st));
+                EP_NCCL(ncclAllGather(w.ids_l, w.ids, (size_t)t_local * topk, ncclInt32, g_comm, st));
+                EP_NCCL(ncclAllGather(w.wts_l, w.wts, (size_t)t_local * topk, ncclFloat, g_comm, st));
+                EP_NCCL(ncclGroupEnd());
+                EP_NCCL(ncclGroupStart());
+                for (uint32_t p = 0; p < G; p++) {
+                    EP_NCCL(ncclSend(w.partial + p * blk, blk, ncclFloat, (int)p, g_comm, st));
+                    EP_NCCL(ncclRecv(w.recv + p * blk, blk, ncclFloat, (int)p, g_comm, st));
+                }
+                EP_NCCL(ncclGroupEnd());
+            } else {
+                EP_NCCL(ncclAllReduce(w.partial, w.recv, (size_t)T * n_embd, ncclFloat, ncclSum, g_comm, st));
+            }
+        }
+        cudaEventRecord(e1, st);
+        if (cudaEventSynchronize(e1) != cudaSuccess) return false;
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        out2[form] = 1e3f * ms / (float)iters;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return true;
+}

@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include "../../include/q4cuda.h"
+#include "q4_gguf_experts.h"
 
 uint64_t q4b_iq3s_row_bytes(uint32_t ncols) { return (uint64_t)(ncols / 256u) * 110u; }
 
@@ -71,6 +72,39 @@ bool q4b_moe_layer_load_stacked(q4b_moe_layer *L, int arena, const uint8_t *gate
     L->n_ff = n_ff;
     L->n_expert = n_expert;
     q4b_moe_layer_offsets(L);
+    return true;
+}
+
+bool q4b_moe_layer_load_gguf(q4b_moe_layer *L, int arena, const void *gguf, int32_t layer) {
+    const q4b_gguf *g = (const q4b_gguf *)gguf;
+    const q4b_gguf_tensor *tg, *tu, *td;
+    uint64_t og, ou, od, pb;
+    uint32_t n_expert;
+    if (!L || !q4b_gguf_expert_parts(g, layer, &tg, &tu, &td, &og, &ou, &od, &pb, &n_expert)) return false;
+    uint8_t *stage = (uint8_t *)q4_hip_host_alloc_coh(2 * pb);
+    if (!stage) return false;
+    const bool sh = q4b_gguf_read_shared_pack(g, layer, stage, pb) == (int64_t)pb;
+    bool ok = q4_hip_experts_alloc_a(arena, n_expert + (sh ? 1u : 0u), pb);
+    if (ok && sh) ok = q4_hip_experts_put_async_a(arena, n_expert, stage, pb);
+    if (ok && sh) q4_hip_copy_wait();
+    for (uint32_t e = 0; ok && e < n_expert; e++) {
+        uint8_t *p = stage + (uint64_t)(e & 1u) * pb;
+        if (e >= 2 && (e & 1u) == 0) q4_hip_copy_wait();   /* both staging packs may be in flight */
+        ok = q4b_gguf_read_pack(g, layer, (int32_t)e, p) == (int64_t)pb &&
+             q4_hip_experts_put_async_a(arena, e, p, pb);
+    }
+    q4_hip_copy_wait();
+    q4_hip_host_free_coh(stage);
+    if (!ok) return false;
+    L->arena = arena;
+    L->first_slot = 0;
+    L->shared_slot = sh ? (int32_t)n_expert : -1;
+    L->n_embd = (uint32_t)tg->ne[0];
+    L->n_ff = (uint32_t)tg->ne[1];
+    L->n_expert = n_expert;
+    L->og = og;
+    L->ou = ou;
+    L->od = od;
     return true;
 }
 

@@ -49,6 +49,13 @@ bool q4b_moe_layer_load_stacked(q4b_moe_layer *L, int arena, const uint8_t *gate
                                 const uint8_t *sh_gate, const uint8_t *sh_up, const uint8_t *sh_down,
                                 uint32_t n_expert, uint32_t n_embd, uint32_t n_ff);
 
+/* The same from a GGUF model file (host/q4_gguf_experts.h): the layer's stacked expert tensors
+ * are sliced into packs expert by expert (src/q4_expert.c:962-993) and uploaded, the shared
+ * expert's tensors (if the layer has them) into the slot after the last routed expert.  The
+ * shapes come from the tensors.  Takes any pack the file holds; the arena is tiled only when
+ * the pack is all IQ3_S.  `gguf` is a q4b_gguf the caller opened. */
+bool q4b_moe_layer_load_gguf(q4b_moe_layer *L, int arena, const void *gguf, int32_t layer);
+
 /* Scratch floats q4_moe_layer_dev needs at d_ws (src/q4_moe.c:2062-2065 sizes it the same way). */
 uint64_t q4_moe_layer_dev_ws_floats(const q4b_moe_layer *L);
 

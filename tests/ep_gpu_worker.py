@@ -93,6 +93,19 @@ def main():
         dev.sync()
         ys.append(dev.download(d_y, (T_LOCAL, H), np.float32))
     assert np.array_equal(ys[0], ys[1])
+    # the one-collective form: all token rows on every rank, one all-reduce; the rows of this
+    # rank's tokens must agree with the two-exchange form (another order of the sum over ranks)
+    d_xa = dev.upload(xs)
+    d_ya = dev.malloc(world * T_LOCAL * H * 4)
+    assert ep.q4_cuda_ep_layer_ar(base, stride, 0, F * rb, 2 * F * rb, 1, d_xa, d_norm, 1e-6, d_router,
+                                  E, K, H, F, T_LOCAL, d_ya, d_ws, ws)
+    dev.sync()
+    ya = dev.download(d_ya, (world * T_LOCAL, H), np.float32)
+    mine = ya[rank * T_LOCAL:(rank + 1) * T_LOCAL]
+    assert np.linalg.norm(mine - ys[0]) <= 1e-5 * np.linalg.norm(ys[0])
+    np.save(os.path.join(out_dir, "ya%d.npy" % rank), ya)
+    f2 = (ctypes.c_float * 2)()
+    assert ep.q4_cuda_ep_exchange_floor_us(T_LOCAL, H, K, E, F, d_ws, ws, 5, f2) and f2[0] > 0 and f2[1] > 0
     assert lib.q4_cuda_device_error() == 0
     f = ctypes.c_float(float(rank + 1))
     assert ep.q4_cuda_ep_allreduce_max(ctypes.byref(f)) and f.value == float(world)

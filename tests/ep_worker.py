@@ -71,6 +71,20 @@ def main():
         assert ids0.tolist() == ids[t].tolist()
         worst = max(worst, float(np.linalg.norm(y[i] - y0) / np.linalg.norm(y0)))
     assert worst < 1e-5, worst
+    # The one-collective form: every rank norms and routes ALL tokens, computes its own experts
+    # (the shared expert for its own tokens) and one all-reduce sums the partial rows everywhere.
+    xn_a = np.stack([O.rms_norm(x, L["norm_w"], 1e-6) for x in xs])
+    picks_a = [O.topk(O.softmax(O.gemv_f32(L["router"], x)), K, True) for x in xn_a]
+    ids_a = np.stack([p[0] for p in picks_a]).astype(np.int32)
+    wts_a = np.stack([p[1] for p in picks_a]).astype(np.float32)
+    assert np.array_equal(ids_a, ids) and np.array_equal(wts_a, wts)      # replicated routing = gathered routing
+    total = torch.from_numpy(partial.copy())
+    dist.all_reduce(total)
+    worst_ar = 0.0
+    for t in range(T):
+        y0 = O.moe_layer(xs[t], L["norm_w"], 1e-6, L["router"], K, L["experts"], L["shared"], H, F)[0]
+        worst_ar = max(worst_ar, float(np.linalg.norm(total.numpy()[t] - y0) / np.linalg.norm(y0)))
+    assert worst_ar < 1e-5, worst_ar
     # every pick is owned by exactly one rank
     owned = torch.from_numpy((lids[:, :K] >= 0).astype(np.int32))
     dist.all_reduce(owned)

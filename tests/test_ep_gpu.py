@@ -55,3 +55,9 @@ def test_ep_layer_two_gpus(tmp_path, dev, pkg, oracle):
         n0 = np.linalg.norm(y0)
         assert np.linalg.norm(y[t] - y1[t]) / n0 < 1e-5        # only the summation order differs
         assert np.linalg.norm(y[t] - y0) / n0 < 1e-3
+    # the one-collective form: every rank ends with all rows, the same on every rank
+    ya = [np.load(os.path.join(str(tmp_path), "ya%d.npy" % r)) for r in range(world)]
+    assert np.array_equal(ya[0], ya[1])
+    for t in range(T):
+        n0 = np.linalg.norm(y1[t])
+        assert np.linalg.norm(ya[0][t] - y1[t]) / n0 < 1e-5

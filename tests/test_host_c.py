@@ -15,7 +15,8 @@ def _build(pkg):
     cmd = ["gcc", "-O2", "-std=c11", "-Wall", "-Werror", "-mfma", "-ffp-contract=off",
            "-I", os.path.join(PKG, "csrc"), "-o", EXE,
            os.path.join(ROOT, "tests", "host_c", "q4_moe_host_test.c"),
-           os.path.join(PKG, "host", "q4_moe_b200.c"), os.path.join(ROOT, "oracle", "q4_oracle.c"),
+           os.path.join(PKG, "host", "q4_moe_b200.c"), os.path.join(PKG, "host", "q4_gguf_experts.c"),
+           os.path.join(ROOT, "oracle", "q4_oracle.c"),
            "-L", PKG, "-lq4cuda", "-lm", "-Wl,-rpath," + PKG]
     r = subprocess.run(cmd, capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
