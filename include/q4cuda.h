@@ -132,6 +132,18 @@ bool q4_hip_grouped_rms(const float *x, const float *w, float *y, uint32_t n_emb
                         float eps);
 bool q4_hip_grouped_rms_n(const float *x, const float *w, float *y, uint32_t n_embd,
                           uint32_t hc, float eps, uint32_t n_tok);
+/* Hyper-connection streams (src/q4.h:1366-1377): a token carries hc residual streams of n_embd
+ * floats.  combine: res[t][c] += block[t] * 2 sigmoid(inject[t][c] / hc).  comb_rms: the same
+ * update (block + hy when hy is given) and y[t][c] = RMSNorm(res[t][c]) * wn[c] in one launch,
+ * bit for bit what combine followed by q4_hip_grouped_rms gives (the reference tests exactly
+ * that, src/q4_test.c:1400-1430); y == NULL in the _n form: the update only. */
+bool q4_hip_hc_combine(float *res, const float *block, const float *inject, uint32_t n_embd, uint32_t hc);
+bool q4_hip_hc_combine_n(float *res, const float *block, const float *inject, uint32_t n_embd, uint32_t hc,
+                         uint32_t n_tok);
+bool q4_hip_hc_comb_rms(float *res, const float *block, const float *inject, const float *wn, float *y,
+                        uint32_t n_embd, uint32_t hc, float eps);
+bool q4_hip_hc_comb_rms_n(float *res, const float *block, const float *hy, const float *inject,
+                          const float *wn, float *y, uint32_t n_embd, uint32_t hc, float eps, uint32_t n_tok);
 /* d_y = scale * W d_x, all device pointers, overwrites y.  F32 or IQ3_S rows. */
 bool q4_hip_gemv_dd(uint32_t ggml_type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
                     const float *d_x, float *d_y, float scale);

@@ -71,6 +71,10 @@ SIGNATURES = {
     "q4_hip_softmax_topk_launch": (b, [vp, u32, u32, vp, vp]),
     "q4_hip_grouped_rms": (b, [vp, vp, vp, u32, u32, f32]),
     "q4_hip_grouped_rms_n": (b, [vp, vp, vp, u32, u32, f32, u32]),
+    "q4_hip_hc_combine": (b, [vp, vp, vp, u32, u32]),
+    "q4_hip_hc_combine_n": (b, [vp, vp, vp, u32, u32, u32]),
+    "q4_hip_hc_comb_rms": (b, [vp, vp, vp, vp, vp, u32, u32, f32]),
+    "q4_hip_hc_comb_rms_n": (b, [vp, vp, vp, vp, vp, vp, u32, u32, f32, u32]),
     "q4_hip_gemv_dd": (b, [u32, vp, u64, u64, vp, vp, f32]),
     "q4_hip_gemv_dd_n": (b, [u32, vp, u64, u64, vp, vp, f32, u32]),
     "q4_mmq_on": (C.c_int, []),

@@ -95,6 +95,54 @@ __global__ void rms_q8_k(const float *__restrict__ x, const float *__restrict__ 
     }
 }
 
+// ------------------------------------------------------------------ hyper-connection streams
+// A token carries hc residual streams of n floats.  After a block, stream c takes the block's
+// output row times 2 sigmoid(inject[c] / hc); the next block's input is the RMSNorm of every
+// updated stream (reference: hc_combine_k and hc_comb_rms_k, src/q4_rocm.cu:11341-11408).
+// One CTA per (stream, token).  NORM: the update and the norm in one pass -- a thread squares
+// the values it has just formed, in the element order rms_q8_k squares them in, so the sum,
+// the scale and the normalised row are bit for bit those of the update followed by the norm
+// as two launches.  hy: a second row added to the block's (exactly: b + hy).
+__device__ __forceinline__ float hc_stream_factor(const float *inject, uint32_t tok, uint32_t hc, uint32_t c) {
+    const float t = inject[(uint64_t)tok * hc + c] / (float)hc;
+    return 2.f * (1.f / (1.f + expf(-t)));
+}
+template <bool NORM>
+__global__ void __launch_bounds__(256) hc_streams_k(float *__restrict__ res, const float *__restrict__ block,
+                                                    const float *__restrict__ hy,
+                                                    const float *__restrict__ inject,
+                                                    const float *__restrict__ wn, float *__restrict__ y,
+                                                    uint32_t n, uint32_t hc, float eps) {
+    const uint32_t c = blockIdx.x, tok = blockIdx.y;
+    const uint64_t row = (uint64_t)tok * hc + c;
+    float *rc = res + row * n;
+    const float *bt = block + (uint64_t)tok * n;
+    const float *ht = hy ? hy + (uint64_t)tok * n : nullptr;
+    const float f = hc_stream_factor(inject, tok, hc, c);
+    double ss = 0.0;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {
+        const float b = ht ? __fadd_rn(bt[i], ht[i]) : bt[i];
+        const float v = __fadd_rn(rc[i], __fmul_rn(b, f));
+        rc[i] = v;
+        ss += (double)v * (double)v;
+    }
+    if (!NORM) return;
+    __shared__ double sh[8];
+#pragma unroll
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31u) == 0) sh[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    double tot = 0.0;
+    for (uint32_t i = 0; i < (blockDim.x >> 5); i++) tot += sh[i];
+    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(tot / (double)n), eps)));
+    const float *wc = wn ? wn + (uint64_t)c * n : nullptr;
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) {   // a thread re-reads what it wrote
+        float v = __fmul_rn(rc[i], scale);
+        if (wc) v = __fmul_rn(v, wc[i]);
+        y[row * n + i] = v;
+    }
+}
+
 // ------------------------------------------------------------------ fp32 GEMV (router)
 // One warp per weight row; grid.y = batch.
 __global__ void gemv_f32_k(const float *__restrict__ W, uint64_t nrows, uint64_t ncols,
@@ -875,6 +923,38 @@ extern "C" bool q4_hip_grouped_rms_n(const float *x, const float *w, float *y, u
                                                        nullptr, 0, 0);
     g_q4b_launches++;
     return q4b_launch_ok("grouped_rms");
+}
+// Stream update alone (reference q4_hip_hc_combine[_n], src/q4.h:1366,1376).
+extern "C" bool q4_hip_hc_combine_n(float *res, const float *block, const float *inject, uint32_t n_embd,
+                                    uint32_t hc, uint32_t n_tok) {
+    if (!g_q4b.ok || !res || !block || !inject || n_embd == 0 || hc == 0) return false;
+    hc_streams_k<false><<<dim3(hc, n_tok ? n_tok : 1), 256, 0, g_q4b.stream>>>(res, block, nullptr, inject, nullptr,
+                                                                               nullptr, n_embd, hc, 0.f);
+    g_q4b_launches++;
+    return q4b_launch_ok("hc_combine");
+}
+extern "C" bool q4_hip_hc_combine(float *res, const float *block, const float *inject, uint32_t n_embd,
+                                  uint32_t hc) {
+    return q4_hip_hc_combine_n(res, block, inject, n_embd, hc, 1);
+}
+// Update + norm in one launch (reference q4_hip_hc_comb_rms[_n], src/q4.h:1368-1375); y == NULL:
+// the update only (with the hy merge).
+extern "C" bool q4_hip_hc_comb_rms_n(float *res, const float *block, const float *hy, const float *inject,
+                                     const float *wn, float *y, uint32_t n_embd, uint32_t hc, float eps,
+                                     uint32_t n_tok) {
+    if (!g_q4b.ok || !res || !block || !inject || !n_tok || n_embd == 0 || hc == 0) return false;
+    const dim3 grid(hc, n_tok);
+    if (y)
+        hc_streams_k<true><<<grid, 256, 0, g_q4b.stream>>>(res, block, hy, inject, wn, y, n_embd, hc, eps);
+    else
+        hc_streams_k<false><<<grid, 256, 0, g_q4b.stream>>>(res, block, hy, inject, nullptr, nullptr, n_embd, hc, eps);
+    g_q4b_launches++;
+    return q4b_launch_ok("hc_comb_rms");
+}
+extern "C" bool q4_hip_hc_comb_rms(float *res, const float *block, const float *inject, const float *wn,
+                                   float *y, uint32_t n_embd, uint32_t hc, float eps) {
+    if (!y) return false;
+    return q4_hip_hc_comb_rms_n(res, block, nullptr, inject, wn, y, n_embd, hc, eps, 1);
 }
 extern "C" bool q4_hip_grouped_rms(const float *x, const float *w, float *y, uint32_t n_embd,
                                    uint32_t hc, float eps) {

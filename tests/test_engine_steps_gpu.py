@@ -347,3 +347,55 @@ def test_batched_fp32_gemv_all_kernel_paths(dev, n_batch):
     d_y1 = dev.malloc(nrows * 4)
     assert lib.q4_hip_gemv_dd_n(F32, dev.upload(w), nrows, ncols, dev.upload(x[n_batch - 1]), d_y1, 0.5, 1)
     assert _rel(dev.download(d_y1, (nrows,), np.float32), y[n_batch - 1]) < 2e-6
+
+
+def test_hyper_connection_update_and_norm_in_one_launch(dev):
+    """The reference's own check (src/q4_test.c:1400-1430): stream update + grouped RMSNorm in one
+    launch is bit for bit the two separate calls, for the residual streams and for the normalised
+    rows; the inputs are that test's closed-form patterns.  Then several tokens, with a second
+    block row merged in, against numpy."""
+    lib = dev.lib
+    hc, ne = 4, 512
+    tot = hc * ne
+    i = np.arange(tot)
+    hres = ((i * 37 % 101) - 50).astype(np.float32) * np.float32(0.01171875)
+    hblk = ((np.arange(ne) * 53 % 89) - 44).astype(np.float32) * np.float32(0.0078125)
+    hinj = ((np.arange(hc) * 29 % 41) - 20).astype(np.float32) * np.float32(0.0625)
+    hwn = np.float32(0.75) + ((i * 7) % 19).astype(np.float32) * np.float32(0.015625)
+    d_ra, d_rb = dev.upload(hres), dev.upload(hres)
+    d_b, d_i, d_w = dev.upload(hblk), dev.upload(hinj), dev.upload(hwn)
+    d_ya, d_yb = dev.malloc(tot * 4), dev.malloc(tot * 4)
+    assert lib.q4_hip_hc_combine(d_ra, d_b, d_i, ne, hc)
+    assert lib.q4_hip_grouped_rms(d_ra, d_w, d_ya, ne, hc, 1e-6)
+    assert lib.q4_hip_hc_comb_rms(d_rb, d_b, d_i, d_w, d_yb, ne, hc, 1e-6)
+    ra, rb = dev.download(d_ra, (tot,), np.float32), dev.download(d_rb, (tot,), np.float32)
+    ya, yb = dev.download(d_ya, (tot,), np.float32), dev.download(d_yb, (tot,), np.float32)
+    assert np.array_equal(ra.view(np.uint32), rb.view(np.uint32))
+    assert np.array_equal(ya.view(np.uint32), yb.view(np.uint32))
+    f = 2.0 / (1.0 + np.exp(-hinj.astype(np.float64) / hc))
+    want_r = hres.reshape(hc, ne) + hblk[None, :] * f[:, None]
+    np.testing.assert_allclose(ra.reshape(hc, ne), want_r, rtol=1e-6, atol=1e-6)
+    want_y = want_r / np.sqrt((want_r ** 2).mean(axis=1, keepdims=True) + 1e-6) * hwn.reshape(hc, ne)
+    np.testing.assert_allclose(ya.reshape(hc, ne), want_y, rtol=1e-5, atol=1e-6)
+    # n tokens, a second block row merged in; and the update-only form (y == NULL)
+    rng = np.random.default_rng(12)
+    T, H = 3, 2048
+    res0 = rng.standard_normal((T, hc, H)).astype(np.float32)
+    blk, hy = (rng.standard_normal((T, H)).astype(np.float32) for _ in range(2))
+    inj = rng.standard_normal((T, hc)).astype(np.float32)
+    wn = (1 + 0.1 * rng.standard_normal((hc, H))).astype(np.float32)
+    d_r, d_y = dev.upload(res0), dev.malloc(T * hc * H * 4)
+    assert lib.q4_hip_hc_comb_rms_n(d_r, dev.upload(blk), dev.upload(hy), dev.upload(inj), dev.upload(wn), d_y, H,
+                                    hc, 1e-6, T)
+    f = 2.0 / (1.0 + np.exp(-inj.astype(np.float64) / hc))
+    want_r = res0 + (blk.astype(np.float64) + hy)[:, None, :] * f[:, :, None]
+    want_y = want_r / np.sqrt((want_r ** 2).mean(axis=2, keepdims=True) + 1e-6) * wn[None]
+    np.testing.assert_allclose(dev.download(d_r, (T, hc, H), np.float32), want_r, rtol=1e-5, atol=1e-5)
+    np.testing.assert_allclose(dev.download(d_y, (T, hc, H), np.float32), want_y, rtol=1e-5, atol=1e-5)
+    d_r2 = dev.upload(res0)
+    assert lib.q4_hip_hc_comb_rms_n(d_r2, dev.upload(blk), dev.upload(hy), dev.upload(inj), None, None, H, hc,
+                                    1e-6, T)
+    assert np.array_equal(dev.download(d_r2, (T, hc, H), np.float32).view(np.uint32),
+                          dev.download(d_r, (T, hc, H), np.float32).view(np.uint32))
+    assert not lib.q4_hip_hc_comb_rms(d_r, dev.upload(blk), dev.upload(inj), None, None, H, hc, 1e-6)
+    assert lib.q4_cuda_device_error() == 0
