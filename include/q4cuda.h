@@ -252,8 +252,16 @@ bool q4_hip_moe_exec_tok(const uint8_t *base, uint64_t stride, const int32_t *d_
                          uint64_t og, uint32_t ut, uint64_t ou, uint32_t dt, uint64_t od,
                          const float *d_x, float *d_h, float *d_h2, float *d_y, uint32_t n_ff,
                          uint32_t in_dim, uint32_t n_embd);
-/* 2..8-row GEMV on 8-bit activations (src/q4.h:913-927): d_y[t][r] = scale * W[r] . q8(d_x[t]),
- * IQ3_S rows; between hold(x) and release() calls on the same x reuse its quantisation. */
+/* Dense product of up to 8 activation rows in 8-bit form (src/q4.h:913-927, src/q4_mmvq.cu):
+ * d_y[t][r] = scale * W[r] . q8(d_x[t]).  Weight types Q6_K (14), Q4_K (12), Q5_K (13), IQ4_XS (23),
+ * IQ4_NL (20) with the reference's arithmetic (activations per 32 values, d = amax / 127,
+ * q = rint(v / d); runs of 16 weights; fused multiply-adds in a fixed order, so a row's bits do
+ * not depend on n), and IQ3_S (21) through the grouped expert product.  ncols <= 16384, whole
+ * blocks; Q4_K / Q5_K rows 16-byte aligned, IQ4_XS 8, the others 2.
+ * q4_mmvq_set(mode): 0 off, 1 (default) calls of 2..8 rows, 2 calls of 1..8 rows but only between
+ * q4_mmvq_verify(1) and q4_mmvq_verify(0).  q4_mmvq_warm() allocates the row scratch (q4_hip_init
+ * already does).  Between hold(x) and release() calls on the same x (same width, no more rows)
+ * reuse its quantisation.  false: nothing was queued, the caller keeps its float path. */
 bool q4_mmvq_n(uint32_t ty, const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const float *d_x,
                float *d_y, float scale, uint32_t n);
 void q4_mmvq_warm(void);

@@ -55,6 +55,9 @@ class Oracle:
         L.q4o_iq4nl_dot8.argtypes = [_u8p, C.c_void_p, C.c_uint64]
         L.q4o_dot8_t.restype = C.c_float
         L.q4o_dot8_t.argtypes = [C.c_uint32, _u8p, C.c_void_p, C.c_uint64]
+        L.q4o_mv_row.restype = C.c_float
+        L.q4o_mv_row.argtypes = [C.c_uint32, _u8p, C.c_uint64, _i8p, _f32p, C.c_void_p]
+        L.q4o_mv_geometry.restype = C.c_int
 
     def grid(self):
         return np.array([self.lib.q4o_iq3s_grid(i) for i in range(512)], dtype=np.uint32)
@@ -226,6 +229,41 @@ class Oracle:
         d = np.zeros(x.size // 32, np.float32)
         self.lib.q4o_quant8_mmq(_p(x, _f32p), C.c_uint64(x.size), _p(q, _i8p), _p(d, _f32p))
         return q, d
+
+    # ---- dense product of up to 8 activation rows in 8-bit form (src/q4_mmvq.cu)
+    def quant8_d(self, x):
+        """(q int8 [n], d f32 [n/32], s16 i32 [n/16]) of one activation row."""
+        x = _f32(x).ravel()
+        q = np.zeros(x.size, np.int8)
+        d = np.zeros(x.size // 32, np.float32)
+        s16 = np.zeros(x.size // 16, np.int32)
+        self.lib.q4o_quant8_d(_p(x, _f32p), C.c_uint64(x.size), _p(q, _i8p), _p(d, _f32p),
+                              C.c_void_p(s16.ctypes.data))
+        return q, d, s16
+
+    def mv_geometry(self, type_id):
+        bb, bv = C.c_uint32(), C.c_uint32()
+        assert self.lib.q4o_mv_geometry(C.c_uint32(type_id), C.byref(bb), C.byref(bv))
+        return bb.value, bv.value
+
+    def mv_dequant_row(self, type_id, row, n):
+        row = _u8(row)
+        out = np.zeros(n, np.float32)
+        self.lib.q4o_mv_dequant_row(C.c_uint32(type_id), _p(row, _u8p), C.c_uint64(n), _p(out, _f32p))
+        return out
+
+    def mv_rows(self, type_id, w, nrows, ncols, xs, scale=1.0):
+        """y [n, nrows] = scale * W . q8(x[t]) in the order of src/q4_mmvq.cu:195-243."""
+        w = _u8(w).reshape(nrows, -1)
+        xs = _f32(xs).reshape(-1, ncols)
+        y = np.zeros((xs.shape[0], nrows), np.float32)
+        for t in range(xs.shape[0]):
+            q, d, s16 = self.quant8_d(xs[t])
+            for r in range(nrows):
+                v = self.lib.q4o_mv_row(C.c_uint32(type_id), _p(w[r], _u8p), C.c_uint64(ncols), _p(q, _i8p),
+                                        _p(d, _f32p), C.c_void_p(s16.ctypes.data))
+                y[t, r] = np.float32(scale) * np.float32(v)
+        return y
 
     def dot_mmq(self, row, q, d, n):
         row = _u8(row)

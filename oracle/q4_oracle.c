@@ -471,3 +471,154 @@ float q4o_iq3s_dot_mmq(const uint8_t *row, const int8_t *q, const float *dq,
     }
     return sum;
 }
+
+/* ---- dense product of up to 8 activation rows in 8-bit form (src/q4_mmvq.cu) ----
+ * Weight types: Q6_K, Q4_K, Q5_K (public ggml K-quant block formats), IQ4_XS, IQ4_NL.
+ * The unit of work is a run of 16 consecutive weights that share one scale: every value in
+ * it is a * w_i + c with integer w_i, so its dot with 16 quantised activations of scale dx is
+ * dx * (a * sum(w_i q_i) + c * sum(q_i)). */
+
+/* src/q4_mmvq.cu:36-57: per 32 values d = amax / 127, q = rint(v / d) (a division, not a
+ * product with the reciprocal), and the integer sum of each half of the group. */
+void q4o_quant8_d(const float *x, uint64_t n, int8_t *q, float *d, int32_t *s16) {
+    for (uint64_t g = 0; g < n / 32; g++) {
+        const float *xb = x + 32 * g;
+        float a = 0.f;
+        for (int i = 0; i < 32; i++) a = fmaxf(a, fabsf(xb[i]));
+        const float dg = a / 127.f;
+        int32_t s[2] = {0, 0};
+        for (int i = 0; i < 32; i++) {
+            const int v = dg > 0.f ? (int)rintf(xb[i] / dg) : 0;
+            q[32 * g + i] = (int8_t)v;
+            s[i >> 4] += v;
+        }
+        d[g] = dg;
+        s16[2 * g] = s[0];
+        s16[2 * g + 1] = s[1];
+    }
+}
+
+static float mv_f16(const uint8_t *p) { return q4o_f16_to_f32((uint16_t)(p[0] | (p[1] << 8))); }
+
+/* 6-bit scale and minimum of 32-value sub-block j out of the 12 packed bytes of a Q4_K /
+ * Q5_K block: j < 4 sits in the low 6 bits of bytes j and j + 4; j >= 4 takes its low
+ * nibbles from byte j + 4 and its two high bits from the top of bytes j - 4 and j. */
+static void mv_k_scale_min(const uint8_t *p, int j, int *sc, int *mn) {
+    if (j < 4) {
+        *sc = p[j] & 63;
+        *mn = p[j + 4] & 63;
+    } else {
+        *sc = (p[j + 4] & 15) | ((p[j - 4] >> 6) << 4);
+        *mn = (p[j + 4] >> 4) | ((p[j] >> 6) << 4);
+    }
+}
+
+int q4o_mv_geometry(uint32_t type, uint32_t *block_bytes, uint32_t *block_vals) {
+    uint32_t bb = 0, bv = 256;
+    switch (type) {
+    case Q4O_T_Q6_K: bb = 210; break;
+    case Q4O_T_Q4_K: bb = 144; break;
+    case Q4O_T_Q5_K: bb = 176; break;
+    case Q4O_T_IQ4_XS: bb = 136; break;
+    case Q4O_T_IQ4_NL: bb = 18; bv = 32; break;
+    default: return 0;
+    }
+    if (block_bytes) *block_bytes = bb;
+    if (block_vals) *block_vals = bv;
+    return 1;
+}
+
+/* Run r (16 values) of a block: the integer weights, the scale a, the offset c and the
+ * position of its first value inside the block (src/q4_mmvq.cu:101-190). */
+static void mv_run(uint32_t type, const uint8_t *blk, int r, int32_t w[16], float *a, float *c, int *first) {
+    *c = 0.f;
+    if (type == Q4O_T_Q6_K) {
+        /* ql[128] | qh[64] | int8 scales[16] | f16 d.  Each half of the block (128 values) is
+         * four strips of 32: strip s takes its low nibbles from ql bytes 32*(s&1)..+31 of the
+         * half (upper nibble for s >= 2) and its two high bits from bits 2s..2s+1 of the
+         * half's 32 qh bytes.  Stored values are offset by 32. */
+        const int half = r >> 3, strip = (r >> 1) & 3, lo = (r & 1) * 16;
+        const uint8_t *ql = blk + 64 * half + 32 * (strip & 1) + lo;
+        const uint8_t *qh = blk + 128 + 32 * half + lo;
+        for (int i = 0; i < 16; i++)
+            w[i] = ((ql[i] >> (4 * (strip >> 1))) & 15) | (((qh[i] >> (2 * strip)) & 3) << 4);
+        *a = mv_f16(blk + 208) * (float)(int8_t)blk[192 + 8 * half + 2 * strip + (r & 1)];
+        *c = -32.f * *a;
+        *first = 128 * half + 32 * strip + lo;
+        return;
+    }
+    if (type == Q4O_T_Q4_K || type == Q4O_T_Q5_K) {
+        /* f16 d | f16 dmin | scales[12] | (Q5_K: qh[32]) | qs[128].  Sub-block j = r / 2 (32
+         * values): sub-blocks 2p and 2p + 1 are the low and high nibbles of qs bytes 32p..32p+31;
+         * Q5_K adds bit j of qh byte l as bit 4 of value l. */
+        const int j = r >> 1, lo = (r & 1) * 16;
+        const uint8_t *qs = blk + (type == Q4O_T_Q5_K ? 48 : 16) + 32 * (j >> 1) + lo;
+        for (int i = 0; i < 16; i++) {
+            w[i] = (qs[i] >> (4 * (j & 1))) & 15;
+            if (type == Q4O_T_Q5_K) w[i] |= ((blk[16 + lo + i] >> j) & 1) << 4;
+        }
+        int sc, mn;
+        mv_k_scale_min(blk + 4, j, &sc, &mn);
+        *a = mv_f16(blk) * (float)sc;
+        *c = -mv_f16(blk + 2) * (float)mn;
+        *first = 32 * j + lo;
+        return;
+    }
+    /* IQ4_XS group r / 2 of the block, IQ4_NL the block itself: run r & 1 is the low (0) or high
+     * (1) nibbles of the group's 16 bytes, looked up in the 16-value codebook */
+    const int ib = r >> 1, hi = r & 1;
+    const uint8_t *qs = type == Q4O_T_IQ4_XS ? blk + 8 + 16 * ib : blk + 2;
+    for (int i = 0; i < 16; i++) w[i] = q4o_iq4nl_values[(qs[i] >> (4 * hi)) & 15];
+    *a = type == Q4O_T_IQ4_XS ? mv_f16(blk) * (float)(iq4xs_ls(blk, ib) - 32) : mv_f16(blk);
+    *first = 32 * ib + 16 * hi;
+}
+
+void q4o_mv_dequant_row(uint32_t type, const uint8_t *row, uint64_t n, float *dst) {
+    uint32_t bb, bv;
+    if (!q4o_mv_geometry(type, &bb, &bv)) return;
+    for (uint64_t b = 0; b < n / bv; b++)
+        for (int r = 0; r < (int)bv / 16; r++) {
+            int32_t w[16];
+            float a, c;
+            int first;
+            mv_run(type, row + b * bb, r, w, &a, &c, &first);
+            for (int i = 0; i < 16; i++) dst[b * bv + (uint64_t)first + i] = a * (float)w[i] + c;
+        }
+}
+
+/* One weight row against one quantised activation row, before the caller's scale
+ * (src/q4_mmvq.cu:195-243): 32 lanes take the row's runs round robin, each lane adds
+ * dx * (a * s + c * sum16) to its own accumulator with explicit fused multiply-adds, and the
+ * lanes are summed by the butterfly (offsets 16, 8, 4, 2, 1).  Nothing here depends on how
+ * many activation rows the call has. */
+float q4o_mv_row(uint32_t type, const uint8_t *row, uint64_t n, const int8_t *q, const float *d,
+                 const int32_t *s16) {
+    uint32_t bb, bv;
+    if (!q4o_mv_geometry(type, &bb, &bv)) return 0.f;
+    const uint32_t rpb = bv / 16;
+    const uint64_t n_runs = n / 16;
+    const int has_c = type == Q4O_T_Q6_K || type == Q4O_T_Q4_K || type == Q4O_T_Q5_K;
+    float acc[32];
+    for (int lane = 0; lane < 32; lane++) {
+        acc[lane] = 0.f;
+        for (uint64_t t = (uint64_t)lane; t < n_runs; t += 32) {
+            const uint64_t b = t / rpb;
+            int32_t w[16];
+            float a, c;
+            int first;
+            mv_run(type, row + b * bb, (int)(t % rpb), w, &a, &c, &first);
+            const uint64_t e0 = b * bv + (uint64_t)first;
+            int32_t s = 0;
+            for (int i = 0; i < 16; i++) s += w[i] * (int32_t)q[e0 + i];
+            float v = a * (float)s;
+            if (has_c) v = fmaf(c, (float)s16[e0 >> 4], v);
+            acc[lane] = fmaf(d[e0 >> 5], v, acc[lane]);
+        }
+    }
+    for (int o = 16; o; o >>= 1) {
+        float nx[32];
+        for (int lane = 0; lane < 32; lane++) nx[lane] = acc[lane] + acc[lane ^ o];
+        memcpy(acc, nx, sizeof acc);
+    }
+    return acc[0];
+}

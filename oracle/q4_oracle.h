@@ -150,6 +150,20 @@ void q4o_quant8_mmq(const float *x, uint64_t n, int8_t *q, float *d);
 float q4o_iq3s_dot_mmq(const uint8_t *row, const int8_t *q, const float *dq,
                        uint64_t n);
 
+/* ---- dense product of up to 8 activation rows in 8-bit form (src/q4_mmvq.cu) ---- */
+#define Q4O_T_Q4_K 12u
+#define Q4O_T_Q5_K 13u
+#define Q4O_T_Q6_K 14u
+/* src/q4_mmvq.cu:36-57: q = rint(v / d), d = amax / 127 per 32 values; s16 = sums per 16 */
+void q4o_quant8_d(const float *x, uint64_t n, int8_t *q, float *d, int32_t *s16);
+/* bytes and values per block of a type this product takes; 0 = not one of them */
+int q4o_mv_geometry(uint32_t type, uint32_t *block_bytes, uint32_t *block_vals);
+/* a * w + c of every run: pins the run decoders against the reference's q4_dequant_row */
+void q4o_mv_dequant_row(uint32_t type, const uint8_t *row, uint64_t n, float *dst);
+/* src/q4_mmvq.cu:195-243: one weight row x one quantised activation row, unscaled */
+float q4o_mv_row(uint32_t type, const uint8_t *row, uint64_t n, const int8_t *q, const float *d,
+                 const int32_t *s16);
+
 #ifdef __cplusplus
 }
 #endif

@@ -210,17 +210,12 @@ __global__ void tok_lists_k(const int32_t *__restrict__ slots, const float *__re
     }
 }
 
-// library-owned scratch: window lists for exec_tok; q8 rows, bounds and hold state for mmvq
+// library-owned scratch: window lists for exec_tok; q8 rows and bounds of the IQ3_S rows of q4_mmvq_n
 int32_t *g_tok_es = nullptr;
 float *g_tok_ew = nullptr;
 int32_t *g_tok_nh = nullptr;
 void *g_mv_xq = nullptr;        // q8 of up to 8 rows of Q4B_XQ_MAXLEN
 int32_t *g_mv_bounds = nullptr; // [9][2]: {0, n}
-const float *g_mv_hold = nullptr;
-bool g_mv_hold_valid = false;
-uint32_t g_mv_hold_n = 0;
-uint64_t g_mv_hold_cols = 0;
-int g_mv_on = 1;
 // expert-indexed weight buffers handed out by q4_mmq_wbuf
 uint8_t *g_wbuf_gu = nullptr, *g_wbuf_d = nullptr;
 uint64_t g_wbuf_gu_bytes = 0, g_wbuf_d_bytes = 0;
@@ -280,8 +275,6 @@ void q4b_elem_shutdown() {
     g_wbuf_gu = g_wbuf_d = nullptr;
     g_wbuf_gu_bytes = g_wbuf_d_bytes = 0;
     g_wbuf_tiled = false;
-    g_mv_hold = nullptr;
-    g_mv_hold_valid = false;
 }
 
 // ------------------------------------------------------------------ entry points
@@ -429,40 +422,6 @@ extern "C" bool q4_hip_moe_exec_tok(const uint8_t *base, uint64_t stride, const 
             return false;
     }
     return true;
-}
-
-// ---- 2..8-row GEMV on 8-bit activations (src/q4.h:913-927): y[t][r] = scale * W[r] . q8(x[t]) ----
-// Rows are quantised like every other activation here (per 32 values, d = amax / 127, round to
-// nearest even) and go through the grouped product as one "expert" that owns all n rows.
-extern "C" void q4_mmvq_warm(void) { (void)elem::warm(); }
-extern "C" int q4_mmvq_on(void) { return g_q4b.ok && elem::g_mv_on ? 1 : 0; }
-extern "C" void q4_mmvq_set(int v) { elem::g_mv_on = v ? 1 : 0; }
-extern "C" void q4_mmvq_verify(int on) { (void)on; }  // the reference's self-check against its float GEMV
-extern "C" void q4_mmvq_hold(const float *d_x) {
-    elem::g_mv_hold = d_x;
-    elem::g_mv_hold_valid = false;
-}
-extern "C" void q4_mmvq_release(void) {
-    elem::g_mv_hold = nullptr;
-    elem::g_mv_hold_valid = false;
-}
-extern "C" bool q4_mmvq_n(uint32_t ty, const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const float *d_x,
-                          float *d_y, float scale, uint32_t n) {
-    if (!g_q4b.ok || !elem::g_mv_on || !d_w || !d_x || !d_y || n < 2 || n > 8) return false;
-    if (ncols > Q4B_XQ_MAXLEN || !grouped::shape_ok(ty, nrows, ncols) || !elem::g_mv_xq) return false;
-    const bool held = elem::g_mv_hold == d_x && elem::g_mv_hold_valid && elem::g_mv_hold_n == n &&
-                      elem::g_mv_hold_cols == ncols;
-    if (!held) {
-        if (!q4_mmq_quantize(d_x, nullptr, elem::g_mv_xq, ty, ncols, n)) return false;
-        if (elem::g_mv_hold == d_x) {
-            elem::g_mv_hold_valid = true;
-            elem::g_mv_hold_n = n;
-            elem::g_mv_hold_cols = ncols;
-        }
-    }
-    if (!q4_mmq_mul_id(d_w, ty, nrows, ncols, 0, 1, elem::g_mv_xq, elem::g_mv_bounds + 2 * n, n, n, d_y, nrows))
-        return false;
-    return scale == 1.0f || q4_hip_scale(d_y, scale, (uint64_t)n * nrows);
 }
 
 // ---- expert-indexed weight buffers and the gather into them (src/q4.h:1144-1174) ----

@@ -19,6 +19,8 @@ static void timer_marks_shutdown();
 bool q4b_window_warm();  // q4b_grouped.cu: scratch of the verify-window path
 bool q4b_elem_warm();    // q4b_elem.cu: lists of the per-token exec, rows of the 2..8-row GEMV
 void q4b_elem_shutdown();
+bool q4b_mmvq_warm();    // q4b_mmvq.cu: quantised rows of the dense 8-bit product
+void q4b_mmvq_shutdown();
 bool q4b_wbuf_tiled(const void *p);
 bool q4b_mmq_tc_warm();  // q4b_grouped.cu: tensor-core grouped product (optional)
 std::atomic<uint64_t> g_q4b_launches{0};
@@ -123,7 +125,7 @@ bool alloc_scratch() {
     Q4B_CHECK(cudaMalloc(&s.r_cnt, (size_t)Q4B_MAX_TOK * sizeof(int32_t)));
     Q4B_CHECK(cudaMalloc(&s.hbuf, nq * sizeof(float)));
     q4b_mmq_tc_warm();  // without it the grouped product stays on the CUDA cores
-    return q4b_fused_warm() && q4b_window_warm() && q4b_elem_warm();
+    return q4b_fused_warm() && q4b_window_warm() && q4b_elem_warm() && q4b_mmvq_warm();
 }
 
 }  // namespace
@@ -205,6 +207,7 @@ extern "C" void q4_hip_shutdown(void) {
         g_arena[a] = Arena{};
     }
     q4b_elem_shutdown();
+    q4b_mmvq_shutdown();
     q4b_fused_shutdown();
     q4b_stack_forget_host(nullptr);
     cudaFree(s.xq);

@@ -10,5 +10,6 @@
 #include "q4b_few.cu"
 #include "q4b_grouped.cu"
 #include "q4b_elem.cu"
+#include "q4b_mmvq.cu"
 #include "q4b_compat.cu"
 #include "q4b_noalloc.cu"

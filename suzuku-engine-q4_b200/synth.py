@@ -70,11 +70,33 @@ def iq4xs_blocks(rng, n_blocks):
     return b
 
 
+# K-quant super-blocks (public ggml formats): {bytes per 256 values, offsets of the fp16 d and dmin}
+KQUANT = {12: (144, 0, 2), 13: (176, 0, 2), 14: (210, 208, None)}
+
+
+def kquant_blocks(rng, type_id, n_blocks):
+    """n_blocks random Q4_K (12), Q5_K (13) or Q6_K (14) super-blocks: uniform bytes, fp16
+    d = |N(0,1)| * 2^-8 and (Q4_K, Q5_K) dmin = |N(0,1)| * 2^-9, the magnitudes of the
+    reference's own test of this product (src/q4_test.c:2678-2682)."""
+    bs, od, om = KQUANT[type_id]
+    b = rng.integers(0, 256, size=(n_blocks, bs), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal(n_blocks)) * 2.0 ** -8).astype(np.float16)
+    b[:, od:od + 2] = d.view(np.uint8).reshape(n_blocks, 2)
+    if om is not None:
+        m = (np.abs(rng.standard_normal(n_blocks)) * 2.0 ** -9).astype(np.float16)
+        b[:, om:om + 2] = m.view(np.uint8).reshape(n_blocks, 2)
+    return b
+
+
 def row_bytes(type_id, ncols):
+    if type_id in KQUANT:
+        return ncols // 256 * KQUANT[type_id][0]
     return {21: ncols // 256 * IQ3S_BLOCK, 20: ncols // 32 * IQ4NL_BLOCK, 23: ncols // 256 * IQ4XS_BLOCK}[type_id]
 
 
 def blocks_of(rng, type_id, nbytes):
+    if type_id in KQUANT:
+        return kquant_blocks(rng, type_id, nbytes // KQUANT[type_id][0]).reshape(-1)
     make, bs = {21: (iq3s_blocks, IQ3S_BLOCK), 20: (iq4nl_blocks, IQ4NL_BLOCK), 23: (iq4xs_blocks, IQ4XS_BLOCK)}[type_id]
     return make(rng, nbytes // bs).reshape(-1)
 

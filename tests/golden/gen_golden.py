@@ -1,5 +1,6 @@
 #!/usr/bin/env python3
-"""Generate tests/golden/iq3s_moe_small.npz from the reference's own CPU code.
+"""Generate tests/golden/iq3s_moe_small.npz and tests/golden/dense_types_dequant.npz from the
+reference's own CPU code.
 
 Needs oracle/_ref/libq4ref.so (built by oracle/build.py from a reference
 checkout).  The fixture holds the inputs as bytes, so checking it needs neither
@@ -62,6 +63,22 @@ def main():
              deq=deq, y1=y1, y2=y2, router=router, norm_w=norm_w, xn=xn, logits=logits,
              probs=probs, top_ids=ids, top_w=w, kat=np.float32(kat))
     print("wrote", out, os.path.getsize(out), "bytes")
+    dense_types(synth, R)
+
+
+def dense_types(synth, R):
+    """Seeded rows of the five weight types of the dense 8-bit product (Q4_K, Q5_K, Q6_K, IQ4_XS,
+    IQ4_NL) with the reference's q4_dequant_row of each: pins the 16-value run decoders."""
+    rng = np.random.default_rng(20261126)
+    n = 512
+    out = {}
+    for ty in (12, 13, 14, 23, 20):
+        rows = np.stack([synth.blocks_of(rng, ty, synth.row_bytes(ty, n)) for _ in range(3)])
+        out["rows_%d" % ty] = rows
+        out["deq_%d" % ty] = np.stack([R.dequant_row_t(ty, r, n) for r in rows])
+    path = os.path.join(HERE, "dense_types_dequant.npz")
+    np.savez(path, n=n, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
 
 
 if __name__ == "__main__":

@@ -254,3 +254,56 @@ def test_expert_job_other_format_mixes_match_reference(pkg, oracle, reference, g
         reference.set_down_type(21)
     got = oracle.expert_job_t(list(packs), wts, x, H, F, dn, gu)
     assert np.linalg.norm(got - want) / np.linalg.norm(want) < 2e-6
+
+
+# ---- the dense product of up to 8 activation rows in 8-bit form (src/q4_mmvq.cu) ----
+DENSE_GOLD = os.path.join(os.path.dirname(__file__), "golden", "dense_types_dequant.npz")
+DENSE_TYPES = (12, 13, 14, 23, 20)      # Q4_K, Q5_K, Q6_K, IQ4_XS, IQ4_NL
+
+
+@pytest.mark.parametrize("ty", DENSE_TYPES)
+def test_dense_run_decoders_against_reference_dequant(oracle, reference, ty):
+    """value = a * w + c of every 16-value run against the reference's q4_dequant_row (fixture made by
+    tests/golden/gen_golden.py, and the compiled reference itself where it is present).  One wrong bit
+    in a decoded weight moves a value by a whole step `a`; the bound is a few float roundings."""
+    g = np.load(DENSE_GOLD)
+    n = int(g["n"])
+    for row, want in zip(g["rows_%d" % ty], g["deq_%d" % ty]):
+        got = oracle.mv_dequant_row(ty, row, n)
+        assert np.abs(got - want).max() <= 4e-7 * np.abs(want).max()
+        if reference is not None:
+            live = reference.dequant_row_t(ty, row, n)
+            assert np.array_equal(live.view(np.uint32), want.view(np.uint32))
+
+
+def test_dense_quantiser_divides_and_sums_halves(oracle):
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal(256).astype(np.float32)
+    x[32:64] = 0.0
+    x[64], x[65] = 127.0, 0.5              # d = 1: 0.5 rounds to even (0)
+    x[66:96] = 0.25
+    q, d, s16 = oracle.quant8_d(x)
+    assert d[1] == 0 and not q[32:64].any() and d[2] == 1.0 and q[64] == 127 and q[65] == 0
+    for gi in range(8):
+        xb = x[32 * gi:32 * gi + 32]
+        dg = np.float32(np.abs(xb).max()) / np.float32(127)
+        assert d[gi] == dg
+        if dg > 0:
+            assert np.array_equal(q[32 * gi:32 * gi + 32], np.rint(xb / dg).astype(np.int8))
+    assert np.array_equal(s16, q.astype(np.int32).reshape(-1, 16).sum(1))
+
+
+@pytest.mark.parametrize("ty", DENSE_TYPES)
+def test_dense_product_accuracy_and_row_independence(pkg, oracle, ty):
+    """The bound of the reference's own test (src/q4_test.c:2702-2716: rel-L2 < 2e-2 against the
+    dequantised weights in double) and a row's result not depending on the rows beside it."""
+    rng = np.random.default_rng(40 + ty)
+    K, R, NT = 2560, 24, 3
+    w = np.stack([pkg.synth.blocks_of(rng, ty, pkg.synth.row_bytes(ty, K)) for _ in range(R)])
+    xs = (rng.integers(-1000, 1001, (NT, K)) * 1e-3).astype(np.float32)
+    y = oracle.mv_rows(ty, w, R, K, xs, 0.5)
+    deq = np.stack([oracle.mv_dequant_row(ty, r, K) for r in w]).astype(np.float64)
+    want = 0.5 * xs.astype(np.float64) @ deq.T
+    assert np.linalg.norm(y - want) / np.linalg.norm(want) < 2e-2
+    y1 = oracle.mv_rows(ty, w, R, K, xs[1:2], 0.5)
+    assert np.array_equal(y1[0].view(np.uint32), y[1].view(np.uint32))
