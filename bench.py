@@ -387,7 +387,29 @@ class Decode1:
             raise RuntimeError("q4_cuda_decode_stack_host refused")
         ctypes.memmove(self.y_out.ctypes.data, self.h_y, N_EMBD * 4)
 
+    def session_begin(self):
+        """The resident form of the same kernel: one launch, then one doorbell ring per step; step s runs
+        layer s mod n_layers of the model."""
+        self.ses = self.lib.q4_cuda_decode_session_begin(self.stack_plan(0, self.m.n_layers), 1, 0, 0)
+        if not self.ses:
+            raise RuntimeError("q4_cuda_decode_session_begin refused")
+        self.x_ptrs = [self.x_host[i].ctypes.data for i in range(self.n_x)]
+
+    def session_steps(self, k, r):
+        """k steps of the session: the token's row goes from host memory into the kernel, the layer's
+        8 KB result comes back into host memory -- every step."""
+        step, ses, y, xp, n = self.lib.q4_cuda_decode_session_step, self.ses, self.y_out.ctypes.data, self.x_ptrs, self.n_x
+        for i in range(r * k, r * k + k):
+            if not step(ses, xp[i % n], y):
+                raise RuntimeError("q4_cuda_decode_session_step failed")
+
+    def session_end(self):
+        if getattr(self, "ses", None):
+            self.lib.q4_cuda_decode_session_end(self.ses)
+            self.ses = None
+
     def release(self):
+        self.session_end()
         for p in self.stack_plans.values():
             self.lib.q4_cuda_decode_stack_free(p)
         for p in self.plans or []:
@@ -980,6 +1002,11 @@ def run_config1(a, pkg, local, warmup):
     ke = min(k, 256)
     ms_e2e, rep_e2e = median_wall(lambda r: d1.e2e_steps(ke, r), ke, max(1, (min(warmup, 50) + ke - 1) // ke))
     ms_e2e_stack, _ = median_wall(d1.e2e_stack, model.n_layers, 2)
+    # --- end to end through a session: the same kernel resident, a doorbell ring per step ---
+    d1.session_begin()
+    ms_e2e_ses, rep_e2e_ses = median_wall(lambda r: d1.session_steps(ke, r), ke,
+                                          max(1, (min(warmup, 50) + ke - 1) // ke))
+    d1.session_end()
     clocks = sampler.stop()
     err = lib.q4_cuda_device_error()
     if err:
@@ -997,7 +1024,12 @@ def run_config1(a, pkg, local, warmup):
     details["repeats"] = repeats
     details["timed_ms"] = timed_ms
     details["steps_per_launch"] = min(k, model.n_layers)
-    details["e2e_repeats"] = rep_e2e
+    details["e2e_repeats"] = rep_e2e_ses
+    details["e2e_api"] = ("q4_cuda_decode_session_step: the stack kernel stays resident, each step's 8 KB row goes "
+                          "from host memory into the kernel and its 8 KB result back, one layer per step")
+    details["e2e_one_launch_per_step"] = {"value": 1e3 / ms_e2e, "unit": UNIT, "repeats": rep_e2e,
+                                          "what": "q4_cuda_decode_plan_host: one kernel launch per layer-step, "
+                                                  "8 KB in and 8 KB out per call"}
     details["e2e_stack"] = {"value": 1e3 / ms_e2e_stack, "unit": UNIT,
                             "what": "one host-buffer call per token through all %d layers (8 KB in, 8 KB out per "
                                     "call)" % model.n_layers}
@@ -1017,7 +1049,7 @@ def run_config1(a, pkg, local, warmup):
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": DTYPE, "data": "synthetic", "config": dict(CONFIG1, layers_rotated=a.layers),
         "details": details, "clocks": clocks,
-        "e2e": {"value": 1e3 / ms_e2e, "unit": UNIT, "h2d_bytes_per_step": N_EMBD * 4,
+        "e2e": {"value": 1e3 / ms_e2e_ses, "unit": UNIT, "h2d_bytes_per_step": N_EMBD * 4,
                 "d2h_bytes_per_step": N_EMBD * 4},
         "gpu_launches": launches,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s", "frac": achieved / hbm,

@@ -510,6 +510,20 @@ uint32_t q4_cuda_decode_stack_layers(void *plan);
 bool q4_cuda_decode_stack_dev(void *plan, const float *d_x, float *d_y, int32_t *d_ids, float *d_wts);
 bool q4_cuda_decode_stack_host(void *plan, const float *h_x, float *h_y);
 void q4_cuda_decode_stack_free(void *plan);
+/* Sessions: the stack kernel stays resident and a step costs no launch.  begin launches it on
+ * the library's stream over `plan`; it then waits on a doorbell in pinned host memory.  step
+ * copies the token's row (n_embd floats, any host memory) into the session's pinned buffer and
+ * rings; the kernel runs the next layers_per_step layers of the plan (cyclically: with 1, step s
+ * is layer s mod n_layers; 0 = all of them) and writes the result row and the step number into
+ * pinned host memory, where step is spinning; step copies the row to h_y and returns.  While a
+ * session is live its kernel holds every SM: other work on the device waits and the other decode
+ * calls of this library answer false, so end the session before anything else has to run.  The
+ * kernel leaves by itself after max_steps steps (0: 2^20) or idle_ms without a ring (0: 2000,
+ * at most 10000); the next step starts it again.  One session at a time.  step returns false if
+ * the kernel reported an error (q4_cuda_device_error) or never answered. */
+void *q4_cuda_decode_session_begin(void *plan, uint32_t layers_per_step, uint32_t max_steps, uint32_t idle_ms);
+bool q4_cuda_decode_session_step(void *session, const float *h_x, float *h_y);
+bool q4_cuda_decode_session_end(void *session);
 
 /* Diagnostics of the single-kernel layer path: when enabled, the kernel records
  * the GPU's nanosecond timer at the phase boundaries of one layer of the launch

@@ -189,6 +189,9 @@ SIGNATURES = {
     "q4_cuda_decode_stack_dev": (b, [vp, vp, vp, vp, vp]),
     "q4_cuda_decode_stack_host": (b, [vp, vp, vp]),
     "q4_cuda_decode_stack_free": (None, [vp]),
+    "q4_cuda_decode_session_begin": (vp, [vp, u32, u32, u32]),
+    "q4_cuda_decode_session_step": (b, [vp, vp, vp]),
+    "q4_cuda_decode_session_end": (b, [vp]),
     "q4_cuda_fused_profile_enable": (b, [C.c_int]),
     "q4_cuda_fused_profile_layer": (None, [u32]),
     "q4_cuda_decode_wait_limit": (None, [u32]),

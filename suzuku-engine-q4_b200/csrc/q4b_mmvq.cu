@@ -266,7 +266,6 @@ void shutdown() {
 
 template <uint32_t TY>
 bool launch(uint32_t n, const uint8_t *w, float *y, uint32_t K, uint32_t rows, float scale) {
-    if (K % Fmt<TY>::vals || ((uintptr_t)w % Fmt<TY>::align)) return false;
     const unsigned grid = (rows + 7u) / 8u;
     switch (n) {
 #define Q4B_MV_CASE(N)                                                                              \
@@ -283,6 +282,22 @@ bool launch(uint32_t n, const uint8_t *w, float *y, uint32_t K, uint32_t rows, f
 }
 
 bool dense_type(uint32_t ty) { return ty == 14u || ty == 12u || ty == 13u || ty == 23u || ty == 20u; }
+
+// whole blocks and the row alignment the type's loads need (checked before anything is queued)
+template <uint32_t TY> bool fits(const uint8_t *w, uint64_t K) {
+    return K % Fmt<TY>::vals == 0 && ((uintptr_t)w % Fmt<TY>::align) == 0 &&
+           (K / Fmt<TY>::vals * Fmt<TY>::bytes) % Fmt<TY>::align == 0;
+}
+bool dense_fits(uint32_t ty, const uint8_t *w, uint64_t K) {
+    switch (ty) {
+    case 14u: return fits<14u>(w, K);
+    case 12u: return fits<12u>(w, K);
+    case 13u: return fits<13u>(w, K);
+    case 23u: return fits<23u>(w, K);
+    case 20u: return fits<20u>(w, K);
+    default: return false;
+    }
+}
 
 }  // namespace mv
 
@@ -334,7 +349,7 @@ extern "C" bool q4_mmvq_n(uint32_t ty, const uint8_t *d_w, uint64_t nrows, uint6
             return false;
         return scale == 1.0f || q4_hip_scale(d_y, scale, (uint64_t)n * nrows);
     }
-    if (!mv::g_q) return false;   // q4_mmvq_warm allocates, outside any stream capture
+    if (!mv::g_q || !mv::dense_fits(ty, d_w, ncols)) return false;   // q4_mmvq_warm allocates, outside any stream capture
     const uint32_t K = (uint32_t)ncols, R = (uint32_t)nrows;
     if (!held) {
         const uint64_t ngr = (uint64_t)n * (K / 32u);

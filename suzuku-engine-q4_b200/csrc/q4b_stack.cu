@@ -37,6 +37,7 @@
 #include "q4b_tile.cuh"
 
 #include <atomic>
+#include <chrono>
 
 #include "../../include/q4cuda.h"
 
@@ -66,6 +67,10 @@ constexpr uint32_t N_MBAR = MB_CHUNK0 + MAX_CHUNKS;
 
 // error word bits (1 and 2 keep their meaning from the mbarrier / grid waits of the other kernels)
 constexpr uint32_t ERR_MBAR = 1u, ERR_POLL = 4u;
+// session: doorbell value that ends it; commands CTA 0 hands to the other CTAs; flag bits the host sees
+constexpr uint32_t BELL_STOP = 0xffffffffu;
+constexpr uint32_t CMD_GO = 1u, CMD_END = 2u;
+constexpr uint32_t FLAG_ERR = 0x80000000u, FLAG_EXIT = 0x40000000u;
 
 struct Layer {
     const uint8_t *base;      // slot 0 of this layer's experts
@@ -97,6 +102,15 @@ struct Args {
     volatile uint32_t *flag_host; // host-mapped word that receives flag_val (bit 31: error word was set)
     uint32_t flag_val;
     uint32_t poll_limit;
+    // session form (moe_decode_session_k): the kernel stays resident and serves one step per ring
+    // of a doorbell in host memory; a step runs lps consecutive layers of the plan (cyclically)
+    const float *x_host;          // host-mapped input row [H] of the step
+    const uint32_t *bell_host;    // host-mapped doorbell: the number of the step to run, or BELL_STOP
+    unsigned long long *cw;       // exchange word that carries a step's command from CTA 0 to the others
+    uint32_t lps;                 // layers per step
+    uint32_t li0;                 // the plan's layer the first step starts with
+    uint32_t max_steps;           // the kernel returns after this many steps
+    unsigned long long idle_ns;   // ... or when no ring comes for this long
     // shared-memory carve-up (bytes from the 1024-aligned start)
     uint32_t off_stage, off_down, off_sh;
 };
@@ -165,6 +179,29 @@ __device__ __forceinline__ float4 xw_poll4(const unsigned long long *p, uint32_t
                        __uint_as_float((uint32_t)c), __uint_as_float((uint32_t)d));
 }
 
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+// One word whose wait may be long (a session between two rings): bounded by time, not by polls.
+// Returns the word's value, or CMD_END (with the error bit set) when the time ran out.
+__device__ __forceinline__ uint32_t xw_poll_timed(const unsigned long long *p, uint32_t ep, unsigned long long ns,
+                                                  uint32_t *err) {
+    const unsigned long long t0 = global_ns();
+    for (uint32_t i = 0;; i++) {
+        unsigned long long w;
+        asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+        if ((uint32_t)(w >> 32) == ep) return (uint32_t)w;
+        if ((i & 1023u) == 1023u) {
+            if (global_ns() - t0 > ns) break;
+            if (i > (1u << 17)) __nanosleep(200);   // idle for a tenth of a second already: poll less often
+        }
+    }
+    atomicOr(err, ERR_POLL);
+    return CMD_END;
+}
+
 // Phase time stamp for the optional in-kernel profile.
 __device__ __forceinline__ void stamp(const Args &a, bool on, uint32_t slot) {
     if (on && threadIdx.x == 0) {
@@ -201,6 +238,7 @@ __device__ __forceinline__ uint32_t quant8_oct(float4 v, float *d_out, int *bs_o
 //   [65536, +...)     small arrays (below), then the staging regions
 struct Small {
     uint32_t last;   // 1 in the CTA that finished last (host hand-off)
+    uint32_t cmd;    // session: this step's command
     uint32_t ep0;    // epoch of layer 0 of this launch
     uint64_t mbar[N_MBAR];
     alignas(16) float xn[H];            // normalised x (router input)
@@ -393,6 +431,7 @@ __device__ __forceinline__ void issue_down(const Args &a, const Layer &L, Small 
 
 // The kernel body; xrow is the token's hidden row as H/4 float4: device memory for the
 // device-pointer call, the kernel's own parameter block for the host-buffer call.
+template <bool SESSION>
 __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
     // used directly (no integer round trip), so that the compiler keeps these as
     // shared-space accesses; dynamic shared memory starts on the declared alignment
@@ -427,11 +466,11 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
     const uint32_t v1 = (uint32_t)((uint64_t)(cta + 1) * (H / 4) / ncta) * ne;
 
     // loads with nothing before them in the dependency chain go first
-    Layer cur = a.layers ? a.layers[0] : a.l0;
+    Layer cur = a.layers ? a.layers[SESSION ? a.li0 : 0u] : a.l0;
     float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), wv = make_float4(1.f, 1.f, 1.f, 1.f);
     uint32_t code = 0;
     if (tid < H / 4) {
-        xv = xrow[tid];
+        if constexpr (!SESSION) xv = xrow[tid];
         if (cur.norm_w) wv = reinterpret_cast<const float4 *>(cur.norm_w)[tid];
         code = a.codes[tid];
     }
@@ -476,11 +515,69 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
     uint32_t par = 0;        // parity of the once-per-layer mbarriers
     uint32_t par_chunk = 0;  // parity of the mbarriers armed once per selection: gate/up chunks, down tiles
 
-    for (uint32_t l = 0; l < a.n_layers; l++) {
-        const bool prof = a.prof && l == a.prof_layer;
-        const bool more = l + 1 < a.n_layers;
+    uint32_t li = SESSION ? a.li0 : 0u;   // index of `cur` among the plan's layers
+    uint32_t step = 0;   // session: steps served so far
+    if constexpr (SESSION) __syncthreads();   // S.ep0
+    for (;;) {           // one pass; a session: one pass per ring of the doorbell
+    uint32_t epb = 0;    // this pass's first layer epoch, relative to S.ep0
+    if constexpr (SESSION) {
+        // A step owns MAX_LAYERS epochs: the first for its input row and command, the rest for its layers.
+        epb = step * MAX_LAYERS + 1u;
+        uint32_t ep_in = S.ep0 + step * MAX_LAYERS;
+        if (ep_in < S.ep0) ep_in += 1u;
+        if (cta == 0) {
+            // CTA 0 watches the doorbell (reads of host memory: a microsecond or two each), fetches
+            // the row from host memory and hands row and command to the other CTAs as exchange words
+            if (tid == 0) {
+                uint32_t cmd = CMD_END;
+                const unsigned long long t0 = global_ns();
+                for (;;) {
+                    uint32_t b;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(b) : "l"(a.bell_host) : "memory");
+                    if (b == step + 1u) {
+                        cmd = CMD_GO;
+                        break;
+                    }
+                    if (b == BELL_STOP || global_ns() - t0 > a.idle_ns) break;
+                }
+                S.cmd = cmd;
+            }
+            __syncthreads();
+            if (tid < H / 4) {
+                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (S.cmd == CMD_GO)
+                    asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                                 : "l"(reinterpret_cast<const float4 *>(a.x_host) + tid)
+                                 : "memory");
+                // read by every CTA right below; written again only after the host has seen this
+                // step's result, i.e. after every CTA finished the step
+                xw_store(a.xw + 4u * tid, v.x, ep_in);
+                xw_store(a.xw + 4u * tid + 1, v.y, ep_in);
+                xw_store(a.xw + 4u * tid + 2, v.z, ep_in);
+                xw_store(a.xw + 4u * tid + 3, v.w, ep_in);
+                xv = v;
+            }
+            if (tid == 0) {
+                xw_store(a.cw, __uint_as_float(S.cmd), ep_in);
+                // leaving without having been told to: the host must not wait for a result
+                if (S.cmd != CMD_GO) *a.flag_host = FLAG_EXIT;
+            }
+        } else {
+            if (tid == 0) S.cmd = xw_poll_timed(a.cw, ep_in, a.idle_ns + 1000000000ull, a.err);
+            __syncthreads();
+            if (S.cmd == CMD_GO && tid < H / 4) xv = xw_poll4(a.xw + 4u * tid, ep_in, limit, a.err);
+        }
+        if (S.cmd != CMD_GO) break;
+    }
+    const uint32_t n_run = SESSION ? a.lps : a.n_layers;
+    for (uint32_t l = 0; l < n_run; l++) {
+        const bool prof = a.prof && li == a.prof_layer;
+        const bool out = l + 1 == n_run;      // the pass's last layer: its y leaves the kernel
+        const bool more = SESSION || !out;    // some layer follows (a session: the next step's first)
+        const uint32_t nli = li + 1 < a.n_layers ? li + 1 : 0u;
         Layer nxt = cur;
-        if (more) nxt = a.layers[l + 1];
+        if (more && a.layers) nxt = a.layers[nli];
         stamp(a, prof, 0);
         // ---- phase 0: RMSNorm, Q8-A ----
         {
@@ -522,7 +619,7 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         }
         __syncthreads();
         stamp(a, prof, 1);
-        uint32_t ep = S.ep0 + l;      // this layer's epoch (skips 0 on wrap-around)
+        uint32_t ep = S.ep0 + epb + l;      // this layer's epoch (skips 0 on wrap-around)
         if (ep < S.ep0) ep += 1u;
 
         // ---- phase 1: router rows x xn, one warp per quarter row ----
@@ -757,15 +854,16 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
             // the layer's output row: written here, read by every CTA at the top of the next
             // layer; a CTA reaches this line for the next layer only after all CTAs published
             // that layer's hidden values, i.e. after they all read these words
-            if (more)
+            if (!out)
                 xw_store(a.xw + r, sum, ep);
             else
                 a.y[r] = sum;
         }
         stamp(a, prof, 12);
+        if (!out && tid < H / 4) xv = xw_poll4(a.xw + 4u * tid, ep, limit, a.err);
         if (more) {
-            if (tid < H / 4) xv = xw_poll4(a.xw + 4u * tid, ep, limit, a.err);
             cur = nxt;
+            li = nli;
             par ^= 1u;
         }
         par_chunk ^= 1u;
@@ -792,15 +890,26 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
             if (tid == 0) {
                 uint32_t ew;
                 asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ew) : "l"(a.err) : "memory");
-                *a.flag_host = a.flag_val | (ew ? 0x80000000u : 0u);   // every writer fenced at system scope above
+                *a.flag_host = (a.flag_val + step) | (ew ? FLAG_ERR : 0u);   // every writer fenced at system scope above
             }
             stamp(a, a.prof != nullptr, 15);   // in the last CTA only: when the flag was written
         }
     }
+    if constexpr (!SESSION) break;
+    step++;
+    if (step >= a.max_steps) break;
+    }
+    if constexpr (SESSION) {
+        // the epochs this launch used: later launches start beyond them (every CTA adds the same)
+        if (tid == 64) atomicAdd(a.ctr, (unsigned long long)(step + 1u));
+    }
 }
 
 __global__ void __launch_bounds__(NT, 1) moe_decode_stack_k(const Args a) {
-    stack_body(a, reinterpret_cast<const float4 *>(a.x));
+    stack_body<false>(a, reinterpret_cast<const float4 *>(a.x));
+}
+__global__ void __launch_bounds__(NT, 1) moe_decode_session_k(const Args a) {
+    stack_body<true>(a, nullptr);
 }
 
 // The host-buffer form: the 8 KB hidden row travels inside the launch's parameter block, so
@@ -809,7 +918,7 @@ struct XRow {
     float4 v[H / 4];
 };
 __global__ void __launch_bounds__(NT, 1) moe_decode_stack_xp_k(const Args a, const __grid_constant__ XRow xr) {
-    stack_body(a, xr.v);
+    stack_body<false>(a, xr.v);
 }
 
 }  // namespace stk
@@ -821,10 +930,11 @@ static bool g_s_attr_set = false;
 static unsigned long long *g_s_prof = nullptr;  // set by q4_cuda_fused_profile_enable(1)
 static uint32_t g_s_prof_layer = 0;
 static uint32_t g_s_poll_limit = stk::POLL_LIMIT;
+static struct Q4bSession *g_s_session = nullptr;   // the live session, if any (its kernel owns the GPU)
 
 static bool stack_scratch() {
     if (g_s_ctr) return true;
-    const size_t words = (size_t)stk::H + 4u * stk::NT + (size_t)stk::MAX_E * stk::F;
+    const size_t words = (size_t)stk::H + 4u * stk::NT + (size_t)stk::MAX_E * stk::F + 4u;   // xw | lw | hw | cw
     Q4B_CHECK(cudaMalloc(&g_s_words, words * sizeof(unsigned long long)));
     Q4B_CHECK(cudaMemset(g_s_words, 0, words * sizeof(unsigned long long)));
     Q4B_CHECK(cudaMalloc(&g_s_ctr, 2 * sizeof(unsigned long long)));
@@ -833,7 +943,9 @@ static bool stack_scratch() {
 }
 
 bool q4b_fused_warm() { return stack_scratch(); }
+static void session_end_of(const struct Q4bStackPlan *p);
 void q4b_fused_shutdown() {
+    session_end_of(nullptr);
     cudaFree(g_s_words);
     cudaFree(g_s_ctr);
     if (g_s_prof) cudaFree(g_s_prof);
@@ -872,18 +984,22 @@ static bool stack_shape_ok(const uint8_t *base, uint64_t stride, uint64_t og, ui
     return true;
 }
 
+static void session_args(const struct Q4bSession *ses, stk::Args *a);
+
 // Launches the kernel over n_layers layers (layers == NULL: the one layer l0).  Returns false,
 // with nothing enqueued, when the kernel does not apply.
 static bool stack_launch(const stk::Layer &l0, const stk::Layer *d_layers, uint32_t n_layers,
                          uint64_t stride, uint64_t og, uint64_t ou, uint64_t od, int32_t shared_slot,
                          const float *d_x, float eps, uint32_t n_expert, uint32_t topk, uint32_t n_embd,
                          uint32_t n_ff, float *d_y, int32_t *d_ids, float *d_wts, float *y_host_dev,
-                         uint32_t *flag_host_dev, uint32_t flag_val, const float *h_x_param) {
+                         uint32_t *flag_host_dev, uint32_t flag_val, const float *h_x_param,
+                         const struct Q4bSession *ses = nullptr) {
     using namespace stk;
     Q4bState &s = g_q4b;
     Args a;
     size_t smem = 0;
     if (n_layers == 0 || n_layers > MAX_LAYERS || (n_layers > 1 && !d_layers)) return false;
+    if (g_s_session && !ses) return false;   // a session's kernel is resident: nothing else can run until it ends
     if (!stack_shape_ok(l0.base, stride, og, ou, od, shared_slot, n_expert, topk, n_embd, n_ff, &a, &smem))
         return false;
     if (((uintptr_t)l0.router % 16) || (!h_x_param && ((uintptr_t)d_x % 16)) ||
@@ -917,10 +1033,19 @@ static bool stack_launch(const stk::Layer &l0, const stk::Layer *d_layers, uint3
     a.flag_host = flag_host_dev;
     a.flag_val = flag_val;
     a.poll_limit = g_s_poll_limit;
+    a.x_host = nullptr;
+    a.bell_host = nullptr;
+    a.cw = g_s_words + H + 4u * NT + (size_t)MAX_E * F;
+    a.lps = n_layers;
+    a.li0 = 0;
+    a.max_steps = 1;
+    a.idle_ns = 0;
     if (!g_s_attr_set) {
         Q4B_CHECK(cudaFuncSetAttribute(moe_decode_stack_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        227 * 1024));
         Q4B_CHECK(cudaFuncSetAttribute(moe_decode_stack_xp_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       227 * 1024));
+        Q4B_CHECK(cudaFuncSetAttribute(moe_decode_session_k, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        227 * 1024));
         g_s_attr_set = true;
     }
@@ -935,7 +1060,10 @@ static bool stack_launch(const stk::Layer &l0, const stk::Layer *d_layers, uint3
     cfg.attrs = at;
     cfg.numAttrs = 1;
     cudaError_t le;
-    if (h_x_param) {
+    if (ses) {
+        session_args(ses, &a);
+        le = cudaLaunchKernelEx(&cfg, moe_decode_session_k, a);
+    } else if (h_x_param) {
         XRow xr;   // the launch copies its parameters
         memcpy(xr.v, h_x_param, sizeof(xr.v));
         le = cudaLaunchKernelEx(&cfg, moe_decode_stack_xp_k, a, xr);
@@ -1024,9 +1152,11 @@ extern "C" void *q4_cuda_decode_stack_plan(const q4_cuda_stack_layer_t *layers, 
     g_s_plans[slot] = p;
     return p;
 }
+static void session_end_of(const Q4bStackPlan *p);   // ends the live session if it runs on p (NULL: any)
 extern "C" void q4_cuda_decode_stack_free(void *plan) {
     Q4bStackPlan *p = (Q4bStackPlan *)plan;
     if (!p) return;
+    session_end_of(p);
     for (int i = 0; i < 64; i++)
         if (g_s_plans[i] == p) g_s_plans[i] = nullptr;
     if (g_q4b.ok) {
@@ -1114,6 +1244,162 @@ extern "C" bool q4_cuda_decode_stack_host(void *plan, const float *h_x, float *h
     Q4B_CHECK(cudaMemcpyAsync(h_y, d_y, (size_t)p->n_embd * 4, cudaMemcpyDeviceToHost, s.stream));
     Q4B_CHECK(cudaStreamSynchronize(s.stream));
     return true;
+}
+
+// ---- sessions: the kernel stays resident, a step costs no launch ----
+// A decode loop that calls one MoE layer per launch pays the launch (5 us of host time, about
+// as much again on the device) and the drain of the previous kernel on every call.  A session
+// launches the stack kernel once; it then waits on a doorbell word in pinned host memory.  A
+// step: the host writes the token's row into the session's pinned row buffer and rings; CTA 0
+// reads bell and row over the bus and hands the row to the other CTAs through the exchange
+// words; the step's layers run as in any stack launch (the next step's router rows and shared
+// expert tiles were fetched while the kernel waited); the last CTA writes y and the step number
+// into pinned host memory, where the host is spinning.  While a session is live its kernel
+// holds every SM: other work queued on the device waits, and the library's other decode calls
+// answer false.  The kernel leaves by itself when told (end), after max_steps steps, or when no
+// ring came for idle_ms; the next step call then starts it again.
+struct Q4bSession {
+    Q4bStackPlan *plan;
+    uint32_t lps, max_steps, idle_ms;
+    uint32_t rung;          // steps rung since the kernel was launched
+    uint32_t pos;           // the plan's layer the next step starts with
+    bool launched;
+    float *x_h, *y_h;       // pinned, mapped
+    uint32_t *bell_h, *flag_h;
+    float *x_d, *y_hd;      // their device aliases
+    uint32_t *bell_d, *flag_d;
+    float *y_d;             // device row the CTAs write their parts of y into
+};
+
+static void session_args(const Q4bSession *ses, stk::Args *a) {
+    a->x = nullptr;
+    a->x_host = ses->x_d;
+    a->bell_host = ses->bell_d;
+    a->lps = ses->lps;
+    a->li0 = ses->pos;
+    a->max_steps = ses->max_steps;
+    a->idle_ns = (unsigned long long)ses->idle_ms * 1000000ull;
+    a->flag_val = 1u;       // step n (from 1) reports n
+}
+
+static bool session_launch(Q4bSession *ses) {
+    Q4bStackPlan *p = ses->plan;
+    *ses->bell_h = 0;
+    *ses->flag_h = 0;
+    std::atomic_thread_fence(std::memory_order_seq_cst);
+    ses->rung = 0;
+    ses->launched = stack_launch(p->first, p->d_layers, p->n_layers, p->stride, p->og, p->ou, p->od,
+                                 p->shared_slot, nullptr, p->eps, p->n_expert, p->topk, p->n_embd, p->n_ff,
+                                 ses->y_d, nullptr, nullptr, ses->y_hd, ses->flag_d, 1u, nullptr, ses);
+    return ses->launched;
+}
+
+extern "C" void *q4_cuda_decode_session_begin(void *plan, uint32_t layers_per_step, uint32_t max_steps,
+                                              uint32_t idle_ms) {
+    Q4bStackPlan *p = (Q4bStackPlan *)plan;
+    if (!g_q4b.ok || !p || g_s_session) return nullptr;
+    if (layers_per_step == 0) layers_per_step = p->n_layers;
+    if (layers_per_step > p->n_layers || layers_per_step > stk::MAX_LAYERS - 2u) return nullptr;
+    if (p->n_layers > 1 && !p->d_layers) return nullptr;
+    Q4bSession *ses = new Q4bSession{};
+    ses->plan = p;
+    ses->lps = layers_per_step;
+    ses->max_steps = max_steps == 0 || max_steps > (1u << 20) ? (1u << 20) : max_steps;
+    ses->idle_ms = idle_ms == 0 ? 2000u : (idle_ms > 10000u ? 10000u : idle_ms);
+    void *host = nullptr;
+    const size_t row = (size_t)stk::H * sizeof(float);
+    if (cudaHostAlloc(&host, 2 * row + 256, cudaHostAllocMapped) != cudaSuccess ||
+        cudaMalloc(&ses->y_d, row) != cudaSuccess) {
+        cudaGetLastError();
+        if (host) cudaFreeHost(host);
+        delete ses;
+        return nullptr;
+    }
+    ses->x_h = (float *)host;
+    ses->y_h = ses->x_h + stk::H;
+    ses->bell_h = (uint32_t *)(ses->y_h + stk::H);
+    ses->flag_h = ses->bell_h + 32;    // its own cache line
+    void *dev = nullptr;
+    if (cudaHostGetDevicePointer(&dev, host, 0) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFreeHost(host);
+        cudaFree(ses->y_d);
+        delete ses;
+        return nullptr;
+    }
+    ses->x_d = (float *)dev;
+    ses->y_hd = ses->x_d + stk::H;
+    ses->bell_d = (uint32_t *)(ses->y_hd + stk::H);
+    ses->flag_d = ses->bell_d + 32;
+    if (!session_launch(ses)) {
+        cudaFreeHost(host);
+        cudaFree(ses->y_d);
+        delete ses;
+        return nullptr;
+    }
+    g_s_session = ses;
+    return ses;
+}
+
+// Waits until the kernel has left (it does so by itself: stop bell, step limit or idle time).
+static bool session_drain(Q4bSession *ses) {
+    if (!ses->launched) return true;
+    ses->launched = false;
+    return cudaStreamSynchronize(g_q4b.stream) == cudaSuccess;
+}
+
+extern "C" bool q4_cuda_decode_session_step(void *session, const float *h_x, float *h_y) {
+    Q4bSession *ses = (Q4bSession *)session;
+    if (!g_q4b.ok || !ses || ses != g_s_session || !h_x || !h_y) return false;
+    volatile uint32_t *flag = ses->flag_h;
+    for (int attempt = 0; attempt < 2; attempt++) {
+        if (!ses->launched || ses->rung >= ses->max_steps || (*flag & stk::FLAG_EXIT)) {
+            if (!session_drain(ses) || !session_launch(ses)) return false;
+        }
+        memcpy(ses->x_h, h_x, (size_t)stk::H * sizeof(float));
+        const uint32_t n = ++ses->rung;
+        __atomic_store_n(ses->bell_h, n, __ATOMIC_RELEASE);
+        uint32_t f = 0;
+        bool done = false;
+        const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(ses->idle_ms + 3000u);
+        for (uint64_t spins = 0;; spins++) {
+            f = *flag;
+            if ((f & stk::FLAG_EXIT) || (f & 0x3fffffffu) == n) {
+                done = true;
+                break;
+            }
+            if ((spins & 0xffffu) == 0xffffu && std::chrono::steady_clock::now() > deadline) break;
+#if defined(__x86_64__)
+            __builtin_ia32_pause();
+#endif
+        }
+        std::atomic_thread_fence(std::memory_order_acquire);
+        if (!done) {                      // far beyond any step: stop the kernel and let the stream say why
+            __atomic_store_n(ses->bell_h, stk::BELL_STOP, __ATOMIC_RELEASE);
+            session_drain(ses);
+            return false;
+        }
+        if (f & stk::FLAG_EXIT) continue;   // the kernel had just left on its idle limit: start it again, once
+        memcpy(h_y, ses->y_h, (size_t)stk::H * sizeof(float));
+        ses->pos = (ses->pos + ses->lps) % ses->plan->n_layers;
+        return !(f & stk::FLAG_ERR);
+    }
+    return false;
+}
+
+static void session_end_of(const Q4bStackPlan *p) {
+    if (g_s_session && (!p || g_s_session->plan == p)) q4_cuda_decode_session_end(g_s_session);
+}
+extern "C" bool q4_cuda_decode_session_end(void *session) {
+    Q4bSession *ses = (Q4bSession *)session;
+    if (!ses || ses != g_s_session) return false;
+    __atomic_store_n(ses->bell_h, stk::BELL_STOP, __ATOMIC_RELEASE);
+    const bool ok = session_drain(ses);
+    g_s_session = nullptr;
+    cudaFreeHost(ses->x_h);
+    cudaFree(ses->y_d);
+    delete ses;
+    return ok;
 }
 
 // In-kernel phase profile of the persistent decode kernel (diagnostics).

@@ -269,3 +269,50 @@ def test_a_wait_that_runs_out_is_reported_and_the_next_call_works(dev, pkg, orac
     finally:
         lib.q4_cuda_decode_wait_limit(0)
         st.close()
+
+
+def test_session_steps_match_launches_bit_for_bit(dev, pkg):
+    """A session (the kernel stays resident, a step costs no launch) gives, step by step, what the
+    same layers give as launches: one layer per step walks the plan cyclically, all layers per step
+    is the stack call.  Also: the kernel leaving on its idle limit and on its step limit is
+    transparent to the caller, and the library works as before once the session has ended."""
+    import time
+    n_expert, topk, n_layers = 64, 6, 3
+    layers = [pkg.synth.layer(700 + l, n_expert, H, F) for l in range(n_layers)]
+    st = Stack(dev, pkg, layers, topk)
+    lib = dev.lib
+    try:
+        plan = st.plan()
+        xs = pkg.synth.hidden(71, 8, H)
+        want1 = [st.one_layer(s % n_layers, x) for s, x in enumerate(xs)]      # step s = layer s mod 3
+        wantL = [st.run(plan, x, n_layers)[0] for x in xs[:3]]
+        y = np.zeros(H, np.float32)
+
+        def step(ses, x):
+            x = np.ascontiguousarray(x, np.float32)
+            assert lib.q4_cuda_decode_session_step(ses, x.ctypes.data, y.ctypes.data)
+            return y.copy()
+        ses = lib.q4_cuda_decode_session_begin(plan, 1, 5, 150)      # at most 5 steps per launch, 150 ms idle
+        assert ses
+        assert not lib.q4_cuda_decode_session_begin(plan, 1, 0, 0), "one session at a time"
+        # while the session's kernel is resident the launching decode calls answer false
+        assert not lib.q4_cuda_decode_stack_dev(plan, st.d_x, st.d_y, None, None)
+        for s in range(8):                  # crosses the 5-step limit: the kernel is started again where it was
+            got = step(ses, xs[s])
+            assert np.array_equal(got.view(np.uint32), want1[s].view(np.uint32)), s
+        time.sleep(0.4)                     # beyond the idle limit: the kernel has left
+        got = step(ses, xs[2])              # step 8: layer 8 mod 3 = 2
+        assert np.array_equal(got.view(np.uint32), want1[2].view(np.uint32))
+        assert lib.q4_cuda_decode_session_end(ses)
+        assert lib.q4_cuda_device_error() == 0
+        ses = lib.q4_cuda_decode_session_begin(plan, 0, 0, 0)        # every layer of the plan per step
+        assert ses
+        for x, w in zip(xs[:3], wantL):
+            assert np.array_equal(step(ses, x).view(np.uint32), w.view(np.uint32))
+        lib.q4_cuda_decode_stack_free(plan)                          # ends the session that runs on the plan
+        plan = st.plan()
+        assert np.array_equal(st.run(plan, xs[0], n_layers)[0].view(np.uint32), wantL[0].view(np.uint32))
+        lib.q4_cuda_decode_stack_free(plan)
+        assert lib.q4_cuda_device_error() == 0
+    finally:
+        st.close()
