@@ -373,12 +373,13 @@ class Decode1:
                 if not p:
                     raise RuntimeError("q4_cuda_decode_plan refused")
                 self.plans.append(p)
-        run, h_x, h_y = lib.q4_cuda_decode_plan_host, self.h_x, self.h_y
+        run, h_y = lib.q4_cuda_decode_plan_host, self.h_y
+        xp = [self.x_host[i].ctypes.data for i in range(self.n_x)]      # the call copies the row itself
+        y_out, nb = self.y_out.ctypes.data, N_EMBD * 4
         for i in range(r * k, r * k + k):
-            ctypes.memmove(h_x, self.x_host[i % self.n_x].ctypes.data, N_EMBD * 4)
-            if not run(self.plans[i % m.n_layers], h_x, h_y):
+            if not run(self.plans[i % m.n_layers], xp[i % self.n_x], h_y):
                 raise RuntimeError("q4_cuda_decode_plan_host refused")
-            ctypes.memmove(self.y_out.ctypes.data, h_y, N_EMBD * 4)
+            ctypes.memmove(y_out, h_y, nb)
 
     def e2e_stack(self, r):
         """One token through all layers in one host-buffer call (row in, row out)."""

@@ -431,7 +431,7 @@ __device__ __forceinline__ void issue_down(const Args &a, const Layer &L, Small 
 
 // The kernel body; xrow is the token's hidden row as H/4 float4: device memory for the
 // device-pointer call, the kernel's own parameter block for the host-buffer call.
-template <bool SESSION>
+template <bool SESSION, bool XPARAM = false>
 __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
     // used directly (no integer round trip), so that the compiler keeps these as
     // shared-space accesses; dynamic shared memory starts on the declared alignment
@@ -470,7 +470,19 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
     float4 xv = make_float4(0.f, 0.f, 0.f, 0.f), wv = make_float4(1.f, 1.f, 1.f, 1.f);
     uint32_t code = 0;
     if (tid < H / 4) {
-        if constexpr (!SESSION) xv = xrow[tid];
+        if constexpr (XPARAM) {
+            // The row sits in the parameter block (constant bank): a warp whose lanes ask for 32
+            // different addresses is served one address at a time, each a miss of the constant
+            // cache (measured: 6 us).  So the warp reads its 32 entries one by one, every lane
+            // the same address, and lane i keeps entry i.
+#pragma unroll 8
+            for (uint32_t i = 0; i < 32; i++) {
+                const float4 t = xrow[(tid & ~31u) + i];
+                if ((tid & 31u) == i) xv = t;
+            }
+        } else if constexpr (!SESSION) {
+            xv = xrow[tid];
+        }
         if (cur.norm_w) wv = reinterpret_cast<const float4 *>(cur.norm_w)[tid];
         code = a.codes[tid];
     }
@@ -918,7 +930,7 @@ struct XRow {
     float4 v[H / 4];
 };
 __global__ void __launch_bounds__(NT, 1) moe_decode_stack_xp_k(const Args a, const __grid_constant__ XRow xr) {
-    stack_body<false>(a, xr.v);
+    stack_body<false, true>(a, xr.v);
 }
 
 }  // namespace stk
