@@ -10,8 +10,10 @@
  *
  * Conventions (same as the reference, src/q4_rocm.cu:5433-5438):
  *  - every operation returns bool: true = enqueued; false = NOTHING was enqueued
- *    (bad shape, unsupported type, library not initialised), so a caller may take
- *    another path without double-counting work;
+ *    (bad shape, unsupported type, library not initialised: all checks come before
+ *    the first launch), so a caller may take another path without double-counting
+ *    work.  The one exception is a CUDA launch error in the middle of a call that
+ *    issues several kernels: false then follows launches that already went out;
  *  - d_* pointers are device pointers owned by the caller; everything is enqueued
  *    on one library-owned stream (q4_hip_stream) and nothing synchronises unless
  *    its comment says so;
