@@ -512,6 +512,15 @@ uint32_t q4_cuda_decode_stack_layers(void *plan);
 bool q4_cuda_decode_stack_dev(void *plan, const float *d_x, float *d_y, int32_t *d_ids, float *d_wts);
 bool q4_cuda_decode_stack_host(void *plan, const float *h_x, float *h_y);
 void q4_cuda_decode_stack_free(void *plan);
+/* Optional per-plan extras.  set_sgate: the shared expert of `layer` is weighted by
+ * sigmoid(d_sgate . xn) (xn = the layer's normalised input row; src/q4_moe.c:1404-1435) instead of 1;
+ * d_sgate = n_embd floats on the device, 16-byte aligned, NULL = weight 1 again.  set_final: the
+ * plan's last layer also adds its output to the hc residual streams, d_res[c][i] += y[i] *
+ * 2 sigmoid(d_inject[c] / hc), c < hc <= 64 -- bit for bit what q4_hip_moe_final(d_res, y, 0, 0, NULL,
+ * d_inject, n_embd, hc) gives after the layer (src/q4_rocm.cu:15990-16003); d_res = NULL turns it off.
+ * Both apply to q4_cuda_decode_stack_dev / _host calls on the plan, not to sessions. */
+bool q4_cuda_decode_stack_set_sgate(void *plan, uint32_t layer, const float *d_sgate);
+bool q4_cuda_decode_stack_set_final(void *plan, float *d_res, const float *d_inject, uint32_t hc);
 /* Sessions: the stack kernel stays resident and a step costs no launch.  begin launches it on
  * the library's stream over `plan`; it then waits on a doorbell in pinned host memory.  step
  * copies the token's row (n_embd floats, any host memory) into the session's pinned buffer and
@@ -568,6 +577,15 @@ bool q4_cuda_assign_local(const int32_t *d_ids, const float *d_wts, int32_t *d_a
  * 2 = the general CUDA-core kernel only.  Returns false for an unknown mode, or for 1
  * when the tensor-core path could not be set up. */
 bool q4_cuda_mmq_tc_mode(int mode);
+/* Activation quantiser of the many-token sequence (q4_mmq_quantize, q4_cuda_mmq_swiglu_quantize,
+ * q4_cuda_moe_layer_n): 0 (default) = Q8-A, the product's own (d = amax / 127, round to nearest
+ * even: the reference's CPU path); 1 = Q8-C, ggml's q8_1 (d_inv = 127 / amax, round half away from
+ * zero, d = 1 / d_inv: what the reference's grouped device product quantises with,
+ * third_party/llama.cpp/ggml/src/ggml-cuda/quantize.cu:491-553).  q8_sections gives the device
+ * pointers of a row buffer's parts for stage tests. */
+void q4_cuda_mmq_q8_compat(int on);
+bool q4_cuda_mmq_q8_sections(const void *xq, uint64_t rows, uint64_t cols, const int8_t **q, const float **d,
+                             const int32_t **sums);
 
 /* Seeded synthetic tensors generated on the device (benchmark and smoke
  * support, no reference counterpart): n_blocks IQ3_S super-blocks with

@@ -189,6 +189,8 @@ SIGNATURES = {
     "q4_cuda_decode_stack_dev": (b, [vp, vp, vp, vp, vp]),
     "q4_cuda_decode_stack_host": (b, [vp, vp, vp]),
     "q4_cuda_decode_stack_free": (None, [vp]),
+    "q4_cuda_decode_stack_set_sgate": (b, [vp, u32, vp]),
+    "q4_cuda_decode_stack_set_final": (b, [vp, vp, vp, u32]),
     "q4_cuda_decode_session_begin": (vp, [vp, u32, u32, u32]),
     "q4_cuda_decode_session_step": (b, [vp, vp, vp]),
     "q4_cuda_decode_session_end": (b, [vp]),
@@ -200,6 +202,8 @@ SIGNATURES = {
     "q4_cuda_expert_reduce_set": (b, [vp, vp, vp, vp, u32, u32, u32]),
     "q4_cuda_assign_local": (b, [vp, vp, vp, vp, vp, vp, u32, u32, u32, u32, C.c_int, u32, u32]),
     "q4_cuda_mmq_tc_mode": (b, [C.c_int]),
+    "q4_cuda_mmq_q8_compat": (None, [C.c_int]),
+    "q4_cuda_mmq_q8_sections": (b, [vp, u64, u64, vp, vp, vp]),
     "q4_cuda_synth_iq3s": (b, [vp, u64, u64]),
     "q4_cuda_synth_iq3s_at": (b, [vp, u64, u64, u64]),
     "q4_cuda_synth_normal": (b, [vp, u64, u64, f32, f32]),

@@ -139,15 +139,14 @@ __global__ void __launch_bounds__(256) moe_final_k(float *res, const float *y, c
                                                    const float *dot, const float *inj, uint32_t n_embd,
                                                    uint32_t hc) {
     __shared__ float factor[FINAL_MAX_HC];
-    const OpSigmoid sig{};
-    for (uint32_t c = threadIdx.x; c < hc; c += blockDim.x) factor[c] = 2.f * sig(inj[c] / (float)hc, 0.f, 0.f);
+    for (uint32_t c = threadIdx.x; c < hc; c += blockDim.x) factor[c] = hc_stream_factor(inj, 0, hc, c);
     __syncthreads();
     const float gate = dot ? *dot : 1.f;
     const uint32_t step = gridDim.x * blockDim.x;
     for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < n_embd; i += step) {
         const float sum = (y[i] + hy[i]) + sh[i] * gate;
         float *stream = res + i;
-        for (uint32_t c = 0; c < hc; c++, stream += n_embd) *stream += sum * factor[c];
+        for (uint32_t c = 0; c < hc; c++, stream += n_embd) *stream = __fmaf_rn(sum, factor[c], *stream);
     }
 }
 

@@ -65,8 +65,23 @@ __host__ __device__ inline Q8View q8_view(const void *buf, uint64_t rows, uint64
     return v;
 }
 
+// The two 8-bit quantisers of activation rows.  Q8-A (the product's own; the reference's CPU path):
+// d = amax / 127, q = round-to-nearest-even(x * (127 / amax)).  Q8-C (COMPAT = true; ggml's q8_1, what
+// the reference's grouped device product quantises with, quantize.cu:491-553 of its vendored ggml):
+// d_inv = 127 / amax, q = round-half-away(x * d_inv), d = 1 / d_inv.  They differ on exact halves and
+// in the last bit of d.
+template <bool COMPAT> __device__ __forceinline__ int q8_round(float v, float sc) {
+    const float t = __fmul_rn(v, sc);
+    return max(-128, min(127, COMPAT ? (int)roundf(t) : __float2int_rn(t)));
+}
+template <bool COMPAT> __device__ __forceinline__ float q8_scale(float amax, float sc) {
+    return COMPAT ? (sc > 0.f ? __fdiv_rn(1.0f, sc) : 0.f) : __fdiv_rn(amax, 127.f);
+}
+int g_q8_compat = 0;   // q4_cuda_mmq_q8_compat
+
 // Four lanes per 32 values of one gathered row, eight values each (a negative source row
-// gives zeros).  Same arithmetic as quant8_k: d = amax / 127, q = rne(x * (127 / amax)).
+// gives zeros).
+template <bool COMPAT>
 __global__ void quantize_rows_k(const float *__restrict__ x, const int32_t *__restrict__ ids,
                                 uint64_t cols, uint64_t rows, int8_t *__restrict__ q,
                                 float *__restrict__ d, int32_t *__restrict__ bs) {
@@ -88,7 +103,7 @@ __global__ void quantize_rows_k(const float *__restrict__ x, const int32_t *__re
     a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
     a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
     const float sc = a > 0.f ? __fdiv_rn(127.f, a) : 0.f;
-    auto qz = [&](float v) { return max(-128, min(127, __float2int_rn(__fmul_rn(v, sc)))); };
+    auto qz = [&](float v) { return q8_round<COMPAT>(v, sc); };
     const int q0 = qz(v0.x), q1 = qz(v0.y), q2 = qz(v0.z), q3 = qz(v0.w);
     const int q4 = qz(v1.x), q5 = qz(v1.y), q6 = qz(v1.z), q7 = qz(v1.w);
     int sum = q0 + q1 + q2 + q3 + q4 + q5 + q6 + q7;
@@ -102,7 +117,7 @@ __global__ void quantize_rows_k(const float *__restrict__ x, const int32_t *__re
           ((uint32_t)(q7 & 0xff) << 24);
     *reinterpret_cast<uint2 *>(q + r * cols + gl * 32u + part * 8u) = o;
     if (part == 0) {
-        d[g] = __fdiv_rn(a, 127.f);
+        d[g] = q8_scale<COMPAT>(a, sc);
         bs[g] = sum;
     }
 }
@@ -223,6 +238,7 @@ __global__ void swiglu_rows_k(const float *__restrict__ gu, float *__restrict__ 
 
 // h = silu(g) * u and its Q8-A quantisation in one pass (the values swiglu_rows_k followed by
 // quantize_rows_k would give): four lanes per 32 hidden values, eight each.
+template <bool COMPAT>
 __global__ void swiglu_quant_rows_k(const float *__restrict__ gu, uint64_t rows, uint64_t n_ff,
                                     int8_t *__restrict__ q, float *__restrict__ d,
                                     int32_t *__restrict__ bs) {
@@ -253,7 +269,7 @@ __global__ void swiglu_quant_rows_k(const float *__restrict__ gu, uint64_t rows,
     int qi[8], sum = 0;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        qi[i] = max(-128, min(127, __float2int_rn(__fmul_rn(v[i], sc))));
+        qi[i] = q8_round<COMPAT>(v[i], sc);
         sum += qi[i];
     }
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
@@ -266,7 +282,7 @@ __global__ void swiglu_quant_rows_k(const float *__restrict__ gu, uint64_t rows,
           ((uint32_t)(qi[7] & 0xff) << 24);
     *reinterpret_cast<uint2 *>(q + r * n_ff + gl * 32u + part * 8u) = o;
     if (part == 0) {
-        d[g] = __fdiv_rn(a, 127.f);
+        d[g] = q8_scale<COMPAT>(a, sc);
         bs[g] = sum;
     }
 }
@@ -676,8 +692,12 @@ extern "C" bool q4_mmq_quantize(const float *x, const int32_t *ids, void *xq, ui
         return false;
     const Q8View v = q8_view(xq, rows, cols);
     const uint64_t ngr = rows * (cols / 32u);
-    quantize_rows_k<<<(unsigned)((ngr * 4 + 255) / 256), 256, 0, g_q4b.stream>>>(
-        x, ids, cols, rows, (int8_t *)v.q, (float *)v.d, (int32_t *)v.bs);
+    if (g_q8_compat)
+        quantize_rows_k<true><<<(unsigned)((ngr * 4 + 255) / 256), 256, 0, g_q4b.stream>>>(
+            x, ids, cols, rows, (int8_t *)v.q, (float *)v.d, (int32_t *)v.bs);
+    else
+        quantize_rows_k<false><<<(unsigned)((ngr * 4 + 255) / 256), 256, 0, g_q4b.stream>>>(
+            x, ids, cols, rows, (int8_t *)v.q, (float *)v.d, (int32_t *)v.bs);
     g_q4b_launches++;
     return q4b_launch_ok("quantize_rows");
 }
@@ -724,10 +744,30 @@ extern "C" bool q4_cuda_mmq_swiglu_quantize(const float *gu, void *hq, uint64_t 
     if (!g_q4b.ok || !gu || !hq || rows == 0 || n_ff == 0 || (n_ff % 32u)) return false;
     const Q8View v = q8_view(hq, rows, n_ff);
     const uint64_t ngr = rows * (n_ff / 32u);
-    swiglu_quant_rows_k<<<(unsigned)((ngr * 4 + 255) / 256), 256, 0, g_q4b.stream>>>(
-        gu, rows, n_ff, (int8_t *)v.q, (float *)v.d, (int32_t *)v.bs);
+    if (g_q8_compat)
+        swiglu_quant_rows_k<true><<<(unsigned)((ngr * 4 + 255) / 256), 256, 0, g_q4b.stream>>>(
+            gu, rows, n_ff, (int8_t *)v.q, (float *)v.d, (int32_t *)v.bs);
+    else
+        swiglu_quant_rows_k<false><<<(unsigned)((ngr * 4 + 255) / 256), 256, 0, g_q4b.stream>>>(
+            gu, rows, n_ff, (int8_t *)v.q, (float *)v.d, (int32_t *)v.bs);
     g_q4b_launches++;
     return q4b_launch_ok("swiglu_quantize");
+}
+
+// Which quantiser the row buffers of the many-token sequence are filled with (q4_mmq_quantize,
+// q4_cuda_mmq_swiglu_quantize, and through them q4_cuda_moe_layer_n): 0 = Q8-A (default), 1 = Q8-C,
+// ggml's q8_1 rounding, for bit-level comparisons with the reference's grouped device product.
+extern "C" void q4_cuda_mmq_q8_compat(int on) { g_q8_compat = on ? 1 : 0; }
+// The sections of a row buffer (device pointers into xq): int8 q [rows][cols], float d and int32
+// sums [rows][cols / 32].  For stage tests.
+extern "C" bool q4_cuda_mmq_q8_sections(const void *xq, uint64_t rows, uint64_t cols, const int8_t **q,
+                                        const float **d, const int32_t **sums) {
+    if (!xq || !rows || !cols || (cols % 32u)) return false;
+    const Q8View v = q8_view(xq, rows, cols);
+    if (q) *q = v.q;
+    if (d) *d = v.d;
+    if (sums) *sums = v.bs;
+    return true;
 }
 
 extern "C" bool q4_hip_route_pf(const float *d_rlog, int32_t *d_ids, float *d_wts, uint32_t n_tok,

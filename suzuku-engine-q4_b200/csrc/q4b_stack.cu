@@ -76,6 +76,7 @@ struct Layer {
     const uint8_t *base;      // slot 0 of this layer's experts
     const float *norm_w;      // may be NULL
     const float *router;      // [n_expert][H]
+    const float *sgate;       // [H] or NULL: the shared expert's weight is sigmoid(sgate . xn) instead of 1
 };
 
 struct Args {
@@ -102,6 +103,11 @@ struct Args {
     volatile uint32_t *flag_host; // host-mapped word that receives flag_val (bit 31: error word was set)
     uint32_t flag_val;
     uint32_t poll_limit;
+    // optional epilogue of the last layer (src/q4_rocm.cu:15990-16003, moe_final): besides y, the
+    // hc residual streams res[c][.] += y * 2 sigmoid(inject[c] / hc)
+    float *res;
+    const float *inject;
+    uint32_t hc;
     // session form (moe_decode_session_k): the kernel stays resident and serves one step per ring
     // of a doorbell in host memory; a step runs lps consecutive layers of the plan (cyclically)
     const float *x_host;          // host-mapped input row [H] of the step
@@ -239,6 +245,7 @@ __device__ __forceinline__ uint32_t quant8_oct(float4 v, float *d_out, int *bs_o
 struct Small {
     uint32_t last;   // 1 in the CTA that finished last (host hand-off)
     uint32_t cmd;    // session: this step's command
+    float fac[64];   // epilogue: the streams' factors
     uint32_t ep0;    // epoch of layer 0 of this launch
     uint64_t mbar[N_MBAR];
     alignas(16) float xn[H];            // normalised x (router input)
@@ -490,6 +497,7 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         for (uint32_t i = 0; i < N_MBAR; i++) mbar_init(&S.mbar[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    if (a.res && tid >= 64 && tid - 64 < a.hc) S.fac[tid - 64] = hc_stream_factor(a.inject, 0, a.hc, tid - 64);
     if (tid < MAX_E) {   // entry topk of the expert list is the shared expert, in every layer
         S.ids[tid] = (has_sh && tid == a.topk) ? a.shared_slot : 0;
         S.wts[tid] = 1.0f;
@@ -653,6 +661,24 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
             // this layer; a CTA reaches this line for the next layer only after all CTAs published
             // this layer's y, i.e. after they all finished reading these words
             if (lane == 0) xw_store(a.lw + 4u * logit_pos(r0 + rl, nwe) + part, acc, ep);
+        }
+        // the shared expert's gate (src/q4_moe.c:1404-1435, sgate): its weight in this layer's sum.
+        // On a warp that has a router task only; read in phase 3, block barriers lie between.
+        if (has_sh && warp == 4) {
+            float g = 1.0f;
+            if (cur.sgate) {
+                const float4 *g4 = reinterpret_cast<const float4 *>(cur.sgate);
+                const float4 *x4 = reinterpret_cast<const float4 *>(S.xn);
+                float acc = 0.f;
+#pragma unroll 4
+                for (uint32_t i = lane; i < H / 4; i += 32) {
+                    const float4 gw = __ldg(g4 + i), gx = x4[i];
+                    acc += gw.x * gx.x + gw.y * gx.y + gw.z * gx.z + gw.w * gx.w;
+                }
+                acc = q4b_warp_sum(acc);
+                g = 1.f / (1.f + expf(-acc));
+            }
+            if (lane == 0) S.wts[a.topk] = g;
         }
         stamp(a, prof, 3);
 
@@ -866,10 +892,14 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
             // the layer's output row: written here, read by every CTA at the top of the next
             // layer; a CTA reaches this line for the next layer only after all CTAs published
             // that layer's hidden values, i.e. after they all read these words
-            if (!out)
+            if (!out) {
                 xw_store(a.xw + r, sum, ep);
-            else
+            } else {
                 a.y[r] = sum;
+                if (a.res)
+                    for (uint32_t c = 0; c < a.hc; c++)
+                        a.res[(size_t)c * H + r] = __fmaf_rn(sum, S.fac[c], a.res[(size_t)c * H + r]);
+            }
         }
         stamp(a, prof, 12);
         if (!out && tid < H / 4) xv = xw_poll4(a.xw + 4u * tid, ep, limit, a.err);
@@ -997,6 +1027,7 @@ static bool stack_shape_ok(const uint8_t *base, uint64_t stride, uint64_t og, ui
 }
 
 static void session_args(const struct Q4bSession *ses, stk::Args *a);
+static void plan_args(const struct Q4bStackPlan *pl, stk::Args *a);
 
 // Launches the kernel over n_layers layers (layers == NULL: the one layer l0).  Returns false,
 // with nothing enqueued, when the kernel does not apply.
@@ -1005,7 +1036,7 @@ static bool stack_launch(const stk::Layer &l0, const stk::Layer *d_layers, uint3
                          const float *d_x, float eps, uint32_t n_expert, uint32_t topk, uint32_t n_embd,
                          uint32_t n_ff, float *d_y, int32_t *d_ids, float *d_wts, float *y_host_dev,
                          uint32_t *flag_host_dev, uint32_t flag_val, const float *h_x_param,
-                         const struct Q4bSession *ses = nullptr) {
+                         const struct Q4bSession *ses = nullptr, const struct Q4bStackPlan *pl = nullptr) {
     using namespace stk;
     Q4bState &s = g_q4b;
     Args a;
@@ -1015,7 +1046,7 @@ static bool stack_launch(const stk::Layer &l0, const stk::Layer *d_layers, uint3
     if (!stack_shape_ok(l0.base, stride, og, ou, od, shared_slot, n_expert, topk, n_embd, n_ff, &a, &smem))
         return false;
     if (((uintptr_t)l0.router % 16) || (!h_x_param && ((uintptr_t)d_x % 16)) ||
-        (l0.norm_w && ((uintptr_t)l0.norm_w % 16)) || ((uintptr_t)d_y % 16))
+        (l0.norm_w && ((uintptr_t)l0.norm_w % 16)) || ((uintptr_t)d_y % 16) || ((uintptr_t)l0.sgate % 16))
         return false;
     if (!stack_scratch()) return false;
     a.l0 = l0;
@@ -1045,6 +1076,10 @@ static bool stack_launch(const stk::Layer &l0, const stk::Layer *d_layers, uint3
     a.flag_host = flag_host_dev;
     a.flag_val = flag_val;
     a.poll_limit = g_s_poll_limit;
+    a.res = nullptr;
+    a.inject = nullptr;
+    a.hc = 0;
+    if (pl) plan_args(pl, &a);
     a.x_host = nullptr;
     a.bell_host = nullptr;
     a.cw = g_s_words + H + 4u * NT + (size_t)MAX_E * F;
@@ -1098,7 +1133,7 @@ bool q4b_moe_decode_fused(const uint8_t *base, uint64_t stride, uint64_t og, uin
                           uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
                           float *d_y, int32_t *d_ids, float *d_wts, float *y_host_dev,
                           uint32_t *flag_host_dev, uint32_t flag_val, const float *h_x_param) {
-    const stk::Layer l0 = {base, d_norm_w, d_router};
+    const stk::Layer l0 = {base, d_norm_w, d_router, nullptr};
     return stack_launch(l0, nullptr, 1, stride, og, ou, od, shared_slot, d_x, eps, n_expert, topk, n_embd,
                         n_ff, d_y, d_ids, d_wts, y_host_dev, flag_host_dev, flag_val, h_x_param);
 }
@@ -1114,7 +1149,15 @@ struct Q4bStackPlan {
     uint32_t n_expert, topk, n_embd, n_ff;
     float *y_alias;        // device alias of the host result buffer last used with _host
     const void *y_alias_of;
+    float *res;            // optional epilogue (q4_cuda_decode_stack_set_final)
+    const float *inject;
+    uint32_t hc;
 };
+static void plan_args(const Q4bStackPlan *pl, stk::Args *a) {
+    a->res = pl->res;
+    a->inject = pl->inject;
+    a->hc = pl->hc;
+}
 static Q4bStackPlan *g_s_plans[64] = {};   // live plans (their cached aliases die with host_free)
 
 extern "C" void *q4_cuda_decode_stack_plan(const q4_cuda_stack_layer_t *layers, uint32_t n_layers,
@@ -1140,7 +1183,8 @@ extern "C" void *q4_cuda_decode_stack_plan(const q4_cuda_stack_layer_t *layers, 
         }
     if (slot < 0) return nullptr;
     stk::Layer host[stk::MAX_LAYERS];
-    for (uint32_t l = 0; l < n_layers; l++) host[l] = stk::Layer{layers[l].base, layers[l].d_norm_w, layers[l].d_router};
+    for (uint32_t l = 0; l < n_layers; l++)
+        host[l] = stk::Layer{layers[l].base, layers[l].d_norm_w, layers[l].d_router, nullptr};
     Q4bStackPlan *p = new Q4bStackPlan{};
     if (cudaMalloc(&p->d_layers, n_layers * sizeof(stk::Layer)) != cudaSuccess ||
         cudaMemcpy(p->d_layers, host, n_layers * sizeof(stk::Layer), cudaMemcpyHostToDevice) != cudaSuccess) {
@@ -1186,7 +1230,29 @@ extern "C" bool q4_cuda_decode_stack_dev(void *plan, const float *d_x, float *d_
     if (!g_q4b.ok || !p || !d_x || !d_y) return false;
     return stack_launch(p->first, p->d_layers, p->n_layers, p->stride, p->og, p->ou, p->od, p->shared_slot,
                         d_x, p->eps, p->n_expert, p->topk, p->n_embd, p->n_ff, d_y, d_ids, d_wts, nullptr,
-                        nullptr, 0, nullptr);
+                        nullptr, 0, nullptr, nullptr, p);
+}
+// The shared expert's gate vector of one layer of the plan ([n_embd] floats on the device, 16-byte
+// aligned; NULL: weight 1).  Waits for the stream: the layer table is rewritten in place.
+extern "C" bool q4_cuda_decode_stack_set_sgate(void *plan, uint32_t layer, const float *d_sgate) {
+    Q4bStackPlan *p = (Q4bStackPlan *)plan;
+    if (!g_q4b.ok || !p || layer >= p->n_layers || ((uintptr_t)d_sgate % 16) || p->shared_slot < 0) return false;
+    if (g_s_session) return false;
+    Q4B_CHECK(cudaStreamSynchronize(g_q4b.stream));
+    Q4B_CHECK(cudaMemcpy(reinterpret_cast<uint8_t *>(p->d_layers + layer) + offsetof(stk::Layer, sgate), &d_sgate,
+                         sizeof d_sgate, cudaMemcpyHostToDevice));
+    if (layer == 0) p->first.sgate = d_sgate;
+    return true;
+}
+// Epilogue of the plan's last layer: besides y, d_res[c][i] += y[i] * 2 sigmoid(d_inject[c] / hc) for
+// the hc residual streams (what q4_hip_moe_final does with y after the layer); d_res == NULL: off.
+extern "C" bool q4_cuda_decode_stack_set_final(void *plan, float *d_res, const float *d_inject, uint32_t hc) {
+    Q4bStackPlan *p = (Q4bStackPlan *)plan;
+    if (!p || (d_res && (!d_inject || hc == 0 || hc > 64))) return false;
+    p->res = d_res;
+    p->inject = d_res ? d_inject : nullptr;
+    p->hc = d_res ? hc : 0;
+    return true;
 }
 
 // Device alias of a mapped, page-locked host buffer (NULL when it is anything else).
@@ -1247,7 +1313,7 @@ extern "C" bool q4_cuda_decode_stack_host(void *plan, const float *h_x, float *h
             const uint32_t epoch = q4b_next_flag_epoch();
             if (stack_launch(p->first, p->d_layers, p->n_layers, p->stride, p->og, p->ou, p->od, p->shared_slot,
                              d_x, p->eps, p->n_expert, p->topk, p->n_embd, p->n_ff, d_y, nullptr, nullptr,
-                             p->y_alias, s.flag_d, epoch, h_x))
+                             p->y_alias, s.flag_d, epoch, h_x, nullptr, p))
                 return q4b_wait_flag(epoch);
         }
     }

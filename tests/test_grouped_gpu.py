@@ -384,3 +384,51 @@ def test_tensor_core_product_with_an_outlier_channel(dev, pkg, oracle):
     finally:
         lib.q4_cuda_mmq_tc_mode(-1)
         layer.close()
+
+
+def test_q8_compat_quantiser_is_ggml_q8_1(dev, pkg, oracle):
+    """q4_cuda_mmq_q8_compat(1): the row buffers are filled with ggml's q8_1 rounding (what the
+    reference's grouped device product uses, restated as q4o_quant8_mmq) instead of Q8-A: q and d bit for
+    bit, on rows with exact halves planted; the grouped product on those rows against the oracle's
+    dot in the grouped order."""
+    import ctypes as C
+    lib = dev.lib
+    rng = np.random.default_rng(33)
+    rows, K, R = 6, 512, 64
+    x = rng.standard_normal((rows, K)).astype(np.float32)
+    x[0, :32] = 0.0
+    x[1, 32:64] = np.array([127.0, 0.5, -0.5, 2.5, -2.5, 1.5] + [0.25] * 26, np.float32)   # d_inv = 1: halves
+    w = pkg.synth.iq3s_blocks(rng, R * K // 256).reshape(R, -1)
+    d_x = dev.upload(x)
+    d_xq = dev.malloc(lib.q4_mmq_q8_bytes(rows, K))
+    d_dst = dev.malloc(rows * R * 4)
+    bounds = dev.upload(np.array([0, rows], np.int32))
+    got = {}
+    try:
+        for mode in (1, 0):
+            lib.q4_cuda_mmq_q8_compat(mode)
+            assert lib.q4_mmq_quantize(d_x, None, d_xq, IQ3_S, K, rows)
+            pq, pd, ps = C.c_void_p(), C.c_void_p(), C.c_void_p()
+            assert lib.q4_cuda_mmq_q8_sections(d_xq, rows, K, C.byref(pq), C.byref(pd), C.byref(ps))
+            q = dev.download(pq.value, (rows, K), np.int8)
+            d = dev.download(pd.value, (rows, K // 32), np.float32)
+            s = dev.download(ps.value, (rows, K // 32), np.int32)
+            assert np.array_equal(s, q.astype(np.int32).reshape(rows, K // 32, 32).sum(2))
+            assert lib.q4_cuda_mmq_tc_mode(0)
+            assert lib.q4_mmq_mul_id(dev.upload(w), IQ3_S, R, K, 0, 1, d_xq, bounds, rows, rows, d_dst, R)
+            got[mode] = (q, d, dev.download(d_dst, (rows, R), np.float32))
+    finally:
+        lib.q4_cuda_mmq_q8_compat(0)
+        lib.q4_cuda_mmq_tc_mode(-1)
+    qc, dc, yc = got[1]
+    qa, da, _ = got[0]
+    for r in range(rows):
+        q0, d0 = oracle.quant8_mmq(x[r])
+        assert np.array_equal(qc[r], q0) and np.array_equal(dc[r].view(np.uint32), d0.view(np.uint32)), r
+        xa = oracle.quant8(x[r])
+        assert np.array_equal(qa[r], xa["q"].ravel()) and np.array_equal(da[r].view(np.uint32), xa["d"].view(np.uint32))
+        want = np.array([oracle.dot_mmq(w[i], q0, d0, K) for i in range(R)], np.float64)
+        assert np.linalg.norm(yc[r] - want) / np.linalg.norm(want) < 1e-5, r
+    assert qc[1, 33] == 1 and qa[1, 33] == 0 and qc[1, 34] == -1 and qa[1, 34] == 0      # 0.5: away / to even
+    assert qc[1, 35] == 3 and qa[1, 35] == 2 and qc[1, 37] == 2 and qa[1, 37] == 2      # 2.5, 1.5
+    assert not qc[0, :32].any() and dc[0, 0] == 0

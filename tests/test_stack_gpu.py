@@ -316,3 +316,53 @@ def test_session_steps_match_launches_bit_for_bit(dev, pkg):
         assert lib.q4_cuda_device_error() == 0
     finally:
         st.close()
+
+
+def test_shared_expert_gate_and_stream_epilogue(dev, pkg, oracle):
+    """The two optional extras of a plan.  set_sgate: the shared expert enters with weight
+    sigmoid(sgate . xn) (src/q4_moe.c:1404-1435) -- against the oracle's routed sum plus the gated
+    shared expert.  set_final: the last layer also updates the hc residual streams -- bit for bit
+    what q4_hip_moe_final does with the layer's y (src/q4_rocm.cu:15990-16003)."""
+    n_expert, topk, hc = 64, 6, 4
+    L = pkg.synth.layer(900, n_expert, H, F)
+    st = Stack(dev, pkg, [L], topk)
+    lib = dev.lib
+    rng = np.random.default_rng(91)
+    try:
+        plan = st.plan()
+        x = pkg.synth.hidden(92, 1, H)[0]
+        y_plain = st.run(plan, x, 1)[0]
+        sg = (rng.standard_normal(H) * 0.05).astype(np.float32)
+        assert lib.q4_cuda_decode_stack_set_sgate(plan, 0, dev.upload(sg))
+        assert not lib.q4_cuda_decode_stack_set_sgate(plan, 1, None)
+        y_g = st.run(plan, x, 1)[0]
+        y_routed, ids, wts, xn = oracle.moe_layer(x, L["norm_w"], 1e-6, L["router"], topk, L["experts"], None, H, F)
+        gate = 1.0 / (1.0 + np.exp(-float(np.dot(sg.astype(np.float64), xn.astype(np.float64)))))
+        assert 0.02 < gate < 0.98
+        want = y_routed + oracle.expert_job([L["shared"]], [np.float32(gate)], xn, H, F)
+        assert _rel(y_g, want) <= REL_TOL
+        assert _rel(y_g, y_plain) > 1e-2, "the gate must have changed the result"
+        assert lib.q4_cuda_decode_stack_set_sgate(plan, 0, None)
+        assert np.array_equal(st.run(plan, x, 1)[0].view(np.uint32), y_plain.view(np.uint32))
+        # the stream epilogue
+        res0 = rng.standard_normal((hc, H)).astype(np.float32)
+        inj = rng.standard_normal(hc).astype(np.float32)
+        zeros = dev.upload(np.zeros(H, np.float32))
+        d_inj = dev.upload(inj)
+        d_res_a, d_res_b = dev.upload(res0), dev.upload(res0)
+        assert lib.q4_hip_moe_final(d_res_a, st.d_y, zeros, zeros, None, d_inj, H, hc)   # st.d_y holds y_plain
+        assert lib.q4_cuda_decode_stack_set_final(plan, d_res_b, d_inj, hc)
+        assert not lib.q4_cuda_decode_stack_set_final(plan, d_res_b, d_inj, 65)
+        y2 = st.run(plan, x, 1)[0]
+        assert np.array_equal(y2.view(np.uint32), y_plain.view(np.uint32))
+        ra, rb = dev.download(d_res_a, (hc, H), np.float32), dev.download(d_res_b, (hc, H), np.float32)
+        assert np.array_equal(ra.view(np.uint32), rb.view(np.uint32))
+        f = 2.0 / (1.0 + np.exp(-inj.astype(np.float64) / hc))
+        assert np.abs(rb - (res0 + y_plain[None, :] * f[:, None])).max() <= 1e-5 * np.abs(rb).max()
+        assert lib.q4_cuda_decode_stack_set_final(plan, None, None, 0)
+        st.run(plan, x, 1)
+        assert np.array_equal(dev.download(d_res_b, (hc, H), np.float32).view(np.uint32), rb.view(np.uint32))
+        lib.q4_cuda_decode_stack_free(plan)
+        assert lib.q4_cuda_device_error() == 0
+    finally:
+        st.close()
