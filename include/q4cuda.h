@@ -428,6 +428,14 @@ bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64_t og, uint
                          uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
                          uint32_t n_tok, float *d_y, int32_t *d_ids, float *d_wts, void *d_ws,
                          uint64_t ws_bytes);
+/* The same with the experts' formats named: gate and up of type gt, down of type dt, each IQ3_S (21),
+ * IQ4_NL (20) or IQ4_XS (23); a pack with a part that is not IQ3_S sits in an arena in the engine's byte
+ * order.  Workspace size as for q4_cuda_moe_layer_n. */
+bool q4_cuda_moe_layer_nt(const uint8_t *base, uint64_t stride, uint32_t gt, uint64_t og, uint64_t ou,
+                          uint32_t dt, uint64_t od, int32_t shared_slot, const float *d_x,
+                          const float *d_norm_w, float eps, const float *d_router, uint32_t n_expert,
+                          uint32_t topk, uint32_t n_embd, uint32_t n_ff, uint32_t n_tok, float *d_y,
+                          int32_t *d_ids, float *d_wts, void *d_ws, uint64_t ws_bytes);
 
 /* Routed experts for one token without any allocation on the call path.  It has no
  * counterpart in the reference: it exists for hosts that cannot call cudaMalloc by the

@@ -172,6 +172,8 @@ SIGNATURES = {
     "q4_cuda_moe_layer_n_ws_bytes": (u64, [u32, u32, u32, u32, u32]),
     "q4_cuda_moe_layer_n": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32, u32,
                                 u32, vp, vp, vp, vp, u64]),
+    "q4_cuda_moe_layer_nt": (b, [vp, u64, u32, u64, u64, u32, u64, i32, vp, vp, f32, vp, u32, u32, u32, u32,
+                                 u32, vp, vp, vp, vp, u64]),
     "q4_cuda_moe_exec_noalloc": (b, [vp, u64, vp, vp, u32, u64, u64, u64, vp, vp, vp, u32, u32, u32,
                                      vp]),
     "q4_cuda_set_tiled_default": (None, [C.c_int]),

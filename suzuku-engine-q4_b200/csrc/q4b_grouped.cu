@@ -542,6 +542,89 @@ __global__ void __launch_bounds__(512) win_assign_k(
     }
 }
 
+// The grouped product for IQ4_NL / IQ4_XS weights (type T; arenas in the engine's byte order): one
+// warp per weight row of an entry.  A lane owns the row's 32-groups lane, lane + 32, ... (at most
+// four: rows up to 4096 wide), turns their 4-bit codes into table values once, and dots them with
+// every activation row of the entry; a row's 32 lane sums are added by the butterfly.  Integer parts
+// exact (codes x int8 by dp4a); the result is the sum over groups of (d * dx) * (I * ls).
+template <uint32_t T>
+__global__ void __launch_bounds__(256) grouped_rows4_k(const uint8_t *__restrict__ w, uint64_t expert_stride,
+                                                       const int32_t *__restrict__ act,
+                                                       const uint32_t *__restrict__ n_act,
+                                                       const int32_t *__restrict__ bounds, Q8View xq, uint32_t cols,
+                                                       uint32_t w_rows, float *__restrict__ dst, uint64_t ld_dst) {
+    __shared__ uint16_t pair[256];
+    iq4_fill_pair_table(pair);
+    __syncthreads();
+    const uint32_t entry = blockIdx.y;
+    if (n_act && entry >= *n_act) return;
+    const int32_t r0 = bounds[entry], r1 = bounds[entry + 1];
+    const uint32_t wrow = blockIdx.x * 8u + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (r1 <= r0 || wrow >= w_rows) return;
+    const uint32_t ng = cols >> 5;
+    const uint8_t *row = w + (uint64_t)(act ? act[entry] : (int32_t)entry) * expert_stride +
+                         (uint64_t)wrow * iq4_row_bytes(T, cols);
+    constexpr uint32_t GPL = 4;          // groups per lane
+    uint32_t wv[GPL][8];                 // table values: words 0..3 = weights 0..15, 4..7 = weights 16..31
+    float dl[GPL];                       // d * ls of the group
+#pragma unroll
+    for (uint32_t k = 0; k < GPL; k++) {
+        const uint32_t g = lane + 32u * k;
+        dl[k] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) wv[k][i] = 0u;
+        if (g < ng) {
+            int lsf;
+            float d;
+            const uint8_t *codes = iq4_group<T>(row, g, &lsf, &d);
+            dl[k] = __fmul_rn(d, (float)lsf);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t c01 = q4b_ld_u16(codes + 4 * i), c23 = q4b_ld_u16(codes + 4 * i + 2);
+                const uint32_t p0 = pair[c01 & 0xffu], p1 = pair[c01 >> 8], p2 = pair[c23 & 0xffu], p3 = pair[c23 >> 8];
+                wv[k][i] = (p0 & 0xffu) | ((p1 & 0xffu) << 8) | ((p2 & 0xffu) << 16) | ((p3 & 0xffu) << 24);
+                wv[k][4 + i] = (p0 >> 8) | ((p1 >> 8) << 8) | ((p2 >> 8) << 16) | ((p3 >> 8) << 24);
+            }
+        }
+    }
+    for (int32_t r = r0; r < r1; r++) {
+        float acc = 0.f;
+#pragma unroll
+        for (uint32_t k = 0; k < GPL; k++) {
+            const uint32_t g = lane + 32u * k;
+            if (g < ng) {
+                const int4 *qp = reinterpret_cast<const int4 *>(xq.q + (uint64_t)r * cols + g * 32u);
+                const int4 q0 = __ldg(qp), q1 = __ldg(qp + 1);
+                int I = __dp4a((int)wv[k][0], q0.x, 0);
+                I = __dp4a((int)wv[k][1], q0.y, I);
+                I = __dp4a((int)wv[k][2], q0.z, I);
+                I = __dp4a((int)wv[k][3], q0.w, I);
+                I = __dp4a((int)wv[k][4], q1.x, I);
+                I = __dp4a((int)wv[k][5], q1.y, I);
+                I = __dp4a((int)wv[k][6], q1.z, I);
+                I = __dp4a((int)wv[k][7], q1.w, I);
+                acc = fmaf(__fmul_rn(dl[k], __ldg(xq.d + (uint64_t)r * ng + g)), (float)I, acc);
+            }
+        }
+        acc = q4b_warp_sum(acc);
+        if (lane == 0) dst[(uint64_t)r * ld_dst + wrow] = acc;
+    }
+}
+
+bool launch_grouped4(uint32_t type, const uint8_t *w, uint64_t expert_stride, const int32_t *act,
+                     const uint32_t *n_act, uint32_t n_entries, const int32_t *bounds, Q8View xq, uint32_t cols,
+                     uint32_t w_rows, float *dst, uint64_t ld_dst) {
+    const dim3 grid((w_rows + 7u) / 8u, n_entries);
+    if (type == Q4_T_IQ4_NL)
+        grouped_rows4_k<Q4_T_IQ4_NL><<<grid, 256, 0, g_q4b.stream>>>(w, expert_stride, act, n_act, bounds, xq, cols,
+                                                                    w_rows, dst, ld_dst);
+    else
+        grouped_rows4_k<Q4_T_IQ4_XS><<<grid, 256, 0, g_q4b.stream>>>(w, expert_stride, act, n_act, bounds, xq, cols,
+                                                                    w_rows, dst, ld_dst);
+    g_q4b_launches++;
+    return q4b_launch_ok("grouped_rows4");
+}
+
 bool launch_grouped(const uint8_t *w, uint64_t expert_stride, const int32_t *act,
                     const uint32_t *n_act, uint32_t n_entries, const int32_t *bounds, Q8View xq,
                     uint32_t cols, uint32_t w_rows, float *dst, uint64_t ld_dst) {
@@ -582,7 +665,10 @@ constexpr uint32_t TC_MIN_ROWS = 12;
 bool launch_grouped_any(const uint8_t *w, uint64_t expert_stride, const int32_t *act,
                         const uint32_t *n_act, uint32_t n_entries, const int32_t *bounds, Q8View xq,
                         uint64_t total_rows, uint32_t cols, uint32_t w_rows, float *dst,
-                        uint64_t ld_dst, uint64_t max_rows_hint) {
+                        uint64_t ld_dst, uint64_t max_rows_hint, uint32_t type = Q4_T_IQ3_S) {
+    if (type != Q4_T_IQ3_S)   // IQ4_NL / IQ4_XS: one CUDA-core kernel, engine byte order only
+        return !q4b_ptr_tiled(w) &&
+               launch_grouped4(type, w, expert_stride, act, n_act, n_entries, bounds, xq, cols, w_rows, dst, ld_dst);
     // max_rows_hint: the caller's bound on the rows of its largest entry (0 = unknown).  When
     // it says no entry reaches the tensor-core threshold that kernel is not launched at all;
     // should an entry exceed the hint anyway, the streaming kernel still takes it.
@@ -644,12 +730,18 @@ bool launch_grouped_any(const uint8_t *w, uint64_t expert_stride, const int32_t 
     return launch_grouped(w, expert_stride, act, n_act, n_entries, bounds, xq, cols, w_rows, dst, ld_dst);
 }
 
+// bytes of one weight row of a type the grouped products take
+uint64_t row_bytes_t(uint32_t type, uint64_t cols) {
+    return type == Q4_T_IQ3_S ? (cols / 256u) * Q4B_IQ3S_BYTES : iq4_row_bytes(type, cols);
+}
 bool pow2_blocks(uint64_t w_cols) {
     const uint64_t B = w_cols / 256u;
     return B == 1 || B == 2 || B == 4 || B == 8;
 }
 
 bool shape_ok(uint32_t type, uint64_t w_rows, uint64_t w_cols) {
+    if (type == Q4_T_IQ4_NL || type == Q4_T_IQ4_XS)
+        return w_rows != 0 && w_cols != 0 && w_cols <= 4096u && (w_cols % (type == Q4_T_IQ4_NL ? 32u : 256u)) == 0;
     if (type != Q4_T_IQ3_S || w_rows == 0 || w_cols == 0 || (w_cols % 256u)) return false;
     const uint64_t B = w_cols / 256u;
     return ((w_rows * B) % 8u) == 0;
@@ -678,7 +770,9 @@ extern "C" bool q4_cuda_mmq_tc_mode(int mode) {
 extern "C" int q4_mmq_on(void) { return g_q4b.ok ? 1 : 0; }
 extern "C" uint32_t q4_mmq_group(void) { return 4096u; }
 extern "C" bool q4_mmq_supported(uint32_t type, uint64_t w_rows) {
-    return g_q4b.ok && type == Q4_T_IQ3_S && w_rows != 0 && (w_rows % 8u) == 0;
+    if (!g_q4b.ok || w_rows == 0) return false;
+    if (type == Q4_T_IQ4_NL || type == Q4_T_IQ4_XS) return true;   // weights in the engine's byte order
+    return type == Q4_T_IQ3_S && (w_rows % 8u) == 0;
 }
 extern "C" uint64_t q4_mmq_q8_bytes(uint64_t rows, uint64_t cols) { return q8_bytes(rows, cols); }
 extern "C" uint64_t q4_mmq_pad(uint64_t row_bytes) {
@@ -688,8 +782,8 @@ extern "C" uint64_t q4_mmq_pad(uint64_t row_bytes) {
 
 extern "C" bool q4_mmq_quantize(const float *x, const int32_t *ids, void *xq, uint32_t w_type,
                                 uint64_t cols, uint64_t rows) {
-    if (!g_q4b.ok || !x || !xq || w_type != Q4_T_IQ3_S || rows == 0 || cols == 0 || (cols % 32u))
-        return false;
+    if (!g_q4b.ok || !x || !xq || rows == 0 || cols == 0 || (cols % 32u)) return false;
+    if (w_type != Q4_T_IQ3_S && w_type != Q4_T_IQ4_NL && w_type != Q4_T_IQ4_XS) return false;
     const Q8View v = q8_view(xq, rows, cols);
     const uint64_t ngr = rows * (cols / 32u);
     if (g_q8_compat)
@@ -708,12 +802,13 @@ extern "C" bool q4_mmq_mul_id(const void *w, uint32_t type, uint64_t w_rows, uin
                               float *dst, uint64_t ld_dst) {
     if (!g_q4b.ok || !w || !xq || !bounds || !dst || n_expert == 0 || total_rows == 0) return false;
     if (!grouped::shape_ok(type, w_rows, w_cols) || ld_dst < w_rows) return false;
-    if (!grouped::pow2_blocks(w_cols) &&
+    if (type != Q4_T_IQ3_S && q4b_ptr_tiled(w)) return false;
+    if (type == Q4_T_IQ3_S && !grouped::pow2_blocks(w_cols) &&
         cudaMemsetAsync(dst, 0, total_rows * ld_dst * sizeof(float), g_q4b.stream) != cudaSuccess)
         return false;
     return launch_grouped_any((const uint8_t *)w, expert_stride_bytes, nullptr, nullptr, n_expert, bounds,
                               q8_view(xq, total_rows, w_cols), total_rows, (uint32_t)w_cols,
-                              (uint32_t)w_rows, dst, ld_dst, max_rows);
+                              (uint32_t)w_rows, dst, ld_dst, max_rows, type);
 }
 
 extern "C" bool q4_mmq_swiglu(const float *gu, float *h, uint64_t rows, uint64_t n_ff) {
@@ -881,11 +976,23 @@ extern "C" bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64
                                     uint32_t n_expert, uint32_t topk, uint32_t n_embd,
                                     uint32_t n_ff, uint32_t n_tok, float *d_y, int32_t *d_ids,
                                     float *d_wts, void *d_ws, uint64_t ws_bytes) {
+    return q4_cuda_moe_layer_nt(base, stride, Q4_T_IQ3_S, og, ou, Q4_T_IQ3_S, od, shared_slot, d_x, d_norm_w, eps,
+                                d_router, n_expert, topk, n_embd, n_ff, n_tok, d_y, d_ids, d_wts, d_ws, ws_bytes);
+}
+
+// The same with the experts' formats named: gate and up of type gt, down of type dt, each IQ3_S,
+// IQ4_NL or IQ4_XS (a pack with a part that is not IQ3_S sits in an arena in the engine's byte order).
+extern "C" bool q4_cuda_moe_layer_nt(const uint8_t *base, uint64_t stride, uint32_t gt, uint64_t og, uint64_t ou,
+                                     uint32_t dt, uint64_t od, int32_t shared_slot, const float *d_x,
+                                     const float *d_norm_w, float eps, const float *d_router,
+                                     uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
+                                     uint32_t n_tok, float *d_y, int32_t *d_ids, float *d_wts, void *d_ws,
+                                     uint64_t ws_bytes) {
     if (!g_q4b.ok || !base || !d_x || !d_router || !d_y || !d_ws || n_tok == 0) return false;
     if (n_expert == 0 || n_expert >= 1024u || topk == 0 || topk > 63u || topk > n_expert) return false;
-    if (!grouped::shape_ok(Q4_T_IQ3_S, 2ull * n_ff, n_embd) || !grouped::shape_ok(Q4_T_IQ3_S, n_embd, n_ff))
-        return false;
-    if (ou != og + (uint64_t)n_ff * (n_embd / 256u) * Q4B_IQ3S_BYTES) return false;  // gate|up contiguous
+    if (!grouped::shape_ok(gt, 2ull * n_ff, n_embd) || !grouped::shape_ok(dt, n_embd, n_ff)) return false;
+    if ((gt != Q4_T_IQ3_S || dt != Q4_T_IQ3_S) && q4b_ptr_tiled(base)) return false;
+    if (ou != og + (uint64_t)n_ff * grouped::row_bytes_t(gt, n_embd)) return false;  // gate|up contiguous
     if (shared_slot >= 0 && (uint32_t)shared_slot != n_expert) return false;  // shared = slot n_expert
     const LayerWs w = carve((uint8_t *)d_ws, n_tok, topk, n_expert, n_embd, n_ff);
     if (ws_bytes < w.bytes) return false;
@@ -903,19 +1010,20 @@ extern "C" bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64
     if (!launch_assign(w.ids, w.wts, w.atok, w.rsrc, w.rw, w.stg, w.stgn, nullptr, w.cbounds, n_tok, k1,
                        n_e, n_tok, n_e, topk, sh ? (int32_t)n_expert : -1))
         return false;
-    if (!q4_mmq_quantize(w.xn, w.atok, w.xq, Q4_T_IQ3_S, n_embd, rows)) return false;
-    if (!grouped::pow2_blocks(n_embd) &&
+    if (!q4_mmq_quantize(w.xn, w.atok, w.xq, gt, n_embd, rows)) return false;
+    if (gt == Q4_T_IQ3_S && !grouped::pow2_blocks(n_embd) &&
         cudaMemsetAsync(w.gu, 0, rows * 2 * n_ff * 4, st) != cudaSuccess)
         return false;
     if (!launch_grouped_any(base + og, stride, w.stg, w.stgn, n_entries, w.cbounds,
                             q8_view(w.xq, rows, n_embd), rows, n_embd, 2u * n_ff, w.gu, 2ull * n_ff,
-                            n_tok))
+                            n_tok, gt))
         return false;
     if (!q4_cuda_mmq_swiglu_quantize(w.gu, w.hq, rows, n_ff)) return false;
-    if (!grouped::pow2_blocks(n_ff) && cudaMemsetAsync(w.pd, 0, rows * n_embd * 4, st) != cudaSuccess)
+    if (dt == Q4_T_IQ3_S && !grouped::pow2_blocks(n_ff) &&
+        cudaMemsetAsync(w.pd, 0, rows * n_embd * 4, st) != cudaSuccess)
         return false;
     if (!launch_grouped_any(base + od, stride, w.stg, w.stgn, n_entries, w.cbounds,
-                            q8_view(w.hq, rows, n_ff), rows, n_ff, n_embd, w.pd, n_embd, n_tok))
+                            q8_view(w.hq, rows, n_ff), rows, n_ff, n_embd, w.pd, n_embd, n_tok, dt))
         return false;
     if (!q4_cuda_expert_reduce_set(d_y, w.pd, w.rsrc, w.rw, n_tok, k1, n_embd)) return false;
     if (d_ids && cudaMemcpyAsync(d_ids, w.ids, (uint64_t)n_tok * topk * 4, cudaMemcpyDeviceToDevice, st) !=
@@ -930,9 +1038,10 @@ extern "C" bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64
 // ---- verify window (2..8 tokens), reference entry point ----
 extern "C" bool q4_hip_moe_win_ok(uint32_t gt, uint32_t ut, uint32_t dt, uint32_t in_dim,
                                   uint32_t n_ff, uint32_t n_tok) {
-    return g_q4b.ok && gt == Q4_T_IQ3_S && ut == Q4_T_IQ3_S && dt == Q4_T_IQ3_S && n_tok >= 2 &&
-           n_tok <= 8 && in_dim <= 16384u && n_ff <= 4096u &&
-           grouped::shape_ok(Q4_T_IQ3_S, n_ff, in_dim) && grouped::shape_ok(Q4_T_IQ3_S, in_dim, n_ff);
+    // gate and up of one type, down of any; each IQ3_S, IQ4_NL or IQ4_XS (src/q4_rocm.cu:4926-4944
+    // takes more formats; the others answer false here and the engine keeps its own path)
+    return g_q4b.ok && gt == ut && n_tok >= 2 && n_tok <= 8 && in_dim <= 16384u && n_ff <= 4096u &&
+           grouped::shape_ok(gt, n_ff, in_dim) && grouped::shape_ok(dt, in_dim, n_ff);
 }
 
 // Library-owned scratch of the window path (allocated by init / scratch_warm):
@@ -961,8 +1070,9 @@ extern "C" bool q4_hip_moe_exec_win(const uint8_t *base, uint64_t stride, const 
     (void)d_h;
     if (!g_q4b.ok || !base || !d_es || !d_ew || !d_nh || !d_x || !d_y) return false;
     if (!q4_hip_moe_win_ok(gt, ut, dt, in_dim, n_ff, n_tok) || n_embd > 16384u ||
-        !grouped::shape_ok(Q4_T_IQ3_S, n_embd, n_ff))
+        !grouped::shape_ok(dt, n_embd, n_ff))
         return false;
+    if ((gt != Q4_T_IQ3_S || dt != Q4_T_IQ3_S) && q4b_ptr_tiled(base)) return false;
     if (!q4b_window_warm()) return false;
     cudaStream_t st = g_q4b.stream;
     const uint64_t rows = 512;  // 8 tokens x 64 picks; only the placed rows are touched
@@ -989,28 +1099,28 @@ extern "C" bool q4_hip_moe_exec_win(const uint8_t *base, uint64_t stride, const 
     g_q4b_launches++;
     if (!q4b_launch_ok("win_assign")) return false;
     const uint32_t n_pairs = n_tok * 64u;
-    if (!q4_mmq_quantize(d_x, atok, xq, Q4_T_IQ3_S, in_dim, n_pairs)) return false;
+    if (!q4_mmq_quantize(d_x, atok, xq, gt, in_dim, n_pairs)) return false;
     const Q8View xv = q8_view(xq, n_pairs, in_dim);
-    if (!grouped::pow2_blocks(in_dim) &&
+    if (gt == Q4_T_IQ3_S && !grouped::pow2_blocks(in_dim) &&
         cudaMemsetAsync(gu, 0, (uint64_t)n_pairs * 2 * n_ff * 4, st) != cudaSuccess)
         return false;
-    if (!grouped::pow2_blocks(n_ff) &&
+    if (dt == Q4_T_IQ3_S && !grouped::pow2_blocks(n_ff) &&
         cudaMemsetAsync(pd, 0, (uint64_t)n_pairs * n_embd * 4, st) != cudaSuccess)
         return false;
-    if (ou == og + (uint64_t)n_ff * (in_dim / 256u) * Q4B_IQ3S_BYTES) {
+    if (ou == og + (uint64_t)n_ff * grouped::row_bytes_t(gt, in_dim)) {
         if (!launch_grouped_any(base + og, stride, act, n_act, n_pairs, bounds, xv, n_pairs, in_dim,
-                                2u * n_ff, gu, 2ull * n_ff, n_tok))
+                                2u * n_ff, gu, 2ull * n_ff, n_tok, gt))
             return false;
     } else if (!launch_grouped_any(base + og, stride, act, n_act, n_pairs, bounds, xv, n_pairs, in_dim, n_ff,
-                                   gu, 2ull * n_ff, n_tok) ||
+                                   gu, 2ull * n_ff, n_tok, gt) ||
                !launch_grouped_any(base + ou, stride, act, n_act, n_pairs, bounds, xv, n_pairs, in_dim, n_ff,
-                                   gu + n_ff, 2ull * n_ff, n_tok)) {
+                                   gu + n_ff, 2ull * n_ff, n_tok, gt)) {
         return false;
     }
     if (!q4_mmq_swiglu(gu, h, n_pairs, n_ff)) return false;
-    if (!q4_mmq_quantize(h, nullptr, hq, Q4_T_IQ3_S, n_ff, n_pairs)) return false;
+    if (!q4_mmq_quantize(h, nullptr, hq, dt, n_ff, n_pairs)) return false;
     if (!launch_grouped_any(base + od, stride, act, n_act, n_pairs, bounds, q8_view(hq, n_pairs, n_ff),
-                            n_pairs, n_ff, n_embd, pd, n_embd, n_tok))
+                            n_pairs, n_ff, n_embd, pd, n_embd, n_tok, dt))
         return false;
     return q4_hip_expert_reduce(d_y, pd, rsrc, rw, n_tok, 64u, n_embd);
 }

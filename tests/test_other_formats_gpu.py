@@ -152,3 +152,70 @@ def test_mixed_pack_of_a_tile_multiple_size_is_not_tiled(dev, pkg, oracle):
         assert lib.q4_cuda_device_error() == 0
     finally:
         lib.q4_hip_experts_free_a(3)
+
+
+@pytest.mark.parametrize("H,F,gu,dn,n_tok", [(2048, 512, IQ3_S, IQ4_NL, 5), (512, 256, IQ4_XS, IQ3_S, 33),
+                                             (512, 256, IQ4_NL, IQ4_XS, 3), (2048, 512, IQ4_XS, IQ4_XS, 20)])
+def test_many_token_layer_with_other_formats(dev, pkg, oracle, H, F, gu, dn, n_tok):
+    """A layer whose experts mix formats through the many-token call (q4_cuda_moe_layer_nt: grouped
+    products per format) and, for 2..8 tokens, the verify-window call: routing ids exact, outputs
+    within 1e-3 of the oracle token by token, and the window equal to the one-token call."""
+    rng = np.random.default_rng(11 * H + gu + 3 * dn)
+    E, K = 16, 4
+    packs = pkg.synth.expert_packs_typed(rng, E + 1, H, F, gu, dn)      # slot E: the shared expert
+    pb = packs.shape[1]
+    router = (rng.standard_normal((E, H)) * 0.05).astype(np.float32)
+    norm_w = (1 + 0.1 * rng.standard_normal(H)).astype(np.float32)
+    xs = rng.standard_normal((n_tok, H)).astype(np.float32)
+    lib = dev.lib
+    lib.q4_cuda_set_tiled_default(0)
+    try:
+        assert lib.q4_hip_experts_alloc_a(3, E + 1, pb)
+    finally:
+        lib.q4_cuda_set_tiled_default(1)
+    try:
+        for e in range(E + 1):
+            row = np.ascontiguousarray(packs[e])
+            assert lib.q4_hip_experts_put_a(3, e, row.ctypes.data, pb)
+        base, stride = lib.q4_hip_experts_base_a(3), lib.q4_hip_experts_stride_a(3)
+        rb = pkg.synth.row_bytes(gu, H)
+        og, ou, od = 0, F * rb, 2 * F * rb
+        ws = lib.q4_cuda_moe_layer_n_ws_bytes(n_tok, K, E, H, F)
+        d_ws, d_x = dev.malloc(ws), dev.upload(xs)
+        d_y, d_ids, d_wts = dev.malloc(n_tok * H * 4), dev.malloc(n_tok * K * 4), dev.malloc(n_tok * K * 4)
+        assert lib.q4_cuda_moe_layer_nt(base, stride, gu, og, ou, dn, od, E, d_x, dev.upload(norm_w), 1e-6,
+                                        dev.upload(router), E, K, H, F, n_tok, d_y, d_ids, d_wts, d_ws, ws)
+        y = dev.download(d_y, (n_tok, H), np.float32)
+        ids = dev.download(d_ids, (n_tok, K), np.int32)
+        wts = dev.download(d_wts, (n_tok, K), np.float32)
+        for t in range(n_tok):
+            xn = oracle.rms_norm(xs[t], norm_w, 1e-6)
+            p = oracle.softmax(oracle.gemv_f32(router, xn))
+            ids0, w0 = oracle.topk(p, K)
+            assert ids[t].tolist() == ids0.tolist(), t
+            assert np.abs(wts[t] - w0).max() <= 1e-6
+            want = oracle.expert_job_t([packs[i] for i in ids0] + [packs[E]], list(w0) + [1.0], xn, H, F, dn, gu)
+            assert np.linalg.norm(y[t] - want) / np.linalg.norm(want) <= 1e-3, t
+        assert not lib.q4_cuda_moe_layer_nt(base, stride, gu, og, ou, 12, od, E, d_x, None, 1e-6,
+                                            dev.upload(router), E, K, H, F, n_tok, d_y, None, None, d_ws, ws)
+        if n_tok <= 8:
+            # the verify window (src/q4.h:887-897) on the same picks: 64 list entries per token
+            assert lib.q4_hip_moe_win_ok(gu, gu, dn, H, F, n_tok)
+            es = np.full((n_tok, 64), -1, np.int32)
+            ew = np.zeros((n_tok, 64), np.float32)
+            xn_all = np.stack([oracle.rms_norm(x, norm_w, 1e-6) for x in xs])
+            for t in range(n_tok):
+                es[t, :K], ew[t, :K] = ids[t], wts[t]
+            nh = np.full(n_tok, K, np.int32)
+            d_yw = dev.malloc(n_tok * H * 4)
+            assert lib.q4_hip_fill(d_yw, 0.0, n_tok * H)
+            assert lib.q4_hip_moe_exec_win(base, stride, dev.upload(es), dev.upload(ew), dev.upload(nh), n_tok,
+                                           gu, og, gu, ou, dn, od, dev.upload(xn_all), dev.malloc(n_tok * 64 * F * 4),
+                                           d_yw, F, H, H)
+            yw = dev.download(d_yw, (n_tok, H), np.float32)
+            for t in range(n_tok):
+                want = oracle.expert_job_t([packs[i] for i in ids[t]], wts[t], xn_all[t], H, F, dn, gu)
+                assert np.linalg.norm(yw[t] - want) / np.linalg.norm(want) <= 1e-3, t
+        assert lib.q4_cuda_device_error() == 0
+    finally:
+        lib.q4_hip_experts_free_a(3)
