@@ -136,7 +136,7 @@ def _grouped_fixture(dev, pkg, oracle, wr, wc):
     assert np.sqrt(num / den) < 1e-2
     assert np.sqrt(num8 / den8) < 1e-5
     # rows of the empty expert's neighbours are untouched by it; unsupported shapes refuse
-    assert not lib.q4_mmq_mul_id(d_w, 20, wr, wc, eb, n_exp, d_xq, dev.upload(bounds), 100, rows, d_dst, wr)
+    assert not lib.q4_mmq_mul_id(d_w, 12, wr, wc, eb, n_exp, d_xq, dev.upload(bounds), 100, rows, d_dst, wr)
     assert not lib.q4_mmq_mul_id(d_w, IQ3_S, wr, wc, eb, n_exp, d_xq, dev.upload(bounds), 100, rows, d_dst, wr - 1)
 
 
