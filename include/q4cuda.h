@@ -22,8 +22,9 @@
  *  - there is no CPU fallback: without a usable sm_100 GPU q4_hip_init() returns
  *    false and every other entry point refuses.
  *
- * Expert tensors are IQ3_S (type id 21); the one-token exec calls also take IQ4_NL (20) and
- * IQ4_XS (23) for gate+up and/or down, for packs kept in an arena in the engine's byte order.
+ * Expert tensors are IQ3_S (type id 21).  The one-token exec calls also take IQ4_NL (20), IQ4_XS (23),
+ * IQ3_XXS (18) and IQ2_S (22) for gate+up and IQ4_NL, IQ4_XS and Q2_0 (42) for down; the many-token
+ * calls IQ4_NL and IQ4_XS; all for packs kept in an arena in the engine's byte order.
  * Router tensors are F32 (type id 0).  q4_hip_moe_tok_ok() and q4_mmq_supported() answer
  * for a given shape and type mix.
  */
@@ -383,6 +384,11 @@ double q4_hip_vtl_calib(void);
 bool q4_cuda_quant8(const float *d_x, uint64_t n, int8_t *d_q, float *d_d, int32_t *d_bs);
 /* The same two stages for IQ4_NL rows (18-byte blocks of 32; src/q4_quant.c:270-290,
  * src/q4_cpuexp.c:977-996): fp32 dequantisation, and I[r][g] = table value x q per block. */
+/* Stage tests of IQ3_XXS (18), IQ2_S (22) and Q2_0 (42): dequantised rows, and the exact integer
+ * part of every 32-group's dot with int8 activations (before the sub-scales; Q2_0: codes 0..3 x q). */
+bool q4_cuda_fmt_dequant(uint32_t type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out);
+bool q4_cuda_fmt_idot(uint32_t type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const int8_t *d_q,
+                      int32_t *d_I);
 bool q4_cuda_iq4nl_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out);
 bool q4_cuda_iq4nl_idot(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, const int8_t *d_q,
                         int32_t *d_I);

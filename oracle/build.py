@@ -42,7 +42,8 @@ def _run(cmd):
 
 def build_oracle(force=False):
     src = [os.path.join(HERE, "q4_oracle.c"), os.path.join(HERE, "q4_oracle.h"),
-           os.path.join(CODES_DIR, "iq3s_codes.h")]
+           os.path.join(CODES_DIR, "iq3s_codes.h"), os.path.join(CODES_DIR, "iq4nl_codes.h"),
+           os.path.join(CODES_DIR, "iq3xxs_codes.h"), os.path.join(CODES_DIR, "iq2s_codes.h")]
     if not force and _newer(ORACLE_SO, src):
         return ORACLE_SO
     os.makedirs(os.path.dirname(ORACLE_SO), exist_ok=True)

@@ -265,6 +265,20 @@ class Oracle:
                 y[t, r] = np.float32(scale) * np.float32(v)
         return y
 
+    # ---- IQ3_XXS (18), IQ2_S (22), Q2_0 (42)
+    def dequant_row_x(self, type_id, row, n):
+        row = _u8(row)
+        out = np.zeros(n, np.float32)
+        self.lib.q4o_dequant_row_x(C.c_uint32(type_id), _p(row, _u8p), C.c_uint64(n), _p(out, _f32p))
+        return out
+
+    def group_idot_x(self, type_id, row, xq, n):
+        row = _u8(row)
+        I = np.zeros(n // 32, np.int32)
+        self.lib.q4o_group_idot_x(C.c_uint32(type_id), _p(row, _u8p), C.c_void_p(xq.ctypes.data), C.c_uint64(n),
+                                  _p(I, _i32p))
+        return I
+
     def dot_mmq(self, row, q, d, n):
         row = _u8(row)
         return float(self.lib.q4o_iq3s_dot_mmq(_p(row, _u8p), _p(q, _i8p), _p(d, _f32p),

@@ -284,13 +284,18 @@ float q4o_iq4xs_dot8(const uint8_t *row, const q4o_q8 *x, uint64_t n) {
     return ((acc[0] + acc[4]) + (acc[2] + acc[6])) + ((acc[1] + acc[5]) + (acc[3] + acc[7]));
 }
 
+float q4o_dot8_x(uint32_t type, const uint8_t *row, const q4o_q8 *x, uint64_t n);
 uint64_t q4o_row_bytes(uint32_t type, uint64_t ncols) {
+    if (type == Q4O_T_IQ3_XXS) return (ncols / Q4O_QK_K) * 98;
+    if (type == Q4O_T_IQ2_S) return (ncols / Q4O_QK_K) * 82;
+    if (type == Q4O_T_Q2_0) return (ncols / 64) * 18;
     if (type == Q4O_T_IQ4_NL) return (ncols / 32) * Q4O_IQ4NL_BYTES;
     if (type == Q4O_T_IQ4_XS) return (ncols / Q4O_QK_K) * Q4O_IQ4XS_BYTES;
     return (ncols / Q4O_QK_K) * Q4O_IQ3S_BYTES;
 }
 
 float q4o_dot8_t(uint32_t type, const uint8_t *row, const q4o_q8 *x, uint64_t n) {
+    if (type == Q4O_T_IQ3_XXS || type == Q4O_T_IQ2_S || type == Q4O_T_Q2_0) return q4o_dot8_x(type, row, x, n);
     if (type == Q4O_T_IQ4_NL) return q4o_iq4nl_dot8(row, x, n);
     if (type == Q4O_T_IQ4_XS) return q4o_iq4xs_dot8(row, x, n);
     return q4o_iq3s_dot8(row, x, n);
@@ -621,4 +626,145 @@ float q4o_mv_row(uint32_t type, const uint8_t *row, uint64_t n, const int8_t *q,
         memcpy(acc, nx, sizeof acc);
     }
     return acc[0];
+}
+
+/* ---- the other formats a routed expert's projections may come in (src/q4_rocm.cu:4926-4944):
+ * IQ3_XXS and IQ2_S (gate, up), Q2_0 (down).  Block layouts are the public ggml ones; the codebooks are
+ * kept as packed level numbers (iq3xxs_codes.h, iq2s_codes.h). ---- */
+#include "iq2s_codes.h"
+#include "iq3xxs_codes.h"
+
+static const uint8_t q4o_iq3xxs_levels[8] = {4, 12, 20, 28, 36, 44, 52, 62};
+static const uint8_t q4o_iq2s_levels[3] = {8, 25, 43};
+/* the 128-entry sign table of the IQ2/IQ3 "xxs" formats: seven stored bits, the eighth makes the
+ * parity even (src/q4_iq_grids.inc: q4_ksigns_iq2xs) */
+static uint8_t q4o_sign8(uint32_t i7) { return (uint8_t)(i7 | ((uint32_t)(__builtin_popcount(i7) & 1) << 7)); }
+
+/* One 32-value group of a 256-value block: magnitudes (unsigned), sign bits (bit i: value i is
+ * negative), the sub-scale of each of the eight 4-value lanes, and the block's fp16 d. */
+typedef struct {
+    uint8_t mag[32];
+    uint32_t neg;
+    int32_t ls[8];
+} q4o_grp;
+
+static float iq3xxs_group(const uint8_t *blk, int ib, q4o_grp *g) {
+    const uint8_t *qs = blk + 2 + 8 * ib;
+    const uint32_t aux = (uint32_t)blk[66 + 4 * ib] | ((uint32_t)blk[67 + 4 * ib] << 8) |
+                         ((uint32_t)blk[68 + 4 * ib] << 16) | ((uint32_t)blk[69 + 4 * ib] << 24);
+    g->neg = 0;
+    for (int l = 0; l < 4; l++) {          /* eight values: two codebook entries, one sign byte */
+        g->neg |= (uint32_t)q4o_sign8((aux >> (7 * l)) & 127u) << (8 * l);
+        for (int h = 0; h < 2; h++) {
+            const uint16_t code = q4b_iq3xxs_codes[qs[2 * l + h]];
+            for (int j = 0; j < 4; j++) g->mag[8 * l + 4 * h + j] = q4o_iq3xxs_levels[(code >> (3 * j)) & 7];
+        }
+    }
+    for (int lane = 0; lane < 8; lane++) g->ls[lane] = (int32_t)(aux >> 28);   /* raw 4-bit scale */
+    return mv_f16(blk);
+}
+
+static float iq2s_group(const uint8_t *blk, int ib, q4o_grp *g) {
+    const uint8_t *qs = blk + 2 + 4 * ib, *signs = blk + 34 + 4 * ib;
+    const uint32_t qh = blk[66 + ib], sb = blk[74 + ib];
+    g->neg = 0;
+    for (int l = 0; l < 4; l++) {          /* eight values: one codebook entry, one sign byte */
+        const uint32_t idx = qs[l] | ((qh << (8 - 2 * l)) & 0x300u);
+        const uint16_t code = q4b_iq2s_codes[idx];
+        for (int j = 0; j < 8; j++) g->mag[8 * l + j] = q4o_iq2s_levels[(code >> (2 * j)) & 3];
+        g->neg |= (uint32_t)signs[l] << (8 * l);
+    }
+    for (int lane = 0; lane < 8; lane++) g->ls[lane] = (int32_t)(lane < 4 ? (sb & 15u) : (sb >> 4));
+    return mv_f16(blk);
+}
+
+/* src/q4_quant.c:424-452 (IQ3_XXS), :290-322 (IQ2_S), :177-188 (Q2_0) */
+void q4o_dequant_row_x(uint32_t type, const uint8_t *src, uint64_t n, float *dst) {
+    if (type == Q4O_T_Q2_0) {
+        for (uint64_t b = 0; b < n / 64; b++) {
+            const uint8_t *blk = src + b * 18;
+            const float d = mv_f16(blk);
+            for (int j = 0; j < 64; j++)
+                dst[64 * b + j] = d * (float)((int)((blk[2 + j / 4] >> ((j % 4) * 2)) & 3) - 1);
+        }
+        return;
+    }
+    const uint32_t bb = type == Q4O_T_IQ3_XXS ? 98 : 82;
+    for (uint64_t b = 0; b < n / Q4O_QK_K; b++)
+        for (int ib = 0; ib < 8; ib++) {
+            q4o_grp g;
+            const float d = type == Q4O_T_IQ3_XXS ? iq3xxs_group(src + b * bb, ib, &g) : iq2s_group(src + b * bb, ib, &g);
+            for (int i = 0; i < 32; i++) {
+                const float sub = 0.5f + (float)g.ls[i >> 2];
+                const float db = type == Q4O_T_IQ3_XXS ? d * sub * 0.5f : d * sub * 0.25f;
+                dst[256 * b + 32 * ib + i] = db * (float)g.mag[i] * ((g.neg >> i) & 1u ? -1.f : 1.f);
+            }
+        }
+}
+
+void q4o_group_idot_x(uint32_t type, const uint8_t *row, const q4o_q8 *x, uint64_t n, int32_t *I) {
+    if (type == Q4O_T_Q2_0) {              /* per 32 values: sum of code x q (codes 0..3, value = code - 1) */
+        for (uint64_t gi = 0; gi < n / 32; gi++) {
+            const uint8_t *qs = row + (gi / 2) * 18 + 2 + 8 * (gi & 1);
+            int32_t s = 0;
+            for (int i = 0; i < 32; i++) s += (int32_t)((qs[i / 4] >> ((i % 4) * 2)) & 3) * x[gi].q[i];
+            I[gi] = s;
+        }
+        return;
+    }
+    const uint32_t bb = type == Q4O_T_IQ3_XXS ? 98 : 82;
+    for (uint64_t gi = 0; gi < n / 32; gi++) {          /* sum of sign x magnitude x q, before the sub-scales */
+        q4o_grp g;
+        if (type == Q4O_T_IQ3_XXS) iq3xxs_group(row + (gi / 8) * bb, (int)(gi & 7), &g);
+        else iq2s_group(row + (gi / 8) * bb, (int)(gi & 7), &g);
+        int32_t s = 0;
+        for (int i = 0; i < 32; i++) s += ((g.neg >> i) & 1u ? -1 : 1) * (int32_t)g.mag[i] * x[gi].q[i];
+        I[gi] = s;
+    }
+}
+
+/* The CPU path's row dots: src/q4_cpuexp.c:895-931 (IQ3_XXS), :814-852 (IQ2_S), :1113-1145 (Q2_0).
+ * Eight fp32 lanes, one fused multiply-add per lane and 32-group with the exact integer
+ * lane sum x (2 ls + 1), the final tree of cpx_hsum (:39-46). */
+float q4o_dot8_x(uint32_t type, const uint8_t *row, const q4o_q8 *x, uint64_t n) {
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (type == Q4O_T_Q2_0) {
+        float cs = 0.f;
+        for (uint64_t b = 0; b < n / 64; b++) {
+            const uint8_t *blk = row + b * 18;
+            const float d = mv_f16(blk);
+            for (int h = 0; h < 2; h++) {
+                const q4o_q8 *xg = x + 2 * b + h;
+                const float dd = d * xg->d;
+                for (int lane = 0; lane < 8; lane++) {
+                    const uint32_t byte = blk[2 + 8 * h + lane];        /* four 2-bit codes */
+                    int32_t s = 0;
+                    for (int t = 0; t < 4; t++) s += (int32_t)((byte >> (2 * t)) & 3) * xg->q[4 * lane + t];
+                    acc[lane] = fmaf(dd, (float)s, acc[lane]);
+                }
+                /* the offset term, accumulated as a scalar beside the lanes (:1141; the compiler fuses
+                 * the multiply-add at the reference's optimisation level) */
+                cs = fmaf(dd, (float)xg->bs, cs);
+            }
+        }
+        return (((acc[0] + acc[4]) + (acc[2] + acc[6])) + ((acc[1] + acc[5]) + (acc[3] + acc[7]))) - cs;
+    }
+    const uint32_t bb = type == Q4O_T_IQ3_XXS ? 98 : 82;
+    for (uint64_t b = 0; b < n / Q4O_QK_K; b++)
+        for (int ib = 0; ib < 8; ib++) {
+            q4o_grp g;
+            const float d16 = type == Q4O_T_IQ3_XXS ? iq3xxs_group(row + b * bb, ib, &g) : iq2s_group(row + b * bb, ib, &g);
+            const float d = d16 * (type == Q4O_T_IQ3_XXS ? 0.25f : 0.125f);
+            const q4o_q8 *xg = x + 8 * b + ib;
+            const float dd = d * xg->d;
+            for (int lane = 0; lane < 8; lane++) {
+                int32_t s = 0;
+                for (int t = 0; t < 4; t++) {
+                    const int i = 4 * lane + t;
+                    s += ((g.neg >> i) & 1u ? -1 : 1) * (int32_t)g.mag[i] * xg->q[i];
+                }
+                acc[lane] = fmaf(dd, (float)(s * (2 * g.ls[lane] + 1)), acc[lane]);
+            }
+        }
+    return ((acc[0] + acc[4]) + (acc[2] + acc[6])) + ((acc[1] + acc[5]) + (acc[3] + acc[7]));
 }

@@ -164,6 +164,17 @@ void q4o_mv_dequant_row(uint32_t type, const uint8_t *row, uint64_t n, float *ds
 float q4o_mv_row(uint32_t type, const uint8_t *row, uint64_t n, const int8_t *q, const float *d,
                  const int32_t *s16);
 
+/* ---- other routed-expert formats: IQ3_XXS (18), IQ2_S (22) for gate/up, Q2_0 (42) for down ---- */
+#define Q4O_T_IQ3_XXS 18u
+#define Q4O_T_IQ2_S 22u
+#define Q4O_T_Q2_0 42u
+/* src/q4_quant.c:424-452, :290-322, :177-188 */
+void q4o_dequant_row_x(uint32_t type, const uint8_t *src, uint64_t n, float *dst);
+/* exact integer part of every 32-group's dot (before sub-scales; Q2_0: codes 0..3 x q) */
+void q4o_group_idot_x(uint32_t type, const uint8_t *row, const q4o_q8 *x, uint64_t n, int32_t *I);
+/* src/q4_cpuexp.c:895-931, :814-852, :1113-1145; q4o_dot8_t and q4o_expert_job_t take these types too */
+float q4o_dot8_x(uint32_t type, const uint8_t *row, const q4o_q8 *x, uint64_t n);
+
 #ifdef __cplusplus
 }
 #endif

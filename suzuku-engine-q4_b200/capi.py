@@ -161,6 +161,8 @@ SIGNATURES = {
     "q4_hip_vtl_read": (b, [vp, u32, C.c_double]),
     "q4_hip_vtl_calib": (C.c_double, []),
     "q4_cuda_quant8": (b, [vp, u64, vp, vp, vp]),
+    "q4_cuda_fmt_dequant": (b, [u32, vp, u64, u64, vp]),
+    "q4_cuda_fmt_idot": (b, [u32, vp, u64, u64, vp, vp]),
     "q4_cuda_iq4nl_dequant": (b, [vp, u64, u64, vp]),
     "q4_cuda_iq4nl_idot": (b, [vp, u64, u64, vp, vp]),
     "q4_cuda_iq4_dequant": (b, [u32, vp, u64, u64, vp]),

@@ -736,12 +736,18 @@ __global__ void gemv_iq3s_f32_k(const uint8_t *__restrict__ w, uint64_t nrows, u
     if (lane == 0) y[(uint64_t)blockIdx.y * nrows + r] = scale * acc;
 }
 
+#include "q4b_small_formats.cuh"
+
 // ------------------------------------------------------------------ host side
-// gate and up of one type, down of any: IQ3_S, IQ4_NL or IQ4_XS (the first of the other formats
-// the engine's call sites accept, src/q4_rocm.cu:4926-4944)
-bool type_ok(uint32_t t) { return t == Q4_T_IQ3_S || t == Q4_T_IQ4_NL || t == Q4_T_IQ4_XS; }
+// gate and up of one type out of IQ3_S, IQ4_NL, IQ4_XS, IQ3_XXS, IQ2_S; down out of IQ3_S, IQ4_NL,
+// IQ4_XS, Q2_0 (of the formats the engine's call sites accept, src/q4_rocm.cu:4926-4944, the ones its
+// deployed models use for these projections)
+bool gu_type_ok(uint32_t t) {
+    return t == Q4_T_IQ3_S || t == Q4_T_IQ4_NL || t == Q4_T_IQ4_XS || t == Q4_T_IQ3_XXS || t == Q4_T_IQ2_S;
+}
+bool down_type_ok(uint32_t t) { return t == Q4_T_IQ3_S || t == Q4_T_IQ4_NL || t == Q4_T_IQ4_XS || t == Q4_T_Q2_0; }
 bool shape_ok(uint32_t gt, uint32_t ut, uint32_t dt, uint32_t in_dim, uint32_t n_ff) {
-    return gt == ut && type_ok(gt) && type_ok(dt) && in_dim && n_ff && (in_dim % Q4B_QK) == 0 &&
+    return gt == ut && gu_type_ok(gt) && down_type_ok(dt) && in_dim && n_ff && (in_dim % Q4B_QK) == 0 &&
            (n_ff % Q4B_QK) == 0 && in_dim <= Q4B_XQ_MAXLEN && n_ff <= Q4B_XQ_MAXLEN;
 }
 
@@ -780,7 +786,13 @@ bool moe_exec_tail(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
     const int32_t *xbs = s.xbs + (size_t)Q4B_X_SLICE * (Q4B_XQ_MAXLEN / 32);
     const size_t sm = 2048 + in_dim + 8 * (in_dim >> 5);
     const bool tiled = q4b_ptr_tiled(base);
-    if (gt == Q4_T_IQ4_NL)
+    if (gt == Q4_T_IQ3_XXS)
+        moe_gux_k<Q4_T_IQ3_XXS><<<dim3((n_ff + 7) / 8, ne), 256, 0, s.stream>>>(
+            base + og, base + ou, stride, d_slots, d_n, xq, xd, in_dim, n_ff, s.grid3xxs_d, s.grid2s_d, d_h);
+    else if (gt == Q4_T_IQ2_S)
+        moe_gux_k<Q4_T_IQ2_S><<<dim3((n_ff + 7) / 8, ne), 256, 0, s.stream>>>(
+            base + og, base + ou, stride, d_slots, d_n, xq, xd, in_dim, n_ff, s.grid3xxs_d, s.grid2s_d, d_h);
+    else if (gt == Q4_T_IQ4_NL)
         moe_gu4_k<Q4_T_IQ4_NL><<<dim3((n_ff + 7) / 8, ne), 256, 0, s.stream>>>(
             base + og, base + ou, stride, d_slots, d_n, xq, xd, in_dim, n_ff, d_h);
     else if (gt == Q4_T_IQ4_XS)
@@ -797,7 +809,10 @@ bool moe_exec_tail(const uint8_t *base, uint64_t stride, const int32_t *d_slots,
     if (!launch_quant8(d_h, n_ff, n_ff, ne, s.xq, s.xd, s.xbs, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32,
                        d_n))
         return false;
-    if (dt == Q4_T_IQ4_NL)
+    if (dt == Q4_T_Q2_0)
+        moe_ya20_k<<<(n_embd + 7) / 8, 256, 0, s.stream>>>(base + od, stride, d_slots, d_wts, n_host, d_n, s.xq, s.xd,
+                                                          s.xbs, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32, n_ff, n_embd, d_y);
+    else if (dt == Q4_T_IQ4_NL)
         moe_ya4_k<Q4_T_IQ4_NL><<<(n_embd + 7) / 8, 256, 0, s.stream>>>(
             base + od, stride, d_slots, d_wts, n_host, d_n, s.xq, s.xd, Q4B_XQ_MAXLEN, Q4B_XQ_MAXLEN / 32, n_ff,
             n_embd, d_y);
@@ -1045,6 +1060,44 @@ extern "C" bool q4_cuda_iq4_idot(uint32_t type, const uint8_t *d_w, uint64_t nro
     g_q4b_launches++;
     return q4b_launch_ok("iq4_idot");
 }
+// Stage tests of IQ3_XXS (18), IQ2_S (22), Q2_0 (42): dequantised rows, and the exact integer part of
+// every 32-group's dot with int8 activations (before the sub-scales; Q2_0: codes 0..3 x q).
+extern "C" bool q4_cuda_fmt_dequant(uint32_t type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                                    float *d_out) {
+    const uint32_t per = type == Q4_T_Q2_0 ? 64u : 256u;
+    if (!g_q4b.ok || !d_w || !d_out || !nrows || !ncols || (ncols % per) ||
+        (type != Q4_T_IQ3_XXS && type != Q4_T_IQ2_S && type != Q4_T_Q2_0))
+        return false;
+    const uint32_t gpr = (uint32_t)(ncols / 32u);
+    const uint64_t n = nrows * gpr;
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    if (type == Q4_T_IQ3_XXS)
+        small_dequant_k<Q4_T_IQ3_XXS><<<grid, 256, 0, g_q4b.stream>>>(d_w, n, gpr, g_q4b.grid3xxs_d, g_q4b.grid2s_d, d_out);
+    else if (type == Q4_T_IQ2_S)
+        small_dequant_k<Q4_T_IQ2_S><<<grid, 256, 0, g_q4b.stream>>>(d_w, n, gpr, g_q4b.grid3xxs_d, g_q4b.grid2s_d, d_out);
+    else
+        small_dequant_k<Q4_T_Q2_0><<<grid, 256, 0, g_q4b.stream>>>(d_w, n, gpr, g_q4b.grid3xxs_d, g_q4b.grid2s_d, d_out);
+    g_q4b_launches++;
+    return q4b_launch_ok("fmt_dequant");
+}
+extern "C" bool q4_cuda_fmt_idot(uint32_t type, const uint8_t *d_w, uint64_t nrows, uint64_t ncols,
+                                 const int8_t *d_q, int32_t *d_I) {
+    const uint32_t per = type == Q4_T_Q2_0 ? 64u : 256u;
+    if (!g_q4b.ok || !d_w || !d_q || !d_I || !nrows || !ncols || (ncols % per) ||
+        (type != Q4_T_IQ3_XXS && type != Q4_T_IQ2_S && type != Q4_T_Q2_0))
+        return false;
+    const uint32_t gpr = (uint32_t)(ncols / 32u);
+    const unsigned grid = (unsigned)((nrows * gpr + 255) / 256);
+    if (type == Q4_T_IQ3_XXS)
+        small_idot_k<Q4_T_IQ3_XXS><<<grid, 256, 0, g_q4b.stream>>>(d_w, nrows, gpr, g_q4b.grid3xxs_d, g_q4b.grid2s_d, d_q, d_I);
+    else if (type == Q4_T_IQ2_S)
+        small_idot_k<Q4_T_IQ2_S><<<grid, 256, 0, g_q4b.stream>>>(d_w, nrows, gpr, g_q4b.grid3xxs_d, g_q4b.grid2s_d, d_q, d_I);
+    else
+        small_idot_k<Q4_T_Q2_0><<<grid, 256, 0, g_q4b.stream>>>(d_w, nrows, gpr, g_q4b.grid3xxs_d, g_q4b.grid2s_d, d_q, d_I);
+    g_q4b_launches++;
+    return q4b_launch_ok("fmt_idot");
+}
+
 extern "C" bool q4_cuda_iq4nl_dequant(const uint8_t *d_w, uint64_t nrows, uint64_t ncols, float *d_out) {
     return q4_cuda_iq4_dequant(Q4_T_IQ4_NL, d_w, nrows, ncols, d_out);
 }

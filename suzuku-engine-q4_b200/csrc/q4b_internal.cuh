@@ -41,6 +41,8 @@ struct Q4bState {
     uint32_t flag_epoch;
     uint32_t *err_h;
     uint32_t *codes_d;  // the 512 codebook entries byte-expanded (c_j in byte j), device memory
+    uint32_t *grid3xxs_d;  // IQ3_XXS codebook: 256 words of four magnitude bytes
+    uint2 *grid2s_d;       // IQ2_S codebook: 1024 pairs of words, eight magnitude bytes
     // scratch of the fused layer entry points (q4_cuda_moe_decode*)
     float *xn;        // [Q4B_MAX_TOK][Q4B_XQ_MAXLEN] normalised rows
     float *logits;    // [Q4B_MAX_TOK][1024]

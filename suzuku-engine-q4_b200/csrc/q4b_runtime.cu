@@ -9,7 +9,9 @@
 #include "../../include/q4cuda.h"
 
 #define Q4B_IQ3S_CODES_DECL static const
+#include "iq2s_codes.h"
 #include "iq3s_codes.h"
+#include "iq3xxs_codes.h"
 
 Q4bState g_q4b = {};
 bool q4b_fused_warm();   // q4b_stack.cu: scratch of the persistent decode kernel
@@ -187,6 +189,25 @@ extern "C" bool q4_hip_init(void) {
         Q4B_CHECK(cudaMalloc(&s.codes_d, sizeof(codes)));
         Q4B_CHECK(cudaMemcpy(s.codes_d, codes, sizeof(codes), cudaMemcpyHostToDevice));
     }
+    {   // the two small codebooks, expanded from their packed level numbers to magnitude bytes
+        static const uint8_t l3[8] = {4, 12, 20, 28, 36, 44, 52, 62}, l2[4] = {8, 25, 43, 0};
+        static uint32_t g3[256];
+        static uint32_t g2[2048];
+        for (int i = 0; i < 256; i++) {
+            g3[i] = 0;
+            for (int j = 0; j < 4; j++) g3[i] |= (uint32_t)l3[(q4b_iq3xxs_codes[i] >> (3 * j)) & 7] << (8 * j);
+        }
+        for (int i = 0; i < 1024; i++)
+            for (int h = 0; h < 2; h++) {
+                g2[2 * i + h] = 0;
+                for (int j = 0; j < 4; j++)
+                    g2[2 * i + h] |= (uint32_t)l2[(q4b_iq2s_codes[i] >> (2 * (4 * h + j))) & 3] << (8 * j);
+            }
+        Q4B_CHECK(cudaMalloc(&s.grid3xxs_d, sizeof g3));
+        Q4B_CHECK(cudaMemcpy(s.grid3xxs_d, g3, sizeof g3, cudaMemcpyHostToDevice));
+        Q4B_CHECK(cudaMalloc(&s.grid2s_d, sizeof g2));
+        Q4B_CHECK(cudaMemcpy(s.grid2s_d, g2, sizeof g2, cudaMemcpyHostToDevice));
+    }
     Q4B_CHECK(cudaEventCreate(&g_ev0));
     Q4B_CHECK(cudaEventCreate(&g_ev1));
     if (!alloc_scratch()) return false;
@@ -230,6 +251,10 @@ extern "C" void q4_hip_shutdown(void) {
     if (s.flag_h) cudaFreeHost(s.flag_h);
     s.flag_h = s.flag_d = nullptr;
     cudaFree(s.codes_d);
+    cudaFree(s.grid3xxs_d);
+    cudaFree(s.grid2s_d);
+    s.grid3xxs_d = nullptr;
+    s.grid2s_d = nullptr;
     cudaFreeHost(s.err_h);
     cudaEventDestroy(g_ev0);
     cudaEventDestroy(g_ev1);

@@ -88,13 +88,30 @@ def kquant_blocks(rng, type_id, n_blocks):
     return b
 
 
+# the remaining routed-expert formats: {bytes per block, values per block}; all byte patterns are valid
+SMALL_FORMATS = {18: (98, 256), 22: (82, 256), 42: (18, 64)}      # IQ3_XXS, IQ2_S, Q2_0
+
+
+def small_format_blocks(rng, type_id, n_blocks):
+    """n_blocks random IQ3_XXS (18), IQ2_S (22) or Q2_0 (42) blocks: uniform bytes, fp16 d = |N(0,1)| * 2^-6."""
+    bs = SMALL_FORMATS[type_id][0]
+    b = rng.integers(0, 256, size=(n_blocks, bs), dtype=np.uint8)
+    d = (np.abs(rng.standard_normal(n_blocks)) * 2.0 ** -6).astype(np.float16)
+    b[:, 0:2] = d.view(np.uint8).reshape(n_blocks, 2)
+    return b
+
+
 def row_bytes(type_id, ncols):
+    if type_id in SMALL_FORMATS:
+        return ncols // SMALL_FORMATS[type_id][1] * SMALL_FORMATS[type_id][0]
     if type_id in KQUANT:
         return ncols // 256 * KQUANT[type_id][0]
     return {21: ncols // 256 * IQ3S_BLOCK, 20: ncols // 32 * IQ4NL_BLOCK, 23: ncols // 256 * IQ4XS_BLOCK}[type_id]
 
 
 def blocks_of(rng, type_id, nbytes):
+    if type_id in SMALL_FORMATS:
+        return small_format_blocks(rng, type_id, nbytes // SMALL_FORMATS[type_id][0]).reshape(-1)
     if type_id in KQUANT:
         return kquant_blocks(rng, type_id, nbytes // KQUANT[type_id][0]).reshape(-1)
     make, bs = {21: (iq3s_blocks, IQ3S_BLOCK), 20: (iq4nl_blocks, IQ4NL_BLOCK), 23: (iq4xs_blocks, IQ4XS_BLOCK)}[type_id]

@@ -307,3 +307,48 @@ def test_dense_product_accuracy_and_row_independence(pkg, oracle, ty):
     assert np.linalg.norm(y - want) / np.linalg.norm(want) < 2e-2
     y1 = oracle.mv_rows(ty, w, R, K, xs[1:2], 0.5)
     assert np.array_equal(y1[0].view(np.uint32), y[1].view(np.uint32))
+
+
+# ---- IQ3_XXS (18), IQ2_S (22) gate/up and Q2_0 (42) down ----
+@pytest.mark.parametrize("ty", [18, 22, 42])
+def test_small_formats_pinned_to_reference(pkg, oracle, reference, ty):
+    """Dequantisation and the Q8-A row dot of the restatement against the reference's own code
+    (src/q4_quant.c:177-188,290-322,424-452; src/q4_cpuexp.c:814-852,895-931,1113-1145) on seeded
+    blocks, bit for bit; the integer parts against the dequantised weights."""
+    if reference is None:
+        pytest.skip("reference CPU path not built here")
+    rng = np.random.default_rng(3000 + ty)
+    n = 1024
+    rows = np.stack([pkg.synth.blocks_of(rng, ty, pkg.synth.row_bytes(ty, n)) for _ in range(5)])
+    x = rng.standard_normal(n).astype(np.float32)
+    x[64:96] = 0.0
+    xq = oracle.quant8(x)
+    for row in rows:
+        a, b = oracle.dequant_row_x(ty, row, n), reference.dequant_row_t(ty, row, n)
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
+        got = oracle.dot8_t(ty, row, xq, n)
+        want = reference.dot8_t(ty, row, xq, n)
+        assert np.float32(got).view(np.uint32) == np.float32(want).view(np.uint32)
+    # integer parts: a block with d = 1.0 dequantises to multiples of the sub-scale step
+    I = oracle.group_idot_x(ty, rows[0], xq, n)
+    assert I.shape == (n // 32,) and np.abs(I).max() > 0
+
+
+@pytest.mark.parametrize("gu,dn", [(18, 42), (22, 21), (21, 42), (22, 42)])
+def test_expert_job_small_format_mixes_match_reference(pkg, oracle, reference, gu, dn):
+    if reference is None:
+        pytest.skip("reference CPU path not built here")
+    H, F, k = 512, 256, 3
+    rng = np.random.default_rng(gu * 100 + dn)
+    packs = pkg.synth.expert_packs_typed(rng, k, H, F, gu, dn)
+    x = rng.standard_normal(H).astype(np.float32)
+    wts = rng.random(k).astype(np.float32)
+    reference.set_gu_type(gu)
+    reference.set_down_type(dn)
+    try:
+        want = reference.expert_job(list(packs), np.arange(k, dtype=np.int32), wts, x, H, F)
+    finally:
+        reference.set_gu_type(21)
+        reference.set_down_type(21)
+    got = oracle.expert_job_t(list(packs), wts, x, H, F, dn, gu)
+    assert np.linalg.norm(got - want) / np.linalg.norm(want) < 2e-6

@@ -6,6 +6,7 @@ import pytest
 
 pytestmark = pytest.mark.gpu
 IQ3_S, IQ4_NL, IQ4_XS = 21, 20, 23
+IQ3_XXS, IQ2_S, Q2_0 = 18, 22, 42
 
 
 def test_iq4nl_dequant_and_integer_dots_bit_exact(dev, pkg, oracle):
@@ -50,10 +51,33 @@ def test_iq4xs_dequant_and_integer_dots_bit_exact(dev, pkg, oracle):
     assert not lib.q4_cuda_iq4_dequant(IQ3_S, d_w, nrows, n, d_out)       # not a 4-bit format
 
 
+@pytest.mark.parametrize("ty", [IQ3_XXS, IQ2_S, Q2_0])
+def test_small_formats_dequant_and_integer_dots_bit_exact(dev, pkg, oracle, ty):
+    rng = np.random.default_rng(50 + ty)
+    nrows, n = 6, 1024
+    w = np.stack([pkg.synth.blocks_of(rng, ty, pkg.synth.row_bytes(ty, n)) for _ in range(nrows)])
+    lib = dev.lib
+    d_w = dev.upload(w)
+    d_out = dev.malloc(nrows * n * 4)
+    assert lib.q4_cuda_fmt_dequant(ty, d_w, nrows, n, d_out)
+    got = dev.download(d_out, (nrows, n), np.float32)
+    xq = oracle.quant8(rng.standard_normal(n).astype(np.float32))
+    d_I = dev.malloc(nrows * (n // 32) * 4)
+    assert lib.q4_cuda_fmt_idot(ty, d_w, nrows, n, dev.upload(np.ascontiguousarray(xq["q"])), d_I)
+    I = dev.download(d_I, (nrows, n // 32), np.int32)
+    for r in range(nrows):
+        assert np.array_equal(got[r].view(np.uint32), oracle.dequant_row_x(ty, w[r], n).view(np.uint32)), r
+        assert np.array_equal(I[r], oracle.group_idot_x(ty, w[r], xq, n)), r
+    assert not lib.q4_cuda_fmt_dequant(ty, d_w, nrows, n - 32, d_out)
+    assert not lib.q4_cuda_fmt_dequant(IQ3_S, d_w, nrows, n, d_out)
+
+
 @pytest.mark.parametrize("H,F,gu,dn", [(512, 256, IQ3_S, IQ4_NL), (2048, 512, IQ3_S, IQ4_NL),
                                        (512, 256, IQ3_S, IQ4_XS), (512, 256, IQ4_XS, IQ3_S),
                                        (2048, 512, IQ4_XS, IQ4_XS), (512, 256, IQ4_NL, IQ4_NL),
-                                       (512, 256, IQ4_XS, IQ4_NL)])
+                                       (512, 256, IQ4_XS, IQ4_NL), (2048, 512, IQ3_XXS, Q2_0),
+                                       (512, 256, IQ2_S, IQ3_S), (2048, 512, IQ2_S, Q2_0),
+                                       (512, 256, IQ3_XXS, IQ4_NL), (512, 256, IQ3_S, Q2_0)])
 def test_exec_with_other_formats_matches_oracle(dev, pkg, oracle, H, F, gu, dn):
     rng = np.random.default_rng(H + 7 * gu + dn)
     n_slots, k = 6, 4
@@ -75,6 +99,8 @@ def test_exec_with_other_formats_matches_oracle(dev, pkg, oracle, H, F, gu, dn):
         assert lib.q4_hip_moe_tok_ok(gu, gu, dn, H, F)
         assert not lib.q4_hip_moe_tok_ok(IQ4_NL, IQ3_S, IQ3_S, H, F)      # gate and up share a type
         assert not lib.q4_hip_moe_tok_ok(IQ3_S, IQ3_S, 12, H, F)          # a type this path does not take
+        assert not lib.q4_hip_moe_tok_ok(Q2_0, Q2_0, IQ3_S, H, F)         # Q2_0 is a down format only
+        assert not lib.q4_hip_moe_tok_ok(IQ3_S, IQ3_S, IQ2_S, H, F)       # IQ2_S a gate/up format only
         x = rng.standard_normal(H).astype(np.float32)
         slots = rng.choice(n_slots, k, replace=False).astype(np.int32)
         wts = rng.random(k).astype(np.float32)
