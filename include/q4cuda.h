@@ -539,7 +539,7 @@ bool q4_cuda_decode_stack_set_final(void *plan, float *d_res, const float *d_inj
  * the library's stream over `plan`; it then waits on a doorbell in pinned host memory.  step
  * copies the token's row (n_embd floats, any host memory) into the session's pinned buffer and
  * rings; the kernel runs the next layers_per_step layers of the plan (cyclically: with 1, step s
- * is layer s mod n_layers; 0 = all of them; at most 31) and writes the result row and the step number into
+ * is layer s mod n_layers; 0 = all of them) and writes the result row and the step number into
  * pinned host memory, where step is spinning; step copies the row to h_y and returns.  While a
  * session is live its kernel holds every SM: other work on the device waits and the other decode
  * calls of this library answer false, so end the session before anything else has to run.  The
