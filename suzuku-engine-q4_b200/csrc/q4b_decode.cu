@@ -384,20 +384,16 @@ __global__ void iq3s_idot_k(const uint8_t *__restrict__ w, uint64_t nrows, uint3
 // values keep the lower index; weights renormalised over the picks in rank
 // order (src/q4_quant.c:715-755).  Optionally appends the shared expert's slot
 // with weight 1 and writes the entry count.
-__global__ void softmax_topk_k(const float *__restrict__ logits, uint32_t n, uint32_t k,
-                               int32_t *__restrict__ ids, float *__restrict__ wts,
-                               uint32_t out_stride, int32_t shared_slot,
-                               int32_t *__restrict__ n_out) {
-    __shared__ float p[1024];
-    __shared__ float wsel[64];
-    const uint32_t lane = threadIdx.x;
-    const float *l = logits + (uint64_t)blockIdx.x * n;
+__device__ __forceinline__ void softmax_topk_warp(const float *__restrict__ l, uint32_t n, uint32_t k,
+                                                  int32_t *__restrict__ ids, float *__restrict__ wts,
+                                                  int32_t shared_slot, int32_t *__restrict__ n_out,
+                                                  float *p, float *wsel, uint32_t lane) {
     float m = -INFINITY;
-    for (uint32_t i = lane; i < n; i += 32) m = fmaxf(m, l[i]);
+    for (uint32_t i = lane; i < n; i += 32) m = fmaxf(m, __ldcg(l + i));
     m = q4b_warp_max(m);
     float s = 0.f;
     for (uint32_t i = lane; i < n; i += 32) {
-        const float e = expf(l[i] - m);
+        const float e = expf(__ldcg(l + i) - m);
         p[i] = e;
         s += e;
     }
@@ -429,7 +425,7 @@ __global__ void softmax_topk_k(const float *__restrict__ logits, uint32_t n, uin
         }
         const uint32_t idx = 0xffffffffu - (uint32_t)(best & 0xffffffffu);
         if (lane == 0) {
-            ids[(uint64_t)blockIdx.x * out_stride + t] = (int32_t)idx;
+            ids[t] = (int32_t)idx;
             wsel[t] = __uint_as_float((uint32_t)(best >> 32));
         }
         if ((idx & 31u) == lane) {
@@ -442,16 +438,90 @@ __global__ void softmax_topk_k(const float *__restrict__ logits, uint32_t n, uin
         float sum = 0.f;
         for (uint32_t t = 0; t < k; t++) sum = __fadd_rn(sum, wsel[t]);
         const float wi = sum > 0.f ? __fdiv_rn(1.0f, sum) : 1.f;
-        for (uint32_t t = 0; t < k; t++)
-            wts[(uint64_t)blockIdx.x * out_stride + t] = sum > 0.f ? __fmul_rn(wsel[t], wi) : wsel[t];
+        for (uint32_t t = 0; t < k; t++) wts[t] = sum > 0.f ? __fmul_rn(wsel[t], wi) : wsel[t];
         uint32_t cnt = k;
         if (shared_slot >= 0) {
-            ids[(uint64_t)blockIdx.x * out_stride + k] = shared_slot;
-            wts[(uint64_t)blockIdx.x * out_stride + k] = 1.0f;
+            ids[k] = shared_slot;
+            wts[k] = 1.0f;
             cnt++;
         }
-        if (n_out) n_out[blockIdx.x] = (int32_t)cnt;
+        if (n_out) *n_out = (int32_t)cnt;
     }
+}
+__global__ void softmax_topk_k(const float *__restrict__ logits, uint32_t n, uint32_t k,
+                               int32_t *__restrict__ ids, float *__restrict__ wts,
+                               uint32_t out_stride, int32_t shared_slot,
+                               int32_t *__restrict__ n_out) {
+    __shared__ float p[1024];
+    __shared__ float wsel[64];
+    softmax_topk_warp(logits + (uint64_t)blockIdx.x * n, n, k, ids + (uint64_t)blockIdx.x * out_stride,
+                      wts + (uint64_t)blockIdx.x * out_stride, shared_slot, n_out ? n_out + blockIdx.x : nullptr, p,
+                      wsel, threadIdx.x);
+}
+
+// RMSNorm, router product and softmax / top-k of up to 8 tokens in ONE launch (n_embd == 2048): what
+// rms_q8_k (norm only), gemv_f32_x16_k and softmax_topk_k do as three, with the same operations in the
+// same order, so every value is bit for bit theirs.  A verify window's layer is a dozen launches of a
+// few microseconds each; this removes two.  Every CTA normalises all the rows itself (8 tokens x 8 KB
+// from L2) and keeps them in shared memory; a warp takes one router row; the CTA that finishes last
+// (a counter, no waiting) runs the top-k, one warp per token.
+__global__ void __launch_bounds__(256) route_small_k(const float *__restrict__ x, const float *__restrict__ norm_w,
+                                                     float eps, const float *__restrict__ W, uint32_t n_expert,
+                                                     uint32_t n_tok, uint32_t topk, float *__restrict__ xn_out,
+                                                     float *__restrict__ logits, int32_t *__restrict__ ids,
+                                                     float *__restrict__ wts, unsigned int *__restrict__ counter) {
+    extern __shared__ __align__(16) float rs_rows[];   // [n_tok][2048]; the last CTA reuses it for the probabilities
+    __shared__ double sh[8];
+    __shared__ float wsel[8][64];
+    __shared__ uint32_t is_last;
+    constexpr uint32_t n = 2048;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    for (uint32_t t = 0; t < n_tok; t++) {
+        const float *xc = x + (uint64_t)t * n;
+        double ss = 0.0;
+        for (uint32_t i = tid; i < n; i += 256) ss += (double)xc[i] * (double)xc[i];
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) sh[warp] = ss;
+        __syncthreads();
+        double tot = 0.0;
+        for (uint32_t i = 0; i < 8; i++) tot += sh[i];
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(tot / (double)n), eps)));
+        for (uint32_t i = tid; i < n; i += 256) {
+            float v = __fmul_rn(xc[i], scale);
+            if (norm_w) v = __fmul_rn(v, norm_w[i]);
+            rs_rows[t * n + i] = v;
+            if (blockIdx.x == 0) xn_out[(uint64_t)t * n + i] = v;
+        }
+        __syncthreads();
+    }
+    const uint32_t r = blockIdx.x * 8u + warp;
+    if (r < n_expert) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(W + (uint64_t)r * n);
+        float4 w[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) w[j] = __ldg(w4 + lane + 32 * j);
+        for (uint32_t t = 0; t < n_tok; t++) {
+            const float4 *x4 = reinterpret_cast<const float4 *>(rs_rows + t * n);
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < 16; j++) {
+                const float4 b = x4[lane + 32 * j];
+                acc += w[j].x * b.x + w[j].y * b.y + w[j].z * b.z + w[j].w * b.w;
+            }
+            acc = q4b_warp_sum(acc);
+            if (lane == 0) logits[(uint64_t)t * n_expert + r] = 1.0f * acc;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) is_last = atomicInc(counter, gridDim.x - 1u) == gridDim.x - 1u ? 1u : 0u;   // wraps to 0 by itself
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (uint32_t t = warp; t < n_tok; t += 8)
+        softmax_topk_warp(logits + (uint64_t)t * n_expert, n_expert, topk, ids + (uint64_t)t * topk,
+                          wts + (uint64_t)t * topk, -1, nullptr, rs_rows + t * 1024u, wsel[warp], lane);
 }
 
 // ------------------------------------------------------------------ gate/up + SwiGLU
@@ -1270,6 +1340,34 @@ bool q4b_route_tokens(const float *d_rlog, int32_t *d_ids, float *d_wts, uint32_
     softmax_topk_k<<<n_tok, 32, 0, g_q4b.stream>>>(d_rlog, n_exp, topk, d_ids, d_wts, topk, -1, nullptr);
     g_q4b_launches++;
     return q4b_launch_ok("route_tokens");
+}
+// norm + router + top-k of a few tokens in one launch; false: the shape is not this kernel's (nothing
+// queued, the caller issues the three launches)
+static unsigned int *g_route_counter = nullptr;
+bool q4b_route_small_warm() {
+    if (g_route_counter) return true;
+    if (cudaMalloc(&g_route_counter, sizeof(unsigned int)) != cudaSuccess ||
+        cudaMemset(g_route_counter, 0, sizeof(unsigned int)) != cudaSuccess ||
+        cudaFuncSetAttribute(route_small_k, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2048 * 4) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    return true;
+}
+void q4b_route_small_shutdown() {
+    cudaFree(g_route_counter);
+    g_route_counter = nullptr;
+}
+bool q4b_route_small(const float *x, const float *norm_w, float eps, const float *router, uint32_t n_expert,
+                     uint32_t topk, uint32_t n_embd, uint32_t n_tok, float *xn, float *logits, int32_t *ids,
+                     float *wts) {
+    if (!g_route_counter || n_embd != 2048u || n_tok == 0 || n_tok > 8u || n_expert > 1024u || topk > 64u ||
+        (((uintptr_t)router | (uintptr_t)x) & 15u))
+        return false;
+    route_small_k<<<(n_expert + 7u) / 8u, 256, (size_t)n_tok * 2048u * 4u, g_q4b.stream>>>(
+        x, norm_w, eps, router, n_expert, n_tok, topk, xn, logits, ids, wts, g_route_counter);
+    g_q4b_launches++;
+    return q4b_launch_ok("route_small");
 }
 bool q4b_rms_rows(const float *x, const float *w, float *y, uint32_t n_embd, float eps,
                   uint32_t n_tok) {

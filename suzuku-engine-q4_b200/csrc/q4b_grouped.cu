@@ -28,6 +28,9 @@ bool q4b_ptr_tiled(const void *p);
 // defined in q4b_decode.cu
 bool q4b_route_tokens(const float *d_rlog, int32_t *d_ids, float *d_wts, uint32_t n_tok,
                       uint32_t n_exp, uint32_t topk);
+bool q4b_route_small(const float *x, const float *norm_w, float eps, const float *router, uint32_t n_expert,
+                     uint32_t topk, uint32_t n_embd, uint32_t n_tok, float *xn, float *logits, int32_t *ids,
+                     float *wts);
 bool q4b_rms_rows(const float *x, const float *w, float *y, uint32_t n_embd, float eps,
                   uint32_t n_tok);
 
@@ -1001,11 +1004,15 @@ extern "C" bool q4_cuda_moe_layer_nt(const uint8_t *base, uint64_t stride, uint3
     const uint32_t k1 = topk + (sh ? 1u : 0u), n_e = n_expert + (sh ? 1u : 0u);
     const uint64_t rows = (uint64_t)n_tok * k1;
     const uint32_t n_entries = (uint32_t)(rows < n_e ? rows : n_e);  // used experts <= rows
-    if (!q4b_rms_rows(d_x, d_norm_w, w.xn, n_embd, eps, n_tok)) return false;
-    if (!q4_hip_gemv_dd_n(Q4_T_F32, (const uint8_t *)d_router, n_expert, n_embd, w.xn, w.logits, 1.0f,
-                          n_tok))
-        return false;
-    if (!q4b_route_tokens(w.logits, w.ids, w.wts, n_tok, n_expert, topk)) return false;
+    // a few tokens: norm, router and top-k as one launch (same values); else the three launches
+    if (!q4b_route_small(d_x, d_norm_w, eps, d_router, n_expert, topk, n_embd, n_tok, w.xn, w.logits, w.ids,
+                         w.wts)) {
+        if (!q4b_rms_rows(d_x, d_norm_w, w.xn, n_embd, eps, n_tok)) return false;
+        if (!q4_hip_gemv_dd_n(Q4_T_F32, (const uint8_t *)d_router, n_expert, n_embd, w.xn, w.logits, 1.0f,
+                              n_tok))
+            return false;
+        if (!q4b_route_tokens(w.logits, w.ids, w.wts, n_tok, n_expert, topk)) return false;
+    }
     // the shared expert is one more pick (id n_expert, weight 1) of every token, added on the fly
     if (!launch_assign(w.ids, w.wts, w.atok, w.rsrc, w.rw, w.stg, w.stgn, nullptr, w.cbounds, n_tok, k1,
                        n_e, n_tok, n_e, topk, sh ? (int32_t)n_expert : -1))

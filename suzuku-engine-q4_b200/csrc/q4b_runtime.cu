@@ -22,6 +22,8 @@ bool q4b_window_warm();  // q4b_grouped.cu: scratch of the verify-window path
 bool q4b_elem_warm();    // q4b_elem.cu: lists of the per-token exec, rows of the 2..8-row GEMV
 void q4b_elem_shutdown();
 bool q4b_mmvq_warm();    // q4b_mmvq.cu: quantised rows of the dense 8-bit product
+bool q4b_route_small_warm();   // q4b_decode.cu: counter of the one-launch routing of a few tokens
+void q4b_route_small_shutdown();
 void q4b_mmvq_shutdown();
 bool q4b_wbuf_tiled(const void *p);
 bool q4b_mmq_tc_warm();  // q4b_grouped.cu: tensor-core grouped product (optional)
@@ -127,7 +129,7 @@ bool alloc_scratch() {
     Q4B_CHECK(cudaMalloc(&s.r_cnt, (size_t)Q4B_MAX_TOK * sizeof(int32_t)));
     Q4B_CHECK(cudaMalloc(&s.hbuf, nq * sizeof(float)));
     q4b_mmq_tc_warm();  // without it the grouped product stays on the CUDA cores
-    return q4b_fused_warm() && q4b_window_warm() && q4b_elem_warm() && q4b_mmvq_warm();
+    return q4b_fused_warm() && q4b_window_warm() && q4b_elem_warm() && q4b_mmvq_warm() && q4b_route_small_warm();
 }
 
 }  // namespace
@@ -229,6 +231,7 @@ extern "C" void q4_hip_shutdown(void) {
     }
     q4b_elem_shutdown();
     q4b_mmvq_shutdown();
+    q4b_route_small_shutdown();
     q4b_fused_shutdown();
     q4b_stack_forget_host(nullptr);
     cudaFree(s.xq);
