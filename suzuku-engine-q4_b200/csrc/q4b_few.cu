@@ -22,10 +22,12 @@
 
 namespace few {
 
-constexpr uint32_t NCW = 16;                 // warps = tiles per chunk
+constexpr uint32_t NCW = 16;                 // warps
+constexpr uint32_t TPW = 2;                  // tiles a warp takes from a chunk (loop and ring tests paid once for both)
+constexpr uint32_t CT = NCW * TPW;           // tiles per chunk
 constexpr uint32_t NT = NCW * 32;
-constexpr uint32_t CHUNK_BYTES = NCW * Q4B_TILE_BYTES;
-constexpr uint32_t NSTAGE = 9;
+constexpr uint32_t CHUNK_BYTES = CT * Q4B_TILE_BYTES;
+constexpr uint32_t NSTAGE = 5;
 constexpr uint32_t RB = 3;                   // activation rows held in registers
 constexpr uint32_t MAX_ENTRIES = 1024;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
@@ -135,7 +137,7 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
     if (n_live == 0) return;
     constexpr uint32_t B = BB;
     const uint32_t n_tiles = (a.w_rows * B) >> 3;
-    const uint32_t cpe = (n_tiles + NCW - 1u) / NCW;           // chunks per entry (the last may be short)
+    const uint32_t cpe = (n_tiles + CT - 1u) / CT;             // chunks per entry (the last may be short)
     // split by cost, not by chunk count: entries differ in rows
     {
         uint32_t v[2];
@@ -192,7 +194,7 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
         const uint32_t e = s.live[li];
         const uint8_t *src = a.w + (uint64_t)(a.act ? a.act[e] : (int32_t)e) * a.expert_stride +
                              (uint64_t)ch * CHUNK_BYTES;
-        const uint32_t bytes = min(NCW, n_tiles - ch * NCW) * Q4B_TILE_BYTES;
+        const uint32_t bytes = min(CT, n_tiles - ch * CT) * Q4B_TILE_BYTES;
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&s.full[st])),
                      "r"(bytes)
                      : "memory");
@@ -216,18 +218,20 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
     int q[RB][16];
     float dx[RB][2];
     int bs[RB][2];
+    float *orow[RB];               // the rows' places in dst
     uint32_t have_e = 0xffffffffu;
     int32_t r0 = 0, r1 = 0;
+    uint32_t nr = 0;               // rows held in registers: min(r1 - r0, RB)
     uint32_t limit = WAIT_LIMIT;   // after a wait gave up the rest run through with short waits
     uint32_t li = c_lo / cpe, ch = c_lo - li * cpe, st = 0, ph = 0;
     // sum over the lanes of a weight row, then one lane stores
-    auto finish = [&](float v, int32_t r, uint32_t wrow) {
+    auto finish = [&](float v, float *o) {
         v += __shfl_xor_sync(0xffffffffu, v, 1);
         v += __shfl_xor_sync(0xffffffffu, v, 2);
         if (B >= 2) v += __shfl_xor_sync(0xffffffffu, v, 4);
         if (B >= 4) v += __shfl_xor_sync(0xffffffffu, v, 8);
         if (B >= 8) v += __shfl_xor_sync(0xffffffffu, v, 16);
-        if ((lane & (lanes_per_row - 1u)) == 0) a.dst[(uint64_t)r * a.ld_dst + wrow] = v;
+        if ((lane & (lanes_per_row - 1u)) == 0) *o = v;
     };
     for (uint32_t c = c_lo, k = 0; c < c_hi; c++, k++) {
         if (tid == 0) produce(k + NSTAGE - 1u);
@@ -237,9 +241,10 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
             have_e = e;
             r0 = a.bounds[e];
             r1 = a.bounds[e + 1];
+            nr = min((uint32_t)(r1 - r0), RB);
 #pragma unroll
             for (uint32_t i = 0; i < RB; i++) {
-                if (r0 + (int32_t)i < r1) {
+                if (i < nr) {
                     const uint64_t r = (uint64_t)(r0 + (int32_t)i);
                     const int4 *qp = reinterpret_cast<const int4 *>(a.xq + r * a.cols + gcol * 32u);
                     const int4 v0 = __ldg(qp), v1 = __ldg(qp + 1), v2 = __ldg(qp + 2), v3 = __ldg(qp + 3);
@@ -251,77 +256,88 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
                     const int2 bv = __ldg(reinterpret_cast<const int2 *>(a.xbs + r * ngr + gcol));
                     dx[i][0] = dv.x, dx[i][1] = dv.y;
                     bs[i][0] = bv.x, bs[i][1] = bv.y;
+                    orow[i] = a.dst + r * a.ld_dst;
                 }
             }
         }
         if (!mbar_wait(&s.full[st], ph, limit, a.err)) limit = 1024u;
-        // decode this warp's tile into registers, then give the stage back
-        const uint8_t *tile = s.stage[st] + warp * Q4B_TILE_BYTES;
-        const uint4 qs = *reinterpret_cast<const uint4 *>(tile + Q4B_TILE_OFF_QS + 16u * lane);
-        const uint2 sg = *reinterpret_cast<const uint2 *>(tile + Q4B_TILE_OFF_SG + 8u * lane);
-        const uint32_t qh = *reinterpret_cast<const uint16_t *>(tile + Q4B_TILE_OFF_QH + 2u * lane);
-        const uint32_t sc = tile[Q4B_TILE_OFF_SC + lane];
-        const float d = __half2float(*reinterpret_cast<const __half *>(tile + 2u * blk));
-        __syncwarp();
-        if (lane == 0)
-            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s.empty[st])) : "memory");
-        uint32_t cw[16];
-        {
-            const uint32_t h0 = ((qh & 0xfu) * 0x00204081u) & 0x01010101u;
-            const uint32_t h1 = (((qh >> 4) & 0xfu) * 0x00204081u) & 0x01010101u;
-            const uint32_t h2 = (((qh >> 8) & 0xfu) * 0x00204081u) & 0x01010101u;
-            const uint32_t h3 = ((qh >> 12) * 0x00204081u) & 0x01010101u;
 #pragma unroll
-            for (int j = 0; j < 16; j++) {
-                const uint32_t wq = j < 4 ? qs.x : j < 8 ? qs.y : j < 12 ? qs.z : qs.w;
-                const uint32_t hh = j < 4 ? h0 : j < 8 ? h1 : j < 12 ? h2 : h3;
-                const uint32_t b = (uint32_t)j & 3u;
-                const uint32_t sel = b | ((4u + b) << 4) | ((12u + b) << 8) | ((12u + b) << 12);
-                const uint32_t idx = q4b_prmt(wq, hh, sel);
-                const uint32_t t = (j < 8 ? sg.x : sg.y) << (j & 7);
-                cw[j] = tab[idx * 32u] ^ q4b_prmt(t, t, 0xba98u);
+        for (uint32_t sub = 0; sub < TPW; sub++) {
+            // decode this warp's tile into registers; after the last one, give the stage back
+            const uint32_t tc = sub * NCW + warp;                      // tile within the chunk
+            const uint8_t *tile = s.stage[st] + tc * Q4B_TILE_BYTES;
+            const uint4 qs = *reinterpret_cast<const uint4 *>(tile + Q4B_TILE_OFF_QS + 16u * lane);
+            const uint2 sg = *reinterpret_cast<const uint2 *>(tile + Q4B_TILE_OFF_SG + 8u * lane);
+            const uint32_t qh = *reinterpret_cast<const uint16_t *>(tile + Q4B_TILE_OFF_QH + 2u * lane);
+            const uint32_t sc = tile[Q4B_TILE_OFF_SC + lane];
+            const float d = __half2float(*reinterpret_cast<const __half *>(tile + 2u * blk));
+            if (sub + 1u == TPW) {
+                __syncwarp();
+                if (lane == 0)
+                    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&s.empty[st])) : "memory");
             }
-        }
-        const int ls0 = (int)(2u * (sc & 15u) + 1u), ls1 = (int)(2u * (sc >> 4) + 1u);
-        const uint32_t ti = ch * NCW + warp;                       // tile within the matrix
-        const uint32_t wrow = ti * rows_per_tile + blk / B;        // this lane's weight row
-        if (ti < n_tiles) {                                        // a short last chunk leaves warps idle
+            uint32_t cw[16];
+            {
+                const uint32_t h0 = ((qh & 0xfu) * 0x00204081u) & 0x01010101u;
+                const uint32_t h1 = (((qh >> 4) & 0xfu) * 0x00204081u) & 0x01010101u;
+                const uint32_t h2 = (((qh >> 8) & 0xfu) * 0x00204081u) & 0x01010101u;
+                const uint32_t h3 = ((qh >> 12) * 0x00204081u) & 0x01010101u;
 #pragma unroll
-            for (uint32_t i = 0; i < RB; i++) {
-                if (r0 + (int32_t)i < r1) {                        // uniform over the warp
+                for (int j = 0; j < 16; j++) {
+                    const uint32_t wq = j < 4 ? qs.x : j < 8 ? qs.y : j < 12 ? qs.z : qs.w;
+                    const uint32_t hh = j < 4 ? h0 : j < 8 ? h1 : j < 12 ? h2 : h3;
+                    const uint32_t b = (uint32_t)j & 3u;
+                    const uint32_t sel = b | ((4u + b) << 4) | ((12u + b) << 8) | ((12u + b) << 12);
+                    const uint32_t idx = q4b_prmt(wq, hh, sel);
+                    const uint32_t t = (j < 8 ? sg.x : sg.y) << (j & 7);
+                    cw[j] = tab[idx * 32u] ^ q4b_prmt(t, t, 0xba98u);
+                }
+            }
+            const int ls0 = (int)(2u * (sc & 15u) + 1u), ls1 = (int)(2u * (sc >> 4) + 1u);
+            const uint32_t ti = ch * CT + tc;                          // tile within the matrix
+            const uint32_t wrow = ti * rows_per_tile + blk / B;        // this lane's weight row
+            if (ti < n_tiles) {                                        // a short last chunk leaves warps idle
+                // one row held in registers: same expression as grouped_rows_k
+                auto row_reg = [&](uint32_t i) {
                     int a0 = 0, a1 = 0;
 #pragma unroll
                     for (int j = 0; j < 8; j++) {
                         a0 = __dp4a((int)cw[j], q[i][j], a0);
                         a1 = __dp4a((int)cw[8 + j], q[i][8 + j], a1);
                     }
-                    // sum sign*(2c+1)*q = 2 sum c'q + sum q; same expression as grouped_rows_k
+                    // sum sign*(2c+1)*q = 2 sum c'q + sum q
                     const int I0 = 2 * a0 + bs[i][0], I1 = 2 * a1 + bs[i][1];
-                    finish(d * ((float)(I0 * ls0) * dx[i][0] + (float)(I1 * ls1) * dx[i][1]),
-                           r0 + (int32_t)i, wrow);
+                    finish(d * ((float)(I0 * ls0) * dx[i][0] + (float)(I1 * ls1) * dx[i][1]), orow[i] + wrow);
+                };
+                // straight-line code per row count: no per-row guards
+                row_reg(0);
+                if (nr >= 2u) {
+                    row_reg(1);
+                    if (nr == 3u) row_reg(2);
                 }
-            }
-            for (int32_t r = r0 + (int32_t)RB; r < r1; r++) {      // further rows: straight from memory
-                const int4 *qp = reinterpret_cast<const int4 *>(a.xq + (uint64_t)r * a.cols + gcol * 32u);
-                int a0 = 0, a1 = 0;
-                {
-                    const int4 v0 = __ldg(qp), v1 = __ldg(qp + 1);
-                    a0 = __dp4a((int)cw[0], v0.x, a0), a0 = __dp4a((int)cw[1], v0.y, a0);
-                    a0 = __dp4a((int)cw[2], v0.z, a0), a0 = __dp4a((int)cw[3], v0.w, a0);
-                    a0 = __dp4a((int)cw[4], v1.x, a0), a0 = __dp4a((int)cw[5], v1.y, a0);
-                    a0 = __dp4a((int)cw[6], v1.z, a0), a0 = __dp4a((int)cw[7], v1.w, a0);
+                for (int32_t r = r0 + (int32_t)RB; r < r1; r++) {      // further rows: straight from memory
+                    const int4 *qp = reinterpret_cast<const int4 *>(a.xq + (uint64_t)r * a.cols + gcol * 32u);
+                    int a0 = 0, a1 = 0;
+                    {
+                        const int4 v0 = __ldg(qp), v1 = __ldg(qp + 1);
+                        a0 = __dp4a((int)cw[0], v0.x, a0), a0 = __dp4a((int)cw[1], v0.y, a0);
+                        a0 = __dp4a((int)cw[2], v0.z, a0), a0 = __dp4a((int)cw[3], v0.w, a0);
+                        a0 = __dp4a((int)cw[4], v1.x, a0), a0 = __dp4a((int)cw[5], v1.y, a0);
+                        a0 = __dp4a((int)cw[6], v1.z, a0), a0 = __dp4a((int)cw[7], v1.w, a0);
+                    }
+                    {
+                        const int4 v2 = __ldg(qp + 2), v3 = __ldg(qp + 3);
+                        a1 = __dp4a((int)cw[8], v2.x, a1), a1 = __dp4a((int)cw[9], v2.y, a1);
+                        a1 = __dp4a((int)cw[10], v2.z, a1), a1 = __dp4a((int)cw[11], v2.w, a1);
+                        a1 = __dp4a((int)cw[12], v3.x, a1), a1 = __dp4a((int)cw[13], v3.y, a1);
+                        a1 = __dp4a((int)cw[14], v3.z, a1), a1 = __dp4a((int)cw[15], v3.w, a1);
+                    }
+                    const float2 dv = __ldg(reinterpret_cast<const float2 *>(a.xd + (uint64_t)r * ngr + gcol));
+                    const int2 bv = __ldg(reinterpret_cast<const int2 *>(a.xbs + (uint64_t)r * ngr + gcol));
+                    const int I0 = 2 * a0 + bv.x, I1 = 2 * a1 + bv.y;
+                    finish(d * ((float)(I0 * ls0) * dv.x + (float)(I1 * ls1) * dv.y),
+                           a.dst + (uint64_t)r * a.ld_dst + wrow);
                 }
-                {
-                    const int4 v2 = __ldg(qp + 2), v3 = __ldg(qp + 3);
-                    a1 = __dp4a((int)cw[8], v2.x, a1), a1 = __dp4a((int)cw[9], v2.y, a1);
-                    a1 = __dp4a((int)cw[10], v2.z, a1), a1 = __dp4a((int)cw[11], v2.w, a1);
-                    a1 = __dp4a((int)cw[12], v3.x, a1), a1 = __dp4a((int)cw[13], v3.y, a1);
-                    a1 = __dp4a((int)cw[14], v3.z, a1), a1 = __dp4a((int)cw[15], v3.w, a1);
-                }
-                const float2 dv = __ldg(reinterpret_cast<const float2 *>(a.xd + (uint64_t)r * ngr + gcol));
-                const int2 bv = __ldg(reinterpret_cast<const int2 *>(a.xbs + (uint64_t)r * ngr + gcol));
-                const int I0 = 2 * a0 + bv.x, I1 = 2 * a1 + bv.y;
-                finish(d * ((float)(I0 * ls0) * dv.x + (float)(I1 * ls1) * dv.y), r, wrow);
             }
         }
         if (++ch == cpe) ch = 0, li++;
