@@ -7,15 +7,20 @@
 // the general form; this kernel needs the tiled arena format and 1, 2, 4 or 8
 // super-blocks per weight row.
 //
-// Work: the live entries (those with rows) times the matrix's chunks of 16 tiles
-// (14,080 contiguous bytes; the last chunk of a matrix may be shorter).  CTAs split
+// Work: the live entries (those with rows) times the matrix's chunks of 64 tiles
+// (56,320 contiguous bytes; the last chunk of a matrix may be shorter).  CTAs split
 // that list by estimated cost into contiguous shares, so a CTA stays on one expert
-// for many chunks.  One lane keeps a 9-stage ring of chunks in flight (full/empty
-// mbarriers); each of the 16 warps takes one tile of a chunk: lane l decodes block
-// l/4, groups 2(l%4) and 2(l%4)+1 into registers, releases the stage, and dots the
-// decoded codes with the expert's activation rows.  The first three rows' bytes for
-// exactly those 64 columns stay in registers from tile to tile (they change only
-// when the CTA moves to the next expert); further rows come from L1/L2 per tile.
+// for many chunks.  One lane keeps two chunks in flight (full/empty mbarriers); each
+// of the 16 warps takes four tiles of a chunk, one after the other: lane l decodes
+// block l/4, groups 2(l%4) and 2(l%4)+1 into registers and dots the decoded codes
+// with the expert's activation rows; after its last tile's fields are read the warp
+// releases the stage.  The first three rows' bytes for exactly those 64 columns stay
+// in registers from tile to tile (they change only when the CTA moves to the next
+// expert); further rows come from L1/L2 per tile.
+// The kernel is bound by instruction issue, so what is paid per loop trip counts:
+// measured on 48 layers of 64 tokens (ms): one tile per trip with row guards 18.6;
+// straight-line code per row count 16.8; two tiles per trip (5 chunks in flight)
+// 16.0, three (3) 15.4, four (2) 14.8, five (2) 15.5.
 // 16 warps x 128 registers: measured faster than more warps with fewer registers
 // (a few spilled registers cost more here than the lost occupancy).
 #include "q4b_tile.cuh"
@@ -23,11 +28,11 @@
 namespace few {
 
 constexpr uint32_t NCW = 16;                 // warps
-constexpr uint32_t TPW = 2;                  // tiles a warp takes from a chunk (loop and ring tests paid once for both)
+constexpr uint32_t TPW = 4;                  // tiles a warp takes from a chunk (loop and ring tests paid once for all)
 constexpr uint32_t CT = NCW * TPW;           // tiles per chunk
 constexpr uint32_t NT = NCW * 32;
 constexpr uint32_t CHUNK_BYTES = CT * Q4B_TILE_BYTES;
-constexpr uint32_t NSTAGE = 5;
+constexpr uint32_t NSTAGE = 2;
 constexpr uint32_t RB = 3;                   // activation rows held in registers
 constexpr uint32_t MAX_ENTRIES = 1024;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;
