@@ -25,6 +25,7 @@ N >= 2 (one process per GPU, torchrun environment): config 4, expert-parallel
 decode of 64 tokens through 48 layers, strong scaling.
 """
 import argparse
+import faulthandler
 import atexit
 import ctypes
 import json
@@ -618,33 +619,108 @@ def cpu_layers_tokens(ref, layers, x, n_tok, budget_s, chain=True):
             "experts_ms": 1e3 * (t - t_router) / lt, "omp_threads": int(os.environ.get("OMP_NUM_THREADS", "1"))}
 
 
+# Every CPU leg runs in a child process.  The reference's worker pool is its own code, run unmodified,
+# and a run of small jobs has been seen not to return from it (about one default run in three hung in
+# the one-expert jobs of config 0); a child can be given a time limit and tried again, the parent cannot.
+_CPU_DIRS = []
+
+
+def _cpu_dir():
+    import shutil
+    import tempfile
+    base = "/dev/shm" if os.path.isdir("/dev/shm") and shutil.disk_usage("/dev/shm").free > (4 << 30) else None
+    d = tempfile.mkdtemp(prefix="q4b_cpu_", dir=base)
+    _CPU_DIRS.append(d)
+    atexit.register(shutil.rmtree, d, True)
+    return d
+
+
+def dump_layers(layers):
+    """The layers' tensors as .npy files a child maps (two layers: 1.4 GB); returns the directory."""
+    d = _cpu_dir()
+    for i, L in enumerate(layers):
+        for k in ("experts", "shared", "router", "norm_w"):
+            np.save(os.path.join(d, "l%d_%s.npy" % (i, k)), np.ascontiguousarray(L[k]))
+    return d
+
+
+def load_layers(d):
+    out, i = [], 0
+    while os.path.exists(os.path.join(d, "l%d_experts.npy" % i)):
+        out.append({k: np.load(os.path.join(d, "l%d_%s.npy" % (i, k)), mmap_mode="r")
+                    for k in ("experts", "shared", "router", "norm_w")})
+        i += 1
+    return out
+
+
+def cpu_child(kind, seconds, layers_dir=None, x=None, n_tok=1, chain=True, env=None, extra=()):
+    """One CPU leg in a child: kind 'layers' (cpu_layers_tokens), 'config0' (cpu_config0) or 'arm'
+    (the --impl reference loop).  Weights from layers_dir, else generated on the host.  Returns the
+    child's JSON object, or {"unavailable": why} after two attempts."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--cpu-probe", "--cpu-kind", kind, "--cpu-seconds",
+           str(seconds), "--cpu-tokens", str(n_tok)] + list(extra)
+    if not chain:
+        cmd.append("--cpu-nochain")
+    if layers_dir:
+        cmd += ["--cpu-dir", layers_dir]
+        if x is not None:
+            np.save(os.path.join(layers_dir, "x.npy"), np.ascontiguousarray(x, np.float32))
+    limit = 120 + 8 * float(seconds)
+    why = "not run"
+    for _ in (1, 2):
+        try:
+            r = subprocess.run(cmd, env=env or os.environ, capture_output=True, text=True, timeout=limit)
+            lines = [ln for ln in r.stdout.splitlines() if ln.startswith("{")]
+            if lines:
+                return json.loads(lines[-1])
+            why = "child exited %d: %s" % (r.returncode, r.stderr.strip()[-300:])
+        except subprocess.TimeoutExpired:
+            why = "the reference's worker pool did not return within %d s (tried twice)" % limit
+    return {"unavailable": why}
+
+
 def cpu_probe_main(a):
-    """Child process of the default run: config 1 on the CPU path with the OpenMP settings the
-    parent put into the environment, host-generated weights; prints one JSON object."""
+    """The child: one CPU leg, one JSON object on stdout."""
     pkg = entry.load_package()
     ref = ref_lib()
     if ref is None:
         print(json.dumps({"unavailable": "compiled reference CPU path (oracle/_ref) not present"}))
         return
-    layers = [pkg.synth.layer(SEED + 17 * l, N_EXPERT, N_EMBD, N_FF) for l in range(2)]
-    x = pkg.synth.hidden(7, 64, N_EMBD)
-    d = cpu_layers_tokens(ref, layers, x, 1, a.cpu_seconds)
-    print(json.dumps({k: d[k] for k in ("value", "ms_per_step", "router_ms", "experts_ms", "cores", "omp_threads")}))
+    if a.cpu_dir:
+        layers = load_layers(a.cpu_dir)
+        xp = os.path.join(a.cpu_dir, "x.npy")
+        x = np.load(xp) if os.path.exists(xp) else pkg.synth.hidden(7, 64, N_EMBD)
+    else:
+        layers = [pkg.synth.layer(SEED + 17 * l, N_EXPERT, N_EMBD, N_FF) for l in range(2)]
+        x = pkg.synth.hidden(7, 64, N_EMBD)
+    if a.cpu_kind == "config0":
+        d = cpu_config0(ref, layers[0], x, a.cpu_seconds)
+    elif a.cpu_kind == "arm":
+        # the --impl reference loop: warm-up, then `steps` timed samples of `jobs` layer jobs each
+        xs = x[:a.cpu_tokens]
+        ref.time_layers_win(layers, TOPK, 2, xs, N_EMBD, N_FF, True, EPS)
+        for _ in range(a.cpu_warm):
+            ref.time_layers_win(layers, TOPK, a.cpu_jobs, xs, N_EMBD, N_FF, True, EPS)
+        t = t_router = 0.0
+        for _ in range(a.cpu_steps):
+            dt, dr, _y = ref.time_layers_win(layers, TOPK, a.cpu_jobs, xs, N_EMBD, N_FF, True, EPS)
+            t += dt
+            t_router += dr
+        d = {"t": t, "t_router": t_router, "cores": ref.threads(), "cpu_model": cpu_model(),
+             "omp_threads": int(os.environ.get("OMP_NUM_THREADS", "1"))}
+    else:
+        d = cpu_layers_tokens(ref, layers, x, a.cpu_tokens, a.cpu_seconds, chain=not a.cpu_nochain)
+    print(json.dumps(d))
 
 
 def cpu_probe_passive_omp(seconds):
-    """The same CPU arm with a small passive OpenMP team for the router product (the default
-    arm keeps it on one thread), so that choice is visible in numbers."""
-    env = dict(os.environ, OMP_NUM_THREADS="4", OMP_WAIT_POLICY="passive")
-    try:
-        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--cpu-probe", "--cpu-seconds", str(seconds)],
-                           env=env, capture_output=True, text=True, timeout=240)
-        line = [ln for ln in r.stdout.splitlines() if ln.startswith("{")][-1]
-        d = json.loads(line)
+    """The config-1 CPU arm with a small passive OpenMP team for the router product (the default
+    arm keeps it on one thread), so that choice is visible in numbers; host-generated weights."""
+    d = cpu_child("layers", seconds, env=dict(os.environ, OMP_NUM_THREADS="4", OMP_WAIT_POLICY="passive"))
+    if "unavailable" not in d:
+        d = {k: d[k] for k in ("value", "ms_per_step", "router_ms", "experts_ms", "cores", "omp_threads")}
         d["omp_wait_policy"] = "passive"
-        return d
-    except Exception as e:   # the figure is an extra: its absence must not fail the run
-        return {"unavailable": "%s" % e}
+    return d
 
 
 def cpu_config0(ref, layer, x, budget_s):
@@ -731,10 +807,8 @@ def measure_config0(pkg, model, ref_layer=None, cpu_s=0.0):
               "e2e": {"value": 1e3 / ms_e2e, "unit": "expert-tok/s", "h2d_bytes_per_step": N_EMBD * 4,
                       "d2h_bytes_per_step": N_EMBD * 4},
               "roofline": roof_hbm(PACK, ms * 1e-3, "whole unit (launch chain)"), "cpu_baseline": None}
-    if ref_layer is not None and cpu_s > 0:
-        ref = ref_lib()
-        if ref is not None:
-            entry_["cpu_baseline"] = cpu_config0(ref, ref_layer, pkg.synth.hidden(7, 64, N_EMBD), cpu_s)
+    if ref_layer is not None and cpu_s > 0:     # ref_layer: the directory of the dumped layers
+        entry_["cpu_baseline"] = cpu_child("config0", cpu_s, ref_layer, pkg.synth.hidden(7, 64, N_EMBD))
     return entry_
 
 
@@ -790,15 +864,13 @@ def measure_batch(pkg, model, kind, steps, warmup, cpu_layers=None, cpu_s=0.0):
                    "d2h_bytes_per_step": job.nb},
            "roofline": roof, "cpu_baseline": None}
     if kind == "prefill" and cpu_s > 0:     # the skewed routers
-        cpu_layers = model.host_layers(range(min(2, model.n_layers)))
-    if cpu_layers is not None and cpu_s > 0:
-        ref = ref_lib()
-        if ref is not None:
-            n_tok = min(tokens, 64 if kind != "prefill" else 160)
-            cb = cpu_layers_tokens(ref, cpu_layers, x_all, n_tok, cpu_s, chain=(kind != "prefill"))
-            if n_tok != tokens:
-                cb["sample"] += "; %d of the step's %d tokens" % (n_tok, tokens)
-            out["cpu_baseline"] = cb
+        cpu_layers = dump_layers(model.host_layers(range(min(2, model.n_layers))))
+    if cpu_layers is not None and cpu_s > 0:    # cpu_layers: the directory of the dumped layers
+        n_tok = min(tokens, 64 if kind != "prefill" else 160)
+        cb = cpu_child("layers", cpu_s, cpu_layers, x_all[:n_tok], n_tok, chain=(kind != "prefill"))
+        if n_tok != tokens and "sample" in cb:
+            cb["sample"] += "; %d of the step's %d tokens" % (n_tok, tokens)
+        out["cpu_baseline"] = cb
     job.release()
     return out
 
@@ -947,12 +1019,6 @@ def run_reference(a, pkg, rank, world, warmup):
     step is a bounded sample of the workload.  Rank 0 alone runs it."""
     if rank != 0:
         return
-    ref = ref_lib()
-    if ref is None:
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "compiled reference CPU path (oracle/_ref) not present"}))
-        return
-    layers = [pkg.synth.layer(SEED + 17 * l, N_EXPERT, N_EMBD, N_FF) for l in range(2)]
     steps = min(a.steps, 200)
     if world == 1:
         config, n_tok, jobs, scaling = CONFIG1, 1, 64, "weak"
@@ -961,25 +1027,23 @@ def run_reference(a, pkg, rank, world, warmup):
         config, n_tok, jobs, scaling = config4(world, a.layers or N_LAYERS), EP_TOKENS, 4, "strong"
         what = "%d layers of the step's %d per step, all 64 tokens, over 2 layers of weights" % (
             jobs, a.layers or N_LAYERS)
-    x = pkg.synth.hidden(7, 64, N_EMBD)[:n_tok]
-    ref.time_layers_win(layers, TOPK, 2, x, N_EMBD, N_FF, True, EPS)
-    for _ in range(min(warmup, 3)):
-        ref.time_layers_win(layers, TOPK, jobs, x, N_EMBD, N_FF, True, EPS)
-    t, t_router = 0.0, 0.0
-    for _ in range(steps):
-        dt, dr, _ = ref.time_layers_win(layers, TOPK, jobs, x, N_EMBD, N_FF, True, EPS)
-        t += dt
-        t_router += dr
+    # in a child with a time limit (the pool is the reference's own code and has been seen not to return)
+    d = cpu_child("arm", 0.25 * steps, None, None, n_tok,
+                  extra=["--cpu-jobs", str(jobs), "--cpu-steps", str(steps), "--cpu-warm", str(min(warmup, 3))])
+    if "unavailable" in d:
+        print(json.dumps({"impl": "reference", "unavailable": d["unavailable"]}))
+        return
+    t, t_router = d["t"], d["t_router"]
     lt = steps * jobs * n_tok
     val = lt / t
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": a.gpus, "steps": steps,
         "warmup": warmup, "ms_per_step": 1e3 * t / steps, "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": DTYPE, "data": "synthetic", "config": config,
-        "cpu_baseline": {"value": val, "unit": UNIT, "cores": ref.threads(), "kind": "reference",
-                         "cpu_model": cpu_model(), "sample": "%d steps x %s" % (steps, what),
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": d["cores"], "kind": "reference",
+                         "cpu_model": d["cpu_model"], "sample": "%d steps x %s" % (steps, what),
                          "router_ms": 1e3 * t_router / lt, "experts_ms": 1e3 * (t - t_router) / lt,
-                         "omp_threads": int(os.environ.get("OMP_NUM_THREADS", "1"))},
+                         "omp_threads": d["omp_threads"]},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
@@ -1017,10 +1081,9 @@ def run_config1(a, pkg, local, warmup):
     tr = read_traffic("decode_stack_kernel.json")
     cpu_layers, cpu, details = None, None, {}
     if not a.no_cpu:
-        cpu_layers = model.host_layers(range(min(2, model.n_layers)))
-        ref = ref_lib()
-        if ref is not None:
-            cpu = cpu_layers_tokens(ref, cpu_layers, d1.x_host, 1, a.cpu_seconds)
+        cpu_layers = dump_layers(model.host_layers(range(min(2, model.n_layers))))
+        cpu = cpu_child("layers", a.cpu_seconds, cpu_layers, d1.x_host, 1)
+        if "unavailable" not in cpu:
             cpu["jobs_router_on_a_passive_openmp_team"] = cpu_probe_passive_omp(min(a.cpu_seconds, 5.0))
     details["repeats"] = repeats
     details["timed_ms"] = timed_ms
@@ -1037,7 +1100,7 @@ def run_config1(a, pkg, local, warmup):
     d1.release()
     if not a.no_others:
         cs = 0.0 if a.no_cpu else min(a.cpu_seconds, 4.0)
-        others = [measure_config0(pkg, model, cpu_layers[0] if cpu_layers else None, cs),
+        others = [measure_config0(pkg, model, cpu_layers, cs),
                   measure_batch(pkg, model, "verify", 5, 3, cpu_layers, cs),
                   measure_batch(pkg, model, "ep1", 3, 3, cpu_layers, cs)]
         model.release()
@@ -1074,8 +1137,20 @@ def main():
     ap.add_argument("--no-others", action="store_true", help="config 1 only: skip details.other_workloads")
     ap.add_argument("--workload", default="auto", choices=["auto", "config0", "verify", "prefill", "ep"],
                     help="one of the other configurations alone on one GPU (its entry is printed)")
-    ap.add_argument("--cpu-probe", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--cpu-probe", action="store_true", help=argparse.SUPPRESS)       # the child of a CPU leg
+    ap.add_argument("--cpu-kind", default="layers", help=argparse.SUPPRESS)
+    ap.add_argument("--cpu-dir", default="", help=argparse.SUPPRESS)
+    ap.add_argument("--cpu-tokens", type=int, default=1, help=argparse.SUPPRESS)
+    ap.add_argument("--cpu-nochain", action="store_true", help=argparse.SUPPRESS)
+    ap.add_argument("--cpu-jobs", type=int, default=64, help=argparse.SUPPRESS)
+    ap.add_argument("--cpu-steps", type=int, default=20, help=argparse.SUPPRESS)
+    ap.add_argument("--cpu-warm", type=int, default=3, help=argparse.SUPPRESS)
+    ap.add_argument("--watchdog-s", type=int, default=900,
+                    help="dump every thread's stack to stderr and exit if the run takes longer than this")
     a = ap.parse_args()
+    # A run that does not end is worse than one that fails: after 15 minutes say where every thread is
+    # (stderr) and leave.  The default run takes about a minute.
+    faulthandler.dump_traceback_later(a.watchdog_s, exit=True)
     rank, world, local = dist_setup()
     warmup = max(a.warmup, 3)
     if world > 1:       # one process per GPU: each sees only its own device
@@ -1100,9 +1175,9 @@ def main():
             out = measure_batch(pkg, model, "prefill", min(a.steps, 20), warmup, None, cs)
         else:
             model = Model(dev, a.layers)
-            cl = model.host_layers(range(min(2, a.layers))) if cs else None
+            cl = dump_layers(model.host_layers(range(min(2, a.layers)))) if cs else None
             if a.workload == "config0":
-                out = measure_config0(pkg, model, cl[0] if cl else None, cs)
+                out = measure_config0(pkg, model, cl, cs)
             else:
                 out = measure_batch(pkg, model, "verify" if a.workload == "verify" else "ep1", min(a.steps, 20),
                                     warmup, cl, cs)

@@ -35,7 +35,7 @@ constexpr uint32_t CHUNK_BYTES = CT * Q4B_TILE_BYTES;
 constexpr uint32_t NSTAGE = 2;
 constexpr uint32_t RB = 3;                   // activation rows held in registers
 constexpr uint32_t MAX_ENTRIES = 1024;
-constexpr uint32_t WAIT_LIMIT = 1u << 21;
+constexpr uint32_t WAIT_LIMIT = 1u << 18;    // tries of at most 2 us each before a wait gives up: half a second
 constexpr uint32_t ERR_FEW = 0x800u;
 
 struct Smem {
@@ -59,10 +59,10 @@ __device__ __forceinline__ bool mbar_wait(unsigned long long *bar, uint32_t pari
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok)
-            : "r"(a), "r"(parity)
+            : "r"(a), "r"(parity), "r"(2000u)   // parked for at most 2 us per try, so the bound is in time
             : "memory");
         if (ok) return true;
     }
