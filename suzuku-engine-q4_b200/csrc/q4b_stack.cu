@@ -58,7 +58,7 @@ constexpr uint32_t MAX_SH = 8;        // shared-expert units per CTA
 constexpr uint32_t MAX_DT = 72;       // down tiles per CTA
 constexpr uint32_t MAX_RROWS = 4;     // router rows per CTA
 constexpr uint32_t MAX_LAYERS = 64;   // layers per launch (epochs are spaced by this)
-constexpr uint32_t MBAR_LIMIT = 400000u;    // tries (at most 1 us each, 40 ns apart) before an mbarrier wait gives up
+constexpr uint32_t MBAR_LIMIT = 1000000u;   // polls before an mbarrier wait gives up (or a third of a second)
 constexpr uint32_t POLL_LIMIT = 400000u;    // default polls before an exchange-word wait gives up
 
 // mbarrier slots
@@ -136,18 +136,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(1000u)   // parked for at most a microsecond per try
+        : "r"(smem_u32(bar)), "r"(parity)
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after MBAR_LIMIT polls and records it.
+// Bounded wait: gives up after MBAR_LIMIT polls or a third of a second and records it.
 __device__ __forceinline__ void mbar_wait(uint64_t *bar, uint32_t parity, uint32_t *err) {
+    unsigned long long t0 = 0;
     for (uint32_t i = 0; i < MBAR_LIMIT; i++) {
         if (mbar_try_wait(bar, parity)) return;
         __nanosleep(40);
+        if ((i & 1023u) == 1023u) {
+            unsigned long long t;
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > 300000000ull) break;
+        }
     }
     atomicOr(err, ERR_MBAR);
 }
