@@ -51,6 +51,14 @@ bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64_t og, uint
                          int has_shared, const float *d_x, const float *d_norm_w, float eps,
                          const float *d_router, uint32_t n_expert, uint32_t topk, uint32_t n_embd,
                          uint32_t n_ff, uint32_t t_local, float *d_y, void *d_ws, uint64_t ws_bytes);
+/* The all-reduce of q4_cuda_ep_layer_ar: 1 (default) = the library's own kernel over peer memory
+ * (every rank exports one buffer through CUDA IPC at q4_cuda_ep_init; a rank's kernel copies its
+ * partial rows there, signals every rank with plain stores, waits -- bounded -- for the others'
+ * signals and sums the ranks' rows in rank order with plain loads over NVLink), used when every
+ * rank could map every other rank's buffer; 0 = ncclAllReduce.  Returns the mode in effect; every
+ * rank must make the same call.  q4_cuda_ep_error: 0, or 0x1000 after a wait ran out (synchronises). */
+int q4_cuda_ep_allreduce_mode(int mode);
+uint32_t q4_cuda_ep_error(void);
 /* Cost of one layer's collectives alone, microseconds (mean of iters rounds with the layer's
  * payload sizes): out2[0] the two exchanges of q4_cuda_ep_layer, out2[1] the all-reduce of
  * q4_cuda_ep_layer_ar.  Synchronises; d_ws as for the layer calls. */

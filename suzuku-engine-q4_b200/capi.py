@@ -249,6 +249,8 @@ EP_SIGNATURES = {
     "q4_cuda_ep_rank": (C.c_int, []),
     "q4_cuda_ep_world": (C.c_int, []),
     "q4_cuda_ep_allreduce_max": (b, [vp]),
+    "q4_cuda_ep_allreduce_mode": (C.c_int, [C.c_int]),
+    "q4_cuda_ep_error": (u32, []),
     "q4_cuda_ep_layer_ws_bytes": (u64, [u32, u32, u32, u32, u32, u32]),
     "q4_cuda_ep_layer": (b, [vp, u64, u64, u64, u64, C.c_int, vp, vp, f32, vp, u32, u32, u32, u32, u32,
                              vp, vp, u64]),

@@ -56,6 +56,108 @@ __global__ void ep_sum_k(const float *__restrict__ recv, float *__restrict__ y, 
     y[i] = acc;
 }
 
+// ---- the layer's all-reduce over peer memory (one kernel, no library call) ----
+// Every rank exports one buffer (two copies of up to AR_MAX_ELEMS floats, then ready words) through
+// CUDA IPC; the others map it.  The kernel on rank r: (1) copies its partial rows into its exported
+// buffer (copy p = epoch & 1), fences at system scope, and the CTA that finishes last stores the
+// epoch into word [p][r] of EVERY rank's ready words (plain stores to peer memory); (2) waits,
+// bounded in time, until its own ready words [p][0..G) all show the epoch; (3) every thread sums its
+// elements over the ranks' buffers in rank order (plain loads from peer memory over NVLink), so all
+// ranks end with the same bits; (4) the CTA that finishes last publishes the epoch for the next
+// launch.  Two copies suffice: a rank can overwrite copy p only two launches later, and it gets
+// there only after every peer has signalled the launch in between, which a peer does after it has
+// finished reading copy p.  No multicast, no TMA: plain ld/st on mapped peer memory.
+constexpr uint32_t AR_MAX_ELEMS = 64u * 4096u;
+constexpr uint32_t AR_MAX_RANKS = 8;
+constexpr uint32_t AR_CTAS = 32, AR_THREADS = 512;
+constexpr uint32_t AR_ERR = 0x1000u;   // bit of the device error word: a peer's rows did not come in time
+struct ArArgs {
+    const float *src;
+    float *dst;
+    uint32_t n4;                       // float4 elements
+    uint32_t world, rank;
+    float *bufs[AR_MAX_RANKS];         // every rank's exported buffer (own: local pointer)
+    uint32_t *ready[AR_MAX_RANKS];     // every rank's ready words [2][AR_MAX_RANKS]
+    uint32_t *ctl;                     // local: [0] epoch of the last finished launch, [1] copies done, [2] CTAs done, [3] error
+    unsigned long long wait_ns;
+};
+__global__ void __launch_bounds__(AR_THREADS) ep_allreduce_k(const __grid_constant__ ArArgs a) {
+    __shared__ uint32_t s_epoch;
+    const uint32_t tid = threadIdx.x;
+    if (tid == 0) {
+        uint32_t e;
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(e) : "l"(a.ctl) : "memory");
+        s_epoch = e + 1u;
+    }
+    __syncthreads();
+    const uint32_t epoch = s_epoch, p = epoch & 1u;
+    const uint32_t gtid = blockIdx.x * AR_THREADS + tid, gsz = gridDim.x * AR_THREADS;
+    float4 *mine = reinterpret_cast<float4 *>(a.bufs[a.rank]) + (size_t)p * (AR_MAX_ELEMS / 4u);
+    const float4 *src4 = reinterpret_cast<const float4 *>(a.src);
+    for (uint32_t i = gtid; i < a.n4; i += gsz) mine[i] = src4[i];
+    __threadfence_system();
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t old = atomicAdd(a.ctl + 1, 1u);
+        if (old % gridDim.x == gridDim.x - 1u) {   // every CTA's rows are out: tell every rank (this one too)
+            __threadfence_system();
+            for (uint32_t r = 0; r < a.world; r++)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.ready[r] + p * AR_MAX_RANKS + a.rank), "r"(epoch)
+                             : "memory");
+        }
+    }
+    if (tid < a.world) {
+        const uint32_t *w = a.ready[a.rank] + p * AR_MAX_RANKS + tid;
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+        for (uint32_t i = 0;; i++) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(w) : "memory");
+            if (v == epoch) break;
+            if ((i & 255u) == 255u) {
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+                if (t - t0 > a.wait_ns) {
+                    atomicOr(a.ctl + 3, AR_ERR);
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    float4 *dst4 = reinterpret_cast<float4 *>(a.dst);
+    for (uint32_t i = gtid; i < a.n4; i += gsz) {
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (uint32_t r = 0; r < a.world; r++) {
+            const float4 *b = reinterpret_cast<const float4 *>(a.bufs[r]) + (size_t)p * (AR_MAX_ELEMS / 4u) + i;
+            float4 v;
+            asm volatile("ld.volatile.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                         : "l"(b)
+                         : "memory");
+            acc.x += v.x, acc.y += v.y, acc.z += v.z, acc.w += v.w;
+        }
+        dst4[i] = acc;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t old = atomicAdd(a.ctl + 2, 1u);
+        if (old % gridDim.x == gridDim.x - 1u)
+            asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(a.ctl), "r"(epoch) : "memory");
+    }
+}
+
+struct ArState {
+    bool ok;
+    uint8_t *mem;                      // exported: [2][AR_MAX_ELEMS] floats | ready words
+    uint32_t *ctl;                     // local control words
+    float *bufs[AR_MAX_RANKS];
+    uint32_t *ready[AR_MAX_RANKS];
+    void *opened[AR_MAX_RANKS];
+} g_ar = {};
+constexpr size_t AR_BUF_BYTES = 2ull * AR_MAX_ELEMS * sizeof(float);
+constexpr size_t AR_MEM_BYTES = AR_BUF_BYTES + 256;
+
 struct EpWs {
     float *xn_l, *logits, *wts_l, *xn, *wts, *rw, *gu, *pd, *partial, *recv;
     int32_t *ids_l, *ids, *atok, *rsrc, *bounds;
@@ -94,6 +196,95 @@ EpWs carve(uint8_t *p, uint32_t world, uint32_t t_local, uint32_t topk, uint32_t
     return w;
 }
 
+int g_ar_mode = 1;   // 1: the peer-memory kernel where it was set up, 0: ncclAllReduce
+
+void ar_teardown() {
+    for (uint32_t r = 0; r < AR_MAX_RANKS; r++)
+        if (g_ar.opened[r]) cudaIpcCloseMemHandle(g_ar.opened[r]);
+    if (g_ar.mem) cudaFree(g_ar.mem);
+    if (g_ar.ctl) cudaFree(g_ar.ctl);
+    g_ar = ArState{};
+}
+
+// Maps every rank's exported buffer.  All ranks end with the same answer (a minimum over the ranks):
+// either every rank uses the peer kernel or none does.
+bool ar_setup() {
+    cudaStream_t st = (cudaStream_t)q4_hip_stream();
+    int ok = 1;
+    cudaIpcMemHandle_t mine;
+    memset(&mine, 0, sizeof mine);
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    if (g_world > (int)AR_MAX_RANKS || g_world < 2 || cudaMalloc(&g_ar.mem, AR_MEM_BYTES) != cudaSuccess ||
+        cudaMemset(g_ar.mem, 0, AR_MEM_BYTES) != cudaSuccess || cudaMalloc(&g_ar.ctl, 64) != cudaSuccess ||
+        cudaMemset(g_ar.ctl, 0, 64) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess ||
+        cudaIpcGetMemHandle(&mine, g_ar.mem) != cudaSuccess) {
+        cudaGetLastError();
+        ok = 0;
+    }
+    // the handles of all ranks, gathered through the communicator
+    uint8_t *d_all = (uint8_t *)q4_hip_malloc(64u * (size_t)g_world + 256);
+    cudaIpcMemHandle_t all[AR_MAX_RANKS];
+    memset(all, 0, sizeof all);
+    if (!d_all) return false;
+    bool gathered = g_world <= (int)AR_MAX_RANKS &&
+                    cudaMemcpy(d_all + 64 * g_rank, &mine, 64, cudaMemcpyHostToDevice) == cudaSuccess &&
+                    ncclAllGather(d_all + 64 * g_rank, d_all, 64, ncclUint8, g_comm, st) == ncclSuccess &&
+                    cudaStreamSynchronize(st) == cudaSuccess &&
+                    cudaMemcpy(all, d_all, 64u * (size_t)g_world, cudaMemcpyDeviceToHost) == cudaSuccess;
+    if (!gathered) ok = 0;
+    // every rank learns whether every rank got this far before anyone opens a handle
+    float v = (float)ok;
+    if (cudaMemcpy(g_scalar, &v, 4, cudaMemcpyHostToDevice) != cudaSuccess ||
+        ncclAllReduce(g_scalar, g_scalar, 1, ncclFloat, ncclMin, g_comm, st) != ncclSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess || cudaMemcpy(&v, g_scalar, 4, cudaMemcpyDeviceToHost) != cudaSuccess)
+        v = 0.f;
+    if (v >= 1.f) {
+        for (int r = 0; r < g_world && ok; r++) {
+            void *ptr = g_ar.mem;
+            if (r != g_rank) {
+                if (cudaIpcOpenMemHandle(&ptr, all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+                    cudaGetLastError();
+                    ok = 0;
+                    break;
+                }
+                g_ar.opened[r] = ptr;
+            }
+            g_ar.bufs[r] = (float *)ptr;
+            g_ar.ready[r] = (uint32_t *)((uint8_t *)ptr + AR_BUF_BYTES);
+        }
+        v = (float)ok;
+        if (cudaMemcpy(g_scalar, &v, 4, cudaMemcpyHostToDevice) != cudaSuccess ||
+            ncclAllReduce(g_scalar, g_scalar, 1, ncclFloat, ncclMin, g_comm, st) != ncclSuccess ||
+            cudaStreamSynchronize(st) != cudaSuccess ||
+            cudaMemcpy(&v, g_scalar, 4, cudaMemcpyDeviceToHost) != cudaSuccess)
+            v = 0.f;
+    }
+    q4_hip_free(d_all);
+    if (v < 1.f) {
+        ar_teardown();
+        return false;
+    }
+    g_ar.ok = true;
+    return true;
+}
+
+bool ar_launch(const float *src, float *dst, size_t n, cudaStream_t st) {
+    ArArgs a;
+    a.src = src;
+    a.dst = dst;
+    a.n4 = (uint32_t)(n / 4u);
+    a.world = (uint32_t)g_world;
+    a.rank = (uint32_t)g_rank;
+    for (uint32_t r = 0; r < AR_MAX_RANKS; r++) {
+        a.bufs[r] = g_ar.bufs[r];
+        a.ready[r] = g_ar.ready[r];
+    }
+    a.ctl = g_ar.ctl;
+    a.wait_ns = 2000000000ull;
+    ep_allreduce_k<<<AR_CTAS, AR_THREADS, 0, st>>>(a);
+    return cudaGetLastError() == cudaSuccess;
+}
+
 }  // namespace
 
 // ---- communicator ----
@@ -115,12 +306,30 @@ extern "C" bool q4_cuda_ep_init(const uint8_t *id128, int rank, int world) {
     g_rank = rank;
     g_world = world;
     g_scalar = (float *)q4_hip_malloc(256);
-    return g_scalar != nullptr;
+    if (!g_scalar) return false;
+    if (world > 1) (void)ar_setup();   // without it q4_cuda_ep_layer_ar keeps ncclAllReduce
+    return true;
+}
+// Which all-reduce q4_cuda_ep_layer_ar uses: 1 (default) the library's own kernel over mapped peer
+// memory where every rank could map every other rank's buffer, 0 ncclAllReduce.  Returns what is in
+// effect.  Every rank must make the same call.
+extern "C" int q4_cuda_ep_allreduce_mode(int mode) {
+    if (mode == 0 || mode == 1) g_ar_mode = mode;
+    return g_ar.ok && g_ar_mode ? 1 : 0;
+}
+// Error word of the peer all-reduce (0x1000: a peer's rows did not arrive within two seconds).  Synchronises.
+extern "C" uint32_t q4_cuda_ep_error(void) {
+    uint32_t e = 0;
+    if (!g_ar.ok) return 0;
+    q4_hip_sync();
+    if (cudaMemcpy(&e, g_ar.ctl + 3, 4, cudaMemcpyDeviceToHost) != cudaSuccess) return 0xffffffffu;
+    return e;
 }
 
 extern "C" void q4_cuda_ep_shutdown(void) {
     if (!g_comm) return;
     q4_hip_sync();
+    ar_teardown();
     ncclCommDestroy(g_comm);
     g_comm = nullptr;
     q4_hip_free(g_scalar);
@@ -257,7 +466,10 @@ extern "C" bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64
                        max_hint, rows, w.pd, n_embd))
         return false;
     if (!q4_cuda_expert_reduce_set(w.partial, w.pd, w.rsrc, w.rw, T, k1, n_embd)) return false;
-    EP_NCCL(ncclAllReduce(w.partial, d_y, (size_t)T * n_embd, ncclFloat, ncclSum, g_comm, st));
+    const size_t n = (size_t)T * n_embd;
+    if (g_ar.ok && g_ar_mode && n <= AR_MAX_ELEMS && (n % 4u) == 0 && (((uintptr_t)w.partial | (uintptr_t)d_y) & 15u) == 0)
+        return ar_launch(w.partial, d_y, n, st);
+    EP_NCCL(ncclAllReduce(w.partial, d_y, n, ncclFloat, ncclSum, g_comm, st));
     return true;
 }
 

@@ -104,6 +104,26 @@ def main():
     mine = ya[rank * T_LOCAL:(rank + 1) * T_LOCAL]
     assert np.linalg.norm(mine - ys[0]) <= 1e-5 * np.linalg.norm(ys[0])
     np.save(os.path.join(out_dir, "ya%d.npy" % rank), ya)
+    # the all-reduce itself: the library's kernel over mapped peer memory where every rank could map
+    # the others' buffers (mode 1), else ncclAllReduce.  Repeated calls give the same bits (sum in rank
+    # order; the two buffer copies alternate), and the two modes agree up to the order of the sum.
+    mode = ep.q4_cuda_ep_allreduce_mode(-1)
+    open(os.path.join(out_dir, "mode%d.txt" % rank), "w").write(str(mode))
+    for _ in range(5):
+        assert ep.q4_cuda_ep_layer_ar(base, stride, 0, F * rb, 2 * F * rb, 1, d_xa, d_norm, 1e-6, d_router,
+                                      E, K, H, F, T_LOCAL, d_ya, d_ws, ws)
+        dev.sync()
+        again = dev.download(d_ya, (world * T_LOCAL, H), np.float32)
+        if mode == 1:
+            assert np.array_equal(again.view(np.uint32), ya.view(np.uint32))
+    assert ep.q4_cuda_ep_error() == 0
+    assert ep.q4_cuda_ep_allreduce_mode(0) == 0
+    assert ep.q4_cuda_ep_layer_ar(base, stride, 0, F * rb, 2 * F * rb, 1, d_xa, d_norm, 1e-6, d_router,
+                                  E, K, H, F, T_LOCAL, d_ya, d_ws, ws)
+    dev.sync()
+    nccl = dev.download(d_ya, (world * T_LOCAL, H), np.float32)
+    assert np.linalg.norm(nccl - ya) <= 1e-6 * np.linalg.norm(ya)
+    assert ep.q4_cuda_ep_allreduce_mode(1) == mode
     f2 = (ctypes.c_float * 2)()
     assert ep.q4_cuda_ep_exchange_floor_us(T_LOCAL, H, K, E, F, d_ws, ws, 5, f2) and f2[0] > 0 and f2[1] > 0
     assert lib.q4_cuda_device_error() == 0

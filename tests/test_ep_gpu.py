@@ -58,6 +58,10 @@ def test_ep_layer_two_gpus(tmp_path, dev, pkg, oracle):
     # the one-collective form: every rank ends with all rows, the same on every rank
     ya = [np.load(os.path.join(str(tmp_path), "ya%d.npy" % r)) for r in range(world)]
     assert np.array_equal(ya[0], ya[1])
+    modes = [open(os.path.join(str(tmp_path), "mode%d.txt" % r)).read() for r in range(world)]
+    assert modes[0] == modes[1]
+    print("all-reduce of the one-collective form: %s" %
+          ("the library's kernel over peer memory" if modes[0] == "1" else "ncclAllReduce (peer buffers not mapped)"))
     for t in range(T):
         n0 = np.linalg.norm(y1[t])
         assert np.linalg.norm(ya[0][t] - y1[t]) / n0 < 1e-5
