@@ -72,7 +72,7 @@ CONFIG1 = {"workload": "config1: one MoE layer, decode batch 1, hidden 2048, ff 
 
 def config4(world, n_layers):
     return {"workload": "config4: expert-parallel decode, 64 tokens x %d MoE layers per step, 512 "
-                        "experts top-10 + shared, experts sharded %d-way over NCCL"
+                        "experts top-10 + shared, experts sharded %d-way, one process per GPU"
                         % (n_layers, world),
             "l2": "inputs larger than L2: a step reads %d layers of weights" % n_layers,
             "tokens_per_rank": 64 // world, "experts_per_rank": N_EXPERT // world}
@@ -946,6 +946,21 @@ def run_ep(a, pkg, rank, world, local, warmup):
     y_ep = job.output() if rank == 0 else None
     details = {"cuda_graph": graphed, "repeats": repeats, "exchange_floor_us": floor,
                "form": "every rank holds all 64 token rows; one all-reduce of the partial rows per layer"}
+    if ep is not None:
+        peer = ep.q4_cuda_ep_allreduce_mode(-1) == 1
+        details["all_reduce"] = ("the library's kernel over IPC-mapped peer memory (plain loads and stores over NVLink, "
+                                 "bounded waits)" if peer else "ncclAllReduce (peer buffers could not be mapped)")
+        e2 = ep.q4_cuda_ep_error()
+        if e2:
+            raise SystemExit("expert-parallel error word %#x" % e2)
+        if peer:    # the same job with ncclAllReduce in place of the kernel, for comparison
+            ep.q4_cuda_ep_allreduce_mode(0)
+            job_n = BatchJob(pkg, model, ep, rank, world, EP_TOKENS, range(n_layers))
+            ms_n, _, _, _ = time_job(job_n, a.steps, warmup, barrier_max, min_ms=20.0)
+            details["with_nccl_all_reduce"] = {"ms_per_step": ms_n, "value": EP_TOKENS * n_layers / (ms_n * 1e-3),
+                                               "unit": UNIT}
+            job_n.release()
+            ep.q4_cuda_ep_allreduce_mode(1)
     if ep is not None:
         # the two-exchange form of the same job (tokens split over the ranks), for comparison
         job2 = BatchJob(pkg, model, ep, rank, world, EP_TOKENS, range(n_layers), form="a2a")
