@@ -948,19 +948,20 @@ def run_ep(a, pkg, rank, world, local, warmup):
                "form": "every rank holds all 64 token rows; one all-reduce of the partial rows per layer"}
     if ep is not None:
         peer = ep.q4_cuda_ep_allreduce_mode(-1) == 1
-        details["all_reduce"] = ("the library's kernel over IPC-mapped peer memory (plain loads and stores over NVLink, "
-                                 "bounded waits)" if peer else "ncclAllReduce (peer buffers could not be mapped)")
+        names = {True: "the library's kernel over IPC-mapped peer memory (plain loads and stores over NVLink, bounded "
+                       "waits)", False: "ncclAllReduce"}
+        details["all_reduce"] = names[peer]
         e2 = ep.q4_cuda_ep_error()
         if e2:
             raise SystemExit("expert-parallel error word %#x" % e2)
-        if peer:    # the same job with ncclAllReduce in place of the kernel, for comparison
-            ep.q4_cuda_ep_allreduce_mode(0)
+        # the same job with the other all-reduce, for comparison
+        if ep.q4_cuda_ep_allreduce_mode(0 if peer else 1) == (0 if peer else 1):
             job_n = BatchJob(pkg, model, ep, rank, world, EP_TOKENS, range(n_layers))
             ms_n, _, _, _ = time_job(job_n, a.steps, warmup, barrier_max, min_ms=20.0)
-            details["with_nccl_all_reduce"] = {"ms_per_step": ms_n, "value": EP_TOKENS * n_layers / (ms_n * 1e-3),
-                                               "unit": UNIT}
+            details["with_the_other_all_reduce"] = {"all_reduce": names[not peer], "ms_per_step": ms_n,
+                                                    "value": EP_TOKENS * n_layers / (ms_n * 1e-3), "unit": UNIT}
             job_n.release()
-            ep.q4_cuda_ep_allreduce_mode(1)
+        ep.q4_cuda_ep_allreduce_mode(2)
     if ep is not None:
         # the two-exchange form of the same job (tokens split over the ranks), for comparison
         job2 = BatchJob(pkg, model, ep, rank, world, EP_TOKENS, range(n_layers), form="a2a")

@@ -51,7 +51,8 @@ bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64_t og, uint
                          int has_shared, const float *d_x, const float *d_norm_w, float eps,
                          const float *d_router, uint32_t n_expert, uint32_t topk, uint32_t n_embd,
                          uint32_t n_ff, uint32_t t_local, float *d_y, void *d_ws, uint64_t ws_bytes);
-/* The all-reduce of q4_cuda_ep_layer_ar: 1 (default) = the library's own kernel over peer memory
+/* The all-reduce of q4_cuda_ep_layer_ar: mode 2 (default) = by the number of ranks (the kernel from 4
+ * ranks on, ncclAllReduce below: what was measured faster), 1 = the library's own kernel over peer memory
  * (every rank exports one buffer through CUDA IPC at q4_cuda_ep_init; a rank's kernel copies its
  * partial rows there, signals every rank with plain stores, waits -- bounded -- for the others'
  * signals and sums the ranks' rows in rank order with plain loads over NVLink), used when every

@@ -69,7 +69,7 @@ __global__ void ep_sum_k(const float *__restrict__ recv, float *__restrict__ y, 
 // finished reading copy p.  No multicast, no TMA: plain ld/st on mapped peer memory.
 constexpr uint32_t AR_MAX_ELEMS = 64u * 4096u;
 constexpr uint32_t AR_MAX_RANKS = 8;
-constexpr uint32_t AR_CTAS = 32, AR_THREADS = 512;
+constexpr uint32_t AR_CTAS = 64, AR_THREADS = 512;
 constexpr uint32_t AR_ERR = 0x1000u;   // bit of the device error word: a peer's rows did not come in time
 struct ArArgs {
     const float *src;
@@ -95,9 +95,9 @@ __global__ void __launch_bounds__(AR_THREADS) ep_allreduce_k(const __grid_consta
     float4 *mine = reinterpret_cast<float4 *>(a.bufs[a.rank]) + (size_t)p * (AR_MAX_ELEMS / 4u);
     const float4 *src4 = reinterpret_cast<const float4 *>(a.src);
     for (uint32_t i = gtid; i < a.n4; i += gsz) mine[i] = src4[i];
-    __threadfence_system();
     __syncthreads();
     if (tid == 0) {
+        __threadfence_system();   // one fence per CTA, after the barrier: it covers the CTA's stores
         const uint32_t old = atomicAdd(a.ctl + 1, 1u);
         if (old % gridDim.x == gridDim.x - 1u) {   // every CTA's rows are out: tell every rank (this one too)
             __threadfence_system();
@@ -196,7 +196,10 @@ EpWs carve(uint8_t *p, uint32_t world, uint32_t t_local, uint32_t topk, uint32_t
     return w;
 }
 
-int g_ar_mode = 1;   // 1: the peer-memory kernel where it was set up, 0: ncclAllReduce
+int g_ar_mode = 2;   // 0: ncclAllReduce, 1: the peer-memory kernel where it was set up, 2: by the number of ranks
+// The kernel's cost is a handful of NVLink round trips whatever the number of ranks; at 2 ranks
+// ncclAllReduce was measured 4 us per layer faster, at 8 ranks slower.
+bool ar_use_kernel() { return g_ar.ok && (g_ar_mode == 1 || (g_ar_mode == 2 && g_world >= 4)); }
 
 void ar_teardown() {
     for (uint32_t r = 0; r < AR_MAX_RANKS; r++)
@@ -314,8 +317,8 @@ extern "C" bool q4_cuda_ep_init(const uint8_t *id128, int rank, int world) {
 // memory where every rank could map every other rank's buffer, 0 ncclAllReduce.  Returns what is in
 // effect.  Every rank must make the same call.
 extern "C" int q4_cuda_ep_allreduce_mode(int mode) {
-    if (mode == 0 || mode == 1) g_ar_mode = mode;
-    return g_ar.ok && g_ar_mode ? 1 : 0;
+    if (mode >= 0 && mode <= 2) g_ar_mode = mode;
+    return ar_use_kernel() ? 1 : 0;
 }
 // Error word of the peer all-reduce (0x1000: a peer's rows did not arrive within two seconds).  Synchronises.
 extern "C" uint32_t q4_cuda_ep_error(void) {
@@ -467,7 +470,7 @@ extern "C" bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64
         return false;
     if (!q4_cuda_expert_reduce_set(w.partial, w.pd, w.rsrc, w.rw, T, k1, n_embd)) return false;
     const size_t n = (size_t)T * n_embd;
-    if (g_ar.ok && g_ar_mode && n <= AR_MAX_ELEMS && (n % 4u) == 0 && (((uintptr_t)w.partial | (uintptr_t)d_y) & 15u) == 0)
+    if (ar_use_kernel() && n <= AR_MAX_ELEMS && (n % 4u) == 0 && (((uintptr_t)w.partial | (uintptr_t)d_y) & 15u) == 0)
         return ar_launch(w.partial, d_y, n, st);
     EP_NCCL(ncclAllReduce(w.partial, d_y, n, ncclFloat, ncclSum, g_comm, st));
     return true;
