@@ -59,6 +59,10 @@ bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64_t og, uint
  * rank could map every other rank's buffer; 0 = ncclAllReduce.  Returns the mode in effect; every
  * rank must make the same call.  q4_cuda_ep_error: 0, or 0x1000 after a wait ran out (synchronises). */
 int q4_cuda_ep_allreduce_mode(int mode);
+/* Routing of q4_cuda_ep_layer_ar when the peer kernel is in use: 1 = a rank routes only its own tokens
+ * (norm, router product, top-k in one launch) and the ranks' picks are gathered through peer memory;
+ * 0 (default) = every rank routes all tokens itself.  Every rank must make the same call. */
+void q4_cuda_ep_split_routing(int on);
 uint32_t q4_cuda_ep_error(void);
 /* Cost of one layer's collectives alone, microseconds (mean of iters rounds with the layer's
  * payload sizes): out2[0] the two exchanges of q4_cuda_ep_layer, out2[1] the all-reduce of

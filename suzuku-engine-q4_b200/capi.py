@@ -174,6 +174,7 @@ SIGNATURES = {
     "q4_cuda_moe_layer_n_ws_bytes": (u64, [u32, u32, u32, u32, u32]),
     "q4_cuda_moe_layer_n": (b, [vp, u64, u64, u64, u64, i32, vp, vp, f32, vp, u32, u32, u32, u32,
                                 u32, vp, vp, vp, vp, u64]),
+    "q4_cuda_route_small": (b, [vp, vp, f32, vp, u32, u32, u32, u32, vp, vp, vp, vp]),
     "q4_cuda_moe_layer_nt": (b, [vp, u64, u32, u64, u64, u32, u64, i32, vp, vp, f32, vp, u32, u32, u32, u32,
                                  u32, vp, vp, vp, vp, u64]),
     "q4_cuda_moe_exec_noalloc": (b, [vp, u64, vp, vp, u32, u64, u64, u64, vp, vp, vp, u32, u32, u32,
@@ -250,6 +251,7 @@ EP_SIGNATURES = {
     "q4_cuda_ep_world": (C.c_int, []),
     "q4_cuda_ep_allreduce_max": (b, [vp]),
     "q4_cuda_ep_allreduce_mode": (C.c_int, [C.c_int]),
+    "q4_cuda_ep_split_routing": (None, [C.c_int]),
     "q4_cuda_ep_error": (u32, []),
     "q4_cuda_ep_layer_ws_bytes": (u64, [u32, u32, u32, u32, u32, u32]),
     "q4_cuda_ep_layer": (b, [vp, u64, u64, u64, u64, C.c_int, vp, vp, f32, vp, u32, u32, u32, u32, u32,

@@ -71,6 +71,12 @@ constexpr uint32_t AR_MAX_ELEMS = 64u * 4096u;
 constexpr uint32_t AR_MAX_RANKS = 8;
 constexpr uint32_t AR_CTAS = 64, AR_THREADS = 512;
 constexpr uint32_t AR_ERR = 0x1000u;   // bit of the device error word: a peer's rows did not come in time
+constexpr size_t AR_BUF_BYTES = 2ull * AR_MAX_ELEMS * sizeof(float);
+// after the two row copies: 256 bytes of ready words (all-reduce [2][8], gather [2][8]), then the
+// gather area [2][AR_MAX_RANKS][GATHER_SLOT] that the peers write their picks into
+constexpr uint32_t GATHER_SLOT = 4096;
+constexpr size_t AR_GATHER_OFF = AR_BUF_BYTES + 256;
+constexpr size_t AR_MEM_BYTES = AR_GATHER_OFF + 2ull * AR_MAX_RANKS * GATHER_SLOT;
 struct ArArgs {
     const float *src;
     float *dst;
@@ -147,6 +153,83 @@ __global__ void __launch_bounds__(AR_THREADS) ep_allreduce_k(const __grid_consta
     }
 }
 
+// The picks of every rank's own tokens, gathered on every rank (a few hundred bytes per rank): each
+// rank pushes its block into slot [copy][rank] of every rank's gather area and stores the epoch into
+// that rank's gather-ready word; then waits (bounded) for all ranks' words and copies the slots out.
+// One CTA.  Epochs and the two copies work as in the all-reduce (their own counter, ctl[4]).
+struct GatherArgs {
+    const int32_t *ids_l;
+    const float *wts_l;
+    int32_t *ids;
+    float *wts;
+    uint32_t n;                        // entries per rank (tokens x picks)
+    uint32_t world, rank;
+    uint8_t *mem[AR_MAX_RANKS];        // every rank's exported memory
+    uint32_t *ctl;
+    unsigned long long wait_ns;
+};
+__global__ void __launch_bounds__(256) ep_gather_picks_k(const __grid_constant__ GatherArgs a) {
+    __shared__ uint32_t s_epoch;
+    const uint32_t tid = threadIdx.x;
+    if (tid == 0) {
+        uint32_t e;
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(e) : "l"(a.ctl + 4) : "memory");
+        s_epoch = e + 1u;
+    }
+    __syncthreads();
+    const uint32_t epoch = s_epoch, p = epoch & 1u;
+    const size_t slot = AR_GATHER_OFF + ((size_t)p * AR_MAX_RANKS + a.rank) * GATHER_SLOT;
+    for (uint32_t r = 0; r < a.world; r++) {
+        uint32_t *dst = reinterpret_cast<uint32_t *>(a.mem[r] + slot);
+        for (uint32_t i = tid; i < a.n; i += 256) {
+            dst[i] = (uint32_t)a.ids_l[i];
+            dst[a.n + i] = __float_as_uint(a.wts_l[i]);
+        }
+    }
+    __syncthreads();
+    if (tid == 0) {
+        __threadfence_system();
+        for (uint32_t r = 0; r < a.world; r++)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t *>(a.mem[r] + AR_BUF_BYTES) +
+                                                                  2u * AR_MAX_RANKS + p * AR_MAX_RANKS + a.rank),
+                         "r"(epoch)
+                         : "memory");
+    }
+    if (tid < a.world) {
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(a.mem[a.rank] + AR_BUF_BYTES) + 2u * AR_MAX_RANKS +
+                            p * AR_MAX_RANKS + tid;
+        unsigned long long t0;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+        for (uint32_t i = 0;; i++) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(w) : "memory");
+            if (v == epoch) break;
+            if ((i & 255u) == 255u) {
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+                if (t - t0 > a.wait_ns) {
+                    atomicOr(a.ctl + 3, AR_ERR);
+                    break;
+                }
+            }
+        }
+    }
+    __syncthreads();
+    for (uint32_t r = 0; r < a.world; r++) {
+        const uint32_t *src =
+            reinterpret_cast<const uint32_t *>(a.mem[a.rank] + AR_GATHER_OFF + ((size_t)p * AR_MAX_RANKS + r) * GATHER_SLOT);
+        for (uint32_t i = tid; i < a.n; i += 256) {
+            uint32_t vi, vw;
+            asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(vi) : "l"(src + i) : "memory");
+            asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(vw) : "l"(src + a.n + i) : "memory");
+            a.ids[(size_t)r * a.n + i] = (int32_t)vi;
+            a.wts[(size_t)r * a.n + i] = __uint_as_float(vw);
+        }
+    }
+    __syncthreads();
+    if (tid == 0) asm volatile("st.volatile.global.u32 [%0], %1;" ::"l"(a.ctl + 4), "r"(epoch) : "memory");
+}
+
 struct ArState {
     bool ok;
     uint8_t *mem;                      // exported: [2][AR_MAX_ELEMS] floats | ready words
@@ -155,8 +238,6 @@ struct ArState {
     uint32_t *ready[AR_MAX_RANKS];
     void *opened[AR_MAX_RANKS];
 } g_ar = {};
-constexpr size_t AR_BUF_BYTES = 2ull * AR_MAX_ELEMS * sizeof(float);
-constexpr size_t AR_MEM_BYTES = AR_BUF_BYTES + 256;
 
 struct EpWs {
     float *xn_l, *logits, *wts_l, *xn, *wts, *rw, *gu, *pd, *partial, *recv;
@@ -199,6 +280,7 @@ EpWs carve(uint8_t *p, uint32_t world, uint32_t t_local, uint32_t topk, uint32_t
 int g_ar_mode = 2;   // 0: ncclAllReduce, 1: the peer-memory kernel where it was set up, 2: by the number of ranks
 // The kernel's cost is a handful of NVLink round trips whatever the number of ranks; at 2 ranks
 // ncclAllReduce was measured 4 us per layer faster, at 8 ranks slower.
+int g_split_routing = 0;   // q4_cuda_ep_split_routing
 bool ar_use_kernel() { return g_ar.ok && (g_ar_mode == 1 || (g_ar_mode == 2 && g_world >= 4)); }
 
 void ar_teardown() {
@@ -271,6 +353,22 @@ bool ar_setup() {
     return true;
 }
 
+bool gather_launch(const int32_t *ids_l, const float *wts_l, int32_t *ids, float *wts, uint32_t n, cudaStream_t st) {
+    GatherArgs a;
+    a.ids_l = ids_l;
+    a.wts_l = wts_l;
+    a.ids = ids;
+    a.wts = wts;
+    a.n = n;
+    a.world = (uint32_t)g_world;
+    a.rank = (uint32_t)g_rank;
+    for (uint32_t r = 0; r < AR_MAX_RANKS; r++) a.mem[r] = (uint8_t *)g_ar.bufs[r];
+    a.ctl = g_ar.ctl;
+    a.wait_ns = 2000000000ull;
+    ep_gather_picks_k<<<1, 256, 0, st>>>(a);
+    return cudaGetLastError() == cudaSuccess;
+}
+
 bool ar_launch(const float *src, float *dst, size_t n, cudaStream_t st) {
     ArArgs a;
     a.src = src;
@@ -320,6 +418,9 @@ extern "C" int q4_cuda_ep_allreduce_mode(int mode) {
     if (mode >= 0 && mode <= 2) g_ar_mode = mode;
     return ar_use_kernel() ? 1 : 0;
 }
+// 1: with the peer buffers mapped, a rank routes only its own tokens and the picks are gathered through
+// peer memory; 0 (default): every rank routes all tokens.  Every rank must make the same call.
+extern "C" void q4_cuda_ep_split_routing(int on) { g_split_routing = on ? 1 : 0; }
 // Error word of the peer all-reduce (0x1000: a peer's rows did not arrive within two seconds).  Synchronises.
 extern "C" uint32_t q4_cuda_ep_error(void) {
     uint32_t e = 0;
@@ -450,9 +551,19 @@ extern "C" bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64
     // hold them as long as n_expert <= n_embd)
     if (n_expert > n_embd) return false;
     if (!q4_hip_grouped_rms_n(d_x, d_norm_w, w.xn, n_embd, 1, eps, T)) return false;
-    if (!q4_hip_gemv_dd_n(Q4_T_F32, (const uint8_t *)d_router, n_expert, n_embd, w.xn, w.recv, 1.0f, T))
-        return false;
-    if (!q4_hip_route_pf(w.recv, w.ids, w.wts, T, n_expert, topk)) return false;
+    // Routing: with the peer buffers mapped a rank routes only its own tokens (norm, router product and
+    // top-k in one launch: the same values as the three launches) and the ranks' picks are gathered
+    // through peer memory (a few hundred bytes each); else every rank routes all T tokens itself.
+    const bool split = g_split_routing && ar_use_kernel() && t_local <= 8u && (size_t)t_local * topk * 8u <= GATHER_SLOT &&
+                       q4_cuda_route_small(d_x + (size_t)g_rank * t_local * n_embd, d_norm_w, eps, d_router, n_expert, topk,
+                                           n_embd, t_local, w.xn_l, w.logits, w.ids_l, w.wts_l);
+    if (split) {
+        if (!gather_launch(w.ids_l, w.wts_l, w.ids, w.wts, t_local * topk, st)) return false;
+    } else {
+        if (!q4_hip_gemv_dd_n(Q4_T_F32, (const uint8_t *)d_router, n_expert, n_embd, w.xn, w.recv, 1.0f, T))
+            return false;
+        if (!q4_hip_route_pf(w.recv, w.ids, w.wts, T, n_expert, topk)) return false;
+    }
     // local experts on the rows that picked them, the shared expert for this rank's tokens
     if (!q4_cuda_assign_local(w.ids, w.wts, w.atok, w.rsrc, w.rw, w.bounds, T, topk,
                               (uint32_t)g_rank * e_local, e_local, has_shared, (uint32_t)g_rank * t_local,

@@ -983,6 +983,17 @@ extern "C" bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64
                                 d_router, n_expert, topk, n_embd, n_ff, n_tok, d_y, d_ids, d_wts, d_ws, ws_bytes);
 }
 
+// RMSNorm, router product and softmax / top-k of up to 8 tokens in one launch (n_embd == 2048): the
+// values of q4_hip_grouped_rms_n + q4_hip_gemv_dd_n + q4_hip_route_pf, bit for bit.  false: not this
+// kernel's shape, nothing queued.
+extern "C" bool q4_cuda_route_small(const float *d_x, const float *d_norm_w, float eps, const float *d_router,
+                                    uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_tok, float *d_xn,
+                                    float *d_logits, int32_t *d_ids, float *d_wts) {
+    if (!g_q4b.ok || !d_x || !d_router || !d_xn || !d_logits || !d_ids || !d_wts || topk == 0 || topk > n_expert)
+        return false;
+    return q4b_route_small(d_x, d_norm_w, eps, d_router, n_expert, topk, n_embd, n_tok, d_xn, d_logits, d_ids, d_wts);
+}
+
 // The same with the experts' formats named: gate and up of type gt, down of type dt, each IQ3_S,
 // IQ4_NL or IQ4_XS (a pack with a part that is not IQ3_S sits in an arena in the engine's byte order).
 extern "C" bool q4_cuda_moe_layer_nt(const uint8_t *base, uint64_t stride, uint32_t gt, uint64_t og, uint64_t ou,

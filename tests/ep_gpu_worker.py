@@ -123,6 +123,17 @@ def main():
     dev.sync()
     nccl = dev.download(d_ya, (world * T_LOCAL, H), np.float32)
     assert np.linalg.norm(nccl - ya) <= 1e-6 * np.linalg.norm(ya)
+    if mode == 1:
+        # a rank routes only its own tokens, the picks are gathered through peer memory: the same bits
+        ep.q4_cuda_ep_split_routing(1)
+        for _ in range(3):
+            assert ep.q4_cuda_ep_layer_ar(base, stride, 0, F * rb, 2 * F * rb, 1, d_xa, d_norm, 1e-6, d_router,
+                                          E, K, H, F, T_LOCAL, d_ya, d_ws, ws)
+            dev.sync()
+            got = dev.download(d_ya, (world * T_LOCAL, H), np.float32)
+            assert np.array_equal(got.view(np.uint32), ya.view(np.uint32))
+        assert ep.q4_cuda_ep_error() == 0
+        ep.q4_cuda_ep_split_routing(0)
     ep.q4_cuda_ep_allreduce_mode(2)
     f2 = (ctypes.c_float * 2)()
     assert ep.q4_cuda_ep_exchange_floor_us(T_LOCAL, H, K, E, F, d_ws, ws, 5, f2) and f2[0] > 0 and f2[1] > 0
