@@ -947,21 +947,29 @@ def run_ep(a, pkg, rank, world, local, warmup):
     details = {"cuda_graph": graphed, "repeats": repeats, "exchange_floor_us": floor,
                "form": "every rank holds all 64 token rows; one all-reduce of the partial rows per layer"}
     if ep is not None:
-        peer = ep.q4_cuda_ep_allreduce_mode(-1) == 1
-        names = {True: "the library's kernel over IPC-mapped peer memory (plain loads and stores over NVLink, bounded "
-                       "waits)", False: "ncclAllReduce"}
-        details["all_reduce"] = names[peer]
         e2 = ep.q4_cuda_ep_error()
         if e2:
             raise SystemExit("expert-parallel error word %#x" % e2)
-        # the same job with the other all-reduce, for comparison
-        if ep.q4_cuda_ep_allreduce_mode(0 if peer else 1) == (0 if peer else 1):
-            job_n = BatchJob(pkg, model, ep, rank, world, EP_TOKENS, range(n_layers))
-            ms_n, _, _, _ = time_job(job_n, a.steps, warmup, barrier_max, min_ms=20.0)
-            details["with_the_other_all_reduce"] = {"all_reduce": names[not peer], "ms_per_step": ms_n,
-                                                    "value": EP_TOKENS * n_layers / (ms_n * 1e-3), "unit": UNIT}
-            job_n.release()
+        details["all_reduce"] = "ncclAllReduce"
+        # variants of the same job, for comparison: the library's own all-reduce kernel over IPC-mapped
+        # peer memory, and the routing split over the ranks with a peer gather of the picks
+        variants = {}
+        if ep.q4_cuda_ep_allreduce_mode(1) == 1:
+            for name, ar, split in (("own_all_reduce_kernel", 1, 0), ("split_routing", 0, 1)):
+                ep.q4_cuda_ep_allreduce_mode(ar)
+                ep.q4_cuda_ep_split_routing(split)
+                job_n = BatchJob(pkg, model, ep, rank, world, EP_TOKENS, range(n_layers))
+                ms_n, _, _, _ = time_job(job_n, a.steps, warmup, barrier_max, min_ms=20.0)
+                variants[name] = {"ms_per_step": ms_n, "value": EP_TOKENS * n_layers / (ms_n * 1e-3), "unit": UNIT}
+                job_n.release()
+            e2 = ep.q4_cuda_ep_error()
+            if e2:
+                raise SystemExit("expert-parallel error word %#x" % e2)
+        else:
+            variants["unavailable"] = "the ranks' buffers could not be mapped through CUDA IPC"
         ep.q4_cuda_ep_allreduce_mode(2)
+        ep.q4_cuda_ep_split_routing(0)
+        details["variants"] = variants
     if ep is not None:
         # the two-exchange form of the same job (tokens split over the ranks), for comparison
         job2 = BatchJob(pkg, model, ep, rank, world, EP_TOKENS, range(n_layers), form="a2a")

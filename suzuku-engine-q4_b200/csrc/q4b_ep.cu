@@ -277,11 +277,13 @@ EpWs carve(uint8_t *p, uint32_t world, uint32_t t_local, uint32_t topk, uint32_t
     return w;
 }
 
-int g_ar_mode = 2;   // 0: ncclAllReduce, 1: the peer-memory kernel where it was set up, 2: by the number of ranks
-// The kernel's cost is a handful of NVLink round trips whatever the number of ranks; at 2 ranks
-// ncclAllReduce was measured 4 us per layer faster, at 8 ranks slower.
+int g_ar_mode = 2;   // 0: ncclAllReduce, 1: the peer-memory kernel where it was set up, 2: the default
+// The kernel's cost is a handful of NVLink round trips (copy out, signal, wait, read) whatever the number
+// of ranks.  Measured inside the 48-layer job: 4 us per layer slower than ncclAllReduce at 2 ranks, 2 us
+// slower at 8 (NCCL reduces inside the switch there).  So the default is ncclAllReduce; the kernel stays
+// selectable (mode 1).
 int g_split_routing = 0;   // q4_cuda_ep_split_routing
-bool ar_use_kernel() { return g_ar.ok && (g_ar_mode == 1 || (g_ar_mode == 2 && g_world >= 4)); }
+bool ar_use_kernel() { return g_ar.ok && g_ar_mode == 1; }
 
 void ar_teardown() {
     for (uint32_t r = 0; r < AR_MAX_RANKS; r++)
@@ -554,7 +556,7 @@ extern "C" bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64
     // Routing: with the peer buffers mapped a rank routes only its own tokens (norm, router product and
     // top-k in one launch: the same values as the three launches) and the ranks' picks are gathered
     // through peer memory (a few hundred bytes each); else every rank routes all T tokens itself.
-    const bool split = g_split_routing && ar_use_kernel() && t_local <= 8u && (size_t)t_local * topk * 8u <= GATHER_SLOT &&
+    const bool split = g_split_routing && g_ar.ok && t_local <= 8u && (size_t)t_local * topk * 8u <= GATHER_SLOT &&
                        q4_cuda_route_small(d_x + (size_t)g_rank * t_local * n_embd, d_norm_w, eps, d_router, n_expert, topk,
                                            n_embd, t_local, w.xn_l, w.logits, w.ids_l, w.wts_l);
     if (split) {

@@ -28,27 +28,25 @@
 namespace few {
 
 constexpr uint32_t NCW = 16;                 // warps
-constexpr uint32_t TPW = 4;                  // tiles a warp takes from a chunk (loop and ring tests paid once for all)
-constexpr uint32_t CT = NCW * TPW;           // tiles per chunk
+// Two shapes of the ring, picked per call by the amount of work (see launch()): <TPW, NSTAGE> = tiles a
+// warp takes from a chunk (loop and ring tests are paid once for all of them) and chunks in flight.
 constexpr uint32_t NT = NCW * 32;
-constexpr uint32_t CHUNK_BYTES = CT * Q4B_TILE_BYTES;
-constexpr uint32_t NSTAGE = 2;
 constexpr uint32_t RB = 3;                   // activation rows held in registers
 constexpr uint32_t MAX_ENTRIES = 1024;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;    // tries before a wait gives up ...
 constexpr unsigned long long WAIT_NS = 500000000ull;   // ... or half a second, whichever comes first
 constexpr uint32_t ERR_FEW = 0x800u;
 
-struct Smem {
+template <uint32_t TPW, uint32_t NSTAGE> struct Smem {
     uint32_t tab[32 * 512];                  // code table, one column per lane
-    uint8_t stage[NSTAGE][CHUNK_BYTES];
+    uint8_t stage[NSTAGE][NCW * TPW * Q4B_TILE_BYTES];
     unsigned long long full[NSTAGE], empty[NSTAGE];
     uint32_t live[MAX_ENTRIES];              // compacted live entries
     uint32_t cost[MAX_ENTRIES + 1];          // cost of all chunks before entry i (prefix)
     uint32_t wcount[32];
     uint32_t n_live;
 };
-constexpr uint32_t SMEM_BYTES = sizeof(Smem) + 128;
+template <uint32_t TPW, uint32_t NSTAGE> constexpr uint32_t smem_bytes() { return sizeof(Smem<TPW, NSTAGE>) + 128; }
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -107,12 +105,14 @@ __device__ __forceinline__ uint32_t chunk_cost(uint32_t rows) {
 
 // BB = super-blocks per weight row (1, 2, 4 or 8), a template parameter so that the row
 // geometry and the depth of the shuffle sum are compile-time constants.
-template <uint32_t BB>
+template <uint32_t BB, uint32_t TPW, uint32_t NSTAGE>
 __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
+    constexpr uint32_t CT = NCW * TPW;           // tiles per chunk
+    constexpr uint32_t CHUNK_BYTES = CT * Q4B_TILE_BYTES;
     // used directly (no integer round trip), so that the compiler keeps these as
     // shared-space accesses; dynamic shared memory starts on the declared alignment
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    Smem &s = *reinterpret_cast<Smem *>(smem_raw);
+    Smem<TPW, NSTAGE> &s = *reinterpret_cast<Smem<TPW, NSTAGE> *>(smem_raw);
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const uint32_t n_ent = a.n_act ? min(*a.n_act, a.n_entries) : a.n_entries;
 
@@ -362,15 +362,19 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
 }
 
 static bool g_ready = false;
+template <uint32_t TPW, uint32_t NSTAGE> static bool warm_shape() {
+    const int bytes = (int)smem_bytes<TPW, NSTAGE>();
+    return cudaFuncSetAttribute(grouped_few_k<1, TPW, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) ==
+               cudaSuccess &&
+           cudaFuncSetAttribute(grouped_few_k<2, TPW, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) ==
+               cudaSuccess &&
+           cudaFuncSetAttribute(grouped_few_k<4, TPW, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) ==
+               cudaSuccess &&
+           cudaFuncSetAttribute(grouped_few_k<8, TPW, NSTAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) ==
+               cudaSuccess;
+}
 bool warm() {
-    if (cudaFuncSetAttribute(grouped_few_k<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(grouped_few_k<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(grouped_few_k<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(grouped_few_k<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
-            cudaSuccess) {
+    if (!warm_shape<4, 2>() || !warm_shape<2, 4>()) {
         cudaGetLastError();
         return false;
     }
@@ -386,15 +390,25 @@ bool shape_ok(uint64_t w_rows, uint64_t w_cols, uint32_t n_entries) {
     return blocks != 0 && (blocks % 8u) == 0;
 }
 
-bool launch(const Args &a) {
+template <uint32_t TPW, uint32_t NSTAGE> static bool launch_shape(const Args &a) {
+    const size_t sm = smem_bytes<TPW, NSTAGE>();
     switch (a.cols >> 8) {
-    case 1: grouped_few_k<1><<<g_q4b.n_sm, NT, SMEM_BYTES, g_q4b.stream>>>(a); break;
-    case 2: grouped_few_k<2><<<g_q4b.n_sm, NT, SMEM_BYTES, g_q4b.stream>>>(a); break;
-    case 4: grouped_few_k<4><<<g_q4b.n_sm, NT, SMEM_BYTES, g_q4b.stream>>>(a); break;
-    case 8: grouped_few_k<8><<<g_q4b.n_sm, NT, SMEM_BYTES, g_q4b.stream>>>(a); break;
+    case 1: grouped_few_k<1, TPW, NSTAGE><<<g_q4b.n_sm, NT, sm, g_q4b.stream>>>(a); break;
+    case 2: grouped_few_k<2, TPW, NSTAGE><<<g_q4b.n_sm, NT, sm, g_q4b.stream>>>(a); break;
+    case 4: grouped_few_k<4, TPW, NSTAGE><<<g_q4b.n_sm, NT, sm, g_q4b.stream>>>(a); break;
+    case 8: grouped_few_k<8, TPW, NSTAGE><<<g_q4b.n_sm, NT, sm, g_q4b.stream>>>(a); break;
     default: return false;
     }
     return true;
+}
+// Large chunks pay the loop and ring tests once per four tiles, but a CTA wants a few dozen of them to
+// fill its pipeline and to balance against the others: with little work (an expert-parallel rank's 64
+// experts, a verify window's 40) the smaller chunks win.  The entry count is the caller's upper bound
+// on the live entries.
+bool launch(const Args &a) {
+    const uint64_t tiles = ((uint64_t)a.w_rows * (a.cols >> 8)) >> 3;
+    const uint64_t big_chunks_per_cta = (uint64_t)a.n_entries * ((tiles + 63u) / 64u) / (uint64_t)g_q4b.n_sm;
+    return big_chunks_per_cta >= 20u ? launch_shape<4, 2>(a) : launch_shape<2, 4>(a);
 }
 
 }  // namespace few
