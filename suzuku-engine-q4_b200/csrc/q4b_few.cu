@@ -31,7 +31,7 @@ constexpr uint32_t NCW = 16;                 // warps
 // Two shapes of the ring, picked per call by the amount of work (see launch()): <TPW, NSTAGE> = tiles a
 // warp takes from a chunk (loop and ring tests are paid once for all of them) and chunks in flight.
 constexpr uint32_t NT = NCW * 32;
-constexpr uint32_t RB = 3;                   // activation rows held in registers
+constexpr uint32_t RB = 3;                   // activation rows held in registers (2: 14 % slower, 4 spills)
 constexpr uint32_t MAX_ENTRIES = 1024;
 constexpr uint32_t WAIT_LIMIT = 1u << 21;    // tries before a wait gives up ...
 constexpr unsigned long long WAIT_NS = 500000000ull;   // ... or half a second, whichever comes first
@@ -277,7 +277,7 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
             }
         }
         if (!mbar_wait(&s.full[st], ph, limit, a.err)) limit = 1024u;
-#pragma unroll
+#pragma unroll 1   // one copy of the body: unrolled it was 1 % slower (four times the code to fetch)
         for (uint32_t sub = 0; sub < TPW; sub++) {
             // decode this warp's tile into registers; after the last one, give the stage back
             const uint32_t tc = sub * NCW + warp;                      // tile within the chunk
@@ -329,7 +329,9 @@ __global__ void __launch_bounds__(NT, 1) grouped_few_k(const Args a) {
                 row_reg(0);
                 if (nr >= 2u) {
                     row_reg(1);
-                    if (nr == 3u) row_reg(2);
+                    if constexpr (RB >= 3) {
+                        if (nr == 3u) row_reg(2);
+                    }
                 }
                 for (int32_t r = r0 + (int32_t)RB; r < r1; r++) {      // further rows: straight from memory
                     const int4 *qp = reinterpret_cast<const int4 *>(a.xq + (uint64_t)r * a.cols + gcol * 32u);
