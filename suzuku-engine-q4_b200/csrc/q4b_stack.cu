@@ -906,6 +906,7 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
                 xw_store(a.xw + r, sum, ep);
             } else {
                 a.y[r] = sum;
+                if (a.y_host) a.y_host[r] = sum;   // straight into the caller's mapped host row (see the hand-off)
                 if (a.res)
                     for (uint32_t c = 0; c < a.hc; c++)
                         a.res[(size_t)c * H + r] = __fmaf_rn(sum, S.fac[c], a.res[(size_t)c * H + r]);
@@ -920,11 +921,12 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         }
         par_chunk ^= 1u;
     }
-    // Host hand-off (the call with host buffers): the CTA that finishes last copies y into the
-    // caller's pinned, mapped host buffer and then raises the flag the host is spinning on, so
-    // the result needs neither a copy node nor a stream wake-up.  One CTA writes and fences at
-    // system scope: having every CTA write its own rows and fence was measured slower (148
-    // system-scope fences over the PCIe writes instead of one).
+    // Host hand-off (the call with host buffers): every CTA has written its rows of y straight into
+    // the caller's pinned, mapped host row (posted writes, as soon as the rows were summed), fences at
+    // GPU scope and counts itself; the CTA that finishes last fences once at system scope -- the
+    // fence is cumulative over what it has observed through the counter -- and raises the flag the
+    // host is spinning on.  No copy node, no stream wake-up, one system-scope fence (148 of them, one
+    // per CTA, measured slower; so did a copy of the whole row by the last CTA: one more L2 round trip).
     if (a.y_host) {
         __threadfence();
         __syncthreads();
@@ -934,12 +936,8 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         }
         __syncthreads();
         if (S.last) {
-            __threadfence();
-            for (uint32_t i = tid; i < H / 4u; i += NT)
-                reinterpret_cast<float4 *>(a.y_host)[i] = __ldcg(reinterpret_cast<const float4 *>(a.y) + i);
-            __threadfence_system();
-            __syncthreads();
             if (tid == 0) {
+                __threadfence_system();
                 uint32_t ew;
                 asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(ew) : "l"(a.err) : "memory");
                 *a.flag_host = (a.flag_val + step) | (ew ? FLAG_ERR : 0u);   // every writer fenced at system scope above
