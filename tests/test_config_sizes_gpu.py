@@ -61,8 +61,9 @@ def test_config3_prefill_2048_tokens_zipf(dev, pkg, oracle):
         ws = lib.q4_cuda_moe_layer_n_ws_bytes(T, K, E, H, F)
         d_ws, d_x = dev.malloc(ws), dev.upload(xs)
         d_y, d_ids = dev.malloc(T * H * 4), dev.malloc(T * K * 4)
-        # sampled tokens: rows of the hottest expert, of experts either side of the 12-row switch
-        # between the two grouped kernels, of a one-row expert, and random ones
+        # sampled tokens: rows of the hottest expert, of experts with few rows (the streaming kernel's;
+        # the switch to the tensor-core kernel is at 6 rows in a call of this size, at 12 in small
+        # ones), of a one-row expert, and random ones
         rng = np.random.default_rng(5)
 
         def tokens_of(e, n):
@@ -73,7 +74,7 @@ def test_config3_prefill_2048_tokens_zipf(dev, pkg, oracle):
             c = np.nonzero((hist >= lo) & (hist <= hi))[0]
             return int(c[0]) if len(c) else None
         picks = tokens_of(int(hist.argmax()), 8)
-        for lo, hi in ((11, 11), (12, 12), (1, 1), (2, 10), (13, 64), (65, 400)):
+        for lo, hi in ((5, 5), (6, 6), (11, 11), (12, 12), (1, 1), (2, 4), (13, 64), (65, 400)):
             e = expert_with(lo, hi)
             if e is not None:
                 picks += tokens_of(e, 3)
