@@ -831,11 +831,31 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         // ---- phase 3a: the hidden rows (all experts), Q8-A; 8 lanes per group ----
         {
             constexpr uint32_t HQ_IT = (MAX_E * (F / 4) + NT - 1) / NT;
+            // First look at all of a thread's groups with the loads in flight together; the poll loop then
+            // only takes the groups that had not arrived.
+            unsigned long long hw_[HQ_IT][4];
+#pragma unroll
+            for (uint32_t it = 0; it < HQ_IT; it++) {
+                const uint32_t w4 = tid + it * NT;
+                if (w4 < ne * (F / 4)) {
+                    const unsigned long long *p = a.hw + 4u * w4;
+                    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];"
+                                 : "=l"(hw_[it][0]), "=l"(hw_[it][1]) : "l"(p) : "memory");
+                    asm volatile("ld.relaxed.gpu.global.v2.u64 {%0, %1}, [%2];"
+                                 : "=l"(hw_[it][2]), "=l"(hw_[it][3]) : "l"(p + 2) : "memory");
+                }
+            }
 #pragma unroll
             for (uint32_t it = 0; it < HQ_IT; it++) {
                 const uint32_t w4 = tid + it * NT;
                 if (w4 < ne * (F / 4)) {  // warp-uniform: ne * F / 4 is a multiple of 32
-                    const float4 hv = xw_poll4(a.hw + 4u * w4, ep, limit, a.err);
+                    float4 hv;
+                    if ((uint32_t)(hw_[it][0] >> 32) == ep && (uint32_t)(hw_[it][1] >> 32) == ep &&
+                        (uint32_t)(hw_[it][2] >> 32) == ep && (uint32_t)(hw_[it][3] >> 32) == ep)
+                        hv = make_float4(__uint_as_float((uint32_t)hw_[it][0]), __uint_as_float((uint32_t)hw_[it][1]),
+                                         __uint_as_float((uint32_t)hw_[it][2]), __uint_as_float((uint32_t)hw_[it][3]));
+                    else
+                        hv = xw_poll4(a.hw + 4u * w4, ep, limit, a.err);
                     float d;
                     int bs;
                     const uint32_t word = quant8_oct(hv, &d, &bs);
