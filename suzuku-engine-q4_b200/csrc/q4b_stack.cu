@@ -37,6 +37,7 @@
 #include "q4b_tile.cuh"
 
 #include <atomic>
+#include <type_traits>
 #include <chrono>
 
 #include "../../include/q4cuda.h"
@@ -427,19 +428,20 @@ __device__ __forceinline__ void issue_gate_up(const Args &a, const Layer &L, Sma
     }
 }
 
-// Bulk copies of this CTA's down tiles (one per (row quad, expert)), issued by the last two warps.
+// Bulk copies of this CTA's down tiles: its row quads of one expert lie back to back in the pack,
+// so one copy per expert, staged expert by expert (tile (row quad rq, expert e) at slot
+// e * nrq + rq - rq0).  Many small copies cost more to issue than they take to arrive.
 __device__ __forceinline__ void issue_down(const Args &a, const Layer &L, Small &S, uint8_t *dstage,
                                            uint32_t v0, uint32_t v1, uint32_t ne, uint32_t tid) {
-    if (tid >= (NW - 2) * 32) {
-        const uint32_t t64 = tid - (NW - 2) * 32;
-        if (t64 == 0) mbar_expect_tx(&S.mbar[MB_DOWN], (v1 - v0) * Q4B_TILE_BYTES);
+    if (tid >= (NW - 1) * 32 && v1 > v0) {
+        const uint32_t e = tid - (NW - 1) * 32;
+        const uint32_t rq0 = v0 / ne, nrq = (v1 - v0) / ne;
+        if (e == 0) mbar_expect_tx(&S.mbar[MB_DOWN], (v1 - v0) * Q4B_TILE_BYTES);
         __syncwarp();
-        for (uint32_t v = v0 + t64; v < v1; v += 64) {
-            const uint32_t rq = v / ne, e = v - rq * ne;
-            bulk_g2s(dstage + (size_t)(v - v0) * Q4B_TILE_BYTES,
-                     L.base + (uint64_t)S.ids[e] * a.stride + a.od + (size_t)rq * Q4B_TILE_BYTES,
-                     Q4B_TILE_BYTES, &S.mbar[MB_DOWN]);
-        }
+        if (e < ne)
+            bulk_g2s(dstage + (size_t)e * nrq * Q4B_TILE_BYTES,
+                     L.base + (uint64_t)S.ids[e] * a.stride + a.od + (size_t)rq0 * Q4B_TILE_BYTES,
+                     nrq * Q4B_TILE_BYTES, &S.mbar[MB_DOWN]);
     }
 }
 
@@ -805,7 +807,6 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         for (uint32_t ul = warp; ul < u1 - u0; ul += NW) {
             const uint32_t k = ul / UCHUNK, j = ul - k * UCHUNK;
             mbar_wait(&S.mbar[MB_CHUNK0 + k], par_chunk, a.err);
-            if (ul == 0) stamp(a, prof, 13);
             const uint8_t *tile = stage + ((size_t)k * UCHUNK * 2u + j) * Q4B_TILE_BYTES;
             float g = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
             float u = q4b_tile_lane_dot(tile + (size_t)UCHUNK * Q4B_TILE_BYTES, lane, tl, q, dx0, dx1, bs0, bs1);
@@ -816,7 +817,6 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
             }
             if (lane == 0) xw_store(a.hw + u0 + ul, q4b_swiglu(g, u), ep);
         }
-        stamp(a, prof, 14);
         __syncthreads();   // every warp is done with the gate/up tiles
         if (tid == 0 && more && r1 > r0) {   // next layer's router rows
             const uint32_t bytes = (r1 - r0) * H * 4u;
@@ -877,40 +877,53 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         {
             const uint32_t col16 = 16u * (lane & 7u);  // first activation word of this lane's 64 columns
             const uint32_t g0 = 2u * (lane & 7u);
-            // DK tiles per warp task: DK independent instruction streams for the scheduler to
-            // interleave (a lone tile dot is a chain of dependent shared-memory lookups)
-            constexpr uint32_t DK = 3;
+            // A warp task: up to DK row quads of one expert.  The expert's activation words are
+            // loaded once for the task, and the DK tile dots are independent instruction streams for
+            // the scheduler to interleave (a lone tile dot is a chain of dependent shared-memory
+            // lookups).  DK = 3 or 4: with 148 CTAs a CTA holds 3 or 4 row quads.
+            const uint32_t nrq = (v1 - v0) / ne;
+            auto down_tasks = [&](auto dk_tag) {
+                constexpr uint32_t DK = decltype(dk_tag)::value;
+                const uint32_t ngr = (nrq + DK - 1u) / DK;   // tasks per expert
 #pragma unroll 1
-            for (uint32_t v = v0 + DK * warp; v < v1; v += DK * NW) {
-                float r[DK];
-                uint32_t e[DK];
-#pragma unroll
-                for (uint32_t i = 0; i < DK; i++) {
-                    const uint32_t vi = min(v + i, v1 - 1u);   // past the end: the last tile again, not stored
-                    e[i] = vi % ne;
+                for (uint32_t task = warp; task < ne * ngr; task += NW) {
+                    const uint32_t gq = task / ne, e = task - gq * ne;
+                    const uint32_t q0 = gq * DK;
                     int hqr[16];
 #pragma unroll
                     for (int c = 0; c < 16; c += 4) {
-                        const uint4 t4 = *reinterpret_cast<const uint4 *>(&S.hq[e[i]][col16 + c]);
+                        const uint4 t4 = *reinterpret_cast<const uint4 *>(&S.hq[e][col16 + c]);
                         hqr[c] = (int)t4.x;
                         hqr[c + 1] = (int)t4.y;
                         hqr[c + 2] = (int)t4.z;
                         hqr[c + 3] = (int)t4.w;
                     }
-                    r[i] = q4b_tile_lane_dot(dstage + (size_t)(vi - v0) * Q4B_TILE_BYTES, lane, tl, hqr,
-                                             S.hd[e[i]][g0], S.hd[e[i]][g0 + 1], S.hbs[e[i]][g0], S.hbs[e[i]][g0 + 1]);
-                }
+                    const float hd0 = S.hd[e][g0], hd1 = S.hd[e][g0 + 1];
+                    const int hb0 = S.hbs[e][g0], hb1 = S.hbs[e][g0 + 1];
+                    float r[DK];
 #pragma unroll
-                for (int o = 1; o < 8; o <<= 1) {
+                    for (uint32_t i = 0; i < DK; i++) {
+                        const uint32_t rql = min(q0 + i, nrq - 1u);   // past the end: the last tile again, not stored
+                        r[i] = q4b_tile_lane_dot(dstage + (size_t)(e * nrq + rql) * Q4B_TILE_BYTES, lane, tl, hqr,
+                                                 hd0, hd1, hb0, hb1);
+                    }
 #pragma unroll
-                    for (uint32_t i = 0; i < DK; i++) r[i] += __shfl_xor_sync(0xffffffffu, r[i], o);
-                }
-                if ((lane & 7u) == 0) {
+                    for (int o = 1; o < 8; o <<= 1) {
 #pragma unroll
-                    for (uint32_t i = 0; i < DK; i++)
-                        if (v + i < v1) S.part[v + i - v0][lane >> 3] = S.wts[e[i]] * r[i];
+                        for (uint32_t i = 0; i < DK; i++) r[i] += __shfl_xor_sync(0xffffffffu, r[i], o);
+                    }
+                    if ((lane & 7u) == 0) {
+                        const float w = S.wts[e];
+#pragma unroll
+                        for (uint32_t i = 0; i < DK; i++)
+                            if (q0 + i < nrq) S.part[(q0 + i) * ne + e][lane >> 3] = w * r[i];
+                    }
                 }
-            }
+            };
+            if (nrq % 4u == 0u)
+                down_tasks(std::integral_constant<uint32_t, 4>{});
+            else
+                down_tasks(std::integral_constant<uint32_t, 3>{});
         }
         __syncthreads();
         stamp(a, prof, 11);
