@@ -476,6 +476,7 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
     const uint32_t n_chunks = (u1 - u0 + UCHUNK - 1) / UCHUNK;
     const uint32_t s0 = has_sh ? (uint32_t)((uint64_t)cta * F / ncta) : 0u;  // shared-expert units
     const uint32_t s1 = has_sh ? (uint32_t)((uint64_t)(cta + 1) * F / ncta) : 0u;
+    const bool sh_split = 2u * (s1 - s0) <= NW;   // few shared units: one tile per warp
     // down tiles = (row quad, expert) pairs, expert fastest; a CTA takes whole row quads, so every
     // output row is summed over the experts by one CTA, in list order, and written once
     const uint32_t v0 = (uint32_t)((uint64_t)cta * (H / 4) / ncta) * ne;
@@ -711,19 +712,34 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
             // Hidden values: written here and after the routed dots, read by every CTA in phase 3
             // of this layer; a CTA reaches these lines for the next layer only after all CTAs
             // published this layer's y, i.e. after they all finished reading these words.
-            for (uint32_t ul = NW - 1u - warp; ul < s1 - s0; ul += NW) {
-                const uint8_t *tile = sstage + (size_t)ul * Q4B_TILE_BYTES;
-                float g = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
-                float u = q4b_tile_lane_dot(tile + (size_t)MAX_SH * Q4B_TILE_BYTES, lane, tl, q, dx0, dx1, bs0, bs1);
+            if (sh_split) {
+                // few units: gate tile and up tile on different warps, the two sums meet after the barrier
+                const uint32_t wv = NW - 1u - warp;
+                if (wv < 2u * (s1 - s0)) {
+                    float x = q4b_tile_lane_dot(sstage + (size_t)((wv & 1u) * MAX_SH + (wv >> 1)) * Q4B_TILE_BYTES, lane,
+                                                tl, q, dx0, dx1, bs0, bs1);
 #pragma unroll
-                for (int o = 16; o; o >>= 1) {
-                    g += __shfl_xor_sync(0xffffffffu, g, o);
-                    u += __shfl_xor_sync(0xffffffffu, u, o);
+                    for (int o = 16; o; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+                    if (lane == 0) S.red[wv] = x;   // free until this layer's softmax sum
                 }
-                if (lane == 0) xw_store(a.hw + a.topk * F + s0 + ul, q4b_swiglu(g, u), ep);
+            } else {
+                for (uint32_t ul = NW - 1u - warp; ul < s1 - s0; ul += NW) {
+                    const uint8_t *tile = sstage + (size_t)ul * Q4B_TILE_BYTES;
+                    float g = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
+                    float u = q4b_tile_lane_dot(tile + (size_t)MAX_SH * Q4B_TILE_BYTES, lane, tl, q, dx0, dx1, bs0,
+                                                bs1);
+#pragma unroll
+                    for (int o = 16; o; o >>= 1) {
+                        g += __shfl_xor_sync(0xffffffffu, g, o);
+                        u += __shfl_xor_sync(0xffffffffu, u, o);
+                    }
+                    if (lane == 0) xw_store(a.hw + a.topk * F + s0 + ul, q4b_swiglu(g, u), ep);
+                }
             }
         }
         __syncthreads();   // every warp is done with the router rows and the shared tiles
+        if (sh_split && tid < s1 - s0)
+            xw_store(a.hw + a.topk * F + s0 + tid, q4b_swiglu(S.red[2u * tid], S.red[2u * tid + 1u]), ep);
         if (tid == 32 && more && s1 > s0) {   // next layer's shared-expert tiles
             const uint32_t bytes = (s1 - s0) * Q4B_TILE_BYTES;
             const uint8_t *pk = nxt.base + (uint64_t)a.shared_slot * a.stride;
@@ -803,13 +819,21 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
         }
         stamp(a, prof, 7);
         // ---- phase 2c: routed hidden units (gate and up tile of a unit by one warp), SwiGLU ----
-#pragma unroll 1
-        for (uint32_t ul = warp; ul < u1 - u0; ul += NW) {
+        // The units beyond the last full round of NW: when they are few, their gate tiles and up tiles
+        // go to different warps (one more tile for 2 n_tail warps instead of one more unit-long round
+        // with n_tail warps at work) and meet after the block barrier below.
+        const uint32_t n_u = u1 - u0;
+        const uint32_t n_tail = (n_u >= NW && 2u * (n_u % NW) <= NW) ? n_u % NW : 0u;
+        const uint32_t n_pair = n_u - n_tail;
+        auto gu_tile = [&](uint32_t ul, uint32_t up) {
             const uint32_t k = ul / UCHUNK, j = ul - k * UCHUNK;
-            mbar_wait(&S.mbar[MB_CHUNK0 + k], par_chunk, a.err);
-            const uint8_t *tile = stage + ((size_t)k * UCHUNK * 2u + j) * Q4B_TILE_BYTES;
-            float g = q4b_tile_lane_dot(tile, lane, tl, q, dx0, dx1, bs0, bs1);
-            float u = q4b_tile_lane_dot(tile + (size_t)UCHUNK * Q4B_TILE_BYTES, lane, tl, q, dx0, dx1, bs0, bs1);
+            return stage + ((size_t)k * UCHUNK * 2u + (up ? UCHUNK : 0u) + j) * Q4B_TILE_BYTES;
+        };
+#pragma unroll 1
+        for (uint32_t ul = warp; ul < n_pair; ul += NW) {
+            mbar_wait(&S.mbar[MB_CHUNK0 + ul / UCHUNK], par_chunk, a.err);
+            float g = q4b_tile_lane_dot(gu_tile(ul, 0), lane, tl, q, dx0, dx1, bs0, bs1);
+            float u = q4b_tile_lane_dot(gu_tile(ul, 1), lane, tl, q, dx0, dx1, bs0, bs1);
 #pragma unroll
             for (int o = 16; o; o >>= 1) {
                 g += __shfl_xor_sync(0xffffffffu, g, o);
@@ -817,7 +841,17 @@ __device__ __forceinline__ void stack_body(const Args &a, const float4 *xrow) {
             }
             if (lane == 0) xw_store(a.hw + u0 + ul, q4b_swiglu(g, u), ep);
         }
+        if (warp < 2u * n_tail) {
+            const uint32_t ul = n_pair + (warp >> 1);
+            mbar_wait(&S.mbar[MB_CHUNK0 + ul / UCHUNK], par_chunk, a.err);
+            float x = q4b_tile_lane_dot(gu_tile(ul, warp & 1u), lane, tl, q, dx0, dx1, bs0, bs1);
+#pragma unroll
+            for (int o = 16; o; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+            if (lane == 0) S.red[warp] = x;   // free between the softmax sums of two layers
+        }
         __syncthreads();   // every warp is done with the gate/up tiles
+        if (tid < n_tail)
+            xw_store(a.hw + u0 + n_pair + tid, q4b_swiglu(S.red[2u * tid], S.red[2u * tid + 1u]), ep);
         if (tid == 0 && more && r1 > r0) {   // next layer's router rows
             const uint32_t bytes = (r1 - r0) * H * 4u;
             mbar_expect_tx(&S.mbar[MB_ROUTER], bytes);
