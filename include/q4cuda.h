@@ -434,7 +434,7 @@ bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64_t og, uint
                          uint32_t n_expert, uint32_t topk, uint32_t n_embd, uint32_t n_ff,
                          uint32_t n_tok, float *d_y, int32_t *d_ids, float *d_wts, void *d_ws,
                          uint64_t ws_bytes);
-/* RMSNorm, router product and softmax / top-k of up to 8 tokens in ONE launch (n_embd == 2048): d_xn
+/* RMSNorm, router product and softmax / top-k of up to 256 tokens in ONE launch (n_embd == 2048): d_xn
  * [n_tok][n_embd], d_logits [n_tok][n_expert], d_ids / d_wts [n_tok][topk], the values of
  * q4_hip_grouped_rms_n + q4_hip_gemv_dd_n + q4_hip_route_pf bit for bit.  false: another shape. */
 bool q4_cuda_route_small(const float *d_x, const float *d_norm_w, float eps, const float *d_router,

@@ -459,49 +459,61 @@ __global__ void softmax_topk_k(const float *__restrict__ logits, uint32_t n, uin
                       wsel, threadIdx.x);
 }
 
-// RMSNorm, router product and softmax / top-k of up to 8 tokens in ONE launch (n_embd == 2048): what
-// rms_q8_k (norm only), gemv_f32_x16_k and softmax_topk_k do as three, with the same operations in the
-// same order, so every value is bit for bit theirs.  A verify window's layer is a dozen launches of a
-// few microseconds each; this removes two.  Every CTA normalises all the rows itself (8 tokens x 8 KB
-// from L2) and keeps them in shared memory; a warp takes one router row; the CTA that finishes last
-// (a counter, no waiting) runs the top-k, one warp per token.
+// RMSNorm, router product and softmax / top-k of a batch of tokens in ONE launch (n_embd == 2048): what
+// rms_q8_k (norm only), gemv_f32_x16_k and softmax_topk_k do as three, with the same products and sums
+// in the same order (the sum of squares is formed in double in another order, which does not change
+// its float value).  grid (router rows / 8, tokens / 8): a CTA normalises its group's eight rows (a
+// warp per row, all loads in flight at once) into shared memory, then a warp takes one router row
+// through the eight tokens; the CTA that finishes a group last (a counter per group, no waiting) runs
+// the group's top-k, one warp per token.
 __global__ void __launch_bounds__(256) route_small_k(const float *__restrict__ x, const float *__restrict__ norm_w,
                                                      float eps, const float *__restrict__ W, uint32_t n_expert,
                                                      uint32_t n_tok, uint32_t topk, float *__restrict__ xn_out,
                                                      float *__restrict__ logits, int32_t *__restrict__ ids,
-                                                     float *__restrict__ wts, unsigned int *__restrict__ counter) {
-    extern __shared__ __align__(16) float rs_rows[];   // [n_tok][2048]; the last CTA reuses it for the probabilities
-    __shared__ double sh[8];
+                                                     float *__restrict__ wts, unsigned int *__restrict__ counters) {
+    extern __shared__ __align__(16) float rs_rows[];   // [8][2048]; the last CTA reuses it for the probabilities
     __shared__ float wsel[8][64];
     __shared__ uint32_t is_last;
     constexpr uint32_t n = 2048;
     const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
-    for (uint32_t t = 0; t < n_tok; t++) {
-        const float *xc = x + (uint64_t)t * n;
+    const uint32_t t0 = blockIdx.y * 8u, nt = min(8u, n_tok - t0);
+    if (warp < nt) {
+        const float4 *x4 = reinterpret_cast<const float4 *>(x + (uint64_t)(t0 + warp) * n);
+        float4 v[16];
+#pragma unroll
+        for (int j = 0; j < 16; j++) v[j] = x4[lane + 32 * j];
         double ss = 0.0;
-        for (uint32_t i = tid; i < n; i += 256) ss += (double)xc[i] * (double)xc[i];
+#pragma unroll
+        for (int j = 0; j < 16; j++)
+            ss += (double)v[j].x * (double)v[j].x + (double)v[j].y * (double)v[j].y +
+                  (double)v[j].z * (double)v[j].z + (double)v[j].w * (double)v[j].w;
 #pragma unroll
         for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) sh[warp] = ss;
-        __syncthreads();
-        double tot = 0.0;
-        for (uint32_t i = 0; i < 8; i++) tot += sh[i];
-        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(tot / (double)n), eps)));
-        for (uint32_t i = tid; i < n; i += 256) {
-            float v = __fmul_rn(xc[i], scale);
-            if (norm_w) v = __fmul_rn(v, norm_w[i]);
-            rs_rows[t * n + i] = v;
-            if (blockIdx.x == 0) xn_out[(uint64_t)t * n + i] = v;
+        const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn((float)(ss / (double)n), eps)));
+        float4 *r4 = reinterpret_cast<float4 *>(rs_rows + warp * n);
+        float4 *o4 = blockIdx.x == 0 ? reinterpret_cast<float4 *>(xn_out + (uint64_t)(t0 + warp) * n) : nullptr;
+#pragma unroll
+        for (int j = 0; j < 16; j++) {
+            float4 u;
+            u.x = __fmul_rn(v[j].x, scale), u.y = __fmul_rn(v[j].y, scale);
+            u.z = __fmul_rn(v[j].z, scale), u.w = __fmul_rn(v[j].w, scale);
+            if (norm_w) {
+                const float4 g = __ldg(reinterpret_cast<const float4 *>(norm_w) + lane + 32 * j);
+                u.x = __fmul_rn(u.x, g.x), u.y = __fmul_rn(u.y, g.y);
+                u.z = __fmul_rn(u.z, g.z), u.w = __fmul_rn(u.w, g.w);
+            }
+            r4[lane + 32 * j] = u;
+            if (o4) o4[lane + 32 * j] = u;
         }
-        __syncthreads();
     }
+    __syncthreads();
     const uint32_t r = blockIdx.x * 8u + warp;
     if (r < n_expert) {
         const float4 *w4 = reinterpret_cast<const float4 *>(W + (uint64_t)r * n);
         float4 w[16];
 #pragma unroll
         for (int j = 0; j < 16; j++) w[j] = __ldg(w4 + lane + 32 * j);
-        for (uint32_t t = 0; t < n_tok; t++) {
+        for (uint32_t t = 0; t < nt; t++) {
             const float4 *x4 = reinterpret_cast<const float4 *>(rs_rows + t * n);
             float acc = 0.f;
 #pragma unroll
@@ -510,18 +522,19 @@ __global__ void __launch_bounds__(256) route_small_k(const float *__restrict__ x
                 acc += w[j].x * b.x + w[j].y * b.y + w[j].z * b.z + w[j].w * b.w;
             }
             acc = q4b_warp_sum(acc);
-            if (lane == 0) logits[(uint64_t)t * n_expert + r] = 1.0f * acc;
+            if (lane == 0) logits[(uint64_t)(t0 + t) * n_expert + r] = 1.0f * acc;
         }
     }
     __threadfence();
     __syncthreads();
-    if (tid == 0) is_last = atomicInc(counter, gridDim.x - 1u) == gridDim.x - 1u ? 1u : 0u;   // wraps to 0 by itself
+    if (tid == 0)   // wraps to 0 by itself
+        is_last = atomicInc(counters + blockIdx.y, gridDim.x - 1u) == gridDim.x - 1u ? 1u : 0u;
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (uint32_t t = warp; t < n_tok; t += 8)
-        softmax_topk_warp(logits + (uint64_t)t * n_expert, n_expert, topk, ids + (uint64_t)t * topk,
-                          wts + (uint64_t)t * topk, -1, nullptr, rs_rows + t * 1024u, wsel[warp], lane);
+    if (warp < nt)
+        softmax_topk_warp(logits + (uint64_t)(t0 + warp) * n_expert, n_expert, topk, ids + (uint64_t)(t0 + warp) * topk,
+                          wts + (uint64_t)(t0 + warp) * topk, -1, nullptr, rs_rows + warp * 1024u, wsel[warp], lane);
 }
 
 // ------------------------------------------------------------------ gate/up + SwiGLU
@@ -1341,13 +1354,14 @@ bool q4b_route_tokens(const float *d_rlog, int32_t *d_ids, float *d_wts, uint32_
     g_q4b_launches++;
     return q4b_launch_ok("route_tokens");
 }
-// norm + router + top-k of a few tokens in one launch; false: the shape is not this kernel's (nothing
+// norm + router + top-k of up to ROUTE_MAX_TOK tokens in one launch; false: the shape is not this kernel's (nothing
 // queued, the caller issues the three launches)
-static unsigned int *g_route_counter = nullptr;
+static unsigned int *g_route_counter = nullptr;   // one counter per group of eight tokens
+constexpr uint32_t ROUTE_MAX_TOK = 256;
 bool q4b_route_small_warm() {
     if (g_route_counter) return true;
-    if (cudaMalloc(&g_route_counter, sizeof(unsigned int)) != cudaSuccess ||
-        cudaMemset(g_route_counter, 0, sizeof(unsigned int)) != cudaSuccess ||
+    if (cudaMalloc(&g_route_counter, (ROUTE_MAX_TOK / 8u) * sizeof(unsigned int)) != cudaSuccess ||
+        cudaMemset(g_route_counter, 0, (ROUTE_MAX_TOK / 8u) * sizeof(unsigned int)) != cudaSuccess ||
         cudaFuncSetAttribute(route_small_k, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2048 * 4) != cudaSuccess) {
         cudaGetLastError();
         return false;
@@ -1361,10 +1375,10 @@ void q4b_route_small_shutdown() {
 bool q4b_route_small(const float *x, const float *norm_w, float eps, const float *router, uint32_t n_expert,
                      uint32_t topk, uint32_t n_embd, uint32_t n_tok, float *xn, float *logits, int32_t *ids,
                      float *wts) {
-    if (!g_route_counter || n_embd != 2048u || n_tok == 0 || n_tok > 8u || n_expert > 1024u || topk > 64u ||
-        (((uintptr_t)router | (uintptr_t)x) & 15u))
+    if (!g_route_counter || n_embd != 2048u || n_tok == 0 || n_tok > ROUTE_MAX_TOK || n_expert > 1024u ||
+        topk > 64u || (((uintptr_t)router | (uintptr_t)x | (uintptr_t)norm_w | (uintptr_t)xn) & 15u))
         return false;
-    route_small_k<<<(n_expert + 7u) / 8u, 256, (size_t)n_tok * 2048u * 4u, g_q4b.stream>>>(
+    route_small_k<<<dim3((n_expert + 7u) / 8u, (n_tok + 7u) / 8u), 256, 8u * 2048u * 4u, g_q4b.stream>>>(
         x, norm_w, eps, router, n_expert, n_tok, topk, xn, logits, ids, wts, g_route_counter);
     g_q4b_launches++;
     return q4b_launch_ok("route_small");

@@ -552,16 +552,20 @@ extern "C" bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64
     // all tokens: norm, router, top-k (w.recv doubles as the T x n_expert logits: T * n_embd floats
     // hold them as long as n_expert <= n_embd)
     if (n_expert > n_embd) return false;
-    if (!q4_hip_grouped_rms_n(d_x, d_norm_w, w.xn, n_embd, 1, eps, T)) return false;
-    // Routing: with the peer buffers mapped a rank routes only its own tokens (norm, router product and
-    // top-k in one launch: the same values as the three launches) and the ranks' picks are gathered
-    // through peer memory (a few hundred bytes each); else every rank routes all T tokens itself.
-    const bool split = g_split_routing && g_ar.ok && t_local <= 8u && (size_t)t_local * topk * 8u <= GATHER_SLOT &&
-                       q4_cuda_route_small(d_x + (size_t)g_rank * t_local * n_embd, d_norm_w, eps, d_router, n_expert, topk,
-                                           n_embd, t_local, w.xn_l, w.logits, w.ids_l, w.wts_l);
-    if (split) {
+    // Routing.  Default: every rank routes all T tokens itself, norm + router product + top-k in one
+    // launch where the shape allows (the same values as the three launches).  With the peer buffers
+    // mapped and the split switched on, a rank routes only its own tokens and the ranks' picks are
+    // gathered through peer memory (a few hundred bytes each).
+    const bool want_split = g_split_routing && g_ar.ok && t_local <= 8u && (size_t)t_local * topk * 8u <= GATHER_SLOT;
+    if (want_split) {
+        if (!q4_hip_grouped_rms_n(d_x, d_norm_w, w.xn, n_embd, 1, eps, T)) return false;
+        if (!q4_cuda_route_small(d_x + (size_t)g_rank * t_local * n_embd, d_norm_w, eps, d_router, n_expert, topk,
+                                 n_embd, t_local, w.xn_l, w.logits, w.ids_l, w.wts_l))
+            return false;
         if (!gather_launch(w.ids_l, w.wts_l, w.ids, w.wts, t_local * topk, st)) return false;
-    } else {
+    } else if (!q4_cuda_route_small(d_x, d_norm_w, eps, d_router, n_expert, topk, n_embd, T, w.xn, w.recv, w.ids,
+                                    w.wts)) {
+        if (!q4_hip_grouped_rms_n(d_x, d_norm_w, w.xn, n_embd, 1, eps, T)) return false;
         if (!q4_hip_gemv_dd_n(Q4_T_F32, (const uint8_t *)d_router, n_expert, n_embd, w.xn, w.recv, 1.0f, T))
             return false;
         if (!q4_hip_route_pf(w.recv, w.ids, w.wts, T, n_expert, topk)) return false;

@@ -986,7 +986,7 @@ extern "C" bool q4_cuda_moe_layer_n(const uint8_t *base, uint64_t stride, uint64
                                 d_router, n_expert, topk, n_embd, n_ff, n_tok, d_y, d_ids, d_wts, d_ws, ws_bytes);
 }
 
-// RMSNorm, router product and softmax / top-k of up to 8 tokens in one launch (n_embd == 2048): the
+// RMSNorm, router product and softmax / top-k of up to 256 tokens in one launch (n_embd == 2048): the
 // values of q4_hip_grouped_rms_n + q4_hip_gemv_dd_n + q4_hip_route_pf, bit for bit.  false: not this
 // kernel's shape, nothing queued.
 extern "C" bool q4_cuda_route_small(const float *d_x, const float *d_norm_w, float eps, const float *d_router,
@@ -1018,7 +1018,7 @@ extern "C" bool q4_cuda_moe_layer_nt(const uint8_t *base, uint64_t stride, uint3
     const uint32_t k1 = topk + (sh ? 1u : 0u), n_e = n_expert + (sh ? 1u : 0u);
     const uint64_t rows = (uint64_t)n_tok * k1;
     const uint32_t n_entries = (uint32_t)(rows < n_e ? rows : n_e);  // used experts <= rows
-    // a few tokens: norm, router and top-k as one launch (same values); else the three launches
+    // up to 256 tokens: norm, router and top-k as one launch (same values); else the three launches
     if (!q4b_route_small(d_x, d_norm_w, eps, d_router, n_expert, topk, n_embd, n_tok, w.xn, w.logits, w.ids,
                          w.wts)) {
         if (!q4b_rms_rows(d_x, d_norm_w, w.xn, n_embd, eps, n_tok)) return false;

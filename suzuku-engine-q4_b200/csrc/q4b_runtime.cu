@@ -22,7 +22,7 @@ bool q4b_window_warm();  // q4b_grouped.cu: scratch of the verify-window path
 bool q4b_elem_warm();    // q4b_elem.cu: lists of the per-token exec, rows of the 2..8-row GEMV
 void q4b_elem_shutdown();
 bool q4b_mmvq_warm();    // q4b_mmvq.cu: quantised rows of the dense 8-bit product
-bool q4b_route_small_warm();   // q4b_decode.cu: counter of the one-launch routing of a few tokens
+bool q4b_route_small_warm();   // q4b_decode.cu: counters of the one-launch routing
 void q4b_route_small_shutdown();
 void q4b_mmvq_shutdown();
 bool q4b_wbuf_tiled(const void *p);

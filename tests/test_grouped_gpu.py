@@ -30,6 +30,45 @@ def test_route_pf_matches_host_softmax_topk(dev, oracle):
     assert not dev.lib.q4_hip_route_pf(dev.upload(logits), d_ids, d_w, n_tok, n_exp, 0)
 
 
+@pytest.mark.parametrize("n_tok", [1, 4, 8, 9, 37, 64, 256])
+def test_one_launch_routing_is_the_three_launches_bit_for_bit(dev, n_tok):
+    """q4_cuda_route_small (norm + router product + top-k in one launch, a counter per group of eight
+    tokens) against q4_hip_grouped_rms_n + q4_hip_gemv_dd_n + q4_hip_route_pf on the same rows, twice in
+    a row (the counters must be back at zero); a batch beyond its limit is refused with nothing queued."""
+    lib = dev.lib
+    rng = np.random.default_rng(100 + n_tok)
+    n_exp, topk, n = 512, 10, 2048
+    x = (rng.standard_normal((n_tok, n)) * rng.uniform(0.1, 30.0, (n_tok, 1))).astype(np.float32)
+    nw = rng.uniform(0.5, 1.5, n).astype(np.float32)
+    router = (rng.standard_normal((n_exp, n)) * 0.02).astype(np.float32)
+    d_x, d_nw, d_r = dev.upload(x), dev.upload(nw), dev.upload(router)
+    d_xn0, d_lg0 = dev.malloc(n_tok * n * 4), dev.malloc(n_tok * n_exp * 4)
+    d_i0, d_w0 = dev.malloc(n_tok * topk * 4), dev.malloc(n_tok * topk * 4)
+    assert lib.q4_hip_grouped_rms_n(d_x, d_nw, d_xn0, n, 1, 1e-6, n_tok)
+    assert lib.q4_hip_gemv_dd_n(0, d_r, n_exp, n, d_xn0, d_lg0, 1.0, n_tok)
+    assert lib.q4_hip_route_pf(d_lg0, d_i0, d_w0, n_tok, n_exp, topk)
+    ref = (dev.download(d_xn0, (n_tok, n), np.uint32), dev.download(d_lg0, (n_tok, n_exp), np.uint32),
+           dev.download(d_i0, (n_tok, topk), np.int32), dev.download(d_w0, (n_tok, topk), np.uint32))
+    for nw_ptr in (d_nw, None):
+        if nw_ptr is None:
+            assert lib.q4_hip_grouped_rms_n(d_x, None, d_xn0, n, 1, 1e-6, n_tok)
+            assert lib.q4_hip_gemv_dd_n(0, d_r, n_exp, n, d_xn0, d_lg0, 1.0, n_tok)
+            assert lib.q4_hip_route_pf(d_lg0, d_i0, d_w0, n_tok, n_exp, topk)
+            ref = (dev.download(d_xn0, (n_tok, n), np.uint32), dev.download(d_lg0, (n_tok, n_exp), np.uint32),
+                   dev.download(d_i0, (n_tok, topk), np.int32), dev.download(d_w0, (n_tok, topk), np.uint32))
+        for rep in range(2):
+            d_xn, d_lg = dev.malloc(n_tok * n * 4), dev.malloc(n_tok * n_exp * 4)
+            d_i, d_w = dev.malloc(n_tok * topk * 4), dev.malloc(n_tok * topk * 4)
+            assert lib.q4_cuda_route_small(d_x, nw_ptr, 1e-6, d_r, n_exp, topk, n, n_tok, d_xn, d_lg, d_i, d_w)
+            got = (dev.download(d_xn, (n_tok, n), np.uint32), dev.download(d_lg, (n_tok, n_exp), np.uint32),
+                   dev.download(d_i, (n_tok, topk), np.int32), dev.download(d_w, (n_tok, topk), np.uint32))
+            for a, b, what in zip(got, ref, ("xn", "logits", "ids", "weights")):
+                assert (a == b).all(), (what, rep)
+    assert not lib.q4_cuda_route_small(d_x, d_nw, 1e-6, d_r, n_exp, topk, n, 257, d_xn, d_lg, d_i, d_w)
+    assert not lib.q4_cuda_route_small(d_x, d_nw, 1e-6, d_r, n_exp, topk, 1024, n_tok, d_xn, d_lg, d_i, d_w)
+    assert lib.q4_cuda_device_error() == 0
+
+
 def test_assign_pf_invariants(dev):
     """17 tokens in groups of 8 (src/q4_test.c:1927-2145): every row placed once,
     back-map consistent, rows of an expert contiguous and hole-free."""
