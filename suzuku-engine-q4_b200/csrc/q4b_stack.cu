@@ -174,9 +174,10 @@ __device__ __forceinline__ void xw_store(unsigned long long *p, float v, uint32_
     asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 // Four consecutive words (32-byte aligned); bounded.  The loop polls without pausing: a pause
-// between polls (nanosleep) cost a microsecond per layer, and so did keeping more than one
-// group of a thread in flight or letting one lane per warp watch for the rest -- what counts
-// is how soon after the store the first successful load is issued.
+// between polls (nanosleep) cost a microsecond per layer, and so did polling several groups of
+// a thread together until all had come or letting one lane per warp watch for the rest -- what
+// counts is how soon after the store the first successful load is issued.  (A single first
+// look at several groups before their poll loops does pay: see the hidden rows.)
 __device__ __forceinline__ float4 xw_poll4(const unsigned long long *p, uint32_t ep, uint32_t limit,
                                            uint32_t *err) {
     unsigned long long a = 0, b = 0, c = 0, d = 0;
