@@ -59,8 +59,9 @@ __global__ void ep_sum_k(const float *__restrict__ recv, float *__restrict__ y, 
 // ---- the layer's all-reduce over peer memory (one kernel, no library call) ----
 // Every rank exports one buffer (two copies of up to AR_MAX_ELEMS floats, then ready words) through
 // CUDA IPC; the others map it.  The kernel on rank r: (1) copies its partial rows into its exported
-// buffer (copy p = epoch & 1), fences at system scope, and the CTA that finishes last stores the
-// epoch into word [p][r] of EVERY rank's ready words (plain stores to peer memory); (2) waits,
+// buffer (copy p = epoch & 1), fences at GPU scope (the rows stay in its own memory) and counts; the
+// CTA that counts last stores the epoch into word [p][r] of EVERY rank's ready words (release stores
+// at system scope to peer memory, one thread per rank); (2) waits,
 // bounded in time, until its own ready words [p][0..G) all show the epoch; (3) every thread sums its
 // elements over the ranks' buffers in rank order (plain loads from peer memory over NVLink), so all
 // ranks end with the same bits; (4) the CTA that finishes last publishes the epoch for the next
@@ -88,7 +89,7 @@ struct ArArgs {
     unsigned long long wait_ns;
 };
 __global__ void __launch_bounds__(AR_THREADS) ep_allreduce_k(const __grid_constant__ ArArgs a) {
-    __shared__ uint32_t s_epoch;
+    __shared__ uint32_t s_epoch, s_last;
     const uint32_t tid = threadIdx.x;
     if (tid == 0) {
         uint32_t e;
@@ -102,16 +103,19 @@ __global__ void __launch_bounds__(AR_THREADS) ep_allreduce_k(const __grid_consta
     const float4 *src4 = reinterpret_cast<const float4 *>(a.src);
     for (uint32_t i = gtid; i < a.n4; i += gsz) mine[i] = src4[i];
     __syncthreads();
+    // The rows live in this GPU's memory: a fence at GPU scope and a count per CTA; the CTA that counts
+    // last tells every rank (this one too), one thread per rank so that the system-scope release stores
+    // go out side by side (one thread storing them in turn spent a fence per rank).
     if (tid == 0) {
-        __threadfence_system();   // one fence per CTA, after the barrier: it covers the CTA's stores
+        __threadfence();
         const uint32_t old = atomicAdd(a.ctl + 1, 1u);
-        if (old % gridDim.x == gridDim.x - 1u) {   // every CTA's rows are out: tell every rank (this one too)
-            __threadfence_system();
-            for (uint32_t r = 0; r < a.world; r++)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.ready[r] + p * AR_MAX_RANKS + a.rank), "r"(epoch)
-                             : "memory");
-        }
+        s_last = old % gridDim.x == gridDim.x - 1u ? 1u : 0u;
+        if (s_last) __threadfence();
     }
+    __syncthreads();
+    if (s_last && tid < a.world)
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.ready[tid] + p * AR_MAX_RANKS + a.rank), "r"(epoch)
+                     : "memory");
     if (tid < a.world) {
         const uint32_t *w = a.ready[a.rank] + p * AR_MAX_RANKS + tid;
         unsigned long long t0;
@@ -187,14 +191,11 @@ __global__ void __launch_bounds__(256) ep_gather_picks_k(const __grid_constant__
         }
     }
     __syncthreads();
-    if (tid == 0) {
-        __threadfence_system();
-        for (uint32_t r = 0; r < a.world; r++)
-            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t *>(a.mem[r] + AR_BUF_BYTES) +
-                                                                  2u * AR_MAX_RANKS + p * AR_MAX_RANKS + a.rank),
-                         "r"(epoch)
-                         : "memory");
-    }
+    if (tid < a.world)   // one thread per rank: the release stores (each orders the CTA's pushes before it) go out side by side
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(reinterpret_cast<uint32_t *>(a.mem[tid] + AR_BUF_BYTES) +
+                                                              2u * AR_MAX_RANKS + p * AR_MAX_RANKS + a.rank),
+                     "r"(epoch)
+                     : "memory");
     if (tid < a.world) {
         const uint32_t *w = reinterpret_cast<const uint32_t *>(a.mem[a.rank] + AR_BUF_BYTES) + 2u * AR_MAX_RANKS +
                             p * AR_MAX_RANKS + tid;

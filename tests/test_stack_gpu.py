@@ -75,7 +75,7 @@ class Stack:
         self.lib.q4_hip_experts_free_a(self.arena)
 
 
-@pytest.mark.parametrize("n_expert,topk,n_layers", [(64, 8, 4), (512, 10, 2), (24, 4, 3)])
+@pytest.mark.parametrize("n_expert,topk,n_layers", [(64, 8, 4), (512, 10, 2), (24, 4, 3), (32, 11, 1), (16, 1, 2)])
 def test_stack_matches_oracle_and_one_layer_calls(dev, pkg, oracle, n_expert, topk, n_layers):
     layers = [pkg.synth.layer(300 + 7 * l + n_expert, n_expert, H, F) for l in range(n_layers)]
     st = Stack(dev, pkg, layers, topk)
