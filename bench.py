@@ -950,12 +950,14 @@ def run_ep(a, pkg, rank, world, local, warmup):
         e2 = ep.q4_cuda_ep_error()
         if e2:
             raise SystemExit("expert-parallel error word %#x" % e2)
-        details["all_reduce"] = "ncclAllReduce"
-        # variants of the same job, for comparison: the library's own all-reduce kernel over IPC-mapped
-        # peer memory, and the routing split over the ranks with a peer gather of the picks
+        own = ep.q4_cuda_ep_allreduce_mode(2) == 1
+        details["all_reduce"] = ("ep_allreduce_k: the library's kernel over IPC-mapped peer memory" if own
+                                 else "ncclAllReduce (the ranks' buffers could not be mapped through CUDA IPC)")
+        # variants of the same job, for comparison: ncclAllReduce instead of the library's kernel, and the
+        # routing split over the ranks with a peer gather of the picks
         variants = {}
-        if ep.q4_cuda_ep_allreduce_mode(1) == 1:
-            for name, ar, split in (("own_all_reduce_kernel", 1, 0), ("split_routing", 0, 1)):
+        if own:
+            for name, ar, split in (("nccl_all_reduce", 0, 0), ("split_routing", 2, 1)):
                 ep.q4_cuda_ep_allreduce_mode(ar)
                 ep.q4_cuda_ep_split_routing(split)
                 job_n = BatchJob(pkg, model, ep, rank, world, EP_TOKENS, range(n_layers))

@@ -51,13 +51,13 @@ bool q4_cuda_ep_layer_ar(const uint8_t *base, uint64_t stride, uint64_t og, uint
                          int has_shared, const float *d_x, const float *d_norm_w, float eps,
                          const float *d_router, uint32_t n_expert, uint32_t topk, uint32_t n_embd,
                          uint32_t n_ff, uint32_t t_local, float *d_y, void *d_ws, uint64_t ws_bytes);
-/* The all-reduce of q4_cuda_ep_layer_ar: 0 or 2 (default) = ncclAllReduce; 1 = the library's own kernel
- * over peer memory (every rank exports one buffer through CUDA IPC at q4_cuda_ep_init; a rank's kernel
- * copies its partial rows there, signals every rank with plain stores, waits -- bounded -- for the
- * others' signals and sums the ranks' rows in rank order with plain loads over NVLink), available when
- * every rank could map every other rank's buffer.  Measured inside the 48-layer job it is 2-4 us per
- * layer slower than ncclAllReduce, hence not the default.  Returns 1 when the kernel is in effect; every
- * rank must make the same call.  q4_cuda_ep_error: 0, or 0x1000 after a wait ran out (synchronises). */
+/* The all-reduce of q4_cuda_ep_layer_ar: 1 or 2 (default) = the library's own kernel over peer memory
+ * (every rank exports one buffer through CUDA IPC at q4_cuda_ep_init; a rank's kernel copies its partial
+ * rows there, signals every rank with release stores, waits -- bounded -- for the others' signals and sums
+ * the ranks' rows in rank order with plain loads over NVLink), used when every rank could map every other
+ * rank's buffer, ncclAllReduce otherwise; 0 = ncclAllReduce.  Measured inside the 48-layer job the kernel
+ * is 9-10 us per layer faster.  Returns 1 when the kernel is in effect; every rank must make the same
+ * call.  q4_cuda_ep_error: 0, or 0x1000 after a wait ran out (synchronises). */
 int q4_cuda_ep_allreduce_mode(int mode);
 /* Routing of q4_cuda_ep_layer_ar when the peer buffers are mapped: 1 = a rank routes only its own tokens
  * (norm, router product, top-k in one launch) and the ranks' picks are gathered through peer memory;

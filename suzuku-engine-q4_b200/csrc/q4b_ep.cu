@@ -278,13 +278,13 @@ EpWs carve(uint8_t *p, uint32_t world, uint32_t t_local, uint32_t topk, uint32_t
     return w;
 }
 
-int g_ar_mode = 2;   // 0: ncclAllReduce, 1: the peer-memory kernel where it was set up, 2: the default
+int g_ar_mode = 2;   // 0: ncclAllReduce, 1: the peer-memory kernel, 2 (default): the kernel where it was set up
 // The kernel's cost is a handful of NVLink round trips (copy out, signal, wait, read) whatever the number
-// of ranks.  Measured inside the 48-layer job: 4 us per layer slower than ncclAllReduce at 2 ranks, 2 us
-// slower at 8 (NCCL reduces inside the switch there).  So the default is ncclAllReduce; the kernel stays
-// selectable (mode 1).
+// of ranks.  Measured inside the 48-layer job of 64 tokens it is 10 us per layer faster than
+// ncclAllReduce at 2 ranks and 9 us at 8 (512 KB per layer: latency, not bandwidth); with one thread
+// storing the ranks' ready flags in turn it had been 2-4 us slower.
 int g_split_routing = 0;   // q4_cuda_ep_split_routing
-bool ar_use_kernel() { return g_ar.ok && g_ar_mode == 1; }
+bool ar_use_kernel() { return g_ar.ok && g_ar_mode != 0; }
 
 void ar_teardown() {
     for (uint32_t r = 0; r < AR_MAX_RANKS; r++)
@@ -414,9 +414,9 @@ extern "C" bool q4_cuda_ep_init(const uint8_t *id128, int rank, int world) {
     if (world > 1) (void)ar_setup();   // without it q4_cuda_ep_layer_ar keeps ncclAllReduce
     return true;
 }
-// Which all-reduce q4_cuda_ep_layer_ar uses: 1 (default) the library's own kernel over mapped peer
-// memory where every rank could map every other rank's buffer, 0 ncclAllReduce.  Returns what is in
-// effect.  Every rank must make the same call.
+// Which all-reduce q4_cuda_ep_layer_ar uses: 1 or 2 (default) the library's own kernel over mapped peer
+// memory where every rank could map every other rank's buffer (else ncclAllReduce), 0 ncclAllReduce.
+// Returns 1 when the kernel is in effect.  Every rank must make the same call.
 extern "C" int q4_cuda_ep_allreduce_mode(int mode) {
     if (mode >= 0 && mode <= 2) g_ar_mode = mode;
     return ar_use_kernel() ? 1 : 0;
@@ -625,8 +625,13 @@ extern "C" bool q4_cuda_ep_exchange_floor_us(uint32_t t_local, uint32_t n_embd, 
                     EP_NCCL(ncclRecv(w.recv + p * blk, blk, ncclFloat, (int)p, g_comm, st));
                 }
                 EP_NCCL(ncclGroupEnd());
-            } else {
-                EP_NCCL(ncclAllReduce(w.partial, w.recv, (size_t)T * n_embd, ncclFloat, ncclSum, g_comm, st));
+            } else {   // the all-reduce q4_cuda_ep_layer_ar would use
+                const size_t n = (size_t)T * n_embd;
+                if (ar_use_kernel() && n <= AR_MAX_ELEMS && (n % 4u) == 0) {
+                    if (!ar_launch(w.partial, w.recv, n, st)) return false;
+                } else {
+                    EP_NCCL(ncclAllReduce(w.partial, w.recv, n, ncclFloat, ncclSum, g_comm, st));
+                }
             }
         }
         cudaEventRecord(e1, st);

@@ -107,7 +107,7 @@ def main():
     # the all-reduce itself: the library's kernel over mapped peer memory where every rank could map
     # the others' buffers (mode 1), else ncclAllReduce.  Repeated calls give the same bits (sum in rank
     # order; the two buffer copies alternate), and the two modes agree up to the order of the sum.
-    mode = ep.q4_cuda_ep_allreduce_mode(1)        # ask for the kernel (the default is ncclAllReduce)
+    mode = ep.q4_cuda_ep_allreduce_mode(1)        # ask for the kernel (also the default where the buffers could be mapped)
     open(os.path.join(out_dir, "mode%d.txt" % rank), "w").write(str(mode))
     for _ in range(5):
         assert ep.q4_cuda_ep_layer_ar(base, stride, 0, F * rb, 2 * F * rb, 1, d_xa, d_norm, 1e-6, d_router,
