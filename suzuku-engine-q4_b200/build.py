@@ -19,7 +19,7 @@ def sources():
     out = []
     for root, _, files in os.walk(CSRC):
         for f in files:
-            if f.endswith((".cu", ".cuh", ".h")) and f != "q4b_ep.cu":
+            if f.endswith((".cu", ".cuh", ".h")) and f not in ("q4b_ep.cu", "tile_dot_bench.cu"):
                 out.append(os.path.join(root, f))
     out.append(os.path.join(os.path.dirname(HERE), "include", "q4cuda.h"))
     return out
