@@ -68,22 +68,20 @@ namespace mmqtc {
 constexpr uint32_t NDW = 16;           // decode + epilogue warps
 constexpr uint32_t NT = 32 * (NDW + 2); // plus one warp that issues the MMAs and one that issues the copies
 constexpr uint32_t MT = 128;           // weight rows per CTA
-constexpr uint32_t NB = 64;            // activation rows per pass
+constexpr uint32_t NB = 128;           // activation rows per pass at most (the MMA's N is two planes of them: 256)
 constexpr uint32_t KS = 128;           // k per step (four groups = 16 K chunks of 8 halves)
 constexpr uint32_t A_ATOM = MT * 128;  // 64 k of the CTA's weight rows: [row][128 B], 128-byte swizzle
 constexpr uint32_t A_BYTES = 2 * A_ATOM;         // a step: 32 KB
-constexpr uint32_t B_ATOM = 2 * NB * 128;  // 64 k of the pass's rows, first plane then second plane:
-                                           // [plane][row][128 B] under the 128-byte swizzle
+// An activation atom: 64 k of the pass's rows, first plane then second plane, [plane][row][128 B]
+// under the 128-byte swizzle: 2 * box * 128 bytes, box = rows per pass of the launch (16, 64 or 128).
 constexpr uint32_t B_SBO = 1024;       // eight rows of 128 bytes
 constexpr uint32_t NSTAGE_B = 2;
 constexpr uint32_t NA = 2;             // weight-operand buffers (decode runs up to NA steps ahead of the MMAs)
 constexpr uint32_t NACC = 2;           // accumulators: super-blocks in flight between MMA and epilogue
-constexpr uint32_t ACC_COLS = 2 * NB;  // an accumulator: the two planes' products side by side
-constexpr uint32_t TMEM_COLS = NACC * ACC_COLS;
+// an accumulator: the two planes' products side by side, 2 * box columns; NACC of them are allocated
 
 struct __align__(1024) Smem {
     uint8_t a[NA][A_BYTES];
-    uint8_t b[NSTAGE_B][2][B_ATOM];   // every [row][128 B] block starts on a 1024-byte boundary
     float dr[4][MT];           // d of the weight rows of the last four super-blocks
     uint32_t tabk[512];        // code bytes 2c with bit 7 flipped
     unsigned long long bar_mma[NA];    // a step's MMAs are complete (operand buffer free)
@@ -94,8 +92,13 @@ struct __align__(1024) Smem {
     uint32_t tmem_base;
     uint32_t failed;
 };
-constexpr uint32_t SMEM_BYTES = 136 * 1024;
-static_assert(sizeof(Smem) <= SMEM_BYTES, "shared memory layout");
+// behind it: b[NSTAGE_B][2][atom], every [row][128 B] block on a 1024-byte boundary
+constexpr uint32_t B_OFF = (uint32_t)((sizeof(Smem) + 1023u) & ~1023u);
+__host__ __device__ constexpr uint32_t b_atom_bytes(uint32_t box) { return 2u * box * 128u; }
+__host__ __device__ constexpr uint32_t smem_bytes(uint32_t box) {
+    return B_OFF + NSTAGE_B * 2u * b_atom_bytes(box) + 1024u;
+}
+static_assert(smem_bytes(NB) <= 227u * 1024u, "shared memory layout");
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
     return (uint32_t)__cvta_generic_to_shared(p);
@@ -204,7 +207,7 @@ struct Args {
     uint32_t min_rows;           // entries with fewer rows are left to the CUDA-core kernel
     const uint2 *work;           // (entry, first row) per pass, built by worklist_k
     const uint32_t *n_work;
-    uint32_t pass_rows;          // activation rows per pass: 64, or 16 to spread a small call over more CTAs
+    uint32_t pass_rows;          // activation rows per pass: 128 or 64, or 16 to spread a small call over more CTAs
     uint32_t box_rows;           // rows per activation copy = the MMA's N per plane
     uint32_t mt_per_cta;         // 128-row weight tiles one CTA walks (grid.x = tiles / this)
     const float *rs;             // per activation row: the power of two its fp16 planes were divided by
@@ -358,8 +361,12 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
     const uint32_t row0 = blockIdx.x * MT * n_mt;
     const uint32_t n_s = n_it * n_mt;               // steps over all its tiles: one pipeline
     const uint32_t nrows = (uint32_t)(r1 - rc);
-    const uint32_t box = a.box_rows;                // rows a copy brings: 64, or 16 for the small passes
+    const uint32_t box = a.box_rows;                // rows a copy brings = rows per pass: 16, 64 or 128
     const uint32_t idesc = instr_desc(2u * box);
+    const uint32_t b_atom = b_atom_bytes(box);
+    const uint32_t acc_cols = 2u * box;             // columns of one accumulator
+    const uint32_t tmem_cols = max(32u, NACC * acc_cols);   // 64, 256 or 512: a power of two
+    uint8_t *const sb_base = smem_raw + B_OFF;
 
     if (tid < 512u) s.tabk[tid] = (__ldg(a.codes + tid) << 1) ^ 0x80808080u;
     if (tid == 0) {
@@ -378,7 +385,7 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          smem_u32(&s.tmem_base)),
-                     "r"(TMEM_COLS)
+                     "r"(tmem_cols)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -399,7 +406,7 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
     if (warp == NDW) {
         // ---- the MMA warp (one lane): waits for both operands of a step, issues its MMAs, commits ----
         if (lane == 0) {
-            const uint64_t a_d0 = smem_desc_sw128(smem_u32(s.a[0])), b_d0 = smem_desc_sw128(smem_u32(s.b[0][0]));
+            const uint64_t a_d0 = smem_desc_sw128(smem_u32(s.a[0])), b_d0 = smem_desc_sw128(smem_u32(sb_base));
             const uint32_t a_lo0 = (uint32_t)a_d0, a_hi = (uint32_t)(a_d0 >> 32);
             const uint32_t b_lo0 = (uint32_t)b_d0, b_hi = (uint32_t)(b_d0 >> 32);
             for (uint32_t it = 0; it < n_s; it++) {   // it: step over all tiles
@@ -410,12 +417,12 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
                 wait(&s.bar_b[sb], (it / NSTAGE_B) & 1u, 1u);
                 tc_fence_after();
                 // descriptors differ from step to step only in the start-address field (low word)
-                const uint32_t a_lo = a_lo0 + buf * (A_BYTES >> 4), b_lo = b_lo0 + sb * ((2u * B_ATOM) >> 4);
-                const uint32_t d_addr = tmem + accb * ACC_COLS;
+                const uint32_t a_lo = a_lo0 + buf * (A_BYTES >> 4), b_lo = b_lo0 + sb * ((2u * b_atom) >> 4);
+                const uint32_t d_addr = tmem + accb * acc_cols;
 #pragma unroll
                 for (uint32_t k = 0; k < 8; k++)   // one MMA per 16 k: both planes are its N side
                     mma_f16(d_addr, desc64(a_lo + (k >> 2) * (A_ATOM >> 4) + (k & 3u) * 2u, a_hi),
-                            desc64(b_lo + (k >> 2) * (B_ATOM >> 4) + (k & 3u) * 2u, b_hi), idesc,
+                            desc64(b_lo + (k >> 2) * (b_atom >> 4) + (k & 3u) * 2u, b_hi), idesc,
                             k ? 1u : (it & 1u));
                 mma_commit(&s.bar_mma[buf]);
                 mma_commit(&s.b_empty[sb]);
@@ -432,8 +439,9 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
                 mbar_expect_tx(&s.bar_b[sb], 4u * box * 128u);
 #pragma unroll
                 for (uint32_t at = 0; at < 2; at++) {
-                    tma_load_2d(s.b[sb][at], &map_h1, &s.bar_b[sb], (int)(it * KS + at * 64u), rc);
-                    tma_load_2d(s.b[sb][at] + box * 128u, &map_h2, &s.bar_b[sb], (int)(it * KS + at * 64u), rc);
+                    uint8_t *dstb = sb_base + (sb * 2u + at) * b_atom;
+                    tma_load_2d(dstb, &map_h1, &s.bar_b[sb], (int)(it * KS + at * 64u), rc);
+                    tma_load_2d(dstb + box * 128u, &map_h2, &s.bar_b[sb], (int)(it * KS + at * 64u), rc);
                 }
             }
         }
@@ -448,14 +456,20 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
         // chunk (4 (d_g & 1) + j) ^ (row & 7)
         const uint32_t d_base = (d_g >> 1) * A_ATOM + d_row * 128u;
         const uint32_t d_c0 = 4u * (d_g & 1u), d_x = lane & 7u;
-        // epilogue: tensor-memory lanes of this warp's quadrant, 16 of the 64 columns
+        // epilogue: tensor-memory lanes of this warp's quadrant; of the pass's columns (activation
+        // rows) the 16-column slabs e_cs and, in a pass of more than 64 rows, e_cs + 4
+        constexpr uint32_t NSL = NB / 64u;
         const uint32_t e_q = warp & 3u, e_cs = warp >> 2;
         const uint32_t e_row = 32u * e_q + lane;
         const uint32_t e_taddr = tmem + ((32u * e_q) << 16) + 16u * e_cs;
-        const bool e_live = 16u * e_cs < nrows;
-        float acc[16];
+        bool e_live[NSL];
+        float acc[NSL][16];
 #pragma unroll
-        for (int j = 0; j < 16; j++) acc[j] = 0.f;
+        for (uint32_t h = 0; h < NSL; h++) {
+            e_live[h] = 16u * (e_cs + 4u * h) < nrows;
+#pragma unroll
+            for (int j = 0; j < 16; j++) acc[h][j] = 0.f;
+        }
 
         // steps are fetched in order: (tile, step in tile) advance by counters, not divisions
         uint32_t pf_it = 0;
@@ -476,28 +490,36 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
             if (done & 1u) {
                 const uint32_t sbk = done >> 1;
                 tc_fence_after();
-                if (e_live) {
-                    const float dr = s.dr[sbk & 3u][e_row];
-                    uint32_t v[16], v2[16];
-                    tmem_ld16(e_taddr + (sbk % NACC) * ACC_COLS, v);
-                    tmem_ld16(e_taddr + (sbk % NACC) * ACC_COLS + box, v2);
-                    tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; j++)
-                        acc[j] = fmaf(dr, __uint_as_float(v[j]) + __uint_as_float(v2[j]), acc[j]);
+                for (uint32_t h = 0; h < NSL; h++) {
+                    if (e_live[h]) {   // warp-uniform
+                        const float dr = s.dr[sbk & 3u][e_row];
+                        uint32_t v[16], v2[16];
+                        tmem_ld16(e_taddr + (sbk % NACC) * acc_cols + 64u * h, v);
+                        tmem_ld16(e_taddr + (sbk % NACC) * acc_cols + 64u * h + box, v2);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            acc[h][j] = fmaf(dr, __uint_as_float(v[j]) + __uint_as_float(v2[j]), acc[h][j]);
+                    }
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&s.acc_empty[sbk % NACC]);
                 if (rt_it + 1u == n_it) {   // the tile's last super-block: write its rows out
-                    if (e_live)
-                        store_tile(a.dst + (uint64_t)(rc + 16 * (int32_t)e_cs) * a.ld_dst + row0 + rt_m * MT + e_row,
-                                   a.ld_dst, a.rs + rc + 16 * (int32_t)e_cs, min(16u, nrows - 16u * e_cs),
-                                   make_float4(acc[0], acc[1], acc[2], acc[3]), make_float4(acc[4], acc[5], acc[6], acc[7]),
-                                   make_float4(acc[8], acc[9], acc[10], acc[11]),
-                                   make_float4(acc[12], acc[13], acc[14], acc[15]));
 #pragma unroll
-                    for (int j = 0; j < 16; j++) acc[j] = 0.f;
+                    for (uint32_t h = 0; h < NSL; h++) {
+                        const uint32_t cs = e_cs + 4u * h;
+                        if (e_live[h])
+                            store_tile(a.dst + (uint64_t)(rc + 16 * (int32_t)cs) * a.ld_dst + row0 + rt_m * MT + e_row,
+                                       a.ld_dst, a.rs + rc + 16 * (int32_t)cs, min(16u, nrows - 16u * cs),
+                                       make_float4(acc[h][0], acc[h][1], acc[h][2], acc[h][3]),
+                                       make_float4(acc[h][4], acc[h][5], acc[h][6], acc[h][7]),
+                                       make_float4(acc[h][8], acc[h][9], acc[h][10], acc[h][11]),
+                                       make_float4(acc[h][12], acc[h][13], acc[h][14], acc[h][15]));
+#pragma unroll
+                        for (int j = 0; j < 16; j++) acc[h][j] = 0.f;
+                    }
                 }
             }
             if (++rt_it == n_it) {
@@ -544,7 +566,7 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
     __syncthreads();
     if (warp == 0) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(tmem_cols)
                      : "memory");
     }
 }
@@ -607,7 +629,8 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
                                   CUtensorMapFloatOOBfill);
 static EncodeTiledFn g_encode = nullptr;
 static bool g_ready = false, g_tried = false;
-constexpr uint32_t WORK_CAP = 1u << 16;   // passes per launch: entries + rows / 64 must fit
+constexpr uint32_t WORK_CAP = 1u << 16;   // passes per launch: entries + rows / (rows per pass) must fit
+constexpr uint64_t PASS128_MIN_ROWS = 8192;   // calls with at least this many rows take 128 of them per pass
 static uint2 *g_work = nullptr;           // two lists, used alternately, so that two launches in a
 static uint32_t *g_n_work = nullptr;      // row (gate/up, then down) never share one
 static uint32_t g_work_turn = 0;
@@ -625,9 +648,9 @@ bool warm() {
         return false;
     }
     g_encode = (EncodeTiledFn)fn;
-    if (cudaFuncSetAttribute(mmq_tc_k<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+    if (cudaFuncSetAttribute(mmq_tc_k<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(NB)) !=
             cudaSuccess ||
-        cudaFuncSetAttribute(mmq_tc_k<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) !=
+        cudaFuncSetAttribute(mmq_tc_k<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(NB)) !=
             cudaSuccess) {
         cudaGetLastError();
         return false;
@@ -654,7 +677,9 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
     if (!g_ready || !shape_ok(w_rows, cols) || rows == 0 || rows > 0x7fffffffull) return false;
     // a small call (decode batches: a handful of entries reach the threshold) is cut into
     // passes of 16 rows so that its few entries still spread over many SMs
-    const uint32_t pass_rows = rows <= 2048u ? 16u : NB;
+    // a large one in passes of 128 rows: an expert's weights are decoded once per pass, and with a
+    // skewed routing most rows belong to experts with hundreds of them
+    const uint32_t pass_rows = rows <= 2048u ? 16u : rows < PASS128_MIN_ROWS ? 64u : NB;
     const uint64_t max_items = (uint64_t)n_entries + rows / pass_rows;
     if (max_items > WORK_CAP || max_items > 65535u) return false;   // the pass index is gridDim.y
     CUtensorMap maps[2];
@@ -704,9 +729,9 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
     a.mt_per_cta = mt;
     const dim3 grid(n_tiles / mt, (unsigned)max_items);
     if (tiled)
-        mmq_tc_k<true><<<grid, NT, SMEM_BYTES, stream>>>(a, maps[0], maps[1]);
+        mmq_tc_k<true><<<grid, NT, smem_bytes(a.box_rows), stream>>>(a, maps[0], maps[1]);
     else
-        mmq_tc_k<false><<<grid, NT, SMEM_BYTES, stream>>>(a, maps[0], maps[1]);
+        mmq_tc_k<false><<<grid, NT, smem_bytes(a.box_rows), stream>>>(a, maps[0], maps[1]);
     return true;
 }
 
