@@ -82,7 +82,9 @@ constexpr uint32_t NACC = 2;           // accumulators: super-blocks in flight b
 
 struct __align__(1024) Smem {
     uint8_t a[NA][A_BYTES];
-    float dr[4][MT];           // d of the weight rows of the last four super-blocks
+    uint16_t dr[3][MT];        // d (its fp16 bits) of the weight rows of the last three super-blocks: the
+                               // decode of the fastest warp is at most two super-blocks ahead of the
+                               // slowest warp's epilogue (operand buffers and their barriers bound it)
     uint32_t tabk[512];        // code bytes 2c with bit 7 flipped
     unsigned long long bar_mma[NA];    // a step's MMAs are complete (operand buffer free)
     unsigned long long a_full[NA];     // all decode warps have written a step's weights
@@ -95,9 +97,14 @@ struct __align__(1024) Smem {
 // behind it: b[NSTAGE_B][2][atom], every [row][128 B] block on a 1024-byte boundary
 constexpr uint32_t B_OFF = (uint32_t)((sizeof(Smem) + 1023u) & ~1023u);
 __host__ __device__ constexpr uint32_t b_atom_bytes(uint32_t box) { return 2u * box * 128u; }
+// What a launch asks for decides how the SM's 256 KB are split between shared memory and L1, and the
+// decode warps' field loads live in L1 (a CTA reads its 110 KB of weight fields again and again).
+// Measured on the prefill step: passes of up to 64 rows 1.084 ms when asking for 136 KB, 1.16 ms for
+// the 131 KB they need; passes of 128 rows 1.018 ms for the 195 KB they need, 1.042 ms with 1 KB more.
 __host__ __device__ constexpr uint32_t smem_bytes(uint32_t box) {
-    return B_OFF + NSTAGE_B * 2u * b_atom_bytes(box) + 1024u;
+    return box > 64u ? B_OFF + NSTAGE_B * 2u * b_atom_bytes(box) : 136u * 1024u;
 }
+static_assert(B_OFF + NSTAGE_B * 2u * b_atom_bytes(64) <= 136u * 1024u, "shared memory layout");
 static_assert(smem_bytes(NB) <= 227u * 1024u, "shared memory layout");
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -341,7 +348,10 @@ __device__ __noinline__ void store_tile(float *o, uint64_t ld, const float *rs, 
         if ((uint32_t)j < n) o[(uint64_t)j * ld] = v[j] * __ldg(rs + j);
 }
 
-template <bool TILED>
+// NSL: 16-column slabs of the accumulator per epilogue thread: 1 for passes of up to 64 rows, 2 for 128
+// (16 more running sums per thread: at 96 registers that spills a little, so the narrow passes keep
+// their own instance).
+template <bool TILED, uint32_t NSL>
 __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_constant__ CUtensorMap map_h1,
                                                   const __grid_constant__ CUtensorMap map_h2) {
     // used directly (no integer round trip), so that the compiler keeps these as
@@ -458,7 +468,6 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
         const uint32_t d_c0 = 4u * (d_g & 1u), d_x = lane & 7u;
         // epilogue: tensor-memory lanes of this warp's quadrant; of the pass's columns (activation
         // rows) the 16-column slabs e_cs and, in a pass of more than 64 rows, e_cs + 4
-        constexpr uint32_t NSL = NB / 64u;
         const uint32_t e_q = warp & 3u, e_cs = warp >> 2;
         const uint32_t e_row = 32u * e_q + lane;
         const uint32_t e_taddr = tmem + ((32u * e_q) << 16) + 16u * e_cs;
@@ -493,7 +502,7 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
 #pragma unroll
                 for (uint32_t h = 0; h < NSL; h++) {
                     if (e_live[h]) {   // warp-uniform
-                        const float dr = s.dr[sbk & 3u][e_row];
+                        const float dr = __half2float(__ushort_as_half(s.dr[sbk % 3u][e_row]));
                         uint32_t v[16], v2[16];
                         tmem_ld16(e_taddr + (sbk % NACC) * acc_cols + 64u * h, v);
                         tmem_ld16(e_taddr + (sbk % NACC) * acc_cols + 64u * h + box, v2);
@@ -552,7 +561,7 @@ __global__ void __launch_bounds__(NT, 1) mmq_tc_k(const Args a, const __grid_con
                     for (uint32_t c = 0; c < 4; c++)
                         *reinterpret_cast<uint4 *>(p + (((d_c0 + c) ^ d_x) << 4)) =
                             make_uint4(hv[4 * c], hv[4 * c + 1], hv[4 * c + 2], hv[4 * c + 3]);
-                    if (d_g == 0 && (it & 1u) == 0) s.dr[(it >> 1) & 3u][d_row] = f.d;
+                    if (d_g == 0 && (it & 1u) == 0) s.dr[(it >> 1) % 3u][d_row] = (uint16_t)fq[u].d;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
@@ -630,7 +639,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t
 static EncodeTiledFn g_encode = nullptr;
 static bool g_ready = false, g_tried = false;
 constexpr uint32_t WORK_CAP = 1u << 16;   // passes per launch: entries + rows / (rows per pass) must fit
-constexpr uint64_t PASS128_MIN_ROWS = 8192;   // calls with at least this many rows take 128 of them per pass
+#ifndef Q4B_PASS128_MIN_ROWS
+#define Q4B_PASS128_MIN_ROWS 8192
+#endif
+constexpr uint64_t PASS128_MIN_ROWS = Q4B_PASS128_MIN_ROWS;   // calls with at least this many rows take 128 of them per pass
 static uint2 *g_work = nullptr;           // two lists, used alternately, so that two launches in a
 static uint32_t *g_n_work = nullptr;      // row (gate/up, then down) never share one
 static uint32_t g_work_turn = 0;
@@ -648,9 +660,13 @@ bool warm() {
         return false;
     }
     g_encode = (EncodeTiledFn)fn;
-    if (cudaFuncSetAttribute(mmq_tc_k<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(NB)) !=
+    if (cudaFuncSetAttribute(mmq_tc_k<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(64)) !=
             cudaSuccess ||
-        cudaFuncSetAttribute(mmq_tc_k<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(NB)) !=
+        cudaFuncSetAttribute(mmq_tc_k<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(64)) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(mmq_tc_k<true, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(NB)) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(mmq_tc_k<false, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes(NB)) !=
             cudaSuccess) {
         cudaGetLastError();
         return false;
@@ -728,10 +744,18 @@ bool launch(const uint8_t *w, uint64_t expert_stride, const int32_t *act, const 
         if (n_tiles % c == 0) mt = c;
     a.mt_per_cta = mt;
     const dim3 grid(n_tiles / mt, (unsigned)max_items);
-    if (tiled)
-        mmq_tc_k<true><<<grid, NT, smem_bytes(a.box_rows), stream>>>(a, maps[0], maps[1]);
-    else
-        mmq_tc_k<false><<<grid, NT, smem_bytes(a.box_rows), stream>>>(a, maps[0], maps[1]);
+    const uint32_t smem = smem_bytes(a.box_rows);
+    if (a.box_rows > 64u) {
+        if (tiled)
+            mmq_tc_k<true, 2><<<grid, NT, smem, stream>>>(a, maps[0], maps[1]);
+        else
+            mmq_tc_k<false, 2><<<grid, NT, smem, stream>>>(a, maps[0], maps[1]);
+    } else {
+        if (tiled)
+            mmq_tc_k<true, 1><<<grid, NT, smem, stream>>>(a, maps[0], maps[1]);
+        else
+            mmq_tc_k<false, 1><<<grid, NT, smem, stream>>>(a, maps[0], maps[1]);
+    }
     return true;
 }
 
